@@ -1,0 +1,141 @@
+"""ctypes bindings for the CPU oracle and, where it was built, the reference's own launchers
+compiled for host cores.  TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and
+by bench.py's CPU-baseline leg, never by the product package."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "_build", "libattn_oracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libhipgpt_ref.so")
+
+_fp = C.POINTER(C.c_float)
+_ip = C.POINTER(C.c_int)
+
+
+def build(ref_root: str = "/root/reference") -> None:
+    """Compile the oracle and, if the reference tree is mounted, oracle/_ref."""
+    env = dict(os.environ)
+    subprocess.run(["make", "-C", _HERE, f"REF={ref_root}"], check=True, env=env,
+                   stdout=subprocess.DEVNULL)
+
+
+def _f(a):
+    if a is None:
+        return None
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_fp)
+
+
+def _i(a):
+    assert a.dtype == np.int32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_ip)
+
+
+_oracle = None
+_ref = None
+
+
+def oracle_lib():
+    global _oracle
+    if _oracle is None:
+        if not os.path.exists(ORACLE_SO):
+            build()
+        _oracle = C.CDLL(ORACLE_SO)
+    return _oracle
+
+
+def have_ref() -> bool:
+    return os.path.exists(REF_SO)
+
+
+def ref_lib():
+    global _ref
+    if _ref is None:
+        _ref = C.CDLL(REF_SO)
+    return _ref
+
+
+def num_threads() -> int:
+    return int(oracle_lib().oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    oracle_lib().oracle_set_num_threads(C.c_int(n))
+
+
+# ---- oracle -----------------------------------------------------------------------------
+def mha(qkv: np.ndarray, B: int, S: int, E: int, H: int, causal: bool = False,
+        want_probs: bool = False, path: str = "dispatch"):
+    """Attention forward on three stacked planes.  path: 'dispatch' follows the launcher's
+    rule, 'flash' / 'fallback' force one kernel's arithmetic.  Returns (out, probs|None)."""
+    qkv = np.ascontiguousarray(qkv, dtype=np.float32).reshape(3, B * S, E)
+    out = np.zeros((B * S, E), dtype=np.float32)
+    probs = np.zeros((B, H, S, S), dtype=np.float32) if want_probs else None
+    lib = oracle_lib()
+    if path == "dispatch":
+        rc = lib.oracle_mha_dispatch(_f(qkv), _f(out), _f(probs), B, S, E, H, int(causal))
+    else:
+        fn = lib.oracle_mha_flash if path == "flash" else lib.oracle_mha_fallback
+        rc = fn(_f(qkv[0]), _f(qkv[1]), _f(qkv[2]), _f(out), _f(probs), B, S, E, H, int(causal))
+    if rc < 0:
+        raise ValueError(f"oracle rejected shape B={B} S={S} E={E} H={H}")
+    return out, probs
+
+
+def sdp(Q: np.ndarray, K: np.ndarray, B: int, S: int, D: int) -> np.ndarray:
+    scores = np.zeros((B, S, S), dtype=np.float32)
+    oracle_lib().oracle_sdp(_f(Q), _f(K), _f(scores), B, S, D)
+    return scores
+
+
+def softmax(scores: np.ndarray, B: int, S: int) -> np.ndarray:
+    out = np.zeros((B, S, S), dtype=np.float32)
+    oracle_lib().oracle_softmax(_f(scores), _f(out), B, S)
+    return out
+
+
+def weighted_sum(P: np.ndarray, V: np.ndarray, B: int, S: int, D: int) -> np.ndarray:
+    out = np.zeros((B, S, D), dtype=np.float32)
+    oracle_lib().oracle_weighted_sum(_f(P), _f(V), _f(out), B, S, D)
+    return out
+
+
+def decode_row(q, kcache, vcache, B, H, D, ctx, cap) -> np.ndarray:
+    out = np.zeros((B, H * D), dtype=np.float32)
+    rc = oracle_lib().oracle_decode_row(_f(q), _f(kcache), _f(vcache), _f(out), B, H, D, ctx, cap)
+    if rc < 0:
+        raise ValueError("oracle rejected decode shape")
+    return out
+
+
+# ---- the reference's own code on host cores ---------------------------------------------
+def ref_mha(qkv: np.ndarray, B: int, S: int, E: int, H: int, unique_rows_only: bool = False):
+    """launch_multihead_attention of the reference (non-causal, always stores probs)."""
+    qkv = np.ascontiguousarray(qkv, dtype=np.float32).reshape(3, B * S, E)
+    out = np.zeros((B * S, E), dtype=np.float32)
+    probs = np.zeros((B, H, S, S), dtype=np.float32)
+    ref_lib().ref_mha(_f(qkv), _f(out), _f(probs), B, S, E, H, int(unique_rows_only))
+    return out, probs
+
+
+def ref_sdp(Q, K, B, S, D):
+    scores = np.zeros((B, S, S), dtype=np.float32)
+    ref_lib().ref_sdp(_f(Q), _f(K), _f(scores), B, S, D)
+    return scores
+
+
+def ref_softmax(scores, B, S):
+    out = np.zeros((B, S, S), dtype=np.float32)
+    ref_lib().ref_softmax(_f(scores), _f(out), B, S)
+    return out
+
+
+def ref_weighted_sum(P, V, B, S, D):
+    out = np.zeros((B, S, D), dtype=np.float32)
+    ref_lib().ref_weighted_sum(_f(P), _f(V), _f(out), B, S, D)
+    return out
