@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the causal multi-head-attention forward path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c3|c5] [--causal 0|1] [--probs 0|1] [--gather 0|1]
+
+One JSON line on stdout (rank 0).  A *step* is one pass of the attention forward over SETS
+different input batches of the workload's shape, one kernel launch per batch; the SETS batches
+together are larger than the 126 MB L2, so no launch finds its inputs cached by the one before.
+Default workload: B=32 H=8 S=256 head_dim=32, fp32, causal, probabilities not stored.
+
+  value     algorithmic TFLOP/s (2*B*H*D*S*(S+1) per causal batch), inputs resident in HBM,
+            CUDA events around the K timed steps, max over ranks
+  e2e       the same metric through the host-buffer C-ABI call (pinned host memory in, host
+            memory out), copies inside the timed region
+  roofline  the attention kernel against the fp32 FMA-pipe ceiling measured in the same run
+  cpu_baseline  the CPU oracle (a port of the reference arithmetic) on this box's host cores
+
+With N > 1 (torchrun, one rank per GPU) every rank runs the same step on its own batches
+(batch-major shards of an N-times larger batch; no kernel reads another GPU's memory), and
+--gather 1 adds an NCCL all-gather of the outputs.  `--impl reference` times the reference
+arithmetic on the host cores instead (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from hipgpt_b200 import synth  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+
+
+def flops_of(B, H, S, D, causal):
+    return 2.0 * B * H * D * S * (S + 1) if causal else 4.0 * B * H * float(S) * S * D
+
+
+def bytes_of(B, H, S, D, probs):
+    return 4.0 * B * S * H * D * 4 + (4.0 * B * H * S * S if probs else 0.0)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--causal", type=int, default=1)
+    ap.add_argument("--probs", type=int, default=0)
+    ap.add_argument("--gather", type=int, default=0)
+    ap.add_argument("--sets", type=int, default=0, help="input batches per step (0: enough to exceed L2)")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline leg")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------- clocks ----
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int, period: float = 0.02):
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
+        return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------- CPU legs ----
+def cpu_leg(cfg, causal, seconds, steps=None, warmup=0):
+    """Times the CPU oracle (port of src/hip_kernels.cpp:263-402 with the causal switch) with all
+    host threads on a bounded sample: whole batch items of the workload, as many as fit the
+    time budget.  Returns (tflops, info dict)."""
+    from oracle import bindings as ob
+    B, H, S, D = cfg["B"], cfg["H"], cfg["S"], cfg["D"]
+    E = H * D
+    threads = ob.num_threads()
+    one = synth.qkv_planes(cfg["seed"], 1, S, E, cfg["scale"])
+    t0 = time.perf_counter()
+    ob.mha(one, 1, S, E, H, causal=bool(causal))
+    t_item = max(time.perf_counter() - t0, 1e-6)
+    n_steps = steps if steps is not None else 3
+    items = int(max(1, min(B, seconds / ((n_steps + warmup) * t_item))))
+    qkv = np.ascontiguousarray(np.concatenate([one] * items, axis=1)) if items > 1 else one
+    for _ in range(warmup):
+        ob.mha(qkv, items, S, E, H, causal=bool(causal))
+    times = []
+    for _ in range(n_steps):
+        t0 = time.perf_counter()
+        ob.mha(qkv, items, S, E, H, causal=bool(causal))
+        times.append(time.perf_counter() - t0)
+    t = float(np.mean(times))
+    tf = flops_of(items, H, S, D, causal) / t / 1e12
+    info = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"{items} of {B} batch items (all {H} heads, S={S}, D={D}, causal={int(bool(causal))}) per step, "
+                      f"{n_steps} steps, mean {t * 1e3:.1f} ms/step",
+            "ms_per_step": t * 1e3}
+    if ob.have_ref() and S <= 1024:
+        # the reference's own launcher on host cores (never causal, always stores probabilities);
+        # block rows that repeat the same query are skipped, which changes no result
+        ob.ref_lib().ref_set_num_threads(threads)
+        t0 = time.perf_counter()
+        ob.ref_mha(one, 1, S, E, H, unique_rows_only=True)
+        tr = time.perf_counter() - t0
+        info["reference_build_noncausal"] = {"tflops": flops_of(1, H, S, D, False) / tr / 1e12,
+                                             "sample": "1 batch item, launch_multihead_attention compiled for the host"}
+    return tf, info
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = synth.CONFIGS[args.workload]
+    tf, info = cpu_leg(cfg, args.causal, seconds=90.0, steps=max(args.steps, 1), warmup=args.warmup)
+    line = {"impl": "reference", "metric": "causal_attn_fwd_tflops", "value": tf, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": info["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, cfg, 1),
+            "cpu_baseline": info,
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, cfg, sets):
+    return {"workload": f"{args.workload}: causal MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} fp32"
+                        if args.causal else f"{args.workload}: full MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} fp32",
+            "B": cfg["B"], "H": cfg["H"], "S": cfg["S"], "head_dim": cfg["D"], "causal": int(args.causal),
+            "probs_stored": int(args.probs), "batches_per_step": sets,
+            "l2": f"{sets} distinct input batches per step, {sets * bytes_of(cfg['B'], cfg['H'], cfg['S'], cfg['D'], args.probs) / 1e6:.0f} MB > 126 MB L2",
+            "parallelism": f"batch-major shards x{args.gpus}" + (", NCCL all-gather of outputs" if args.gather else ", no collective")}
+
+
+# ----------------------------------------------------------------------------- GPU arm ----
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from hipgpt_b200 import _capi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = _capi.lib()
+    cfg = synth.CONFIGS[args.workload]
+    B, H, S, D = cfg["B"], cfg["H"], cfg["S"], cfg["D"]
+    E = H * D
+    per_batch_bytes = bytes_of(B, H, S, D, args.probs)
+    sets = args.sets or max(1, int(np.ceil(1.5 * L2_BYTES / per_batch_bytes)))
+    plane = B * S * E
+
+    # inputs: `sets` different batches per rank, resident in HBM before the timed region
+    h_in = torch.empty((sets, 3, B * S, E), dtype=torch.float32).pin_memory()
+    gen = min(sets, 2)                                    # two seeded batches, the rest are rolls of them
+    for s in range(gen):
+        h_in[s] = torch.from_numpy(synth.qkv_planes(cfg["seed"] + 100 * rank + s, B, S, E, cfg["scale"]))
+    for s in range(gen, sets):
+        h_in[s] = torch.roll(h_in[s % gen], shifts=s, dims=1)   # other token order: other data, same distribution
+    d_in = h_in.cuda(non_blocking=True)
+    d_out = torch.empty((sets, B * S, E), dtype=torch.float32, device="cuda")
+    d_probs = torch.empty((B, H, S, S), dtype=torch.float32, device="cuda") if args.probs else None
+    gathered = torch.empty((world, sets, B * S, E), dtype=torch.float32, device="cuda") if (args.gather and world > 1) else None
+    stream = torch.cuda.current_stream()
+    st = stream.cuda_stream
+
+    in_ptrs = [d_in[s].data_ptr() for s in range(sets)]
+    out_ptrs = [d_out[s].data_ptr() for s in range(sets)]
+    probs_ptr = d_probs.data_ptr() if args.probs else None
+    fwd = lib.hipgpt_mha_forward
+
+    def step():
+        for s in range(sets):
+            base = in_ptrs[s]
+            rc = fwd(base, base + 4 * plane, base + 8 * plane, out_ptrs[s], probs_ptr, B, S, E, H, args.causal, st)
+            if rc:
+                _capi.check(rc)
+        if gathered is not None:
+            dist.all_gather_into_tensor(gathered.view(-1), d_out.view(-1))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    with ClockSampler(local) as clocks:
+        ms = timed(step, args.steps)
+    ms_per_step = ms / args.steps
+    flops_step = flops_of(B, H, S, D, args.causal) * sets
+    value = world * flops_step / (ms_per_step * 1e-3) / 1e12
+
+    # roofline of the attention kernel: FMA-pipe ceiling measured now, on this GPU, at these clocks
+    sink = torch.zeros(1, device="cuda")
+    import ctypes as C
+    fl = C.c_double()
+    blocks, iters = 148 * 8, 4096
+    for _ in range(3):
+        _capi.check(lib.hipgpt_probe_fma(sink.data_ptr(), blocks, iters, C.byref(fl), st))
+    probe_ms = timed(lambda: _capi.check(lib.hipgpt_probe_fma(sink.data_ptr(), blocks, iters, C.byref(fl), st)), 20) / 20
+    fma_peak = fl.value / (probe_ms * 1e-3) / 1e12
+    launch_ms = ms_per_step / sets                        # one launch per batch, back to back
+    achieved = flops_of(B, H, S, D, args.causal) / (launch_ms * 1e-3) / 1e12
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
+    hbm_achieved = per_batch_bytes / (launch_ms * 1e-3) / 1e9
+    roofline = {"bound": "fma", "kernel": "mha_rows_kernel", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s",
+                "frac": achieved / fma_peak, "traffic": None,
+                "peak_source": "fp32 FFMA loop timed in this run (the measured-peaks file has no fp32 figure)",
+                "us_per_launch": launch_ms * 1e3,
+                "hbm": {"achieved": hbm_achieved, "peak": hbm_peak, "unit": "GB/s", "frac": hbm_achieved / hbm_peak,
+                        "peak_source": "measured" if peaks else "fallback"}}
+
+    line = {"metric": "causal_attn_fwd_tflops" if args.causal else "attn_fwd_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, cfg, sets), "clocks": clocks.summary(), "roofline": roofline,
+            "gpu_launches": args.steps * sets}
+
+    # end to end through the host-buffer entry point: pinned host memory in, host memory out
+    if not args.no_e2e:
+        h_out = torch.empty((B * S, E), dtype=torch.float32).pin_memory()
+        h_probs = torch.empty((B, H, S, S), dtype=torch.float32).pin_memory() if args.probs else None
+        e2e_steps = max(1, min(args.steps, 20))
+
+        def e2e_step():
+            for s in range(sets):
+                rc = lib.hipgpt_mha_forward_host(h_in[s].data_ptr(), h_out.data_ptr(),
+                                                 h_probs.data_ptr() if args.probs else None, B, S, E, H, args.causal)
+                if rc:
+                    _capi.check(rc)
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        line["e2e"] = {"value": world * flops_step * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
+                       "h2d_bytes_per_step": int(sets * 3 * plane * 4),
+                       "d2h_bytes_per_step": int(sets * (plane * 4 + (B * H * S * S * 4 if args.probs else 0))),
+                       "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps,
+                       "api": "hipgpt_mha_forward_host (C ABI, host pointers)"}
+        lib.hipgpt_release_workspace()
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        _, info = cpu_leg(cfg, args.causal, seconds=args.cpu_seconds)
+        line["cpu_baseline"] = info
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,73 @@
+"""ctypes view of libhipgpt_attn.so (the C ABI declared in include/hipgpt_attn.h).
+
+There is no fallback: if the library is missing and cannot be built, or a call fails, an
+exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+OK = 0
+ERR_BAD_ARG, ERR_NULL, ERR_UNSUPPORTED, ERR_CUDA, ERR_SCRATCH = -1, -2, -3, -4, -5
+ALGO_AUTO, ALGO_GENERIC, ALGO_ROWS = 0, 1, 2
+
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+
+# name -> (restype, argtypes); one entry per declaration in include/hipgpt_attn.h
+SIGNATURES = {
+    "hipgpt_mha_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_mha_forward_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_mha_forward_planes": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_mha_forward_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i]),
+    "hipgpt_release_workspace": (None, []),
+    "hipgpt_scaled_dot_product": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hipgpt_softmax": (_i, [_vp, _vp, _i, _i, _vp]),
+    "hipgpt_attention_weighted_sum": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hipgpt_mha_decode_scratch_bytes": (_sz, [_i, _i, _i, _i]),
+    "hipgpt_mha_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_shard_range": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "hipgpt_probe_fma": (_i, [_vp, _i, _i, C.POINTER(C.c_double), _vp]),
+    "hipgpt_last_error": (C.c_char_p, []),
+    "hipgpt_version": (_i, []),
+}
+# the reference-named C++ launchers (include/hipgpt_launchers.hpp), by mangled name
+CXX_LAUNCHERS = {
+    "launch_multihead_attention": "_Z26launch_multihead_attentionPKfPfS1_iiii",
+    "launch_scaled_dot_product": "_Z25launch_scaled_dot_productPKfS0_Pfiii",
+    "launch_softmax": "_Z14launch_softmaxPKfPfii",
+    "launch_attention_weighted_sum": "_Z29launch_attention_weighted_sumPKfS0_Pfiii",
+}
+
+_lib = None
+
+
+class HipGPTError(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"hipgpt error {code}: {text}")
+        self.code = code
+
+
+def lib_path() -> str:
+    return _build.LIB
+
+
+def lib() -> C.CDLL:
+    """Loads the library, building it first if the .so is absent (needs nvcc)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_build.LIB):
+            _build.build()
+        handle = C.CDLL(_build.LIB)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        raise HipGPTError(rc, lib().hipgpt_last_error().decode("utf-8", "replace"))

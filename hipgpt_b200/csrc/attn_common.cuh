@@ -1,0 +1,49 @@
+// Shared device helpers and the error channel of the attention library (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "hipgpt_attn.h"
+
+namespace hipgpt {
+
+// Records the calling thread's failure text and returns `code` (host side, capi.cu).
+int fail(int code, const char *fmt, ...);
+// Checks the launch that was just enqueued; HIPGPT_OK or HIPGPT_ERR_CUDA.
+int check_launch(const char *what);
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// 16-byte asynchronous global -> shared copy; `valid == false` writes zeros and reads nothing.
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src, bool valid)
+{
+    const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Kernel launch wrappers (one per .cu file), all returning an HIPGPT_* status.
+int launch_mha_rows(const float *q, const float *k, const float *v, float *out, float *probs,
+                    int B, int S, int E, int H, int causal, int warps, cudaStream_t st);
+bool mha_rows_supports(int D);
+int launch_mha_generic(const float *q, const float *k, const float *v, float *out, float *probs,
+                       int B, int S, int E, int H, int causal, cudaStream_t st);
+int launch_sdp(const float *Q, const float *K, float *scores, int B, int S, int D, cudaStream_t st);
+int launch_softmax_rows(const float *scores, float *out, int B, int S, cudaStream_t st);
+int launch_weighted_sum(const float *P, const float *V, float *out, int B, int S, int D, cudaStream_t st);
+int launch_decode(const float *q, const float *kc, const float *vc, float *out, float *scratch,
+                  int B, int H, int D, int ctx, int cap, int nsplit, cudaStream_t st);
+int decode_splits(int B, int H, int D, int ctx);
+
+}  // namespace hipgpt

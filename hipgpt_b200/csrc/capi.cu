@@ -1,0 +1,232 @@
+// C ABI of the attention library: argument checks, dispatch, the host-buffer call and the
+// per-thread error text.  Declarations and the reference interfaces they replace are in
+// include/hipgpt_attn.h.
+#include "attn_common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+namespace hipgpt {
+
+namespace {
+thread_local char g_err[512] = "";
+}
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char *what)
+{
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return HIPGPT_OK;
+}
+
+namespace {
+
+int check_mha_args(const void *q, const void *k, const void *v, const void *out, int B, int S, int E, int H)
+{
+    if (H <= 0 || E <= 0 || (E % H) != 0) return fail(HIPGPT_ERR_BAD_ARG, "Bad MHA config: E=%d H=%d", E, H);
+    if (B < 0 || S < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: B=%d S=%d", B, S);
+    if (B == 0 || S == 0) return 1;   // nothing to do
+    if (!q || !k || !v || !out) return fail(HIPGPT_ERR_NULL, "q, k, v and out must not be NULL");
+    return HIPGPT_OK;
+}
+
+int mha_dispatch(const float *q, const float *k, const float *v, float *out, float *probs,
+                 int B, int S, int E, int H, int causal, int algo, int warps, cudaStream_t st)
+{
+    const int rc = check_mha_args(q, k, v, out, B, S, E, H);
+    if (rc != HIPGPT_OK) return rc > 0 ? HIPGPT_OK : rc;
+    const int D = E / H;
+    // The rows kernel moves 16 bytes at a time: every row start must be 16-byte aligned.
+    const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                         (probs == nullptr || (reinterpret_cast<uintptr_t>(probs) & 15) == 0);
+    switch (algo) {
+    case HIPGPT_ALGO_AUTO:
+        if (mha_rows_supports(D) && aligned) return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
+        return launch_mha_generic(q, k, v, out, probs, B, S, E, H, causal, st);
+    case HIPGPT_ALGO_GENERIC:
+        return launch_mha_generic(q, k, v, out, probs, B, S, E, H, causal, st);
+    case HIPGPT_ALGO_ROWS:
+        if (!aligned) return fail(HIPGPT_ERR_BAD_ARG, "rows kernel needs 16-byte aligned pointers");
+        return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
+    default:
+        return fail(HIPGPT_ERR_BAD_ARG, "unknown algo %d", algo);
+    }
+}
+
+// Device workspace of the host-buffer call: grows to the largest request, one per process.
+struct Workspace {
+    std::mutex mu;
+    float *dev = nullptr;
+    size_t bytes = 0;
+    cudaStream_t stream = nullptr;
+    int device = -1;
+};
+Workspace g_ws;
+
+}  // namespace
+}  // namespace hipgpt
+
+using namespace hipgpt;
+
+extern "C" {
+
+int hipgpt_mha_forward(const float *d_q, const float *d_k, const float *d_v, float *d_out, float *d_probs,
+                       int B, int S, int E, int H, int causal, void *stream)
+{
+    return mha_dispatch(d_q, d_k, d_v, d_out, d_probs, B, S, E, H, causal, HIPGPT_ALGO_AUTO, 0,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int hipgpt_mha_forward_ex(const float *d_q, const float *d_k, const float *d_v, float *d_out, float *d_probs,
+                          int B, int S, int E, int H, int causal, int algo, int warps, void *stream)
+{
+    return mha_dispatch(d_q, d_k, d_v, d_out, d_probs, B, S, E, H, causal, algo, warps,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int hipgpt_mha_forward_planes(const float *d_qkv, float *d_out, float *d_probs,
+                              int B, int S, int E, int H, int causal, void *stream)
+{
+    if (B < 0 || S < 0 || E < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: B=%d S=%d E=%d", B, S, E);
+    const size_t plane = (size_t)B * S * E;
+    const float *k = d_qkv ? d_qkv + plane : nullptr;
+    const float *v = d_qkv ? d_qkv + 2 * plane : nullptr;
+    return mha_dispatch(d_qkv, k, v, d_out, d_probs, B, S, E, H, causal, HIPGPT_ALGO_AUTO, 0,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
+                            int B, int S, int E, int H, int causal)
+{
+    const int rc = check_mha_args(h_qkv, h_qkv, h_qkv, h_out, B, S, E, H);
+    if (rc != HIPGPT_OK) return rc > 0 ? HIPGPT_OK : rc;
+    const size_t plane = (size_t)B * S * E;
+    const size_t nprobs = h_probs ? (size_t)B * H * S * S : 0;
+    const size_t need = (4 * plane + nprobs) * sizeof(float);
+    std::lock_guard<std::mutex> lock(g_ws.mu);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (g_ws.device != dev || g_ws.bytes < need) {
+        if (g_ws.dev) cudaFree(g_ws.dev);
+        g_ws.dev = nullptr;
+        g_ws.bytes = 0;
+        if (g_ws.stream && g_ws.device != dev) { cudaStreamDestroy(g_ws.stream); g_ws.stream = nullptr; }
+        e = cudaMalloc(&g_ws.dev, need);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMalloc(%zu): %s", need, cudaGetErrorString(e));
+        g_ws.bytes = need;
+        g_ws.device = dev;
+    }
+    if (!g_ws.stream) {
+        e = cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+    }
+    float *d_qkv = g_ws.dev, *d_out = g_ws.dev + 3 * plane, *d_probs = h_probs ? g_ws.dev + 4 * plane : nullptr;
+    e = cudaMemcpyAsync(d_qkv, h_qkv, 3 * plane * sizeof(float), cudaMemcpyHostToDevice, g_ws.stream);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to device: %s", cudaGetErrorString(e));
+    const int krc = mha_dispatch(d_qkv, d_qkv + plane, d_qkv + 2 * plane, d_out, d_probs, B, S, E, H, causal,
+                                 HIPGPT_ALGO_AUTO, 0, g_ws.stream);
+    if (krc != HIPGPT_OK) return krc;
+    e = cudaMemcpyAsync(h_out, d_out, plane * sizeof(float), cudaMemcpyDeviceToHost, g_ws.stream);
+    if (e == cudaSuccess && h_probs)
+        e = cudaMemcpyAsync(h_probs, d_probs, nprobs * sizeof(float), cudaMemcpyDeviceToHost, g_ws.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g_ws.stream);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to host: %s", cudaGetErrorString(e));
+    return HIPGPT_OK;
+}
+
+void hipgpt_release_workspace(void)
+{
+    std::lock_guard<std::mutex> lock(g_ws.mu);
+    if (g_ws.dev) cudaFree(g_ws.dev);
+    if (g_ws.stream) cudaStreamDestroy(g_ws.stream);
+    g_ws.dev = nullptr;
+    g_ws.stream = nullptr;
+    g_ws.bytes = 0;
+    g_ws.device = -1;
+}
+
+int hipgpt_scaled_dot_product(const float *d_Q, const float *d_K, float *d_scores, int B, int S, int D, void *stream)
+{
+    if (B < 0 || S < 0 || D <= 0) return fail(HIPGPT_ERR_BAD_ARG, "bad size: B=%d S=%d D=%d", B, S, D);
+    if (B == 0 || S == 0) return HIPGPT_OK;
+    if (!d_Q || !d_K || !d_scores) return fail(HIPGPT_ERR_NULL, "Q, K and scores must not be NULL");
+    return launch_sdp(d_Q, d_K, d_scores, B, S, D, static_cast<cudaStream_t>(stream));
+}
+
+int hipgpt_softmax(const float *d_scores, float *d_softmax_out, int B, int S, void *stream)
+{
+    if (B < 0 || S < 0) return fail(HIPGPT_ERR_BAD_ARG, "bad size: B=%d S=%d", B, S);
+    if (B == 0 || S == 0) return HIPGPT_OK;
+    if (!d_scores || !d_softmax_out) return fail(HIPGPT_ERR_NULL, "scores and softmax_out must not be NULL");
+    return launch_softmax_rows(d_scores, d_softmax_out, B, S, static_cast<cudaStream_t>(stream));
+}
+
+int hipgpt_attention_weighted_sum(const float *d_softmax, const float *d_V, float *d_output,
+                                  int B, int S, int D, void *stream)
+{
+    if (B < 0 || S < 0 || D <= 0) return fail(HIPGPT_ERR_BAD_ARG, "bad size: B=%d S=%d D=%d", B, S, D);
+    if (B == 0 || S == 0) return HIPGPT_OK;
+    if (!d_softmax || !d_V || !d_output) return fail(HIPGPT_ERR_NULL, "softmax, V and output must not be NULL");
+    return launch_weighted_sum(d_softmax, d_V, d_output, B, S, D, static_cast<cudaStream_t>(stream));
+}
+
+size_t hipgpt_mha_decode_scratch_bytes(int B, int H, int D, int ctx)
+{
+    if (B <= 0 || H <= 0 || D <= 0 || ctx <= 0) return 0;
+    const int ns = decode_splits(B, H, D, ctx);
+    if (ns <= 1) return 0;
+    const size_t stride = (size_t)((D + 3) / 4) * 4 + 4;
+    return (size_t)B * H * ns * stride * sizeof(float);
+}
+
+int hipgpt_mha_decode(const float *d_q, const float *d_kcache, const float *d_vcache, float *d_out,
+                      float *d_scratch, size_t scratch_bytes,
+                      int B, int H, int D, int ctx, int cap, void *stream)
+{
+    if (B < 0 || H <= 0 || D <= 0 || ctx < 0 || cap < ctx)
+        return fail(HIPGPT_ERR_BAD_ARG, "bad size: B=%d H=%d D=%d ctx=%d cap=%d", B, H, D, ctx, cap);
+    if (B == 0) return HIPGPT_OK;
+    if (!d_q || !d_out || (ctx > 0 && (!d_kcache || !d_vcache)))
+        return fail(HIPGPT_ERR_NULL, "q, out and the caches must not be NULL");
+    const size_t need = hipgpt_mha_decode_scratch_bytes(B, H, D, ctx);
+    if (need > 0 && (!d_scratch || scratch_bytes < need))
+        return fail(HIPGPT_ERR_SCRATCH, "scratch of %zu bytes needed, %zu given", need, d_scratch ? scratch_bytes : (size_t)0);
+    if (D % 4 == 0 && ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_kcache) |
+                        reinterpret_cast<uintptr_t>(d_vcache) | reinterpret_cast<uintptr_t>(d_out) |
+                        reinterpret_cast<uintptr_t>(d_scratch)) & 15) != 0)
+        return fail(HIPGPT_ERR_BAD_ARG, "decode needs 16-byte aligned pointers");
+    const int ns = need > 0 ? decode_splits(B, H, D, ctx) : 1;
+    return launch_decode(d_q, d_kcache, d_vcache, d_out, d_scratch, B, H, D, ctx, cap, ns, static_cast<cudaStream_t>(stream));
+}
+
+int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end)
+{
+    if (B < 0 || world <= 0 || rank < 0 || rank >= world)
+        return fail(HIPGPT_ERR_BAD_ARG, "bad shard request: B=%d world=%d rank=%d", B, world, rank);
+    if (!b_begin || !b_end) return fail(HIPGPT_ERR_NULL, "b_begin and b_end must not be NULL");
+    // the first B % world ranks take one batch more
+    const int base = B / world, extra = B % world;
+    *b_begin = rank * base + (rank < extra ? rank : extra);
+    *b_end = *b_begin + base + (rank < extra ? 1 : 0);
+    return HIPGPT_OK;
+}
+
+const char *hipgpt_last_error(void) { return g_err; }
+
+int hipgpt_version(void) { return 100; }
+
+}  // extern "C"

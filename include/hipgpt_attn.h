@@ -1,0 +1,142 @@
+/*
+ * hipgpt_attn.h — C ABI of the B200 (sm_100a) attention-forward library.
+ *
+ * The library replaces the attention group of HipGPT's kernel API
+ * (include/hip_kernels.h:38-46 there) with hand-written CUDA kernels.  Two layers:
+ *
+ *   1. the C entry points below: plain pointers and sizes, an explicit stream, an int status;
+ *   2. include/hipgpt_launchers.hpp: C++ functions with the reference's exact names and
+ *      signatures (launch_multihead_attention, ...) that forward here, so that HipGPT's
+ *      TransformerLayer / GPTModel objects link against this library unchanged.
+ *
+ * Conventions shared by every entry point
+ *   - pointers named d_* are DEVICE pointers, h_* are HOST pointers; the caller owns them all;
+ *   - nothing is allocated, kept or freed by the device-pointer entry points;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream, which is
+ *     what the reference's hipLaunchKernelGGL(..., 0, 0, ...) calls use); calls are
+ *     asynchronous with respect to the host;
+ *   - the return value is HIPGPT_OK or a negative HIPGPT_ERR_* code; hipgpt_last_error()
+ *     then describes the failure for the calling thread.  Nothing aborts here; the
+ *     reference-named wrappers reproduce the reference's abort on a bad head configuration;
+ *   - all arithmetic is fp32; offsets are 64-bit, so planes and probability tensors beyond
+ *     2^31 elements are addressed correctly.
+ */
+#ifndef HIPGPT_ATTN_H
+#define HIPGPT_ATTN_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The library is built with hidden visibility; these are its exports. */
+#if defined(__GNUC__)
+#define HIPGPT_API __attribute__((visibility("default")))
+#else
+#define HIPGPT_API
+#endif
+
+#define HIPGPT_OK               0
+#define HIPGPT_ERR_BAD_ARG     (-1)   /* a size is negative, H <= 0, E % H != 0, ctx > cap ...   */
+#define HIPGPT_ERR_NULL        (-2)   /* a required pointer is NULL                              */
+#define HIPGPT_ERR_UNSUPPORTED (-3)   /* head_dim beyond what the kernels hold in registers      */
+#define HIPGPT_ERR_CUDA        (-4)   /* the CUDA runtime reported an error (text in last_error) */
+#define HIPGPT_ERR_SCRATCH     (-5)   /* scratch buffer missing or smaller than required         */
+
+/* Kernel selector of hipgpt_mha_forward_ex (profiling and tests; 0 is what every other
+ * entry point uses). */
+#define HIPGPT_ALGO_AUTO     0   /* rows kernel for head_dim 32/64/128, generic kernel otherwise   */
+#define HIPGPT_ALGO_GENERIC  1   /* one warp per query row, any head_dim <= 512                    */
+#define HIPGPT_ALGO_ROWS     2   /* register-resident query rows, shared-memory K/V tiles          */
+
+/*
+ * Fused multi-head attention forward:  out = softmax(Q K^T / sqrt(D)) V  per (batch, head).
+ * Replaces launch_multihead_attention's two kernels (src/hip_kernels.cpp:263-325 and
+ * :329-402, dispatch :404-451).
+ *   d_q, d_k, d_v  [B*S][E] fp32; head h of token t at t*E + h*D, D = E/H
+ *   d_out          [B*S][E], same indexing, fully overwritten
+ *   d_probs        [B][H][S][S] normalised probabilities, fully overwritten, or NULL to skip
+ *   causal         0 = the reference's semantics (every query sees all S keys);
+ *                  1 = extension: query i sees keys j <= i; stored probabilities above the
+ *                      diagonal are 0
+ */
+HIPGPT_API int hipgpt_mha_forward(const float *d_q, const float *d_k, const float *d_v,
+                       float *d_out, float *d_probs,
+                       int B, int S, int E, int H, int causal, void *stream);
+
+/* The same with an explicit kernel selector (HIPGPT_ALGO_*) and, for HIPGPT_ALGO_ROWS,
+ * the number of warps per thread block (0 = default). */
+HIPGPT_API int hipgpt_mha_forward_ex(const float *d_q, const float *d_k, const float *d_v,
+                          float *d_out, float *d_probs,
+                          int B, int S, int E, int H, int causal,
+                          int algo, int warps, void *stream);
+
+/* The launcher's own view of its input: d_qkv holds three stacked [B*S][E] planes, Q then K
+ * then V (src/hip_kernels.cpp:415-417). */
+HIPGPT_API int hipgpt_mha_forward_planes(const float *d_qkv, float *d_out, float *d_probs,
+                              int B, int S, int E, int H, int causal, void *stream);
+
+/* The same call for HOST buffers: copies the planes to the device, runs the kernel, copies
+ * the output (and the probabilities when h_probs is not NULL) back and waits.  The device
+ * workspace is owned by the library, grows to the largest call and is released by
+ * hipgpt_release_workspace().  Pinned host memory makes the copies asynchronous. */
+HIPGPT_API int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
+                            int B, int S, int E, int H, int causal);
+HIPGPT_API void hipgpt_release_workspace(void);
+
+/*
+ * The unfused chain, head-contiguous layout: Q, K, V, out are [B'][S][D] (the caller folds
+ * heads into B'), scores / probabilities are [B'][S][S].
+ *   hipgpt_scaled_dot_product       replaces launch_scaled_dot_product      (src/hip_kernels.cpp:455-473)
+ *   hipgpt_softmax                  replaces launch_softmax                 (src/hip_kernels.cpp:478-511)
+ *   hipgpt_attention_weighted_sum   replaces launch_attention_weighted_sum  (src/hip_kernels.cpp:514-532)
+ * The two contractions keep the reference's summation order (one accumulator, ascending
+ * index, fused multiply-add), so they are equal bit for bit to that arithmetic.
+ */
+HIPGPT_API int hipgpt_scaled_dot_product(const float *d_Q, const float *d_K, float *d_scores,
+                              int B, int S, int D, void *stream);
+HIPGPT_API int hipgpt_softmax(const float *d_scores, float *d_softmax_out, int B, int S, void *stream);
+HIPGPT_API int hipgpt_attention_weighted_sum(const float *d_softmax, const float *d_V, float *d_output,
+                                  int B, int S, int D, void *stream);
+
+/*
+ * Single-query-row attention over a key/value cache, split over the context (extension; the
+ * reference's generation loop, src/gpt_model.cpp:261-280, re-runs the whole window instead).
+ *   d_q, d_out       [B][E]          the new token's query / the attention output
+ *   d_kcache/vcache  [B][cap][E]     head h of position j at (b*cap + j)*E + h*D
+ *   ctx              positions 0..ctx-1 are attended (ctx <= cap)
+ *   d_scratch        hipgpt_mha_decode_scratch_bytes(B, H, D, ctx) bytes of device memory for
+ *                    the per-split partial results (may be NULL when that size is 0)
+ */
+HIPGPT_API size_t hipgpt_mha_decode_scratch_bytes(int B, int H, int D, int ctx);
+HIPGPT_API int hipgpt_mha_decode(const float *d_q, const float *d_kcache, const float *d_vcache, float *d_out,
+                      float *d_scratch, size_t scratch_bytes,
+                      int B, int H, int D, int ctx, int cap, void *stream);
+
+/*
+ * Batch-major sharding of the (batch x head) space over the GPUs of one box: rank r of
+ * `world` owns batches [*b_begin, *b_end), a contiguous slab of every [B*S][E] plane and of
+ * the output.  Every (batch, head) pair is independent (src/hip_kernels.cpp:269-277), so the
+ * kernels exchange nothing; the outputs are all-gathered afterwards by the caller.
+ */
+HIPGPT_API int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end);
+
+/*
+ * Measurement helper (no counterpart in the reference): enqueues a register-resident fp32
+ * FMA loop on `blocks` thread blocks of 256 threads and stores in *flops the floating-point
+ * operations it performs.  Timed with CUDA events by the caller it gives the FMA-pipe ceiling
+ * that the exact-fp32 kernels are measured against.  d_sink: one float of device memory.
+ */
+HIPGPT_API int hipgpt_probe_fma(float *d_sink, int blocks, int iters, double *flops, void *stream);
+
+/* Text of the calling thread's most recent failure ("" if none). */
+HIPGPT_API const char *hipgpt_last_error(void);
+
+/* 10000*major + 100*minor + patch of this library. */
+HIPGPT_API int hipgpt_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HIPGPT_ATTN_H */

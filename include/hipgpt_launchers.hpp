@@ -1,0 +1,31 @@
+// hipgpt_launchers.hpp — the attention group of HipGPT's kernel API, with the reference's
+// exact names and signatures (include/hip_kernels.h:39-46 in the HipGPT tree), defined by this
+// library.  C++ linkage on purpose: HipGPT's TransformerLayer and GPTModel objects refer to
+// the mangled names, so linking them against libhipgpt_attn.so in place of the reference's
+// hip_kernels.o needs no source change.
+//
+// Behaviour kept from the reference: all pointers are device pointers owned by the caller;
+// the call is asynchronous on the legacy default stream (the reference launches with stream
+// 0); nothing is returned; a head configuration with H <= 0 or E % H != 0 prints
+// "Bad MHA config: E=.. H=.." to stderr and aborts (src/hip_kernels.cpp:410-413).
+// Behaviour added: d_attn_probs may be nullptr on every path (the probabilities are then not
+// written); any other failure prints the library's error text to stderr and aborts, where the
+// reference would have continued silently.
+#pragma once
+
+#if defined(__GNUC__)
+#define HIPGPT_LAUNCHER_API __attribute__((visibility("default")))
+#else
+#define HIPGPT_LAUNCHER_API
+#endif
+
+// softmax(Q K^T / sqrt(E/H)) V for every (batch, head); NOT causal, like the reference.
+// d_qkv: three stacked [B*S][E] planes; d_output [B*S][E]; d_attn_probs [B][H][S][S] or nullptr.
+HIPGPT_LAUNCHER_API void launch_multihead_attention(const float* d_qkv, float* d_output, float* d_attn_probs,
+                                int B, int S, int E, int H);
+// scores[t][j] = (Q[t] . K[batch(t)][j]) / sqrt(D) on [B][S][D] tensors (B counts batch*heads).
+HIPGPT_LAUNCHER_API void launch_scaled_dot_product(const float* Q, const float* K, float* scores, int B, int S, int D);
+// Row softmax over the last dimension of [B*S][S].
+HIPGPT_LAUNCHER_API void launch_softmax(const float* scores, float* softmax_out, int B, int S);
+// output[t][d] = sum_j softmax[t][j] * V[batch(t)][j][d].
+HIPGPT_LAUNCHER_API void launch_attention_weighted_sum(const float* softmax, const float* V, float* output, int B, int S, int D);

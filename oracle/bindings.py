@@ -10,7 +10,8 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-ORACLE_SO = os.path.join(_HERE, "_build", "libattn_oracle.so")
+ORACLE_SO = os.path.join(_HERE, "_build", "libattn_oracle.so")          # pinned: equal to the reference build
+ORACLE_FMA_SO = os.path.join(_HERE, "_build", "libattn_oracle_fma.so")  # multiply-accumulates as fmaf, like a GPU
 REF_SO = os.path.join(_HERE, "_ref", "libhipgpt_ref.so")
 
 _fp = C.POINTER(C.c_float)
@@ -36,17 +37,17 @@ def _i(a):
     return a.ctypes.data_as(_ip)
 
 
-_oracle = None
+_oracle = {}
 _ref = None
 
 
-def oracle_lib():
-    global _oracle
-    if _oracle is None:
-        if not os.path.exists(ORACLE_SO):
+def oracle_lib(fma: bool = False):
+    path = ORACLE_FMA_SO if fma else ORACLE_SO
+    if path not in _oracle:
+        if not os.path.exists(path):
             build()
-        _oracle = C.CDLL(ORACLE_SO)
-    return _oracle
+        _oracle[path] = C.CDLL(path)
+    return _oracle[path]
 
 
 def have_ref() -> bool:
@@ -87,9 +88,9 @@ def mha(qkv: np.ndarray, B: int, S: int, E: int, H: int, causal: bool = False,
     return out, probs
 
 
-def sdp(Q: np.ndarray, K: np.ndarray, B: int, S: int, D: int) -> np.ndarray:
+def sdp(Q: np.ndarray, K: np.ndarray, B: int, S: int, D: int, fma: bool = False) -> np.ndarray:
     scores = np.zeros((B, S, S), dtype=np.float32)
-    oracle_lib().oracle_sdp(_f(Q), _f(K), _f(scores), B, S, D)
+    oracle_lib(fma).oracle_sdp(_f(Q), _f(K), _f(scores), B, S, D)
     return scores
 
 
@@ -99,9 +100,9 @@ def softmax(scores: np.ndarray, B: int, S: int) -> np.ndarray:
     return out
 
 
-def weighted_sum(P: np.ndarray, V: np.ndarray, B: int, S: int, D: int) -> np.ndarray:
+def weighted_sum(P: np.ndarray, V: np.ndarray, B: int, S: int, D: int, fma: bool = False) -> np.ndarray:
     out = np.zeros((B, S, D), dtype=np.float32)
-    oracle_lib().oracle_weighted_sum(_f(P), _f(V), _f(out), B, S, D)
+    oracle_lib(fma).oracle_weighted_sum(_f(P), _f(V), _f(out), B, S, D)
     return out
 
 

@@ -1,0 +1,223 @@
+"""GPU parity tests of the fused attention forward, through the C ABI, against the CPU oracle
+and the golden vectors of the reference's own launchers.  Tolerance for the exact-fp32 path:
+max-abs-error <= 1e-5 (outputs are O(1), probabilities <= 1)."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from hipgpt_b200 import _capi, synth
+from oracle import bindings as ob
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+torch = pytest.importorskip("torch")
+from tests.gpu_util import dev, gpu_mha  # noqa: E402
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "attn_golden.npz"))
+
+
+def _maxerr(a, b):
+    return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64)))) if a.size else 0.0
+
+
+# (B, H, S, D): tails around the 32-key tile and the 8-key chunk, one key, S just past the
+# reference's flash limit, head dims of the rows kernel and of the generic kernel
+SHAPES = [(2, 8, 64, 32), (1, 2, 1, 32), (2, 3, 7, 32), (1, 2, 31, 32), (2, 2, 33, 32), (1, 1, 100, 32),
+          (1, 2, 257, 32), (1, 1, 513, 32), (2, 2, 65, 64), (1, 3, 130, 64), (1, 2, 40, 128),
+          (2, 2, 24, 16), (1, 3, 50, 48), (1, 1, 37, 80), (1, 2, 20, 256), (1, 1, 9, 5)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("want_probs", [False, True])
+def test_mha_matches_oracle(shape, causal, want_probs):
+    B, H, S, D = shape
+    E = H * D
+    qkv = synth.qkv_planes(1000 + S + D, B, S, E)
+    ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=want_probs)
+    out, probs = gpu_mha(qkv, B, S, E, H, causal, want_probs)
+    assert np.isfinite(out).all()
+    assert _maxerr(out, ref_out) <= TOL
+    if want_probs:
+        assert np.isfinite(probs).all()
+        assert _maxerr(probs, ref_probs) <= TOL
+        np.testing.assert_allclose(probs.sum(-1), 1.0, atol=1e-5)
+        if causal:
+            assert np.all(np.triu(probs, 1) == 0.0)
+
+
+@pytest.mark.parametrize("warps", [1, 2, 4])
+@pytest.mark.parametrize("D", [32, 64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_rows_kernel_every_block_shape(warps, D, causal):
+    B, H, S = 2, 2, 150
+    E = H * D
+    qkv = synth.qkv_planes(7 + D, B, S, E)
+    ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=True)
+    out, probs = gpu_mha(qkv, B, S, E, H, causal, True, algo=_capi.ALGO_ROWS, warps=warps)
+    assert _maxerr(out, ref_out) <= TOL
+    assert _maxerr(probs, ref_probs) <= TOL
+
+
+@pytest.mark.parametrize("D", [32, 64])
+def test_generic_kernel_agrees_on_rows_kernel_shapes(D):
+    B, H, S = 2, 2, 77
+    E = H * D
+    qkv = synth.qkv_planes(3, B, S, E)
+    for causal in (False, True):
+        ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=True)
+        out, probs = gpu_mha(qkv, B, S, E, H, causal, True, algo=_capi.ALGO_GENERIC)
+        assert _maxerr(out, ref_out) <= TOL and _maxerr(probs, ref_probs) <= TOL
+
+
+@pytest.mark.parametrize("name", ["flash_d32", "flash_d64", "fallback_d16", "flash_s1"])
+def test_mha_matches_reference_golden(name):
+    """Non-causal, probabilities stored: the reference-exact point, against outputs of the
+    reference's own launch_multihead_attention."""
+    B, H, S, D, _ = (int(x) for x in GOLDEN[f"{name}.shape"])
+    E = H * D
+    out, probs = gpu_mha(GOLDEN[f"{name}.qkv"], B, S, E, H, False, True)
+    assert _maxerr(out, GOLDEN[f"{name}.out"]) <= TOL
+    assert _maxerr(probs, GOLDEN[f"{name}.probs"]) <= TOL
+
+
+@pytest.mark.parametrize("cfg", ["c1", "c2", "c3"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_benchmark_shapes_match_oracle(cfg, causal):
+    c = synth.CONFIGS[cfg]
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    E = H * D
+    qkv = synth.qkv_planes(c["seed"], B, S, E, c["scale"])
+    want_probs = cfg != "c3"       # 512 MiB of probabilities at c3: checked on one batch below
+    ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=want_probs)
+    out, probs = gpu_mha(qkv, B, S, E, H, causal, want_probs)
+    assert _maxerr(out, ref_out) <= TOL
+    if want_probs:
+        assert _maxerr(probs, ref_probs) <= TOL
+    else:
+        q1 = np.ascontiguousarray(qkv.reshape(3, B, S, E)[:, :1])
+        r_out, r_probs = ob.mha(q1, 1, S, E, H, causal=causal, want_probs=True)
+        g_out, g_probs = gpu_mha(q1, 1, S, E, H, causal, True)
+        assert _maxerr(g_probs, r_probs) <= TOL and _maxerr(g_out, r_out) <= TOL
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_largest_shape_sampled_against_oracle_and_sliced(causal):
+    """B=64 H=16 S=2048 D=64: the full problem runs on the GPU; the oracle checks two whole
+    batches; a GPU run on just those batches must give the same bits (each (batch, head) is
+    independent, which is also what makes the multi-GPU split exact)."""
+    c = synth.CONFIGS["c5"]
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    E = H * D
+    d_qkv = torch.empty((3, B * S, E), dtype=torch.float32, device="cuda")
+    picks = [0, B - 1]
+    host = {}
+    for b in range(B):                               # generate batch by batch: 1.5 GiB on the host otherwise
+        blk = synth.qkv_planes(c["seed"] * 1000 + b, 1, S, E, c["scale"])
+        d_qkv[:, b * S:(b + 1) * S] = torch.from_numpy(blk).cuda()
+        if b in picks:
+            host[b] = blk
+    d_out = torch.full((B * S, E), float("nan"), dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _capi.check(_capi.lib().hipgpt_mha_forward_planes(d_qkv.data_ptr(), d_out.data_ptr(), None, B, S, E, H, int(causal), st))
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(d_out).all())
+    for b in picks:
+        ref_out, _ = ob.mha(host[b], 1, S, E, H, causal=causal)
+        got = d_out[b * S:(b + 1) * S].cpu().numpy()
+        assert _maxerr(got, ref_out) <= TOL
+        alone, _ = gpu_mha(host[b], 1, S, E, H, causal)
+        assert np.array_equal(alone, got)
+
+
+def test_batch_slices_are_bit_identical():
+    B, H, S, D = 6, 4, 96, 32
+    E = H * D
+    qkv = synth.qkv_planes(42, B, S, E)
+    full, fprobs = gpu_mha(qkv, B, S, E, H, True, True)
+    planes = qkv.reshape(3, B, S, E)
+    for b0, b1 in [(0, 2), (2, 3), (3, 6)]:
+        part, pprobs = gpu_mha(np.ascontiguousarray(planes[:, b0:b1]), b1 - b0, S, E, H, True, True)
+        assert np.array_equal(part, full.reshape(B, S, E)[b0:b1].reshape(-1, E))
+        assert np.array_equal(pprobs, fprobs[b0:b1])
+
+
+def test_inputs_are_not_modified_and_output_fully_written():
+    B, H, S, D = 2, 2, 45, 32
+    E = H * D
+    qkv = synth.qkv_planes(8, B, S, E)
+    d_qkv = dev(qkv)
+    d_out = torch.full((B * S, E), float("nan"), device="cuda")
+    d_probs = torch.full((B, H, S, S), float("nan"), device="cuda")
+    _capi.check(_capi.lib().hipgpt_mha_forward_planes(d_qkv.data_ptr(), d_out.data_ptr(), d_probs.data_ptr(),
+                                                      B, S, E, H, 1, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert np.array_equal(d_qkv.cpu().numpy(), qkv)
+    assert bool(torch.isfinite(d_out).all()) and bool(torch.isfinite(d_probs).all())
+
+
+def test_large_magnitude_scores_stay_finite():
+    B, H, S, D = 1, 2, 64, 32
+    E = H * D
+    qkv = synth.qkv_planes(77, B, S, E, scale=6.0)      # scores of a few hundred: exp would overflow unshifted
+    ref_out, ref_probs = ob.mha(qkv, B, S, E, H, want_probs=True)
+    out, probs = gpu_mha(qkv, B, S, E, H, False, True)
+    assert np.isfinite(out).all()
+    assert _maxerr(probs, ref_probs) <= 2e-5 and _maxerr(out, ref_out) <= 2e-4   # |v| ~ 6 scales the error
+
+
+def test_reference_named_launchers_on_default_stream():
+    """The C++ entry points a HipGPT object file binds to (include/hipgpt_launchers.hpp)."""
+    raw = C.CDLL(_capi.lib_path())
+    mha = getattr(raw, _capi.CXX_LAUNCHERS["launch_multihead_attention"])
+    mha.restype = None
+    mha.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
+    B, H, S, D = 2, 8, 64, 32
+    E = H * D
+    qkv = synth.qkv_planes(0, B, S, E)
+    ref_out, ref_probs = ob.mha(qkv, B, S, E, H, want_probs=True)
+    d_qkv = dev(qkv)
+    d_out = torch.empty((B * S, E), device="cuda")
+    d_probs = torch.empty((B, H, S, S), device="cuda")
+    torch.cuda.synchronize()
+    mha(d_qkv.data_ptr(), d_out.data_ptr(), d_probs.data_ptr(), B, S, E, H)
+    mha(d_qkv.data_ptr(), d_out.data_ptr(), None, B, S, E, H)      # nullptr probs accepted on every path
+    torch.cuda.synchronize()
+    assert _maxerr(d_out.cpu().numpy(), ref_out) <= TOL
+    assert _maxerr(d_probs.cpu().numpy(), ref_probs) <= TOL
+
+
+def test_host_buffer_entry_point():
+    from hipgpt_b200 import launchers
+    B, H, S, D = 3, 4, 70, 64
+    E = H * D
+    qkv = synth.qkv_planes(5, B, S, E)
+    for causal in (False, True):
+        ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=True)
+        h_qkv = torch.from_numpy(qkv).pin_memory()
+        h_out = torch.empty((B * S, E)).pin_memory()
+        h_probs = np.empty((B, H, S, S), dtype=np.float32)          # pageable memory works too
+        launchers.mha_forward_host(h_qkv, h_out, h_probs, B, S, E, H, causal=causal)
+        assert _maxerr(h_out.numpy(), ref_out) <= TOL
+        assert _maxerr(h_probs, ref_probs) <= TOL
+    _capi.lib().hipgpt_release_workspace()
+
+
+def test_python_launcher_mirror_uses_current_stream():
+    from hipgpt_b200 import launchers
+    B, H, S, D = 2, 2, 50, 32
+    E = H * D
+    qkv = synth.qkv_planes(6, B, S, E)
+    ref_out, _ = ob.mha(qkv, B, S, E, H)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        d_qkv = dev(qkv)
+        d_out = torch.empty((B * S, E), device="cuda")
+        launchers.launch_multihead_attention(d_qkv, d_out, None, B, S, E, H)
+    side.synchronize()
+    assert _maxerr(d_out.cpu().numpy(), ref_out) <= TOL
+    with pytest.raises(ValueError):
+        launchers.launch_multihead_attention(d_qkv, d_out, None, B, S, 30, 4)

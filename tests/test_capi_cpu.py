@@ -1,0 +1,100 @@
+"""CPU checks of the drop-in boundary: the library loads without a GPU, exports every symbol
+that include/hipgpt_attn.h declares and every reference-named launcher, and the host-only
+entry points (sharding arithmetic, error text, size queries) behave."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from hipgpt_b200 import _capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "hipgpt_attn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hipgpt_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_bindings_agree():
+    assert _declared_symbols() == sorted(_capi.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _capi.lib()
+    for name in _declared_symbols():
+        assert hasattr(lib, name), name
+
+
+def test_library_exports_reference_named_launchers():
+    raw = C.CDLL(_capi.lib_path())
+    for name, mangled in _capi.CXX_LAUNCHERS.items():
+        assert getattr(raw, mangled) is not None, name
+
+
+def test_reference_objects_would_resolve_against_the_library():
+    """The mangled names HipGPT's own objects refer to are the ones g++ makes of the
+    declarations in include/hip_kernels.h:39-46; check with the compiler, not by hand."""
+    import subprocess
+    import tempfile
+    src = '#include "hipgpt_launchers.hpp"\nvoid f(const float* a, float* b){launch_multihead_attention(a,b,b,1,1,1,1);' \
+          'launch_scaled_dot_product(a,a,b,1,1,1);launch_softmax(a,b,1,1);launch_attention_weighted_sum(a,a,b,1,1,1);}\n'
+    with tempfile.TemporaryDirectory() as td:
+        cpp = os.path.join(td, "t.cpp")
+        open(cpp, "w").write(src)
+        obj = os.path.join(td, "t.o")
+        subprocess.run(["g++", "-c", "-I", os.path.join(ROOT, "include"), cpp, "-o", obj], check=True)
+        undefined = subprocess.run(["nm", "-u", obj], check=True, capture_output=True, text=True).stdout
+    for mangled in _capi.CXX_LAUNCHERS.values():
+        assert mangled in undefined
+
+
+def test_version_and_error_text():
+    lib = _capi.lib()
+    assert lib.hipgpt_version() >= 100
+    b0, b1 = C.c_int(), C.c_int()
+    rc = lib.hipgpt_shard_range(8, 0, 0, C.byref(b0), C.byref(b1))
+    assert rc == _capi.ERR_BAD_ARG
+    assert b"world=0" in lib.hipgpt_last_error()
+    with pytest.raises(_capi.HipGPTError):
+        _capi.check(rc)
+
+
+@pytest.mark.parametrize("B,world", [(64, 8), (32, 1), (10, 4), (3, 8), (0, 2), (7, 7)])
+def test_shard_range_partitions_batches(B, world):
+    lib = _capi.lib()
+    covered = []
+    sizes = []
+    for r in range(world):
+        b0, b1 = C.c_int(), C.c_int()
+        assert lib.hipgpt_shard_range(B, world, r, C.byref(b0), C.byref(b1)) == 0
+        covered += list(range(b0.value, b1.value))
+        sizes.append(b1.value - b0.value)
+    assert covered == list(range(B))            # contiguous, ordered, no gaps, no overlap
+    assert max(sizes) - min(sizes) <= 1
+
+
+def test_bad_arguments_are_rejected_before_any_cuda_call():
+    lib = _capi.lib()
+    # E % H != 0 and H <= 0: the reference aborts (src/hip_kernels.cpp:410-413); the C ABI returns a code
+    assert lib.hipgpt_mha_forward(None, None, None, None, None, 1, 4, 30, 4, 0, None) == _capi.ERR_BAD_ARG
+    assert b"Bad MHA config" in lib.hipgpt_last_error()
+    assert lib.hipgpt_mha_forward(None, None, None, None, None, 1, 4, 32, 0, 0, None) == _capi.ERR_BAD_ARG
+    assert lib.hipgpt_mha_forward(None, None, None, None, None, 1, 4, 32, 1, 0, None) == _capi.ERR_NULL
+    assert lib.hipgpt_mha_forward(None, None, None, None, None, -1, 4, 32, 1, 0, None) == _capi.ERR_BAD_ARG
+    # empty problems succeed without touching a pointer
+    assert lib.hipgpt_mha_forward(None, None, None, None, None, 0, 4, 32, 1, 0, None) == 0
+    assert lib.hipgpt_mha_forward(None, None, None, None, None, 2, 0, 32, 1, 0, None) == 0
+    assert lib.hipgpt_scaled_dot_product(None, None, None, 1, 4, 0, None) == _capi.ERR_BAD_ARG
+    assert lib.hipgpt_softmax(None, None, 1, 4, None) == _capi.ERR_NULL
+    assert lib.hipgpt_mha_decode(None, None, None, None, None, 0, 1, 1, 32, 5, 4, None) == _capi.ERR_BAD_ARG  # ctx > cap
+
+
+def test_decode_scratch_size_query():
+    lib = _capi.lib()
+    assert lib.hipgpt_mha_decode_scratch_bytes(8, 8, 32, 256) > 0
+    assert lib.hipgpt_mha_decode_scratch_bytes(8, 8, 32, 16) == 0       # one split: no scratch
+    assert lib.hipgpt_mha_decode_scratch_bytes(1024, 8, 32, 256) == 0   # enough rows already
+    assert lib.hipgpt_mha_decode_scratch_bytes(0, 8, 32, 256) == 0
