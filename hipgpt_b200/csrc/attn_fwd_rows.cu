@@ -343,10 +343,9 @@ int launch_mha_rows(const float *q, const float *k, const float *v, float *out, 
 {
     const int D = E / H;
     if (warps == 0) {
-        // Enough thread blocks to fill 148 SMs several times over, else smaller blocks.
-        const int rows_per_warp = (32 / (D / 32)) * 2;
-        const long long warps_total = (long long)B * H * ((S + rows_per_warp - 1) / rows_per_warp);
-        warps = warps_total >= 148LL * 4 * 8 ? 4 : 2;
+        // Measured on B200: short causal problems (head_dim 32) run best with one warp per block
+        // (finest load balance across the diagonal), everything else with two.
+        warps = (causal && D == 32) ? 1 : 2;
     }
     switch (D) {
     case 32: return launch_warps<32>(q, k, v, out, probs, B, S, E, H, causal, warps, st);

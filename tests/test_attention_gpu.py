@@ -166,7 +166,8 @@ def test_large_magnitude_scores_stay_finite():
     ref_out, ref_probs = ob.mha(qkv, B, S, E, H, want_probs=True)
     out, probs = gpu_mha(qkv, B, S, E, H, False, True)
     assert np.isfinite(out).all()
-    assert _maxerr(probs, ref_probs) <= 2e-5 and _maxerr(out, ref_out) <= 2e-4   # |v| ~ 6 scales the error
+    # scores near 300 carry an fp32 rounding error of 3e-5 before the exponential, |v| ~ 6..20 scales it
+    assert _maxerr(probs, ref_probs) <= 1e-4 and _maxerr(out, ref_out) <= 2e-3
 
 
 def test_reference_named_launchers_on_default_stream():
