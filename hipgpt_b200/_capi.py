@@ -12,7 +12,7 @@ from . import build as _build
 
 OK = 0
 ERR_BAD_ARG, ERR_NULL, ERR_UNSUPPORTED, ERR_CUDA, ERR_SCRATCH = -1, -2, -3, -4, -5
-ALGO_AUTO, ALGO_GENERIC, ALGO_ROWS = 0, 1, 2
+ALGO_AUTO, ALGO_GENERIC, ALGO_ROWS, ALGO_TENSOR = 0, 1, 2, 3
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 
@@ -30,6 +30,7 @@ SIGNATURES = {
     "hipgpt_mha_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_shard_range": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     "hipgpt_probe_fma": (_i, [_vp, _i, _i, C.POINTER(C.c_double), _vp]),
+    "hipgpt_kernel_status": (_i, [C.POINTER(_i)]),
     "hipgpt_last_error": (C.c_char_p, []),
     "hipgpt_version": (_i, []),
 }

@@ -37,6 +37,10 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 int launch_mha_rows(const float *q, const float *k, const float *v, float *out, float *probs,
                     int B, int S, int E, int H, int causal, int warps, cudaStream_t st);
 bool mha_rows_supports(int D);
+int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
+                  int B, int S, int E, int H, int causal, cudaStream_t st);
+bool mha_tc_supports(int D);
+int tc_status_fetch(int *status);
 int launch_mha_generic(const float *q, const float *k, const float *v, float *out, float *probs,
                        int B, int S, int E, int H, int causal, cudaStream_t st);
 int launch_sdp(const float *Q, const float *K, float *scores, int B, int S, int D, cudaStream_t st);

@@ -61,6 +61,11 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
     case HIPGPT_ALGO_ROWS:
         if (!aligned) return fail(HIPGPT_ERR_BAD_ARG, "rows kernel needs 16-byte aligned pointers");
         return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
+    case HIPGPT_ALGO_TENSOR:
+        if (!aligned) return fail(HIPGPT_ERR_BAD_ARG, "tensor-core kernel needs 16-byte aligned pointers");
+        if (probs) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel does not store probabilities");
+        if (!mha_tc_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
+        return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
     default:
         return fail(HIPGPT_ERR_BAD_ARG, "unknown algo %d", algo);
     }
@@ -223,6 +228,12 @@ int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end)
     *b_begin = rank * base + (rank < extra ? rank : extra);
     *b_end = *b_begin + base + (rank < extra ? 1 : 0);
     return HIPGPT_OK;
+}
+
+int hipgpt_kernel_status(int *status)
+{
+    if (!status) return fail(HIPGPT_ERR_NULL, "status must not be NULL");
+    return tc_status_fetch(status);
 }
 
 const char *hipgpt_last_error(void) { return g_err; }

@@ -49,6 +49,7 @@ extern "C" {
 #define HIPGPT_ALGO_AUTO     0   /* rows kernel for head_dim 32/64/128, generic kernel otherwise   */
 #define HIPGPT_ALGO_GENERIC  1   /* one warp per query row, any head_dim <= 512                    */
 #define HIPGPT_ALGO_ROWS     2   /* register-resident query rows, shared-memory K/V tiles          */
+#define HIPGPT_ALGO_TENSOR   3   /* tcgen05 split-TF32 kernel, head_dim 32/64, no probabilities    */
 
 /*
  * Fused multi-head attention forward:  out = softmax(Q K^T / sqrt(D)) V  per (batch, head).
@@ -129,6 +130,14 @@ HIPGPT_API int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int 
  * that the exact-fp32 kernels are measured against.  d_sink: one float of device memory.
  */
 HIPGPT_API int hipgpt_probe_fma(float *d_sink, int blocks, int iters, double *flops, void *stream);
+
+/*
+ * Device-side status of the tensor-core kernels (no counterpart in the reference).  Their
+ * waits on hardware barriers are bounded; a block whose wait runs out stores nothing and sets
+ * the status to 1.  This call waits for the device, stores the status word in *status and
+ * clears it.  0 means every launch since the last call completed normally.
+ */
+HIPGPT_API int hipgpt_kernel_status(int *status);
 
 /* Text of the calling thread's most recent failure ("" if none). */
 HIPGPT_API const char *hipgpt_last_error(void);

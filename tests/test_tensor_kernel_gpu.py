@@ -1,0 +1,67 @@
+"""GPU parity tests of the tcgen05 split-TF32 attention kernel (HIPGPT_ALGO_TENSOR) against the
+CPU oracle.  The kernel claims fp32-grade results, so it is held to the same tolerance as the
+FFMA kernel: max-abs-error <= 1e-5."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from hipgpt_b200 import _capi, synth
+from oracle import bindings as ob
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+from tests.gpu_util import gpu_mha  # noqa: E402
+
+TOL = 1e-5
+
+
+def _status():
+    st = C.c_int(-1)
+    _capi.check(_capi.lib().hipgpt_kernel_status(C.byref(st)))
+    return st.value
+
+
+# one key tile, tails of the 64-key tile and of the 128-row block, several blocks, both head dims
+SHAPES = [(1, 1, 64, 32), (1, 1, 1, 32), (2, 2, 7, 32), (1, 2, 65, 32), (2, 2, 128, 32), (1, 3, 129, 32),
+          (2, 2, 200, 32), (2, 8, 256, 32), (1, 1, 513, 32), (1, 2, 64, 64), (2, 2, 130, 64), (1, 2, 300, 64)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+def test_tensor_kernel_matches_oracle(shape, causal):
+    B, H, S, D = shape
+    E = H * D
+    qkv = synth.qkv_planes(2000 + S + D, B, S, E)
+    ref_out, _ = ob.mha(qkv, B, S, E, H, causal=causal)
+    out, _ = gpu_mha(qkv, B, S, E, H, causal, False, algo=_capi.ALGO_TENSOR)
+    assert _status() == 0
+    assert np.isfinite(out).all()
+    assert float(np.abs(out - ref_out).max()) <= TOL
+
+
+@pytest.mark.parametrize("cfg", ["c2", "c3"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tensor_kernel_benchmark_shapes(cfg, causal):
+    c = synth.CONFIGS[cfg]
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    E = H * D
+    qkv = synth.qkv_planes(c["seed"], B, S, E, c["scale"])
+    ref_out, _ = ob.mha(qkv, B, S, E, H, causal=causal)
+    out, _ = gpu_mha(qkv, B, S, E, H, causal, False, algo=_capi.ALGO_TENSOR)
+    assert _status() == 0
+    assert float(np.abs(out - ref_out).max()) <= TOL
+
+
+def test_tensor_kernel_refuses_what_it_cannot_do():
+    lib = _capi.lib()
+    t = torch.zeros((64, 48), device="cuda")
+    p = torch.zeros((1, 1, 64, 64), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    # head_dim 48
+    assert lib.hipgpt_mha_forward_ex(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), None,
+                                     1, 64, 48, 1, 0, _capi.ALGO_TENSOR, 0, st) == _capi.ERR_UNSUPPORTED
+    # probabilities requested
+    t32 = torch.zeros((64, 32), device="cuda")
+    assert lib.hipgpt_mha_forward_ex(t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), p.data_ptr(),
+                                     1, 64, 32, 1, 0, _capi.ALGO_TENSOR, 0, st) == _capi.ERR_UNSUPPORTED
