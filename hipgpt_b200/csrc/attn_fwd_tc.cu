@@ -95,18 +95,20 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, for a tile made of 128-byte rows grouped
-// by 8 (1024 bytes per group).  K-major operands: sbo = bytes between 8-row groups, lbo unused
-// (1).  N-major operand: sbo = bytes between groups of 8 reduction rows, lbo = bytes between
-// 32-float column blocks.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+// Shared-memory matrix descriptor for a tile made of 128-byte rows.
+//   K-major operands (Q, K): layout 2 = SWIZZLE_128B, rows grouped by 8 (1024 bytes); sbo = bytes
+//     between groups, lbo unused (16).
+//   N-major operand (V): 32-bit operands that are contiguous along N must use layout 1,
+//     SWIZZLE_128B with a 32-byte base: reduction rows grouped by 4 (512 bytes); sbo = bytes
+//     between groups, lbo = bytes between 32-float column blocks.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
 {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;          // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;          // SWIZZLE_128B
+    d |= (uint64_t)layout_type << 61;   // 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte base
     return d;
 }
 
@@ -154,6 +156,17 @@ __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__flo
 __device__ __forceinline__ void store_split(float *hi_blk, float *lo_blk, int row, int chunk, float4 x)
 {
     const int off = row * 32 + ((chunk ^ (row & 7)) << 2);
+    const float4 h = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
+    *reinterpret_cast<float4 *>(hi_blk + off) = h;
+    *reinterpret_cast<float4 *>(lo_blk + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+}
+
+// The same for the N-major operand: 32-byte pieces of a row are permuted by the row index
+// modulo 4; the 16-byte half inside a piece keeps its place.
+__device__ __forceinline__ void store_split_nmajor(float *hi_blk, float *lo_blk, int row, int chunk, float4 x)
+{
+    const int piece = (chunk >> 1) ^ (row & 3);
+    const int off = row * 32 + (((piece << 1) | (chunk & 1)) << 2);
     const float4 h = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
     *reinterpret_cast<float4 *>(hi_blk + off) = h;
     *reinterpret_cast<float4 *>(lo_blk + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
@@ -237,7 +250,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                 const float4 kx = ok ? __ldg(reinterpret_cast<const float4 *>(K + g)) : zero;
                 const float4 vx = ok ? __ldg(reinterpret_cast<const float4 *>(V + g)) : zero;
                 store_split(k_hi + (c >> 3) * KBLK, k_lo + (c >> 3) * KBLK, r, c & 7, kx);
-                store_split(v_hi + (c >> 3) * KBLK, v_lo + (c >> 3) * KBLK, r, c & 7, vx);
+                store_split_nmajor(v_hi + (c >> 3) * KBLK, v_lo + (c >> 3) * KBLK, r, c & 7, vx);
             }
         }
         proxy_fence();                 // generic-proxy writes -> visible to the tensor core's reads
@@ -250,12 +263,14 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             uint32_t acc = 0;
 #pragma unroll
             for (int pass = 0; pass < 3; ++pass) {
-                const float *qa = pass == 2 ? q_lo : q_hi;
+                // the two correction terms first: the accumulator is still tiny while they are
+                // added, so the tensor core's truncating adds cost no accuracy there
+                const float *qa = pass == 0 ? q_lo : q_hi;
                 const float *kb = pass == 1 ? k_lo : k_hi;
 #pragma unroll
                 for (int db = 0; db < DB; ++db) {
-                    const uint64_t da = make_desc(smem_u32(qa + db * QBLK), 16, 1024);
-                    const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024);
+                    const uint64_t da = make_desc(smem_u32(qa + db * QBLK), 16, 1024, 2);
+                    const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024, 2);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {            // 8 floats = 32 bytes per instruction
                         mma_ss(tmem + kColS, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
@@ -326,10 +341,10 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             uint32_t acc = 0;
 #pragma unroll
             for (int pass = 0; pass < 3; ++pass) {
-                const uint32_t pa = tmem + (pass == 2 ? kColPlo : kColPhi);
+                const uint32_t pa = tmem + (pass == 0 ? kColPlo : kColPhi);
                 const float *vb = pass == 1 ? v_lo : v_hi;
                 // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
-                const uint64_t dv = make_desc(smem_u32(vb), KBLK * 4, 1024);
+                const uint64_t dv = make_desc(smem_u32(vb), KBLK * 4, 512, 1);
 #pragma unroll
                 for (int k = 0; k < kN / 8; ++k) {
                     mma_ts(tmem + kColO, pa + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv, acc);
@@ -347,6 +362,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                 float ot[32];
                 tmem_ld32(lane_base + kColO + db * 32, ot);
                 tmem_wait_ld();
+
 #pragma unroll
                 for (int d = 0; d < 32; ++d) o[db * 32 + d] = fmaf(o[db * 32 + d], alpha, ot[d]);
             }
