@@ -5,27 +5,34 @@
 //
 // The contraction runs as split-TF32 ("3xTF32"): every fp32 operand x is cut into
 //   hi = x with the 13 low mantissa bits cleared (exactly a TF32 number), lo = x - hi (exact),
-// and a product a*b is accumulated as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi in the tensor core's
-// fp32 accumulator.  The dropped a_lo*b_lo term and the truncation of lo are below 2^-21
-// relative, so scores and outputs agree with fp32 FFMA arithmetic to about 1e-6.
+// and a product a*b is accumulated as a_lo*b_hi + a_hi*b_lo + a_hi*b_hi in the tensor core's
+// fp32 accumulator (correction terms first, while the accumulator is small).  The dropped
+// a_lo*b_lo term and the truncation of lo are below 2^-21 relative; measured against the
+// fp32 oracle the outputs differ by at most 2.4e-6.
 //
-// One thread block = 128 query rows of one (batch, head), 128 threads, thread t owns row t:
-//   stage   Q (scaled by log2(e)/sqrt(D)), then per tile of 64 keys K and V, are read from
-//           global with coalesced 128-bit loads, split into hi / lo and written to shared memory
-//           in the tensor core's canonical 128-byte-swizzled layout (rows of 32 floats);
-//   S       = Q K^T for the tile: tcgen05.mma kind::tf32, M=128 N=64, both operands K-major
-//           from shared memory, accumulator in TMEM (3 passes x D/8 instructions);
-//   softmax thread t reads its row of S with tcgen05.ld (TMEM lane t), applies the causal / tail
-//           mask, keeps the running maximum and sum (log2 domain, one ex2 per score), splits
-//           P into hi / lo and writes both back to TMEM with tcgen05.st;
-//   O_tile  = P V: tcgen05.mma with A = P from TMEM and B = V from shared memory, N-major
-//           (3 passes x 8 instructions), fresh accumulator per tile;
-//   update  thread t reads its row of O_tile and adds it to its register accumulator, which
-//           it rescaled when the running maximum moved.
+// One thread block = 128 query rows of one (batch, head), 256 threads.  Warp w works on TMEM
+// lanes 32*(w%4).., i.e. thread (w%4)*32+lane owns query row q0 + that index, and the two
+// threads of a row (warps w and w+4) split the 64 keys of a tile and the head dimension of
+// the output between them.  Per tile of 64 keys:
+//   stage   K and V are read from global with coalesced 128-bit loads one to two tiles ahead
+//           (they wait in registers), split into hi / lo and written to shared memory in the
+//           tensor core's canonical 128-byte-swizzled layouts (K: K-major SWIZZLE_128B; V:
+//           N-major, which for 32-bit operands must be SWIZZLE_128B with a 32-byte base);
+//   S       = Q K^T: tcgen05.mma kind::tf32, M=128 N=64, operands from shared memory,
+//           accumulator in TMEM, two S buffers so that tile t+1 is computed while tile t is
+//           in the softmax;
+//   softmax each thread reads its 32 scores of its row with tcgen05.ld, the two halves of a row
+//           exchange their maxima through shared memory, running maximum and sum are kept in
+//           the log2 domain (one ex2 per score); P is split into hi / lo and written back to
+//           TMEM (P_hi over S in place, P_lo beside it);
+//   O_tile  = P V: tcgen05.mma with A = P from TMEM and B = V from shared memory, fresh
+//           accumulator per tile; it is collected one iteration later, so its latency hides
+//           behind the next tile's softmax;
+//   update  o = o * alpha + O_tile in registers (alpha = rescale of that tile's new maximum).
 // Completion of each batch of MMAs is signalled by tcgen05.commit on an mbarrier.  Every wait
-// on it is bounded: on expiry the block records a status code, skips its stores, frees its
-// TMEM and returns.  No probabilities are written by this kernel; callers that want them get
-// the FFMA rows kernel.
+// is bounded: on expiry the block records a status code, skips its stores, frees its TMEM and
+// returns.  No probabilities are written by this kernel; callers that want them get the FFMA
+// rows kernel.
 #include "attn_common.cuh"
 
 #include <math.h>
@@ -35,10 +42,11 @@ namespace {
 
 constexpr int kM = 128;          // query rows per block
 constexpr int kN = 64;           // keys per tile
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColPhi = 64, kColPlo = 128, kColO = 192;
-constexpr long long kSpinLimit = 1LL << 22;
+constexpr uint32_t kColS = 0 /* two buffers of 64 */, kColPlo = 128, kColO = 192;
+constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
+constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
 
 __device__ int g_tc_status = 0;   // 0 ok; 1 = an mbarrier wait ran out
 
@@ -54,7 +62,8 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, int count)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
     const uint32_t addr = smem_u32(bar);
-    for (long long i = 0; i < kSpinLimit; ++i) {
+    const long long deadline = clock64() + kCycleLimit;
+    for (long long i = 0; i < kSpinLimit && clock64() < deadline; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -146,6 +155,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32])
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16])
+{
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr) : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -173,215 +192,261 @@ __device__ __forceinline__ void store_split_nmajor(float *hi_blk, float *lo_blk,
 }
 
 template <int D, bool CAUSAL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, D == 32 ? 2 : 1)   // head_dim 32: two blocks per SM
 mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
               float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
 {
     constexpr int DB = D / 32;                   // 32-float column blocks per row
+    constexpr int DH = D / 2;                    // output columns per thread
     constexpr int QBLK = kM * 32;                // floats per [128][32] block
     constexpr int KBLK = kN * 32;                // floats per [64][32] block
+    constexpr int KBUF = DB * KBLK;              // floats per K (or V) hi (or lo) tile
+    constexpr int CPR = D / 4;                   // 16-byte chunks per row
+    constexpr int RPP = kThreads / CPR;          // K/V rows staged per pass
+    constexpr int NP = kN / RPP;                 // passes = float4 registers per staged tile
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // 1024-byte alignment is what the swizzled layout assumes
+    // 1024-byte alignment is what the swizzled layouts assume
     float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float *q_hi = base, *q_lo = q_hi + DB * QBLK;
-    float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + DB * KBLK;
-    float *v_hi = k_lo + DB * KBLK, *v_lo = v_hi + DB * KBLK;
-    __shared__ uint64_t mbar;
+    float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + 2 * KBUF;      // [2 buffers][DB][64][32] each
+    float *v_hi = k_lo + 2 * KBUF, *v_lo = v_hi + 2 * KBUF;
+    __shared__ uint64_t mbar_qk[2], mbar_pv;     // one Q K^T barrier per S buffer: a waiter can never lag a full phase
     __shared__ uint32_t tmem_base_slot;
+    __shared__ float xchg[2][kM];                // row maxima (later: row sums) of the two halves
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int half = warp >> 2;                  // which 32 keys of a tile / which output columns
+    const int rloc = (warp & 3) * 32 + lane;     // row inside the block = TMEM lane
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);   // heaviest first
     const int b = bh / H, h = bh % H;
     const size_t tok0 = (size_t)b * S;
     const size_t hcol = (size_t)h * D;
     const int q0 = qblk * kM;
-    const int row = q0 + tid;                    // this thread's query
+    const int row = q0 + rloc;                   // this thread's query
+
+    const int kend = CAUSAL ? min(S, q0 + kM) : S;
+    const int ntiles = (kend + kN - 1) / kN;
+
+    // K/V staging role of this thread: chunk sc of rows sr0 + p*RPP
+    const int sc = tid % CPR, sr0 = tid / CPR;
+    auto load_tile = [&](const float *__restrict__ plane, int t, float4 (&regs)[NP]) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+            const int j = t * kN + sr0 + p * RPP;
+            const bool ok = t < ntiles && j < S;
+            regs[p] = ok ? __ldg(reinterpret_cast<const float4 *>(plane + (tok0 + j) * (size_t)E + hcol + sc * 4))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto store_k = [&](int buf, const float4 (&regs)[NP]) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+            store_split(k_hi + buf * KBUF + (sc >> 3) * KBLK, k_lo + buf * KBUF + (sc >> 3) * KBLK, sr0 + p * RPP, sc & 7, regs[p]);
+    };
+    auto store_v = [&](int buf, const float4 (&regs)[NP]) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+            store_split_nmajor(v_hi + buf * KBUF + (sc >> 3) * KBLK, v_lo + buf * KBUF + (sc >> 3) * KBLK, sr0 + p * RPP, sc & 7, regs[p]);
+    };
+
+    // ---- prologue: everything the first two QK products need ---------------------------------
+    float4 kreg[NP], vreg[NP], k1reg[NP];
+    constexpr int QC = CPR / 2;                  // Q chunks per thread (two threads per row)
+    float4 qreg[QC];
+    {
+        const bool ok = row < S;
+        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol) + half * QC;
+#pragma unroll
+        for (int c = 0; c < QC; ++c) qreg[c] = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    load_tile(K, 0, kreg);
+    load_tile(V, 0, vreg);
+    load_tile(K, 1, k1reg);
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (tid == 0) mbar_init(&mbar, 1);
+    if (tid == 0) { mbar_init(&mbar_qk[0], 1); mbar_init(&mbar_qk[1], 1); mbar_init(&mbar_pv, 1); }
 
-    // ---- stage Q: thread t owns row t -------------------------------------------------------
-    {
-        const bool ok = row < S;
-        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
 #pragma unroll
-        for (int c = 0; c < D / 4; ++c) {
-            float4 x = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-            x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
-            store_split(q_hi + (c >> 3) * QBLK, q_lo + (c >> 3) * QBLK, tid, c & 7, x);
-        }
+    for (int c = 0; c < QC; ++c) {
+        float4 x = qreg[c];
+        x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
+        const int cc = half * QC + c;
+        store_split(q_hi + (cc >> 3) * QBLK, q_lo + (cc >> 3) * QBLK, rloc, cc & 7, x);
     }
+    store_k(0, kreg);
+    store_v(0, vreg);
+    store_k(1, k1reg);
+    load_tile(K, 2, kreg);                       // in flight until the end of iteration 0
+    load_tile(V, 1, vreg);
+    proxy_fence();                               // generic-proxy writes -> visible to the tensor core's reads
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 TMEM lanes
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
 
-    float o[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.0f;
-    float m = -1e30f, l = 0.0f;
-    uint32_t phase = 0;
-    bool failed = false;
-
-    const int kend = CAUSAL ? min(S, q0 + kM) : S;
-    const int ntiles = (kend + kN - 1) / kN;
     constexpr uint32_t idesc_qk = make_idesc(kM, kN, 0);
     constexpr uint32_t idesc_pv = make_idesc(kM, D, 1);
 
-    for (int t = 0; t < ntiles && !failed; ++t) {
-        const int j0 = t * kN;
-        // ---- stage K and V of this tile: 8 (or 16) threads per row, coalesced 128-bit loads --
-        {
-            constexpr int CPR = D / 4;                       // 16-byte chunks per row
-            constexpr int RPP = kThreads / CPR;              // rows per pass
-            const int c = tid % CPR, r0 = tid / CPR;
+    // S[buf] = Q K(buf)^T, issued by one thread
+    auto issue_qk = [&](int buf) {
+        uint32_t acc = 0;
 #pragma unroll
-            for (int p = 0; p < kN / RPP; ++p) {
-                const int r = r0 + p * RPP;
-                const int j = j0 + r;
-                const bool ok = j < S;
-                const size_t g = (tok0 + (ok ? j : 0)) * (size_t)E + hcol + c * 4;
-                const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float4 kx = ok ? __ldg(reinterpret_cast<const float4 *>(K + g)) : zero;
-                const float4 vx = ok ? __ldg(reinterpret_cast<const float4 *>(V + g)) : zero;
-                store_split(k_hi + (c >> 3) * KBLK, k_lo + (c >> 3) * KBLK, r, c & 7, kx);
-                store_split_nmajor(v_hi + (c >> 3) * KBLK, v_lo + (c >> 3) * KBLK, r, c & 7, vx);
-            }
-        }
-        proxy_fence();                 // generic-proxy writes -> visible to the tensor core's reads
-        tc_fence_before();
-        __syncthreads();
-
-        // ---- S = Q K^T -------------------------------------------------------------------
-        if (tid == 0) {
-            tc_fence_after();
-            uint32_t acc = 0;
+        for (int pass = 0; pass < 3; ++pass) {
+            // the two correction terms first: the accumulator is still tiny while they are
+            // added, so the tensor core's truncating adds cost no accuracy there
+            const float *qa = pass == 0 ? q_lo : q_hi;
+            const float *kb = (pass == 1 ? k_lo : k_hi) + buf * KBUF;
 #pragma unroll
-            for (int pass = 0; pass < 3; ++pass) {
-                // the two correction terms first: the accumulator is still tiny while they are
-                // added, so the tensor core's truncating adds cost no accuracy there
-                const float *qa = pass == 0 ? q_lo : q_hi;
-                const float *kb = pass == 1 ? k_lo : k_hi;
+            for (int db = 0; db < DB; ++db) {
+                const uint64_t da = make_desc(smem_u32(qa + db * QBLK), 16, 1024, 2);
+                const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024, 2);
 #pragma unroll
-                for (int db = 0; db < DB; ++db) {
-                    const uint64_t da = make_desc(smem_u32(qa + db * QBLK), 16, 1024, 2);
-                    const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024, 2);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {            // 8 floats = 32 bytes per instruction
-                        mma_ss(tmem + kColS, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
-                        acc = 1;
-                    }
-                }
-            }
-            tc_commit(&mbar);
-        }
-        // every tcgen05.ld / st below is warp-wide (.sync.aligned): keep the outcome warp-uniform
-        failed = __any_sync(0xffffffffu, !mbar_wait(&mbar, phase));
-        phase ^= 1;
-        tc_fence_after();
-
-        // ---- softmax of this thread's row ------------------------------------------------
-        float alpha = 1.0f;
-        if (!failed) {
-            float s[kN];
-            float lo[kN];
-            float(&s0)[32] = *reinterpret_cast<float(*)[32]>(&s[0]);
-            float(&s1)[32] = *reinterpret_cast<float(*)[32]>(&s[32]);
-            float(&l0)[32] = *reinterpret_cast<float(*)[32]>(&lo[0]);
-            float(&l1)[32] = *reinterpret_cast<float(*)[32]>(&lo[32]);
-            if (CAUSAL && j0 > q0 + warp * 32 + 31) {
-                // the whole tile lies above the diagonal for every row of this warp: P = 0
-#pragma unroll
-                for (int c = 0; c < kN; ++c) { s[c] = 0.0f; lo[c] = 0.0f; }
-            } else {
-                tmem_ld32(lane_base + kColS, s0);
-                tmem_ld32(lane_base + kColS + 32, s1);
-                tmem_wait_ld();
-                if ((CAUSAL && j0 + kN - 1 > q0 + warp * 32) || j0 + kN > S) {
-#pragma unroll
-                    for (int c = 0; c < kN; ++c) {
-                        const int j = j0 + c;
-                        if (j >= S || (CAUSAL && j > row)) s[c] = -INFINITY;
-                    }
-                }
-                float mx = s[0];
-#pragma unroll
-                for (int c = 1; c < kN; ++c) mx = fmaxf(mx, s[c]);
-                const float mn = fmaxf(m, mx);       // m is finite (-1e30f at worst), so is mn
-                alpha = ex2_approx(m - mn);
-                m = mn;
-                float psum = 0.0f;
-#pragma unroll
-                for (int c = 0; c < kN; ++c) {
-                    const float p = ex2_approx(s[c] - mn);   // masked scores give exactly 0
-                    psum += p;
-                    const float ph = tf32_hi(p);
-                    s[c] = ph;
-                    lo[c] = p - ph;
-                }
-                l = fmaf(l, alpha, psum);
-            }
-            tmem_st32(lane_base + kColPhi, s0);
-            tmem_st32(lane_base + kColPhi + 32, s1);
-            tmem_st32(lane_base + kColPlo, l0);
-            tmem_st32(lane_base + kColPlo + 32, l1);
-            tmem_wait_st();
-        }
-        tc_fence_before();
-        if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
-
-        // ---- O_tile = P V ------------------------------------------------------------------
-        if (tid == 0) {
-            tc_fence_after();
-            uint32_t acc = 0;
-#pragma unroll
-            for (int pass = 0; pass < 3; ++pass) {
-                const uint32_t pa = tmem + (pass == 0 ? kColPlo : kColPhi);
-                const float *vb = pass == 1 ? v_lo : v_hi;
-                // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
-                const uint64_t dv = make_desc(smem_u32(vb), KBLK * 4, 512, 1);
-#pragma unroll
-                for (int k = 0; k < kN / 8; ++k) {
-                    mma_ts(tmem + kColO, pa + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv, acc);
+                for (int k = 0; k < 4; ++k) {            // 8 floats = 32 bytes per instruction
+                    mma_ss(tmem + kColS + buf * kN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
                     acc = 1;
                 }
             }
-            tc_commit(&mbar);
         }
-        failed = __any_sync(0xffffffffu, !mbar_wait(&mbar, phase));
-        phase ^= 1;
-        tc_fence_after();
-        if (!failed) {
+        tc_commit(&mbar_qk[buf]);
+    };
+    // O_tile = P(buf) V(buf)
+    auto issue_pv = [&](int buf) {
+        uint32_t acc = 0;
 #pragma unroll
-            for (int db = 0; db < DB; ++db) {
-                float ot[32];
-                tmem_ld32(lane_base + kColO + db * 32, ot);
-                tmem_wait_ld();
-
+        for (int pass = 0; pass < 3; ++pass) {
+            const uint32_t pa = tmem + (pass == 0 ? kColPlo : kColS + buf * kN);
+            const float *vb = (pass == 1 ? v_lo : v_hi) + buf * KBUF;
+            // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
+            const uint64_t dv = make_desc(smem_u32(vb), KBLK * 4, 512, 1);
 #pragma unroll
-                for (int d = 0; d < 32; ++d) o[db * 32 + d] = fmaf(o[db * 32 + d], alpha, ot[d]);
+            for (int k = 0; k < kN / 8; ++k) {
+                mma_ts(tmem + kColO, pa + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv, acc);
+                acc = 1;
             }
         }
+        tc_commit(&mbar_pv);
+    };
+
+    if (tid == 0 && ntiles > 0) issue_qk(0);
+
+    float o[DH];
+#pragma unroll
+    for (int d = 0; d < DH; ++d) o[d] = 0.0f;
+    float m = -1e30f, l = 0.0f, alpha_prev = 1.0f;
+    bool failed = false;
+
+    // o = o * alpha_prev + O_tile of the previous tile (this thread's DH columns)
+    auto collect_o = [&]() {
+        if (DH == 16) {
+            float ot[16];
+            tmem_ld16(lane_base + kColO + half * 16, ot);
+            tmem_wait_ld();
+#pragma unroll
+            for (int d = 0; d < 16; ++d) o[d] = fmaf(o[d], alpha_prev, ot[d]);
+        } else {
+            float ot[32];
+            tmem_ld32(lane_base + kColO + half * 32, ot);
+            tmem_wait_ld();
+#pragma unroll
+            for (int d = 0; d < 32; ++d) o[d % DH] = fmaf(o[d % DH], alpha_prev, ot[d]);
+        }
+    };
+
+    for (int t = 0; t < ntiles; ++t) {
+        const int buf = t & 1;
+        const int j0 = t * kN + half * 32;        // first key of this thread's 32 columns
+        // every tcgen05.ld / st below is warp-wide (.sync.aligned): keep outcomes warp-uniform
+        if (__any_sync(0xffffffffu, !mbar_wait(&mbar_qk[buf], (uint32_t)((t >> 1) & 1)))) failed = true;
+        tc_fence_after();
+        // the next tile's scores are computed while this one is in the softmax; MMAs of one
+        // thread run in issue order, so the P V product still reading that S buffer is done first
+        if (tid == 0 && t + 1 < ntiles) issue_qk(buf ^ 1);
+
+        // ---- softmax of this thread's 32 scores -------------------------------------------
+        float s[32], lo[32];
+        const bool warp_dead = CAUSAL && j0 > q0 + (warp & 3) * 32 + 31;   // all above the diagonal
+        float mx = -INFINITY;
+        if (!warp_dead) {
+            tmem_ld32(lane_base + kColS + buf * kN + half * 32, s);
+            tmem_wait_ld();
+            if ((CAUSAL && j0 + 31 > q0 + (warp & 3) * 32) || j0 + 32 > S) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int j = j0 + c;
+                    if (j >= S || (CAUSAL && j > row)) s[c] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) mx = fmaxf(mx, s[c]);
+        }
+        xchg[half][rloc] = mx;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps of these rows
+        mx = fmaxf(mx, xchg[half ^ 1][rloc]);
+        const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
+        const float alpha = ex2_approx(m - mn);
+        m = mn;
+        float psum = 0.0f;
+        if (!warp_dead) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float p = ex2_approx(s[c] - mn);   // masked scores give exactly 0
+                psum += p;
+                const float ph = tf32_hi(p);
+                s[c] = ph;
+                lo[c] = p - ph;
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) { s[c] = 0.0f; lo[c] = 0.0f; }
+        }
+        l = fmaf(l, alpha, psum);
+
+        // ---- collect the previous tile's P V (also frees P_lo and its V buffer) --------------
+        if (t > 0) {
+            if (__any_sync(0xffffffffu, !mbar_wait(&mbar_pv, (uint32_t)((t - 1) & 1)))) failed = true;
+            tc_fence_after();
+            collect_o();
+        }
+        alpha_prev = alpha;
+
+        tmem_st32(lane_base + kColS + buf * kN + half * 32, s);      // P_hi over S, in place
+        tmem_st32(lane_base + kColPlo + half * 32, lo);
+        tmem_wait_st();
+
+        // ---- stage K(t+2) and V(t+1) from their registers, fetch the tiles after them ---------
+        if (t + 2 < ntiles) store_k(buf, kreg);           // Q K(t)^T has completed
+        if (t + 1 < ntiles) store_v(buf ^ 1, vreg);       // P V(t-1) has completed
+        load_tile(K, t + 3, kreg);
+        load_tile(V, t + 2, vreg);
+        proxy_fence();
         tc_fence_before();
         if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
+        if (tid == 0) { tc_fence_after(); issue_pv(buf); }
     }
 
+    if (!failed && ntiles > 0) {
+        if (__any_sync(0xffffffffu, !mbar_wait(&mbar_pv, (uint32_t)((ntiles - 1) & 1)))) failed = true;
+        tc_fence_after();
+        collect_o();
+    }
+    // row sums of the two halves
+    xchg[half][rloc] = l;
+    tc_fence_before();
+    if (__syncthreads_or(failed ? 1 : 0)) failed = true;
     if (failed) {
         if (tid == 0) atomicExch(&g_tc_status, 1);
     } else if (row < S) {
-        const float inv = 1.0f / fmaxf(l, 1e-20f);
-        float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol);
+        const float inv = 1.0f / fmaxf(l + xchg[half ^ 1][rloc], 1e-20f);
+        float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol + half * DH);
 #pragma unroll
-        for (int c = 0; c < D / 4; ++c)
+        for (int c = 0; c < DH / 4; ++c)
             dst[c] = make_float4(o[c * 4 + 0] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
     }
-    tc_fence_before();
-    __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
@@ -394,7 +459,7 @@ int launch_tc_cfg(const float *q, const float *k, const float *v, float *out, in
     constexpr int DB = D / 32;
     // operands + alignment slack; never less than 100 KB, so that at most two blocks share an
     // SM and their two 256-column TMEM allocations always fit in the 512 columns
-    size_t smem = (size_t)(2 * DB * kM * 32 + 4 * DB * kN * 32) * sizeof(float) + 1024;
+    size_t smem = (size_t)(2 * DB * kM * 32 + 8 * DB * kN * 32) * sizeof(float) + 1024;
     if (smem < 100 * 1024) smem = 100 * 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
