@@ -284,7 +284,7 @@ def run_ours(args):
         pass
     hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
     hbm_achieved = per_batch_bytes / (launch_ms * 1e-3) / 1e9
-    roofline = {"bound": "fma", "kernel": "mha_rows_kernel", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s",
+    roofline = {"bound": "fma", "kernel": "mha_tc_kernel" if not args.probs else "mha_rows_kernel", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s",
                 "frac": achieved / fma_peak, "traffic": None,
                 "peak_source": "fp32 FFMA loop timed in this run (the measured-peaks file has no fp32 figure)",
                 "us_per_launch": launch_ms * 1e3,

@@ -10,29 +10,32 @@
 // a_lo*b_lo term and the truncation of lo are below 2^-21 relative; measured against the
 // fp32 oracle the outputs differ by at most 2.4e-6.
 //
-// One thread block = 128 query rows of one (batch, head), 256 threads.  Warp w works on TMEM
-// lanes 32*(w%4).., i.e. thread (w%4)*32+lane owns query row q0 + that index, and the two
-// threads of a row (warps w and w+4) split the 64 keys of a tile and the head dimension of
-// the output between them.  Per tile of 64 keys:
-//   stage   K and V are read from global with coalesced 128-bit loads one to two tiles ahead
-//           (they wait in registers), split into hi / lo and written to shared memory in the
-//           tensor core's canonical 128-byte-swizzled layouts (K: K-major SWIZZLE_128B; V:
-//           N-major, which for 32-bit operands must be SWIZZLE_128B with a 32-byte base);
-//   S       = Q K^T: tcgen05.mma kind::tf32, M=128 N=64, operands from shared memory,
-//           accumulator in TMEM, two S buffers so that tile t+1 is computed while tile t is
-//           in the softmax;
-//   softmax each thread reads its 32 scores of its row with tcgen05.ld, the two halves of a row
-//           exchange their maxima through shared memory, running maximum and sum are kept in
-//           the log2 domain (one ex2 per score); P is split into hi / lo and written back to
-//           TMEM (P_hi over S in place, P_lo beside it);
-//   O_tile  = P V: tcgen05.mma with A = P from TMEM and B = V from shared memory, fresh
-//           accumulator per tile; it is collected one iteration later, so its latency hides
-//           behind the next tile's softmax;
-//   update  o = o * alpha + O_tile in registers (alpha = rescale of that tile's new maximum).
-// Completion of each batch of MMAs is signalled by tcgen05.commit on an mbarrier.  Every wait
-// is bounded: on expiry the block records a status code, skips its stores, frees its TMEM and
-// returns.  No probabilities are written by this kernel; callers that want them get the FFMA
-// rows kernel.
+// One thread block = 128 query rows of one (batch, head): 256 worker threads plus one warp
+// whose single elected lane issues the MMAs.  Worker warp w works on TMEM lanes 32*(w%4)..,
+// i.e. worker (w%4)*32+lane owns query row q0 + that index, and the two workers of a row
+// (warps w and w+4) split the 64 keys of a tile and the head dimension of the output.
+// A tcgen05.mma with M=128, K=8 costs 64 cycles for any N up to 128 (measured), so operands
+// are concatenated along N where the split allows it.  Per tile of 64 keys:
+//   stage   K and V are read from global with coalesced 128-bit loads one tile ahead (they wait
+//           in registers), split into hi / lo and written to shared memory in the tensor
+//           core's canonical 128-byte-swizzled layouts (K: K-major SWIZZLE_128B, hi rows then
+//           lo rows; V: N-major, which for 32-bit operands must be SWIZZLE_128B with a
+//           32-byte base, hi blocks then lo blocks);
+//   S_ext   = Q_hi [K_hi; K_lo]^T (one N=128 product: columns 0-63 main term, 64-127 first
+//           correction) and Q_lo K_hi^T added to columns 64-127, accumulators in TMEM;
+//   softmax each worker reads its 32 scores (main + corrections) with tcgen05.ld, the two
+//           halves of a row exchange their maxima through shared memory, running maximum
+//           and sum are kept in the log2 domain (one ex2 per score); P is split into hi / lo
+//           and written back to TMEM (P_hi over S in place, P_lo beside it);
+//   O_ext   = P_hi [V_hi | V_lo] (N = 2D) and P_lo V_hi added to its second half, A = P from
+//           TMEM, fresh accumulator per tile; it is collected one iteration later;
+//   update  o = o * alpha + (both halves of O_ext) in registers.
+// The issuing lane runs P V(t) then Q K(t+1)^T back to back; meanwhile the workers of the
+// other resident block do their softmax, so two blocks per SM keep the tensor pipe busy.
+// Hand-offs use mbarriers (tcgen05.commit for the MMAs, 256 arrivals for the workers).  Every
+// wait is bounded: on expiry the block raises a flag that cuts all its later waits short,
+// records a status code, skips its stores, frees its TMEM and returns.  No probabilities are
+// written by this kernel; callers that want them get the FFMA rows kernel.
 #include "attn_common.cuh"
 
 #include <math.h>
@@ -42,9 +45,8 @@ namespace {
 
 constexpr int kM = 128;          // query rows per block
 constexpr int kN = 64;           // keys per tile
-constexpr int kThreads = 256;
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0 /* two buffers of 64 */, kColPlo = 128, kColO = 192;
+constexpr int kWorkers = 256;      // softmax / staging threads
+constexpr int kThreads = kWorkers + 32;   // plus the warp that issues the MMAs
 constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
 constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
 
@@ -165,6 +167,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16])
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(addr) : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const float (&v)[16])
+{
+    const uint32_t *r = reinterpret_cast<const uint32_t *>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -191,31 +203,45 @@ __device__ __forceinline__ void store_split_nmajor(float *hi_blk, float *lo_blk,
     *reinterpret_cast<float4 *>(lo_blk + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
 }
 
+template <int D>
+struct TcCfg {
+    static constexpr int DB = D / 32;                     // 32-float column blocks per row
+    static constexpr int QBLK = kM * 32;                  // floats per [128][32] block
+    static constexpr int KBLK = kN * 32;                  // floats per [64][32] block
+    // TMEM columns: S_ext | P_lo | O_ext
+    static constexpr uint32_t kColS = 0;                  // [0,64): Q_hi K_hi (later P_hi), [64,128): Q_hi K_lo + Q_lo K_hi
+    static constexpr uint32_t kColPlo = 128;              // 64 columns
+    static constexpr uint32_t kColO = 192;                // [0,D): P_hi V_hi, [D,2D): P_hi V_lo + P_lo V_hi
+    static constexpr uint32_t kTmemCols = (192 + 2 * D) <= 256 ? 256 : 512;
+    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 4 * DB * KBLK;
+};
+
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(kThreads, D == 32 ? 2 : 1)   // head_dim 32: two blocks per SM
 mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
               float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
 {
-    constexpr int DB = D / 32;                   // 32-float column blocks per row
-    constexpr int DH = D / 2;                    // output columns per thread
-    constexpr int QBLK = kM * 32;                // floats per [128][32] block
-    constexpr int KBLK = kN * 32;                // floats per [64][32] block
-    constexpr int KBUF = DB * KBLK;              // floats per K (or V) hi (or lo) tile
+    using C = TcCfg<D>;
+    constexpr int DB = C::DB, QBLK = C::QBLK, KBLK = C::KBLK;
+    constexpr int DH = D / 2;                    // output columns per worker thread
     constexpr int CPR = D / 4;                   // 16-byte chunks per row
-    constexpr int RPP = kThreads / CPR;          // K/V rows staged per pass
+    constexpr int RPP = kWorkers / CPR;          // K/V rows staged per pass
     constexpr int NP = kN / RPP;                 // passes = float4 registers per staged tile
+    constexpr uint32_t kColS = C::kColS, kColPlo = C::kColPlo, kColO = C::kColO;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment is what the swizzled layouts assume
     float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    float *q_hi = base, *q_lo = q_hi + DB * QBLK;
-    float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + 2 * KBUF;      // [2 buffers][DB][64][32] each
-    float *v_hi = k_lo + 2 * KBUF, *v_lo = v_hi + 2 * KBUF;
-    __shared__ uint64_t mbar_qk[2], mbar_pv;     // one Q K^T barrier per S buffer: a waiter can never lag a full phase
+    float *q_hi = base, *q_lo = q_hi + DB * QBLK;        // [DB][128][32] each
+    float *k_s = q_lo + DB * QBLK;                       // [DB][hi, lo][64][32]: hi and lo rows form one 128-row operand
+    float *v_s = k_s + 2 * DB * KBLK;                    // [hi, lo][DB][64][32]: hi and lo blocks form one 2D-column operand
+    __shared__ uint64_t mbar_s, mbar_p, mbar_o;
     __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
     __shared__ float xchg[2][kM];                // row maxima (later: row sums) of the two halves
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int half = warp >> 2;                  // which 32 keys of a tile / which output columns
+    const bool is_mma_warp = warp == kWorkers / 32;
+    const int half = (warp >> 2) & 1;            // which 32 keys of a tile / which output columns
     const int rloc = (warp & 3) * 32 + lane;     // row inside the block = TMEM lane
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);   // heaviest first
@@ -223,13 +249,26 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     const size_t tok0 = (size_t)b * S;
     const size_t hcol = (size_t)h * D;
     const int q0 = qblk * kM;
-    const int row = q0 + rloc;                   // this thread's query
+    const int row = q0 + rloc;                   // this worker's query
 
     const int kend = CAUSAL ? min(S, q0 + kM) : S;
     const int ntiles = (kend + kN - 1) / kN;
 
-    // K/V staging role of this thread: chunk sc of rows sr0 + p*RPP
-    const int sc = tid % CPR, sr0 = tid / CPR;
+    if (tid == 0) {
+        abort_flag = 0;
+        mbar_init(&mbar_s, 1);                   // tcgen05.commit after Q K^T
+        mbar_init(&mbar_p, kWorkers);            // every worker: P written, K and V staged
+        mbar_init(&mbar_o, 1);                   // tcgen05.commit after P V
+    }
+
+    // Bounded wait that gives up at once when another thread already gave up.
+    auto wait = [&](uint64_t *bar, uint32_t parity) {
+        if (abort_flag) return;
+        if (!mbar_wait(bar, parity)) abort_flag = 1;
+    };
+
+    // K/V staging role of a worker: chunk sc of rows sr0 + p*RPP
+    const int sc = tid % CPR, sr0 = (tid % kWorkers) / CPR;
     auto load_tile = [&](const float *__restrict__ plane, int t, float4 (&regs)[NP]) {
 #pragma unroll
         for (int p = 0; p < NP; ++p) {
@@ -239,216 +278,217 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                          : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
-    auto store_k = [&](int buf, const float4 (&regs)[NP]) {
+    auto store_k = [&](const float4 (&regs)[NP]) {
+        float *blk = k_s + (sc >> 3) * 2 * KBLK;
 #pragma unroll
-        for (int p = 0; p < NP; ++p)
-            store_split(k_hi + buf * KBUF + (sc >> 3) * KBLK, k_lo + buf * KBUF + (sc >> 3) * KBLK, sr0 + p * RPP, sc & 7, regs[p]);
+        for (int p = 0; p < NP; ++p) store_split(blk, blk + KBLK, sr0 + p * RPP, sc & 7, regs[p]);
     };
-    auto store_v = [&](int buf, const float4 (&regs)[NP]) {
+    auto store_v = [&](const float4 (&regs)[NP]) {
+        float *blk = v_s + (sc >> 3) * KBLK;
 #pragma unroll
-        for (int p = 0; p < NP; ++p)
-            store_split_nmajor(v_hi + buf * KBUF + (sc >> 3) * KBLK, v_lo + buf * KBUF + (sc >> 3) * KBLK, sr0 + p * RPP, sc & 7, regs[p]);
+        for (int p = 0; p < NP; ++p) store_split_nmajor(blk, blk + DB * KBLK, sr0 + p * RPP, sc & 7, regs[p]);
     };
 
-    // ---- prologue: everything the first two QK products need ---------------------------------
-    float4 kreg[NP], vreg[NP], k1reg[NP];
-    constexpr int QC = CPR / 2;                  // Q chunks per thread (two threads per row)
-    float4 qreg[QC];
-    {
+    // ---- prologue ------------------------------------------------------------------------------
+    float4 kreg[NP], vreg[NP];
+    if (!is_mma_warp) {
+        constexpr int QC = CPR / 2;              // Q chunks per worker (two workers per row)
+        float4 qreg[QC];
         const bool ok = row < S;
         const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol) + half * QC;
 #pragma unroll
         for (int c = 0; c < QC; ++c) qreg[c] = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    load_tile(K, 0, kreg);
-    load_tile(V, 0, vreg);
-    load_tile(K, 1, k1reg);
-
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        load_tile(K, 0, kreg);
+        load_tile(V, 0, vreg);
+#pragma unroll
+        for (int c = 0; c < QC; ++c) {
+            float4 x = qreg[c];
+            x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
+            const int cc = half * QC + c;
+            store_split(q_hi + (cc >> 3) * QBLK, q_lo + (cc >> 3) * QBLK, rloc, cc & 7, x);
+        }
+        store_k(kreg);
+        load_tile(K, 1, kreg);                   // in flight until Q K(0)^T has completed
+        proxy_fence();                           // generic-proxy writes -> visible to the tensor core's reads
+    } else {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (tid == 0) { mbar_init(&mbar_qk[0], 1); mbar_init(&mbar_qk[1], 1); mbar_init(&mbar_pv, 1); }
-
-#pragma unroll
-    for (int c = 0; c < QC; ++c) {
-        float4 x = qreg[c];
-        x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
-        const int cc = half * QC + c;
-        store_split(q_hi + (cc >> 3) * QBLK, q_lo + (cc >> 3) * QBLK, rloc, cc & 7, x);
-    }
-    store_k(0, kreg);
-    store_v(0, vreg);
-    store_k(1, k1reg);
-    load_tile(K, 2, kreg);                       // in flight until the end of iteration 0
-    load_tile(V, 1, vreg);
-    proxy_fence();                               // generic-proxy writes -> visible to the tensor core's reads
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
-    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
 
-    constexpr uint32_t idesc_qk = make_idesc(kM, kN, 0);
-    constexpr uint32_t idesc_pv = make_idesc(kM, D, 1);
-
-    // S[buf] = Q K(buf)^T, issued by one thread
-    auto issue_qk = [&](int buf) {
-        uint32_t acc = 0;
+    if (is_mma_warp) {
+        // ================= the issuing warp: one lane feeds the tensor core ====================
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk1 = make_idesc(kM, 2 * kN, 0);    // Q_hi  x [K_hi; K_lo]
+            constexpr uint32_t idesc_qk2 = make_idesc(kM, kN, 0);        // Q_lo  x K_hi
+            constexpr uint32_t idesc_pv1 = make_idesc(kM, 2 * D, 1);     // P_hi  x [V_hi | V_lo]
+            constexpr uint32_t idesc_pv2 = make_idesc(kM, D, 1);         // P_lo  x V_hi
+            auto issue_qk = [&]() {
+                uint32_t acc = 0;
 #pragma unroll
-        for (int pass = 0; pass < 3; ++pass) {
-            // the two correction terms first: the accumulator is still tiny while they are
-            // added, so the tensor core's truncating adds cost no accuracy there
-            const float *qa = pass == 0 ? q_lo : q_hi;
-            const float *kb = (pass == 1 ? k_lo : k_hi) + buf * KBUF;
+                for (int db = 0; db < DB; ++db) {
+                    const uint64_t da = make_desc(smem_u32(q_hi + db * QBLK), 16, 1024, 2);
+                    const uint64_t dk = make_desc(smem_u32(k_s + db * 2 * KBLK), 16, 1024, 2);
 #pragma unroll
-            for (int db = 0; db < DB; ++db) {
-                const uint64_t da = make_desc(smem_u32(qa + db * QBLK), 16, 1024, 2);
-                const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024, 2);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {            // 8 floats = 32 bytes per instruction
-                    mma_ss(tmem + kColS + buf * kN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
-                    acc = 1;
+                    for (int k = 0; k < 4; ++k) {            // 8 floats = 32 bytes per instruction
+                        mma_ss(tmem + kColS, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk1, acc);
+                        acc = 1;
+                    }
                 }
-            }
-        }
-        tc_commit(&mbar_qk[buf]);
-    };
-    // O_tile = P(buf) V(buf)
-    auto issue_pv = [&](int buf) {
-        uint32_t acc = 0;
+                // the second correction term joins the first one in columns [64,128): both are
+                // small, so the tensor core's truncating adds cost no accuracy there
 #pragma unroll
-        for (int pass = 0; pass < 3; ++pass) {
-            const uint32_t pa = tmem + (pass == 0 ? kColPlo : kColS + buf * kN);
-            const float *vb = (pass == 1 ? v_lo : v_hi) + buf * KBUF;
-            // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
-            const uint64_t dv = make_desc(smem_u32(vb), KBLK * 4, 512, 1);
+                for (int db = 0; db < DB; ++db) {
+                    const uint64_t da = make_desc(smem_u32(q_lo + db * QBLK), 16, 1024, 2);
+                    const uint64_t dk = make_desc(smem_u32(k_s + db * 2 * KBLK), 16, 1024, 2);
 #pragma unroll
-            for (int k = 0; k < kN / 8; ++k) {
-                mma_ts(tmem + kColO, pa + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv, acc);
-                acc = 1;
-            }
-        }
-        tc_commit(&mbar_pv);
-    };
-
-    if (tid == 0 && ntiles > 0) issue_qk(0);
-
-    float o[DH];
-#pragma unroll
-    for (int d = 0; d < DH; ++d) o[d] = 0.0f;
-    float m = -1e30f, l = 0.0f, alpha_prev = 1.0f;
-    bool failed = false;
-
-    // o = o * alpha_prev + O_tile of the previous tile (this thread's DH columns)
-    auto collect_o = [&]() {
-        if (DH == 16) {
-            float ot[16];
-            tmem_ld16(lane_base + kColO + half * 16, ot);
-            tmem_wait_ld();
-#pragma unroll
-            for (int d = 0; d < 16; ++d) o[d] = fmaf(o[d], alpha_prev, ot[d]);
-        } else {
-            float ot[32];
-            tmem_ld32(lane_base + kColO + half * 32, ot);
-            tmem_wait_ld();
-#pragma unroll
-            for (int d = 0; d < 32; ++d) o[d % DH] = fmaf(o[d % DH], alpha_prev, ot[d]);
-        }
-    };
-
-    for (int t = 0; t < ntiles; ++t) {
-        const int buf = t & 1;
-        const int j0 = t * kN + half * 32;        // first key of this thread's 32 columns
-        // every tcgen05.ld / st below is warp-wide (.sync.aligned): keep outcomes warp-uniform
-        if (__any_sync(0xffffffffu, !mbar_wait(&mbar_qk[buf], (uint32_t)((t >> 1) & 1)))) failed = true;
-        tc_fence_after();
-        // the next tile's scores are computed while this one is in the softmax; MMAs of one
-        // thread run in issue order, so the P V product still reading that S buffer is done first
-        if (tid == 0 && t + 1 < ntiles) issue_qk(buf ^ 1);
-
-        // ---- softmax of this thread's 32 scores -------------------------------------------
-        float s[32], lo[32];
-        const bool warp_dead = CAUSAL && j0 > q0 + (warp & 3) * 32 + 31;   // all above the diagonal
-        float mx = -INFINITY;
-        if (!warp_dead) {
-            tmem_ld32(lane_base + kColS + buf * kN + half * 32, s);
-            tmem_wait_ld();
-            if ((CAUSAL && j0 + 31 > q0 + (warp & 3) * 32) || j0 + 32 > S) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int j = j0 + c;
-                    if (j >= S || (CAUSAL && j > row)) s[c] = -INFINITY;
+                    for (int k = 0; k < 4; ++k)
+                        mma_ss(tmem + kColS + kN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk2, 1);
                 }
+                tc_commit(&mbar_s);
+            };
+            auto issue_pv = [&]() {
+                // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
+                const uint64_t dv = make_desc(smem_u32(v_s), KBLK * 4, 512, 1);
+#pragma unroll
+                for (int k = 0; k < kN / 8; ++k)
+                    mma_ts(tmem + kColO, tmem + kColS + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv1, k ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < kN / 8; ++k)
+                    mma_ts(tmem + kColO + D, tmem + kColPlo + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv2, 1);
+                tc_commit(&mbar_o);
+            };
+            if (ntiles > 0) issue_qk();
+            for (int t = 0; t < ntiles; ++t) {
+                wait(&mbar_p, (uint32_t)(t & 1));        // P(t) in TMEM, V(t) and K(t+1) in shared memory
+                tc_fence_after();
+                issue_pv();
+                if (t + 1 < ntiles) issue_qk();          // runs after P V(t): MMAs of one thread execute in order
             }
-#pragma unroll
-            for (int c = 0; c < 32; ++c) mx = fmaxf(mx, s[c]);
         }
-        xchg[half][rloc] = mx;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps of these rows
-        mx = fmaxf(mx, xchg[half ^ 1][rloc]);
-        const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
-        const float alpha = ex2_approx(m - mn);
-        m = mn;
-        float psum = 0.0f;
-        if (!warp_dead) {
+        __syncwarp();
+    } else {
+        // ================= the 256 workers: softmax, staging, output ===========================
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
+        float o[DH];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const float p = ex2_approx(s[c] - mn);   // masked scores give exactly 0
-                psum += p;
-                const float ph = tf32_hi(p);
-                s[c] = ph;
-                lo[c] = p - ph;
-            }
-        } else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) { s[c] = 0.0f; lo[c] = 0.0f; }
-        }
-        l = fmaf(l, alpha, psum);
+        for (int d = 0; d < DH; ++d) o[d] = 0.0f;
+        float m = -1e30f, l = 0.0f, alpha_prev = 1.0f;
 
-        // ---- collect the previous tile's P V (also frees P_lo and its V buffer) --------------
-        if (t > 0) {
-            if (__any_sync(0xffffffffu, !mbar_wait(&mbar_pv, (uint32_t)((t - 1) & 1)))) failed = true;
+        // o = o * alpha_prev + (both parts of) O_tile of the previous tile, this worker's DH columns
+        auto collect_o = [&]() {
+            if (DH == 16) {
+                float a[16], c[16];
+                tmem_ld16(lane_base + kColO + half * 16, a);
+                tmem_ld16(lane_base + kColO + D + half * 16, c);
+                tmem_wait_ld();
+#pragma unroll
+                for (int d = 0; d < 16; ++d) o[d] = fmaf(o[d], alpha_prev, a[d] + c[d]);
+            } else {
+                float a[32], c[32];
+                tmem_ld32(lane_base + kColO + half * 32, a);
+                tmem_ld32(lane_base + kColO + D + half * 32, c);
+                tmem_wait_ld();
+#pragma unroll
+                for (int d = 0; d < 32; ++d) o[d % DH] = fmaf(o[d % DH], alpha_prev, a[d] + c[d]);
+            }
+        };
+
+        for (int t = 0; t < ntiles; ++t) {
+            const int j0 = t * kN + half * 32;        // first key of this worker's 32 columns
+            wait(&mbar_s, (uint32_t)(t & 1));         // S(t) is in TMEM; the K buffer is free again
+            tc_fence_after();
+            if (t + 1 < ntiles) store_k(kreg);        // K(t+1) for the product that follows P V(t)
+            load_tile(K, t + 2, kreg);
+
+            // ---- softmax of this worker's 32 scores (tcgen05 ops are warp-wide: uniform control) ----
+            float s[32];
+            const bool warp_dead = CAUSAL && j0 > q0 + (warp & 3) * 32 + 31;   // all above the diagonal
+            float mx = -INFINITY;
+            if (!warp_dead) {
+                tmem_ld32(lane_base + kColS + half * 32, s);
+                {
+                    float c0[16], c1[16];
+                    tmem_ld16(lane_base + kColS + kN + half * 32, c0);
+                    tmem_ld16(lane_base + kColS + kN + half * 32 + 16, c1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) { s[c] += c0[c]; s[16 + c] += c1[c]; }
+                }
+                if ((CAUSAL && j0 + 31 > q0 + (warp & 3) * 32) || j0 + 32 > S) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int j = j0 + c;
+                        if (j >= S || (CAUSAL && j > row)) s[c] = -INFINITY;
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, s[c]);
+            }
+            xchg[half][rloc] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps of these rows
+            mx = fmaxf(mx, xchg[half ^ 1][rloc]);
+            const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
+            const float alpha = ex2_approx(m - mn);
+            m = mn;
+
+            // ---- the previous tile's P V: collect it; P_lo and the V buffer are free afterwards ----
+            if (t > 0) {
+                wait(&mbar_o, (uint32_t)((t - 1) & 1));
+                tc_fence_after();
+                collect_o();
+            }
+            alpha_prev = alpha;
+            store_v(vreg);                            // V(t)
+            load_tile(V, t + 1, vreg);
+
+            float psum = 0.0f;
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                float lo[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const float p = warp_dead ? 0.0f : ex2_approx(s[g * 16 + c] - mn);   // masked scores give exactly 0
+                    psum += p;
+                    const float ph = tf32_hi(p);
+                    s[g * 16 + c] = ph;
+                    lo[c] = p - ph;
+                }
+                tmem_st16(lane_base + kColPlo + half * 32 + g * 16, lo);
+            }
+            l = fmaf(l, alpha, psum);
+            tmem_st32(lane_base + kColS + half * 32, s);       // P_hi over S, in place
+            tmem_wait_st();
+            proxy_fence();
+            tc_fence_before();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&mbar_p)) : "memory");
+            // the exchange slots are reused next iteration: the partner has read them before it
+            // arrives here, and nobody passes the next wait on mbar_s before all have arrived
+        }
+        if (ntiles > 0) {
+            wait(&mbar_o, (uint32_t)((ntiles - 1) & 1));
             tc_fence_after();
             collect_o();
         }
-        alpha_prev = alpha;
-
-        tmem_st32(lane_base + kColS + buf * kN + half * 32, s);      // P_hi over S, in place
-        tmem_st32(lane_base + kColPlo + half * 32, lo);
-        tmem_wait_st();
-
-        // ---- stage K(t+2) and V(t+1) from their registers, fetch the tiles after them ---------
-        if (t + 2 < ntiles) store_k(buf, kreg);           // Q K(t)^T has completed
-        if (t + 1 < ntiles) store_v(buf ^ 1, vreg);       // P V(t-1) has completed
-        load_tile(K, t + 3, kreg);
-        load_tile(V, t + 2, vreg);
-        proxy_fence();
-        tc_fence_before();
-        if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
-        if (tid == 0) { tc_fence_after(); issue_pv(buf); }
-    }
-
-    if (!failed && ntiles > 0) {
-        if (__any_sync(0xffffffffu, !mbar_wait(&mbar_pv, (uint32_t)((ntiles - 1) & 1)))) failed = true;
-        tc_fence_after();
-        collect_o();
-    }
-    // row sums of the two halves
-    xchg[half][rloc] = l;
-    tc_fence_before();
-    if (__syncthreads_or(failed ? 1 : 0)) failed = true;
-    if (failed) {
-        if (tid == 0) atomicExch(&g_tc_status, 1);
-    } else if (row < S) {
-        const float inv = 1.0f / fmaxf(l + xchg[half ^ 1][rloc], 1e-20f);
-        float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol + half * DH);
+        xchg[half][rloc] = l;                     // row sums of the two halves
+        asm volatile("bar.sync 5, %0;" ::"r"(kWorkers) : "memory");
+        if (!abort_flag && row < S) {
+            const float inv = 1.0f / fmaxf(l + xchg[half ^ 1][rloc], 1e-20f);
+            float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol + half * DH);
 #pragma unroll
-        for (int c = 0; c < DH / 4; ++c)
-            dst[c] = make_float4(o[c * 4 + 0] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
+            for (int c = 0; c < DH / 4; ++c)
+                dst[c] = make_float4(o[c * 4 + 0] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
+        }
     }
-    if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag && tid == 0) atomicExch(&g_tc_status, 1);
+    if (is_mma_warp) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
     }
 }
 
@@ -456,10 +496,9 @@ template <int D, bool CAUSAL>
 int launch_tc_cfg(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, cudaStream_t st)
 {
     auto kern = mha_tc_kernel<D, CAUSAL>;
-    constexpr int DB = D / 32;
     // operands + alignment slack; never less than 100 KB, so that at most two blocks share an
     // SM and their two 256-column TMEM allocations always fit in the 512 columns
-    size_t smem = (size_t)(2 * DB * kM * 32 + 8 * DB * kN * 32) * sizeof(float) + 1024;
+    size_t smem = TcCfg<D>::kSmemFloats * sizeof(float) + 1024;
     if (smem < 100 * 1024) smem = 100 * 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));

@@ -54,6 +54,9 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
                          (probs == nullptr || (reinterpret_cast<uintptr_t>(probs) & 15) == 0);
     switch (algo) {
     case HIPGPT_ALGO_AUTO:
+        // tensor pipe when it applies (fp32-grade split-TF32); FFMA rows kernel when the
+        // probabilities are wanted or head_dim is 128; generic kernel for everything else
+        if (mha_tc_supports(D) && aligned && probs == nullptr) return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
         if (mha_rows_supports(D) && aligned) return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
         return launch_mha_generic(q, k, v, out, probs, B, S, E, H, causal, st);
     case HIPGPT_ALGO_GENERIC:

@@ -46,7 +46,8 @@ extern "C" {
 
 /* Kernel selector of hipgpt_mha_forward_ex (profiling and tests; 0 is what every other
  * entry point uses). */
-#define HIPGPT_ALGO_AUTO     0   /* rows kernel for head_dim 32/64/128, generic kernel otherwise   */
+#define HIPGPT_ALGO_AUTO     0   /* tensor kernel (head_dim 32/64, no probabilities), else rows
+                                    kernel (head_dim 32/64/128), else generic kernel               */
 #define HIPGPT_ALGO_GENERIC  1   /* one warp per query row, any head_dim <= 512                    */
 #define HIPGPT_ALGO_ROWS     2   /* register-resident query rows, shared-memory K/V tiles          */
 #define HIPGPT_ALGO_TENSOR   3   /* tcgen05 split-TF32 kernel, head_dim 32/64, no probabilities    */
