@@ -32,6 +32,7 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src,
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // Kernel launch wrappers (one per .cu file), all returning an HIPGPT_* status.
 int launch_mha_rows(const float *q, const float *k, const float *v, float *out, float *probs,

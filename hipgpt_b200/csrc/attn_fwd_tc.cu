@@ -10,32 +10,31 @@
 // a_lo*b_lo term and the truncation of lo are below 2^-21 relative; measured against the
 // fp32 oracle the outputs differ by at most 2.4e-6.
 //
-// One thread block = 128 query rows of one (batch, head): 256 worker threads plus one warp
-// whose single elected lane issues the MMAs.  Worker warp w works on TMEM lanes 32*(w%4)..,
-// i.e. worker (w%4)*32+lane owns query row q0 + that index, and the two workers of a row
-// (warps w and w+4) split the 64 keys of a tile and the head dimension of the output.
-// A tcgen05.mma with M=128, K=8 costs 64 cycles for any N up to 128 (measured), so operands
-// are concatenated along N where the split allows it.  Per tile of 64 keys:
+// One thread block = 128 query rows of one (batch, head): 128 worker threads (worker t owns
+// query row q0+t = TMEM lane t) plus one warp whose single elected lane issues the MMAs.
+// A tcgen05.mma with M=128, K=8 costs 64 cycles for any N up to 128 (measured), so the P V
+// product concatenates its operands along N.  Per tile of 64 keys:
 //   stage   K and V are read from global with coalesced 128-bit loads one tile ahead (they wait
 //           in registers), split into hi / lo and written to shared memory in the tensor
-//           core's canonical 128-byte-swizzled layouts (K: K-major SWIZZLE_128B, hi rows then
-//           lo rows; V: N-major, which for 32-bit operands must be SWIZZLE_128B with a
-//           32-byte base, hi blocks then lo blocks);
-//   S_ext   = Q_hi [K_hi; K_lo]^T (one N=128 product: columns 0-63 main term, 64-127 first
-//           correction) and Q_lo K_hi^T added to columns 64-127, accumulators in TMEM;
-//   softmax each worker reads its 32 scores (main + corrections) with tcgen05.ld, the two
-//           halves of a row exchange their maxima through shared memory, running maximum
-//           and sum are kept in the log2 domain (one ex2 per score); P is split into hi / lo
-//           and written back to TMEM (P_hi over S in place, P_lo beside it);
+//           core's canonical 128-byte-swizzled layouts (K: K-major SWIZZLE_128B; V: N-major,
+//           which for 32-bit operands must be SWIZZLE_128B with a 32-byte base, hi blocks then
+//           lo blocks so that [V_hi | V_lo] is one operand of 2D columns);
+//   S       = Q K^T in three passes (Q_lo K_hi, Q_hi K_lo, Q_hi K_hi) of D/8 instructions,
+//           M=128 N=64, accumulator in TMEM; two S buffers, so tile t+1 is computed while
+//           tile t is in the softmax;
+//   softmax the worker reads its row with tcgen05.ld, applies the causal / tail mask, keeps the
+//           running maximum and sum in the log2 domain (one ex2 per score), splits P into
+//           hi / lo and writes both back to TMEM (P_hi over S in place, P_lo beside it);
 //   O_ext   = P_hi [V_hi | V_lo] (N = 2D) and P_lo V_hi added to its second half, A = P from
-//           TMEM, fresh accumulator per tile; it is collected one iteration later;
+//           TMEM, fresh accumulator per tile; it is collected one iteration later, so its
+//           latency hides behind the next tile's softmax;
 //   update  o = o * alpha + (both halves of O_ext) in registers.
-// The issuing lane runs P V(t) then Q K(t+1)^T back to back; meanwhile the workers of the
-// other resident block do their softmax, so two blocks per SM keep the tensor pipe busy.
-// Hand-offs use mbarriers (tcgen05.commit for the MMAs, 256 arrivals for the workers).  Every
-// wait is bounded: on expiry the block raises a flag that cuts all its later waits short,
-// records a status code, skips its stores, frees its TMEM and returns.  No probabilities are
-// written by this kernel; callers that want them get the FFMA rows kernel.
+// Hand-offs use mbarriers: tcgen05.commit signals the MMAs' completion, 128 arrivals signal
+// "next K staged" and "P written, V staged".  Two blocks per SM (head_dim 32) overlap one
+// block's softmax with the other's MMAs.  Every wait is bounded: on expiry the block raises a
+// flag that cuts all its later waits short, records a status code, skips its stores, frees
+// its TMEM and returns.  No probabilities are written by this kernel; callers that want them
+// get the FFMA rows kernel.
 #include "attn_common.cuh"
 
 #include <math.h>
@@ -45,7 +44,7 @@ namespace {
 
 constexpr int kM = 128;          // query rows per block
 constexpr int kN = 64;           // keys per tile
-constexpr int kWorkers = 256;      // softmax / staging threads
+constexpr int kWorkers = 128;      // softmax / staging threads, one per query row
 constexpr int kThreads = kWorkers + 32;   // plus the warp that issues the MMAs
 constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
 constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
@@ -130,52 +129,28 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_n_major)
            ((uint32_t)(m >> 4) << 24);
 }
 
+// tcgen05.ld / st, shape 32x32b: thread i of the warp moves N consecutive 32-bit columns of TMEM
+// lane (base lane + i).  Values pass through plain registers (no address is taken).
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32])
 {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(addr) : "memory");
-}
-
-__device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32])
-{
-    const uint32_t *r = reinterpret_cast<const uint32_t *>(v);
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
+    uint32_t r0, r1, r2, r3, r4, r5, r6, r7, r8, r9, r10, r11, r12, r13, r14, r15, r16, r17, r18, r19, r20, r21, r22, r23, r24, r25, r26, r27, r28, r29, r30, r31;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3), "=r"(r4), "=r"(r5), "=r"(r6), "=r"(r7), "=r"(r8), "=r"(r9), "=r"(r10), "=r"(r11), "=r"(r12), "=r"(r13), "=r"(r14), "=r"(r15), "=r"(r16), "=r"(r17), "=r"(r18), "=r"(r19), "=r"(r20), "=r"(r21), "=r"(r22), "=r"(r23), "=r"(r24), "=r"(r25), "=r"(r26), "=r"(r27), "=r"(r28), "=r"(r29), "=r"(r30), "=r"(r31)
+                 : "r"(addr) : "memory");
+    v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3); v[4] = __uint_as_float(r4); v[5] = __uint_as_float(r5); v[6] = __uint_as_float(r6); v[7] = __uint_as_float(r7); v[8] = __uint_as_float(r8); v[9] = __uint_as_float(r9); v[10] = __uint_as_float(r10); v[11] = __uint_as_float(r11); v[12] = __uint_as_float(r12); v[13] = __uint_as_float(r13); v[14] = __uint_as_float(r14); v[15] = __uint_as_float(r15); v[16] = __uint_as_float(r16); v[17] = __uint_as_float(r17); v[18] = __uint_as_float(r18); v[19] = __uint_as_float(r19); v[20] = __uint_as_float(r20); v[21] = __uint_as_float(r21); v[22] = __uint_as_float(r22); v[23] = __uint_as_float(r23); v[24] = __uint_as_float(r24); v[25] = __uint_as_float(r25); v[26] = __uint_as_float(r26); v[27] = __uint_as_float(r27); v[28] = __uint_as_float(r28); v[29] = __uint_as_float(r29); v[30] = __uint_as_float(r30); v[31] = __uint_as_float(r31);
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16])
 {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr) : "memory");
+    uint32_t r0, r1, r2, r3, r4, r5, r6, r7, r8, r9, r10, r11, r12, r13, r14, r15;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3), "=r"(r4), "=r"(r5), "=r"(r6), "=r"(r7), "=r"(r8), "=r"(r9), "=r"(r10), "=r"(r11), "=r"(r12), "=r"(r13), "=r"(r14), "=r"(r15)
+                 : "r"(addr) : "memory");
+    v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3); v[4] = __uint_as_float(r4); v[5] = __uint_as_float(r5); v[6] = __uint_as_float(r6); v[7] = __uint_as_float(r7); v[8] = __uint_as_float(r8); v[9] = __uint_as_float(r9); v[10] = __uint_as_float(r10); v[11] = __uint_as_float(r11); v[12] = __uint_as_float(r12); v[13] = __uint_as_float(r13); v[14] = __uint_as_float(r14); v[15] = __uint_as_float(r15);
 }
 __device__ __forceinline__ void tmem_st16(uint32_t addr, const float (&v)[16])
 {
-    const uint32_t *r = reinterpret_cast<const uint32_t *>(v);
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -208,12 +183,12 @@ struct TcCfg {
     static constexpr int DB = D / 32;                     // 32-float column blocks per row
     static constexpr int QBLK = kM * 32;                  // floats per [128][32] block
     static constexpr int KBLK = kN * 32;                  // floats per [64][32] block
-    // TMEM columns: S_ext | P_lo | O_ext
-    static constexpr uint32_t kColS = 0;                  // [0,64): Q_hi K_hi (later P_hi), [64,128): Q_hi K_lo + Q_lo K_hi
+    // TMEM columns: S (two buffers) | P_lo | O_ext
+    static constexpr uint32_t kColS = 0;                  // [0,64) and [64,128): scores, later P_hi in place
     static constexpr uint32_t kColPlo = 128;              // 64 columns
     static constexpr uint32_t kColO = 192;                // [0,D): P_hi V_hi, [D,2D): P_hi V_lo + P_lo V_hi
     static constexpr uint32_t kTmemCols = (192 + 2 * D) <= 256 ? 256 : 512;
-    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 4 * DB * KBLK;
+    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 4 * DB * KBLK + 2 * kN * D;   // + raw K, V tiles
 };
 
 template <int D, bool CAUSAL>
@@ -223,7 +198,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
 {
     using C = TcCfg<D>;
     constexpr int DB = C::DB, QBLK = C::QBLK, KBLK = C::KBLK;
-    constexpr int DH = D / 2;                    // output columns per worker thread
     constexpr int CPR = D / 4;                   // 16-byte chunks per row
     constexpr int RPP = kWorkers / CPR;          // K/V rows staged per pass
     constexpr int NP = kN / RPP;                 // passes = float4 registers per staged tile
@@ -232,32 +206,33 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     // 1024-byte alignment is what the swizzled layouts assume
     float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float *q_hi = base, *q_lo = q_hi + DB * QBLK;        // [DB][128][32] each
-    float *k_s = q_lo + DB * QBLK;                       // [DB][hi, lo][64][32]: hi and lo rows form one 128-row operand
-    float *v_s = k_s + 2 * DB * KBLK;                    // [hi, lo][DB][64][32]: hi and lo blocks form one 2D-column operand
-    __shared__ uint64_t mbar_s, mbar_p, mbar_o;
+    float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + DB * KBLK;   // [DB][64][32] each
+    float *v_s = k_lo + DB * KBLK;               // [hi, lo][DB][64][32]: hi and lo blocks form one 2D-column operand
+    float *k_raw = v_s + 2 * DB * KBLK;          // [64][D] as it lies in global memory, filled by cp.async
+    float *v_raw = k_raw + kN * D;
+    __shared__ uint64_t mbar_s[2], mbar_k, mbar_p, mbar_o;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
-    __shared__ float xchg[2][kM];                // row maxima (later: row sums) of the two halves
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_mma_warp = warp == kWorkers / 32;
-    const int half = (warp >> 2) & 1;            // which 32 keys of a tile / which output columns
-    const int rloc = (warp & 3) * 32 + lane;     // row inside the block = TMEM lane
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);   // heaviest first
     const int b = bh / H, h = bh % H;
     const size_t tok0 = (size_t)b * S;
     const size_t hcol = (size_t)h * D;
     const int q0 = qblk * kM;
-    const int row = q0 + rloc;                   // this worker's query
+    const int row = q0 + tid;                    // a worker's query row = its TMEM lane
 
     const int kend = CAUSAL ? min(S, q0 + kM) : S;
     const int ntiles = (kend + kN - 1) / kN;
 
     if (tid == 0) {
         abort_flag = 0;
-        mbar_init(&mbar_s, 1);                   // tcgen05.commit after Q K^T
-        mbar_init(&mbar_p, kWorkers);            // every worker: P written, K and V staged
+        mbar_init(&mbar_s[0], 1);                // tcgen05.commit after Q K^T into S buffer 0 / 1
+        mbar_init(&mbar_s[1], 1);
+        mbar_init(&mbar_k, kWorkers);            // every worker: next K tile staged
+        mbar_init(&mbar_p, kWorkers);            // every worker: P written, V staged
         mbar_init(&mbar_o, 1);                   // tcgen05.commit after P V
     }
 
@@ -266,230 +241,243 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         if (abort_flag) return;
         if (!mbar_wait(bar, parity)) abort_flag = 1;
     };
-
-    // K/V staging role of a worker: chunk sc of rows sr0 + p*RPP
-    const int sc = tid % CPR, sr0 = (tid % kWorkers) / CPR;
-    auto load_tile = [&](const float *__restrict__ plane, int t, float4 (&regs)[NP]) {
-#pragma unroll
-        for (int p = 0; p < NP; ++p) {
-            const int j = t * kN + sr0 + p * RPP;
-            const bool ok = t < ntiles && j < S;
-            regs[p] = ok ? __ldg(reinterpret_cast<const float4 *>(plane + (tok0 + j) * (size_t)E + hcol + sc * 4))
-                         : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    auto arrive = [&](uint64_t *bar) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
     };
-    auto store_k = [&](const float4 (&regs)[NP]) {
-        float *blk = k_s + (sc >> 3) * 2 * KBLK;
-#pragma unroll
-        for (int p = 0; p < NP; ++p) store_split(blk, blk + KBLK, sr0 + p * RPP, sc & 7, regs[p]);
-    };
-    auto store_v = [&](const float4 (&regs)[NP]) {
-        float *blk = v_s + (sc >> 3) * KBLK;
-#pragma unroll
-        for (int p = 0; p < NP; ++p) store_split_nmajor(blk, blk + DB * KBLK, sr0 + p * RPP, sc & 7, regs[p]);
-    };
-
-    // ---- prologue ------------------------------------------------------------------------------
-    float4 kreg[NP], vreg[NP];
-    if (!is_mma_warp) {
-        constexpr int QC = CPR / 2;              // Q chunks per worker (two workers per row)
-        float4 qreg[QC];
-        const bool ok = row < S;
-        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol) + half * QC;
-#pragma unroll
-        for (int c = 0; c < QC; ++c) qreg[c] = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-        load_tile(K, 0, kreg);
-        load_tile(V, 0, vreg);
-#pragma unroll
-        for (int c = 0; c < QC; ++c) {
-            float4 x = qreg[c];
-            x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
-            const int cc = half * QC + c;
-            store_split(q_hi + (cc >> 3) * QBLK, q_lo + (cc >> 3) * QBLK, rloc, cc & 7, x);
-        }
-        store_k(kreg);
-        load_tile(K, 1, kreg);                   // in flight until Q K(0)^T has completed
-        proxy_fence();                           // generic-proxy writes -> visible to the tensor core's reads
-    } else {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_base_slot;
 
     if (is_mma_warp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+        const uint32_t tmem = tmem_base_slot;
         // ================= the issuing warp: one lane feeds the tensor core ====================
         if (lane == 0) {
-            constexpr uint32_t idesc_qk1 = make_idesc(kM, 2 * kN, 0);    // Q_hi  x [K_hi; K_lo]
-            constexpr uint32_t idesc_qk2 = make_idesc(kM, kN, 0);        // Q_lo  x K_hi
+            constexpr uint32_t idesc_qk = make_idesc(kM, kN, 0);
             constexpr uint32_t idesc_pv1 = make_idesc(kM, 2 * D, 1);     // P_hi  x [V_hi | V_lo]
             constexpr uint32_t idesc_pv2 = make_idesc(kM, D, 1);         // P_lo  x V_hi
-            auto issue_qk = [&]() {
+            auto issue_qk = [&](int buf) {
                 uint32_t acc = 0;
 #pragma unroll
-                for (int db = 0; db < DB; ++db) {
-                    const uint64_t da = make_desc(smem_u32(q_hi + db * QBLK), 16, 1024, 2);
-                    const uint64_t dk = make_desc(smem_u32(k_s + db * 2 * KBLK), 16, 1024, 2);
+                for (int pass = 0; pass < 3; ++pass) {
+                    // the two correction terms first: the accumulator is still tiny while they
+                    // are added, so the tensor core's truncating adds cost no accuracy there
+                    const float *qa = pass == 0 ? q_lo : q_hi;
+                    const float *kb = pass == 1 ? k_lo : k_hi;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {            // 8 floats = 32 bytes per instruction
-                        mma_ss(tmem + kColS, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk1, acc);
-                        acc = 1;
+                    for (int db = 0; db < DB; ++db) {
+                        const uint64_t da = make_desc(smem_u32(qa + db * QBLK), 16, 1024, 2);
+                        const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024, 2);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {        // 8 floats = 32 bytes per instruction
+                            mma_ss(tmem + kColS + buf * kN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
+                            acc = 1;
+                        }
                     }
                 }
-                // the second correction term joins the first one in columns [64,128): both are
-                // small, so the tensor core's truncating adds cost no accuracy there
-#pragma unroll
-                for (int db = 0; db < DB; ++db) {
-                    const uint64_t da = make_desc(smem_u32(q_lo + db * QBLK), 16, 1024, 2);
-                    const uint64_t dk = make_desc(smem_u32(k_s + db * 2 * KBLK), 16, 1024, 2);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        mma_ss(tmem + kColS + kN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk2, 1);
-                }
-                tc_commit(&mbar_s);
+                tc_commit(&mbar_s[buf]);
             };
-            auto issue_pv = [&]() {
+            auto issue_pv = [&](int buf) {
                 // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
                 const uint64_t dv = make_desc(smem_u32(v_s), KBLK * 4, 512, 1);
 #pragma unroll
                 for (int k = 0; k < kN / 8; ++k)
-                    mma_ts(tmem + kColO, tmem + kColS + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv1, k ? 1u : 0u);
+                    mma_ts(tmem + kColO, tmem + kColS + buf * kN + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv1, k ? 1u : 0u);
+                // the second correction term joins the first one in columns [D,2D): both are small
 #pragma unroll
                 for (int k = 0; k < kN / 8; ++k)
                     mma_ts(tmem + kColO + D, tmem + kColPlo + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv2, 1);
                 tc_commit(&mbar_o);
             };
-            if (ntiles > 0) issue_qk();
+            if (ntiles > 0) issue_qk(0);
             for (int t = 0; t < ntiles; ++t) {
-                wait(&mbar_p, (uint32_t)(t & 1));        // P(t) in TMEM, V(t) and K(t+1) in shared memory
+                wait(&mbar_k, (uint32_t)(t & 1));        // K(t+1) is in shared memory
                 tc_fence_after();
-                issue_pv();
-                if (t + 1 < ntiles) issue_qk();          // runs after P V(t): MMAs of one thread execute in order
+                // MMAs of one thread execute in issue order: P V(t-1), which still reads P_hi from
+                // this S buffer, was issued before
+                if (t + 1 < ntiles) issue_qk((t + 1) & 1);
+                wait(&mbar_p, (uint32_t)(t & 1));        // P(t) is in TMEM, V(t) in shared memory
+                tc_fence_after();
+                issue_pv(t & 1);
             }
         }
         __syncwarp();
-    } else {
-        // ================= the 256 workers: softmax, staging, output ===========================
-        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
-        float o[DH];
-#pragma unroll
-        for (int d = 0; d < DH; ++d) o[d] = 0.0f;
-        float m = -1e30f, l = 0.0f, alpha_prev = 1.0f;
+        tc_fence_before();
+        __syncthreads();                         // the workers have collected the last O_ext
+        if (abort_flag && lane == 0) atomicExch(&g_tc_status, 1);
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
+        return;
+    }
 
-        // o = o * alpha_prev + (both parts of) O_tile of the previous tile, this worker's DH columns
-        auto collect_o = [&]() {
-            if (DH == 16) {
-                float a[16], c[16];
-                tmem_ld16(lane_base + kColO + half * 16, a);
-                tmem_ld16(lane_base + kColO + D + half * 16, c);
+    // ===================== the 128 workers: staging, softmax, output ==========================
+    // K/V staging role: 16-byte chunk sc of rows sr0 + p*RPP.  A tile first lands, as it lies in
+    // global memory, in a raw buffer (cp.async, no registers held while it is in flight); the
+    // worker that fetched a chunk is also the one that later splits it, so only its own
+    // cp.async groups need to be waited for.
+    const int sc = tid % CPR, sr0 = tid / CPR;
+    auto fetch_tile = [&](const float *__restrict__ plane, float *raw, int t) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+            const int r = sr0 + p * RPP;
+            const int j = t * kN + r;
+            const bool ok = t < ntiles && j < S;
+            cp_async16(raw + r * D + sc * 4, plane + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + sc * 4, ok);
+        }
+        cp_async_commit();
+    };
+    auto store_k = [&]() {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+            const int r = sr0 + p * RPP;
+            store_split(k_hi + (sc >> 3) * KBLK, k_lo + (sc >> 3) * KBLK, r, sc & 7,
+                        *reinterpret_cast<const float4 *>(k_raw + r * D + sc * 4));
+        }
+    };
+    auto store_v = [&]() {
+        float *blk = v_s + (sc >> 3) * KBLK;
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+            const int r = sr0 + p * RPP;
+            store_split_nmajor(blk, blk + DB * KBLK, r, sc & 7, *reinterpret_cast<const float4 *>(v_raw + r * D + sc * 4));
+        }
+    };
+
+    fetch_tile(K, k_raw, 0);
+    {
+        float4 qreg[CPR];
+        const bool ok = row < S;
+        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
+#pragma unroll
+        for (int c = 0; c < CPR; ++c) qreg[c] = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < CPR; ++c) {
+            float4 x = qreg[c];
+            x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
+            store_split(q_hi + (c >> 3) * QBLK, q_lo + (c >> 3) * QBLK, tid, c & 7, x);
+        }
+    }
+    cp_async_wait_all();
+    store_k();
+    // from here on two groups are in flight at the top of iteration t: K(t+1), then V(t)
+    fetch_tile(K, k_raw, 1);
+    fetch_tile(V, v_raw, 0);
+    proxy_fence();                               // generic-proxy writes -> visible to the tensor core's reads
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_slot;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 TMEM lanes
+
+    float o[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o[d] = 0.0f;
+    float m = -1e30f, l = 0.0f, alpha_prev = 1.0f;
+
+    // o = o * alpha_prev + (both parts of) O_ext of the previous tile
+    auto collect_o = [&]() {
+#pragma unroll
+        for (int g = 0; g < D / 16; ++g) {
+            float a[16], c[16];
+            tmem_ld16(lane_base + kColO + g * 16, a);
+            tmem_ld16(lane_base + kColO + D + g * 16, c);
+            tmem_wait_ld();
+#pragma unroll
+            for (int d = 0; d < 16; ++d) o[g * 16 + d] = fmaf(o[g * 16 + d], alpha_prev, a[d] + c[d]);
+        }
+    };
+
+    for (int t = 0; t < ntiles; ++t) {
+        const int buf = t & 1;
+        const int j0 = t * kN;
+        wait(&mbar_s[buf], (uint32_t)((t >> 1) & 1));     // S(t) is in TMEM; the K buffer is free again
+        tc_fence_after();
+        cp_async_wait_1();                                // K(t+1) has landed (V(t) may still be in flight)
+        if (t + 1 < ntiles) store_k();
+        proxy_fence();
+        arrive(&mbar_k);
+        fetch_tile(K, k_raw, t + 2);
+
+        // ---- softmax of this worker's row (tcgen05 ops are warp-wide: uniform control flow) ----
+        // Two sweeps over the 64 scores in TMEM, 16 at a time, so that only a few of them are
+        // in registers at once: the first finds the row maximum, the second exponentiates.
+        const bool warp_dead = CAUSAL && j0 > q0 + warp * 32 + 31;     // the tile is above the diagonal
+        const bool need_mask = (CAUSAL && j0 + kN - 1 > q0 + warp * 32) || j0 + kN > S;
+        const uint32_t s_addr = lane_base + kColS + buf * kN;
+        float mx = -INFINITY;
+        if (!warp_dead) {
+#pragma unroll
+            for (int g = 0; g < kN / 32; ++g) {
+                float v[32];
+                tmem_ld32(s_addr + g * 32, v);
                 tmem_wait_ld();
-#pragma unroll
-                for (int d = 0; d < 16; ++d) o[d] = fmaf(o[d], alpha_prev, a[d] + c[d]);
-            } else {
-                float a[32], c[32];
-                tmem_ld32(lane_base + kColO + half * 32, a);
-                tmem_ld32(lane_base + kColO + D + half * 32, c);
-                tmem_wait_ld();
-#pragma unroll
-                for (int d = 0; d < 32; ++d) o[d % DH] = fmaf(o[d % DH], alpha_prev, a[d] + c[d]);
-            }
-        };
-
-        for (int t = 0; t < ntiles; ++t) {
-            const int j0 = t * kN + half * 32;        // first key of this worker's 32 columns
-            wait(&mbar_s, (uint32_t)(t & 1));         // S(t) is in TMEM; the K buffer is free again
-            tc_fence_after();
-            if (t + 1 < ntiles) store_k(kreg);        // K(t+1) for the product that follows P V(t)
-            load_tile(K, t + 2, kreg);
-
-            // ---- softmax of this worker's 32 scores (tcgen05 ops are warp-wide: uniform control) ----
-            float s[32];
-            const bool warp_dead = CAUSAL && j0 > q0 + (warp & 3) * 32 + 31;   // all above the diagonal
-            float mx = -INFINITY;
-            if (!warp_dead) {
-                tmem_ld32(lane_base + kColS + half * 32, s);
-                {
-                    float c0[16], c1[16];
-                    tmem_ld16(lane_base + kColS + kN + half * 32, c0);
-                    tmem_ld16(lane_base + kColS + kN + half * 32 + 16, c1);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) { s[c] += c0[c]; s[16 + c] += c1[c]; }
-                }
-                if ((CAUSAL && j0 + 31 > q0 + (warp & 3) * 32) || j0 + 32 > S) {
+                if (need_mask) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
-                        const int j = j0 + c;
-                        if (j >= S || (CAUSAL && j > row)) s[c] = -INFINITY;
+                        const int j = j0 + g * 32 + c;
+                        if (j >= S || (CAUSAL && j > row)) v[c] = -INFINITY;
                     }
                 }
 #pragma unroll
-                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, s[c]);
+                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, v[c]);
             }
-            xchg[half][rloc] = mx;
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps of these rows
-            mx = fmaxf(mx, xchg[half ^ 1][rloc]);
-            const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
-            const float alpha = ex2_approx(m - mn);
-            m = mn;
-
-            // ---- the previous tile's P V: collect it; P_lo and the V buffer are free afterwards ----
-            if (t > 0) {
-                wait(&mbar_o, (uint32_t)((t - 1) & 1));
-                tc_fence_after();
-                collect_o();
-            }
-            alpha_prev = alpha;
-            store_v(vreg);                            // V(t)
-            load_tile(V, t + 1, vreg);
-
-            float psum = 0.0f;
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
-                float lo[16];
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const float p = warp_dead ? 0.0f : ex2_approx(s[g * 16 + c] - mn);   // masked scores give exactly 0
-                    psum += p;
-                    const float ph = tf32_hi(p);
-                    s[g * 16 + c] = ph;
-                    lo[c] = p - ph;
-                }
-                tmem_st16(lane_base + kColPlo + half * 32 + g * 16, lo);
-            }
-            l = fmaf(l, alpha, psum);
-            tmem_st32(lane_base + kColS + half * 32, s);       // P_hi over S, in place
-            tmem_wait_st();
-            proxy_fence();
-            tc_fence_before();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&mbar_p)) : "memory");
-            // the exchange slots are reused next iteration: the partner has read them before it
-            // arrives here, and nobody passes the next wait on mbar_s before all have arrived
         }
-        if (ntiles > 0) {
-            wait(&mbar_o, (uint32_t)((ntiles - 1) & 1));
+        const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
+        const float alpha = ex2_approx(m - mn);
+        m = mn;
+
+        // ---- the previous tile's P V: collect it; P_lo and the V buffer are free afterwards -------
+        if (t > 0) {
+            wait(&mbar_o, (uint32_t)((t - 1) & 1));
             tc_fence_after();
             collect_o();
         }
-        xchg[half][rloc] = l;                     // row sums of the two halves
-        asm volatile("bar.sync 5, %0;" ::"r"(kWorkers) : "memory");
-        if (!abort_flag && row < S) {
-            const float inv = 1.0f / fmaxf(l + xchg[half ^ 1][rloc], 1e-20f);
-            float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol + half * DH);
-#pragma unroll
-            for (int c = 0; c < DH / 4; ++c)
-                dst[c] = make_float4(o[c * 4 + 0] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
-        }
-    }
+        alpha_prev = alpha;
+        cp_async_wait_1();                        // V(t) has landed (K(t+2) may still be in flight)
+        store_v();
+        fetch_tile(V, v_raw, t + 1);
 
+        float psum = 0.0f;
+#pragma unroll
+        for (int g = 0; g < kN / 16; ++g) {
+            float v[16], lo[16];
+            if (!warp_dead) {
+                tmem_ld16(s_addr + g * 16, v);
+                tmem_wait_ld();
+            }
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const int j = j0 + g * 16 + c;
+                const bool dead = warp_dead || (need_mask && (j >= S || (CAUSAL && j > row)));
+                const float p = dead ? 0.0f : ex2_approx(v[c] - mn);
+                psum += p;
+                v[c] = tf32_hi(p);
+                lo[c] = p - v[c];
+            }
+            tmem_st16(s_addr + g * 16, v);                      // P_hi over S, in place
+            tmem_st16(lane_base + kColPlo + g * 16, lo);
+        }
+        l = fmaf(l, alpha, psum);
+        tmem_wait_st();
+        proxy_fence();
+        tc_fence_before();
+        arrive(&mbar_p);
+    }
+    cp_async_wait_all();
+    if (ntiles > 0) {
+        wait(&mbar_o, (uint32_t)((ntiles - 1) & 1));
+        tc_fence_after();
+        collect_o();
+    }
+    if (!abort_flag && row < S) {
+        const float inv = 1.0f / fmaxf(l, 1e-20f);
+        float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol);
+#pragma unroll
+        for (int c = 0; c < D / 4; ++c)
+            dst[c] = make_float4(o[c * 4 + 0] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
+    }
     tc_fence_before();
     __syncthreads();
-    if (abort_flag && tid == 0) atomicExch(&g_tc_status, 1);
-    if (is_mma_warp) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
-    }
 }
 
 template <int D, bool CAUSAL>
