@@ -54,6 +54,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJDIR, exist_ok=True)
     cc = nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    if os.environ.get("HIPGPT_TC_TRACE"):        # phase tracing of the tensor-core kernel (see attn_fwd_tc.cu)
+        extra.append("-DHIPGPT_TC_TRACE")
 
     def compile_one(src: str) -> str:
         obj = os.path.join(OBJDIR, os.path.splitext(src)[0] + ".o")

@@ -45,11 +45,32 @@ namespace {
 constexpr int kM = 128;          // query rows per block
 constexpr int kN = 64;           // keys per tile
 constexpr int kWorkers = 128;      // softmax / staging threads, one per query row
-constexpr int kThreads = kWorkers + 32;   // plus the warp that issues the MMAs
+// workers, then the warp that issues the MMAs, then the producers that stage K and V tiles
+// (64 threads for head_dim 32, 128 for head_dim 64: twice the bytes per tile)
+constexpr int tc_producers(int D) { return D == 32 ? 64 : 128; }
+constexpr int tc_threads(int D) { return kWorkers + 32 + tc_producers(D); }
 constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
 constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
 
 __device__ int g_tc_status = 0;   // 0 ok; 1 = an mbarrier wait ran out
+
+// Optional phase trace (build with -DHIPGPT_TC_TRACE): thread 0 and the issuing lane of block 0
+// store SM cycle counters at the marked points into a buffer given by hipgpt_debug_trace().
+// Layout: [0] start, [1] prologue done, [2 + 8*t + k] worker marks of tile t, [100 + 4*t + k]
+// issuing-lane marks, [99] end.  Compiled out by default.
+#ifdef HIPGPT_TC_TRACE
+__device__ long long *g_trace = nullptr;
+#define TC_TRACE_AT(i) do { if (g_trace && blockIdx.x == 0) g_trace[(i)] = clock64(); } while (0)
+// per block: [256 + 4*b] start ns, [+1] end ns, [+2] SM id
+__device__ __forceinline__ long long tc_gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ int tc_smid() { int r; asm volatile("mov.u32 %0, %%smid;" : "=r"(r)); return r; }
+#define TC_TRACE_BLOCK(k) do { if (g_trace && tid == 0) { g_trace[256 + 4 * blockIdx.x + (k)] = tc_gtime(); g_trace[256 + 4 * blockIdx.x + 2] = tc_smid(); } } while (0)
+#else
+#define TC_TRACE_BLOCK(k) do { } while (0)
+#define TC_TRACE_AT(i) do { } while (0)
+#endif
+#define TC_TRACE_W(k) do { if (tid == 0 && t < 12) TC_TRACE_AT(2 + 8 * t + (k)); } while (0)
+#define TC_TRACE_M(k) do { if (t < 12) TC_TRACE_AT(100 + 4 * t + (k)); } while (0)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -188,53 +209,55 @@ struct TcCfg {
     static constexpr uint32_t kColPlo = 128;              // 64 columns
     static constexpr uint32_t kColO = 192;                // [0,D): P_hi V_hi, [D,2D): P_hi V_lo + P_lo V_hi
     static constexpr uint32_t kTmemCols = (192 + 2 * D) <= 256 ? 256 : 512;
-    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 4 * DB * KBLK + 2 * kN * D;   // + raw K, V tiles
+    // Q hi/lo, K hi/lo, two V buffers of hi/lo, raw K and V tiles
+    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 2 * DB * KBLK + 4 * DB * KBLK + 2 * kN * D;
 };
 
 template <int D, bool CAUSAL>
-__global__ void __launch_bounds__(kThreads, D == 32 ? 2 : 1)   // head_dim 32: two blocks per SM
+__global__ void __launch_bounds__(tc_threads(D), D == 32 ? 2 : 1)   // head_dim 32: two blocks per SM
 mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
               float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
 {
     using C = TcCfg<D>;
     constexpr int DB = C::DB, QBLK = C::QBLK, KBLK = C::KBLK;
     constexpr int CPR = D / 4;                   // 16-byte chunks per row
-    constexpr int RPP = kWorkers / CPR;          // K/V rows staged per pass
-    constexpr int NP = kN / RPP;                 // passes = float4 registers per staged tile
+    constexpr int kProducers = tc_producers(D);
     constexpr uint32_t kColS = C::kColS, kColPlo = C::kColPlo, kColO = C::kColO;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment is what the swizzled layouts assume
     float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float *q_hi = base, *q_lo = q_hi + DB * QBLK;        // [DB][128][32] each
     float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + DB * KBLK;   // [DB][64][32] each
-    float *v_s = k_lo + DB * KBLK;               // [hi, lo][DB][64][32]: hi and lo blocks form one 2D-column operand
-    float *k_raw = v_s + 2 * DB * KBLK;          // [64][D] as it lies in global memory, filled by cp.async
+    float *v_s = k_lo + DB * KBLK;               // [2 buffers][hi, lo][DB][64][32]: hi and lo blocks form one 2D-column operand
+    float *k_raw = v_s + 4 * DB * KBLK;          // [64][D] as it lies in global memory, filled by cp.async
     float *v_raw = k_raw + kN * D;
-    __shared__ uint64_t mbar_s[2], mbar_k, mbar_p, mbar_o;
+    __shared__ uint64_t mbar_s[2], mbar_k, mbar_v[2], mbar_p, mbar_o;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool is_mma_warp = warp == kWorkers / 32;
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);   // heaviest first
     const int b = bh / H, h = bh % H;
     const size_t tok0 = (size_t)b * S;
     const size_t hcol = (size_t)h * D;
     const int q0 = qblk * kM;
-    const int row = q0 + tid;                    // a worker's query row = its TMEM lane
 
     const int kend = CAUSAL ? min(S, q0 + kM) : S;
     const int ntiles = (kend + kN - 1) / kN;
 
+    TC_TRACE_BLOCK(0);
     if (tid == 0) {
         abort_flag = 0;
         mbar_init(&mbar_s[0], 1);                // tcgen05.commit after Q K^T into S buffer 0 / 1
         mbar_init(&mbar_s[1], 1);
-        mbar_init(&mbar_k, kWorkers);            // every worker: next K tile staged
-        mbar_init(&mbar_p, kWorkers);            // every worker: P written, V staged
+        mbar_init(&mbar_k, kProducers);          // every producer: next K tile staged
+        mbar_init(&mbar_v[0], kProducers);       // every producer: V tile staged in buffer 0 / 1
+        mbar_init(&mbar_v[1], kProducers);
+        mbar_init(&mbar_p, kWorkers);            // every worker: P written
         mbar_init(&mbar_o, 1);                   // tcgen05.commit after P V
     }
+    __syncthreads();                             // barriers are initialised before anyone arrives on them
 
     // Bounded wait that gives up at once when another thread already gave up.
     auto wait = [&](uint64_t *bar, uint32_t parity) {
@@ -245,14 +268,14 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
     };
 
-    if (is_mma_warp) {
+    if (warp == kWorkers / 32) {
+        // ================= the issuing warp: one lane feeds the tensor core ====================
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         tc_fence_before();
-        __syncthreads();
+        __syncthreads();                         // Q, K(0), V(0) staged; TMEM allocated
         tc_fence_after();
         const uint32_t tmem = tmem_base_slot;
-        // ================= the issuing warp: one lane feeds the tensor core ====================
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc(kM, kN, 0);
             constexpr uint32_t idesc_pv1 = make_idesc(kM, 2 * D, 1);     // P_hi  x [V_hi | V_lo]
@@ -280,7 +303,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             };
             auto issue_pv = [&](int buf) {
                 // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
-                const uint64_t dv = make_desc(smem_u32(v_s), KBLK * 4, 512, 1);
+                const uint64_t dv = make_desc(smem_u32(v_s + buf * 2 * DB * KBLK), KBLK * 4, 512, 1);
 #pragma unroll
                 for (int k = 0; k < kN / 8; ++k)
                     mma_ts(tmem + kColO, tmem + kColS + buf * kN + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv1, k ? 1u : 0u);
@@ -292,13 +315,18 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             };
             if (ntiles > 0) issue_qk(0);
             for (int t = 0; t < ntiles; ++t) {
+                TC_TRACE_M(0);
                 wait(&mbar_k, (uint32_t)(t & 1));        // K(t+1) is in shared memory
                 tc_fence_after();
                 // MMAs of one thread execute in issue order: P V(t-1), which still reads P_hi from
                 // this S buffer, was issued before
+                TC_TRACE_M(1);
                 if (t + 1 < ntiles) issue_qk((t + 1) & 1);
-                wait(&mbar_p, (uint32_t)(t & 1));        // P(t) is in TMEM, V(t) in shared memory
+                TC_TRACE_M(2);
+                wait(&mbar_p, (uint32_t)(t & 1));                    // P(t) is in TMEM
+                wait(&mbar_v[t & 1], (uint32_t)((t >> 1) & 1));      // V(t) is in shared memory
                 tc_fence_after();
+                TC_TRACE_M(3);
                 issue_pv(t & 1);
             }
         }
@@ -310,65 +338,92 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         return;
     }
 
-    // ===================== the 128 workers: staging, softmax, output ==========================
-    // K/V staging role: 16-byte chunk sc of rows sr0 + p*RPP.  A tile first lands, as it lies in
-    // global memory, in a raw buffer (cp.async, no registers held while it is in flight); the
-    // worker that fetched a chunk is also the one that later splits it, so only its own
-    // cp.async groups need to be waited for.
-    const int sc = tid % CPR, sr0 = tid / CPR;
-    auto fetch_tile = [&](const float *__restrict__ plane, float *raw, int t) {
+    if (warp > kWorkers / 32) {
+        // ================= the producers: global -> split -> shared memory =====================
+        // A tile first lands, as it lies in global memory, in a raw buffer (cp.async, no
+        // registers held while it is in flight).  The producer that fetched a 16-byte chunk is
+        // also the one that later splits it, so it only waits for its own cp.async groups.
+        constexpr int RPP = kProducers / CPR;    // rows per pass
+        constexpr int NP = kN / RPP;             // passes per tile
+        const int ptid = tid - kWorkers - 32;
+        const int sc = ptid % CPR, sr0 = ptid / CPR;
+        auto fetch_tile = [&](const float *__restrict__ plane, float *raw, int t) {
 #pragma unroll
-        for (int p = 0; p < NP; ++p) {
-            const int r = sr0 + p * RPP;
-            const int j = t * kN + r;
-            const bool ok = t < ntiles && j < S;
-            cp_async16(raw + r * D + sc * 4, plane + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + sc * 4, ok);
-        }
-        cp_async_commit();
-    };
-    auto store_k = [&]() {
+            for (int p = 0; p < NP; ++p) {
+                const int r = sr0 + p * RPP;
+                const int j = t * kN + r;
+                const bool ok = t < ntiles && j < S;
+                cp_async16(raw + r * D + sc * 4, plane + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + sc * 4, ok);
+            }
+            cp_async_commit();
+        };
+        auto store_k = [&]() {
 #pragma unroll
-        for (int p = 0; p < NP; ++p) {
-            const int r = sr0 + p * RPP;
-            store_split(k_hi + (sc >> 3) * KBLK, k_lo + (sc >> 3) * KBLK, r, sc & 7,
-                        *reinterpret_cast<const float4 *>(k_raw + r * D + sc * 4));
-        }
-    };
-    auto store_v = [&]() {
-        float *blk = v_s + (sc >> 3) * KBLK;
+            for (int p = 0; p < NP; ++p) {
+                const int r = sr0 + p * RPP;
+                store_split(k_hi + (sc >> 3) * KBLK, k_lo + (sc >> 3) * KBLK, r, sc & 7,
+                            *reinterpret_cast<const float4 *>(k_raw + r * D + sc * 4));
+            }
+        };
+        auto store_v = [&](int buf) {
+            float *blk = v_s + buf * 2 * DB * KBLK + (sc >> 3) * KBLK;
 #pragma unroll
-        for (int p = 0; p < NP; ++p) {
-            const int r = sr0 + p * RPP;
-            store_split_nmajor(blk, blk + DB * KBLK, r, sc & 7, *reinterpret_cast<const float4 *>(v_raw + r * D + sc * 4));
+            for (int p = 0; p < NP; ++p) {
+                const int r = sr0 + p * RPP;
+                store_split_nmajor(blk, blk + DB * KBLK, r, sc & 7, *reinterpret_cast<const float4 *>(v_raw + r * D + sc * 4));
+            }
+        };
+        fetch_tile(K, k_raw, 0);
+        fetch_tile(V, v_raw, 0);
+        cp_async_wait_1();
+        store_k();
+        fetch_tile(K, k_raw, 1);
+        cp_async_wait_1();
+        store_v(0);
+        fetch_tile(V, v_raw, 1);                 // from here on: K(t+1), then V(t+1) in flight at the top of iteration t
+        proxy_fence();                           // generic-proxy writes -> visible to the tensor core's reads
+        arrive(&mbar_v[0]);
+        __syncthreads();
+        for (int t = 0; t < ntiles; ++t) {
+            wait(&mbar_s[t & 1], (uint32_t)((t >> 1) & 1));     // Q K(t)^T has completed: the K buffer is free
+            cp_async_wait_1();                                  // K(t+1) has landed
+            if (t + 1 < ntiles) store_k();
+            proxy_fence();
+            arrive(&mbar_k);
+            fetch_tile(K, k_raw, t + 2);
+            if (t > 0) wait(&mbar_o, (uint32_t)((t - 1) & 1)); // P V(t-1) has completed: its V buffer is free
+            cp_async_wait_1();                                  // V(t+1) has landed
+            if (t + 1 < ntiles) store_v((t + 1) & 1);
+            proxy_fence();
+            arrive(&mbar_v[(t + 1) & 1]);
+            fetch_tile(V, v_raw, t + 2);
         }
-    };
+        cp_async_wait_all();
+        __syncthreads();
+        return;
+    }
 
-    fetch_tile(K, k_raw, 0);
+    // ===================== the 128 workers: softmax and output ================================
+    const int row = q0 + tid;                    // a worker's query row = its TMEM lane
+    if (tid == 0) TC_TRACE_AT(0);
     {
-        float4 qreg[CPR];
         const bool ok = row < S;
         const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
 #pragma unroll
-        for (int c = 0; c < CPR; ++c) qreg[c] = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
         for (int c = 0; c < CPR; ++c) {
-            float4 x = qreg[c];
+            float4 x = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
             store_split(q_hi + (c >> 3) * QBLK, q_lo + (c >> 3) * QBLK, tid, c & 7, x);
         }
     }
-    cp_async_wait_all();
-    store_k();
-    // from here on two groups are in flight at the top of iteration t: K(t+1), then V(t)
-    fetch_tile(K, k_raw, 1);
-    fetch_tile(V, v_raw, 0);
-    proxy_fence();                               // generic-proxy writes -> visible to the tensor core's reads
+    proxy_fence();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
     const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 TMEM lanes
 
+    if (tid == 0) TC_TRACE_AT(1);
     float o[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) o[d] = 0.0f;
@@ -390,19 +445,18 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     for (int t = 0; t < ntiles; ++t) {
         const int buf = t & 1;
         const int j0 = t * kN;
-        wait(&mbar_s[buf], (uint32_t)((t >> 1) & 1));     // S(t) is in TMEM; the K buffer is free again
+        TC_TRACE_W(0);
+        wait(&mbar_s[buf], (uint32_t)((t >> 1) & 1));     // S(t) is in TMEM
         tc_fence_after();
-        cp_async_wait_1();                                // K(t+1) has landed (V(t) may still be in flight)
-        if (t + 1 < ntiles) store_k();
-        proxy_fence();
-        arrive(&mbar_k);
-        fetch_tile(K, k_raw, t + 2);
+        TC_TRACE_W(1);
 
         // ---- softmax of this worker's row (tcgen05 ops are warp-wide: uniform control flow) ----
-        // Two sweeps over the 64 scores in TMEM, 16 at a time, so that only a few of them are
-        // in registers at once: the first finds the row maximum, the second exponentiates.
+        // Two sweeps over the 64 scores in TMEM, so that only a few of them are in registers at
+        // once: the first finds the row maximum, the second exponentiates.
         const bool warp_dead = CAUSAL && j0 > q0 + warp * 32 + 31;     // the tile is above the diagonal
         const bool need_mask = (CAUSAL && j0 + kN - 1 > q0 + warp * 32) || j0 + kN > S;
+        // columns [0, nvalid) of this tile are visible to this row
+        const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : kN);
         const uint32_t s_addr = lane_base + kColS + buf * kN;
         float mx = -INFINITY;
         if (!warp_dead) {
@@ -413,10 +467,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                 tmem_wait_ld();
                 if (need_mask) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int j = j0 + g * 32 + c;
-                        if (j >= S || (CAUSAL && j > row)) v[c] = -INFINITY;
-                    }
+                    for (int c = 0; c < 32; ++c) v[c] = (g * 32 + c < nvalid) ? v[c] : -INFINITY;
                 }
 #pragma unroll
                 for (int c = 0; c < 32; ++c) mx = fmaxf(mx, v[c]);
@@ -425,50 +476,74 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
         const float alpha = ex2_approx(m - mn);
         m = mn;
+        TC_TRACE_W(3);
 
-        // ---- the previous tile's P V: collect it; P_lo and the V buffer are free afterwards -------
+        // ---- the previous tile's P V: collect it; P_lo is free afterwards ----------------------
         if (t > 0) {
             wait(&mbar_o, (uint32_t)((t - 1) & 1));
             tc_fence_after();
             collect_o();
         }
         alpha_prev = alpha;
-        cp_async_wait_1();                        // V(t) has landed (K(t+2) may still be in flight)
-        store_v();
-        fetch_tile(V, v_raw, t + 1);
+        TC_TRACE_W(4);
 
         float psum = 0.0f;
+        if (warp_dead) {
+            // nothing of this tile is visible to this warp's rows: P = 0
+            float z[16];
 #pragma unroll
-        for (int g = 0; g < kN / 16; ++g) {
-            float v[16], lo[16];
-            if (!warp_dead) {
+            for (int c = 0; c < 16; ++c) z[c] = 0.0f;
+#pragma unroll
+            for (int g = 0; g < kN / 16; ++g) {
+                tmem_st16(s_addr + g * 16, z);
+                tmem_st16(lane_base + kColPlo + g * 16, z);
+            }
+        } else if (need_mask) {
+#pragma unroll
+            for (int g = 0; g < kN / 16; ++g) {
+                float v[16], lo[16];
                 tmem_ld16(s_addr + g * 16, v);
                 tmem_wait_ld();
-            }
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const int j = j0 + g * 16 + c;
-                const bool dead = warp_dead || (need_mask && (j >= S || (CAUSAL && j > row)));
-                const float p = dead ? 0.0f : ex2_approx(v[c] - mn);
-                psum += p;
-                v[c] = tf32_hi(p);
-                lo[c] = p - v[c];
+                for (int c = 0; c < 16; ++c) {
+                    const float p = (g * 16 + c < nvalid) ? ex2_approx(v[c] - mn) : 0.0f;
+                    psum += p;
+                    v[c] = tf32_hi(p);
+                    lo[c] = p - v[c];
+                }
+                tmem_st16(s_addr + g * 16, v);                  // P_hi over S, in place
+                tmem_st16(lane_base + kColPlo + g * 16, lo);
             }
-            tmem_st16(s_addr + g * 16, v);                      // P_hi over S, in place
-            tmem_st16(lane_base + kColPlo + g * 16, lo);
+        } else {
+#pragma unroll
+            for (int g = 0; g < kN / 16; ++g) {
+                float v[16], lo[16];
+                tmem_ld16(s_addr + g * 16, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const float p = ex2_approx(v[c] - mn);
+                    psum += p;
+                    v[c] = tf32_hi(p);
+                    lo[c] = p - v[c];
+                }
+                tmem_st16(s_addr + g * 16, v);                  // P_hi over S, in place
+                tmem_st16(lane_base + kColPlo + g * 16, lo);
+            }
         }
         l = fmaf(l, alpha, psum);
         tmem_wait_st();
-        proxy_fence();
+        TC_TRACE_W(6);
         tc_fence_before();
         arrive(&mbar_p);
     }
-    cp_async_wait_all();
     if (ntiles > 0) {
         wait(&mbar_o, (uint32_t)((ntiles - 1) & 1));
         tc_fence_after();
         collect_o();
     }
+    if (tid == 0) TC_TRACE_AT(99);
+    TC_TRACE_BLOCK(1);
     if (!abort_flag && row < S) {
         const float inv = 1.0f / fmaxf(l, 1e-20f);
         float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol);
@@ -494,7 +569,7 @@ int launch_tc_cfg(const float *q, const float *k, const float *v, float *out, in
     const long long blocks = (long long)B * H * nqblk;
     if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
     const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<(unsigned)blocks, kThreads, smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
+    kern<<<(unsigned)blocks, tc_threads(D), smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
     return check_launch("mha_tc_kernel");
 }
 
@@ -512,6 +587,13 @@ int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
                                : launch_tc_cfg<64, false>(q, k, v, out, B, S, E, H, st);
     return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
 }
+
+#ifdef HIPGPT_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int hipgpt_debug_trace(long long *d_buf)
+{
+    return (int)cudaMemcpyToSymbol(g_trace, &d_buf, sizeof(d_buf));
+}
+#endif
 
 // Reads and clears the status word of the tensor-core kernels (synchronises the device).
 int tc_status_fetch(int *status)
