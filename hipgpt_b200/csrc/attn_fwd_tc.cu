@@ -46,9 +46,9 @@ constexpr int kM = 128;          // query rows per block
 constexpr int kN = 64;           // keys per tile
 constexpr int kWorkers = 128;      // softmax / staging threads, one per query row
 // workers, then the warp that issues the MMAs, then the producers that stage K and V tiles
-// (64 threads for head_dim 32, 128 for head_dim 64: twice the bytes per tile)
-constexpr int tc_producers(int D) { return D == 32 ? 64 : 128; }
-constexpr int tc_threads(int D) { return kWorkers + 32 + tc_producers(D); }
+// (224 threads in all: ptxas budgets registers per group of four warps, so 7 warps cost as 8)
+__host__ __device__ constexpr int tc_producers(int D) { return D <= 64 ? 64 : 128; }
+__host__ __device__ constexpr int tc_threads(int D) { return kWorkers + 32 + tc_producers(D); }
 constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
 constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
 
