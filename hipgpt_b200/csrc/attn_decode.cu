@@ -14,6 +14,8 @@
 
 #include <math.h>
 
+#include <mutex>
+
 namespace hipgpt {
 namespace {
 
@@ -260,3 +262,87 @@ int launch_decode(const float *q, const float *kc, const float *vc, float *out, 
 }
 
 }  // namespace hipgpt
+
+// ---------------------------------------------------------------------------------------------
+// hipgpt_mha_decode_noalloc: the split-context decode for callers that cannot bring scratch.
+//
+// Who that is.  The reference-shaped call sites of this library keep no state and own no spare
+// buffers: a launcher in HipGPT's style is `void launch_x(const float*, float*, ints...)`, and
+// the objects that call it (TransformerLayer) allocate a fixed set of activations once per
+// (batch, sequence) shape.  A generation loop built on them reaches this kernel once per token
+// and layer, from code that has nowhere to keep a scratch pointer and must not call cudaMalloc
+// there: an allocation in the token loop synchronises the whole device, and a serving process
+// that has handed all free memory to its own pool may simply be refused.  For those callers
+// the partial results live in the array below, which is part of the library image: every GPU
+// that loads the library sets these bytes aside until the process exits, so the size is modest.
+//
+// Rules of use
+//   * B*H*splits*(roundup4(D)+4)*4 bytes must fit in HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES; a
+//     larger request is refused with HIPGPT_ERR_SCRATCH (use hipgpt_mha_decode instead).
+//   * All calls on one GPU share the one array.  Two calls whose kernels may overlap on the
+//     GPU (different streams, no dependency between them) race on it; serialise them.
+//   * The array keeps what the last call left.  Nothing needs clearing: the first kernel
+//     writes every partial record the second one reads.
+//   * The first call on each device looks the array's device address up (a lookup, not an
+//     allocation).  Make that first call before any stream capture begins on that device.
+// ---------------------------------------------------------------------------------------------
+namespace hipgpt {
+namespace {
+
+constexpr size_t kNoAllocFloats = HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_decode_scratch[kNoAllocFloats];
+
+constexpr int kMaxDevices = 64;
+float *g_decode_scratch_addr[kMaxDevices];     // device address of the array, per device ordinal
+bool g_decode_scratch_known[kMaxDevices];
+std::mutex g_decode_scratch_mu;
+
+// Device address of g_decode_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress,
+// asked once per device while that device is current.
+int decode_scratch_address(float **addr)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(HIPGPT_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_decode_scratch_mu);
+    if (!g_decode_scratch_known[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_decode_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(HIPGPT_ERR_CUDA, "cudaGetSymbolAddress(decode scratch): %s", cudaGetErrorString(e));
+        g_decode_scratch_addr[dev] = static_cast<float *>(p);
+        g_decode_scratch_known[dev] = true;
+    }
+    *addr = g_decode_scratch_addr[dev];
+    return HIPGPT_OK;
+}
+
+}  // namespace
+}  // namespace hipgpt
+
+extern "C" int hipgpt_mha_decode_noalloc(const float *d_q, const float *d_kcache, const float *d_vcache, float *d_out,
+                                         int B, int H, int D, int ctx, int cap, void *stream)
+{
+    using namespace hipgpt;
+    if (B < 0 || H <= 0 || D <= 0 || ctx < 0 || cap < ctx)
+        return fail(HIPGPT_ERR_BAD_ARG, "bad size: B=%d H=%d D=%d ctx=%d cap=%d", B, H, D, ctx, cap);
+    if (B == 0) return HIPGPT_OK;
+    if (!d_q || !d_out || (ctx > 0 && (!d_kcache || !d_vcache)))
+        return fail(HIPGPT_ERR_NULL, "q, out and the caches must not be NULL");
+    const int ns = ctx > 0 ? decode_splits(B, H, D, ctx) : 1;
+    const size_t need = ns > 1 ? (size_t)B * H * ns * rec_stride(D) * sizeof(float) : 0;
+    if (need > (size_t)HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES)
+        return fail(HIPGPT_ERR_SCRATCH,
+                    "decode without allocation holds %zu bytes of partial results, this call needs %zu "
+                    "(B=%d H=%d D=%d ctx=%d); use hipgpt_mha_decode with caller scratch",
+                    (size_t)HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES, need, B, H, D, ctx);
+    float *scratch = nullptr;
+    const int rc = decode_scratch_address(&scratch);
+    if (rc != HIPGPT_OK) return rc;
+    if (D % 4 == 0 && ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_kcache) |
+                        reinterpret_cast<uintptr_t>(d_vcache) | reinterpret_cast<uintptr_t>(d_out)) & 15) != 0)
+        return fail(HIPGPT_ERR_BAD_ARG, "decode needs 16-byte aligned pointers");
+    return launch_decode(d_q, d_kcache, d_vcache, d_out, scratch, B, H, D, ctx, cap, ns, static_cast<cudaStream_t>(stream));
+}

@@ -117,6 +117,23 @@ HIPGPT_API int hipgpt_mha_decode(const float *d_q, const float *d_kcache, const 
                       int B, int H, int D, int ctx, int cap, void *stream);
 
 /*
+ * The same decode for callers that have no scratch to give and may not allocate (no counterpart
+ * in the reference).  HipGPT-style call sites are stateless `void launch_x(pointers, ints)`
+ * functions under objects that allocate a fixed set of buffers per shape; a per-token
+ * generation loop built on them has nowhere to keep a scratch pointer, and a cudaMalloc in
+ * that loop would synchronise the device (or be refused by a process whose pool already owns
+ * the memory).  Here the partial results live in a fixed array inside the library image
+ * (HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES on every GPU that loads the library, until exit).
+ *   - a call whose partial results do not fit returns HIPGPT_ERR_SCRATCH;
+ *   - all calls on a GPU share that array: calls that may overlap on the GPU race, order them;
+ *   - nothing is allocated or freed; the first call on each device looks up the array's
+ *     device address, so make that call before any stream capture starts on the device.
+ */
+#define HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES (1u << 20)
+HIPGPT_API int hipgpt_mha_decode_noalloc(const float *d_q, const float *d_kcache, const float *d_vcache, float *d_out,
+                              int B, int H, int D, int ctx, int cap, void *stream);
+
+/*
  * Batch-major sharding of the (batch x head) space over the GPUs of one box: rank r of
  * `world` owns batches [*b_begin, *b_end), a contiguous slab of every [B*S][E] plane and of
  * the output.  Every (batch, head) pair is independent (src/hip_kernels.cpp:269-277), so the
