@@ -52,7 +52,7 @@ __host__ __device__ constexpr int tc_threads(int D) { return kWorkers + 32 + tc_
 constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
 constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
 
-__device__ int g_tc_status = 0;   // 0 ok; 1 = an mbarrier wait ran out
+__device__ int g_tc_status = 0;   // 0 ok; otherwise the site code of the first wait that ran out
 
 // Optional phase trace (build with -DHIPGPT_TC_TRACE): thread 0 and the issuing lane of block 0
 // store SM cycle counters at the marked points into a buffer given by hipgpt_debug_trace().
@@ -260,9 +260,11 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     __syncthreads();                             // barriers are initialised before anyone arrives on them
 
     // Bounded wait that gives up at once when another thread already gave up.
-    auto wait = [&](uint64_t *bar, uint32_t parity) {
+    // `site` names the wait in the status word: 1 S ready (worker), 2 O ready (worker), 3 K staged,
+    // 5 P written, 6 V staged, 7 K buffer free (producer), 8 V buffer free (producer)
+    auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
         if (abort_flag) return;
-        if (!mbar_wait(bar, parity)) abort_flag = 1;
+        if (!mbar_wait(bar, parity)) { abort_flag = 1; atomicCAS(&g_tc_status, 0, site); }
     };
     auto arrive = [&](uint64_t *bar) {
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -316,15 +318,15 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             if (ntiles > 0) issue_qk(0);
             for (int t = 0; t < ntiles; ++t) {
                 TC_TRACE_M(0);
-                wait(&mbar_k, (uint32_t)(t & 1));        // K(t+1) is in shared memory
+                wait(&mbar_k, (uint32_t)(t & 1), 3);        // K(t+1) is in shared memory
                 tc_fence_after();
                 // MMAs of one thread execute in issue order: P V(t-1), which still reads P_hi from
                 // this S buffer, was issued before
                 TC_TRACE_M(1);
                 if (t + 1 < ntiles) issue_qk((t + 1) & 1);
                 TC_TRACE_M(2);
-                wait(&mbar_p, (uint32_t)(t & 1));                    // P(t) is in TMEM
-                wait(&mbar_v[t & 1], (uint32_t)((t >> 1) & 1));      // V(t) is in shared memory
+                wait(&mbar_p, (uint32_t)(t & 1), 5);                    // P(t) is in TMEM
+                wait(&mbar_v[t & 1], (uint32_t)((t >> 1) & 1), 6);      // V(t) is in shared memory
                 tc_fence_after();
                 TC_TRACE_M(3);
                 issue_pv(t & 1);
@@ -333,7 +335,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         __syncwarp();
         tc_fence_before();
         __syncthreads();                         // the workers have collected the last O_ext
-        if (abort_flag && lane == 0) atomicExch(&g_tc_status, 1);
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
         return;
     }
@@ -385,13 +386,13 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         arrive(&mbar_v[0]);
         __syncthreads();
         for (int t = 0; t < ntiles; ++t) {
-            wait(&mbar_s[t & 1], (uint32_t)((t >> 1) & 1));     // Q K(t)^T has completed: the K buffer is free
+            wait(&mbar_s[t & 1], (uint32_t)((t >> 1) & 1), 7);     // Q K(t)^T has completed: the K buffer is free
             cp_async_wait_1();                                  // K(t+1) has landed
             if (t + 1 < ntiles) store_k();
             proxy_fence();
             arrive(&mbar_k);
             fetch_tile(K, k_raw, t + 2);
-            if (t > 0) wait(&mbar_o, (uint32_t)((t - 1) & 1)); // P V(t-1) has completed: its V buffer is free
+            if (t > 0) wait(&mbar_o, (uint32_t)((t - 1) & 1), 8); // P V(t-1) has completed: its V buffer is free
             cp_async_wait_1();                                  // V(t+1) has landed
             if (t + 1 < ntiles) store_v((t + 1) & 1);
             proxy_fence();
@@ -432,13 +433,13 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     // o = o * alpha_prev + (both parts of) O_ext of the previous tile
     auto collect_o = [&]() {
 #pragma unroll
-        for (int g = 0; g < D / 16; ++g) {
-            float a[16], c[16];
-            tmem_ld16(lane_base + kColO + g * 16, a);
-            tmem_ld16(lane_base + kColO + D + g * 16, c);
+        for (int g = 0; g < D / 32; ++g) {
+            float a[32], c[32];
+            tmem_ld32(lane_base + kColO + g * 32, a);            // both loads in flight, one wait
+            tmem_ld32(lane_base + kColO + D + g * 32, c);
             tmem_wait_ld();
 #pragma unroll
-            for (int d = 0; d < 16; ++d) o[g * 16 + d] = fmaf(o[g * 16 + d], alpha_prev, a[d] + c[d]);
+            for (int d = 0; d < 32; ++d) o[g * 32 + d] = fmaf(o[g * 32 + d], alpha_prev, a[d] + c[d]);
         }
     };
 
@@ -446,7 +447,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         const int buf = t & 1;
         const int j0 = t * kN;
         TC_TRACE_W(0);
-        wait(&mbar_s[buf], (uint32_t)((t >> 1) & 1));     // S(t) is in TMEM
+        wait(&mbar_s[buf], (uint32_t)((t >> 1) & 1), 1);     // S(t) is in TMEM
         tc_fence_after();
         TC_TRACE_W(1);
 
@@ -460,18 +461,25 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         const uint32_t s_addr = lane_base + kColS + buf * kN;
         float mx = -INFINITY;
         if (!warp_dead) {
+            float v0[32], v1[32];
+            tmem_ld32(s_addr, v0);                // both loads in flight, one wait
+            tmem_ld32(s_addr + 32, v1);
+            tmem_wait_ld();
+            if (need_mask) {
 #pragma unroll
-            for (int g = 0; g < kN / 32; ++g) {
-                float v[32];
-                tmem_ld32(s_addr + g * 32, v);
-                tmem_wait_ld();
-                if (need_mask) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = (g * 32 + c < nvalid) ? v[c] : -INFINITY;
+                for (int c = 0; c < 32; ++c) {
+                    v0[c] = (c < nvalid) ? v0[c] : -INFINITY;
+                    v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
                 }
-#pragma unroll
-                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, v[c]);
             }
+            // four independent chains instead of one of depth 64
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                m4[(c >> 1) & 1] = fmaxf(m4[(c >> 1) & 1], fmaxf(v0[c], v0[c + 1]));
+                m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
+            }
+            mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
         const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
         const float alpha = ex2_approx(m - mn);
@@ -480,7 +488,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
 
         // ---- the previous tile's P V: collect it; P_lo is free afterwards ----------------------
         if (t > 0) {
-            wait(&mbar_o, (uint32_t)((t - 1) & 1));
+            wait(&mbar_o, (uint32_t)((t - 1) & 1), 2);
             tc_fence_after();
             collect_o();
         }
@@ -515,21 +523,31 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                 tmem_st16(lane_base + kColPlo + g * 16, lo);
             }
         } else {
+            // chunks of 16 scores; the next chunk's load is in flight while this one is computed,
+            // and the row sum runs in four independent chains
+            float cur[16], nxt[16];
+            float ps4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            tmem_ld16(s_addr, cur);
 #pragma unroll
             for (int g = 0; g < kN / 16; ++g) {
-                float v[16], lo[16];
-                tmem_ld16(s_addr + g * 16, v);
                 tmem_wait_ld();
+                if (g + 1 < kN / 16) tmem_ld16(s_addr + (g + 1) * 16, nxt);
+                float lo[16];
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float p = ex2_approx(v[c] - mn);
-                    psum += p;
-                    v[c] = tf32_hi(p);
-                    lo[c] = p - v[c];
+                    const float p = ex2_approx(cur[c] - mn);
+                    ps4[c & 3] += p;
+                    cur[c] = tf32_hi(p);
+                    lo[c] = p - cur[c];
                 }
-                tmem_st16(s_addr + g * 16, v);                  // P_hi over S, in place
+                tmem_st16(s_addr + g * 16, cur);                // P_hi over S, in place
                 tmem_st16(lane_base + kColPlo + g * 16, lo);
+                if (g + 1 < kN / 16) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) cur[c] = nxt[c];
+                }
             }
+            psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
         }
         l = fmaf(l, alpha, psum);
         tmem_wait_st();
@@ -538,7 +556,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         arrive(&mbar_p);
     }
     if (ntiles > 0) {
-        wait(&mbar_o, (uint32_t)((ntiles - 1) & 1));
+        wait(&mbar_o, (uint32_t)((ntiles - 1) & 1), 2);
         tc_fence_after();
         collect_o();
     }
