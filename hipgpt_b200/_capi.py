@@ -29,6 +29,10 @@ SIGNATURES = {
     "hipgpt_mha_decode_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "hipgpt_mha_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_gpt_weight_count": (C.c_longlong, [_i, _i, _i, _i, _i, _i]),
+    "hipgpt_gpt_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i, _i, _i, _i, _i]),
+    "hipgpt_gpt_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "hipgpt_gpt_destroy": (None, [_vp]),
     "hipgpt_shard_range": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     "hipgpt_probe_fma": (_i, [_vp, _i, _i, C.POINTER(C.c_double), _vp]),
     "hipgpt_kernel_status": (_i, [C.POINTER(_i)]),

@@ -68,3 +68,29 @@ CONFIGS = {
     "c3": dict(B=16, H=8, S=1024, D=64, seed=2, scale=1.0),
     "c5": dict(B=64, H=16, S=2048, D=64, seed=4, scale=1.0),
 }
+
+
+# The whole-model benchmark shape (HipGPT's default hyper-parameters, src/train_gpt.cpp:175-183).
+GPT_DEFAULT = dict(V=5000, S=256, E=256, L=8, H=8, F=1024)
+
+
+def gpt_weights(seed: int, V: int, S: int, E: int, L: int, H: int, F: int, std: float = 0.02) -> np.ndarray:
+    """Random-init weight blob in the reference's checkpoint order (src/gpt_model.cpp:355-420,
+    src/transformer_layer.cpp:312-405, integer headers left out): matrices N(0, std^2), biases 0,
+    layer-norm gamma 1 and beta 0."""
+    parts = []
+    stream = 0
+
+    def mat(*shape):
+        nonlocal stream
+        stream += 1
+        return normal(seed, shape, std, stream=stream).reshape(-1)
+
+    parts.append(mat(V, E))
+    parts.append(mat(S, E))
+    for _ in range(L):
+        parts += [mat(E, 3 * E), mat(E, E), mat(E, F), mat(F, E)]
+        parts += [np.zeros(3 * E, np.float32), np.zeros(E, np.float32), np.zeros(F, np.float32), np.zeros(E, np.float32)]
+        parts += [np.ones(E, np.float32), np.zeros(E, np.float32), np.ones(E, np.float32), np.zeros(E, np.float32)]
+    parts.append(mat(E, V))
+    return np.ascontiguousarray(np.concatenate(parts), dtype=np.float32)

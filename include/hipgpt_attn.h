@@ -134,6 +134,28 @@ HIPGPT_API int hipgpt_mha_decode_noalloc(const float *d_q, const float *d_kcache
                               int B, int H, int D, int ctx, int cap, void *stream);
 
 /*
+ * Greedy generation with a HipGPT-shaped model on one GPU, KV-cache form: the host driver that
+ * stands where GPTModel::generate's loop stands (src/gpt_model.cpp:248-353) for the benchmark's
+ * whole-model shape.  Every token runs once, at its own position, against cached keys and
+ * values (hipgpt_mha_decode's kernels); no dropout; the next id is the first maximum of the
+ * logits and stays on the device.  The reference instead re-runs a left-padded, unmasked window
+ * of max_seq_len tokens per token and samples on the host; results of the two are not comparable.
+ *   h_weights  fp32 blob in the reference's checkpoint order without its integer headers
+ *              (src/gpt_model.cpp:355-420, src/transformer_layer.cpp:312-405): tok_emb[V][E],
+ *              pos_emb[S][E], per layer {Wqkv[E][3E], Wo[E][E], W1[E][F], W2[F][E], bqkv, bo, b1, b2,
+ *              attn gamma, beta, ffn gamma, beta}, out_proj[E][V]; hipgpt_gpt_weight_count floats
+ *   h_prompts  [B][n_prompt] token ids; h_out_ids [B][n_new]; h_logits_last [B][V] or NULL
+ *   ms_prompt / ms_decode  (optional) device time of the n_prompt prompt steps / the n_new-1 later steps
+ */
+typedef struct hipgpt_gpt hipgpt_gpt;
+HIPGPT_API long long hipgpt_gpt_weight_count(int V, int S, int E, int L, int H, int F);
+HIPGPT_API int hipgpt_gpt_create(hipgpt_gpt **out, const float *h_weights, int V, int S, int E, int L, int H, int F,
+                      int max_batch);
+HIPGPT_API int hipgpt_gpt_generate(hipgpt_gpt *g, const int *h_prompts, int B, int n_prompt, int n_new, int *h_out_ids,
+                        float *h_logits_last, float *ms_prompt, float *ms_decode);
+HIPGPT_API void hipgpt_gpt_destroy(hipgpt_gpt *g);
+
+/*
  * Batch-major sharding of the (batch x head) space over the GPUs of one box: rank r of
  * `world` owns batches [*b_begin, *b_end), a contiguous slab of every [B*S][E] plane and of
  * the output.  Every (batch, head) pair is independent (src/hip_kernels.cpp:269-277), so the

@@ -140,3 +140,23 @@ def ref_weighted_sum(P, V, B, S, D):
     out = np.zeros((B, S, D), dtype=np.float32)
     ref_lib().ref_weighted_sum(_f(P), _f(V), _f(out), B, S, D)
     return out
+
+
+# ---- whole-model greedy generation (KV-cache form) --------------------------------------
+def gpt_weight_count(V, S, E, L, H, F) -> int:
+    fn = oracle_lib(True).oracle_gpt_weight_count
+    fn.restype = C.c_longlong
+    return int(fn(V, S, E, L, H, F))
+
+
+def gpt_generate(weights: np.ndarray, V, S, E, L, H, F, prompts: np.ndarray, n_new: int, fma: bool = True):
+    """Greedy ids [B, n_new] and the logits [B, V] of the last step."""
+    B, n_prompt = prompts.shape
+    prompts = np.ascontiguousarray(prompts, dtype=np.int32)
+    out = np.zeros((B, n_new), dtype=np.int32)
+    logits = np.zeros((B, V), dtype=np.float32)
+    rc = oracle_lib(fma).oracle_gpt_generate(_f(weights), V, S, E, L, H, F, _i(prompts), B, n_prompt, n_new,
+                                             _i(out), _f(logits))
+    if rc < 0:
+        raise ValueError("oracle rejected the generation request")
+    return out, logits
