@@ -132,7 +132,8 @@ def cpu_leg(cfg, causal, seconds, steps=None, warmup=0):
     from oracle import bindings as ob
     B, H, S, D = cfg["B"], cfg["H"], cfg["S"], cfg["D"]
     E = H * D
-    threads = ob.num_threads()
+    threads = os.cpu_count() or ob.num_threads()     # every host thread, whatever OMP_NUM_THREADS the launcher set
+    ob.set_num_threads(threads)
     one = synth.qkv_planes(cfg["seed"], 1, S, E, cfg["scale"])
     t0 = time.perf_counter()
     ob.mha(one, 1, S, E, H, causal=bool(causal))
@@ -163,6 +164,32 @@ def cpu_leg(cfg, causal, seconds, steps=None, warmup=0):
         info["reference_build_noncausal"] = {"tflops": flops_of(1, H, S, D, False) / tr / 1e12,
                                              "sample": "1 batch item, launch_multihead_attention compiled for the host"}
     return tf, info
+
+
+def decode_leg():
+    """Greedy KV-cache generation with the default model shape (E=256 L=8 H=8 F=1024 V=5000 S=256,
+    random-init weights N(0, 0.02) seed 3, 8 prompts of 16 ids, 128 new tokens): tokens/s of the GPU
+    driver, ids checked against the CPU oracle of the same arithmetic, which is timed beside it."""
+    from hipgpt_b200.generation import GptDecoder
+    from oracle import bindings as ob
+    cfg = dict(synth.GPT_DEFAULT)
+    B, n_prompt, n_new = 8, 16, 128
+    w = synth.gpt_weights(3, **cfg)
+    prompts = synth.token_ids(3, (B, n_prompt), cfg["V"])
+    dec = GptDecoder(w, **cfg, max_batch=B)
+    dec.generate(prompts, n_new)                               # warm-up
+    ids, _, ms_prompt, ms_decode = dec.generate(prompts, n_new)
+    dec.close()
+    ob.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    ref_ids, _ = ob.gpt_generate(w, **cfg, prompts=prompts, n_new=n_new, fma=True)
+    t_cpu = time.perf_counter() - t0
+    return {"metric": "greedy_decode_tokens_per_s", "value": B * n_new / ((ms_prompt + ms_decode) * 1e-3), "unit": "tok/s",
+            "steady_state_tokens_per_s": B * (n_new - 1) / (ms_decode * 1e-3), "us_per_step": ms_decode / (n_new - 1) * 1e3,
+            "ids_equal_cpu_oracle": bool(np.array_equal(ids, ref_ids)),
+            "cpu_oracle_tokens_per_s": B * n_new / t_cpu, "cpu_threads": os.cpu_count(),
+            "config": {"model": "E=256 L=8 H=8 F=1024 V=5000 S=256, ReLU MLP, fp32", "batch": B, "prompt_len": n_prompt, "new_tokens": n_new,
+                       "mode": "causal KV-cache decode (the reference re-runs the padded window per token; not comparable)"}}
 
 
 def run_reference(args):
@@ -354,6 +381,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         _, info = cpu_leg(cfg, args.causal, seconds=args.cpu_seconds)
         line["cpu_baseline"] = info
+        line["decode"] = decode_leg()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
