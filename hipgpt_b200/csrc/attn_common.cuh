@@ -47,8 +47,10 @@ int launch_mha_generic(const float *q, const float *k, const float *v, float *ou
 int launch_sdp(const float *Q, const float *K, float *scores, int B, int S, int D, cudaStream_t st);
 int launch_softmax_rows(const float *scores, float *out, int B, int S, cudaStream_t st);
 int launch_weighted_sum(const float *P, const float *V, float *out, int B, int S, int D, cudaStream_t st);
+// pos_ptr (optional): device int holding ctx - 1; when given it overrides ctx inside the kernels,
+// so that one captured launch serves every step of a generation loop.
 int launch_decode(const float *q, const float *kc, const float *vc, float *out, float *scratch,
-                  int B, int H, int D, int ctx, int cap, int nsplit, cudaStream_t st);
+                  int B, int H, int D, int ctx, int cap, int nsplit, cudaStream_t st, const int *pos_ptr = nullptr);
 int decode_splits(int B, int H, int D, int ctx);
 
 }  // namespace hipgpt

@@ -47,8 +47,9 @@ template <int LPK>
 __global__ void __launch_bounds__(kThreads)
 decode_split_vec_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
                         float *__restrict__ out, float *__restrict__ scratch,
-                        int H, int D, int ctx, int cap, int nsplit, float qscale)
+                        int H, int D, int ctx, int cap, int nsplit, float qscale, const int *__restrict__ pos_ptr)
 {
+    if (pos_ptr) ctx = *pos_ptr + 1;               // context length kept on the device (replayed CUDA graphs)
     constexpr int KPW = 32 / LPK;                  // keys per warp and step
     __shared__ float sm[kWarps][LPK][6];
     const int bh = blockIdx.y, split = blockIdx.x;
@@ -133,8 +134,9 @@ decode_split_vec_kernel(const float *__restrict__ q, const float *__restrict__ k
 __global__ void __launch_bounds__(kThreads)
 decode_split_scalar_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
                            float *__restrict__ out, float *__restrict__ scratch,
-                           int H, int D, int ctx, int cap, int nsplit, float qscale)
+                           int H, int D, int ctx, int cap, int nsplit, float qscale, const int *__restrict__ pos_ptr)
 {
+    if (pos_ptr) ctx = *pos_ptr + 1;
     constexpr int EPL = kMaxD / 32;
     __shared__ float sm_o[kWarps][kMaxD];
     __shared__ float sm_ml[kWarps][2];
@@ -239,7 +241,7 @@ int decode_splits(int B, int H, int D, int ctx)
 }
 
 int launch_decode(const float *q, const float *kc, const float *vc, float *out, float *scratch,
-                  int B, int H, int D, int ctx, int cap, int nsplit, cudaStream_t st)
+                  int B, int H, int D, int ctx, int cap, int nsplit, cudaStream_t st, const int *pos_ptr)
 {
     if (D > kMaxD) return fail(HIPGPT_ERR_UNSUPPORTED, "head_dim %d exceeds %d", D, kMaxD);
     if ((long long)B * H > 65535) return fail(HIPGPT_ERR_BAD_ARG, "B*H = %lld exceeds 65535 rows per launch", (long long)B * H);
@@ -247,13 +249,13 @@ int launch_decode(const float *q, const float *kc, const float *vc, float *out, 
     const dim3 grid(nsplit, B * H);
     if (D % 4 == 0 && D <= 128) {
         if (D <= 32)
-            decode_split_vec_kernel<8><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale);
+            decode_split_vec_kernel<8><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
         else if (D <= 64)
-            decode_split_vec_kernel<16><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale);
+            decode_split_vec_kernel<16><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
         else
-            decode_split_vec_kernel<32><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale);
+            decode_split_vec_kernel<32><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
     } else {
-        decode_split_scalar_kernel<<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale);
+        decode_split_scalar_kernel<<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
     }
     int rc = check_launch("decode_split_kernel");
     if (rc != HIPGPT_OK || nsplit == 1) return rc;

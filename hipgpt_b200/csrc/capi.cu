@@ -76,10 +76,13 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
 
 // Device workspace of the host-buffer call: grows to the largest request, one per process.
 struct Workspace {
+    static constexpr int kStreams = 3;     // copies in, kernels, copies out
+    static constexpr int kChunks = 8;      // pieces a call is cut into
     std::mutex mu;
     float *dev = nullptr;
     size_t bytes = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t streams[kStreams] = {nullptr, nullptr, nullptr};
+    cudaEvent_t in_ready[kChunks] = {}, out_ready[kChunks] = {};
     int device = -1;
 };
 Workspace g_ws;
@@ -132,27 +135,58 @@ int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
         if (g_ws.dev) cudaFree(g_ws.dev);
         g_ws.dev = nullptr;
         g_ws.bytes = 0;
-        if (g_ws.stream && g_ws.device != dev) { cudaStreamDestroy(g_ws.stream); g_ws.stream = nullptr; }
+        if (g_ws.device != dev) {
+            for (int i = 0; i < Workspace::kStreams; ++i) if (g_ws.streams[i]) { cudaStreamDestroy(g_ws.streams[i]); g_ws.streams[i] = nullptr; }
+            for (int i = 0; i < Workspace::kChunks; ++i) {
+                if (g_ws.in_ready[i]) { cudaEventDestroy(g_ws.in_ready[i]); g_ws.in_ready[i] = nullptr; }
+                if (g_ws.out_ready[i]) { cudaEventDestroy(g_ws.out_ready[i]); g_ws.out_ready[i] = nullptr; }
+            }
+        }
         e = cudaMalloc(&g_ws.dev, need);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMalloc(%zu): %s", need, cudaGetErrorString(e));
         g_ws.bytes = need;
         g_ws.device = dev;
     }
-    if (!g_ws.stream) {
-        e = cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking);
-        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+    for (int i = 0; i < Workspace::kStreams; ++i)
+        if (!g_ws.streams[i]) {
+            e = cudaStreamCreateWithFlags(&g_ws.streams[i], cudaStreamNonBlocking);
+            if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+        }
+    for (int i = 0; i < Workspace::kChunks; ++i) {
+        if (!g_ws.in_ready[i]) e = cudaEventCreateWithFlags(&g_ws.in_ready[i], cudaEventDisableTiming);
+        if (e == cudaSuccess && !g_ws.out_ready[i]) e = cudaEventCreateWithFlags(&g_ws.out_ready[i], cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e));
     }
+    // Batches are independent, so the call is cut into chunks of batches that flow through three
+    // streams: host-to-device copies, kernels, device-to-host copies.  PCIe moves both directions
+    // at once, so the call takes about as long as its larger direction alone.
+    cudaStream_t s_in = g_ws.streams[0], s_k = g_ws.streams[1], s_out = g_ws.streams[2];
     float *d_qkv = g_ws.dev, *d_out = g_ws.dev + 3 * plane, *d_probs = h_probs ? g_ws.dev + 4 * plane : nullptr;
-    e = cudaMemcpyAsync(d_qkv, h_qkv, 3 * plane * sizeof(float), cudaMemcpyHostToDevice, g_ws.stream);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to device: %s", cudaGetErrorString(e));
-    const int krc = mha_dispatch(d_qkv, d_qkv + plane, d_qkv + 2 * plane, d_out, d_probs, B, S, E, H, causal,
-                                 HIPGPT_ALGO_AUTO, 0, g_ws.stream);
-    if (krc != HIPGPT_OK) return krc;
-    e = cudaMemcpyAsync(h_out, d_out, plane * sizeof(float), cudaMemcpyDeviceToHost, g_ws.stream);
-    if (e == cudaSuccess && h_probs)
-        e = cudaMemcpyAsync(h_probs, d_probs, nprobs * sizeof(float), cudaMemcpyDeviceToHost, g_ws.stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(g_ws.stream);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to host: %s", cudaGetErrorString(e));
+    const int nchunks = B < Workspace::kChunks ? B : Workspace::kChunks;
+    for (int c = 0; c < nchunks; ++c) {
+        int b0, b1;
+        hipgpt_shard_range(B, nchunks, c, &b0, &b1);
+        const size_t off = (size_t)b0 * S * E, cnt = (size_t)(b1 - b0) * S * E;
+        for (int pl = 0; pl < 3 && e == cudaSuccess; ++pl)
+            e = cudaMemcpyAsync(d_qkv + pl * plane + off, h_qkv + pl * plane + off, cnt * sizeof(float), cudaMemcpyHostToDevice, s_in);
+        if (e == cudaSuccess) e = cudaEventRecord(g_ws.in_ready[c], s_in);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s_k, g_ws.in_ready[c], 0);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to device: %s", cudaGetErrorString(e));
+        float *pr = d_probs ? d_probs + (size_t)b0 * H * S * S : nullptr;
+        const int krc = mha_dispatch(d_qkv + off, d_qkv + plane + off, d_qkv + 2 * plane + off, d_out + off, pr,
+                                     b1 - b0, S, E, H, causal, HIPGPT_ALGO_AUTO, 0, s_k);
+        if (krc != HIPGPT_OK) { cudaDeviceSynchronize(); return krc; }
+        e = cudaEventRecord(g_ws.out_ready[c], s_k);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s_out, g_ws.out_ready[c], 0);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_out + off, d_out + off, cnt * sizeof(float), cudaMemcpyDeviceToHost, s_out);
+        if (e == cudaSuccess && h_probs)
+            e = cudaMemcpyAsync(h_probs + (size_t)b0 * H * S * S, pr, (size_t)(b1 - b0) * H * S * S * sizeof(float), cudaMemcpyDeviceToHost, s_out);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to host: %s", cudaGetErrorString(e));
+    }
+    e = cudaStreamSynchronize(s_out);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s_k);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s_in);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "host-buffer call: %s", cudaGetErrorString(e));
     return HIPGPT_OK;
 }
 
@@ -160,9 +194,12 @@ void hipgpt_release_workspace(void)
 {
     std::lock_guard<std::mutex> lock(g_ws.mu);
     if (g_ws.dev) cudaFree(g_ws.dev);
-    if (g_ws.stream) cudaStreamDestroy(g_ws.stream);
+    for (int i = 0; i < Workspace::kStreams; ++i) if (g_ws.streams[i]) { cudaStreamDestroy(g_ws.streams[i]); g_ws.streams[i] = nullptr; }
+    for (int i = 0; i < Workspace::kChunks; ++i) {
+        if (g_ws.in_ready[i]) { cudaEventDestroy(g_ws.in_ready[i]); g_ws.in_ready[i] = nullptr; }
+        if (g_ws.out_ready[i]) { cudaEventDestroy(g_ws.out_ready[i]); g_ws.out_ready[i] = nullptr; }
+    }
     g_ws.dev = nullptr;
-    g_ws.stream = nullptr;
     g_ws.bytes = 0;
     g_ws.device = -1;
 }

@@ -14,7 +14,7 @@
 // of the projection, the next id is the first maximum of the logits and stays on the device.
 //
 // Arithmetic is fixed so that a CPU restatement can follow it bit for bit outside the
-// attention: matmuls accumulate k ascending with fused multiply-add inside 8 equal segments of K
+// attention: matmuls accumulate k ascending with fused multiply-add inside 16 equal segments of K
 // whose partial sums are added in ascending order;
 // layer-norm sums are 32 lane-strided partial sums joined by a butterfly; nothing else is
 // contracted (explicit __fmul_rn / __fadd_rn), divisions and square roots are IEEE.
@@ -32,32 +32,32 @@ namespace {
 
 constexpr int kRowsPerBlock = 8;     // activation rows a matmul block keeps in shared memory
 
-__global__ void embed_kernel(const int *__restrict__ ids, const float *__restrict__ tok, const float *__restrict__ pos,
-                             float *__restrict__ x, int p, int E, int V)
+// x[b] = tok[id] + pos[p]; the id is the prompt's while p is inside it, afterwards the id picked
+// by the previous step.  p is read from device memory so that one captured step serves all.
+__global__ void embed_kernel(const int *__restrict__ prompts, int n_prompt, const int *__restrict__ ids,
+                             const int *__restrict__ pos_ptr, const float *__restrict__ tok, const float *__restrict__ pos,
+                             float *__restrict__ x, int E, int V)
 {
     const int b = blockIdx.x;
-    const int id = ids[b];
+    const int p = *pos_ptr;
+    const int id = p < n_prompt ? prompts[(size_t)b * n_prompt + p] : ids[b];
     const bool ok = id >= 0 && id < V;
     for (int e = threadIdx.x; e < E; e += blockDim.x)
         x[(size_t)b * E + e] = ok ? __fadd_rn(tok[(size_t)id * E + e], pos[(size_t)p * E + e]) : 0.0f;
 }
 
-// one warp per row
-__global__ void layernorm_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ g,
-                                 const float *__restrict__ b, int rows, int E)
+// Layer norm of one row held in shared memory, by one warp, in place.  Sums are 32 lane-strided
+// partial sums joined by a butterfly; nothing is contracted.
+__device__ __forceinline__ void layernorm_row(float *row, const float *__restrict__ g, const float *__restrict__ b, int E, int lane)
 {
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= rows) return;
-    const float *xr = x + (size_t)row * E;
     float s = 0.0f;
-    for (int i = lane; i < E; i += 32) s = __fadd_rn(s, xr[i]);
+    for (int i = lane; i < E; i += 32) s = __fadd_rn(s, row[i]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, off));
     const float mean = __fdiv_rn(s, (float)E);
     float q = 0.0f;
     for (int i = lane; i < E; i += 32) {
-        const float v = __fsub_rn(xr[i], mean);
+        const float v = __fsub_rn(row[i], mean);
         q = __fadd_rn(q, __fmul_rn(v, v));
     }
 #pragma unroll
@@ -65,28 +65,44 @@ __global__ void layernorm_kernel(const float *__restrict__ x, float *__restrict_
     const float var = __fdiv_rn(q, (float)E);
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, 1e-5f)));
     for (int i = lane; i < E; i += 32)
-        y[(size_t)row * E + i] = __fadd_rn(__fmul_rn(__fmul_rn(g[i], __fsub_rn(xr[i], mean)), inv), b[i]);
+        row[i] = __fadd_rn(__fmul_rn(__fmul_rn(g[i], __fsub_rn(row[i], mean)), inv), b[i]);
 }
 
-// out[m][n] = res[m][n] + relu?( (sum_k A[m][k] * W[k][n]) + bias[n] ) for up to kRowsPerBlock rows.
-// A block owns 32 columns; its 8 warps split K into 8 equal segments (kSeg), lane = column, so a
-// warp reads 128 contiguous bytes of W per k.  Inside a segment the terms are accumulated k
-// ascending into one accumulator with fused multiply-add; the 8 partial sums are then added in
-// ascending segment order.  (The reference's kernel keeps a single accumulator over all of K,
-// src/hip_kernels.cpp:127-140; the fixed 8-way split trades that order for eight times the loads
-// in flight, and the CPU oracle of the generation path follows the same order.)
-constexpr int kSeg = 8;
+// Where a matmul's outputs go: plain [M][ldo] (with optional residual), or the Q/K/V scatter of
+// the attention projection (columns [0,E) -> q[m], [E,2E) -> K cache row p, [2E,3E) -> V cache row p).
+struct MatmulOut {
+    float *out;
+    int ldo;
+    const float *res;
+    float *q, *kc, *vc;          // non-null q selects the scatter
+    const int *pos_ptr;
+    int cap, E;
+};
+
+// y = relu?( LN?(A) * W + bias ) (+ res) for up to kRowsPerBlock rows.  A block owns 32 columns; its
+// 16 warps split K into 16 equal segments (kSeg), lane = column, so a warp reads 128 contiguous
+// bytes of W per k.  Inside a segment the terms are accumulated k ascending into one accumulator
+// with fused multiply-add; the 16 partial sums are then added in ascending segment order.  (The
+// reference's kernel keeps a single accumulator over all of K, src/hip_kernels.cpp:127-140; the
+// fixed 16-way split trades that order for sixteen times the loads in flight, and the CPU oracle of
+// the generation path follows the same order.)  With ln_g the rows are layer-normalised in
+// shared memory first (one warp per row; every block repeats it, which is cheaper than a launch).
+constexpr int kSeg = 16;
 __global__ void __launch_bounds__(32 * kSeg)
-matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict__ W, const float *__restrict__ bias,
-                   const float *res, float *out, int ldo, int M, int K, int N, int relu)
+matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict__ ln_g, const float *__restrict__ ln_b,
+                   const float *__restrict__ W, const float *__restrict__ bias, MatmulOut o, int M, int K, int N, int relu)
 {
     extern __shared__ float a_s[];                 // [rows][K] activations, then [kSeg][rows][32] partial sums
     const int m0 = blockIdx.y * kRowsPerBlock;
     const int rows = min(kRowsPerBlock, M - m0);
     float *part = a_s + kRowsPerBlock * K;
+    const int seg = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < rows * K; i += blockDim.x) a_s[i] = A[(size_t)(m0 + i / K) * lda + i % K];
     __syncthreads();
-    const int seg = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (ln_g) {
+        if (seg < rows) layernorm_row(a_s + seg * K, ln_g, ln_b, K, lane);
+        __syncthreads();
+    }
     const int n = blockIdx.x * 32 + lane;
     const int klen = K / kSeg, k0 = seg * klen;
     float acc[kRowsPerBlock];
@@ -95,12 +111,12 @@ matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict
     if (n < N) {
         const float *wp = W + (size_t)k0 * N + n;
         int k = 0;
-        for (; k + 8 <= klen; k += 8) {
-            float w[8];
+        for (; k + 16 <= klen; k += 16) {
+            float w[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) w[u] = __ldg(wp + (size_t)(k + u) * N);      // eight loads in flight
+            for (int u = 0; u < 16; ++u) w[u] = __ldg(wp + (size_t)(k + u) * N);     // sixteen loads in flight
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
+            for (int u = 0; u < 16; ++u)
 #pragma unroll
                 for (int m = 0; m < kRowsPerBlock; ++m)
                     if (m < rows) acc[m] = fmaf(a_s[m * K + k0 + k + u], w[u], acc[m]);
@@ -115,34 +131,32 @@ matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict
 #pragma unroll
     for (int m = 0; m < kRowsPerBlock; ++m) part[(seg * kRowsPerBlock + m) * 32 + lane] = acc[m];
     __syncthreads();
-    // 256 threads finish the 8 x 32 outputs of the block: thread -> (row, column)
+    // the first 256 threads finish the 8 x 32 outputs of the block: thread -> (row, column)
     const int m = threadIdx.x >> 5;
-    if (m < rows && n < N) {
+    if (m < kRowsPerBlock && m < rows && n < N) {
         float v = part[m * 32 + lane];
 #pragma unroll
         for (int s2 = 1; s2 < kSeg; ++s2) v = __fadd_rn(v, part[(s2 * kRowsPerBlock + m) * 32 + lane]);
         if (bias) v = __fadd_rn(v, bias[n]);
         if (relu) v = fmaxf(0.0f, v);
-        if (res) v = __fadd_rn(res[(size_t)(m0 + m) * ldo + n], v);
-        out[(size_t)(m0 + m) * ldo + n] = v;
+        const int row = m0 + m;
+        if (o.q) {
+            const int p = *o.pos_ptr;
+            if (n < o.E) o.q[(size_t)row * o.E + n] = v;
+            else if (n < 2 * o.E) o.kc[((size_t)row * o.cap + p) * o.E + (n - o.E)] = v;
+            else o.vc[((size_t)row * o.cap + p) * o.E + (n - 2 * o.E)] = v;
+        } else {
+            if (o.res) v = __fadd_rn(o.res[(size_t)row * o.ldo + n], v);
+            o.out[(size_t)row * o.ldo + n] = v;
+        }
     }
 }
 
-// rows of the [B][3E] projection: q -> contiguous [B][E]; k, v -> cache position p
-__global__ void kv_append_kernel(const float *__restrict__ qkv, float *__restrict__ q, float *__restrict__ kc,
-                                 float *__restrict__ vc, int p, int cap, int E)
-{
-    const int b = blockIdx.x;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        q[(size_t)b * E + e] = qkv[(size_t)b * 3 * E + e];
-        kc[((size_t)b * cap + p) * E + e] = qkv[(size_t)b * 3 * E + E + e];
-        vc[((size_t)b * cap + p) * E + e] = qkv[(size_t)b * 3 * E + 2 * E + e];
-    }
-}
-
-// first maximum of each row (lowest index wins ties), stored to ids_next[b] and to out_ids[b*stride+col]
+// first maximum of each row (lowest index wins ties) -> ids_next[b]; recorded in out_ids once the
+// prompt's last position has been reached
 __global__ void __launch_bounds__(256)
-argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ ids_next, int *__restrict__ out_ids, int stride, int col)
+argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ ids_next, int *__restrict__ out_ids, int n_new,
+              int n_prompt, const int *__restrict__ pos_ptr)
 {
     __shared__ float sv[256];
     __shared__ int si[256];
@@ -171,9 +185,12 @@ argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ ids_nex
     }
     if (threadIdx.x == 0) {
         ids_next[b] = si[0];
-        if (out_ids && col >= 0) out_ids[(size_t)b * stride + col] = si[0];
+        const int col = *pos_ptr - (n_prompt - 1);
+        if (col >= 0 && col < n_new) out_ids[(size_t)b * n_new + col] = si[0];
     }
 }
+
+__global__ void advance_pos_kernel(int *pos_ptr) { *pos_ptr += 1; }
 
 struct LayerW {
     const float *wqkv, *wo, *w1, *w2, *bqkv, *bo, *b1, *b2, *g1, *be1, *g2, *be2;
@@ -190,9 +207,12 @@ struct GptDecoder {
     float *d_x = nullptr, *d_h = nullptr, *d_qkv = nullptr, *d_q = nullptr, *d_att = nullptr, *d_ff = nullptr, *d_logits = nullptr;
     float *d_scratch = nullptr;
     size_t scratch_bytes = 0;
-    int *d_ids = nullptr, *d_out = nullptr;
-    int out_cap = 0;
+    int *d_ids = nullptr, *d_out = nullptr, *d_pos = nullptr, *d_prompts = nullptr;
+    int out_cap = 0, prompt_cap = 0;
     cudaStream_t stream = nullptr;
+    // one step of generation captured as a CUDA graph; valid for (graph_B, graph_n_prompt, graph_n_new)
+    cudaGraphExec_t graph = nullptr;
+    int graph_B = 0, graph_n_prompt = 0, graph_n_new = 0;
 };
 
 namespace {
@@ -210,45 +230,59 @@ long long weight_count(int V, int S, int E, int L, int F)
     return (long long)V * E + (long long)S * E + L * per_layer + (long long)E * V;
 }
 
-int matmul(const GptDecoder &g, const float *A, int lda, const float *W, const float *bias, const float *res, float *out,
-           int ldo, int M, int K, int N, int relu)
+int matmul(const GptDecoder &g, const float *A, int lda, const float *ln_g, const float *ln_b, const float *W,
+           const float *bias, const MatmulOut &o, int M, int K, int N, int relu)
 {
     const dim3 grid((N + 31) / 32, (M + kRowsPerBlock - 1) / kRowsPerBlock);
     const size_t smem = (size_t)kRowsPerBlock * (K + kSeg * 32) * sizeof(float);
-    matmul_rows_kernel<<<grid, 32 * kSeg, smem, g.stream>>>(A, lda, W, bias, res, out, ldo, M, K, N, relu);
+    matmul_rows_kernel<<<grid, 32 * kSeg, smem, g.stream>>>(A, lda, ln_g, ln_b, W, bias, o, M, K, N, relu);
     return check_launch("matmul_rows_kernel");
 }
 
-// one token position p for all B sequences; ids are read from g.d_ids, the next ids written back
-int step(GptDecoder &g, int B, int p, int out_col, int out_stride)
+MatmulOut plain_out(float *out, int ldo, const float *res) { return MatmulOut{out, ldo, res, nullptr, nullptr, nullptr, nullptr, 0, 0}; }
+
+// One token position for all B sequences, every launch reading the position from g.d_pos: embed,
+// L x {LN+QKV projection scattered into q and the caches, split-context attention, output
+// projection + residual, LN+FF1+ReLU, FF2 + residual}, logits, first-maximum pick, position + 1.
+int enqueue_step(GptDecoder &g, int B, int n_prompt, int n_new)
 {
     const int E = g.E, F = g.F, V = g.V, D = g.E / g.H;
-    embed_kernel<<<B, 128, 0, g.stream>>>(g.d_ids, g.tok, g.pos, g.d_x, p, E, V);
+    embed_kernel<<<B, 128, 0, g.stream>>>(g.d_prompts, n_prompt, g.d_ids, g.d_pos, g.tok, g.pos, g.d_x, E, V);
     int rc = check_launch("embed_kernel");
     if (rc) return rc;
-    const int ln_blocks = (B + 3) / 4;
+    const int ns = decode_splits(B, g.H, D, g.S);        // fixed for the whole graph; short contexts leave splits empty
     for (int l = 0; l < g.L; ++l) {
         const LayerW &w = g.lw[l];
         float *kc = g.d_kc + (size_t)l * g.max_batch * g.S * E;
         float *vc = g.d_vc + (size_t)l * g.max_batch * g.S * E;
-        layernorm_kernel<<<ln_blocks, 128, 0, g.stream>>>(g.d_x, g.d_h, w.g1, w.be1, B, E);
-        if ((rc = check_launch("layernorm_kernel"))) return rc;
-        if ((rc = matmul(g, g.d_h, E, w.wqkv, w.bqkv, nullptr, g.d_qkv, 3 * E, B, E, 3 * E, 0))) return rc;
-        kv_append_kernel<<<B, 128, 0, g.stream>>>(g.d_qkv, g.d_q, kc, vc, p, g.S, E);
-        if ((rc = check_launch("kv_append_kernel"))) return rc;
-        const int ns = decode_splits(B, g.H, D, p + 1);
-        if ((rc = launch_decode(g.d_q, kc, vc, g.d_att, g.d_scratch, B, g.H, D, p + 1, g.S, ns, g.stream))) return rc;
-        if ((rc = matmul(g, g.d_att, E, w.wo, w.bo, g.d_x, g.d_x, E, B, E, E, 0))) return rc;
-        layernorm_kernel<<<ln_blocks, 128, 0, g.stream>>>(g.d_x, g.d_h, w.g2, w.be2, B, E);
-        if ((rc = check_launch("layernorm_kernel"))) return rc;
-        if ((rc = matmul(g, g.d_h, E, w.w1, w.b1, nullptr, g.d_ff, F, B, E, F, 1))) return rc;
-        if ((rc = matmul(g, g.d_ff, F, w.w2, w.b2, g.d_x, g.d_x, E, B, F, E, 0))) return rc;
+        const MatmulOut scatter{nullptr, 0, nullptr, g.d_q, kc, vc, g.d_pos, g.S, E};
+        if ((rc = matmul(g, g.d_x, E, w.g1, w.be1, w.wqkv, w.bqkv, scatter, B, E, 3 * E, 0))) return rc;
+        if ((rc = launch_decode(g.d_q, kc, vc, g.d_att, g.d_scratch, B, g.H, D, 1, g.S, ns, g.stream, g.d_pos))) return rc;
+        if ((rc = matmul(g, g.d_att, E, nullptr, nullptr, w.wo, w.bo, plain_out(g.d_x, E, g.d_x), B, E, E, 0))) return rc;
+        if ((rc = matmul(g, g.d_x, E, w.g2, w.be2, w.w1, w.b1, plain_out(g.d_ff, F, nullptr), B, E, F, 1))) return rc;
+        if ((rc = matmul(g, g.d_ff, F, nullptr, nullptr, w.w2, w.b2, plain_out(g.d_x, E, g.d_x), B, F, E, 0))) return rc;
     }
-    if (out_col >= 0) {
-        if ((rc = matmul(g, g.d_x, E, g.wout, nullptr, nullptr, g.d_logits, V, B, E, V, 0))) return rc;
-        argmax_kernel<<<B, 256, 0, g.stream>>>(g.d_logits, V, g.d_ids, g.d_out, out_stride, out_col);
-        if ((rc = check_launch("argmax_kernel"))) return rc;
-    }
+    if ((rc = matmul(g, g.d_x, E, nullptr, nullptr, g.wout, nullptr, plain_out(g.d_logits, V, nullptr), B, E, V, 0))) return rc;
+    argmax_kernel<<<B, 256, 0, g.stream>>>(g.d_logits, V, g.d_ids, g.d_out, n_new, n_prompt, g.d_pos);
+    if ((rc = check_launch("argmax_kernel"))) return rc;
+    advance_pos_kernel<<<1, 1, 0, g.stream>>>(g.d_pos);
+    return check_launch("advance_pos_kernel");
+}
+
+int build_graph(GptDecoder &g, int B, int n_prompt, int n_new)
+{
+    if (g.graph && g.graph_B == B && g.graph_n_prompt == n_prompt && g.graph_n_new == n_new) return HIPGPT_OK;
+    if (g.graph) { cudaGraphExecDestroy(g.graph); g.graph = nullptr; }
+    cudaGraph_t captured = nullptr;
+    CUDA_OK(cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = enqueue_step(g, B, n_prompt, n_new);
+    const cudaError_t e = cudaStreamEndCapture(g.stream, &captured);
+    if (rc != HIPGPT_OK) { if (captured) cudaGraphDestroy(captured); return rc; }
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    const cudaError_t e2 = cudaGraphInstantiate(&g.graph, captured, 0);
+    cudaGraphDestroy(captured);
+    if (e2 != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e2));
+    g.graph_B = B; g.graph_n_prompt = n_prompt; g.graph_n_new = n_new;
     return HIPGPT_OK;
 }
 
@@ -268,7 +302,7 @@ long long hipgpt_gpt_weight_count(int V, int S, int E, int L, int H, int F)
 int hipgpt_gpt_create(hipgpt_gpt **out, const float *h_weights, int V, int S, int E, int L, int H, int F, int max_batch)
 {
     if (!out || !h_weights) return fail(HIPGPT_ERR_NULL, "out and h_weights must not be NULL");
-    if (V <= 0 || S <= 0 || E <= 0 || L <= 0 || H <= 0 || F <= 0 || E % H || max_batch <= 0 || E % 8 || F % 8 || F > 6000 || E > 6000)
+    if (V <= 0 || S <= 0 || E <= 0 || L <= 0 || H <= 0 || F <= 0 || E % H || max_batch <= 0 || E % 16 || F % 16 || F > 6000 || E > 6000)
         return fail(HIPGPT_ERR_BAD_ARG, "bad model shape V=%d S=%d E=%d L=%d H=%d F=%d batch=%d", V, S, E, L, H, F, max_batch);
     GptDecoder *g = new (std::nothrow) GptDecoder();
     if (!g) return fail(HIPGPT_ERR_CUDA, "out of host memory");
@@ -302,6 +336,8 @@ int hipgpt_gpt_create(hipgpt_gpt **out, const float *h_weights, int V, int S, in
     TRY(cudaMalloc(&g->d_ff, (size_t)max_batch * F * sizeof(float)));
     TRY(cudaMalloc(&g->d_logits, (size_t)max_batch * V * sizeof(float)));
     TRY(cudaMalloc(&g->d_ids, (size_t)max_batch * sizeof(int)));
+    TRY(cudaMalloc(&g->d_pos, sizeof(int)));
+    TRY(cudaMemsetAsync(g->d_ids, 0, (size_t)max_batch * sizeof(int), g->stream));
     size_t sb = 0;
     for (int ctx = 1; ctx <= S; ++ctx) {
         const size_t b = hipgpt_mha_decode_scratch_bytes(max_batch, H, E / H, ctx);
@@ -334,30 +370,31 @@ int hipgpt_gpt_generate(hipgpt_gpt *handle, const int *h_prompts, int B, int n_p
     if (g->out_cap < B * n_new) {
         if (g->d_out) cudaFree(g->d_out);
         g->d_out = nullptr;
+        g->graph_B = 0;                      // the captured step holds the old pointer
         CUDA_OK(cudaMalloc(&g->d_out, (size_t)B * n_new * sizeof(int)));
         g->out_cap = B * n_new;
     }
-    int *d_prompts = nullptr;
-    CUDA_OK(cudaMalloc(&d_prompts, (size_t)B * n_prompt * sizeof(int)));
-    CUDA_OK(cudaMemcpyAsync(d_prompts, h_prompts, (size_t)B * n_prompt * sizeof(int), cudaMemcpyHostToDevice, g->stream));
+    if (g->prompt_cap < B * n_prompt) {
+        if (g->d_prompts) cudaFree(g->d_prompts);
+        g->d_prompts = nullptr;
+        g->graph_B = 0;
+        CUDA_OK(cudaMalloc(&g->d_prompts, (size_t)B * n_prompt * sizeof(int)));
+        g->prompt_cap = B * n_prompt;
+    }
+    int rc = build_graph(*g, B, n_prompt, n_new);
+    if (rc != HIPGPT_OK) return rc;
+    CUDA_OK(cudaMemcpyAsync(g->d_prompts, h_prompts, (size_t)B * n_prompt * sizeof(int), cudaMemcpyHostToDevice, g->stream));
+    CUDA_OK(cudaMemsetAsync(g->d_pos, 0, sizeof(int), g->stream));
     cudaEvent_t e0, e1, e2;
     CUDA_OK(cudaEventCreate(&e0)); CUDA_OK(cudaEventCreate(&e1)); CUDA_OK(cudaEventCreate(&e2));
     CUDA_OK(cudaEventRecord(e0, g->stream));
-    int rc = HIPGPT_OK;
-    for (int p = 0; p < n_prompt && rc == HIPGPT_OK; ++p) {
-        // column p of the prompts becomes this step's ids
-        CUDA_OK(cudaMemcpy2DAsync(g->d_ids, sizeof(int), d_prompts + p, (size_t)n_prompt * sizeof(int), sizeof(int), B,
-                                  cudaMemcpyDeviceToDevice, g->stream));
-        rc = step(*g, B, p, p == n_prompt - 1 ? 0 : -1, n_new);
-    }
+    for (int p = 0; p < n_prompt; ++p) CUDA_OK(cudaGraphLaunch(g->graph, g->stream));
     CUDA_OK(cudaEventRecord(e1, g->stream));
-    for (int i = 1; i < n_new && rc == HIPGPT_OK; ++i) rc = step(*g, B, n_prompt - 1 + i, i, n_new);
+    for (int i = 1; i < n_new; ++i) CUDA_OK(cudaGraphLaunch(g->graph, g->stream));
     CUDA_OK(cudaEventRecord(e2, g->stream));
-    if (rc == HIPGPT_OK) {
-        CUDA_OK(cudaMemcpyAsync(h_out_ids, g->d_out, (size_t)B * n_new * sizeof(int), cudaMemcpyDeviceToHost, g->stream));
-        if (h_logits_last)
-            CUDA_OK(cudaMemcpyAsync(h_logits_last, g->d_logits, (size_t)B * g->V * sizeof(float), cudaMemcpyDeviceToHost, g->stream));
-    }
+    CUDA_OK(cudaMemcpyAsync(h_out_ids, g->d_out, (size_t)B * n_new * sizeof(int), cudaMemcpyDeviceToHost, g->stream));
+    if (h_logits_last)
+        CUDA_OK(cudaMemcpyAsync(h_logits_last, g->d_logits, (size_t)B * g->V * sizeof(float), cudaMemcpyDeviceToHost, g->stream));
     CUDA_OK(cudaStreamSynchronize(g->stream));
     float a = 0.f, b = 0.f;
     cudaEventElapsedTime(&a, e0, e1);
@@ -365,7 +402,6 @@ int hipgpt_gpt_generate(hipgpt_gpt *handle, const int *h_prompts, int B, int n_p
     if (ms_prompt) *ms_prompt = a;
     if (ms_decode) *ms_decode = b;
     cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
-    cudaFree(d_prompts);
     return rc;
 }
 
@@ -375,8 +411,11 @@ void hipgpt_gpt_destroy(hipgpt_gpt *handle)
     if (!g) return;
     float *bufs[] = {g->d_weights, g->d_kc, g->d_vc, g->d_x, g->d_h, g->d_qkv, g->d_q, g->d_att, g->d_ff, g->d_logits, g->d_scratch};
     for (float *b : bufs) if (b) cudaFree(b);
+    if (g->graph) cudaGraphExecDestroy(g->graph);
     if (g->d_ids) cudaFree(g->d_ids);
     if (g->d_out) cudaFree(g->d_out);
+    if (g->d_pos) cudaFree(g->d_pos);
+    if (g->d_prompts) cudaFree(g->d_prompts);
     if (g->stream) cudaStreamDestroy(g->stream);
     delete g;
 }

@@ -20,7 +20,7 @@
  * a left-padded window of max_seq_len tokens without mask for every token.
  *
  * Reductions whose order matters for bit-level agreement with the GPU implementation are
- * written in that implementation's order: matmuls accumulate k ascending inside 8 segments of K
+ * written in that implementation's order: matmuls accumulate k ascending inside 16 segments of K
  * (fused multiply-add when built with ORACLE_FMA=1) and add the segments in order; layer-norm sums run as 32 lane-strided partial
  * sums followed by a butterfly (lane ^ 16, 8, 4, 2, 1), the order of a warp reduction.
  */
@@ -114,7 +114,7 @@ static void layer_norm(const float *x, float *y, const float *g, const float *b,
  * accumulator and adds the partial sums in ascending segment order; so does this loop.  (The
  * reference keeps one accumulator over all of K, src/hip_kernels.cpp:127-140; the difference is a
  * reordering of the same terms.) */
-#define KSEG 8
+#define KSEG 16
 static void matvec(const float *a, const float *W, const float *bias, const float *res, float *out, int K, int N, int relu)
 {
     const int nseg = (K % KSEG == 0) ? KSEG : 1;
