@@ -39,7 +39,7 @@ int launch_mha_rows(const float *q, const float *k, const float *v, float *out, 
                     int B, int S, int E, int H, int causal, int warps, cudaStream_t st);
 bool mha_rows_supports(int D);
 int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
-                  int B, int S, int E, int H, int causal, cudaStream_t st);
+                  int B, int S, int E, int H, int causal, cudaStream_t st, int variant = 0);
 bool mha_tc_supports(int D);
 int tc_status_fetch(int *status);
 int launch_mha_generic(const float *q, const float *k, const float *v, float *out, float *probs,

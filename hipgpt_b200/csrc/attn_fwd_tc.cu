@@ -43,12 +43,6 @@ namespace hipgpt {
 namespace {
 
 constexpr int kM = 128;          // query rows per block
-constexpr int kN = 64;           // keys per tile
-constexpr int kWorkers = 128;      // softmax / staging threads, one per query row
-// workers, then the warp that issues the MMAs, then the producers that stage K and V tiles
-// (224 threads in all: ptxas budgets registers per group of four warps, so 7 warps cost as 8)
-__host__ __device__ constexpr int tc_producers(int D) { return D <= 64 ? 64 : 128; }
-__host__ __device__ constexpr int tc_threads(int D) { return kWorkers + 32 + tc_producers(D); }
 constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
 constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
 
@@ -199,41 +193,52 @@ __device__ __forceinline__ void store_split_nmajor(float *hi_blk, float *lo_blk,
     *reinterpret_cast<float4 *>(lo_blk + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
 }
 
-template <int D>
+// Shape of one kernel variant.
+//   D        head_dim (32 or 64)
+//   KN       keys per tile (64 or 128)
+//   HALVES   workers per query row (1 or 2): each worker handles 64 consecutive keys of a tile and
+//            D/HALVES output columns, so KN = 64 * HALVES
+//   PRODUCERS threads that stage K and V
+template <int D, int KN, int PRODUCERS>
 struct TcCfg {
+    static constexpr int HALVES = KN / 64;
+    static constexpr int WORKERS = kM * HALVES;
+    static constexpr int THREADS = WORKERS + 32 + PRODUCERS;   // workers, the issuing warp, producers
     static constexpr int DB = D / 32;                     // 32-float column blocks per row
     static constexpr int QBLK = kM * 32;                  // floats per [128][32] block
-    static constexpr int KBLK = kN * 32;                  // floats per [64][32] block
-    // TMEM columns: S (two buffers) | P_lo | O_ext
-    static constexpr uint32_t kColS = 0;                  // [0,64) and [64,128): scores, later P_hi in place
-    static constexpr uint32_t kColPlo = 128;              // 64 columns
-    static constexpr uint32_t kColO = 192;                // [0,D): P_hi V_hi, [D,2D): P_hi V_lo + P_lo V_hi
-    static constexpr uint32_t kTmemCols = (192 + 2 * D) <= 256 ? 256 : 512;
+    static constexpr int KBLK = KN * 32;                  // floats per [KN][32] block
+    // TMEM columns: S (two buffers of KN) | P_lo (KN) | O_ext (2D)
+    static constexpr uint32_t kColS = 0;                  // scores, later P_hi in place
+    static constexpr uint32_t kColPlo = 2 * KN;
+    static constexpr uint32_t kColO = 3 * KN;             // [0,D): P_hi V_hi, [D,2D): P_hi V_lo + P_lo V_hi
+    static constexpr uint32_t kTmemCols = (3 * KN + 2 * D) <= 256 ? 256 : 512;
+    static constexpr int BLOCKS_PER_SM = kTmemCols == 256 ? 2 : 1;
     // Q hi/lo, K hi/lo, two V buffers of hi/lo, raw K and V tiles
-    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 2 * DB * KBLK + 4 * DB * KBLK + 2 * kN * D;
+    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 2 * DB * KBLK + 4 * DB * KBLK + 2 * KN * D;
 };
 
-template <int D, bool CAUSAL>
-__global__ void __launch_bounds__(tc_threads(D), D == 32 ? 2 : 1)   // head_dim 32: two blocks per SM
+template <int D, int KN, int PRODUCERS, bool CAUSAL>
+__global__ void __launch_bounds__(TcCfg<D, KN, PRODUCERS>::THREADS, TcCfg<D, KN, PRODUCERS>::BLOCKS_PER_SM)
 mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
               float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
 {
-    using C = TcCfg<D>;
-    constexpr int DB = C::DB, QBLK = C::QBLK, KBLK = C::KBLK;
+    using C = TcCfg<D, KN, PRODUCERS>;
+    constexpr int DB = C::DB, QBLK = C::QBLK, KBLK = C::KBLK, HALVES = C::HALVES, WORKERS = C::WORKERS;
     constexpr int CPR = D / 4;                   // 16-byte chunks per row
-    constexpr int kProducers = tc_producers(D);
+    constexpr int DW = D / HALVES;               // output columns per worker
     constexpr uint32_t kColS = C::kColS, kColPlo = C::kColPlo, kColO = C::kColO;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment is what the swizzled layouts assume
     float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float *q_hi = base, *q_lo = q_hi + DB * QBLK;        // [DB][128][32] each
-    float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + DB * KBLK;   // [DB][64][32] each
-    float *v_s = k_lo + DB * KBLK;               // [2 buffers][hi, lo][DB][64][32]: hi and lo blocks form one 2D-column operand
-    float *k_raw = v_s + 4 * DB * KBLK;          // [64][D] as it lies in global memory, filled by cp.async
-    float *v_raw = k_raw + kN * D;
+    float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + DB * KBLK;   // [DB][KN][32] each
+    float *v_s = k_lo + DB * KBLK;               // [2 buffers][hi, lo][DB][KN][32]: hi and lo blocks form one 2D-column operand
+    float *k_raw = v_s + 4 * DB * KBLK;          // [KN][D] as it lies in global memory, filled by cp.async
+    float *v_raw = k_raw + KN * D;
     __shared__ uint64_t mbar_s[2], mbar_k, mbar_v[2], mbar_p, mbar_o;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
+    __shared__ float xchg[2][2][kM];             // [tile parity][half][row]: row maxima, at the end row sums
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x % BH;
@@ -244,17 +249,17 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     const int q0 = qblk * kM;
 
     const int kend = CAUSAL ? min(S, q0 + kM) : S;
-    const int ntiles = (kend + kN - 1) / kN;
+    const int ntiles = (kend + KN - 1) / KN;
 
     TC_TRACE_BLOCK(0);
     if (tid == 0) {
         abort_flag = 0;
         mbar_init(&mbar_s[0], 1);                // tcgen05.commit after Q K^T into S buffer 0 / 1
         mbar_init(&mbar_s[1], 1);
-        mbar_init(&mbar_k, kProducers);          // every producer: next K tile staged
-        mbar_init(&mbar_v[0], kProducers);       // every producer: V tile staged in buffer 0 / 1
-        mbar_init(&mbar_v[1], kProducers);
-        mbar_init(&mbar_p, kWorkers);            // every worker: P written
+        mbar_init(&mbar_k, PRODUCERS);           // every producer: next K tile staged
+        mbar_init(&mbar_v[0], PRODUCERS);        // every producer: V tile staged in buffer 0 / 1
+        mbar_init(&mbar_v[1], PRODUCERS);
+        mbar_init(&mbar_p, WORKERS);             // every worker: P written
         mbar_init(&mbar_o, 1);                   // tcgen05.commit after P V
     }
     __syncthreads();                             // barriers are initialised before anyone arrives on them
@@ -270,7 +275,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
     };
 
-    if (warp == kWorkers / 32) {
+    if (warp == WORKERS / 32) {
         // ================= the issuing warp: one lane feeds the tensor core ====================
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -279,7 +284,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         tc_fence_after();
         const uint32_t tmem = tmem_base_slot;
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = make_idesc(kM, kN, 0);
+            constexpr uint32_t idesc_qk = make_idesc(kM, KN, 0);
             constexpr uint32_t idesc_pv1 = make_idesc(kM, 2 * D, 1);     // P_hi  x [V_hi | V_lo]
             constexpr uint32_t idesc_pv2 = make_idesc(kM, D, 1);         // P_lo  x V_hi
             auto issue_qk = [&](int buf) {
@@ -296,7 +301,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                         const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024, 2);
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {        // 8 floats = 32 bytes per instruction
-                            mma_ss(tmem + kColS + buf * kN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
+                            mma_ss(tmem + kColS + buf * KN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
                             acc = 1;
                         }
                     }
@@ -307,18 +312,18 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                 // N-major B: 8 reduction rows (keys) of 128 bytes per instruction = 1024 bytes
                 const uint64_t dv = make_desc(smem_u32(v_s + buf * 2 * DB * KBLK), KBLK * 4, 512, 1);
 #pragma unroll
-                for (int k = 0; k < kN / 8; ++k)
-                    mma_ts(tmem + kColO, tmem + kColS + buf * kN + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv1, k ? 1u : 0u);
+                for (int k = 0; k < KN / 8; ++k)
+                    mma_ts(tmem + kColO, tmem + kColS + buf * KN + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv1, k ? 1u : 0u);
                 // the second correction term joins the first one in columns [D,2D): both are small
 #pragma unroll
-                for (int k = 0; k < kN / 8; ++k)
+                for (int k = 0; k < KN / 8; ++k)
                     mma_ts(tmem + kColO + D, tmem + kColPlo + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv2, 1);
                 tc_commit(&mbar_o);
             };
             if (ntiles > 0) issue_qk(0);
             for (int t = 0; t < ntiles; ++t) {
                 TC_TRACE_M(0);
-                wait(&mbar_k, (uint32_t)(t & 1), 3);        // K(t+1) is in shared memory
+                wait(&mbar_k, (uint32_t)(t & 1), 3);     // K(t+1) is in shared memory
                 tc_fence_after();
                 // MMAs of one thread execute in issue order: P V(t-1), which still reads P_hi from
                 // this S buffer, was issued before
@@ -339,20 +344,20 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         return;
     }
 
-    if (warp > kWorkers / 32) {
+    if (warp > WORKERS / 32) {
         // ================= the producers: global -> split -> shared memory =====================
         // A tile first lands, as it lies in global memory, in a raw buffer (cp.async, no
         // registers held while it is in flight).  The producer that fetched a 16-byte chunk is
         // also the one that later splits it, so it only waits for its own cp.async groups.
-        constexpr int RPP = kProducers / CPR;    // rows per pass
-        constexpr int NP = kN / RPP;             // passes per tile
-        const int ptid = tid - kWorkers - 32;
+        constexpr int RPP = PRODUCERS / CPR;     // rows per pass
+        constexpr int NP = KN / RPP;             // passes per tile
+        const int ptid = tid - WORKERS - 32;
         const int sc = ptid % CPR, sr0 = ptid / CPR;
         auto fetch_tile = [&](const float *__restrict__ plane, float *raw, int t) {
 #pragma unroll
             for (int p = 0; p < NP; ++p) {
                 const int r = sr0 + p * RPP;
-                const int j = t * kN + r;
+                const int j = t * KN + r;
                 const bool ok = t < ntiles && j < S;
                 cp_async16(raw + r * D + sc * 4, plane + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + sc * 4, ok);
             }
@@ -404,17 +409,23 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         return;
     }
 
-    // ===================== the 128 workers: softmax and output ================================
-    const int row = q0 + tid;                    // a worker's query row = its TMEM lane
+    // ===================== the workers: softmax and output ====================================
+    const int half = warp >> 2;                  // which 64 keys of a tile / which output columns (0 when HALVES == 1)
+    const int wq = warp & 3;                     // TMEM lane quadrant of this warp
+    const int rloc = wq * 32 + lane;             // row inside the block = TMEM lane
+    const int row = q0 + rloc;                   // this worker's query row
     if (tid == 0) TC_TRACE_AT(0);
     {
+        // Q: the workers of a row share its chunks
+        constexpr int QC = CPR / HALVES;
         const bool ok = row < S;
-        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
+        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol) + half * QC;
 #pragma unroll
-        for (int c = 0; c < CPR; ++c) {
+        for (int c = 0; c < QC; ++c) {
             float4 x = ok ? __ldg(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
-            store_split(q_hi + (c >> 3) * QBLK, q_lo + (c >> 3) * QBLK, tid, c & 7, x);
+            const int cc = half * QC + c;
+            store_split(q_hi + (cc >> 3) * QBLK, q_lo + (cc >> 3) * QBLK, rloc, cc & 7, x);
         }
     }
     proxy_fence();
@@ -422,43 +433,53 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 TMEM lanes
+    const uint32_t lane_base = tmem + ((uint32_t)(wq * 32) << 16);   // this warp's 32 TMEM lanes
 
     if (tid == 0) TC_TRACE_AT(1);
-    float o[D];
+    float o[DW];
 #pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.0f;
+    for (int d = 0; d < DW; ++d) o[d] = 0.0f;
     float m = -1e30f, l = 0.0f, alpha_prev = 1.0f;
 
-    // o = o * alpha_prev + (both parts of) O_ext of the previous tile
+    // o = o * alpha_prev + (both parts of) O_ext of the previous tile, this worker's DW columns
     auto collect_o = [&]() {
+        if (DW % 32 == 0) {
 #pragma unroll
-        for (int g = 0; g < D / 32; ++g) {
-            float a[32], c[32];
-            tmem_ld32(lane_base + kColO + g * 32, a);            // both loads in flight, one wait
-            tmem_ld32(lane_base + kColO + D + g * 32, c);
+            for (int g = 0; g < DW / 32; ++g) {
+                float a[32], c[32];
+                tmem_ld32(lane_base + kColO + half * DW + g * 32, a);        // both loads in flight, one wait
+                tmem_ld32(lane_base + kColO + D + half * DW + g * 32, c);
+                tmem_wait_ld();
+#pragma unroll
+                for (int d = 0; d < 32; ++d) o[(g * 32 + d) % DW] = fmaf(o[(g * 32 + d) % DW], alpha_prev, a[d] + c[d]);
+            }
+        } else {
+            float a[16], c[16];
+            tmem_ld16(lane_base + kColO + half * DW, a);
+            tmem_ld16(lane_base + kColO + D + half * DW, c);
             tmem_wait_ld();
 #pragma unroll
-            for (int d = 0; d < 32; ++d) o[g * 32 + d] = fmaf(o[g * 32 + d], alpha_prev, a[d] + c[d]);
+            for (int d = 0; d < 16; ++d) o[d % DW] = fmaf(o[d % DW], alpha_prev, a[d] + c[d]);
         }
     };
 
     for (int t = 0; t < ntiles; ++t) {
         const int buf = t & 1;
-        const int j0 = t * kN;
+        const int j0 = t * KN + half * 64;            // first key of this worker's 64 columns
         TC_TRACE_W(0);
         wait(&mbar_s[buf], (uint32_t)((t >> 1) & 1), 1);     // S(t) is in TMEM
         tc_fence_after();
         TC_TRACE_W(1);
 
-        // ---- softmax of this worker's row (tcgen05 ops are warp-wide: uniform control flow) ----
-        // Two sweeps over the 64 scores in TMEM, so that only a few of them are in registers at
+        // ---- softmax of this worker's 64 scores (tcgen05 ops are warp-wide: uniform control flow) ----
+        // Two sweeps over the scores in TMEM, so that only a few of them are in registers at
         // once: the first finds the row maximum, the second exponentiates.
-        const bool warp_dead = CAUSAL && j0 > q0 + warp * 32 + 31;     // the tile is above the diagonal
-        const bool need_mask = (CAUSAL && j0 + kN - 1 > q0 + warp * 32) || j0 + kN > S;
-        // columns [0, nvalid) of this tile are visible to this row
-        const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : kN);
-        const uint32_t s_addr = lane_base + kColS + buf * kN;
+        const bool warp_dead = CAUSAL && j0 > q0 + wq * 32 + 31;       // these columns are above the diagonal
+        const bool need_mask = (CAUSAL && j0 + 63 > q0 + wq * 32) || j0 + 64 > S;
+        // columns [0, nvalid) of this worker's 64 are visible to its row
+        const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : 64);
+        const uint32_t s_addr = lane_base + kColS + buf * KN + half * 64;
+        const uint32_t plo_addr = lane_base + kColPlo + half * 64;
         float mx = -INFINITY;
         if (!warp_dead) {
             float v0[32], v1[32];
@@ -481,6 +502,13 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             }
             mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
+        if (HALVES == 2) {
+            // the two workers of a row agree on the tile's maximum through shared memory; the slot
+            // alternates with the tile parity, so it is not overwritten before the partner read it
+            xchg[buf][half][rloc] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + wq) : "memory");
+            mx = fmaxf(mx, xchg[buf][half ^ 1][rloc]);
+        }
         const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
         const float alpha = ex2_approx(m - mn);
         m = mn;
@@ -497,18 +525,18 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
 
         float psum = 0.0f;
         if (warp_dead) {
-            // nothing of this tile is visible to this warp's rows: P = 0
+            // nothing of these columns is visible to this warp's rows: P = 0
             float z[16];
 #pragma unroll
             for (int c = 0; c < 16; ++c) z[c] = 0.0f;
 #pragma unroll
-            for (int g = 0; g < kN / 16; ++g) {
+            for (int g = 0; g < 4; ++g) {
                 tmem_st16(s_addr + g * 16, z);
-                tmem_st16(lane_base + kColPlo + g * 16, z);
+                tmem_st16(plo_addr + g * 16, z);
             }
         } else if (need_mask) {
 #pragma unroll
-            for (int g = 0; g < kN / 16; ++g) {
+            for (int g = 0; g < 4; ++g) {
                 float v[16], lo[16];
                 tmem_ld16(s_addr + g * 16, v);
                 tmem_wait_ld();
@@ -520,7 +548,7 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                     lo[c] = p - v[c];
                 }
                 tmem_st16(s_addr + g * 16, v);                  // P_hi over S, in place
-                tmem_st16(lane_base + kColPlo + g * 16, lo);
+                tmem_st16(plo_addr + g * 16, lo);
             }
         } else {
             // chunks of 16 scores; the next chunk's load is in flight while this one is computed,
@@ -529,9 +557,9 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             float ps4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             tmem_ld16(s_addr, cur);
 #pragma unroll
-            for (int g = 0; g < kN / 16; ++g) {
+            for (int g = 0; g < 4; ++g) {
                 tmem_wait_ld();
-                if (g + 1 < kN / 16) tmem_ld16(s_addr + (g + 1) * 16, nxt);
+                if (g + 1 < 4) tmem_ld16(s_addr + (g + 1) * 16, nxt);
                 float lo[16];
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
@@ -541,8 +569,8 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
                     lo[c] = p - cur[c];
                 }
                 tmem_st16(s_addr + g * 16, cur);                // P_hi over S, in place
-                tmem_st16(lane_base + kColPlo + g * 16, lo);
-                if (g + 1 < kN / 16) {
+                tmem_st16(plo_addr + g * 16, lo);
+                if (g + 1 < 4) {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) cur[c] = nxt[c];
                 }
@@ -560,34 +588,44 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         tc_fence_after();
         collect_o();
     }
+    if (HALVES == 2) {
+        // row sums of the two halves (the maxima slots are idle now: every worker is past its last tile
+        // once its partner has arrived at this barrier)
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + wq) : "memory");
+        xchg[0][half][rloc] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + wq) : "memory");
+        l += xchg[0][half ^ 1][rloc];
+    }
     if (tid == 0) TC_TRACE_AT(99);
     TC_TRACE_BLOCK(1);
     if (!abort_flag && row < S) {
         const float inv = 1.0f / fmaxf(l, 1e-20f);
-        float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol);
+        float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol + half * DW);
 #pragma unroll
-        for (int c = 0; c < D / 4; ++c)
+        for (int c = 0; c < DW / 4; ++c)
             dst[c] = make_float4(o[c * 4 + 0] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
     }
     tc_fence_before();
     __syncthreads();
 }
 
-template <int D, bool CAUSAL>
+template <int D, int KN, int PRODUCERS, bool CAUSAL>
 int launch_tc_cfg(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, cudaStream_t st)
 {
-    auto kern = mha_tc_kernel<D, CAUSAL>;
-    // operands + alignment slack; never less than 100 KB, so that at most two blocks share an
-    // SM and their two 256-column TMEM allocations always fit in the 512 columns
-    size_t smem = TcCfg<D>::kSmemFloats * sizeof(float) + 1024;
-    if (smem < 100 * 1024) smem = 100 * 1024;
+    using C = TcCfg<D, KN, PRODUCERS>;
+    auto kern = mha_tc_kernel<D, KN, PRODUCERS, CAUSAL>;
+    // operands + alignment slack; a variant that allocates 256 TMEM columns asks for at least 100 KB,
+    // so that at most two blocks share an SM and their allocations always fit in the 512 columns
+    size_t smem = C::kSmemFloats * sizeof(float) + 1024;
+    if (C::BLOCKS_PER_SM == 2 && smem < 100 * 1024) smem = 100 * 1024;
+    if (C::BLOCKS_PER_SM == 1 && smem < 120 * 1024) smem = 120 * 1024;     // 512 columns: one block per SM
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     const int nqblk = (S + kM - 1) / kM;
     const long long blocks = (long long)B * H * nqblk;
     if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
     const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<(unsigned)blocks, tc_threads(D), smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
+    kern<<<(unsigned)blocks, C::THREADS, smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
     return check_launch("mha_tc_kernel");
 }
 
@@ -595,14 +633,21 @@ int launch_tc_cfg(const float *q, const float *k, const float *v, float *out, in
 
 bool mha_tc_supports(int D) { return D == 32 || D == 64; }
 
+// variant: 0 = default, 1 = 64-key tiles (two blocks per SM for head_dim 32), 2 = 128-key tiles with
+// two workers per row (head_dim 32 only, one block per SM)
 int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
-                  int B, int S, int E, int H, int causal, cudaStream_t st)
+                  int B, int S, int E, int H, int causal, cudaStream_t st, int variant)
 {
     const int D = E / H;
-    if (D == 32) return causal ? launch_tc_cfg<32, true>(q, k, v, out, B, S, E, H, st)
-                               : launch_tc_cfg<32, false>(q, k, v, out, B, S, E, H, st);
-    if (D == 64) return causal ? launch_tc_cfg<64, true>(q, k, v, out, B, S, E, H, st)
-                               : launch_tc_cfg<64, false>(q, k, v, out, B, S, E, H, st);
+    if (D == 32) {
+        const bool wide = variant == 2;
+        if (wide) return causal ? launch_tc_cfg<32, 128, 128, true>(q, k, v, out, B, S, E, H, st)
+                                : launch_tc_cfg<32, 128, 128, false>(q, k, v, out, B, S, E, H, st);
+        return causal ? launch_tc_cfg<32, 64, 64, true>(q, k, v, out, B, S, E, H, st)
+                      : launch_tc_cfg<32, 64, 64, false>(q, k, v, out, B, S, E, H, st);
+    }
+    if (D == 64) return causal ? launch_tc_cfg<64, 64, 64, true>(q, k, v, out, B, S, E, H, st)
+                               : launch_tc_cfg<64, 64, 64, false>(q, k, v, out, B, S, E, H, st);
     return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
 }
 

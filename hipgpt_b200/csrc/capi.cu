@@ -68,7 +68,7 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
         if (!aligned) return fail(HIPGPT_ERR_BAD_ARG, "tensor-core kernel needs 16-byte aligned pointers");
         if (probs) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel does not store probabilities");
         if (!mha_tc_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
-        return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
+        return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st, warps);   // `warps` selects the tile variant here
     default:
         return fail(HIPGPT_ERR_BAD_ARG, "unknown algo %d", algo);
     }
