@@ -53,6 +53,23 @@ def test_tensor_kernel_benchmark_shapes(cfg, causal):
     assert float(np.abs(out - ref_out).max()) <= TOL
 
 
+# tile variants of the kernel, chosen through the `warps` argument of hipgpt_mha_forward_ex:
+# 2 = 128-key tiles with two workers per row (head_dim 32), 3 = persistent blocks over a tile stream
+@pytest.mark.parametrize("variant,shape", [(2, (2, 2, 200, 32)), (2, (4, 8, 256, 32)), (2, (1, 1, 513, 32)),
+                                           (3, (2, 2, 200, 32)), (3, (32, 8, 256, 32)), (3, (1, 2, 300, 64)),
+                                           (3, (3, 40, 130, 32)), (3, (2, 4, 1024, 64))])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tensor_kernel_variants_match_oracle(variant, shape, causal):
+    B, H, S, D = shape
+    E = H * D
+    qkv = synth.qkv_planes(3000 + S + D, B, S, E)
+    ref_out, _ = ob.mha(qkv, B, S, E, H, causal=causal)
+    out, _ = gpu_mha(qkv, B, S, E, H, causal, False, algo=_capi.ALGO_TENSOR, warps=variant)
+    assert _status() == 0
+    assert np.isfinite(out).all()
+    assert float(np.abs(out - ref_out).max()) <= TOL
+
+
 def test_tensor_kernel_refuses_what_it_cannot_do():
     lib = _capi.lib()
     t = torch.zeros((64, 48), device="cuda")
