@@ -62,6 +62,7 @@ def parse():
     ap.add_argument("--causal", type=int, default=1)
     ap.add_argument("--probs", type=int, default=0)
     ap.add_argument("--gather", type=int, default=0)
+    ap.add_argument("--strong", type=int, default=0, help="1: the workload's batches are split over the ranks (strong scaling)")
     ap.add_argument("--sets", type=int, default=0, help="input batches per step (0: enough to exceed L2)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline leg")
     ap.add_argument("--no-cpu", action="store_true")
@@ -214,7 +215,7 @@ def workload_config(args, cfg, sets):
             "B": cfg["B"], "H": cfg["H"], "S": cfg["S"], "head_dim": cfg["D"], "causal": int(args.causal),
             "probs_stored": int(args.probs), "batches_per_step": sets,
             "l2": f"{sets} distinct input batches per step, {sets * bytes_of(cfg['B'], cfg['H'], cfg['S'], cfg['D'], args.probs) / 1e6:.0f} MB > 126 MB L2",
-            "parallelism": f"batch-major shards x{args.gpus}" + (", NCCL all-gather of outputs" if args.gather else ", no collective")}
+            "parallelism": f"batch-major shards x{args.gpus}" + (", NCCL all-gather of outputs in chunks, overlapped" if args.gather else ", no collective")}
 
 
 # ----------------------------------------------------------------------------- GPU arm ----
@@ -232,7 +233,14 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = _capi.lib()
-    cfg = synth.CONFIGS[args.workload]
+    cfg = dict(synth.CONFIGS[args.workload])
+    B_total = cfg["B"]
+    if args.strong and world > 1:
+        from hipgpt_b200 import sharding
+        b0, b1 = sharding.shard_range(B_total, world, rank)      # this rank's slab of the workload's batches
+        cfg["B"] = b1 - b0
+        if cfg["B"] == 0:
+            raise SystemExit("more ranks than batches")
     B, H, S, D = cfg["B"], cfg["H"], cfg["S"], cfg["D"]
     E = H * D
     per_batch_bytes = bytes_of(B, H, S, D, args.probs)
@@ -243,13 +251,31 @@ def run_ours(args):
     h_in = torch.empty((sets, 3, B * S, E), dtype=torch.float32).pin_memory()
     gen = min(sets, 2)                                    # two seeded batches, the rest are rolls of them
     for s in range(gen):
-        h_in[s] = torch.from_numpy(synth.qkv_planes(cfg["seed"] + 100 * rank + s, B, S, E, cfg["scale"]))
+        if 3 * B * S * E <= 64_000_000:
+            h_in[s] = torch.from_numpy(synth.qkv_planes(cfg["seed"] + 100 * rank + s, B, S, E, cfg["scale"]))
+        else:
+            # large workloads: a few seeded batch items, the others are rolls of them along the head dimension
+            view = h_in[s].view(3, B, S, E)
+            nb = min(B, 4)
+            for bi in range(nb):
+                view[:, bi] = torch.from_numpy(synth.qkv_planes(cfg["seed"] + 100 * rank + 10 * s + bi, 1, S, E, cfg["scale"])).view(3, S, E)
+            for bi in range(nb, B):
+                view[:, bi] = torch.roll(view[:, bi % nb], shifts=bi, dims=2)
     for s in range(gen, sets):
         h_in[s] = torch.roll(h_in[s % gen], shifts=s, dims=1)   # other token order: other data, same distribution
     d_in = h_in.cuda(non_blocking=True)
     d_out = torch.empty((sets, B * S, E), dtype=torch.float32, device="cuda")
     d_probs = torch.empty((B, H, S, S), dtype=torch.float32, device="cuda") if args.probs else None
-    gathered = torch.empty((world, sets, B * S, E), dtype=torch.float32, device="cuda") if (args.gather and world > 1) else None
+    # --gather: the outputs of all ranks are all-gathered, in chunks of batches, each chunk as soon as
+    # its kernel has been enqueued, so that NVLink traffic overlaps the remaining compute
+    nchunks = 1
+    if args.gather and world > 1:
+        if args.strong and B_total % world:
+            raise SystemExit("--gather with --strong needs the batch count to divide by the ranks")
+        nchunks = 4 if (B % 4 == 0 and B * S * E * 4 >= (64 << 20)) else 1
+    bc = B // nchunks                                         # batches per chunk
+    gathered = (torch.empty((sets, nchunks, world, bc * S, E), dtype=torch.float32, device="cuda")
+                if (args.gather and world > 1) else None)
     stream = torch.cuda.current_stream()
     st = stream.cuda_stream
 
@@ -259,13 +285,24 @@ def run_ours(args):
     fwd = lib.hipgpt_mha_forward
 
     def step():
+        handles = []
         for s in range(sets):
             base = in_ptrs[s]
-            rc = fwd(base, base + 4 * plane, base + 8 * plane, out_ptrs[s], probs_ptr, B, S, E, H, args.causal, st)
-            if rc:
-                _capi.check(rc)
-        if gathered is not None:
-            dist.all_gather_into_tensor(gathered.view(-1), d_out.view(-1))
+            if gathered is None:
+                rc = fwd(base, base + 4 * plane, base + 8 * plane, out_ptrs[s], probs_ptr, B, S, E, H, args.causal, st)
+                if rc:
+                    _capi.check(rc)
+                continue
+            for c in range(nchunks):
+                off = c * bc * S * E * 4                     # byte offset of the chunk inside a plane / the output
+                rc = fwd(base + off, base + 4 * plane + off, base + 8 * plane + off, out_ptrs[s] + off, None,
+                         bc, S, E, H, args.causal, st)
+                if rc:
+                    _capi.check(rc)
+                handles.append(dist.all_gather_into_tensor(gathered[s, c].view(-1), d_out[s].view(nchunks, -1)[c],
+                                                           async_op=True))
+        for h in handles:
+            h.wait()
 
     def barrier():
         torch.cuda.synchronize()
@@ -294,7 +331,10 @@ def run_ours(args):
         ms = timed(step, args.steps)
     ms_per_step = ms / args.steps
     flops_step = flops_of(B, H, S, D, args.causal) * sets
-    value = world * flops_step / (ms_per_step * 1e-3) / 1e12
+    if args.strong and world > 1:
+        value = flops_of(B_total, H, S, D, args.causal) * sets / (ms_per_step * 1e-3) / 1e12
+    else:
+        value = world * flops_step / (ms_per_step * 1e-3) / 1e12
 
     # roofline of the attention kernel: FMA-pipe ceiling measured now, on this GPU, at these clocks
     sink = torch.zeros(1, device="cuda")
@@ -343,7 +383,8 @@ def run_ours(args):
                      "hbm_time_us": t_hbm * 1e6, "pipe_time_us": t_pipe * 1e6})
     line = {"metric": "causal_attn_fwd_tflops" if args.causal else "attn_fwd_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if (args.strong and world > 1) else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
             "config": workload_config(args, cfg, sets), "clocks": clocks.summary(), "roofline": roofline,
             "gpu_launches": args.steps * sets}
 
@@ -371,7 +412,8 @@ def run_ours(args):
             t = torch.tensor([dt], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t.item())
-        line["e2e"] = {"value": world * flops_step * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
+        line["e2e"] = {"value": (flops_of(B_total, H, S, D, args.causal) * sets if (args.strong and world > 1) else world * flops_step) * e2e_steps / dt / 1e12,
+                       "unit": "TFLOP/s",
                        "h2d_bytes_per_step": int(sets * 3 * plane * 4),
                        "d2h_bytes_per_step": int(sets * (plane * 4 + (B * H * S * S * 4 if args.probs else 0))),
                        "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps,
@@ -389,6 +431,8 @@ def run_ours(args):
 
 
 def main():
+    # anything a library prints (NCCL's version banner, for one) goes to stderr: stdout carries the JSON line only
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     args = parse()
     if args.impl == "reference":
         run_reference(args)
