@@ -66,6 +66,7 @@ def parse():
     ap.add_argument("--sets", type=int, default=0, help="input batches per step (0: enough to exceed L2)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline leg")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--decode-only", action="store_true", help="run only the greedy-generation leg and print its JSON")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -451,7 +452,9 @@ def main():
     _REAL_STDOUT = os.dup(1)
     os.dup2(2, 1)
     args = parse()
-    if args.impl == "reference":
+    if args.decode_only:
+        emit(decode_leg())
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
