@@ -60,6 +60,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(synth.CONFIGS))
     ap.add_argument("--causal", type=int, default=1)
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="storage type of Q, K, V and the output (bf16: head_dim 64)")
     ap.add_argument("--probs", type=int, default=0)
     ap.add_argument("--gather", type=int, default=0)
     ap.add_argument("--strong", type=int, default=0, help="1: the workload's batches are split over the ranks (strong scaling)")
@@ -211,11 +212,11 @@ def run_reference(args):
 
 
 def workload_config(args, cfg, sets):
-    return {"workload": f"{args.workload}: causal MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} fp32"
-                        if args.causal else f"{args.workload}: full MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} fp32",
+    return {"workload": f"{args.workload}: causal MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} {args.dtype}"
+                        if args.causal else f"{args.workload}: full MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} {args.dtype}",
             "B": cfg["B"], "H": cfg["H"], "S": cfg["S"], "head_dim": cfg["D"], "causal": int(args.causal),
             "probs_stored": int(args.probs), "batches_per_step": sets,
-            "l2": f"{sets} distinct input batches per step, {sets * bytes_of(cfg['B'], cfg['H'], cfg['S'], cfg['D'], args.probs) / 1e6:.0f} MB > 126 MB L2",
+            "l2": f"{sets} distinct input batches per step, {sets * bytes_of(cfg['B'], cfg['H'], cfg['S'], cfg['D'], args.probs) * (2 if args.dtype == 'bf16' else 4) // 4 / 1e6:.0f} MB > 126 MB L2",
             "parallelism": f"batch-major shards x{args.gpus}" + (", NCCL all-gather of outputs in chunks, overlapped" if args.gather else ", no collective")}
 
 
@@ -244,7 +245,12 @@ def run_ours(args):
             raise SystemExit("more ranks than batches")
     B, H, S, D = cfg["B"], cfg["H"], cfg["S"], cfg["D"]
     E = H * D
-    per_batch_bytes = bytes_of(B, H, S, D, args.probs)
+    bf16 = args.dtype == "bf16"
+    if bf16 and (args.probs or D != 64):
+        raise SystemExit("--dtype bf16: head_dim 64, no stored probabilities")
+    esz = 2 if bf16 else 4                                   # bytes per stored element
+    tdtype = torch.bfloat16 if bf16 else torch.float32
+    per_batch_bytes = bytes_of(B, H, S, D, args.probs) * esz // 4
     sets = args.sets or max(1, int(np.ceil(1.5 * L2_BYTES / per_batch_bytes)))
     plane = B * S * E
 
@@ -264,8 +270,8 @@ def run_ours(args):
                 view[:, bi] = torch.roll(view[:, bi % nb], shifts=bi, dims=2)
     for s in range(gen, sets):
         h_in[s] = torch.roll(h_in[s % gen], shifts=s, dims=1)   # other token order: other data, same distribution
-    d_in = h_in.cuda(non_blocking=True)
-    d_out = torch.empty((sets, B * S, E), dtype=torch.float32, device="cuda")
+    d_in = h_in.cuda(non_blocking=True).to(tdtype)
+    d_out = torch.empty((sets, B * S, E), dtype=tdtype, device="cuda")
     d_probs = torch.empty((B, H, S, S), dtype=torch.float32, device="cuda") if args.probs else None
     # --gather: the outputs of all ranks are all-gathered, in chunks of batches, each chunk as soon as
     # its kernel has been enqueued, so that NVLink traffic overlaps the remaining compute
@@ -273,9 +279,9 @@ def run_ours(args):
     if args.gather and world > 1:
         if args.strong and B_total % world:
             raise SystemExit("--gather with --strong needs the batch count to divide by the ranks")
-        nchunks = 4 if (B % 4 == 0 and B * S * E * 4 >= (64 << 20)) else 1
+        nchunks = 4 if (B % 4 == 0 and B * S * E * esz >= (32 << 20)) else 1
     bc = B // nchunks                                         # batches per chunk
-    gathered = (torch.empty((sets, nchunks, world, bc * S, E), dtype=torch.float32, device="cuda")
+    gathered = (torch.empty((sets, nchunks, world, bc * S, E), dtype=tdtype, device="cuda")
                 if (args.gather and world > 1) else None)
     stream = torch.cuda.current_stream()
     st = stream.cuda_stream
@@ -283,20 +289,24 @@ def run_ours(args):
     in_ptrs = [d_in[s].data_ptr() for s in range(sets)]
     out_ptrs = [d_out[s].data_ptr() for s in range(sets)]
     probs_ptr = d_probs.data_ptr() if args.probs else None
-    fwd = lib.hipgpt_mha_forward
+    if bf16:
+        def fwd(q, k, v, out, probs, B_, S_, E_, H_, causal, st_):
+            return lib.hipgpt_mha_forward_bf16(q, k, v, out, B_, S_, E_, H_, causal, st_)
+    else:
+        fwd = lib.hipgpt_mha_forward
 
     def step():
         handles = []
         for s in range(sets):
             base = in_ptrs[s]
             if gathered is None:
-                rc = fwd(base, base + 4 * plane, base + 8 * plane, out_ptrs[s], probs_ptr, B, S, E, H, args.causal, st)
+                rc = fwd(base, base + esz * plane, base + 2 * esz * plane, out_ptrs[s], probs_ptr, B, S, E, H, args.causal, st)
                 if rc:
                     _capi.check(rc)
                 continue
             for c in range(nchunks):
-                off = c * bc * S * E * 4                     # byte offset of the chunk inside a plane / the output
-                rc = fwd(base + off, base + 4 * plane + off, base + 8 * plane + off, out_ptrs[s] + off, None,
+                off = c * bc * S * E * esz                   # byte offset of the chunk inside a plane / the output
+                rc = fwd(base + off, base + esz * plane + off, base + 2 * esz * plane + off, out_ptrs[s] + off, None,
                          bc, S, E, H, args.causal, st)
                 if rc:
                     _capi.check(rc)
@@ -361,12 +371,16 @@ def run_ours(args):
     # rate.  The FFMA kernel (probabilities stored) is measured against the FFMA ceiling.
     tensor_kernel = not args.probs and D in (32, 64)
     flops_launch = flops_of(B, H, S, D, args.causal)
-    bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
+    # a kernel timed back to back for seconds is compared with the sustained figure
+    bf16_peak = float(peaks.get("bf16_tflops_sustained" if bf16 else "bf16_tflops", 1400.0 if bf16 else 1590.0))
     tf32_peak = bf16_peak / 2.0
     t_hbm = per_batch_bytes / (hbm_peak * 1e9)
-    t_pipe = (3.0 * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
+    t_pipe = (flops_launch / (bf16_peak * 1e12)) if bf16 else (3.0 * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
     src = "measured" if peaks else "fallback"
-    if t_hbm >= t_pipe:
+    if bf16 and t_hbm < t_pipe:
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": bf16_peak, "unit": "TFLOP/s", "frac": achieved / bf16_peak,
+                    "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained ({src}): dense bf16 GEMM rate"}
+    elif t_hbm >= t_pipe:
         roofline = {"bound": "hbm", "achieved": hbm_achieved, "peak": hbm_peak, "unit": "GB/s",
                     "frac": hbm_achieved / hbm_peak, "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({src})"}
     elif tensor_kernel:
@@ -376,7 +390,8 @@ def run_ours(args):
     else:
         roofline = {"bound": "fma", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s", "frac": achieved / fma_peak,
                     "peak_source": "fp32 FFMA loop timed in this run"}
-    roofline.update({"kernel": "mha_tc_kernel" if tensor_kernel else "mha_rows_kernel", "traffic": TRAFFIC.get((args.workload, tensor_kernel)),
+    roofline.update({"kernel": "mha_bf16_kernel" if bf16 else "mha_tc_kernel" if tensor_kernel else "mha_rows_kernel",
+                     "traffic": None if bf16 else TRAFFIC.get((args.workload, tensor_kernel)),
                      "us_per_launch": launch_ms * 1e3, "algorithmic_bytes_per_launch": per_batch_bytes,
                      "algorithmic_flops_per_launch": flops_launch,
                      "vs_fp32_fma_ceiling": {"achieved_tflops": achieved, "ffma_peak_tflops": fma_peak, "ratio": achieved / fma_peak,
@@ -385,12 +400,12 @@ def run_ours(args):
     line = {"metric": "causal_attn_fwd_tflops" if args.causal else "attn_fwd_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong" if (args.strong and world > 1) else "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
+            "dtype": "bf16 storage, fp32 accumulate" if bf16 else "f32", "data": "synthetic",
             "config": workload_config(args, cfg, sets), "clocks": clocks.summary(), "roofline": roofline,
             "gpu_launches": args.steps * sets}
 
     # end to end through the host-buffer entry point: pinned host memory in, host memory out
-    if not args.no_e2e:
+    if not args.no_e2e and not bf16:                       # the host-buffer entry point is fp32 only
         h_out = torch.empty((B * S, E), dtype=torch.float32).pin_memory()
         h_probs = torch.empty((B, H, S, S), dtype=torch.float32).pin_memory() if args.probs else None
         e2e_steps = max(1, min(args.steps, 20))

@@ -20,7 +20,7 @@ LIBDIR = os.path.join(PKG, "_lib")
 LIB = os.path.join(LIBDIR, "libhipgpt_attn.so")
 OBJDIR = os.path.join(LIBDIR, "obj")
 
-SOURCES = ["attn_fwd_rows.cu", "attn_fwd_tc.cu", "attn_fwd_generic.cu", "attn_unfused.cu", "attn_decode.cu", "gpt_decode.cu", "probe.cu", "capi.cu",
+SOURCES = ["attn_fwd_rows.cu", "attn_fwd_tc.cu", "attn_fwd_bf16.cu", "attn_fwd_generic.cu", "attn_unfused.cu", "attn_decode.cu", "gpt_decode.cu", "probe.cu", "capi.cu",
            "compat_launchers.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

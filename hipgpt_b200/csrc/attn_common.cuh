@@ -42,6 +42,9 @@ int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
                   int B, int S, int E, int H, int causal, cudaStream_t st, int variant = 0);
 bool mha_tc_supports(int D);
 int tc_status_fetch(int *status);
+int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st);
+bool mha_bf16_supports(int D);
+int bf16_status_fetch(int *status);
 int launch_mha_generic(const float *q, const float *k, const float *v, float *out, float *probs,
                        int B, int S, int E, int H, int causal, cudaStream_t st);
 int launch_sdp(const float *Q, const float *K, float *scores, int B, int S, int D, cudaStream_t st);

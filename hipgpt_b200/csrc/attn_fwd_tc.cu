@@ -35,7 +35,7 @@
 // flag that cuts all its later waits short, records a status code, skips its stores, frees
 // its TMEM and returns.  No probabilities are written by this kernel; callers that want them
 // get the FFMA rows kernel.
-#include "attn_common.cuh"
+#include "tc_primitives.cuh"
 
 #include <math.h>
 
@@ -43,8 +43,6 @@ namespace hipgpt {
 namespace {
 
 constexpr int kM = 128;          // query rows per block
-constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
-constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
 
 __device__ int g_tc_status = 0;   // 0 ok; otherwise the site code of the first wait that ran out
 
@@ -66,40 +64,6 @@ __device__ __forceinline__ int tc_smid() { int r; asm volatile("mov.u32 %0, %%sm
 #define TC_TRACE_W(k) do { if (tid == 0 && t < 12) TC_TRACE_AT(2 + 8 * t + (k)); } while (0)
 #define TC_TRACE_M(k) do { if (t < 12) TC_TRACE_AT(100 + 4 * t + (k)); } while (0)
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, int count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-
-// Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
-{
-    const uint32_t addr = smem_u32(bar);
-    const long long deadline = clock64() + kCycleLimit;
-    for (long long i = 0; i < kSpinLimit && clock64() < deadline; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint64_t *bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
@@ -120,55 +84,12 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-// Shared-memory matrix descriptor for a tile made of 128-byte rows.
-//   K-major operands (Q, K): layout 2 = SWIZZLE_128B, rows grouped by 8 (1024 bytes); sbo = bytes
-//     between groups, lbo unused (16).
-//   N-major operand (V): 32-bit operands that are contiguous along N must use layout 1,
-//     SWIZZLE_128B with a 32-byte base: reduction rows grouped by 4 (512 bytes); sbo = bytes
-//     between groups, lbo = bytes between 32-float column blocks.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;          // descriptor version of sm_100
-    d |= (uint64_t)layout_type << 61;   // 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte base
-    return d;
-}
-
 // Instruction descriptor: fp32 accumulator, TF32 operands, A K-major, B K- or N-major.
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_n_major)
 {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)b_n_major << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(m >> 4) << 24);
 }
-
-// tcgen05.ld / st, shape 32x32b: thread i of the warp moves N consecutive 32-bit columns of TMEM
-// lane (base lane + i).  Values pass through plain registers (no address is taken).
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32])
-{
-    uint32_t r0, r1, r2, r3, r4, r5, r6, r7, r8, r9, r10, r11, r12, r13, r14, r15, r16, r17, r18, r19, r20, r21, r22, r23, r24, r25, r26, r27, r28, r29, r30, r31;
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3), "=r"(r4), "=r"(r5), "=r"(r6), "=r"(r7), "=r"(r8), "=r"(r9), "=r"(r10), "=r"(r11), "=r"(r12), "=r"(r13), "=r"(r14), "=r"(r15), "=r"(r16), "=r"(r17), "=r"(r18), "=r"(r19), "=r"(r20), "=r"(r21), "=r"(r22), "=r"(r23), "=r"(r24), "=r"(r25), "=r"(r26), "=r"(r27), "=r"(r28), "=r"(r29), "=r"(r30), "=r"(r31)
-                 : "r"(addr) : "memory");
-    v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3); v[4] = __uint_as_float(r4); v[5] = __uint_as_float(r5); v[6] = __uint_as_float(r6); v[7] = __uint_as_float(r7); v[8] = __uint_as_float(r8); v[9] = __uint_as_float(r9); v[10] = __uint_as_float(r10); v[11] = __uint_as_float(r11); v[12] = __uint_as_float(r12); v[13] = __uint_as_float(r13); v[14] = __uint_as_float(r14); v[15] = __uint_as_float(r15); v[16] = __uint_as_float(r16); v[17] = __uint_as_float(r17); v[18] = __uint_as_float(r18); v[19] = __uint_as_float(r19); v[20] = __uint_as_float(r20); v[21] = __uint_as_float(r21); v[22] = __uint_as_float(r22); v[23] = __uint_as_float(r23); v[24] = __uint_as_float(r24); v[25] = __uint_as_float(r25); v[26] = __uint_as_float(r26); v[27] = __uint_as_float(r27); v[28] = __uint_as_float(r28); v[29] = __uint_as_float(r29); v[30] = __uint_as_float(r30); v[31] = __uint_as_float(r31);
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16])
-{
-    uint32_t r0, r1, r2, r3, r4, r5, r6, r7, r8, r9, r10, r11, r12, r13, r14, r15;
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3), "=r"(r4), "=r"(r5), "=r"(r6), "=r"(r7), "=r"(r8), "=r"(r9), "=r"(r10), "=r"(r11), "=r"(r12), "=r"(r13), "=r"(r14), "=r"(r15)
-                 : "r"(addr) : "memory");
-    v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3); v[4] = __uint_as_float(r4); v[5] = __uint_as_float(r5); v[6] = __uint_as_float(r6); v[7] = __uint_as_float(r7); v[8] = __uint_as_float(r8); v[9] = __uint_as_float(r9); v[10] = __uint_as_float(r10); v[11] = __uint_as_float(r11); v[12] = __uint_as_float(r12); v[13] = __uint_as_float(r13); v[14] = __uint_as_float(r14); v[15] = __uint_as_float(r15);
-}
-__device__ __forceinline__ void tmem_st16(uint32_t addr, const float (&v)[16])
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                 ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])) : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 

@@ -119,6 +119,19 @@ int hipgpt_mha_forward_planes(const float *d_qkv, float *d_out, float *d_probs,
                         static_cast<cudaStream_t>(stream));
 }
 
+int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const void *d_v, void *d_out,
+                            int B, int S, int E, int H, int causal, void *stream)
+{
+    if (B < 0 || S < 0 || E < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: B=%d S=%d E=%d", B, S, E);
+    if (H <= 0 || E % H != 0) return fail(HIPGPT_ERR_BAD_ARG, "Bad MHA config: E=%d H=%d", E, H);
+    if (B == 0 || S == 0 || E == 0) return HIPGPT_OK;
+    if (!d_q || !d_k || !d_v || !d_out) return fail(HIPGPT_ERR_NULL, "q, k, v and out must not be NULL");
+    if ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v) |
+         reinterpret_cast<uintptr_t>(d_out)) & 15)
+        return fail(HIPGPT_ERR_BAD_ARG, "bf16 planes must be 16-byte aligned");
+    return launch_mha_bf16(d_q, d_k, d_v, d_out, B, S, E, H, causal, static_cast<cudaStream_t>(stream));
+}
+
 int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
                             int B, int S, int E, int H, int causal)
 {
@@ -273,7 +286,13 @@ int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end)
 int hipgpt_kernel_status(int *status)
 {
     if (!status) return fail(HIPGPT_ERR_NULL, "status must not be NULL");
-    return tc_status_fetch(status);
+    int a = 0, b = 0;
+    int rc = tc_status_fetch(&a);
+    if (rc != HIPGPT_OK) return rc;
+    rc = bf16_status_fetch(&b);
+    if (rc != HIPGPT_OK) return rc;
+    *status = a ? a : (b ? 100 + b : 0);          // 1xx: the bf16 kernel's wait sites
+    return HIPGPT_OK;
 }
 
 const char *hipgpt_last_error(void) { return g_err; }

@@ -42,6 +42,17 @@ def mha_forward(q, k, v, out, probs, B: int, S: int, E: int, H: int, *, causal: 
                                                   B, S, E, H, int(causal), algo, warps, _stream()))
 
 
+def mha_forward_bf16(d_qkv, d_output, B: int, S: int, E: int, H: int, *, causal: bool = False):
+    """The launcher's contract with bf16 storage: d_qkv = three stacked [B*S, E] bf16 planes, d_output
+    [B*S, E] bf16 (head_dim 64), fp32 accumulation."""
+    for t in (d_qkv, d_output):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
+            raise ValueError("expected a contiguous CUDA bfloat16 tensor")
+    plane = B * S * E * 2                                   # bytes
+    p = d_qkv.data_ptr()
+    _capi.check(_capi.lib().hipgpt_mha_forward_bf16(p, p + plane, p + 2 * plane, d_output.data_ptr(), B, S, E, H, int(causal), _stream()))
+
+
 def launch_scaled_dot_product(Q, K, scores, B: int, S: int, D: int):
     _capi.check(_capi.lib().hipgpt_scaled_dot_product(_ptr(Q), _ptr(K), _ptr(scores), B, S, D, _stream()))
 

@@ -79,6 +79,17 @@ HIPGPT_API int hipgpt_mha_forward_ex(const float *d_q, const float *d_k, const f
 HIPGPT_API int hipgpt_mha_forward_planes(const float *d_qkv, float *d_out, float *d_probs,
                               int B, int S, int E, int H, int causal, void *stream);
 
+/*
+ * The same attention with 16-bit storage: d_q, d_k, d_v are [B*S][E] planes of bf16 (IEEE
+ * bfloat16, the upper half of an fp32), d_out is [B*S][E] bf16; products run on the tensor
+ * cores with fp32 accumulation, the softmax in fp32.  head_dim (E/H) must be 64, the four
+ * pointers 16-byte aligned.  Results agree with the fp32 arithmetic on the same
+ * (bf16-rounded) inputs to about 1e-2 absolute for unit-variance data: the probabilities and
+ * the output are rounded to bf16.  No probabilities are written.
+ */
+HIPGPT_API int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const void *d_v, void *d_out,
+                            int B, int S, int E, int H, int causal, void *stream);
+
 /* The same call for HOST buffers: copies the planes to the device, runs the kernel, copies
  * the output (and the probabilities when h_probs is not NULL) back and waits.  The device
  * workspace is owned by the library, grows to the largest call and is released by
