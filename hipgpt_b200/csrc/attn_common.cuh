@@ -42,6 +42,12 @@ int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
                   int B, int S, int E, int H, int causal, cudaStream_t st, int variant = 0);
 bool mha_tc_supports(int D);
 int tc_status_fetch(int *status);
+int launch_mha_tc_pair(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st);
+bool mha_tc_pair_supports(int head_dim);
+int tc_pair_status_fetch(int *status);
+int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st);
+bool mha_tc16_supports(int head_dim);
+int tc16_status_fetch(int *status);
 int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_bf16_supports(int D);
 int bf16_status_fetch(int *status);

@@ -64,56 +64,6 @@ __device__ __forceinline__ int tc_smid() { int r; asm volatile("mov.u32 %0, %%sm
 #define TC_TRACE_W(k) do { if (tid == 0 && t < 12) TC_TRACE_AT(2 + 8 * t + (k)); } while (0)
 #define TC_TRACE_M(k) do { if (t < 12) TC_TRACE_AT(100 + 4 * t + (k)); } while (0)
 
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-// Instruction descriptor: fp32 accumulator, TF32 operands, A K-major, B K- or N-major.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_n_major)
-{
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)b_n_major << 16) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
-
-// Writes one 16-byte chunk of a row, split into hi and lo, at its swizzled place:
-// chunk c of row r of a [rows][128 B] block lands at r*128 + ((c ^ (r & 7)) * 16).
-__device__ __forceinline__ void store_split(float *hi_blk, float *lo_blk, int row, int chunk, float4 x)
-{
-    const int off = row * 32 + ((chunk ^ (row & 7)) << 2);
-    const float4 h = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
-    *reinterpret_cast<float4 *>(hi_blk + off) = h;
-    *reinterpret_cast<float4 *>(lo_blk + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
-}
-
-// The same for the N-major operand: 32-byte pieces of a row are permuted by the row index
-// modulo 4; the 16-byte half inside a piece keeps its place.
-__device__ __forceinline__ void store_split_nmajor(float *hi_blk, float *lo_blk, int row, int chunk, float4 x)
-{
-    const int piece = (chunk >> 1) ^ (row & 3);
-    const int off = row * 32 + (((piece << 1) | (chunk & 1)) << 2);
-    const float4 h = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
-    *reinterpret_cast<float4 *>(hi_blk + off) = h;
-    *reinterpret_cast<float4 *>(lo_blk + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
-}
-
 // Shape of one kernel variant.
 //   D        head_dim (32 or 64)
 //   KN       keys per tile (64 or 128)
@@ -1023,6 +973,10 @@ int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
                   int B, int S, int E, int H, int causal, cudaStream_t st, int variant)
 {
     const int D = E / H;
+    if (variant == 4) return launch_mha_tc_pair(q, k, v, out, B, S, E, H, causal, st);
+    // default for head_dim 32 up to 1024 keys: fewer tensor-core instructions per tile and a softmax
+    // that runs ahead of the P V products; measured faster there, level with variant 1 beyond
+    if (variant == 5 || (variant == 0 && D == 32 && S <= 1024)) return launch_mha_tc16(q, k, v, out, B, S, E, H, causal, st);
     if (variant == 3) {
         if (D == 32) return causal ? launch_tcp_cfg<32, 64, true>(q, k, v, out, B, S, E, H, st)
                                    : launch_tcp_cfg<32, 64, false>(q, k, v, out, B, S, E, H, st);

@@ -1,0 +1,576 @@
+// Fused attention forward on the Blackwell tensor pipe (tcgen05 + TMEM), fp32-grade results,
+// head_dim 32: TF32 main products with FP16 correction products, and a pipeline in which the
+// softmax of tile t+1 does not wait for the P V product of tile t.
+//
+// Replaces the same reference kernels as attn_fwd_tc.cu (HipGPT src/hip_kernels.cpp:263-325 and
+// :329-402).  Arithmetic: every fp32 operand x is cut into hi (TF32-exact, 11 significant bits)
+// and lo = x - hi (exact).  A product a*b = a_hi*b_hi + a_lo*b_hi + a*b_lo is accumulated in the
+// tensor core's fp32 accumulator as
+//     a_hi*b_hi             one kind::tf32 instruction group,
+//     a_lo*b_hi + a*b_lo    one kind::f16 group on fp16 copies, concatenated along the reduction
+//                           dimension: [a_lo | a] x [b_hi | b_lo].  b_hi is exact in fp16 (11 bits),
+//                           a_lo, b_lo and a are rounded to 11 bits, an error of 2^-22 relative to
+//                           the product, the same order as the dropped a_lo*b_lo of plain split-TF32.
+// fp16 has K=16 per instruction against 8 for TF32, so a 64-key tile takes 20 instructions
+// instead of 28 (an instruction with M=128 costs about 64 cycles for any N <= 128).  fp16
+// conversions saturate; operands beyond +-65504 lose accuracy, not finiteness of the lo terms.
+//
+// One block = 128 query rows of one (batch, head): 128 workers (worker = row = TMEM lane), one
+// issuing warp, one warp that stages K and one that stages V.  Two blocks per SM.
+//   TMEM (256 columns): X0, X1 (64 each): S(t), overwritten in place by P_hi(t);  L0, L1 (32
+//   each): P_lo(t) as packed fp16;  O_ext (64): [P_hi V_hi | P_hi V_lo + P_lo V], accumulated over
+//   ALL tiles.  Workers never read O_ext back per tile: the running maximum is only moved (and O_ext
+//   rescaled, by the whole warp) when a row's maximum grew by more than 2^8 since the last rescale.
+//   With P double-buffered, the worker goes from tile t straight to tile t+1 while P V(t) runs.
+//   A worker reads its 64 scores from TMEM once; maximum, exponentials and the hi / lo cut all
+//   work on those registers.
+//   Shared memory: Q_hi (fp32) and [Q_lo | Q] (fp16); two stages of K (raw fp32 = the TF32
+//   operand, since the tensor core ignores the 13 low mantissa bits) and [K_hi | K_lo] (fp16); two
+//   stages of V (raw fp32, N-major), V_lo (fp32, N-major) and an fp16 copy of V (N-major, no swizzle).
+//   The K and V warps copy a tile with cp.async straight into its operand place, then read their
+//   own pieces back to derive the fp16 copies and V_lo.
+// Every wait is bounded: on expiry the block raises a flag that cuts all later waits short,
+// records a status code, skips its stores, frees its TMEM and returns.
+#include "tc_primitives.cuh"
+
+#include <math.h>
+
+namespace hipgpt {
+namespace {
+
+constexpr int kRows = 128;        // query rows per block
+constexpr int kKeys = 64;         // keys per tile
+constexpr int kWorkers = kRows;
+constexpr int kProducers = 64;       // one warp for K, one for V
+constexpr int kThreads = kWorkers + 32 + kProducers;
+constexpr float kRescaleStep = 8.0f;
+constexpr int D = 32;
+constexpr uint32_t kColX = 0, kColL = 128, kColO = 192, kTmemCols = 256;
+// byte sizes of the shared-memory operands
+constexpr int kQhiBytes = kRows * 128, kQ16Bytes = kRows * 128;
+constexpr int kKhiBytes = kKeys * 128, kK16Bytes = kKeys * 128, kKStage = kKhiBytes + kK16Bytes;
+constexpr int kVhlBytes = 2 * kKeys * 128, kV16Bytes = D * 128, kVStage = kVhlBytes + kV16Bytes;
+constexpr size_t kSmemBytes = (size_t)kQhiBytes + kQ16Bytes + 2 * kKStage + 2 * kVStage;
+
+__device__ int g_tc16_status = 0;
+
+// Optional timeline (build with -DHIPGPT_TC_TRACE): worker 0 of every block stores nanosecond
+// timestamps: [0] start, [1] prologue done, [2 + t] P(t) written (t < 6), [8] end, [9] SM id.
+#ifdef HIPGPT_TC_TRACE
+__device__ long long *g_trace16 = nullptr;
+__device__ __forceinline__ long long t16_now() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define T16(i) do { if (trace && tid == 0) trace[(i)] = t16_now(); } while (0)
+// cycle counter marks of worker 0 ([10 + 4t + k]) and of the issuing lane ([34 + 4t + k]), t < 6; [60] cycle counter at start
+#define C16(i) do { if (trace) trace[(i)] = clock64(); } while (0)
+#else
+#define T16(i) do { } while (0)
+#define C16(i) do { } while (0)
+#endif
+
+// fp32 accumulator, fp16 A and B, both K-major
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n)
+{
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_h_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_h_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// two floats -> one word of two fp16 (round to nearest, saturating), `lo` in the low half
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ void tmem_st8_u32(uint32_t addr, const uint32_t (&v)[8])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
+__device__ __forceinline__ float4 hi4(float4 x) { return make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w)); }
+
+// byte offset of 16-byte chunk c of row r in a tile of 128-byte rows, SWIZZLE_128B
+__device__ __forceinline__ int sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+
+template <bool CAUSAL>
+__global__ void __launch_bounds__(kThreads, 2)
+mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
+                float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_hi = base;                            // fp32 [128][32], K-major
+    uint8_t *q_16 = q_hi + kQhiBytes;                // fp16 [128][Q_lo(32) | Q(32)], K-major
+    uint8_t *k_st = q_16 + kQ16Bytes;                // per stage: K_hi fp32 [64][32], then fp16 [64][K_hi(32) | K_lo(32)]
+    uint8_t *v_st = k_st + 2 * kKStage;              // per stage: fp32 [hi block | lo block] N-major, then fp16 V^T [32][64 keys]
+    __shared__ uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], o_done[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef HIPGPT_TC_TRACE
+    long long *trace = g_trace16 ? g_trace16 + 128 * (size_t)blockIdx.x : nullptr;
+    if (trace && tid == 0) { int sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); trace[9] = sm; }
+#endif
+    T16(0);
+    if (tid == 0) C16(60);
+    const int bh = blockIdx.x % BH;
+    const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);     // heaviest first
+    const int b = bh / H, h = bh % H;
+    const size_t tok0 = (size_t)b * S;
+    const size_t hcol = (size_t)h * D;
+    const int q0 = qblk * kRows;
+    const int kend = CAUSAL ? min(S, q0 + kRows) : S;
+    const int nt = (kend + kKeys - 1) / kKeys;       // >= 1: q0 < S
+
+    if (tid == 0) {
+        abort_flag = 0;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);                // the K warp
+            mbar_init(&v_full[i], 1);                // the V warp
+            mbar_init(&k_free[i], 1);                // tcgen05.commit
+            mbar_init(&v_free[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], kWorkers / 32);    // one arrival per worker warp
+            mbar_init(&o_done[i], 1);                // by tile parity: a worker may be two tiles ahead of the P V products
+        }
+    }
+    __syncthreads();
+
+    // site codes in the status word: 1 S ready, 2 O complete (rescale), 3 O complete (end), 4 K staged,
+    // 5 P written, 6 V staged, 7 K stage free, 8 V stage free
+    auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
+        if (abort_flag) return;
+        if (!mbar_wait(bar, parity)) { abort_flag = 1; atomicCAS(&g_tc16_status, 0, site); }
+    };
+    // one arrival for the whole warp: every lane's writes are ordered before it by the warp barrier
+    auto arrive = [&](uint64_t *bar) {
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+    };
+
+    if (warp == kWorkers / 32) {
+        // ================= the issuing warp =====================================================
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncthreads();                             // Q staged; TMEM allocated
+        tc_fence_after();
+        const uint32_t tmem = tmem_base_slot;
+        if (lane == 0) {
+            constexpr uint32_t id_qk_h = idesc_f16(kRows, kKeys);            // [Q_lo | Q] x [K_hi | K_lo], fp16
+            constexpr uint32_t id_qk_t = make_idesc(kRows, kKeys, 0);        // Q_hi x K_hi, tf32
+            constexpr uint32_t id_pv_t = make_idesc(kRows, 2 * D, 1);        // P_hi x [V_hi | V_lo], tf32, B N-major
+            constexpr uint32_t id_pv_h = idesc_f16(kRows, D) | (1u << 16);    // P_lo x V (fp16 copy), B N-major
+            const uint64_t dq_hi = make_desc(smem_u32(q_hi), 16, 1024, 2);
+            const uint64_t dq_16 = make_desc(smem_u32(q_16), 16, 1024, 2);
+            auto issue_qk = [&](int buf, int stage) {
+                const uint64_t dk_hi = make_desc(smem_u32(k_st + stage * kKStage), 16, 1024, 2);
+                const uint64_t dk_16 = make_desc(smem_u32(k_st + stage * kKStage + kKhiBytes), 16, 1024, 2);
+                const uint32_t d = tmem + kColX + buf * kKeys;
+                // the correction terms first: the accumulator is still tiny while they are added
+#pragma unroll
+                for (int k = 0; k < 4; ++k)          // 16 fp16 = 32 bytes per instruction
+                    mma_h_ss(d, dq_16 + (uint64_t)(k * 2), dk_16 + (uint64_t)(k * 2), id_qk_h, k ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)          // 8 floats = 32 bytes per instruction
+                    mma_ss(d, dq_hi + (uint64_t)(k * 2), dk_hi + (uint64_t)(k * 2), id_qk_t, 1);
+                tc_commit(&s_full[buf]);
+                tc_commit(&k_free[stage]);
+            };
+            auto issue_pv = [&](int buf, int stage, bool first) {
+                // N-major fp32 B: 8 keys of 128 bytes per instruction; lbo = bytes between the hi and the lo block
+                const uint64_t dv = make_desc(smem_u32(v_st + stage * kVStage), kKeys * 128, 512, 1);
+                // no swizzle, N-major: lbo = bytes between groups of 8 keys, sbo = bytes between blocks of 8 columns
+                const uint64_t dvt = make_desc(smem_u32(v_st + stage * kVStage + kVhlBytes), 512, 128, 0);
+#pragma unroll
+                for (int k = 0; k < kKeys / 8; ++k)
+                    mma_ts(tmem + kColO, tmem + kColX + buf * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), id_pv_t, (first && k == 0) ? 0u : 1u);
+#pragma unroll
+                for (int k = 0; k < kKeys / 16; ++k)  // 16 keys = 8 TMEM columns of packed fp16 = two key groups (1024 bytes) of the fp16 V
+                    mma_h_ts(tmem + kColO + D, tmem + kColL + buf * 32 + (uint32_t)(k * 8), dvt + (uint64_t)(k * 64), id_pv_h, 1);
+                tc_commit(&o_done[buf]);
+                tc_commit(&v_free[stage]);
+            };
+            wait(&k_full[0], 0, 4);
+            tc_fence_after();
+            C16(58);
+            issue_qk(0, 0);
+            C16(59);
+            for (int t = 0; t < nt; ++t) {
+                const int st = t & 1;
+                if (t + 1 < nt) {
+                    wait(&k_full[st ^ 1], (uint32_t)(((t + 1) >> 1) & 1), 4);    // K(t+1) is in shared memory
+                    tc_fence_after();
+                    if (t < 6) C16(34 + 4 * t);
+                    issue_qk(st ^ 1, st ^ 1);        // its buffer held P(t-1): P V(t-1) was issued before, instructions run in order
+                    if (t < 6) C16(35 + 4 * t);
+                }
+                wait(&p_full[st], (uint32_t)((t >> 1) & 1), 5);                  // P(t) is in TMEM
+                wait(&v_full[st], (uint32_t)((t >> 1) & 1), 6);                  // V(t) is in shared memory
+                tc_fence_after();
+                if (t < 6) C16(36 + 4 * t);
+                issue_pv(st, st, t == 0);
+                if (t < 6) C16(37 + 4 * t);
+            }
+        }
+        __syncwarp();
+        tc_fence_before();
+        __syncthreads();                             // the workers have read the output
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        return;
+    }
+
+    // ================= the producers: one warp for K, one for V ====================================
+    // A tile goes from global memory straight to its place in the TF32 operand (cp.async, no
+    // registers held): the tensor core ignores the 13 low mantissa bits of a TF32 operand, so the
+    // raw fp32 tile IS the hi operand.  When it has landed the same thread reads its pieces back,
+    // derives the fp16 copies (and V_lo) and publishes the stage.  The copy of tile u+1 is issued
+    // before tile u is converted, as soon as its stage is free.
+    // A thread owns 32 bytes (8 floats) of two adjacent rows, four times per tile: an fp16 chunk is
+    // 16 bytes = 8 values, and V^T takes two adjacent keys per 32-bit store.
+    const int pc = lane & 3, pq = lane >> 2;         // 8-float piece of a row, row pair
+    auto piece_row = [&](int p) { return 16 * (p >> 1) + 2 * pq + (p & 1); };
+    // byte offset of 16-byte chunk c of row r in the N-major fp32 operand (32-byte pieces permuted by r mod 4)
+    auto nmaj = [](int r, int c) { return r * 128 + (((((c >> 1) ^ (r & 3)) << 1) | (c & 1)) << 4); };
+    if (warp == kWorkers / 32 + 1) {
+        auto copy_k = [&](int t, int stage) {
+            uint8_t *khi = k_st + stage * kKStage;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int r = piece_row(p), j = t * kKeys + r;
+                const bool ok = j < S;
+                const float *src = K + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + 8 * pc;
+                cp_async16(khi + sw128(r, 2 * pc), src, ok);
+                cp_async16(khi + sw128(r, 2 * pc + 1), src + 4, ok);
+            }
+            cp_async_commit();
+        };
+        auto convert_k = [&](int stage) {
+            uint8_t *khi = k_st + stage * kKStage, *k16 = khi + kKhiBytes;
+            float4 a[8], c[8];                       // all loads first: the stores below may alias them for the compiler
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int r = piece_row(p);
+                a[p] = *reinterpret_cast<const float4 *>(khi + sw128(r, 2 * pc));
+                c[p] = *reinterpret_cast<const float4 *>(khi + sw128(r, 2 * pc + 1));
+            }
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int r = piece_row(p);
+                const float4 ah = hi4(a[p]), ch = hi4(c[p]);
+                *reinterpret_cast<uint4 *>(k16 + sw128(r, pc)) =
+                    make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+                *reinterpret_cast<uint4 *>(k16 + sw128(r, 4 + pc)) =
+                    make_uint4(pack_f16(a[p].x - ah.x, a[p].y - ah.y), pack_f16(a[p].z - ah.z, a[p].w - ah.w),
+                               pack_f16(c[p].x - ch.x, c[p].y - ch.y), pack_f16(c[p].z - ch.z, c[p].w - ch.w));
+            }
+        };
+        copy_k(0, 0);
+        __syncthreads();                             // matches the block-wide barrier after Q staging
+        for (int u = 0; u < nt; ++u) {
+            const int st = u & 1;
+            if (lane == 0 && u < 6) C16(64 + 4 * u);
+            if (u + 1 < nt) {
+                if (u >= 1) wait(&k_free[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 7);   // Q K(u-1)^T has completed
+                copy_k(u + 1, st ^ 1);
+            } else {
+                cp_async_commit();                   // keeps the group count of the wait below
+            }
+            cp_async_wait_1();                       // K(u) has landed
+            if (lane == 0 && u < 6) C16(66 + 4 * u);
+            convert_k(st);
+            if (lane == 0 && u < 6) C16(65 + 4 * u);
+            proxy_fence();                           // generic-proxy writes -> visible to the tensor core
+            arrive(&k_full[st]);
+            if (lane == 0 && u < 6) C16(67 + 4 * u);
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        return;
+    }
+    if (warp == kWorkers / 32 + 2) {
+        auto copy_v = [&](int t, int stage) {
+            uint8_t *vhi = v_st + stage * kVStage;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int r = piece_row(p), j = t * kKeys + r;
+                const bool ok = j < S;
+                const float *src = V + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + 8 * pc;
+                cp_async16(vhi + nmaj(r, 2 * pc), src, ok);
+                cp_async16(vhi + nmaj(r, 2 * pc + 1), src + 4, ok);
+            }
+            cp_async_commit();
+        };
+        auto convert_v = [&](int stage) {
+            uint8_t *vhi = v_st + stage * kVStage, *vlo = vhi + kKeys * 128, *v16 = vhi + kVhlBytes;
+            float4 a[8], c[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int r = piece_row(p);
+                a[p] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, 2 * pc));
+                c[p] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, 2 * pc + 1));
+            }
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int r = piece_row(p);
+                const float4 ah = hi4(a[p]), ch = hi4(c[p]);
+                *reinterpret_cast<float4 *>(vlo + nmaj(r, 2 * pc)) = make_float4(a[p].x - ah.x, a[p].y - ah.y, a[p].z - ah.z, a[p].w - ah.w);
+                *reinterpret_cast<float4 *>(vlo + nmaj(r, 2 * pc + 1)) = make_float4(c[p].x - ch.x, c[p].y - ch.y, c[p].z - ch.z, c[p].w - ch.w);
+                // fp16 copy, N-major without swizzle: 8 keys x 8 columns form one 128-byte core matrix
+                // (key i of the group at 16 i); column blocks 128 bytes apart, key groups 512 bytes apart
+                *reinterpret_cast<uint4 *>(v16 + (r >> 3) * 512 + pc * 128 + (r & 7) * 16) =
+                    make_uint4(pack_f16(a[p].x, a[p].y), pack_f16(a[p].z, a[p].w), pack_f16(c[p].x, c[p].y), pack_f16(c[p].z, c[p].w));
+            }
+        };
+        copy_v(0, 0);
+        __syncthreads();
+        for (int u = 0; u < nt; ++u) {
+            const int st = u & 1;
+            if (lane == 0 && u < 6) C16(96 + 4 * u);
+            cp_async_wait_all();                     // V(u) has landed
+            if (lane == 0 && u < 6) C16(97 + 4 * u);
+            convert_v(st);
+            proxy_fence();
+            arrive(&v_full[st]);
+            if (lane == 0 && u < 6) C16(98 + 4 * u);
+            if (u + 1 < nt) {
+                // the stage of V(u+1) held V(u-1); V(u) is published before this warp waits for that product
+                if (u >= 1) wait(&v_free[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 8);   // P V(u-1) has completed
+                copy_v(u + 1, st ^ 1);
+            }
+            if (lane == 0 && u < 6) C16(99 + 4 * u);
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        return;
+    }
+
+    // ===================== the workers ===========================================================
+    const int wq = warp;                             // TMEM lane quadrant of this warp
+    const int rloc = wq * 32 + lane;                 // row inside the block = TMEM lane
+    const int row = q0 + rloc;
+    {
+        const bool ok = row < S;
+        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float4 a = ok ? __ldg(src + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 c = ok ? __ldg(src + 2 * j + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+            a.x *= qscale; a.y *= qscale; a.z *= qscale; a.w *= qscale;     // scores come out in the log2 domain
+            c.x *= qscale; c.y *= qscale; c.z *= qscale; c.w *= qscale;
+            const float4 ah = hi4(a), ch = hi4(c);
+            *reinterpret_cast<float4 *>(q_hi + sw128(rloc, 2 * j)) = ah;
+            *reinterpret_cast<float4 *>(q_hi + sw128(rloc, 2 * j + 1)) = ch;
+            *reinterpret_cast<uint4 *>(q_16 + sw128(rloc, j)) =
+                make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
+                           pack_f16(c.x - ch.x, c.y - ch.y), pack_f16(c.z - ch.z, c.w - ch.w));
+            *reinterpret_cast<uint4 *>(q_16 + sw128(rloc, 4 + j)) =
+                make_uint4(pack_f16(a.x, a.y), pack_f16(a.z, a.w), pack_f16(c.x, c.y), pack_f16(c.z, c.w));
+        }
+    }
+    proxy_fence();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t lane_base = tmem_base_slot + ((uint32_t)(wq * 32) << 16);
+    const uint32_t o_addr = lane_base + kColO;
+    T16(1);
+
+    float m_ref = 0.0f, l = 0.0f;                    // reference maximum (log2 domain) and row sum
+    for (int t = 0; t < nt; ++t) {
+        const int buf = t & 1;
+        const int j0 = t * kKeys;
+        const uint32_t s_addr = lane_base + kColX + buf * kKeys, l_addr = lane_base + kColL + buf * 32;
+        wait(&s_full[buf], (uint32_t)((t >> 1) & 1), 1);   // S(t) is in TMEM
+        tc_fence_after();
+        if (tid == 0 && t < 6) C16(10 + 4 * t);
+        const int wrow0 = q0 + wq * 32;              // first row of this warp
+        const bool warp_dead = CAUSAL && j0 > wrow0 + 31;          // these columns are above the diagonal for the whole warp
+        const bool need_mask = (CAUSAL && j0 + kKeys - 1 > wrow0) || j0 + kKeys > S;
+        const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : kKeys);     // visible columns of this row
+
+        // ---- the row's 64 scores are read from TMEM once and stay in registers --------------------
+        float v0[32], v1[32];
+        float mx = -INFINITY;
+        if (!warp_dead) {
+            tmem_ld32(s_addr, v0);
+            tmem_ld32(s_addr + 32, v1);
+            tmem_wait_ld();
+            if (need_mask) {
+                // a masked score becomes -inf: its exponential below is exactly 0
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    v0[c] = (c < nvalid) ? v0[c] : -INFINITY;
+                    v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
+                }
+            }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                m4[(c >> 1) & 1] = fmaxf(m4[(c >> 1) & 1], fmaxf(v0[c], v0[c + 1]));
+                m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
+            }
+            mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        }
+        if (t == 0) {
+            m_ref = fmaxf(mx, -1e30f);
+        } else {
+            const bool grow = mx > m_ref + kRescaleStep;
+            if (__any_sync(0xffffffffu, grow)) {
+                // the accumulator is rescaled by the whole warp (TMEM accesses are warp-wide);
+                // rows that did not grow use factor 1
+                const float alpha = grow ? ex2_approx(m_ref - mx) : 1.0f;
+                if (grow) m_ref = mx;
+                l *= alpha;
+                wait(&o_done[(t - 1) & 1], (uint32_t)(((t - 1) >> 1) & 1), 2);   // P V(t-1) has completed
+                tc_fence_after();
+#pragma unroll
+                for (int hh = 0; hh < 4; ++hh) {
+                    float a[16];
+                    tmem_ld16(o_addr + hh * 16, a);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) a[c] *= alpha;
+                    tmem_st16(o_addr + hh * 16, a);
+                }
+            }
+        }
+
+        if (tid == 0 && t < 6) C16(11 + 4 * t);
+        // ---- exponentials; P_hi over S in place, P_lo as packed fp16 ---------------------------------
+        float psum = 0.0f;
+        if (warp_dead) {
+            float z[16];
+            uint32_t zz[8];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) z[c] = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) zz[c] = 0u;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                tmem_st16(s_addr + k * 16, z);
+                tmem_st8_u32(l_addr + k * 8, zz);
+            }
+        } else {
+            float ps4[4] = {0.0f, 0.0f, 0.0f, 0.0f};    // four summation chains
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float hi[16];
+                uint32_t pk[8];
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                    const float s0 = (k < 2) ? v0[(k & 1) * 16 + c] : v1[(k & 1) * 16 + c];
+                    const float s1 = (k < 2) ? v0[(k & 1) * 16 + c + 1] : v1[(k & 1) * 16 + c + 1];
+                    const float p0 = ex2_approx(s0 - m_ref), p1 = ex2_approx(s1 - m_ref);
+                    ps4[c & 3] += p0;
+                    ps4[(c + 1) & 3] += p1;
+                    hi[c] = tf32_hi(p0);
+                    hi[c + 1] = tf32_hi(p1);
+                    pk[c >> 1] = pack_f16(p0 - hi[c], p1 - hi[c + 1]);
+                }
+                tmem_st16(s_addr + k * 16, hi);
+                tmem_st8_u32(l_addr + k * 8, pk);
+            }
+            psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+        }
+        l += psum;
+        tmem_wait_st();
+        tc_fence_before();
+        arrive(&p_full[buf]);
+        if (t < 6) T16(2 + t);
+        if (tid == 0 && t < 6) C16(12 + 4 * t);
+    }
+
+    {
+        wait(&o_done[(nt - 1) & 1], (uint32_t)(((nt - 1) >> 1) & 1), 3);
+        tc_fence_after();
+        if (tid == 0) C16(62);
+        const float inv = 1.0f / fmaxf(l, 1e-20f);
+        float a[32], c2[32];
+        tmem_ld32(o_addr, a);                        // P_hi V_hi
+        tmem_ld32(o_addr + D, c2);                   // the correction terms
+        tmem_wait_ld();
+        if (!abort_flag && row < S) {
+            float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol);
+#pragma unroll
+            for (int c = 0; c < D / 4; ++c)
+                dst[c] = make_float4((a[c * 4 + 0] + c2[c * 4 + 0]) * inv, (a[c * 4 + 1] + c2[c * 4 + 1]) * inv,
+                                     (a[c * 4 + 2] + c2[c * 4 + 2]) * inv, (a[c * 4 + 3] + c2[c * 4 + 3]) * inv);
+        }
+    }
+    T16(8);
+    if (tid == 0) C16(61);
+    tc_fence_before();
+    __syncthreads();
+}
+
+template <bool CAUSAL>
+int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, cudaStream_t st)
+{
+    auto kern = mha_tc16_kernel<CAUSAL>;
+    // at least 100 KB: at most two blocks share an SM, so their 256-column allocations always fit in the 512 columns
+    size_t smem = kSmemBytes + 1024;
+    if (smem < 100 * 1024) smem = 100 * 1024;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const int nqblk = (S + kRows - 1) / kRows;
+    const long long blocks = (long long)B * H * nqblk;
+    if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
+    const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
+    kern<<<(unsigned)blocks, kThreads, smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
+    return check_launch("mha_tc16_kernel");
+}
+
+}  // namespace
+
+bool mha_tc16_supports(int head_dim) { return head_dim == D; }
+
+int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st)
+{
+    if (!mha_tc16_supports(E / H)) return fail(HIPGPT_ERR_UNSUPPORTED, "tf32+fp16 tensor-core kernel: head_dim %d is not 32", E / H);
+    if (B == 0 || S == 0) return HIPGPT_OK;
+    return causal ? launch_tc16_cfg<true>(q, k, v, out, B, S, E, H, st) : launch_tc16_cfg<false>(q, k, v, out, B, S, E, H, st);
+}
+
+#ifdef HIPGPT_TC_TRACE
+}  // namespace hipgpt
+extern "C" __attribute__((visibility("default"))) void hipgpt_debug_trace16(long long *buf)
+{
+    cudaMemcpyToSymbol(hipgpt::g_trace16, &buf, sizeof(buf));
+}
+namespace hipgpt {
+#endif
+
+int tc16_status_fetch(int *status)
+{
+    int s = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&s, g_tc16_status, sizeof(int));
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+    if (s != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tc16_status, &zero, sizeof(int));
+    }
+    *status = s;
+    return HIPGPT_OK;
+}
+
+}  // namespace hipgpt

@@ -286,12 +286,18 @@ int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end)
 int hipgpt_kernel_status(int *status)
 {
     if (!status) return fail(HIPGPT_ERR_NULL, "status must not be NULL");
-    int a = 0, b = 0;
+    int a = 0, b = 0, c = 0;
     int rc = tc_status_fetch(&a);
     if (rc != HIPGPT_OK) return rc;
     rc = bf16_status_fetch(&b);
     if (rc != HIPGPT_OK) return rc;
-    *status = a ? a : (b ? 100 + b : 0);          // 1xx: the bf16 kernel's wait sites
+    rc = tc_pair_status_fetch(&c);
+    if (rc != HIPGPT_OK) return rc;
+    int d = 0;
+    rc = tc16_status_fetch(&d);
+    if (rc != HIPGPT_OK) return rc;
+    // 1xx: the bf16 kernel's wait sites, 2xx: the paired kernel's, 3xx: the tf32+fp16 kernel's
+    *status = a ? a : (b ? 100 + b : (c ? 200 + c : (d ? 300 + d : 0)));
     return HIPGPT_OK;
 }
 

@@ -67,8 +67,14 @@ HIPGPT_API int hipgpt_mha_forward(const float *d_q, const float *d_k, const floa
                        float *d_out, float *d_probs,
                        int B, int S, int E, int H, int causal, void *stream);
 
-/* The same with an explicit kernel selector (HIPGPT_ALGO_*) and, for HIPGPT_ALGO_ROWS,
- * the number of warps per thread block (0 = default). */
+/* The same with an explicit kernel selector (HIPGPT_ALGO_*).  `warps`: for HIPGPT_ALGO_ROWS the
+ * number of warps per thread block (0 = default); for HIPGPT_ALGO_TENSOR the schedule variant
+ * (profiling and tests): 0 default (variant 5 for head_dim 32 up to 1024 keys, else 1), 1 = split-TF32
+ * with 64-key tiles, 2 = 128-key tiles with two workers per row (head_dim 32),
+ * 3 = persistent blocks over a stream of tiles, 4 = two query tiles per block with the output
+ * accumulated in tensor memory (head_dim 32), 5 = TF32 main products with FP16 correction
+ * products and a softmax that runs ahead of the P V products (head_dim 32).  All variants hold
+ * the same 1e-5 accuracy. */
 HIPGPT_API int hipgpt_mha_forward_ex(const float *d_q, const float *d_k, const float *d_v,
                           float *d_out, float *d_probs,
                           int B, int S, int E, int H, int causal,
@@ -184,9 +190,11 @@ HIPGPT_API int hipgpt_probe_fma(float *d_sink, int blocks, int iters, double *fl
 
 /*
  * Device-side status of the tensor-core kernels (no counterpart in the reference).  Their
- * waits on hardware barriers are bounded; a block whose wait runs out stores nothing and sets
- * the status to 1.  This call waits for the device, stores the status word in *status and
- * clears it.  0 means every launch since the last call completed normally.
+ * waits on hardware barriers are bounded; a block whose wait runs out stores nothing and records
+ * which wait it was: 1..8 for the split-TF32 kernel, 100 + site for the bf16 kernel, 200 + site
+ * and 300 + site for the two other fp32 tensor-core variants.  This call waits for the device,
+ * stores the status word in *status and clears it.  0 means every launch since the last call
+ * completed normally.
  */
 HIPGPT_API int hipgpt_kernel_status(int *status);
 

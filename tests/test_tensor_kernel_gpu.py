@@ -57,7 +57,13 @@ def test_tensor_kernel_benchmark_shapes(cfg, causal):
 # 2 = 128-key tiles with two workers per row (head_dim 32), 3 = persistent blocks over a tile stream
 @pytest.mark.parametrize("variant,shape", [(2, (2, 2, 200, 32)), (2, (4, 8, 256, 32)), (2, (1, 1, 513, 32)),
                                            (3, (2, 2, 200, 32)), (3, (32, 8, 256, 32)), (3, (1, 2, 300, 64)),
-                                           (3, (3, 40, 130, 32)), (3, (2, 4, 1024, 64))])
+                                           (3, (3, 40, 130, 32)), (3, (2, 4, 1024, 64)),
+                                           # 4 = two query tiles per block with the output accumulated in tensor memory,
+                                           # 5 = TF32 main products + FP16 correction products (both head_dim 32)
+                                           (4, (1, 1, 7, 32)), (4, (2, 3, 200, 32)), (4, (1, 1, 513, 32)), (4, (32, 8, 256, 32)),
+                                           (4, (2, 2, 2048, 32)),
+                                           (5, (1, 1, 1, 32)), (5, (1, 1, 7, 32)), (5, (1, 2, 65, 32)), (5, (2, 3, 200, 32)),
+                                           (5, (1, 1, 513, 32)), (5, (32, 8, 256, 32)), (5, (3, 5, 640, 32)), (5, (2, 2, 2048, 32))])
 @pytest.mark.parametrize("causal", [False, True])
 def test_tensor_kernel_variants_match_oracle(variant, shape, causal):
     B, H, S, D = shape
@@ -82,3 +88,31 @@ def test_tensor_kernel_refuses_what_it_cannot_do():
     t32 = torch.zeros((64, 32), device="cuda")
     assert lib.hipgpt_mha_forward_ex(t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), p.data_ptr(),
                                      1, 64, 32, 1, 0, _capi.ALGO_TENSOR, 0, st) == _capi.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("variant", [4, 5])
+def test_accumulating_variants_rescale_when_row_maxima_grow(variant):
+    """Variants that keep the output in tensor memory move the reference maximum only when a row's
+    maximum grew by more than 2^8; keys whose scores rise steeply along the sequence force that
+    rescale at every tile."""
+    B, H, S, D = 1, 2, 640, 32
+    E = H * D
+    qkv = synth.qkv_planes(78, B, S, E).reshape(3, B * S, E).copy()
+    sign = np.sign(qkv[0][:1])
+    ramp = (1.0 + np.arange(S, dtype=np.float32) / 40.0)[:, None]
+    qkv[1] = sign * ramp                      # keys grow along the sequence, aligned with every query
+    qkv[0] = np.abs(qkv[0]) * sign
+    for causal in (False, True):
+        ref_out, _ = ob.mha(qkv, B, S, E, H, causal=causal)
+        out, _ = gpu_mha(qkv, B, S, E, H, causal, False, algo=_capi.ALGO_TENSOR, warps=variant)
+        assert _status() == 0
+        assert float(np.abs(out - ref_out).max()) <= 1e-4     # scores reach ~100: the fp32 arithmetic itself is good to ~1e-5 here
+
+
+@pytest.mark.parametrize("variant", [4, 5])
+def test_head_dim_32_variants_refuse_other_head_dims(variant):
+    lib = _capi.lib()
+    t = torch.zeros((64, 64), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.hipgpt_mha_forward_ex(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), None,
+                                     1, 64, 64, 1, 0, _capi.ALGO_TENSOR, variant, st) == _capi.ERR_UNSUPPORTED
