@@ -375,7 +375,11 @@ def run_ours(args):
     bf16_peak = float(peaks.get("bf16_tflops_sustained" if bf16 else "bf16_tflops", 1400.0 if bf16 else 1590.0))
     tf32_peak = bf16_peak / 2.0
     t_hbm = per_batch_bytes / (hbm_peak * 1e9)
-    t_pipe = (flops_launch / (bf16_peak * 1e12)) if bf16 else (3.0 * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
+    # tensor work per fp32 product, in TF32 products: 3 for split-TF32; the default kernel (all but head_dim 32
+    # beyond 1024 keys) runs one TF32 product and two FP16 products (twice the TF32 rate)
+    tc16 = tensor_kernel and not bf16 and (D == 64 or S <= 1024)
+    tf32_products = 2.0 if tc16 else 3.0
+    t_pipe = (flops_launch / (bf16_peak * 1e12)) if bf16 else (tf32_products * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
     src = "measured" if peaks else "fallback"
     if bf16 and t_hbm < t_pipe:
         roofline = {"bound": "tensor", "achieved": achieved, "peak": bf16_peak, "unit": "TFLOP/s", "frac": achieved / bf16_peak,
@@ -384,13 +388,13 @@ def run_ours(args):
         roofline = {"bound": "hbm", "achieved": hbm_achieved, "peak": hbm_peak, "unit": "GB/s",
                     "frac": hbm_achieved / hbm_peak, "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({src})"}
     elif tensor_kernel:
-        roofline = {"bound": "tensor", "achieved": 3.0 * achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                    "frac": 3.0 * achieved / tf32_peak,
-                    "peak_source": f"half of MEASURED_PEAKS.json bf16_tflops ({src}): TF32 rate; achieved counts the 3 TF32 products per fp32 product"}
+        roofline = {"bound": "tensor", "achieved": tf32_products * achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+                    "frac": tf32_products * achieved / tf32_peak,
+                    "peak_source": f"half of MEASURED_PEAKS.json bf16_tflops ({src}): TF32 rate; achieved counts the {tf32_products:.0f} TF32-equivalent products per fp32 product"}
     else:
         roofline = {"bound": "fma", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s", "frac": achieved / fma_peak,
                     "peak_source": "fp32 FFMA loop timed in this run"}
-    roofline.update({"kernel": "mha_bf16_kernel" if bf16 else "mha_tc_kernel" if tensor_kernel else "mha_rows_kernel",
+    roofline.update({"kernel": "mha_bf16_kernel" if bf16 else "mha_tc16_kernel" if tc16 else "mha_tc_kernel" if tensor_kernel else "mha_rows_kernel",
                      "traffic": None if bf16 else TRAFFIC.get((args.workload, tensor_kernel)),
                      "us_per_launch": launch_ms * 1e3, "algorithmic_bytes_per_launch": per_batch_bytes,
                      "algorithmic_flops_per_launch": flops_launch,

@@ -1,5 +1,5 @@
 // Fused attention forward on the Blackwell tensor pipe (tcgen05 + TMEM), fp32-grade results,
-// head_dim 32: TF32 main products with FP16 correction products, and a pipeline in which the
+// head_dim 32 or 64: TF32 main products with FP16 correction products, and a pipeline in which the
 // softmax of tile t+1 does not wait for the P V product of tile t.
 //
 // Replaces the same reference kernels as attn_fwd_tc.cu (HipGPT src/hip_kernels.cpp:263-325 and
@@ -12,11 +12,12 @@
 //                           a_lo, b_lo and a are rounded to 11 bits, an error of 2^-22 relative to
 //                           the product, the same order as the dropped a_lo*b_lo of plain split-TF32.
 // fp16 has K=16 per instruction against 8 for TF32, so a 64-key tile takes 20 instructions
-// instead of 28 (an instruction with M=128 costs about 64 cycles for any N <= 128).  fp16
+// instead of 28 at head_dim 32 and 28 instead of 40 at head_dim 64 (an instruction with M=128 costs about 64 cycles for any N <= 128).  fp16
 // conversions saturate; operands beyond +-65504 lose accuracy, not finiteness of the lo terms.
 //
 // One block = 128 query rows of one (batch, head): 128 workers (worker = row = TMEM lane), one
-// issuing warp, one warp that stages K and one that stages V.  Two blocks per SM.
+// issuing warp, one warp that stages K and one that stages V.  Two blocks per SM at head_dim 32,
+// one at head_dim 64 (the sizes below are those of head_dim 32).
 //   TMEM (256 columns): X0, X1 (64 each): S(t), overwritten in place by P_hi(t);  L0, L1 (32
 //   each): P_lo(t) as packed fp16;  O_ext (64): [P_hi V_hi | P_hi V_lo + P_lo V], accumulated over
 //   ALL tiles.  Workers never read O_ext back per tile: the running maximum is only moved (and O_ext
@@ -41,16 +42,26 @@ namespace {
 constexpr int kRows = 128;        // query rows per block
 constexpr int kKeys = 64;         // keys per tile
 constexpr int kWorkers = kRows;
-constexpr int kProducers = 64;       // one warp for K, one for V
-constexpr int kThreads = kWorkers + 32 + kProducers;
 constexpr float kRescaleStep = 8.0f;
-constexpr int D = 32;
-constexpr uint32_t kColX = 0, kColL = 128, kColO = 192, kTmemCols = 256;
-// byte sizes of the shared-memory operands
-constexpr int kQhiBytes = kRows * 128, kQ16Bytes = kRows * 128;
-constexpr int kKhiBytes = kKeys * 128, kK16Bytes = kKeys * 128, kKStage = kKhiBytes + kK16Bytes;
-constexpr int kVhlBytes = 2 * kKeys * 128, kV16Bytes = D * 128, kVStage = kVhlBytes + kV16Bytes;
-constexpr size_t kSmemBytes = (size_t)kQhiBytes + kQ16Bytes + 2 * kKStage + 2 * kVStage;
+constexpr uint32_t kColX = 0, kColL = 128, kColO = 192;
+
+// Sizes that depend on head_dim.  An operand row is cut into blocks of 128 bytes (32 floats or 64
+// fp16 values); a block of a tile is [rows][128 bytes], 128-byte swizzled.
+template <int D>
+struct Tc16Cfg {
+    static constexpr int DB = D / 32;                         // fp32 blocks per row
+    static constexpr int HB = (2 * D) / 64;                   // fp16 blocks per row of [x_lo | x] or [x_hi | x_lo]
+    static constexpr int PPR = D / 8;                         // 32-byte pieces per row
+    static constexpr int PW = D / 32;                         // warps that stage K, and as many that stage V
+    static constexpr int THREADS = kWorkers + 32 + 2 * PW * 32;   // workers, the issuing warp, the K warps, the V warps
+    static constexpr uint32_t kTmemCols = (kColO + 2 * D) <= 256 ? 256 : 512;
+    static constexpr int BLOCKS_PER_SM = kTmemCols == 256 ? 2 : 1;
+    static constexpr int kQBlk = kRows * 128, kKBlk = kKeys * 128;      // bytes of one block of a Q / K / V tile
+    static constexpr int kQhiBytes = DB * kQBlk, kQ16Bytes = HB * kQBlk;
+    static constexpr int kKhiBytes = DB * kKBlk, kK16Bytes = HB * kKBlk, kKStage = kKhiBytes + kK16Bytes;
+    static constexpr int kVhlBytes = 2 * DB * kKBlk, kV16Bytes = kKeys * D * 2, kVStage = kVhlBytes + kV16Bytes;
+    static constexpr size_t kSmemBytes = (size_t)kQhiBytes + kQ16Bytes + 2 * kKStage + 2 * kVStage;
+};
 
 __device__ int g_tc16_status = 0;
 
@@ -109,17 +120,20 @@ __device__ __forceinline__ float4 hi4(float4 x) { return make_float4(tf32_hi(x.x
 // byte offset of 16-byte chunk c of row r in a tile of 128-byte rows, SWIZZLE_128B
 __device__ __forceinline__ int sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
 
-template <bool CAUSAL>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(Tc16Cfg<D>::THREADS, Tc16Cfg<D>::BLOCKS_PER_SM)
 mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
                 float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
 {
+    using C = Tc16Cfg<D>;
+    constexpr int DB = C::DB, HB = C::HB, PPR = C::PPR, PW = C::PW;
+    constexpr int kQBlk = C::kQBlk, kKBlk = C::kKBlk, kKStage = C::kKStage, kVStage = C::kVStage;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *q_hi = base;                            // fp32 [128][32], K-major
-    uint8_t *q_16 = q_hi + kQhiBytes;                // fp16 [128][Q_lo(32) | Q(32)], K-major
-    uint8_t *k_st = q_16 + kQ16Bytes;                // per stage: K_hi fp32 [64][32], then fp16 [64][K_hi(32) | K_lo(32)]
-    uint8_t *v_st = k_st + 2 * kKStage;              // per stage: fp32 [hi block | lo block] N-major, then fp16 V^T [32][64 keys]
+    uint8_t *q_hi = base;                            // fp32 [DB][128][32], K-major
+    uint8_t *q_16 = q_hi + C::kQhiBytes;             // fp16 [HB][128][64]: a row is [Q_lo (D) | Q (D)], K-major
+    uint8_t *k_st = q_16 + C::kQ16Bytes;             // per stage: K fp32 [DB][64][32], then fp16 [HB][64][64]: [K_hi (D) | K_lo (D)]
+    uint8_t *v_st = k_st + 2 * kKStage;              // per stage: fp32 N-major [V blocks | V_lo blocks], then the fp16 copy of V
     __shared__ uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
@@ -144,8 +158,8 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         abort_flag = 0;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&k_full[i], 1);                // the K warp
-            mbar_init(&v_full[i], 1);                // the V warp
+            mbar_init(&k_full[i], PW);               // one arrival per K warp
+            mbar_init(&v_full[i], PW);               // one arrival per V warp
             mbar_init(&k_free[i], 1);                // tcgen05.commit
             mbar_init(&v_free[i], 1);
             mbar_init(&s_full[i], 1);
@@ -166,10 +180,13 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
     };
+    // byte offset, inside an fp16 operand of rows [lo (D) | hi (D)], of the 16-byte chunk holding values
+    // 8 e8 .. 8 e8 + 7 of row r; blk = bytes of one 128-byte-row block of that operand
+    auto off16 = [](int r, int e8, int blk) { return (e8 >> 3) * blk + sw128(r, e8 & 7); };
 
     if (warp == kWorkers / 32) {
         // ================= the issuing warp =====================================================
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncthreads();                             // Q staged; TMEM allocated
@@ -179,34 +196,41 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             constexpr uint32_t id_qk_h = idesc_f16(kRows, kKeys);            // [Q_lo | Q] x [K_hi | K_lo], fp16
             constexpr uint32_t id_qk_t = make_idesc(kRows, kKeys, 0);        // Q_hi x K_hi, tf32
             constexpr uint32_t id_pv_t = make_idesc(kRows, 2 * D, 1);        // P_hi x [V_hi | V_lo], tf32, B N-major
-            constexpr uint32_t id_pv_h = idesc_f16(kRows, D) | (1u << 16);    // P_lo x V (fp16 copy), B N-major
-            const uint64_t dq_hi = make_desc(smem_u32(q_hi), 16, 1024, 2);
-            const uint64_t dq_16 = make_desc(smem_u32(q_16), 16, 1024, 2);
+            constexpr uint32_t id_pv_h = idesc_f16(kRows, D) | (1u << 16);   // P_lo x V (fp16 copy), B N-major
             auto issue_qk = [&](int buf, int stage) {
-                const uint64_t dk_hi = make_desc(smem_u32(k_st + stage * kKStage), 16, 1024, 2);
-                const uint64_t dk_16 = make_desc(smem_u32(k_st + stage * kKStage + kKhiBytes), 16, 1024, 2);
                 const uint32_t d = tmem + kColX + buf * kKeys;
                 // the correction terms first: the accumulator is still tiny while they are added
 #pragma unroll
-                for (int k = 0; k < 4; ++k)          // 16 fp16 = 32 bytes per instruction
-                    mma_h_ss(d, dq_16 + (uint64_t)(k * 2), dk_16 + (uint64_t)(k * 2), id_qk_h, k ? 1u : 0u);
+                for (int hb = 0; hb < HB; ++hb) {
+                    const uint64_t dq = make_desc(smem_u32(q_16 + hb * kQBlk), 16, 1024, 2);
+                    const uint64_t dk = make_desc(smem_u32(k_st + stage * kKStage + C::kKhiBytes + hb * kKBlk), 16, 1024, 2);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)          // 8 floats = 32 bytes per instruction
-                    mma_ss(d, dq_hi + (uint64_t)(k * 2), dk_hi + (uint64_t)(k * 2), id_qk_t, 1);
+                    for (int k = 0; k < 4; ++k)      // 16 fp16 = 32 bytes per instruction
+                        mma_h_ss(d, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_qk_h, (hb | k) ? 1u : 0u);
+                }
+#pragma unroll
+                for (int db = 0; db < DB; ++db) {
+                    const uint64_t dq = make_desc(smem_u32(q_hi + db * kQBlk), 16, 1024, 2);
+                    const uint64_t dk = make_desc(smem_u32(k_st + stage * kKStage + db * kKBlk), 16, 1024, 2);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)      // 8 floats = 32 bytes per instruction
+                        mma_ss(d, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_qk_t, 1);
+                }
                 tc_commit(&s_full[buf]);
                 tc_commit(&k_free[stage]);
             };
             auto issue_pv = [&](int buf, int stage, bool first) {
-                // N-major fp32 B: 8 keys of 128 bytes per instruction; lbo = bytes between the hi and the lo block
-                const uint64_t dv = make_desc(smem_u32(v_st + stage * kVStage), kKeys * 128, 512, 1);
-                // no swizzle, N-major: lbo = bytes between groups of 8 keys, sbo = bytes between blocks of 8 columns
-                const uint64_t dvt = make_desc(smem_u32(v_st + stage * kVStage + kVhlBytes), 512, 128, 0);
+                // fp32 N-major B: 8 keys of 128 bytes per instruction; lbo = bytes between 32-column blocks
+                // (V blocks, then V_lo blocks: one operand of 2D columns)
+                const uint64_t dv = make_desc(smem_u32(v_st + stage * kVStage), kKBlk, 512, 1);
+                // fp16 copy, no swizzle, N-major: lbo = bytes between groups of 8 keys, sbo = bytes between blocks of 8 columns
+                const uint64_t dvt = make_desc(smem_u32(v_st + stage * kVStage + C::kVhlBytes), D * 16, 128, 0);
 #pragma unroll
                 for (int k = 0; k < kKeys / 8; ++k)
                     mma_ts(tmem + kColO, tmem + kColX + buf * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), id_pv_t, (first && k == 0) ? 0u : 1u);
 #pragma unroll
-                for (int k = 0; k < kKeys / 16; ++k)  // 16 keys = 8 TMEM columns of packed fp16 = two key groups (1024 bytes) of the fp16 V
-                    mma_h_ts(tmem + kColO + D, tmem + kColL + buf * 32 + (uint32_t)(k * 8), dvt + (uint64_t)(k * 64), id_pv_h, 1);
+                for (int k = 0; k < kKeys / 16; ++k)  // 16 keys = 8 TMEM columns of packed fp16 = two key groups of the fp16 V
+                    mma_h_ts(tmem + kColO + D, tmem + kColL + buf * 32 + (uint32_t)(k * 8), dvt + (uint64_t)(k * 2 * D), id_pv_h, 1);
                 tc_commit(&o_done[buf]);
                 tc_commit(&v_free[stage]);
             };
@@ -235,53 +259,61 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         __syncwarp();
         tc_fence_before();
         __syncthreads();                             // the workers have read the output
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
         return;
     }
 
-    // ================= the producers: one warp for K, one for V ====================================
+    // ================= the producers: D/32 warps for K, as many for V ==============================
     // A tile goes from global memory straight to its place in the TF32 operand (cp.async, no
     // registers held): the tensor core ignores the 13 low mantissa bits of a TF32 operand, so the
     // raw fp32 tile IS the hi operand.  When it has landed the same thread reads its pieces back,
     // derives the fp16 copies (and V_lo) and publishes the stage.  The copy of tile u+1 is issued
     // before tile u is converted, as soon as its stage is free.
-    // A thread owns 32 bytes (8 floats) of two adjacent rows, four times per tile: an fp16 chunk is
-    // 16 bytes = 8 values, and V^T takes two adjacent keys per 32-bit store.
-    const int pc = lane & 3, pq = lane >> 2;         // 8-float piece of a row, row pair
-    auto piece_row = [&](int p) { return 16 * (p >> 1) + 2 * pq + (p & 1); };
-    // byte offset of 16-byte chunk c of row r in the N-major fp32 operand (32-byte pieces permuted by r mod 4)
+    // A thread owns 32-byte pieces (8 floats) of pairs of adjacent rows, eight per tile: an fp16 chunk
+    // is 16 bytes = 8 values.
+    constexpr int PT = 32 * PW;                      // threads per operand
+    constexpr int NPC = (kKeys * PPR) / PT;          // pieces per thread and tile: 8
+    constexpr int RPP = 2 * (PT / PPR);              // rows covered by a pair of passes
+    const int pid = (tid - kWorkers - 32) % PT;      // index among the threads of this operand
+    const int pc = pid % PPR, pq = pid / PPR;        // piece of a row, row pair
+    auto piece_row = [&](int p) { return RPP * (p >> 1) + 2 * pq + (p & 1); };
+    const int pblk = pc >> 2, pch = 2 * (pc & 3);    // fp32 block and first 16-byte chunk of the piece
+    // byte offset of 16-byte chunk c of row r in a block of the N-major fp32 operand (32-byte pieces permuted by r mod 4)
     auto nmaj = [](int r, int c) { return r * 128 + (((((c >> 1) ^ (r & 3)) << 1) | (c & 1)) << 4); };
-    if (warp == kWorkers / 32 + 1) {
+    if (warp > kWorkers / 32 && warp <= kWorkers / 32 + PW) {
         auto copy_k = [&](int t, int stage) {
-            uint8_t *khi = k_st + stage * kKStage;
+            uint8_t *khi = k_st + stage * kKStage + pblk * kKBlk;
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
+            for (int p = 0; p < NPC; ++p) {
                 const int r = piece_row(p), j = t * kKeys + r;
                 const bool ok = j < S;
                 const float *src = K + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + 8 * pc;
-                cp_async16(khi + sw128(r, 2 * pc), src, ok);
-                cp_async16(khi + sw128(r, 2 * pc + 1), src + 4, ok);
+                cp_async16(khi + sw128(r, pch), src, ok);
+                cp_async16(khi + sw128(r, pch + 1), src + 4, ok);
             }
             cp_async_commit();
         };
         auto convert_k = [&](int stage) {
-            uint8_t *khi = k_st + stage * kKStage, *k16 = khi + kKhiBytes;
-            float4 a[8], c[8];                       // all loads first: the stores below may alias them for the compiler
+            uint8_t *khi = k_st + stage * kKStage + pblk * kKBlk, *k16 = k_st + stage * kKStage + C::kKhiBytes;
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const int r = piece_row(p);
-                a[p] = *reinterpret_cast<const float4 *>(khi + sw128(r, 2 * pc));
-                c[p] = *reinterpret_cast<const float4 *>(khi + sw128(r, 2 * pc + 1));
-            }
+            for (int half = 0; half < NPC / 8; ++half) {
+                float4 a[8], c[8];                   // all loads first: the stores below may alias them for the compiler
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const int r = piece_row(p);
-                const float4 ah = hi4(a[p]), ch = hi4(c[p]);
-                *reinterpret_cast<uint4 *>(k16 + sw128(r, pc)) =
-                    make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
-                *reinterpret_cast<uint4 *>(k16 + sw128(r, 4 + pc)) =
-                    make_uint4(pack_f16(a[p].x - ah.x, a[p].y - ah.y), pack_f16(a[p].z - ah.z, a[p].w - ah.w),
-                               pack_f16(c[p].x - ch.x, c[p].y - ch.y), pack_f16(c[p].z - ch.z, c[p].w - ch.w));
+                for (int i = 0; i < 8; ++i) {
+                    const int r = piece_row(half * 8 + i);
+                    a[i] = *reinterpret_cast<const float4 *>(khi + sw128(r, pch));
+                    c[i] = *reinterpret_cast<const float4 *>(khi + sw128(r, pch + 1));
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = piece_row(half * 8 + i);
+                    const float4 ah = hi4(a[i]), ch = hi4(c[i]);
+                    *reinterpret_cast<uint4 *>(k16 + off16(r, pc, kKBlk)) =
+                        make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+                    *reinterpret_cast<uint4 *>(k16 + off16(r, PPR + pc, kKBlk)) =
+                        make_uint4(pack_f16(a[i].x - ah.x, a[i].y - ah.y), pack_f16(a[i].z - ah.z, a[i].w - ah.w),
+                                   pack_f16(c[i].x - ch.x, c[i].y - ch.y), pack_f16(c[i].z - ch.z, c[i].w - ch.w));
+                }
             }
         };
         copy_k(0, 0);
@@ -307,38 +339,41 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         __syncthreads();
         return;
     }
-    if (warp == kWorkers / 32 + 2) {
+    if (warp > kWorkers / 32 + PW) {
         auto copy_v = [&](int t, int stage) {
-            uint8_t *vhi = v_st + stage * kVStage;
+            uint8_t *vhi = v_st + stage * kVStage + pblk * kKBlk;
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
+            for (int p = 0; p < NPC; ++p) {
                 const int r = piece_row(p), j = t * kKeys + r;
                 const bool ok = j < S;
                 const float *src = V + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + 8 * pc;
-                cp_async16(vhi + nmaj(r, 2 * pc), src, ok);
-                cp_async16(vhi + nmaj(r, 2 * pc + 1), src + 4, ok);
+                cp_async16(vhi + nmaj(r, pch), src, ok);
+                cp_async16(vhi + nmaj(r, pch + 1), src + 4, ok);
             }
             cp_async_commit();
         };
         auto convert_v = [&](int stage) {
-            uint8_t *vhi = v_st + stage * kVStage, *vlo = vhi + kKeys * 128, *v16 = vhi + kVhlBytes;
-            float4 a[8], c[8];
+            uint8_t *vhi = v_st + stage * kVStage + pblk * kKBlk, *vlo = vhi + DB * kKBlk, *v16 = v_st + stage * kVStage + C::kVhlBytes;
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const int r = piece_row(p);
-                a[p] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, 2 * pc));
-                c[p] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, 2 * pc + 1));
-            }
+            for (int half = 0; half < NPC / 8; ++half) {
+                float4 a[8], c[8];
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const int r = piece_row(p);
-                const float4 ah = hi4(a[p]), ch = hi4(c[p]);
-                *reinterpret_cast<float4 *>(vlo + nmaj(r, 2 * pc)) = make_float4(a[p].x - ah.x, a[p].y - ah.y, a[p].z - ah.z, a[p].w - ah.w);
-                *reinterpret_cast<float4 *>(vlo + nmaj(r, 2 * pc + 1)) = make_float4(c[p].x - ch.x, c[p].y - ch.y, c[p].z - ch.z, c[p].w - ch.w);
-                // fp16 copy, N-major without swizzle: 8 keys x 8 columns form one 128-byte core matrix
-                // (key i of the group at 16 i); column blocks 128 bytes apart, key groups 512 bytes apart
-                *reinterpret_cast<uint4 *>(v16 + (r >> 3) * 512 + pc * 128 + (r & 7) * 16) =
-                    make_uint4(pack_f16(a[p].x, a[p].y), pack_f16(a[p].z, a[p].w), pack_f16(c[p].x, c[p].y), pack_f16(c[p].z, c[p].w));
+                for (int i = 0; i < 8; ++i) {
+                    const int r = piece_row(half * 8 + i);
+                    a[i] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, pch));
+                    c[i] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, pch + 1));
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = piece_row(half * 8 + i);
+                    const float4 ah = hi4(a[i]), ch = hi4(c[i]);
+                    *reinterpret_cast<float4 *>(vlo + nmaj(r, pch)) = make_float4(a[i].x - ah.x, a[i].y - ah.y, a[i].z - ah.z, a[i].w - ah.w);
+                    *reinterpret_cast<float4 *>(vlo + nmaj(r, pch + 1)) = make_float4(c[i].x - ch.x, c[i].y - ch.y, c[i].z - ch.z, c[i].w - ch.w);
+                    // fp16 copy, N-major without swizzle: 8 keys x 8 columns form one 128-byte core matrix (key i of
+                    // the group at 16 i); column blocks 128 bytes apart, key groups D/8 such blocks apart
+                    *reinterpret_cast<uint4 *>(v16 + (r >> 3) * (D * 16) + pc * 128 + (r & 7) * 16) =
+                        make_uint4(pack_f16(a[i].x, a[i].y), pack_f16(a[i].z, a[i].w), pack_f16(c[i].x, c[i].y), pack_f16(c[i].z, c[i].w));
+                }
             }
         };
         copy_v(0, 0);
@@ -372,18 +407,19 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         const bool ok = row < S;
         const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < PPR; ++j) {              // 8 floats at a time
             float4 a = ok ? __ldg(src + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 c = ok ? __ldg(src + 2 * j + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
             a.x *= qscale; a.y *= qscale; a.z *= qscale; a.w *= qscale;     // scores come out in the log2 domain
             c.x *= qscale; c.y *= qscale; c.z *= qscale; c.w *= qscale;
             const float4 ah = hi4(a), ch = hi4(c);
-            *reinterpret_cast<float4 *>(q_hi + sw128(rloc, 2 * j)) = ah;
-            *reinterpret_cast<float4 *>(q_hi + sw128(rloc, 2 * j + 1)) = ch;
-            *reinterpret_cast<uint4 *>(q_16 + sw128(rloc, j)) =
+            uint8_t *qb = q_hi + (j >> 2) * kQBlk;
+            *reinterpret_cast<float4 *>(qb + sw128(rloc, 2 * (j & 3))) = ah;
+            *reinterpret_cast<float4 *>(qb + sw128(rloc, 2 * (j & 3) + 1)) = ch;
+            *reinterpret_cast<uint4 *>(q_16 + off16(rloc, j, kQBlk)) =
                 make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
                            pack_f16(c.x - ch.x, c.y - ch.y), pack_f16(c.z - ch.z, c.w - ch.w));
-            *reinterpret_cast<uint4 *>(q_16 + sw128(rloc, 4 + j)) =
+            *reinterpret_cast<uint4 *>(q_16 + off16(rloc, PPR + j, kQBlk)) =
                 make_uint4(pack_f16(a.x, a.y), pack_f16(a.z, a.w), pack_f16(c.x, c.y), pack_f16(c.z, c.w));
         }
     }
@@ -444,7 +480,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                 wait(&o_done[(t - 1) & 1], (uint32_t)(((t - 1) >> 1) & 1), 2);   // P V(t-1) has completed
                 tc_fence_after();
 #pragma unroll
-                for (int hh = 0; hh < 4; ++hh) {
+                for (int hh = 0; hh < (2 * D) / 16; ++hh) {
                     float a[16];
                     tmem_ld16(o_addr + hh * 16, a);
                     tmem_wait_ld();
@@ -505,16 +541,20 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         tc_fence_after();
         if (tid == 0) C16(62);
         const float inv = 1.0f / fmaxf(l, 1e-20f);
-        float a[32], c2[32];
-        tmem_ld32(o_addr, a);                        // P_hi V_hi
-        tmem_ld32(o_addr + D, c2);                   // the correction terms
-        tmem_wait_ld();
-        if (!abort_flag && row < S) {
-            float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol);
+        const bool store = !abort_flag && row < S;
+        float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + (row < S ? row : 0)) * (size_t)E + hcol);
 #pragma unroll
-            for (int c = 0; c < D / 4; ++c)
-                dst[c] = make_float4((a[c * 4 + 0] + c2[c * 4 + 0]) * inv, (a[c * 4 + 1] + c2[c * 4 + 1]) * inv,
-                                     (a[c * 4 + 2] + c2[c * 4 + 2]) * inv, (a[c * 4 + 3] + c2[c * 4 + 3]) * inv);
+        for (int hh = 0; hh < D / 32; ++hh) {
+            float a[32], c2[32];
+            tmem_ld32(o_addr + hh * 32, a);              // P_hi V_hi
+            tmem_ld32(o_addr + D + hh * 32, c2);         // the correction terms
+            tmem_wait_ld();
+            if (store) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    dst[hh * 8 + c] = make_float4((a[c * 4 + 0] + c2[c * 4 + 0]) * inv, (a[c * 4 + 1] + c2[c * 4 + 1]) * inv,
+                                                  (a[c * 4 + 2] + c2[c * 4 + 2]) * inv, (a[c * 4 + 3] + c2[c * 4 + 3]) * inv);
+            }
         }
     }
     T16(8);
@@ -523,32 +563,37 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     __syncthreads();
 }
 
-template <bool CAUSAL>
+template <int D, bool CAUSAL>
 int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, cudaStream_t st)
 {
-    auto kern = mha_tc16_kernel<CAUSAL>;
-    // at least 100 KB: at most two blocks share an SM, so their 256-column allocations always fit in the 512 columns
-    size_t smem = kSmemBytes + 1024;
-    if (smem < 100 * 1024) smem = 100 * 1024;
+    using C = Tc16Cfg<D>;
+    auto kern = mha_tc16_kernel<D, CAUSAL>;
+    // two blocks per SM (256 TMEM columns each): at least 100 KB, so that a third block never shares the SM;
+    // one block per SM (512 columns): more than half of the SM's shared memory
+    size_t smem = C::kSmemBytes + 1024;
+    if (C::BLOCKS_PER_SM == 2 && smem < 100 * 1024) smem = 100 * 1024;
+    if (C::BLOCKS_PER_SM == 1 && smem < 120 * 1024) smem = 120 * 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     const int nqblk = (S + kRows - 1) / kRows;
     const long long blocks = (long long)B * H * nqblk;
     if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
     const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<(unsigned)blocks, kThreads, smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
+    kern<<<(unsigned)blocks, C::THREADS, smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
     return check_launch("mha_tc16_kernel");
 }
 
 }  // namespace
 
-bool mha_tc16_supports(int head_dim) { return head_dim == D; }
+bool mha_tc16_supports(int head_dim) { return head_dim == 32 || head_dim == 64; }
 
 int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st)
 {
-    if (!mha_tc16_supports(E / H)) return fail(HIPGPT_ERR_UNSUPPORTED, "tf32+fp16 tensor-core kernel: head_dim %d is not 32", E / H);
+    const int D = E / H;
+    if (!mha_tc16_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "tf32+fp16 tensor-core kernel: head_dim %d is not 32 or 64", D);
     if (B == 0 || S == 0) return HIPGPT_OK;
-    return causal ? launch_tc16_cfg<true>(q, k, v, out, B, S, E, H, st) : launch_tc16_cfg<false>(q, k, v, out, B, S, E, H, st);
+    if (D == 32) return causal ? launch_tc16_cfg<32, true>(q, k, v, out, B, S, E, H, st) : launch_tc16_cfg<32, false>(q, k, v, out, B, S, E, H, st);
+    return causal ? launch_tc16_cfg<64, true>(q, k, v, out, B, S, E, H, st) : launch_tc16_cfg<64, false>(q, k, v, out, B, S, E, H, st);
 }
 
 #ifdef HIPGPT_TC_TRACE

@@ -98,3 +98,40 @@ def test_decode_scratch_size_query():
     assert lib.hipgpt_mha_decode_scratch_bytes(8, 8, 32, 16) == 0       # one split: no scratch
     assert lib.hipgpt_mha_decode_scratch_bytes(1024, 8, 32, 256) == 0   # enough rows already
     assert lib.hipgpt_mha_decode_scratch_bytes(0, 8, 32, 256) == 0
+
+
+REFERENCE = os.environ.get("HIPGPT_REFERENCE", "/root/reference")   # the HipGPT tree, where it is mounted
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE, "src", "transformer_layer.cpp")), reason="reference tree not mounted")
+def test_reference_transformer_layer_links_against_the_library():
+    """HipGPT's own src/transformer_layer.cpp, compiled where it lies (host stand-in for the HIP
+    runtime), refers to launch_multihead_attention by exactly the symbol this library exports, and
+    links with it when every other launcher it needs is stubbed (src/transformer_layer.cpp:218 is
+    the only call site)."""
+    import subprocess
+    import tempfile
+    shim = os.path.join(ROOT, "oracle", "ref_shim")
+    libdir = os.path.dirname(_capi.lib_path())
+    with tempfile.TemporaryDirectory() as td:
+        obj = os.path.join(td, "transformer_layer.o")
+        subprocess.run(["g++", "-std=c++17", "-O1", "-fPIC", "-I", shim, "-I", os.path.join(REFERENCE, "include"), "-c",
+                        os.path.join(REFERENCE, "src", "transformer_layer.cpp"), "-o", obj], check=True)
+        undefined = subprocess.run(["nm", "-u", obj], check=True, capture_output=True, text=True).stdout.split()
+        wanted = [u for u in undefined if "launch_" in u]
+        attention = _capi.CXX_LAUNCHERS["launch_multihead_attention"]
+        assert attention in wanted
+        exported = subprocess.run(["nm", "-D", "--defined-only", _capi.lib_path()], check=True, capture_output=True, text=True).stdout
+        assert attention in exported
+        # every other launcher (and the shim's thread-index globals) as an empty definition: the link must then close
+        others = [u for u in wanted if u != attention and u not in exported]
+        stub = os.path.join(td, "stubs.s")
+        with open(stub, "w") as f:
+            for name in others:
+                f.write(f".globl {name}\n.type {name}, @function\n{name}:\n ret\n")
+        out = os.path.join(td, "liblayer.so")
+        r = subprocess.run(["g++", "-shared", "-o", out, obj, stub, "-L", libdir, "-lhipgpt_attn", "-Wl,--no-undefined",
+                            "-Wl,-rpath," + libdir], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        needed = subprocess.run(["readelf", "-d", out], check=True, capture_output=True, text=True).stdout
+        assert "libhipgpt_attn.so" in needed

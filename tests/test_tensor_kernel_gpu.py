@@ -63,7 +63,9 @@ def test_tensor_kernel_benchmark_shapes(cfg, causal):
                                            (4, (1, 1, 7, 32)), (4, (2, 3, 200, 32)), (4, (1, 1, 513, 32)), (4, (32, 8, 256, 32)),
                                            (4, (2, 2, 2048, 32)),
                                            (5, (1, 1, 1, 32)), (5, (1, 1, 7, 32)), (5, (1, 2, 65, 32)), (5, (2, 3, 200, 32)),
-                                           (5, (1, 1, 513, 32)), (5, (32, 8, 256, 32)), (5, (3, 5, 640, 32)), (5, (2, 2, 2048, 32))])
+                                           (5, (1, 1, 513, 32)), (5, (32, 8, 256, 32)), (5, (3, 5, 640, 32)), (5, (2, 2, 2048, 32)),
+                                           (5, (1, 2, 64, 64)), (5, (2, 2, 130, 64)), (5, (1, 2, 300, 64)), (5, (2, 4, 1024, 64)),
+                                           (5, (1, 1, 7, 64))])
 @pytest.mark.parametrize("causal", [False, True])
 def test_tensor_kernel_variants_match_oracle(variant, shape, causal):
     B, H, S, D = shape
@@ -109,7 +111,7 @@ def test_accumulating_variants_rescale_when_row_maxima_grow(variant):
         assert float(np.abs(out - ref_out).max()) <= 1e-4     # scores reach ~100: the fp32 arithmetic itself is good to ~1e-5 here
 
 
-@pytest.mark.parametrize("variant", [4, 5])
+@pytest.mark.parametrize("variant", [4])
 def test_head_dim_32_variants_refuse_other_head_dims(variant):
     lib = _capi.lib()
     t = torch.zeros((64, 64), device="cuda")
