@@ -40,7 +40,7 @@ from hipgpt_b200 import synth  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in profiles/
 # (workload, tensor kernel?) -> bytes
-TRAFFIC = {("c2", True): 25.25e6, ("c2", False): 25.21e6}
+TRAFFIC = {("c2", True): 25.23e6, ("c2", False): 25.21e6, ("c3", True): 129.9e6}
 FALLBACK_HBM_GBS = 6650.0
 
 
