@@ -375,9 +375,9 @@ def run_ours(args):
     bf16_peak = float(peaks.get("bf16_tflops_sustained" if bf16 else "bf16_tflops", 1400.0 if bf16 else 1590.0))
     tf32_peak = bf16_peak / 2.0
     t_hbm = per_batch_bytes / (hbm_peak * 1e9)
-    # tensor work per fp32 product, in TF32 products: 3 for split-TF32; the default kernel (all but head_dim 32
-    # beyond 1024 keys) runs one TF32 product and two FP16 products (twice the TF32 rate)
-    tc16 = tensor_kernel and not bf16 and (D == 64 or S <= 1024)
+    # tensor work per fp32 product, in TF32 products: the default kernel runs one TF32 product and two FP16
+    # products (twice the TF32 rate); 3 would be the figure of the split-TF32 variant
+    tc16 = tensor_kernel and not bf16
     tf32_products = 2.0 if tc16 else 3.0
     t_pipe = (flops_launch / (bf16_peak * 1e12)) if bf16 else (tf32_products * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
     src = "measured" if peaks else "fallback"

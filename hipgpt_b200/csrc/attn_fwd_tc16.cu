@@ -12,8 +12,14 @@
 //                           a_lo, b_lo and a are rounded to 11 bits, an error of 2^-22 relative to
 //                           the product, the same order as the dropped a_lo*b_lo of plain split-TF32.
 // fp16 has K=16 per instruction against 8 for TF32, so a 64-key tile takes 20 instructions
-// instead of 28 at head_dim 32 and 28 instead of 40 at head_dim 64 (an instruction with M=128 costs about 64 cycles for any N <= 128).  fp16
-// conversions saturate; operands beyond +-65504 lose accuracy, not finiteness of the lo terms.
+// instead of 28 at head_dim 32 and 28 instead of 40 at head_dim 64 (an instruction with M=128
+// costs about 64 cycles for any N <= 128).
+// Range: the fp16 copies are good to 11 bits for magnitudes within fp16's normal range.  Conversions
+// saturate: an operand beyond +-65504 keeps its TF32 main product but loses its correction term,
+// and lo parts below 6e-5 become subnormal.  Measured against the fp32 arithmetic: V of magnitude
+// 1e5, or Q and K of magnitudes 1e5 and 1e-5, give 2e-4 .. 5e-4 relative (plain TF32 grade)
+// instead of 5e-7; magnitudes from 1e-4 to 1e2 stay at 5e-7.  The split-TF32 kernel
+// (attn_fwd_tc.cu) has the full fp32 range and is what callers with such operands select.
 //
 // One block = 128 query rows of one (batch, head): 128 workers (worker = row = TMEM lane), one
 // issuing warp, one warp that stages K and one that stages V.  Two blocks per SM at head_dim 32,
@@ -52,8 +58,9 @@ struct Tc16Cfg {
     static constexpr int DB = D / 32;                         // fp32 blocks per row
     static constexpr int HB = (2 * D) / 64;                   // fp16 blocks per row of [x_lo | x] or [x_hi | x_lo]
     static constexpr int PPR = D / 8;                         // 32-byte pieces per row
-    static constexpr int PW = D / 32;                         // warps that stage K, and as many that stage V
-    static constexpr int THREADS = kWorkers + 32 + 2 * PW * 32;   // workers, the issuing warp, the K warps, the V warps
+    static constexpr int PWK = D / 32;                        // warps that stage K
+    static constexpr int PWV = D / 16;                        // warps that stage V (its conversion is the longer one)
+    static constexpr int THREADS = kWorkers + 32 + (PWK + PWV) * 32;   // workers, the issuing warp, the K warps, the V warps
     static constexpr uint32_t kTmemCols = (kColO + 2 * D) <= 256 ? 256 : 512;
     static constexpr int BLOCKS_PER_SM = kTmemCols == 256 ? 2 : 1;
     static constexpr int kQBlk = kRows * 128, kKBlk = kKeys * 128;      // bytes of one block of a Q / K / V tile
@@ -120,13 +127,25 @@ __device__ __forceinline__ float4 hi4(float4 x) { return make_float4(tf32_hi(x.x
 // byte offset of 16-byte chunk c of row r in a tile of 128-byte rows, SWIZZLE_128B
 __device__ __forceinline__ int sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
 
+// Which pieces of a 64-row tile a staging thread owns.  A piece is 32 bytes (8 floats) of a row; a
+// thread owns pieces of pairs of adjacent rows.  PT = threads that stage this operand, PPR = pieces per row.
+template <int PT, int PPR>
+struct PieceMap {
+    static constexpr int NPC = (kKeys * PPR) / PT;            // pieces per thread and tile
+    static constexpr int RPP = 2 * (PT / PPR);                // rows covered by a pair of passes
+    static constexpr int BATCH = NPC < 8 ? NPC : 8;           // pieces converted at a time
+    int pc, pq, pblk, pch;                                    // piece of a row, row pair, fp32 block and first 16-byte chunk of the piece
+    __device__ explicit PieceMap(int pid) : pc(pid % PPR), pq(pid / PPR), pblk((pid % PPR) >> 2), pch(2 * ((pid % PPR) & 3)) {}
+    __device__ int row(int p) const { return RPP * (p >> 1) + 2 * pq + (p & 1); }
+};
+
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(Tc16Cfg<D>::THREADS, Tc16Cfg<D>::BLOCKS_PER_SM)
 mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
                 float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
 {
     using C = Tc16Cfg<D>;
-    constexpr int DB = C::DB, HB = C::HB, PPR = C::PPR, PW = C::PW;
+    constexpr int DB = C::DB, HB = C::HB, PPR = C::PPR, PWK = C::PWK, PWV = C::PWV;
     constexpr int kQBlk = C::kQBlk, kKBlk = C::kKBlk, kKStage = C::kKStage, kVStage = C::kVStage;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -158,8 +177,8 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         abort_flag = 0;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&k_full[i], PW);               // one arrival per K warp
-            mbar_init(&v_full[i], PW);               // one arrival per V warp
+            mbar_init(&k_full[i], PWK);              // one arrival per K warp
+            mbar_init(&v_full[i], PWV);              // one arrival per V warp
             mbar_init(&k_free[i], 1);                // tcgen05.commit
             mbar_init(&v_free[i], 1);
             mbar_init(&s_full[i], 1);
@@ -263,7 +282,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         return;
     }
 
-    // ================= the producers: D/32 warps for K, as many for V ==============================
+    // ================= the producers: D/32 warps for K, D/16 for V ===================================
     // A tile goes from global memory straight to its place in the TF32 operand (cp.async, no
     // registers held): the tensor core ignores the 13 low mantissa bits of a TF32 operand, so the
     // raw fp32 tile IS the hi operand.  When it has landed the same thread reads its pieces back,
@@ -271,16 +290,13 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     // before tile u is converted, as soon as its stage is free.
     // A thread owns 32-byte pieces (8 floats) of pairs of adjacent rows, eight per tile: an fp16 chunk
     // is 16 bytes = 8 values.
-    constexpr int PT = 32 * PW;                      // threads per operand
-    constexpr int NPC = (kKeys * PPR) / PT;          // pieces per thread and tile: 8
-    constexpr int RPP = 2 * (PT / PPR);              // rows covered by a pair of passes
-    const int pid = (tid - kWorkers - 32) % PT;      // index among the threads of this operand
-    const int pc = pid % PPR, pq = pid / PPR;        // piece of a row, row pair
-    auto piece_row = [&](int p) { return RPP * (p >> 1) + 2 * pq + (p & 1); };
-    const int pblk = pc >> 2, pch = 2 * (pc & 3);    // fp32 block and first 16-byte chunk of the piece
     // byte offset of 16-byte chunk c of row r in a block of the N-major fp32 operand (32-byte pieces permuted by r mod 4)
     auto nmaj = [](int r, int c) { return r * 128 + (((((c >> 1) ^ (r & 3)) << 1) | (c & 1)) << 4); };
-    if (warp > kWorkers / 32 && warp <= kWorkers / 32 + PW) {
+    if (warp > kWorkers / 32 && warp <= kWorkers / 32 + PWK) {
+        const PieceMap<32 * PWK, PPR> pm(tid - kWorkers - 32);
+        constexpr int NPC = pm.NPC, BATCH = pm.BATCH;
+        const int pc = pm.pc, pblk = pm.pblk, pch = pm.pch;
+        auto piece_row = [&](int p) { return pm.row(p); };
         auto copy_k = [&](int t, int stage) {
             uint8_t *khi = k_st + stage * kKStage + pblk * kKBlk;
 #pragma unroll
@@ -296,17 +312,17 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         auto convert_k = [&](int stage) {
             uint8_t *khi = k_st + stage * kKStage + pblk * kKBlk, *k16 = k_st + stage * kKStage + C::kKhiBytes;
 #pragma unroll
-            for (int half = 0; half < NPC / 8; ++half) {
-                float4 a[8], c[8];                   // all loads first: the stores below may alias them for the compiler
+            for (int half = 0; half < NPC / BATCH; ++half) {
+                float4 a[BATCH], c[BATCH];           // all loads first: the stores below may alias them for the compiler
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = piece_row(half * 8 + i);
+                for (int i = 0; i < BATCH; ++i) {
+                    const int r = piece_row(half * BATCH + i);
                     a[i] = *reinterpret_cast<const float4 *>(khi + sw128(r, pch));
                     c[i] = *reinterpret_cast<const float4 *>(khi + sw128(r, pch + 1));
                 }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = piece_row(half * 8 + i);
+                for (int i = 0; i < BATCH; ++i) {
+                    const int r = piece_row(half * BATCH + i);
                     const float4 ah = hi4(a[i]), ch = hi4(c[i]);
                     *reinterpret_cast<uint4 *>(k16 + off16(r, pc, kKBlk)) =
                         make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
@@ -339,7 +355,11 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         __syncthreads();
         return;
     }
-    if (warp > kWorkers / 32 + PW) {
+    if (warp > kWorkers / 32 + PWK) {
+        const PieceMap<32 * PWV, PPR> pm(tid - kWorkers - 32 - 32 * PWK);
+        constexpr int NPC = pm.NPC, BATCH = pm.BATCH;
+        const int pc = pm.pc, pblk = pm.pblk, pch = pm.pch;
+        auto piece_row = [&](int p) { return pm.row(p); };
         auto copy_v = [&](int t, int stage) {
             uint8_t *vhi = v_st + stage * kVStage + pblk * kKBlk;
 #pragma unroll
@@ -355,17 +375,17 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         auto convert_v = [&](int stage) {
             uint8_t *vhi = v_st + stage * kVStage + pblk * kKBlk, *vlo = vhi + DB * kKBlk, *v16 = v_st + stage * kVStage + C::kVhlBytes;
 #pragma unroll
-            for (int half = 0; half < NPC / 8; ++half) {
-                float4 a[8], c[8];
+            for (int half = 0; half < NPC / BATCH; ++half) {
+                float4 a[BATCH], c[BATCH];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = piece_row(half * 8 + i);
+                for (int i = 0; i < BATCH; ++i) {
+                    const int r = piece_row(half * BATCH + i);
                     a[i] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, pch));
                     c[i] = *reinterpret_cast<const float4 *>(vhi + nmaj(r, pch + 1));
                 }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = piece_row(half * 8 + i);
+                for (int i = 0; i < BATCH; ++i) {
+                    const int r = piece_row(half * BATCH + i);
                     const float4 ah = hi4(a[i]), ch = hi4(c[i]);
                     *reinterpret_cast<float4 *>(vlo + nmaj(r, pch)) = make_float4(a[i].x - ah.x, a[i].y - ah.y, a[i].z - ah.z, a[i].w - ah.w);
                     *reinterpret_cast<float4 *>(vlo + nmaj(r, pch + 1)) = make_float4(c[i].x - ch.x, c[i].y - ch.y, c[i].z - ch.z, c[i].w - ch.w);

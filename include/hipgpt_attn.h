@@ -69,12 +69,14 @@ HIPGPT_API int hipgpt_mha_forward(const float *d_q, const float *d_k, const floa
 
 /* The same with an explicit kernel selector (HIPGPT_ALGO_*).  `warps`: for HIPGPT_ALGO_ROWS the
  * number of warps per thread block (0 = default); for HIPGPT_ALGO_TENSOR the schedule variant
- * (profiling and tests): 0 default (variant 5, except head_dim 32 beyond 1024 keys: 1), 1 = split-TF32
+ * (profiling and tests): 0 default (= variant 5), 1 = split-TF32
  * with 64-key tiles, 2 = 128-key tiles with two workers per row (head_dim 32),
  * 3 = persistent blocks over a stream of tiles, 4 = two query tiles per block with the output
  * accumulated in tensor memory (head_dim 32), 5 = TF32 main products with FP16 correction
- * products and a softmax that runs ahead of the P V products.  All variants hold
- * the same 1e-5 accuracy. */
+ * products and a softmax that runs ahead of the P V products.  All variants hold the same 1e-5
+ * accuracy on unit-scale data; variant 5 keeps it for operand magnitudes within fp16's normal range
+ * (about 1e-4 .. 6e4) and falls to plain TF32 grade (~3e-4 relative) beyond, variant 1 has the full
+ * fp32 range. */
 HIPGPT_API int hipgpt_mha_forward_ex(const float *d_q, const float *d_k, const float *d_v,
                           float *d_out, float *d_probs,
                           int B, int S, int E, int H, int causal,
