@@ -3,21 +3,21 @@
 // (src/hip_kernels.cpp:404-451: three [B*S][E] planes in, one out, head h of token t at
 // t*E + h*D), with 16-bit storage; head_dim 64.
 //
-// One thread block works on 256 query rows of one (batch, head) as two tiles of 128 rows, A and
-// B, each owned by one group of 128 worker threads (worker = query row = TMEM lane).  The two
-// tiles share every K/V tile and take turns on the tensor core, so one tile's softmax runs
-// while the other's products are computed:
-//   producers (128 threads)   cp.async K(t), V(t) straight into the 128-byte-swizzled operand
-//                             layout (no conversion), two stages each, ring of full/free mbarriers;
-//   issuing warp (one lane)   S_x(t) = Q_x K(t)^T (M=128, N=128, 4 x K=16) into TMEM, then, once
-//                             the workers have written P_x(t), O_x += P_x(t) V(t) (A operand from
-//                             TMEM, 8 x K=16, N=64) directly followed by S_x(t+1);
-//   workers                   row maximum and exponentials straight from TMEM (two sweeps, 32
-//                             scores in registers at a time), P rounded to bf16 and written over
-//                             S in place; the output accumulates in TMEM across all tiles and is
-//                             only rescaled when a row's maximum grew by more than 2^8 since the
-//                             last rescale (then the whole warp rescales; until then exponentials
-//                             may reach 2^8, harmless in bf16 / fp32).
+// One thread block = 128 query rows of one (batch, head): 128 worker threads (worker = query row
+// = TMEM lane), one warp whose elected lane issues the tensor-core instructions, one warp that
+// copies K tiles and one that copies V tiles.  Two blocks per SM.  Per tile of 64 keys:
+//   copy     cp.async brings the bf16 K / V tile straight into its 128-byte-swizzled operand
+//            layout (no conversion), four stages each, rings of full / free mbarriers;
+//   S        = Q K^T (M=128, N=64, 4 instructions of K=16) into one of two TMEM buffers, issued one
+//            tile ahead of the softmax;
+//   softmax  the worker reads its 64 scores from TMEM once; maximum, exponentials (scale folded into
+//            the exponent, so Q is not rescaled in bf16) and the row sum work on those registers; P is
+//            rounded to bf16 and written over S in place (32 columns of packed pairs);
+//   O        += P V (A operand from TMEM, 4 instructions of K=16, N=64), accumulated in TMEM over ALL
+//            tiles.  The reference maximum is only moved (and O rescaled, by the whole warp) when a
+//            row's maximum grew by more than 2^8 since the last rescale; until then exponentials may
+//            reach 2^8, harmless in bf16 / fp32.  The worker therefore goes from tile t straight to
+//            tile t+1 while P V(t) runs.
 // Every wait is bounded: on expiry the block raises a flag that cuts all later waits short,
 // records a status code, skips its stores, frees its TMEM and returns.
 #include "tc_primitives.cuh"
@@ -28,12 +28,13 @@
 namespace hipgpt {
 namespace {
 
-constexpr int kRows = 128;        // query rows per tile (two tiles per block)
-constexpr int kKeys = 128;        // keys per K/V tile
-constexpr int kWorkers = 2 * kRows;
-constexpr int kProducers = 128;
-constexpr int kThreads = kWorkers + 32 + kProducers;
+constexpr int kRows = 128;        // query rows per block
+constexpr int kKeys = 64;         // keys per tile
+constexpr int kWorkers = kRows;
+constexpr int kThreads = kWorkers + 32 + 64;     // workers, the issuing warp, the K warp, the V warp
+constexpr int kStages = 4;        // K and V tiles in flight
 constexpr float kRescaleStep = 8.0f;     // log2 of the growth of a row maximum that forces a rescale
+constexpr uint32_t kColX = 0, kColO = 128, kTmemCols = 256;
 
 __device__ int g_bf16_status = 0;
 
@@ -71,17 +72,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// TMEM columns: S_A | S_B (128 each, P over the first 64 in place) | O_A | O_B (D each)
 template <int D>
 struct Bf16Cfg {
-    static constexpr uint32_t kColS = 0, kColO = 2 * kKeys;
-    static constexpr uint32_t kTmemCols = 512;
-    static constexpr int kTileBytes = kKeys * D * 2;            // one Q, K or V tile
-    static constexpr size_t kSmemBytes = (size_t)6 * kTileBytes;   // Q_A, Q_B, 2 x K, 2 x V
+    static constexpr int kQBytes = kRows * D * 2;               // the Q tile
+    static constexpr int kTileBytes = kKeys * D * 2;            // one K or V tile
+    static constexpr size_t kSmemBytes = (size_t)kQBytes + 2 * kStages * kTileBytes;
 };
 
 template <int D, bool CAUSAL>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__restrict__ K, const __nv_bfloat16 *__restrict__ V,
                 __nv_bfloat16 *__restrict__ O, int S, int E, int H, int BH, int nqblk, float cscale)
 {
@@ -91,10 +90,10 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     constexpr int TILE = C::kTileBytes;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *q_s = base;                             // [2 tiles][128][D] bf16, row r chunk c at r*128 + ((c ^ (r & 7)) * 16)
-    uint8_t *k_s = q_s + 2 * TILE;                   // [2 stages][128 keys][D], the same layout (K-major operand)
-    uint8_t *v_s = k_s + 2 * TILE;                   // [2 stages][128 keys][D], the same bytes read as an N-major operand
-    __shared__ uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], o_done[2];
+    uint8_t *q_s = base;                             // [128][D] bf16, row r chunk c at r*128 + ((c ^ (r & 7)) * 16)
+    uint8_t *k_s = q_s + C::kQBytes;                 // [stage][64 keys][D], the same layout (K-major operand)
+    uint8_t *v_s = k_s + kStages * TILE;             // [stage][64 keys][D], the same bytes read as an N-major operand
+    __shared__ uint64_t k_full[kStages], k_free[kStages], v_full[kStages], v_free[kStages], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
@@ -104,29 +103,24 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     const int b = bh / H, h = bh % H;
     const size_t tok0 = (size_t)b * S;
     const size_t hcol = (size_t)h * D;
-    const int q0 = qblk * 2 * kRows;
-
-    // key tiles each query tile needs (0 when the tile lies past the end of the sequence)
-    int nt[2];
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-        const int first = q0 + g * kRows;
-        const int kend = CAUSAL ? min(S, first + kRows) : S;
-        nt[g] = first < S ? (kend + kKeys - 1) / kKeys : 0;
-    }
-    const int NT = max(nt[0], nt[1]);
+    const int q0 = qblk * kRows;
+    const int kend = CAUSAL ? min(S, q0 + kRows) : S;
+    const int nt = (kend + kKeys - 1) / kKeys;       // >= 1: q0 < S
 
     if (tid == 0) {
         abort_flag = 0;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&k_full[i], kProducers);
-            mbar_init(&v_full[i], kProducers);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&k_full[i], 1);                // the K warp
+            mbar_init(&v_full[i], 1);                // the V warp
             mbar_init(&k_free[i], 1);                // tcgen05.commit
             mbar_init(&v_free[i], 1);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&o_done[i], 1);
-            mbar_init(&p_full[i], kRows);            // the workers of one tile
+            mbar_init(&p_full[i], kWorkers / 32);    // one arrival per worker warp
+            mbar_init(&o_done[i], 1);                // by tile parity: a worker may be two tiles ahead of the P V products
         }
     }
     __syncthreads();
@@ -137,13 +131,15 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         if (abort_flag) return;
         if (!mbar_wait(bar, parity)) { abort_flag = 1; atomicCAS(&g_bf16_status, 0, site); }
     };
+    // one arrival for the whole warp: every lane's writes are ordered before it by the warp barrier
     auto arrive = [&](uint64_t *bar) {
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
     };
 
     if (warp == kWorkers / 32) {
         // ================= the issuing warp =====================================================
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncthreads();                             // Q staged; TMEM allocated
@@ -152,96 +148,81 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_bf16(kRows, kKeys, 0);
             constexpr uint32_t idesc_pv = idesc_bf16(kRows, D, 1);
-            auto issue_qk = [&](int g, int stage) {
-                const uint64_t dq = make_desc(smem_u32(q_s + g * TILE), 16, 1024, 2);
+            const uint64_t dq = make_desc(smem_u32(q_s), 16, 1024, 2);
+            auto issue_qk = [&](int buf, int stage) {
                 const uint64_t dk = make_desc(smem_u32(k_s + stage * TILE), 16, 1024, 2);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k)         // 16 bf16 = 32 bytes per instruction
-                    mma_f16_ss(tmem + C::kColS + g * kKeys, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
-                tc_commit(&s_full[g]);
+                    mma_f16_ss(tmem + kColX + buf * kKeys, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
+                tc_commit(&s_full[buf]);
+                tc_commit(&k_free[stage]);
             };
-            auto issue_pv = [&](int g, int stage, bool first) {
+            auto issue_pv = [&](int buf, int stage, bool first) {
                 // N-major B: 16 keys (two groups of 8 rows of 128 bytes) per instruction = 2048 bytes
                 const uint64_t dv = make_desc(smem_u32(v_s + stage * TILE), 1024, 1024, 2);
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)
-                    mma_f16_ts(tmem + C::kColO + g * D, tmem + C::kColS + g * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 128), idesc_pv,
+                    mma_f16_ts(tmem + kColO, tmem + kColX + buf * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 128), idesc_pv,
                                (first && k == 0) ? 0u : 1u);
-                tc_commit(&o_done[g]);
+                tc_commit(&o_done[buf]);
+                tc_commit(&v_free[stage]);
             };
-            if (NT > 0) {
-                wait(&k_full[0], 0, 4);
-                tc_fence_after();
-#pragma unroll
-                for (int g = 0; g < 2; ++g)
-                    if (nt[g] > 0) issue_qk(g, 0);
-                tc_commit(&k_free[0]);
-            }
-            for (int t = 0; t < NT; ++t) {
-                const int st = t & 1;
-#pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    if (t < nt[g]) {
-                        wait(&p_full[g], (uint32_t)(t & 1), 5);                  // P_g(t) is in TMEM
-                        wait(&v_full[st], (uint32_t)((t >> 1) & 1), 6);          // V(t) is in shared memory
-                        tc_fence_after();
-                        issue_pv(g, st, t == 0);
-                    }
-                    if (g == 1) tc_commit(&v_free[st]);                          // both tiles' P V(t) issued
-                    if (t + 1 < nt[g]) {
-                        wait(&k_full[st ^ 1], (uint32_t)(((t + 1) >> 1) & 1), 4);   // K(t+1) is in shared memory
-                        tc_fence_after();
-                        issue_qk(g, st ^ 1);                                     // executes after P V_g(t): S_g is free then
-                    }
-                    if (g == 1 && t + 1 < NT) tc_commit(&k_free[st ^ 1]);
+            wait(&k_full[0], 0, 4);
+            tc_fence_after();
+            issue_qk(0, 0);
+            for (int t = 0; t < nt; ++t) {
+                const int buf = t & 1;
+                if (t + 1 < nt) {
+                    wait(&k_full[(t + 1) % kStages], (uint32_t)(((t + 1) / kStages) & 1), 4);    // K(t+1) is in shared memory
+                    tc_fence_after();
+                    issue_qk(buf ^ 1, (t + 1) % kStages);    // its buffer held P(t-1): P V(t-1) was issued before, instructions run in order
                 }
+                wait(&p_full[buf], (uint32_t)((t >> 1) & 1), 5);                         // P(t) is in TMEM
+                wait(&v_full[t % kStages], (uint32_t)((t / kStages) & 1), 6);            // V(t) is in shared memory
+                tc_fence_after();
+                issue_pv(buf, t % kStages, t == 0);
             }
         }
         __syncwarp();
         tc_fence_before();
-        __syncthreads();                             // the workers have read the outputs
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
+        __syncthreads();                             // the workers have read the output
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
         return;
     }
 
     if (warp > kWorkers / 32) {
-        // ================= the producers ========================================================
-        const int ptid = tid - kWorkers - 32;
-        const int sc = ptid % CPR, sr0 = ptid / CPR;     // chunk of a row, first row
-        constexpr int RPP = kProducers / CPR;            // rows per pass
-        auto fetch = [&](const __nv_bfloat16 *__restrict__ plane, uint8_t *stage, int t) {
+        // ================= the K warp and the V warp ==============================================
+        // Tile u goes to stage u mod 4; its copy is issued three tiles ahead, as soon as the product
+        // that read the stage's previous tile has completed.
+        const bool is_v = warp == kWorkers / 32 + 2;
+        const __nv_bfloat16 *__restrict__ plane = is_v ? V : K;
+        uint8_t *ring = is_v ? v_s : k_s;
+        uint64_t *full = is_v ? v_full : k_full, *freeb = is_v ? v_free : k_free;
+        const int sc = lane % CPR, sr0 = lane / CPR;     // chunk of a row, first row
+        constexpr int RPP = 32 / CPR;                    // rows per pass
+        auto copy = [&](int u) {
+            if (u < nt) {
+                uint8_t *stage = ring + (u % kStages) * TILE;
 #pragma unroll
-            for (int p = 0; p < kKeys / RPP; ++p) {
-                const int r = sr0 + p * RPP;
-                const int j = t * kKeys + r;
-                const bool ok = j < S;
-                cp_async16(stage + r * 128 + ((sc ^ (r & 7)) << 4), plane + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + sc * 8, ok);
+                for (int p = 0; p < kKeys / RPP; ++p) {
+                    const int r = sr0 + p * RPP;
+                    const int j = u * kKeys + r;
+                    const bool ok = j < S;
+                    cp_async16(stage + r * 128 + ((sc ^ (r & 7)) << 4), plane + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + sc * 8, ok);
+                }
             }
-            cp_async_commit();
+            cp_async_commit();                       // an empty group keeps the count of the waits
         };
-        fetch(K, k_s, 0);
-        fetch(V, v_s, 0);
+#pragma unroll
+        for (int u = 0; u < kStages - 1; ++u) copy(u);
         __syncthreads();                             // matches the block-wide barrier after Q staging
-        for (int t = 0; t < NT; ++t) {
-            const int st = t & 1;
-            cp_async_wait<1>();                      // K(t) has landed (V(t) may still be in flight)
+        for (int u = 0; u < nt; ++u) {
+            const int w = u + kStages - 1;           // the tile whose copy is issued now
+            if (w < nt && w >= kStages) wait(&freeb[w % kStages], (uint32_t)(((w / kStages) - 1) & 1), is_v ? 8 : 7);
+            copy(w);
+            cp_async_wait<kStages - 1>();            // tile u has landed
             proxy_fence();                           // generic-proxy writes -> visible to the tensor core
-            arrive(&k_full[st]);
-            if (t + 1 < NT) {
-                if (t >= 1) wait(&k_free[st ^ 1], (uint32_t)(((t - 1) >> 1) & 1), 7);   // Q K(t-1)^T has completed
-                fetch(K, k_s + (st ^ 1) * TILE, t + 1);
-            } else {
-                cp_async_commit();                   // keeps the group count of the waits below
-            }
-            cp_async_wait<1>();                      // V(t) has landed
-            proxy_fence();
-            arrive(&v_full[st]);
-            if (t + 1 < NT) {
-                if (t >= 1) wait(&v_free[st ^ 1], (uint32_t)(((t - 1) >> 1) & 1), 8);   // P V(t-1) has completed
-                fetch(V, v_s + (st ^ 1) * TILE, t + 1);
-            } else {
-                cp_async_commit();
-            }
+            arrive(&full[u % kStages]);
         }
         cp_async_wait<0>();
         __syncthreads();
@@ -249,15 +230,13 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     }
 
     // ===================== the workers ===========================================================
-    const int g = warp >> 2;                         // query tile A / B
-    const int wq = warp & 3;                         // TMEM lane quadrant of this warp
-    const int rloc = wq * 32 + lane;                 // row inside the tile = TMEM lane
-    const int row = q0 + g * kRows + rloc;
-    const int ntg = nt[g];
+    const int wq = warp;                             // TMEM lane quadrant of this warp
+    const int rloc = wq * 32 + lane;                 // row inside the block = TMEM lane
+    const int row = q0 + rloc;
     {
         const bool ok = row < S;
         const __nv_bfloat16 *src = Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol;
-        uint8_t *dst = q_s + g * TILE + rloc * 128;
+        uint8_t *dst = q_s + rloc * 128;
 #pragma unroll
         for (int c = 0; c < CPR; ++c) cp_async16(dst + ((c ^ (rloc & 7)) << 4), src + c * 8, ok);
         cp_async_commit();
@@ -268,30 +247,33 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     __syncthreads();
     tc_fence_after();
     const uint32_t lane_base = tmem_base_slot + ((uint32_t)(wq * 32) << 16);
-    const uint32_t s_addr = lane_base + C::kColS + g * kKeys;
-    const uint32_t o_addr = lane_base + C::kColO + g * D;
+    const uint32_t o_addr = lane_base + kColO;
 
     float m_ref = 0.0f, l = 0.0f;                    // reference maximum (scaled, log2 domain) and row sum
-    for (int t = 0; t < ntg; ++t) {
+    for (int t = 0; t < nt; ++t) {
+        const int buf = t & 1;
         const int j0 = t * kKeys;
-        wait(&s_full[g], (uint32_t)(t & 1), 1);      // S_g(t) is in TMEM
+        const uint32_t s_addr = lane_base + kColX + buf * kKeys;
+        wait(&s_full[buf], (uint32_t)((t >> 1) & 1), 1);   // S(t) is in TMEM
         tc_fence_after();
-        const bool need_mask = (CAUSAL && j0 + kKeys - 1 > q0 + g * kRows + wq * 32) || j0 + kKeys > S;
+        const int wrow0 = q0 + wq * 32;              // first row of this warp
+        const bool warp_dead = CAUSAL && j0 > wrow0 + 31;          // these columns are above the diagonal for the whole warp
+        const bool need_mask = (CAUSAL && j0 + kKeys - 1 > wrow0) || j0 + kKeys > S;
         const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : kKeys);     // visible columns of this row
 
-        // ---- first sweep: the row maximum ----------------------------------------------------
+        // ---- the row's 64 scores are read from TMEM once and stay in registers --------------------
+        float v0[32], v1[32];
         float mx = -INFINITY;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            float v0[32], v1[32];
-            tmem_ld32(s_addr + hh * 64, v0);
-            tmem_ld32(s_addr + hh * 64 + 32, v1);
+        if (!warp_dead) {
+            tmem_ld32(s_addr, v0);
+            tmem_ld32(s_addr + 32, v1);
             tmem_wait_ld();
             if (need_mask) {
+                // a masked score becomes -inf: its exponential below is exactly 0
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    v0[c] = (hh * 64 + c < nvalid) ? v0[c] : -INFINITY;
-                    v1[c] = (hh * 64 + 32 + c < nvalid) ? v1[c] : -INFINITY;
+                    v0[c] = (c < nvalid) ? v0[c] : -INFINITY;
+                    v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
                 }
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -300,7 +282,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 m4[(c >> 1) & 1] = fmaxf(m4[(c >> 1) & 1], fmaxf(v0[c], v0[c + 1]));
                 m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
             }
-            mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+            mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
         const float mxs = mx * cscale;               // cscale > 0; -inf stays -inf (a row that sees nothing of this tile)
         if (t == 0) {
@@ -313,58 +295,51 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 const float alpha = grow ? ex2_approx(m_ref - mxs) : 1.0f;
                 if (grow) m_ref = mxs;
                 l *= alpha;
-                wait(&o_done[g], (uint32_t)((t - 1) & 1), 2);       // P V_g(t-1) has completed
+                wait(&o_done[(t - 1) & 1], (uint32_t)(((t - 1) >> 1) & 1), 2);   // P V(t-1) has completed
                 tc_fence_after();
 #pragma unroll
-                for (int hh = 0; hh < D / 32; ++hh) {
-                    float a[32];
-                    tmem_ld32(o_addr + hh * 32, a);
+                for (int hh = 0; hh < D / 16; ++hh) {
+                    float a[16];
+                    tmem_ld16(o_addr + hh * 16, a);
                     tmem_wait_ld();
-                    float lo[16], hi[16];
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) { lo[c] = a[c] * alpha; hi[c] = a[16 + c] * alpha; }
-                    tmem_st16(o_addr + hh * 32, lo);
-                    tmem_st16(o_addr + hh * 32 + 16, hi);
+                    for (int c = 0; c < 16; ++c) a[c] *= alpha;
+                    tmem_st16(o_addr + hh * 16, a);
                 }
             }
         }
 
-        // ---- second sweep: exponentials, rounded to bf16, over S in place ------------------------
-        float ps4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        {
-            float cur[32], nxt[32];
-            tmem_ld32(s_addr, cur);
+        // ---- exponentials, rounded to bf16, over S in place --------------------------------------------
+        float ps4[4] = {0.0f, 0.0f, 0.0f, 0.0f};    // four summation chains
+        if (warp_dead) {
+            uint32_t zz[16];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                tmem_wait_ld();
-                if (k + 1 < 4) tmem_ld32(s_addr + (k + 1) * 32, nxt);
+            for (int c = 0; c < 16; ++c) zz[c] = 0u;
+            tmem_st16_u32(s_addr, zz);
+            tmem_st16_u32(s_addr + 16, zz);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    float p0 = ex2_approx(fmaf(cur[c], cscale, -m_ref));
-                    float p1 = ex2_approx(fmaf(cur[c + 1], cscale, -m_ref));
-                    if (need_mask) {
-                        p0 = (k * 32 + c < nvalid) ? p0 : 0.0f;
-                        p1 = (k * 32 + c + 1 < nvalid) ? p1 : 0.0f;
-                    }
+                    const float s0 = k ? v1[c] : v0[c], s1 = k ? v1[c + 1] : v0[c + 1];
+                    const float p0 = ex2_approx(fmaf(s0, cscale, -m_ref));
+                    const float p1 = ex2_approx(fmaf(s1, cscale, -m_ref));
                     ps4[(c >> 1) & 3] += p0 + p1;
                     pk[c >> 1] = pack_bf16(p0, p1);
                 }
-                tmem_st16_u32(s_addr + k * 16, pk);        // columns [16k, 16k+16): all of them read already
-                if (k + 1 < 4) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) cur[c] = nxt[c];
-                }
+                tmem_st16_u32(s_addr + k * 16, pk);        // columns [16k, 16k+16): all 64 scores are in registers already
             }
         }
         l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
         tmem_wait_st();
         tc_fence_before();
-        arrive(&p_full[g]);
+        arrive(&p_full[buf]);
     }
 
-    if (ntg > 0) {
-        wait(&o_done[g], (uint32_t)((ntg - 1) & 1), 3);
+    {
+        wait(&o_done[(nt - 1) & 1], (uint32_t)(((nt - 1) >> 1) & 1), 3);
         tc_fence_after();
         const float inv = 1.0f / fmaxf(l, 1e-20f);
         const bool store = !abort_flag && row < S;
@@ -391,12 +366,12 @@ int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int 
 {
     using C = Bf16Cfg<D>;
     auto kern = mha_bf16_kernel<D, CAUSAL>;
-    // more than half of an SM's shared memory: one block per SM, so its 512 TMEM columns always fit
+    // at least 100 KB: at most two blocks share an SM, so their 256-column TMEM allocations always fit in the 512 columns
     size_t smem = C::kSmemBytes + 1024;
-    if (smem < 120 * 1024) smem = 120 * 1024;
+    if (smem < 100 * 1024) smem = 100 * 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    const int nqblk = (S + 2 * kRows - 1) / (2 * kRows);
+    const int nqblk = (S + kRows - 1) / kRows;
     const long long blocks = (long long)B * H * nqblk;
     if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
     const float cscale = (1.0f / sqrtf((float)D)) * kLog2e;
