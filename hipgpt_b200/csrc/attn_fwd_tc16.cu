@@ -153,7 +153,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     uint8_t *q_16 = q_hi + C::kQhiBytes;             // fp16 [HB][128][64]: a row is [Q_lo (D) | Q (D)], K-major
     uint8_t *k_st = q_16 + C::kQ16Bytes;             // per stage: K fp32 [DB][64][32], then fp16 [HB][64][64]: [K_hi (D) | K_lo (D)]
     uint8_t *v_st = k_st + 2 * kKStage;              // per stage: fp32 N-major [V blocks | V_lo blocks], then the fp16 copy of V
-    __shared__ uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], o_done[2];
+    __shared__ uint64_t k_full[2], v_full[2], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
@@ -179,11 +179,10 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], PWK);              // one arrival per K warp
             mbar_init(&v_full[i], PWV);              // one arrival per V warp
-            mbar_init(&k_free[i], 1);                // tcgen05.commit
-            mbar_init(&v_free[i], 1);
-            mbar_init(&s_full[i], 1);
+            mbar_init(&s_full[i], 1);                // tcgen05.commit after Q K^T: S is ready, and the K stage is free
             mbar_init(&p_full[i], kWorkers / 32);    // one arrival per worker warp
-            mbar_init(&o_done[i], 1);                // by tile parity: a worker may be two tiles ahead of the P V products
+            mbar_init(&o_done[i], 1);                // tcgen05.commit after P V: O is up to date, and the V stage is free;
+                                                     // by tile parity: a worker may be two tiles ahead of the P V products
         }
     }
     __syncthreads();
@@ -235,8 +234,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                     for (int k = 0; k < 4; ++k)      // 8 floats = 32 bytes per instruction
                         mma_ss(d, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_qk_t, 1);
                 }
-                tc_commit(&s_full[buf]);
-                tc_commit(&k_free[stage]);
+                tc_commit(&s_full[buf]);             // also tells the K warp that this stage (same parity as buf) is free
             };
             auto issue_pv = [&](int buf, int stage, bool first) {
                 // fp32 N-major B: 8 keys of 128 bytes per instruction; lbo = bytes between 32-column blocks
@@ -250,8 +248,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)  // 16 keys = 8 TMEM columns of packed fp16 = two key groups of the fp16 V
                     mma_h_ts(tmem + kColO + D, tmem + kColL + buf * 32 + (uint32_t)(k * 8), dvt + (uint64_t)(k * 2 * D), id_pv_h, 1);
-                tc_commit(&o_done[buf]);
-                tc_commit(&v_free[stage]);
+                tc_commit(&o_done[buf]);             // also tells the V warp that this stage is free
             };
             wait(&k_full[0], 0, 4);
             tc_fence_after();
@@ -338,7 +335,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             const int st = u & 1;
             if (lane == 0 && u < 6) C16(64 + 4 * u);
             if (u + 1 < nt) {
-                if (u >= 1) wait(&k_free[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 7);   // Q K(u-1)^T has completed
+                if (u >= 1) wait(&s_full[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 7);   // Q K(u-1)^T has completed
                 copy_k(u + 1, st ^ 1);
             } else {
                 cp_async_commit();                   // keeps the group count of the wait below
@@ -409,7 +406,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             if (lane == 0 && u < 6) C16(98 + 4 * u);
             if (u + 1 < nt) {
                 // the stage of V(u+1) held V(u-1); V(u) is published before this warp waits for that product
-                if (u >= 1) wait(&v_free[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 8);   // P V(u-1) has completed
+                if (u >= 1) wait(&o_done[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 8);   // P V(u-1) has completed
                 copy_v(u + 1, st ^ 1);
             }
             if (lane == 0 && u < 6) C16(99 + 4 * u);
