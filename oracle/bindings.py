@@ -160,3 +160,54 @@ def gpt_generate(weights: np.ndarray, V, S, E, L, H, F, prompts: np.ndarray, n_n
     if rc < 0:
         raise ValueError("oracle rejected the generation request")
     return out, logits
+
+
+def ref_dropout_forward(x: np.ndarray, p: float, N: int, E: int):
+    """The reference's dropout launcher on host cores -> (output, mask)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    mask = np.empty_like(x)
+    lib = ref_lib()
+    lib.ref_dropout_forward.restype = None
+    lib.ref_dropout_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]
+    lib.ref_dropout_forward(_f(x), _f(out), _f(mask), p, N, E)
+    return out, mask
+
+
+def ref_embedding_lookup(ids: np.ndarray, tok: np.ndarray, pos: np.ndarray, B: int, S: int, V: int, E: int):
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    out = np.empty((B * S, E), dtype=np.float32)
+    lib = ref_lib()
+    lib.ref_embedding_lookup.restype = None
+    lib.ref_embedding_lookup.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
+    lib.ref_embedding_lookup(_i(ids), _f(tok), _f(pos), _f(out), B, S, V, E)
+    return out
+
+
+def gpt_generate_window(weights: np.ndarray, V, S, E, L, H, F, prompts: np.ndarray, n_new: int, dropout_p: float = 0.1,
+                        fma: bool = True):
+    """Greedy ids [B, n_new] of the reference's own generation loop (padded window of S ids re-run
+    per token) and the logits [B, V] of the last step."""
+    B, n_prompt = prompts.shape
+    prompts = np.ascontiguousarray(prompts, dtype=np.int32)
+    out = np.zeros((B, n_new), dtype=np.int32)
+    logits = np.zeros((B, V), dtype=np.float32)
+    lib = oracle_lib(fma)
+    lib.oracle_gpt_generate_window.restype = C.c_int
+    lib.oracle_gpt_generate_window.argtypes = [C.c_void_p] + [C.c_int] * 6 + [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float,
+                                                                              C.c_void_p, C.c_void_p]
+    rc = lib.oracle_gpt_generate_window(_f(weights), V, S, E, L, H, F, _i(prompts), B, n_prompt, n_new, dropout_p, _i(out), _f(logits))
+    if rc < 0:
+        raise ValueError("oracle rejected the generation request")
+    return out, logits
+
+
+def dropout_oracle(x: np.ndarray, p: float):
+    """The oracle's restatement of the reference's dropout on a flat array (for the pin against ref_dropout_forward)."""
+    x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    out = np.empty_like(x)
+    lib = oracle_lib(False)
+    lib.oracle_dropout.restype = None
+    lib.oracle_dropout.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_float]
+    lib.oracle_dropout(_f(x), _f(out), x.size, p)
+    return out

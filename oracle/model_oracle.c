@@ -224,3 +224,113 @@ ORACLE_API int oracle_gpt_generate(const float *weights, int V, int S, int E, in
     free(lw);
     return rc;
 }
+
+/* ------------------------------------------------------------------------------------------------
+ * The reference's own generation loop (src/gpt_model.cpp:248-353), greedy: for every new token the
+ * last min(len, S) ids are right-aligned in a window of S ids padded on the left with id 0
+ * (:263-267), the whole window is run through the model at batch 1 (:273), and the logits of the last
+ * position are read (:276-280).  No mask, no cache; the pad tokens are ordinary tokens.
+ * The forward follows src/gpt_model.cpp:97-118 and src/transformer_layer.cpp:214-253 statement by
+ * statement, including two things a reader might not expect:
+ *   - the [T, 3E] output of the QKV projection is handed to launch_multihead_attention, which reads it
+ *     as three stacked [T*E] planes (src/hip_kernels.cpp:415-417): plane Q is the first third of the
+ *     buffer, not the first E columns;
+ *   - dropout is applied at inference too, with a mask that depends only on the element index
+ *     (src/hip_kernels.cpp:944-964 and the generator at :24-42).
+ * Matmuls keep one accumulator per output and add k ascending, bias once at the end
+ * (src/hip_kernels.cpp:127-143); layer-norm sums are in the order of a warp reduction (see above).
+ * Sampling is replaced by the first maximum.
+ */
+static float dropout_one(float x, unsigned int idx, float p)
+{
+    const unsigned int blk = idx / 256u, thr = idx % 256u;      /* 256-thread blocks, src/hip_kernels.cpp:967-968 */
+    const unsigned int a = idx + 1u, d = idx * blk + 1u;        /* b = blk + 1 and c = thr + 1 do not reach the first output */
+    (void)thr;
+    unsigned int t = d, s = a;
+    t ^= t >> 2;
+    t ^= t << 1;
+    t ^= s ^ (s << 4);
+    const unsigned int r = t + 1u;                              /* counter is 1 after the first draw */
+    const float u = (float)r / (float)4294967295u;              /* (float)UINT_MAX */
+    return u < p ? 0.0f : x / (1.0f - p);
+}
+
+ORACLE_API void oracle_dropout(const float *x, float *out, long long n, float p)
+{
+    for (long long i = 0; i < n; ++i) out[i] = dropout_one(x[i], (unsigned int)i, p);
+}
+
+/* C[r][n] = (sum_k A[r][k] * W[k][n]) + bias[n], optional relu; rows in parallel */
+static void matmul_rows(const float *A, const float *W, const float *bias, float *C, int M, int K, int N, int relu)
+{
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < M; ++r) {
+        float *acc = C + (size_t)r * N;
+        for (int n = 0; n < N; ++n) acc[n] = 0.0f;
+        for (int k = 0; k < K; ++k) {
+            const float ak = A[(size_t)r * K + k];
+            const float *w = W + (size_t)k * N;
+            for (int n = 0; n < N; ++n) acc[n] = MAC(acc[n], ak, w[n]);
+        }
+        for (int n = 0; n < N; ++n) {
+            float v = acc[n];
+            if (bias) v = v + bias[n];
+            if (relu) v = fmaxf(0.0f, v);
+            acc[n] = v;
+        }
+    }
+}
+
+int oracle_mha_dispatch(const float *qkv, float *out, float *probs, int B, int S, int E, int H, int causal);
+
+ORACLE_API int oracle_gpt_generate_window(const float *weights, int V, int S, int E, int L, int H, int F,
+                                          const int *prompts, int B, int n_prompt, int n_new, float dropout_p,
+                                          int *out_ids, float *logits_last)
+{
+    if (V <= 0 || S <= 0 || E <= 0 || L <= 0 || H <= 0 || F <= 0 || E % H || B < 0 || n_prompt <= 0 || n_new < 0) return -1;
+    gpt_cfg c = {V, S, E, L, H, F};
+    const float *tok, *pos, *wout;
+    layer_w *lw = (layer_w *)malloc(sizeof(layer_w) * L);
+    split_weights(weights, &c, &tok, &pos, lw, &wout);
+    const size_t TE = (size_t)S * E;
+    float *x = (float *)malloc(sizeof(float) * TE), *h = (float *)malloc(sizeof(float) * TE), *x1 = (float *)malloc(sizeof(float) * TE);
+    float *qkv = (float *)malloc(sizeof(float) * 3 * TE), *att = (float *)malloc(sizeof(float) * TE), *proj = (float *)malloc(sizeof(float) * TE);
+    float *probs = (float *)malloc(sizeof(float) * (size_t)H * S * S), *ff = (float *)malloc(sizeof(float) * (size_t)S * F);
+    float *logits = (float *)malloc(sizeof(float) * V);
+    int *seq = (int *)malloc(sizeof(int) * (n_prompt + n_new)), *ids = (int *)malloc(sizeof(int) * S);
+    for (int b = 0; b < B; ++b) {
+        int len = n_prompt;
+        memcpy(seq, prompts + (size_t)b * n_prompt, sizeof(int) * n_prompt);
+        for (int step = 0; step < n_new; ++step) {
+            const int cur = len < S ? len : S;
+            for (int t = 0; t < S; ++t) ids[t] = 0;
+            memcpy(ids + (S - cur), seq + (len - cur), sizeof(int) * cur);
+            for (int t = 0; t < S; ++t) {
+                const int id = ids[t];
+                const int valid = id >= 0 && id < V;
+                for (int e = 0; e < E; ++e) x[(size_t)t * E + e] = valid ? tok[(size_t)id * E + e] + pos[(size_t)t * E + e] : 0.0f;
+            }
+            for (int l = 0; l < L; ++l) {
+#pragma omp parallel for schedule(static)
+                for (int t = 0; t < S; ++t) layer_norm(x + (size_t)t * E, h + (size_t)t * E, lw[l].g1, lw[l].be1, E);
+                matmul_rows(h, lw[l].wqkv, lw[l].bqkv, qkv, S, E, 3 * E, 0);
+                if (oracle_mha_dispatch(qkv, att, probs, 1, S, E, H, 0) < 0) { free(lw); return -1; }
+                matmul_rows(att, lw[l].wo, lw[l].bo, proj, S, E, E, 0);
+                for (size_t i = 0; i < TE; ++i) x1[i] = x[i] + dropout_one(proj[i], (unsigned int)i, dropout_p);
+#pragma omp parallel for schedule(static)
+                for (int t = 0; t < S; ++t) layer_norm(x1 + (size_t)t * E, h + (size_t)t * E, lw[l].g2, lw[l].be2, E);
+                matmul_rows(h, lw[l].w1, lw[l].b1, ff, S, E, F, 1);
+                matmul_rows(ff, lw[l].w2, lw[l].b2, proj, S, F, E, 0);
+                for (size_t i = 0; i < TE; ++i) x[i] = x1[i] + dropout_one(proj[i], (unsigned int)i, dropout_p);
+            }
+            matmul_rows(x + (size_t)(S - 1) * E, wout, NULL, logits, 1, E, V, 0);
+            int best = 0;
+            for (int v = 1; v < V; ++v) if (logits[v] > logits[best]) best = v;
+            out_ids[(size_t)b * n_new + step] = best;
+            seq[len++] = best;
+            if (logits_last && step == n_new - 1) memcpy(logits_last + (size_t)b * V, logits, sizeof(float) * V);
+        }
+    }
+    free(x); free(h); free(x1); free(qkv); free(att); free(proj); free(probs); free(ff); free(logits); free(seq); free(ids); free(lw);
+    return 0;
+}

@@ -49,6 +49,21 @@ void ref_weighted_sum(const float *P, const float *V, float *out, int B, int S, 
     launch_attention_weighted_sum(P, V, out, B, S, D);
 }
 
+/* The elementwise launchers around the attention call in the reference's layer and model forward
+ * (src/transformer_layer.cpp:242,250; src/gpt_model.cpp:107): none of their kernels synchronises
+ * threads, so the loop form of a launch is valid for them. */
+__attribute__((visibility("default")))
+void ref_dropout_forward(const float *in, float *out, float *mask, float p, int N, int E)
+{
+    launch_dropout_forward(in, out, mask, p, N, E);
+}
+
+__attribute__((visibility("default")))
+void ref_embedding_lookup(const int *ids, const float *tok, const float *pos, float *out, int B, int S, int V, int E)
+{
+    launch_embedding_lookup(ids, tok, pos, out, B, S, V, E);
+}
+
 __attribute__((visibility("default")))
 int ref_num_threads(void)
 {

@@ -163,3 +163,61 @@ def test_synth_is_deterministic_and_normal():
     assert not np.array_equal(a, synth.normal(4, (1000, 64)))
     ids = synth.token_ids(3, (8, 16), 5000)
     assert ids.min() >= 0 and ids.max() < 5000
+
+
+# ---- the pieces around the attention call in the reference's generation loop ------------------------
+needs_ref = pytest.mark.skipif(not ob.have_ref(), reason="reference build absent (HipGPT tree not mounted here)")
+
+
+@needs_ref
+def test_oracle_dropout_equals_reference_build_bitwise():
+    """The oracle's restatement of launch_dropout_forward (src/hip_kernels.cpp:944-970, generator :24-42)
+    against the reference's own code built for the host, at the element counts of the generation window
+    (256 x 256), of a longer window and of the training batch."""
+    rng = np.random.default_rng(5)
+    for n_rows, E in [(256, 256), (1024, 256), (8192, 256)]:
+        x = rng.standard_normal(n_rows * E).astype(np.float32)
+        ref_out, ref_mask = ob.ref_dropout_forward(x, 0.1, n_rows, E)
+        assert np.array_equal(ob.dropout_oracle(x, 0.1), ref_out)
+        if n_rows * E <= 185384:
+            # the generator's first draw is tiny for small element indices: everything is dropped
+            assert not ref_mask.any()
+        else:
+            assert ref_mask.any()
+
+
+@needs_ref
+def test_reference_embedding_matches_the_oracle_arithmetic():
+    """tok[id] + pos[t], and a zero row for an id outside the vocabulary (src/hip_kernels.cpp:537-581)."""
+    rng = np.random.default_rng(6)
+    V, S, E = 50, 12, 16
+    tok = rng.standard_normal((V, E)).astype(np.float32)
+    pos = rng.standard_normal((S, E)).astype(np.float32)
+    ids = rng.integers(0, V, size=(2, S)).astype(np.int32)
+    ids[0, 3] = -1
+    ids[1, 5] = V
+    got = ob.ref_embedding_lookup(ids, tok, pos, 2, S, V, E).reshape(2, S, E)
+    want = tok[np.clip(ids, 0, V - 1)] + pos[None]
+    want[0, 3] = 0
+    want[1, 5] = 0
+    assert np.array_equal(got, want)
+
+
+def test_window_generation_oracle_with_reference_dropout_is_the_identity_model():
+    """The reference's generation loop (padded window of S ids re-run per token) with its inference-time
+    dropout: at 256 x 256 elements the mask is all zeros, every sub-layer output is dropped, and the ids are
+    those of (tok[id] + pos[S-1]) Wout.  Without dropout the layers matter and the ids differ."""
+    g = synth.GPT_DEFAULT
+    V, S, E, L, H, F = g["V"], g["S"], g["E"], g["L"], g["H"], g["F"]
+    w = synth.gpt_weights(3, **g)
+    prompts = synth.token_ids(3, (2, 16), V, stream=1)
+    ids, _ = ob.gpt_generate_window(w, V, S, E, L, H, F, prompts, 2, 0.1)
+    tok = w[:V * E].reshape(V, E)
+    pos = w[V * E:V * E + S * E].reshape(S, E)
+    wout = w[-E * V:].reshape(E, V)
+    first = ((tok[prompts[:, -1]] + pos[S - 1]).astype(np.float64) @ wout.astype(np.float64)).argmax(1)
+    assert ids[:, 0].tolist() == first.tolist()
+    second = ((tok[ids[:, 0]] + pos[S - 1]).astype(np.float64) @ wout.astype(np.float64)).argmax(1)
+    assert ids[:, 1].tolist() == second.tolist()
+    ids0, _ = ob.gpt_generate_window(w, V, S, E, L, H, F, prompts, 2, 0.0)
+    assert ids0.tolist() != ids.tolist()
