@@ -368,8 +368,9 @@ def run_ours(args):
     # Which roofline binds the kernel that ran: the time HBM needs for the algorithmic bytes against
     # the time the pipe needs for the algorithmic FLOPs.  The tensor-core kernel computes in
     # split-TF32 (three TF32 products per fp32 product); TF32 runs at half the measured dense bf16
-    # rate.  The FFMA kernel (probabilities stored) is measured against the FFMA ceiling.
-    tensor_kernel = not args.probs and D in (32, 64)
+    # rate.  With the probabilities stored the kernel forms Q K^T twice (1.5 times the tensor work)
+    # and writes B H S S floats more.  Other head dims run the FFMA kernel, measured against the FFMA ceiling.
+    tensor_kernel = D in (32, 64)
     flops_launch = flops_of(B, H, S, D, args.causal)
     # a kernel timed back to back for seconds is compared with the sustained figure
     bf16_peak = float(peaks.get("bf16_tflops_sustained" if bf16 else "bf16_tflops", 1400.0 if bf16 else 1590.0))
@@ -378,7 +379,7 @@ def run_ours(args):
     # tensor work per fp32 product, in TF32 products: the default kernel runs one TF32 product and two FP16
     # products (twice the TF32 rate); 3 would be the figure of the split-TF32 variant
     tc16 = tensor_kernel and not bf16
-    tf32_products = 2.0 if tc16 else 3.0
+    tf32_products = (2.0 if tc16 else 3.0) * (1.5 if args.probs else 1.0)
     t_pipe = (flops_launch / (bf16_peak * 1e12)) if bf16 else (tf32_products * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
     src = "measured" if peaks else "fallback"
     if bf16 and t_hbm < t_pipe:
@@ -390,12 +391,12 @@ def run_ours(args):
     elif tensor_kernel:
         roofline = {"bound": "tensor", "achieved": tf32_products * achieved, "peak": tf32_peak, "unit": "TFLOP/s",
                     "frac": tf32_products * achieved / tf32_peak,
-                    "peak_source": f"half of MEASURED_PEAKS.json bf16_tflops ({src}): TF32 rate; achieved counts the {tf32_products:.0f} TF32-equivalent products per fp32 product"}
+                    "peak_source": f"half of MEASURED_PEAKS.json bf16_tflops ({src}): TF32 rate; achieved counts the {tf32_products:g} TF32-equivalent products per fp32 product"}
     else:
         roofline = {"bound": "fma", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s", "frac": achieved / fma_peak,
                     "peak_source": "fp32 FFMA loop timed in this run"}
     roofline.update({"kernel": "mha_bf16_kernel" if bf16 else "mha_tc16_kernel" if tc16 else "mha_tc_kernel" if tensor_kernel else "mha_rows_kernel",
-                     "traffic": None if bf16 else TRAFFIC.get((args.workload, tensor_kernel)),
+                     "traffic": None if (bf16 or args.probs) else TRAFFIC.get((args.workload, tensor_kernel)),
                      "us_per_launch": launch_ms * 1e3, "algorithmic_bytes_per_launch": per_batch_bytes,
                      "algorithmic_flops_per_launch": flops_launch,
                      "vs_fp32_fma_ceiling": {"achieved_tflops": achieved, "ffma_peak_tflops": fma_peak, "ratio": achieved / fma_peak,

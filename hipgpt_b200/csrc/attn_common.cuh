@@ -45,7 +45,8 @@ int tc_status_fetch(int *status);
 int launch_mha_tc_pair(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_tc_pair_supports(int head_dim);
 int tc_pair_status_fetch(int *status);
-int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st);
+int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, float *probs,
+                    int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_tc16_supports(int head_dim);
 int tc16_status_fetch(int *status);
 int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st);

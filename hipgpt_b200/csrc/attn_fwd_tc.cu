@@ -976,7 +976,7 @@ int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
     if (variant == 4) return launch_mha_tc_pair(q, k, v, out, B, S, E, H, causal, st);
     // default: fewer tensor-core instructions per tile and a softmax that runs ahead of the P V
     // products; measured faster than variant 1 at every benchmark shape
-    if (variant == 5 || variant == 0) return launch_mha_tc16(q, k, v, out, B, S, E, H, causal, st);
+    if (variant == 5 || variant == 0) return launch_mha_tc16(q, k, v, out, nullptr, B, S, E, H, causal, st);
     if (variant == 3) {
         if (D == 32) return causal ? launch_tcp_cfg<32, 64, true>(q, k, v, out, B, S, E, H, st)
                                    : launch_tcp_cfg<32, 64, false>(q, k, v, out, B, S, E, H, st);

@@ -139,10 +139,10 @@ struct PieceMap {
     __device__ int row(int p) const { return RPP * (p >> 1) + 2 * pq + (p & 1); }
 };
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool PROBS>
 __global__ void __launch_bounds__(Tc16Cfg<D>::THREADS, Tc16Cfg<D>::BLOCKS_PER_SM)
 mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
-                float *__restrict__ O, int S, int E, int H, int BH, int nqblk, float qscale)
+                float *__restrict__ O, float *__restrict__ P, int S, int E, int H, int BH, int nqblk, float qscale)
 {
     using C = Tc16Cfg<D>;
     constexpr int DB = C::DB, HB = C::HB, PPR = C::PPR, PWK = C::PWK, PWV = C::PWV;
@@ -172,6 +172,10 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     const int q0 = qblk * kRows;
     const int kend = CAUSAL ? min(S, q0 + kRows) : S;
     const int nt = (kend + kKeys - 1) / kKeys;       // >= 1: q0 < S
+    // With PROBS the key tiles are swept a second time once a row's maximum and sum are final:
+    // Q K^T is formed again and the normalised probabilities go to global memory.  Sweep-2 tile
+    // u (nt <= u < 2 nt) is key tile u - nt; stages, buffers and barrier phases continue by u.
+    const int nk = PROBS ? 2 * nt : nt;              // K tiles staged, Q K^T products issued
 
     if (tid == 0) {
         abort_flag = 0;
@@ -271,6 +275,17 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                 issue_pv(st, st, t == 0);
                 if (t < 6) C16(37 + 4 * t);
             }
+            if (PROBS) {
+                // X[u & 1] held P(u-2) (consumed by P V(u-2), issued before) or, from the third tile of
+                // this sweep on, S(u-2), which the workers must have read
+                for (int u = nt; u < nk; ++u) {
+                    const int bf = u & 1;
+                    wait(&k_full[bf], (uint32_t)((u >> 1) & 1), 4);
+                    if (u - 2 >= nt) wait(&p_full[bf], (uint32_t)(((u - 2) >> 1) & 1), 5);
+                    tc_fence_after();
+                    issue_qk(bf, bf);
+                }
+            }
         }
         __syncwarp();
         tc_fence_before();
@@ -331,12 +346,12 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         };
         copy_k(0, 0);
         __syncthreads();                             // matches the block-wide barrier after Q staging
-        for (int u = 0; u < nt; ++u) {
+        for (int u = 0; u < nk; ++u) {
             const int st = u & 1;
             if (lane == 0 && u < 6) C16(64 + 4 * u);
-            if (u + 1 < nt) {
+            if (u + 1 < nk) {
                 if (u >= 1) wait(&s_full[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 7);   // Q K(u-1)^T has completed
-                copy_k(u + 1, st ^ 1);
+                copy_k(u + 1 < nt ? u + 1 : u + 1 - nt, st ^ 1);
             } else {
                 cp_async_commit();                   // keeps the group count of the wait below
             }
@@ -573,6 +588,59 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                                                   (a[c * 4 + 2] + c2[c * 4 + 2]) * inv, (a[c * 4 + 3] + c2[c * 4 + 3]) * inv);
             }
         }
+        if (PROBS) {
+            // ---- second sweep: p = 2^(s - m_ref) / l for every key of the row, zeros where masked -----
+            float *prow = P + ((size_t)bh * S + (row < S ? row : 0)) * (size_t)S;
+            const bool vec = (S & 3) == 0;               // then every 4-column group of a row is 16-byte aligned
+            for (int u = nt; u < nk; ++u) {
+                const int buf = u & 1, j0 = (u - nt) * kKeys;
+                const uint32_t s_addr = lane_base + kColX + buf * kKeys;
+                wait(&s_full[buf], (uint32_t)((u >> 1) & 1), 1);
+                tc_fence_after();
+                const bool warp_dead = CAUSAL && j0 > q0 + wq * 32 + 31;
+                const int ncols = min(kKeys, S - j0);                                   // columns of this tile that exist
+                const int nvalid = min(ncols, CAUSAL ? row - j0 + 1 : kKeys);           // ... that this row sees
+                float v0[32], v1[32];
+                if (!warp_dead) {
+                    tmem_ld32(s_addr, v0);
+                    tmem_ld32(s_addr + 32, v1);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v0[c] = v1[c] = 0.0f;
+                }
+                tc_fence_before();
+                arrive(&p_full[buf]);                    // the issuing lane may overwrite this buffer with S(u+2)
+                if (store) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 16; ++c4) {
+                        float o[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int c = 4 * c4 + i;
+                            const float sc = c < 32 ? v0[c & 31] : v1[c & 31];
+                            o[i] = c < nvalid ? ex2_approx(sc - m_ref) * inv : 0.0f;
+                        }
+                        if (vec) {
+                            if (4 * c4 < ncols) *reinterpret_cast<float4 *>(prow + j0 + 4 * c4) = make_float4(o[0], o[1], o[2], o[3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                if (4 * c4 + i < ncols) prow[j0 + 4 * c4 + i] = o[i];
+                        }
+                    }
+                }
+            }
+            // keys past the last tile of a causal block are all masked
+            if (CAUSAL && store) {
+                const int z0 = nt * kKeys;
+                if (vec) {
+                    for (int c = z0; c < S; c += 4) *reinterpret_cast<float4 *>(prow + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else {
+                    for (int c = z0; c < S; ++c) prow[c] = 0.0f;
+                }
+            }
+        }
     }
     T16(8);
     if (tid == 0) C16(61);
@@ -580,11 +648,11 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     __syncthreads();
 }
 
-template <int D, bool CAUSAL>
-int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, cudaStream_t st)
+template <int D, bool CAUSAL, bool PROBS>
+int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, float *probs, int B, int S, int E, int H, cudaStream_t st)
 {
     using C = Tc16Cfg<D>;
-    auto kern = mha_tc16_kernel<D, CAUSAL>;
+    auto kern = mha_tc16_kernel<D, CAUSAL, PROBS>;
     // two blocks per SM (256 TMEM columns each): at least 100 KB, so that a third block never shares the SM;
     // one block per SM (512 columns): more than half of the SM's shared memory
     size_t smem = C::kSmemBytes + 1024;
@@ -596,7 +664,7 @@ int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, 
     const long long blocks = (long long)B * H * nqblk;
     if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
     const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<(unsigned)blocks, C::THREADS, smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, qscale);
+    kern<<<(unsigned)blocks, C::THREADS, smem, st>>>(q, k, v, out, probs, S, E, H, B * H, nqblk, qscale);
     return check_launch("mha_tc16_kernel");
 }
 
@@ -604,13 +672,24 @@ int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, 
 
 bool mha_tc16_supports(int head_dim) { return head_dim == 32 || head_dim == 64; }
 
-int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st)
+// `probs` (optional): [B][H][S][S], written by a second sweep over the key tiles
+int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, float *probs,
+                    int B, int S, int E, int H, int causal, cudaStream_t st)
 {
     const int D = E / H;
     if (!mha_tc16_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "tf32+fp16 tensor-core kernel: head_dim %d is not 32 or 64", D);
     if (B == 0 || S == 0) return HIPGPT_OK;
-    if (D == 32) return causal ? launch_tc16_cfg<32, true>(q, k, v, out, B, S, E, H, st) : launch_tc16_cfg<32, false>(q, k, v, out, B, S, E, H, st);
-    return causal ? launch_tc16_cfg<64, true>(q, k, v, out, B, S, E, H, st) : launch_tc16_cfg<64, false>(q, k, v, out, B, S, E, H, st);
+    const int sel = (D == 64 ? 4 : 0) | (causal ? 2 : 0) | (probs ? 1 : 0);
+    switch (sel) {
+    case 0: return launch_tc16_cfg<32, false, false>(q, k, v, out, probs, B, S, E, H, st);
+    case 1: return launch_tc16_cfg<32, false, true>(q, k, v, out, probs, B, S, E, H, st);
+    case 2: return launch_tc16_cfg<32, true, false>(q, k, v, out, probs, B, S, E, H, st);
+    case 3: return launch_tc16_cfg<32, true, true>(q, k, v, out, probs, B, S, E, H, st);
+    case 4: return launch_tc16_cfg<64, false, false>(q, k, v, out, probs, B, S, E, H, st);
+    case 5: return launch_tc16_cfg<64, false, true>(q, k, v, out, probs, B, S, E, H, st);
+    case 6: return launch_tc16_cfg<64, true, false>(q, k, v, out, probs, B, S, E, H, st);
+    default: return launch_tc16_cfg<64, true, true>(q, k, v, out, probs, B, S, E, H, st);
+    }
 }
 
 #ifdef HIPGPT_TC_TRACE

@@ -54,9 +54,10 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
                          (probs == nullptr || (reinterpret_cast<uintptr_t>(probs) & 15) == 0);
     switch (algo) {
     case HIPGPT_ALGO_AUTO:
-        // tensor pipe when it applies (fp32-grade split-TF32); FFMA rows kernel when the
-        // probabilities are wanted or head_dim is 128; generic kernel for everything else
-        if (mha_tc_supports(D) && aligned && probs == nullptr) return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
+        // tensor pipe when it applies (fp32-grade TF32 + FP16 products; with the probabilities
+        // it sweeps the key tiles twice); FFMA rows kernel for head_dim 128; generic kernel for everything else
+        if (mha_tc16_supports(D) && aligned && probs != nullptr) return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
+        if (mha_tc_supports(D) && aligned) return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
         if (mha_rows_supports(D) && aligned) return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
         return launch_mha_generic(q, k, v, out, probs, B, S, E, H, causal, st);
     case HIPGPT_ALGO_GENERIC:
@@ -66,8 +67,11 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
         return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
     case HIPGPT_ALGO_TENSOR:
         if (!aligned) return fail(HIPGPT_ERR_BAD_ARG, "tensor-core kernel needs 16-byte aligned pointers");
-        if (probs) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel does not store probabilities");
         if (!mha_tc_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
+        if (probs) {
+            if (warps != 0 && warps != 5) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: only the default variant stores probabilities");
+            return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
+        }
         return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st, warps);   // `warps` selects the tile variant here
     default:
         return fail(HIPGPT_ERR_BAD_ARG, "unknown algo %d", algo);

@@ -40,6 +40,31 @@ def test_tensor_kernel_matches_oracle(shape, causal):
     assert float(np.abs(out - ref_out).max()) <= TOL
 
 
+# the probabilities come from a second sweep over the key tiles: tails of the tile, of the block and of the
+# 4-column store groups (S not a multiple of 4 takes the scalar stores), several tiles per block
+PROB_SHAPES = [(1, 1, 1, 32), (2, 2, 7, 32), (1, 2, 64, 32), (1, 2, 65, 32), (2, 2, 128, 32), (1, 3, 129, 32), (2, 2, 200, 32),
+               (1, 1, 513, 32), (2, 3, 640, 32), (1, 2, 64, 64), (2, 2, 130, 64), (1, 2, 300, 64), (1, 2, 1024, 64), (32, 8, 256, 32)]
+
+
+@pytest.mark.parametrize("shape", PROB_SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+def test_tensor_kernel_probabilities_match_oracle(shape, causal):
+    B, H, S, D = shape
+    E = H * D
+    qkv = synth.qkv_planes(2500 + S + D, B, S, E)
+    ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=True)
+    out, probs = gpu_mha(qkv, B, S, E, H, causal, True, algo=_capi.ALGO_TENSOR)
+    assert _status() == 0
+    assert np.isfinite(out).all() and np.isfinite(probs).all()      # the buffers were pre-filled with NaN
+    assert float(np.abs(out - ref_out).max()) <= TOL
+    assert float(np.abs(probs - ref_probs).max()) <= TOL
+    if causal:
+        assert np.all(np.triu(probs, 1) == 0.0)
+    # the same call without probabilities gives the same output bits: the second sweep only adds stores
+    out2, _ = gpu_mha(qkv, B, S, E, H, causal, False, algo=_capi.ALGO_TENSOR)
+    assert np.array_equal(out, out2)
+
+
 @pytest.mark.parametrize("cfg", ["c2", "c3"])
 @pytest.mark.parametrize("causal", [False, True])
 def test_tensor_kernel_benchmark_shapes(cfg, causal):
@@ -86,10 +111,11 @@ def test_tensor_kernel_refuses_what_it_cannot_do():
     # head_dim 48
     assert lib.hipgpt_mha_forward_ex(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), None,
                                      1, 64, 48, 1, 0, _capi.ALGO_TENSOR, 0, st) == _capi.ERR_UNSUPPORTED
-    # probabilities requested
+    # probabilities requested from a variant that does not store them (only the default one does)
     t32 = torch.zeros((64, 32), device="cuda")
-    assert lib.hipgpt_mha_forward_ex(t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), p.data_ptr(),
-                                     1, 64, 32, 1, 0, _capi.ALGO_TENSOR, 0, st) == _capi.ERR_UNSUPPORTED
+    for variant in (1, 2, 3, 4):
+        assert lib.hipgpt_mha_forward_ex(t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), t32.data_ptr(), p.data_ptr(),
+                                         1, 64, 32, 1, 0, _capi.ALGO_TENSOR, variant, st) == _capi.ERR_UNSUPPORTED
 
 
 @pytest.mark.parametrize("variant", [4, 5])
