@@ -590,14 +590,19 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         }
         if (PROBS) {
             // ---- second sweep: p = 2^(s - m_ref) / l for every key of the row, zeros where masked -----
-            float *prow = P + ((size_t)bh * S + (row < S ? row : 0)) * (size_t)S;
+            // A worker holds one row, so its own stores would be 16-byte pieces S floats apart.  The warp
+            // turns its 32 x 64 tile through shared memory instead (the V stages are free: the last P V
+            // product has completed) and stores two rows of 256 contiguous bytes per instruction.
+            uint8_t *tb = v_st + wq * (32 * kKeys * 4);  // 16-byte chunk c of row r at r * 256 + ((c ^ (r & 7)) << 4)
+            const int wrow0 = q0 + wq * 32;              // first row of this warp
+            float *pwarp = P + ((size_t)bh * S + wrow0) * (size_t)S;
             const bool vec = (S & 3) == 0;               // then every 4-column group of a row is 16-byte aligned
             for (int u = nt; u < nk; ++u) {
                 const int buf = u & 1, j0 = (u - nt) * kKeys;
                 const uint32_t s_addr = lane_base + kColX + buf * kKeys;
                 wait(&s_full[buf], (uint32_t)((u >> 1) & 1), 1);
                 tc_fence_after();
-                const bool warp_dead = CAUSAL && j0 > q0 + wq * 32 + 31;
+                const bool warp_dead = CAUSAL && j0 > wrow0 + 31;
                 const int ncols = min(kKeys, S - j0);                                   // columns of this tile that exist
                 const int nvalid = min(ncols, CAUSAL ? row - j0 + 1 : kKeys);           // ... that this row sees
                 float v0[32], v1[32];
@@ -611,33 +616,47 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                 }
                 tc_fence_before();
                 arrive(&p_full[buf]);                    // the issuing lane may overwrite this buffer with S(u+2)
-                if (store) {
 #pragma unroll
-                    for (int c4 = 0; c4 < 16; ++c4) {
-                        float o[4];
+                for (int c4 = 0; c4 < 16; ++c4) {
+                    float o[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int c = 4 * c4 + i;
-                            const float sc = c < 32 ? v0[c & 31] : v1[c & 31];
-                            o[i] = c < nvalid ? ex2_approx(sc - m_ref) * inv : 0.0f;
+                    for (int i = 0; i < 4; ++i) {
+                        const int c = 4 * c4 + i;
+                        const float sc = c < 32 ? v0[c & 31] : v1[c & 31];
+                        o[i] = c < nvalid ? ex2_approx(sc - m_ref) * inv : 0.0f;
+                    }
+                    *reinterpret_cast<float4 *>(tb + lane * 256 + ((c4 ^ (lane & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
+                }
+                __syncwarp();
+                if (!abort_flag) {
+                    if (vec) {
+                        const int ch = lane & 15;
+#pragma unroll 4
+                        for (int i = 0; i < 16; ++i) {
+                            const int rr = 2 * i + (lane >> 4);
+                            const float4 val = *reinterpret_cast<const float4 *>(tb + rr * 256 + ((ch ^ (rr & 7)) << 4));
+                            if (wrow0 + rr < S && 4 * ch < ncols)
+                                *reinterpret_cast<float4 *>(pwarp + (size_t)rr * S + j0 + 4 * ch) = val;
                         }
-                        if (vec) {
-                            if (4 * c4 < ncols) *reinterpret_cast<float4 *>(prow + j0 + 4 * c4) = make_float4(o[0], o[1], o[2], o[3]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                if (4 * c4 + i < ncols) prow[j0 + 4 * c4 + i] = o[i];
-                        }
+                    } else {
+                        for (int rr = 0; rr < 32 && wrow0 + rr < S; ++rr)
+                            for (int c = lane; c < ncols; c += 32)
+                                pwarp[(size_t)rr * S + j0 + c] =
+                                    *reinterpret_cast<const float *>(tb + rr * 256 + (((c >> 2) ^ (rr & 7)) << 4) + (c & 3) * 4);
                     }
                 }
+                __syncwarp();                            // the tile is out before the next one is staged
             }
             // keys past the last tile of a causal block are all masked
-            if (CAUSAL && store) {
+            if (CAUSAL && !abort_flag) {
                 const int z0 = nt * kKeys;
-                if (vec) {
-                    for (int c = z0; c < S; c += 4) *reinterpret_cast<float4 *>(prow + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-                } else {
-                    for (int c = z0; c < S; ++c) prow[c] = 0.0f;
+                for (int rr = 0; rr < 32 && wrow0 + rr < S; ++rr) {
+                    float *pr = pwarp + (size_t)rr * S;
+                    if (vec) {
+                        for (int c = z0 + 4 * lane; c < S; c += 128) *reinterpret_cast<float4 *>(pr + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    } else {
+                        for (int c = z0 + lane; c < S; c += 32) pr[c] = 0.0f;
+                    }
                 }
             }
         }

@@ -81,7 +81,10 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
 // Device workspace of the host-buffer call: grows to the largest request, one per process.
 struct Workspace {
     static constexpr int kStreams = 3;     // copies in, kernels, copies out
-    static constexpr int kChunks = 8;      // pieces a call is cut into
+#ifndef HIPGPT_HOST_CHUNKS
+#define HIPGPT_HOST_CHUNKS 8
+#endif
+    static constexpr int kChunks = HIPGPT_HOST_CHUNKS;   // pieces a call is cut into
     std::mutex mu;
     float *dev = nullptr;
     size_t bytes = 0;
