@@ -84,7 +84,13 @@ struct Workspace {
 #ifndef HIPGPT_HOST_CHUNKS
 #define HIPGPT_HOST_CHUNKS 8
 #endif
-    static constexpr int kChunks = HIPGPT_HOST_CHUNKS;   // pieces a call is cut into
+#ifndef HIPGPT_HOST_CHUNK_BYTES
+#define HIPGPT_HOST_CHUNK_BYTES (6u << 20)
+#endif
+    static constexpr int kChunks = HIPGPT_HOST_CHUNKS;   // most pieces a call is cut into
+    // input bytes a piece should hold at least: every copy costs several microseconds on top of its
+    // bytes, so a small call is cut into fewer pieces
+    static constexpr size_t kChunkBytes = HIPGPT_HOST_CHUNK_BYTES;
     std::mutex mu;
     float *dev = nullptr;
     size_t bytes = 0;
@@ -182,13 +188,22 @@ int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
     // at once, so the call takes about as long as its larger direction alone.
     cudaStream_t s_in = g_ws.streams[0], s_k = g_ws.streams[1], s_out = g_ws.streams[2];
     float *d_qkv = g_ws.dev, *d_out = g_ws.dev + 3 * plane, *d_probs = h_probs ? g_ws.dev + 4 * plane : nullptr;
-    const int nchunks = B < Workspace::kChunks ? B : Workspace::kChunks;
+    int nchunks = (int)((3 * plane * sizeof(float)) / Workspace::kChunkBytes);
+    nchunks = nchunks < 1 ? 1 : nchunks > Workspace::kChunks ? Workspace::kChunks : nchunks;
+    if (nchunks > B) nchunks = B;
+    // the three planes' slabs of a chunk go up as one strided copy (three rows one plane apart) where the
+    // pitch limit of such copies allows it
+    const bool strided = plane * sizeof(float) <= (size_t)0x7fffffff;
     for (int c = 0; c < nchunks; ++c) {
         int b0, b1;
         hipgpt_shard_range(B, nchunks, c, &b0, &b1);
         const size_t off = (size_t)b0 * S * E, cnt = (size_t)(b1 - b0) * S * E;
-        for (int pl = 0; pl < 3 && e == cudaSuccess; ++pl)
-            e = cudaMemcpyAsync(d_qkv + pl * plane + off, h_qkv + pl * plane + off, cnt * sizeof(float), cudaMemcpyHostToDevice, s_in);
+        if (strided)
+            e = cudaMemcpy2DAsync(d_qkv + off, plane * sizeof(float), h_qkv + off, plane * sizeof(float), cnt * sizeof(float), 3,
+                                  cudaMemcpyHostToDevice, s_in);
+        else
+            for (int pl = 0; pl < 3 && e == cudaSuccess; ++pl)
+                e = cudaMemcpyAsync(d_qkv + pl * plane + off, h_qkv + pl * plane + off, cnt * sizeof(float), cudaMemcpyHostToDevice, s_in);
         if (e == cudaSuccess) e = cudaEventRecord(g_ws.in_ready[c], s_in);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(s_k, g_ws.in_ready[c], 0);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to device: %s", cudaGetErrorString(e));
@@ -203,9 +218,7 @@ int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
             e = cudaMemcpyAsync(h_probs + (size_t)b0 * H * S * S, pr, (size_t)(b1 - b0) * H * S * S * sizeof(float), cudaMemcpyDeviceToHost, s_out);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to host: %s", cudaGetErrorString(e));
     }
-    e = cudaStreamSynchronize(s_out);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s_k);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s_in);
+    e = cudaStreamSynchronize(s_out);                // its last copy waits for the last kernel, which waits for the last copy in
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "host-buffer call: %s", cudaGetErrorString(e));
     return HIPGPT_OK;
 }
