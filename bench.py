@@ -173,7 +173,7 @@ def decode_leg():
     """Greedy KV-cache generation with the default model shape (E=256 L=8 H=8 F=1024 V=5000 S=256,
     random-init weights N(0, 0.02) seed 3, 8 prompts of 16 ids, 128 new tokens): tokens/s of the GPU
     driver, ids checked against the CPU oracle of the same arithmetic, which is timed beside it."""
-    from hipgpt_b200.generation import GptDecoder
+    from hipgpt_b200.generation import GptDecoder, MODE_PERSISTENT
     from oracle import bindings as ob
     cfg = dict(synth.GPT_DEFAULT)
     B, n_prompt, n_new = 8, 16, 128
@@ -182,6 +182,9 @@ def decode_leg():
     dec = GptDecoder(w, **cfg, max_batch=B)
     dec.generate(prompts, n_new)                               # warm-up
     ids, _, ms_prompt, ms_decode = dec.generate(prompts, n_new)
+    dec.set_mode(MODE_PERSISTENT)                              # the same steps inside one cooperative launch, for comparison
+    dec.generate(prompts, n_new)
+    ids_p, _, msp_prompt, msp_decode = dec.generate(prompts, n_new)
     dec.close()
     ob.set_num_threads(os.cpu_count() or 1)
     t0 = time.perf_counter()
@@ -190,6 +193,9 @@ def decode_leg():
     return {"metric": "greedy_decode_tokens_per_s", "value": B * n_new / ((ms_prompt + ms_decode) * 1e-3), "unit": "tok/s",
             "steady_state_tokens_per_s": B * (n_new - 1) / (ms_decode * 1e-3), "us_per_step": ms_decode / (n_new - 1) * 1e3,
             "ids_equal_cpu_oracle": bool(np.array_equal(ids, ref_ids)),
+            "driver": "one CUDA graph of 52 launches per step",
+            "persistent_form": {"value": B * n_new / ((msp_prompt + msp_decode) * 1e-3), "us_per_step": msp_decode / (n_new - 1) * 1e3,
+                           "ids_equal_cpu_oracle": bool(np.array_equal(ids_p, ref_ids))},
             "cpu_oracle_tokens_per_s": B * n_new / t_cpu, "cpu_threads": os.cpu_count(),
             "config": {"model": "E=256 L=8 H=8 F=1024 V=5000 S=256, ReLU MLP, fp32", "batch": B, "prompt_len": n_prompt, "new_tokens": n_new,
                        "mode": "causal KV-cache decode (the reference re-runs the padded window per token; not comparable)"}}

@@ -34,6 +34,7 @@ SIGNATURES = {
     "hipgpt_gpt_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i, _i, _i, _i, _i]),
     "hipgpt_gpt_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hipgpt_gpt_destroy": (None, [_vp]),
+    "hipgpt_gpt_set_mode": (_i, [_vp, _i]),
     "hipgpt_shard_range": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     "hipgpt_probe_fma": (_i, [_vp, _i, _i, C.POINTER(C.c_double), _vp]),
     "hipgpt_kernel_status": (_i, [C.POINTER(_i)]),

@@ -32,6 +32,23 @@ namespace {
 
 constexpr int kRowsPerBlock = 8;     // activation rows a matmul block keeps in shared memory
 
+// running (max, sum, weighted V) of the split-context attention, as in attn_decode.cu
+struct Partial4f {
+    float m, l;
+    float4 o;
+};
+__device__ __forceinline__ void merge_partial(Partial4f &a, float m2, float l2, const float4 &o2)
+{
+    const float mn = fmaxf(a.m, m2);
+    const float a1 = ex2_approx(a.m - mn), a2 = ex2_approx(m2 - mn);
+    a.l = a.l * a1 + l2 * a2;
+    a.o.x = a.o.x * a1 + o2.x * a2;
+    a.o.y = a.o.y * a1 + o2.y * a2;
+    a.o.z = a.o.z * a1 + o2.z * a2;
+    a.o.w = a.o.w * a1 + o2.w * a2;
+    a.m = mn;
+}
+
 // x[b] = tok[id] + pos[p]; the id is the prompt's while p is inside it, afterwards the id picked
 // by the previous step.  p is read from device memory so that one captured step serves all.
 __global__ void embed_kernel(const int *__restrict__ prompts, int n_prompt, const int *__restrict__ ids,
@@ -75,8 +92,9 @@ struct MatmulOut {
     int ldo;
     const float *res;
     float *q, *kc, *vc;          // non-null q selects the scatter
-    const int *pos_ptr;
+    const int *pos_ptr;          // position of the scatter, read from the device ...
     int cap, E;
+    int p_fixed;                 // ... or, when pos_ptr is NULL, given here
 };
 
 // y = relu?( LN?(A) * W + bias ) (+ res) for up to kRowsPerBlock rows.  A block owns 32 columns; its
@@ -88,22 +106,28 @@ struct MatmulOut {
 // the generation path follows the same order.)  With ln_g the rows are layer-normalised in
 // shared memory first (one warp per row; every block repeats it, which is cheaper than a launch).
 constexpr int kSeg = 16;
-__global__ void __launch_bounds__(32 * kSeg)
-matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict__ ln_g, const float *__restrict__ ln_b,
-                   const float *__restrict__ W, const float *__restrict__ bias, MatmulOut o, int M, int K, int N, int relu)
+// One block's share of the matmul: column block bx, row block by.  FUSED = called from the
+// persistent generation kernel, where the activations (A, the residual) were written earlier in
+// the same launch by other blocks: they are read past L1 (ld.global.cg), never through the
+// read-only path.
+template <bool FUSED>
+__device__ __forceinline__ void matmul_rows_body(int bx, int by, float *a_s, const float *A, int lda,
+                                                 const float *__restrict__ ln_g, const float *__restrict__ ln_b,
+                                                 const float *__restrict__ W, const float *__restrict__ bias, const MatmulOut &o,
+                                                 int M, int K, int N, int relu)
 {
-    extern __shared__ float a_s[];                 // [rows][K] activations, then [kSeg][rows][32] partial sums
-    const int m0 = blockIdx.y * kRowsPerBlock;
+    const int m0 = by * kRowsPerBlock;
     const int rows = min(kRowsPerBlock, M - m0);
-    float *part = a_s + kRowsPerBlock * K;
+    float *part = a_s + kRowsPerBlock * K;          // a_s: [rows][K] activations, then [kSeg][rows][32] partial sums
     const int seg = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < rows * K; i += blockDim.x) a_s[i] = A[(size_t)(m0 + i / K) * lda + i % K];
+    for (int i = threadIdx.x; i < rows * K; i += blockDim.x)
+        a_s[i] = FUSED ? __ldcg(A + (size_t)(m0 + i / K) * lda + i % K) : A[(size_t)(m0 + i / K) * lda + i % K];
     __syncthreads();
     if (ln_g) {
         if (seg < rows) layernorm_row(a_s + seg * K, ln_g, ln_b, K, lane);
         __syncthreads();
     }
-    const int n = blockIdx.x * 32 + lane;
+    const int n = bx * 32 + lane;
     const int klen = K / kSeg, k0 = seg * klen;
     float acc[kRowsPerBlock];
 #pragma unroll
@@ -141,15 +165,23 @@ matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict
         if (relu) v = fmaxf(0.0f, v);
         const int row = m0 + m;
         if (o.q) {
-            const int p = *o.pos_ptr;
+            const int p = o.pos_ptr ? *o.pos_ptr : o.p_fixed;
             if (n < o.E) o.q[(size_t)row * o.E + n] = v;
             else if (n < 2 * o.E) o.kc[((size_t)row * o.cap + p) * o.E + (n - o.E)] = v;
             else o.vc[((size_t)row * o.cap + p) * o.E + (n - 2 * o.E)] = v;
         } else {
-            if (o.res) v = __fadd_rn(o.res[(size_t)row * o.ldo + n], v);
+            if (o.res) v = __fadd_rn(FUSED ? __ldcg(o.res + (size_t)row * o.ldo + n) : o.res[(size_t)row * o.ldo + n], v);
             o.out[(size_t)row * o.ldo + n] = v;
         }
     }
+}
+
+__global__ void __launch_bounds__(32 * kSeg)
+matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict__ ln_g, const float *__restrict__ ln_b,
+                   const float *__restrict__ W, const float *__restrict__ bias, MatmulOut o, int M, int K, int N, int relu)
+{
+    extern __shared__ float a_s[];
+    matmul_rows_body<false>(blockIdx.x, blockIdx.y, a_s, A, lda, ln_g, ln_b, W, bias, o, M, K, N, relu);
 }
 
 // first maximum of each row (lowest index wins ties) -> ids_next[b]; recorded in out_ids once the
@@ -196,6 +228,303 @@ struct LayerW {
     const float *wqkv, *wo, *w1, *w2, *bqkv, *bo, *b1, *b2, *g1, *be1, *g2, *be2;
 };
 
+// ------------------------------------------------------------------------------------------------
+// The persistent form: ONE cooperative launch runs `nsteps` token positions.  A step of the graph
+// form is 52 launches of a few microseconds each; here the same phases (the same device
+// functions, the same arithmetic; the split of a (batch, head) that finishes last merges the
+// attention partials instead of a kernel of its own) follow one another inside the kernel,
+// separated by a barrier over the grid.  Measured on B200 at the default model, batch 8: 335 us
+// per step against 327 us of the replayed graph - a barrier over 148 blocks costs about what a
+// launch inside a graph costs, and the phases themselves (a few blocks each, chains of L2 round
+// trips) are the larger part of both.  Selectable (hipgpt_gpt_set_mode), not the default.  The grid is one
+// block per SM, co-resident by the cooperative launch.  The barrier is a counter and a
+// generation word in global memory; its wait is bounded: when it runs out, the block raises the
+// error word, every other block sees it in its own wait, and all of them return.
+struct FusedArgs {
+    const float *tok, *pos, *wout;
+    const LayerW *layers;            // device copy, L entries
+    int V, S, E, L, H, F;
+    float *kc, *vc;                  // [L][max_batch][S][E]
+    size_t layer_stride;             // floats between the caches of two layers
+    float *x, *q, *att, *ff, *logits, *scratch;
+    int *ids, *out_ids, *pos_ptr;
+    const int *prompts;
+    int B, n_prompt, n_new, nsteps, ns;
+    unsigned *bar;                   // [0] arrivals, [1] generation
+    unsigned *cnt;                   // [B*H] splits of a (batch, head) that have finished, zero between phases
+    int *err;
+};
+
+constexpr long long kBarrierLimitCycles = 4000000000LL;     // about two seconds
+
+__device__ __forceinline__ bool grid_barrier(const FusedArgs &a, unsigned &gen, int *ok_s)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        const unsigned target = gen + 1;
+        // the arrival releases this block's writes (the other threads' through the barrier above) and
+        // acquires those of the blocks that arrived before; the last one publishes the generation
+        unsigned old;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(a.bar) : "memory");
+        if (old == gridDim.x - 1) {
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(a.bar), "r"(0u) : "memory");
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.bar + 1), "r"(target) : "memory");
+        } else {
+            const long long t0 = clock64();
+            unsigned seen, spins = 0;
+            for (;;) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.bar + 1) : "memory");
+                if (seen == target) break;
+                if ((++spins & 63u) == 0u) {
+                    if (*reinterpret_cast<volatile int *>(a.err) != 0) { ok = 0; break; }
+                    if (clock64() - t0 > kBarrierLimitCycles) { atomicExch(a.err, 1); ok = 0; break; }
+                }
+            }
+        }
+        *ok_s = ok;
+    }
+    __syncthreads();
+    gen += 1;
+    return *ok_s != 0;
+}
+
+// the arithmetic of decode_split_vec_kernel<LPK> (attn_decode.cu) for four of its 128-thread
+// blocks at a time; q and the caches were written earlier in this launch and are read past L1
+template <int LPK>
+__device__ __forceinline__ void attn_split_phase(const FusedArgs &a, const float *kc, const float *vc, int ctx, float *sm)
+{
+    constexpr int KPW = 32 / LPK, W4 = 4;
+    const int H = a.H, E = a.E, D = E / H, cap = a.S, ns = a.ns;
+    const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
+    const int sub = threadIdx.x >> 7, t = threadIdx.x & 127, warp = t >> 5, lane = t & 31;
+    const int lik = lane % LPK, kg = lane / LPK;
+    const bool act = lik * 4 < D;
+    const int stride = ((D + 3) / 4) * 4 + 4;
+    float *smb = sm + sub * (W4 * LPK * 6);          // [warp][lik][6]
+    const int nvb = ns * a.B * H;
+    for (int vb0 = blockIdx.x * 4; vb0 < nvb; vb0 += gridDim.x * 4) {
+        const int vb = vb0 + sub;
+        const bool live = vb < nvb;
+        const int split = live ? vb % ns : 0, bh = live ? vb / ns : 0;
+        const int b = bh / H, h = bh % H;
+        const size_t col = (size_t)h * D + lik * 4;
+        const int per = (ctx + ns - 1) / ns;
+        const int k0 = split * per, k1 = min(ctx, k0 + per);
+        Partial4f acc{-1e30f, 0.0f, make_float4(0.f, 0.f, 0.f, 0.f)};
+        if (live) {
+            float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (act) {
+                q4 = __ldcg(reinterpret_cast<const float4 *>(a.q + (size_t)b * E + col));
+                q4.x *= qscale; q4.y *= qscale; q4.z *= qscale; q4.w *= qscale;
+            }
+            const int steps = (max(k1 - k0, 0) + W4 * KPW - 1) / (W4 * KPW);
+            for (int it = 0; it < steps; ++it) {
+                const int j = k0 + (it * W4 + warp) * KPW + kg;
+                const bool valid = j < k1;
+                float4 k4 = make_float4(0.f, 0.f, 0.f, 0.f), v4 = k4;
+                if (valid && act) {
+                    const size_t off = ((size_t)b * cap + j) * (size_t)E + col;
+                    k4 = __ldcg(reinterpret_cast<const float4 *>(kc + off));
+                    v4 = __ldcg(reinterpret_cast<const float4 *>(vc + off));
+                }
+                float s = q4.x * k4.x;
+                s = fmaf(q4.y, k4.y, s);
+                s = fmaf(q4.z, k4.z, s);
+                s = fmaf(q4.w, k4.w, s);
+#pragma unroll
+                for (int off = 1; off < LPK; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                if (!valid) s = -INFINITY;
+                const float mn = fmaxf(acc.m, s);
+                const float alpha = ex2_approx(acc.m - mn), pr = ex2_approx(s - mn);
+                acc.l = fmaf(acc.l, alpha, pr);
+                acc.o.x = fmaf(pr, v4.x, acc.o.x * alpha);
+                acc.o.y = fmaf(pr, v4.y, acc.o.y * alpha);
+                acc.o.z = fmaf(pr, v4.z, acc.o.z * alpha);
+                acc.o.w = fmaf(pr, v4.w, acc.o.w * alpha);
+                acc.m = mn;
+            }
+#pragma unroll
+            for (int off = LPK; off < 32; off <<= 1) {
+                const float m2 = __shfl_xor_sync(0xffffffffu, acc.m, off);
+                const float l2 = __shfl_xor_sync(0xffffffffu, acc.l, off);
+                float4 o2;
+                o2.x = __shfl_xor_sync(0xffffffffu, acc.o.x, off);
+                o2.y = __shfl_xor_sync(0xffffffffu, acc.o.y, off);
+                o2.z = __shfl_xor_sync(0xffffffffu, acc.o.z, off);
+                o2.w = __shfl_xor_sync(0xffffffffu, acc.o.w, off);
+                merge_partial(acc, m2, l2, o2);
+            }
+            if (kg == 0) {
+                float *r = smb + (warp * LPK + lik) * 6;
+                r[0] = acc.m; r[1] = acc.l; r[2] = acc.o.x; r[3] = acc.o.y; r[4] = acc.o.z; r[5] = acc.o.w;
+            }
+        }
+        __syncthreads();
+        if (live && warp == 0) {
+            if (lane < LPK) {
+                const float *r0 = smb + lane * 6;
+                Partial4f tt{r0[0], r0[1], make_float4(r0[2], r0[3], r0[4], r0[5])};
+#pragma unroll
+                for (int w = 1; w < W4; ++w) {
+                    const float *r = smb + (w * LPK + lane) * 6;
+                    merge_partial(tt, r[0], r[1], make_float4(r[2], r[3], r[4], r[5]));
+                }
+                if (lane * 4 < D) {
+                    if (ns == 1) {
+                        const float inv = 1.0f / fmaxf(tt.l, 1e-20f);
+                        *reinterpret_cast<float4 *>(a.att + (size_t)b * E + (size_t)h * D + lane * 4) =
+                            make_float4(tt.o.x * inv, tt.o.y * inv, tt.o.z * inv, tt.o.w * inv);
+                    } else {
+                        float *rec = a.scratch + ((size_t)bh * ns + split) * stride;
+                        *reinterpret_cast<float4 *>(rec + lane * 4) = tt.o;
+                        if (lane == 0) { rec[stride - 4] = tt.m; rec[stride - 3] = tt.l; }
+                    }
+                }
+            }
+            if (ns > 1) {
+                // the split that finishes last for this (batch, head) merges the ns records: what
+                // decode_combine_kernel (attn_decode.cu) computes, element d by lane d, d + 32, ...
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    unsigned old;
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(a.cnt + bh) : "memory");
+                    last = old == (unsigned)(ns - 1);
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    const float *rec = a.scratch + (size_t)bh * ns * stride;
+                    float M = -1e30f, L = 0.0f;
+                    if (ns <= 8) {                   // all loads of a pass in flight at once
+                        float ms[8], ls[8];
+#pragma unroll
+                        for (int s = 0; s < 8; ++s)
+                            if (s < ns) { ms[s] = __ldcg(rec + (size_t)s * stride + stride - 4); ls[s] = __ldcg(rec + (size_t)s * stride + stride - 3); }
+#pragma unroll
+                        for (int s = 0; s < 8; ++s) if (s < ns) M = fmaxf(M, ms[s]);
+#pragma unroll
+                        for (int s = 0; s < 8; ++s) if (s < ns) L += ls[s] * ex2_approx(ms[s] - M);
+                        const float inv = 1.0f / fmaxf(L, 1e-20f);
+                        for (int d = lane; d < D; d += 32) {
+                            float os[8];
+#pragma unroll
+                            for (int s = 0; s < 8; ++s) if (s < ns) os[s] = __ldcg(rec + (size_t)s * stride + d);
+                            float av = 0.0f;
+#pragma unroll
+                            for (int s = 0; s < 8; ++s) if (s < ns) av += os[s] * ex2_approx(ms[s] - M);
+                            a.att[(size_t)b * E + (size_t)h * D + d] = av * inv;
+                        }
+                    } else {
+                        for (int s = 0; s < ns; ++s) M = fmaxf(M, __ldcg(rec + (size_t)s * stride + stride - 4));
+                        for (int s = 0; s < ns; ++s)
+                            L += __ldcg(rec + (size_t)s * stride + stride - 3) * ex2_approx(__ldcg(rec + (size_t)s * stride + stride - 4) - M);
+                        const float inv = 1.0f / fmaxf(L, 1e-20f);
+                        for (int d = lane; d < D; d += 32) {
+                            float av = 0.0f;
+                            for (int s = 0; s < ns; ++s)
+                                av += __ldcg(rec + (size_t)s * stride + d) * ex2_approx(__ldcg(rec + (size_t)s * stride + stride - 4) - M);
+                            a.att[(size_t)b * E + (size_t)h * D + d] = av * inv;
+                        }
+                    }
+                    if (lane == 0) a.cnt[bh] = 0u;   // next used after a barrier over the grid
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+
+__global__ void __launch_bounds__(32 * kSeg, 1)
+gpt_steps_kernel(const FusedArgs a)
+{
+    extern __shared__ float dsm[];                   // the matmul's rows and partial sums; the other phases' scratch
+    __shared__ int ok_s;
+    const int B = a.B, E = a.E, F = a.F, V = a.V, D = a.E / a.H;
+    unsigned gen = *reinterpret_cast<volatile unsigned *>(a.bar + 1);   // read before this block's first arrival: cannot move yet
+    const int p0 = __ldcg(a.pos_ptr);
+    const int mrows = (B + kRowsPerBlock - 1) / kRowsPerBlock;
+    // one matmul phase: its blocks (column block, row block) are dealt out over the grid
+    auto matmul_phase = [&](const float *A, int lda, const float *ln_g, const float *ln_b, const float *W,
+                            const float *bias, const MatmulOut &o, int K, int N, int relu) {
+        const int nbx = (N + 31) / 32;
+        for (int vb = blockIdx.x; vb < nbx * mrows; vb += gridDim.x) {
+            matmul_rows_body<true>(vb % nbx, vb / nbx, dsm, A, lda, ln_g, ln_b, W, bias, o, B, K, N, relu);
+            __syncthreads();                         // the rows and partial sums are reused by the next block of work
+        }
+    };
+    for (int step = 0; step < a.nsteps; ++step) {
+        const int p = p0 + step;
+        // embedding: x[b] = tok[id] + pos[p]
+        for (int b = blockIdx.x; b < B; b += gridDim.x) {
+            const int id = p < a.n_prompt ? a.prompts[(size_t)b * a.n_prompt + p] : __ldcg(a.ids + b);
+            const bool ok = id >= 0 && id < V;
+            for (int e = threadIdx.x; e < E; e += blockDim.x)
+                a.x[(size_t)b * E + e] = ok ? __fadd_rn(a.tok[(size_t)id * E + e], a.pos[(size_t)p * E + e]) : 0.0f;
+        }
+        if (!grid_barrier(a, gen, &ok_s)) return;
+        for (int l = 0; l < a.L; ++l) {
+            const LayerW w = a.layers[l];
+            float *kc = a.kc + (size_t)l * a.layer_stride, *vc = a.vc + (size_t)l * a.layer_stride;
+            const MatmulOut scatter{nullptr, 0, nullptr, a.q, kc, vc, nullptr, a.S, E, p};
+            matmul_phase(a.x, E, w.g1, w.be1, w.wqkv, w.bqkv, scatter, E, 3 * E, 0);
+            if (!grid_barrier(a, gen, &ok_s)) return;
+            if (D <= 32) attn_split_phase<8>(a, kc, vc, p + 1, dsm);
+            else if (D <= 64) attn_split_phase<16>(a, kc, vc, p + 1, dsm);
+            else attn_split_phase<32>(a, kc, vc, p + 1, dsm);
+            if (!grid_barrier(a, gen, &ok_s)) return;
+            const MatmulOut to_x{a.x, E, a.x, nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
+            matmul_phase(a.att, E, nullptr, nullptr, w.wo, w.bo, to_x, E, E, 0);
+            if (!grid_barrier(a, gen, &ok_s)) return;
+            const MatmulOut to_ff{a.ff, F, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
+            matmul_phase(a.x, E, w.g2, w.be2, w.w1, w.b1, to_ff, E, F, 1);
+            if (!grid_barrier(a, gen, &ok_s)) return;
+            matmul_phase(a.ff, F, nullptr, nullptr, w.w2, w.b2, to_x, F, E, 0);
+            if (!grid_barrier(a, gen, &ok_s)) return;
+        }
+        const MatmulOut to_logits{a.logits, V, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
+        matmul_phase(a.x, E, nullptr, nullptr, a.wout, nullptr, to_logits, E, V, 0);
+        if (!grid_barrier(a, gen, &ok_s)) return;
+        // first maximum of each row of the logits (lowest index wins ties)
+        for (int b = blockIdx.x; b < B; b += gridDim.x) {
+            float *sv = dsm;
+            int *si = reinterpret_cast<int *>(dsm + blockDim.x);
+            const float *row = a.logits + (size_t)b * V;
+            float best = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int v = threadIdx.x; v < V; v += blockDim.x) {
+                const float xv = __ldcg(row + v);
+                if (xv > best || bi == 0x7fffffff) { best = xv; bi = v; }
+            }
+            sv[threadIdx.x] = best;
+            si[threadIdx.x] = bi;
+            __syncthreads();
+            for (int s2 = blockDim.x >> 1; s2 > 0; s2 >>= 1) {
+                if ((int)threadIdx.x < s2) {
+                    const float ov = sv[threadIdx.x + s2];
+                    const int oi = si[threadIdx.x + s2];
+                    if (oi != 0x7fffffff && (si[threadIdx.x] == 0x7fffffff || ov > sv[threadIdx.x] ||
+                                             (ov == sv[threadIdx.x] && oi < si[threadIdx.x]))) {
+                        sv[threadIdx.x] = ov;
+                        si[threadIdx.x] = oi;
+                    }
+                }
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) {
+                a.ids[b] = si[0];
+                const int col = p - (a.n_prompt - 1);
+                if (col >= 0 && col < a.n_new) a.out_ids[(size_t)b * a.n_new + col] = si[0];
+            }
+            __syncthreads();
+        }
+        if (!grid_barrier(a, gen, &ok_s)) return;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *a.pos_ptr = p0 + a.nsteps;
+}
+
 }  // namespace
 
 struct GptDecoder {
@@ -213,6 +542,14 @@ struct GptDecoder {
     // one step of generation captured as a CUDA graph; valid for (graph_B, graph_n_prompt, graph_n_new)
     cudaGraphExec_t graph = nullptr;
     int graph_B = 0, graph_n_prompt = 0, graph_n_new = 0;
+    // the persistent form (gpt_steps_kernel): device copy of the layer table, barrier words, error word
+    LayerW *d_layers = nullptr;
+    unsigned *d_bar = nullptr, *d_cnt = nullptr;
+    int *d_err = nullptr;
+    int mode = HIPGPT_GPT_MODE_GRAPH;                // measured: the persistent form is no faster (335 against 327 us per step)
+    bool persistent_ok = false;                      // head_dim, shared memory and co-residency allow it
+    int grid_blocks = 0;
+    size_t fused_smem = 0;
 };
 
 namespace {
@@ -239,7 +576,7 @@ int matmul(const GptDecoder &g, const float *A, int lda, const float *ln_g, cons
     return check_launch("matmul_rows_kernel");
 }
 
-MatmulOut plain_out(float *out, int ldo, const float *res) { return MatmulOut{out, ldo, res, nullptr, nullptr, nullptr, nullptr, 0, 0}; }
+MatmulOut plain_out(float *out, int ldo, const float *res) { return MatmulOut{out, ldo, res, nullptr, nullptr, nullptr, nullptr, 0, 0, 0}; }
 
 // One token position for all B sequences, every launch reading the position from g.d_pos: embed,
 // L x {LN+QKV projection scattered into q and the caches, split-context attention, output
@@ -255,7 +592,7 @@ int enqueue_step(GptDecoder &g, int B, int n_prompt, int n_new)
         const LayerW &w = g.lw[l];
         float *kc = g.d_kc + (size_t)l * g.max_batch * g.S * E;
         float *vc = g.d_vc + (size_t)l * g.max_batch * g.S * E;
-        const MatmulOut scatter{nullptr, 0, nullptr, g.d_q, kc, vc, g.d_pos, g.S, E};
+        const MatmulOut scatter{nullptr, 0, nullptr, g.d_q, kc, vc, g.d_pos, g.S, E, 0};
         if ((rc = matmul(g, g.d_x, E, w.g1, w.be1, w.wqkv, w.bqkv, scatter, B, E, 3 * E, 0))) return rc;
         if ((rc = launch_decode(g.d_q, kc, vc, g.d_att, g.d_scratch, B, g.H, D, 1, g.S, ns, g.stream, g.d_pos))) return rc;
         if ((rc = matmul(g, g.d_att, E, nullptr, nullptr, w.wo, w.bo, plain_out(g.d_x, E, g.d_x), B, E, E, 0))) return rc;
@@ -354,6 +691,28 @@ int hipgpt_gpt_create(hipgpt_gpt **out, const float *h_weights, int V, int S, in
         const int need = kRowsPerBlock * ((E > F ? E : F) + kSeg * 32) * (int)sizeof(float);   // activation rows of the widest matmul + partial sums
         if (need > 48 * 1024) TRY(cudaFuncSetAttribute(matmul_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, need));
     }
+    {
+        // the persistent kernel: one block per SM, all resident at once (checked here, enforced by the cooperative launch)
+        const int D = E / H;
+        int dev = 0, sms = 0, coop = 0, per_sm = 0;
+        TRY(cudaGetDevice(&dev));
+        TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+        g->fused_smem = (size_t)kRowsPerBlock * ((E > F ? E : F) + kSeg * 32) * sizeof(float);
+        if (g->fused_smem < 16 * 1024) g->fused_smem = 16 * 1024;      // the attention and first-maximum phases' scratch
+        TRY(cudaFuncSetAttribute(gpt_steps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g->fused_smem));
+        TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gpt_steps_kernel, 32 * kSeg, g->fused_smem));
+        g->persistent_ok = coop && per_sm >= 1 && D % 4 == 0 && D <= 128;
+        g->grid_blocks = sms;
+        TRY(cudaMalloc(&g->d_layers, (size_t)L * sizeof(LayerW)));
+        TRY(cudaMemcpyAsync(g->d_layers, g->lw.data(), (size_t)L * sizeof(LayerW), cudaMemcpyHostToDevice, g->stream));
+        TRY(cudaMalloc(&g->d_bar, 2 * sizeof(unsigned)));
+        TRY(cudaMemsetAsync(g->d_bar, 0, 2 * sizeof(unsigned), g->stream));
+        TRY(cudaMalloc(&g->d_cnt, (size_t)max_batch * H * sizeof(unsigned)));
+        TRY(cudaMemsetAsync(g->d_cnt, 0, (size_t)max_batch * H * sizeof(unsigned), g->stream));
+        TRY(cudaMalloc(&g->d_err, sizeof(int)));
+        TRY(cudaMemsetAsync(g->d_err, 0, sizeof(int), g->stream));
+    }
     TRY(cudaStreamSynchronize(g->stream));
 #undef TRY
     *out = reinterpret_cast<hipgpt_gpt *>(g);
@@ -381,21 +740,49 @@ int hipgpt_gpt_generate(hipgpt_gpt *handle, const int *h_prompts, int B, int n_p
         CUDA_OK(cudaMalloc(&g->d_prompts, (size_t)B * n_prompt * sizeof(int)));
         g->prompt_cap = B * n_prompt;
     }
-    int rc = build_graph(*g, B, n_prompt, n_new);
+    const bool persistent = g->mode == HIPGPT_GPT_MODE_PERSISTENT && g->persistent_ok;
+    int rc = persistent ? HIPGPT_OK : build_graph(*g, B, n_prompt, n_new);
     if (rc != HIPGPT_OK) return rc;
     CUDA_OK(cudaMemcpyAsync(g->d_prompts, h_prompts, (size_t)B * n_prompt * sizeof(int), cudaMemcpyHostToDevice, g->stream));
     CUDA_OK(cudaMemsetAsync(g->d_pos, 0, sizeof(int), g->stream));
     cudaEvent_t e0, e1, e2;
     CUDA_OK(cudaEventCreate(&e0)); CUDA_OK(cudaEventCreate(&e1)); CUDA_OK(cudaEventCreate(&e2));
     CUDA_OK(cudaEventRecord(e0, g->stream));
-    for (int p = 0; p < n_prompt; ++p) CUDA_OK(cudaGraphLaunch(g->graph, g->stream));
-    CUDA_OK(cudaEventRecord(e1, g->stream));
-    for (int i = 1; i < n_new; ++i) CUDA_OK(cudaGraphLaunch(g->graph, g->stream));
+    if (persistent) {
+        FusedArgs a{};
+        a.tok = g->tok; a.pos = g->pos; a.wout = g->wout; a.layers = g->d_layers;
+        a.V = g->V; a.S = g->S; a.E = g->E; a.L = g->L; a.H = g->H; a.F = g->F;
+        a.kc = g->d_kc; a.vc = g->d_vc; a.layer_stride = (size_t)g->max_batch * g->S * g->E;
+        a.x = g->d_x; a.q = g->d_q; a.att = g->d_att; a.ff = g->d_ff; a.logits = g->d_logits; a.scratch = g->d_scratch;
+        a.ids = g->d_ids; a.out_ids = g->d_out; a.pos_ptr = g->d_pos; a.prompts = g->d_prompts;
+        a.B = B; a.n_prompt = n_prompt; a.n_new = n_new; a.ns = decode_splits(B, g->H, g->E / g->H, g->S);
+        a.bar = g->d_bar; a.cnt = g->d_cnt; a.err = g->d_err;
+        void *params[] = {&a};
+        a.nsteps = n_prompt;                         // the prompt positions, then the remaining new tokens
+        CUDA_OK(cudaLaunchCooperativeKernel((const void *)gpt_steps_kernel, dim3(g->grid_blocks), dim3(32 * kSeg), params, g->fused_smem, g->stream));
+        CUDA_OK(cudaEventRecord(e1, g->stream));
+        a.nsteps = n_new - 1;
+        if (a.nsteps > 0)
+            CUDA_OK(cudaLaunchCooperativeKernel((const void *)gpt_steps_kernel, dim3(g->grid_blocks), dim3(32 * kSeg), params, g->fused_smem, g->stream));
+    } else {
+        for (int p = 0; p < n_prompt; ++p) CUDA_OK(cudaGraphLaunch(g->graph, g->stream));
+        CUDA_OK(cudaEventRecord(e1, g->stream));
+        for (int i = 1; i < n_new; ++i) CUDA_OK(cudaGraphLaunch(g->graph, g->stream));
+    }
     CUDA_OK(cudaEventRecord(e2, g->stream));
     CUDA_OK(cudaMemcpyAsync(h_out_ids, g->d_out, (size_t)B * n_new * sizeof(int), cudaMemcpyDeviceToHost, g->stream));
     if (h_logits_last)
         CUDA_OK(cudaMemcpyAsync(h_logits_last, g->d_logits, (size_t)B * g->V * sizeof(float), cudaMemcpyDeviceToHost, g->stream));
+    int h_err = 0;
+    if (persistent) CUDA_OK(cudaMemcpyAsync(&h_err, g->d_err, sizeof(int), cudaMemcpyDeviceToHost, g->stream));
     CUDA_OK(cudaStreamSynchronize(g->stream));
+    if (h_err) {
+        cudaMemsetAsync(g->d_err, 0, sizeof(int), g->stream);
+        cudaMemsetAsync(g->d_bar, 0, 2 * sizeof(unsigned), g->stream);
+        cudaMemsetAsync(g->d_cnt, 0, (size_t)g->max_batch * g->H * sizeof(unsigned), g->stream);
+        cudaStreamSynchronize(g->stream);
+        rc = fail(HIPGPT_ERR_CUDA, "persistent generation kernel: a wait at the grid barrier ran out");
+    }
     float a = 0.f, b = 0.f;
     cudaEventElapsedTime(&a, e0, e1);
     cudaEventElapsedTime(&b, e1, e2);
@@ -403,6 +790,17 @@ int hipgpt_gpt_generate(hipgpt_gpt *handle, const int *h_prompts, int B, int n_p
     if (ms_decode) *ms_decode = b;
     cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
     return rc;
+}
+
+int hipgpt_gpt_set_mode(hipgpt_gpt *handle, int mode)
+{
+    GptDecoder *g = reinterpret_cast<GptDecoder *>(handle);
+    if (!g) return fail(HIPGPT_ERR_NULL, "handle must not be NULL");
+    if (mode != HIPGPT_GPT_MODE_PERSISTENT && mode != HIPGPT_GPT_MODE_GRAPH) return fail(HIPGPT_ERR_BAD_ARG, "unknown mode %d", mode);
+    if (mode == HIPGPT_GPT_MODE_PERSISTENT && !g->persistent_ok)
+        return fail(HIPGPT_ERR_UNSUPPORTED, "persistent form needs head_dim %% 4 == 0, head_dim <= 128 and cooperative launch");
+    g->mode = mode;
+    return HIPGPT_OK;
 }
 
 void hipgpt_gpt_destroy(hipgpt_gpt *handle)
@@ -416,6 +814,10 @@ void hipgpt_gpt_destroy(hipgpt_gpt *handle)
     if (g->d_out) cudaFree(g->d_out);
     if (g->d_pos) cudaFree(g->d_pos);
     if (g->d_prompts) cudaFree(g->d_prompts);
+    if (g->d_layers) cudaFree(g->d_layers);
+    if (g->d_bar) cudaFree(g->d_bar);
+    if (g->d_cnt) cudaFree(g->d_cnt);
+    if (g->d_err) cudaFree(g->d_err);
     if (g->stream) cudaStreamDestroy(g->stream);
     delete g;
 }

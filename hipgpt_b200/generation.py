@@ -10,8 +10,13 @@ import numpy as np
 from . import _capi
 
 
+MODE_GRAPH = 0          # one step = a CUDA graph of 52 launches, replayed per token (default)
+MODE_PERSISTENT = 1     # one cooperative launch for a run of token steps, phases separated by a barrier over the grid
+
+
 class GptDecoder:
-    def __init__(self, weights: np.ndarray, V: int, S: int, E: int, L: int, H: int, F: int, max_batch: int = 8):
+    def __init__(self, weights: np.ndarray, V: int, S: int, E: int, L: int, H: int, F: int, max_batch: int = 8,
+                 mode: int | None = None):
         lib = _capi.lib()
         need = int(lib.hipgpt_gpt_weight_count(V, S, E, L, H, F))
         weights = np.ascontiguousarray(weights, dtype=np.float32)
@@ -20,6 +25,11 @@ class GptDecoder:
         self.shape = (V, S, E, L, H, F)
         self._h = C.c_void_p()
         _capi.check(lib.hipgpt_gpt_create(C.byref(self._h), weights.ctypes.data, V, S, E, L, H, F, max_batch))
+        if mode is not None:
+            self.set_mode(mode)
+
+    def set_mode(self, mode: int):
+        _capi.check(_capi.lib().hipgpt_gpt_set_mode(self._h, int(mode)))
 
     def generate(self, prompts: np.ndarray, n_new: int):
         """prompts [B, n_prompt] int32 -> (ids [B, n_new], logits of the last step [B, V],

@@ -173,6 +173,19 @@ HIPGPT_API int hipgpt_gpt_create(hipgpt_gpt **out, const float *h_weights, int V
 HIPGPT_API int hipgpt_gpt_generate(hipgpt_gpt *g, const int *h_prompts, int B, int n_prompt, int n_new, int *h_out_ids,
                         float *h_logits_last, float *ms_prompt, float *ms_decode);
 HIPGPT_API void hipgpt_gpt_destroy(hipgpt_gpt *g);
+/*
+ * Two forms of the same token step, same arithmetic and the same ids (extension, like the driver itself):
+ *   HIPGPT_GPT_MODE_GRAPH (default): one step = 52 kernel launches captured once as a CUDA graph and replayed
+ *     per token.
+ *   HIPGPT_GPT_MODE_PERSISTENT (head_dim % 4 == 0 and head_dim <= 128): one cooperative launch runs all
+ *     prompt positions, a second one the remaining tokens; the phases of a step follow one another inside the
+ *     kernel, separated by a bounded barrier over the grid (one block per SM).  If a wait at that barrier runs
+ *     out, hipgpt_gpt_generate returns HIPGPT_ERR_CUDA and the handle stays usable.  Measured no faster than the
+ *     graph on B200 (335 against 327 us per step of 8 tokens).
+ */
+#define HIPGPT_GPT_MODE_GRAPH 0
+#define HIPGPT_GPT_MODE_PERSISTENT 1
+HIPGPT_API int hipgpt_gpt_set_mode(hipgpt_gpt *g, int mode);
 
 /*
  * Batch-major sharding of the (batch x head) space over the GPUs of one box: rank r of

@@ -73,10 +73,11 @@ def test_oracle_rejects_requests_past_the_position_table():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["persistent", "graph"])
 @pytest.mark.parametrize("shape", ["tiny", "default"])
-def test_gpu_generation_ids_equal_the_oracle(shape):
+def test_gpu_generation_ids_equal_the_oracle(shape, mode):
     pytest.importorskip("torch")
-    from hipgpt_b200.generation import GptDecoder
+    from hipgpt_b200 import generation
     if shape == "tiny":
         cfg, B, n_prompt, n_new, seed = dict(V=50, S=24, E=32, L=2, H=4, F=64), 3, 5, 12, 9
     else:
@@ -84,7 +85,8 @@ def test_gpu_generation_ids_equal_the_oracle(shape):
     w = synth.gpt_weights(seed, **cfg)
     prompts = synth.token_ids(seed, (B, n_prompt), cfg["V"])
     ref_ids, ref_logits = ob.gpt_generate(w, **cfg, prompts=prompts, n_new=n_new, fma=True)
-    dec = GptDecoder(w, **cfg, max_batch=B)
+    dec = generation.GptDecoder(w, **cfg, max_batch=B,
+                                mode=generation.MODE_PERSISTENT if mode == "persistent" else generation.MODE_GRAPH)
     ids, logits, ms_prompt, ms_decode = dec.generate(prompts, n_new)
     dec.close()
     if not np.array_equal(ids, ref_ids):
@@ -92,3 +94,27 @@ def test_gpu_generation_ids_equal_the_oracle(shape):
         pytest.fail(f"first differing id at prompt {b}, step {i}: gpu {ids[b, i]} oracle {ref_ids[b, i]}")
     assert float(np.abs(logits - ref_logits).max()) <= 1e-4
     assert ms_prompt > 0 and ms_decode > 0
+
+
+@pytest.mark.gpu
+def test_gpu_generation_forms_agree_and_a_handle_serves_many_requests():
+    """The persistent kernel and the replayed graph run the same arithmetic; one handle answers
+    requests of different batch sizes and lengths in either form, in any order (the grid barrier's
+    generation word and the position word carry over from call to call)."""
+    pytest.importorskip("torch")
+    from hipgpt_b200 import generation
+    cfg = dict(V=300, S=48, E=64, L=3, H=2, F=128)          # head_dim 32
+    w = synth.gpt_weights(21, **cfg)
+    dec = generation.GptDecoder(w, **cfg, max_batch=5)
+    for B, n_prompt, n_new in [(5, 4, 20), (2, 7, 1), (1, 1, 48), (3, 10, 30)]:
+        prompts = synth.token_ids(100 + B, (B, n_prompt), cfg["V"])
+        ref_ids, ref_logits = ob.gpt_generate(w, **cfg, prompts=prompts, n_new=n_new, fma=True)
+        got = {}
+        for mode in (generation.MODE_PERSISTENT, generation.MODE_GRAPH, generation.MODE_PERSISTENT):
+            dec.set_mode(mode)
+            ids, logits, _, _ = dec.generate(prompts, n_new)
+            assert np.array_equal(ids, ref_ids)
+            assert float(np.abs(logits - ref_logits).max()) <= 1e-4
+            got[mode] = logits
+        assert float(np.abs(got[generation.MODE_PERSISTENT] - got[generation.MODE_GRAPH]).max()) <= 1e-5
+    dec.close()
