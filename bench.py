@@ -416,15 +416,19 @@ def run_ours(args):
             "gpu_launches": args.steps * sets}
 
     # end to end through the host-buffer entry point: pinned host memory in, host memory out
-    if not args.no_e2e and not bf16:                       # the host-buffer entry point is fp32 only
-        h_out = torch.empty((B * S, E), dtype=torch.float32).pin_memory()
+    if not args.no_e2e:
+        h_e2e = h_in.to(tdtype).pin_memory() if bf16 else h_in      # bf16: the planes as the caller would hold them
+        h_out = torch.empty((B * S, E), dtype=tdtype).pin_memory()
         h_probs = torch.empty((B, H, S, S), dtype=torch.float32).pin_memory() if args.probs else None
         e2e_steps = max(1, min(args.steps, 20))
 
         def e2e_step():
             for s in range(sets):
-                rc = lib.hipgpt_mha_forward_host(h_in[s].data_ptr(), h_out.data_ptr(),
-                                                 h_probs.data_ptr() if args.probs else None, B, S, E, H, args.causal)
+                if bf16:
+                    rc = lib.hipgpt_mha_forward_bf16_host(h_e2e[s].data_ptr(), h_out.data_ptr(), B, S, E, H, args.causal)
+                else:
+                    rc = lib.hipgpt_mha_forward_host(h_e2e[s].data_ptr(), h_out.data_ptr(),
+                                                     h_probs.data_ptr() if args.probs else None, B, S, E, H, args.causal)
                 if rc:
                     _capi.check(rc)
         for _ in range(3):
@@ -441,10 +445,10 @@ def run_ours(args):
             dt = float(t.item())
         line["e2e"] = {"value": (flops_of(B_total, H, S, D, args.causal) * sets if (args.strong and world > 1) else world * flops_step) * e2e_steps / dt / 1e12,
                        "unit": "TFLOP/s",
-                       "h2d_bytes_per_step": int(sets * 3 * plane * 4),
-                       "d2h_bytes_per_step": int(sets * (plane * 4 + (B * H * S * S * 4 if args.probs else 0))),
+                       "h2d_bytes_per_step": int(sets * 3 * plane * esz),
+                       "d2h_bytes_per_step": int(sets * (plane * esz + (B * H * S * S * 4 if args.probs else 0))),
                        "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps,
-                       "api": "hipgpt_mha_forward_host (C ABI, host pointers)"}
+                       "api": ("hipgpt_mha_forward_bf16_host" if bf16 else "hipgpt_mha_forward_host") + " (C ABI, host pointers)"}
         lib.hipgpt_release_workspace()
 
     if rank == 0 and world == 1 and not args.no_cpu:

@@ -23,6 +23,7 @@ SIGNATURES = {
     "hipgpt_mha_forward_planes": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_forward_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_forward_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i]),
+    "hipgpt_mha_forward_bf16_host": (_i, [_vp, _vp, _i, _i, _i, _i, _i]),
     "hipgpt_release_workspace": (None, []),
     "hipgpt_scaled_dot_product": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "hipgpt_softmax": (_i, [_vp, _vp, _i, _i, _vp]),

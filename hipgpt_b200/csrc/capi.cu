@@ -145,14 +145,19 @@ int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const void *d_v, v
     return launch_mha_bf16(d_q, d_k, d_v, d_out, B, S, E, H, causal, static_cast<cudaStream_t>(stream));
 }
 
-int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
-                            int B, int S, int E, int H, int causal)
+// Host buffers in, host buffers out, for planes of `esz`-byte elements (4: fp32, 2: bf16; the
+// probabilities exist in the fp32 form only).
+static int mha_forward_host_impl(const void *h_qkv_v, void *h_out_v, float *h_probs,
+                                 int B, int S, int E, int H, int causal, size_t esz)
 {
+    const uint8_t *h_qkv = static_cast<const uint8_t *>(h_qkv_v);
+    uint8_t *h_out = static_cast<uint8_t *>(h_out_v);
     const int rc = check_mha_args(h_qkv, h_qkv, h_qkv, h_out, B, S, E, H);
     if (rc != HIPGPT_OK) return rc > 0 ? HIPGPT_OK : rc;
-    const size_t plane = (size_t)B * S * E;
+    if (esz == 2 && E / H != 64) return fail(HIPGPT_ERR_UNSUPPORTED, "bf16 tensor-core kernel: head_dim %d is not 64", E / H);
+    const size_t plane = (size_t)B * S * E * esz;    // bytes of one plane
     const size_t nprobs = h_probs ? (size_t)B * H * S * S : 0;
-    const size_t need = (4 * plane + nprobs) * sizeof(float);
+    const size_t need = 4 * plane + nprobs * sizeof(float);
     std::lock_guard<std::mutex> lock(g_ws.mu);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -187,33 +192,36 @@ int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
     // streams: host-to-device copies, kernels, device-to-host copies.  PCIe moves both directions
     // at once, so the call takes about as long as its larger direction alone.
     cudaStream_t s_in = g_ws.streams[0], s_k = g_ws.streams[1], s_out = g_ws.streams[2];
-    float *d_qkv = g_ws.dev, *d_out = g_ws.dev + 3 * plane, *d_probs = h_probs ? g_ws.dev + 4 * plane : nullptr;
-    int nchunks = (int)((3 * plane * sizeof(float)) / Workspace::kChunkBytes);
+    uint8_t *d_qkv = reinterpret_cast<uint8_t *>(g_ws.dev), *d_out = d_qkv + 3 * plane;
+    float *d_probs = h_probs ? reinterpret_cast<float *>(d_qkv + 4 * plane) : nullptr;
+    int nchunks = (int)((3 * plane) / Workspace::kChunkBytes);
     nchunks = nchunks < 1 ? 1 : nchunks > Workspace::kChunks ? Workspace::kChunks : nchunks;
     if (nchunks > B) nchunks = B;
     // the three planes' slabs of a chunk go up as one strided copy (three rows one plane apart) where the
     // pitch limit of such copies allows it
-    const bool strided = plane * sizeof(float) <= (size_t)0x7fffffff;
+    const bool strided = plane <= (size_t)0x7fffffff;
     for (int c = 0; c < nchunks; ++c) {
         int b0, b1;
         hipgpt_shard_range(B, nchunks, c, &b0, &b1);
-        const size_t off = (size_t)b0 * S * E, cnt = (size_t)(b1 - b0) * S * E;
+        const size_t off = (size_t)b0 * S * E * esz, cnt = (size_t)(b1 - b0) * S * E * esz;   // bytes
         if (strided)
-            e = cudaMemcpy2DAsync(d_qkv + off, plane * sizeof(float), h_qkv + off, plane * sizeof(float), cnt * sizeof(float), 3,
-                                  cudaMemcpyHostToDevice, s_in);
+            e = cudaMemcpy2DAsync(d_qkv + off, plane, h_qkv + off, plane, cnt, 3, cudaMemcpyHostToDevice, s_in);
         else
             for (int pl = 0; pl < 3 && e == cudaSuccess; ++pl)
-                e = cudaMemcpyAsync(d_qkv + pl * plane + off, h_qkv + pl * plane + off, cnt * sizeof(float), cudaMemcpyHostToDevice, s_in);
+                e = cudaMemcpyAsync(d_qkv + pl * plane + off, h_qkv + pl * plane + off, cnt, cudaMemcpyHostToDevice, s_in);
         if (e == cudaSuccess) e = cudaEventRecord(g_ws.in_ready[c], s_in);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(s_k, g_ws.in_ready[c], 0);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to device: %s", cudaGetErrorString(e));
         float *pr = d_probs ? d_probs + (size_t)b0 * H * S * S : nullptr;
-        const int krc = mha_dispatch(d_qkv + off, d_qkv + plane + off, d_qkv + 2 * plane + off, d_out + off, pr,
-                                     b1 - b0, S, E, H, causal, HIPGPT_ALGO_AUTO, 0, s_k);
+        const int krc = esz == 2
+            ? launch_mha_bf16(d_qkv + off, d_qkv + plane + off, d_qkv + 2 * plane + off, d_out + off, b1 - b0, S, E, H, causal, s_k)
+            : mha_dispatch(reinterpret_cast<const float *>(d_qkv + off), reinterpret_cast<const float *>(d_qkv + plane + off),
+                           reinterpret_cast<const float *>(d_qkv + 2 * plane + off), reinterpret_cast<float *>(d_out + off), pr,
+                           b1 - b0, S, E, H, causal, HIPGPT_ALGO_AUTO, 0, s_k);
         if (krc != HIPGPT_OK) { cudaDeviceSynchronize(); return krc; }
         e = cudaEventRecord(g_ws.out_ready[c], s_k);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(s_out, g_ws.out_ready[c], 0);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(h_out + off, d_out + off, cnt * sizeof(float), cudaMemcpyDeviceToHost, s_out);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_out + off, d_out + off, cnt, cudaMemcpyDeviceToHost, s_out);
         if (e == cudaSuccess && h_probs)
             e = cudaMemcpyAsync(h_probs + (size_t)b0 * H * S * S, pr, (size_t)(b1 - b0) * H * S * S * sizeof(float), cudaMemcpyDeviceToHost, s_out);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "copy to host: %s", cudaGetErrorString(e));
@@ -221,6 +229,17 @@ int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
     e = cudaStreamSynchronize(s_out);                // its last copy waits for the last kernel, which waits for the last copy in
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "host-buffer call: %s", cudaGetErrorString(e));
     return HIPGPT_OK;
+}
+
+int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
+                            int B, int S, int E, int H, int causal)
+{
+    return mha_forward_host_impl(h_qkv, h_out, h_probs, B, S, E, H, causal, sizeof(float));
+}
+
+int hipgpt_mha_forward_bf16_host(const void *h_qkv, void *h_out, int B, int S, int E, int H, int causal)
+{
+    return mha_forward_host_impl(h_qkv, h_out, nullptr, B, S, E, H, causal, 2);
 }
 
 void hipgpt_release_workspace(void)

@@ -88,3 +88,12 @@ def mha_forward_host(h_qkv, h_out, h_probs, B: int, S: int, E: int, H: int, *, c
         assert a.dtype.name == "float32" and a.flags["C_CONTIGUOUS"]
         return a.ctypes.data
     _capi.check(_capi.lib().hipgpt_mha_forward_host(hp(h_qkv), hp(h_out), hp(h_probs), B, S, E, H, int(causal)))
+
+
+def mha_forward_bf16_host(h_qkv, h_out, B: int, S: int, E: int, H: int, *, causal: bool = False):
+    """The host-buffer call for bf16 planes: CPU torch.bfloat16 tensors (ideally pinned), h_qkv three
+    stacked [B*S, E] planes, h_out [B*S, E]; head_dim 64."""
+    for t in (h_qkv, h_out):
+        if not (isinstance(t, torch.Tensor) and not t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
+            raise ValueError("expected a contiguous CPU bfloat16 tensor")
+    _capi.check(_capi.lib().hipgpt_mha_forward_bf16_host(h_qkv.data_ptr(), h_out.data_ptr(), B, S, E, H, int(causal)))

@@ -104,6 +104,9 @@ HIPGPT_API int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const v
  * hipgpt_release_workspace().  Pinned host memory makes the copies asynchronous. */
 HIPGPT_API int hipgpt_mha_forward_host(const float *h_qkv, float *h_out, float *h_probs,
                             int B, int S, int E, int H, int causal);
+/* The host-buffer call for bf16 planes (hipgpt_mha_forward_bf16's contract: h_qkv = three stacked
+ * [B*S][E] bf16 planes, h_out [B*S][E] bf16, head_dim 64, no probabilities); same workspace. */
+HIPGPT_API int hipgpt_mha_forward_bf16_host(const void *h_qkv, void *h_out, int B, int S, int E, int H, int causal);
 HIPGPT_API void hipgpt_release_workspace(void);
 
 /*

@@ -87,3 +87,27 @@ def test_bf16_rejects_other_head_dims_and_bad_configs():
     assert lib.hipgpt_mha_forward_bf16(x.data_ptr(), x.data_ptr(), x.data_ptr(), o.data_ptr(), 1, 64, 96, 5, 0, None) == _capi.ERR_BAD_ARG
     assert lib.hipgpt_mha_forward_bf16(None, x.data_ptr(), x.data_ptr(), o.data_ptr(), 1, 64, 64, 1, 0, None) == _capi.ERR_NULL
     assert lib.hipgpt_mha_forward_bf16(x.data_ptr(), x.data_ptr(), x.data_ptr(), o.data_ptr(), 0, 64, 64, 1, 0, None) == 0      # nothing to do
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 7, 64), (3, 2, 300, 64), (16, 4, 512, 64)])
+@pytest.mark.parametrize("pinned", [False, True])
+def test_bf16_host_buffer_call_equals_the_device_call(shape, pinned):
+    """hipgpt_mha_forward_bf16_host copies, runs the same kernel on chunks of batches and copies
+    back: its output bits are those of the device-pointer call."""
+    B, H, S, D = shape
+    E = H * D
+    h_qkv = torch.from_numpy(synth.qkv_planes(4000 + S, B, S, E).reshape(3, B * S, E)).bfloat16()
+    h_out = torch.full((B * S, E), float("nan"), dtype=torch.bfloat16)
+    if pinned:
+        h_qkv, h_out = h_qkv.pin_memory(), h_out.pin_memory()
+    for causal in (False, True):
+        launchers.mha_forward_bf16_host(h_qkv, h_out, B, S, E, H, causal=causal)
+        d_out = torch.empty((B * S, E), dtype=torch.bfloat16, device="cuda")
+        launchers.mha_forward_bf16(h_qkv.cuda(), d_out, B, S, E, H, causal=causal)
+        torch.cuda.synchronize()
+        assert _status() == 0
+        assert torch.equal(h_out, d_out.cpu())
+    _capi.lib().hipgpt_release_workspace()
+    # head_dim other than 64 is refused
+    bad = torch.zeros((3, 64, 96), dtype=torch.bfloat16)
+    assert _capi.lib().hipgpt_mha_forward_bf16_host(bad.data_ptr(), bad.data_ptr(), 1, 64, 96, 3, 0) == _capi.ERR_UNSUPPORTED
