@@ -210,7 +210,8 @@ def run_reference(args):
     line = {"impl": "reference", "metric": "causal_attn_fwd_tflops", "value": tf, "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": info["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args, cfg, 1),
+            "config": dict(workload_config(args, cfg, 1), l2="host cores: inputs in host memory, no GPU cache involved",
+                           parallelism="rank 0 only, all host threads"),
             "cpu_baseline": info,
             "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
