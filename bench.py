@@ -69,6 +69,7 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="run only the greedy-generation leg and print its JSON")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--bf16-variant", type=int, default=0, help="--dtype bf16: 0 default, 1 one worker per query row, 2 two workers")
     return ap.parse_args()
 
 
@@ -298,7 +299,7 @@ def run_ours(args):
     probs_ptr = d_probs.data_ptr() if args.probs else None
     if bf16:
         def fwd(q, k, v, out, probs, B_, S_, E_, H_, causal, st_):
-            return lib.hipgpt_mha_forward_bf16(q, k, v, out, B_, S_, E_, H_, causal, st_)
+            return lib.hipgpt_mha_forward_bf16_ex(q, k, v, out, B_, S_, E_, H_, causal, args.bf16_variant, st_)
     else:
         fwd = lib.hipgpt_mha_forward
 

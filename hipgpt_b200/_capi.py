@@ -22,6 +22,7 @@ SIGNATURES = {
     "hipgpt_mha_forward_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_forward_planes": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_forward_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_mha_forward_bf16_ex": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_forward_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "hipgpt_mha_forward_bf16_host": (_i, [_vp, _vp, _i, _i, _i, _i, _i]),
     "hipgpt_release_workspace": (None, []),

@@ -49,7 +49,8 @@ int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, 
                     int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_tc16_supports(int head_dim);
 int tc16_status_fetch(int *status);
-int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st);
+int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st,
+                    int variant = 0);
 bool mha_bf16_supports(int D);
 int bf16_status_fetch(int *status);
 int launch_mha_generic(const float *q, const float *k, const float *v, float *out, float *probs,

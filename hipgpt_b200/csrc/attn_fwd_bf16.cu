@@ -30,9 +30,13 @@ namespace {
 
 constexpr int kRows = 128;        // query rows per block
 constexpr int kKeys = 64;         // keys per tile
-constexpr int kWorkers = kRows;
-constexpr int kThreads = kWorkers + 32 + 64;     // workers, the issuing warp, the K warp, the V warp
+// WPR = workers per query row: 1 (a worker owns the 64 scores of its row) or 2 (two workers, in warps w and
+// w + 4 that share a TMEM lane quadrant, own 32 scores each and exchange the row maximum through shared
+// memory once per tile): twice the warps to hide the latencies of the softmax behind.
+template <int WPR> __host__ __device__ constexpr int workers_of() { return kRows * WPR; }
+template <int WPR> __host__ __device__ constexpr int threads_of() { return workers_of<WPR>() + 32 + 64; }     // workers, the issuing warp, the K warp, the V warp
 constexpr int kStages = 4;        // K and V tiles in flight
+constexpr int kDefaultWorkersPerRow = 1;
 constexpr float kRescaleStep = 8.0f;     // log2 of the growth of a row maximum that forces a rescale
 constexpr uint32_t kColX = 0, kColO = 128, kTmemCols = 256;
 
@@ -79,12 +83,15 @@ struct Bf16Cfg {
     static constexpr size_t kSmemBytes = (size_t)kQBytes + 2 * kStages * kTileBytes;
 };
 
-template <int D, bool CAUSAL>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int D, bool CAUSAL, int WPR>
+__global__ void __launch_bounds__(threads_of<WPR>(), 2)
 mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__restrict__ K, const __nv_bfloat16 *__restrict__ V,
                 __nv_bfloat16 *__restrict__ O, int S, int E, int H, int BH, int nqblk, float cscale)
 {
     static_assert(D == 64, "rows of the operand tiles are 128 bytes");
+    static_assert(WPR == 1 || WPR == 2, "one or two workers per row");
+    constexpr int kWorkers = workers_of<WPR>();
+    constexpr int CW = kKeys / WPR;                  // score columns per worker and tile
     using C = Bf16Cfg<D>;
     constexpr int CPR = D / 8;                       // 16-byte chunks per row
     constexpr int TILE = C::kTileBytes;
@@ -96,6 +103,8 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     __shared__ uint64_t k_full[kStages], k_free[kStages], v_full[kStages], v_free[kStages], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
+    __shared__ float xch[2][2][kRows];               // WPR == 2: row maxima of the two halves, by tile parity
+    __shared__ float lx[2][kRows];                   // WPR == 2: row sums of the two halves
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x % BH;
@@ -230,15 +239,18 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     }
 
     // ===================== the workers ===========================================================
-    const int wq = warp;                             // TMEM lane quadrant of this warp
+    const int wq = warp & 3;                         // TMEM lane quadrant of this warp
+    const int half = warp >> 2;                      // which CW columns of a tile this worker owns (0 when WPR == 1)
     const int rloc = wq * 32 + lane;                 // row inside the block = TMEM lane
     const int row = q0 + rloc;
+    // the two workers of a row meet at a named barrier of their two warps
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + wq) : "memory"); };
     {
         const bool ok = row < S;
         const __nv_bfloat16 *src = Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol;
         uint8_t *dst = q_s + rloc * 128;
 #pragma unroll
-        for (int c = 0; c < CPR; ++c) cp_async16(dst + ((c ^ (rloc & 7)) << 4), src + c * 8, ok);
+        for (int c = half * (CPR / WPR); c < (half + 1) * (CPR / WPR); ++c) cp_async16(dst + ((c ^ (rloc & 7)) << 4), src + c * 8, ok);
         cp_async_commit();
         cp_async_wait<0>();
     }
@@ -257,32 +269,40 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         wait(&s_full[buf], (uint32_t)((t >> 1) & 1), 1);   // S(t) is in TMEM
         tc_fence_after();
         const int wrow0 = q0 + wq * 32;              // first row of this warp
-        const bool warp_dead = CAUSAL && j0 > wrow0 + 31;          // these columns are above the diagonal for the whole warp
+        const bool warp_dead = CAUSAL && j0 > wrow0 + 31;          // these columns are above the diagonal for the whole warp (both halves)
         const bool need_mask = (CAUSAL && j0 + kKeys - 1 > wrow0) || j0 + kKeys > S;
-        const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : kKeys);     // visible columns of this row
+        // visible columns of this row among this worker's CW columns
+        const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : kKeys) - half * CW;
 
-        // ---- the row's 64 scores are read from TMEM once and stay in registers --------------------
-        float v0[32], v1[32];
+        // ---- the worker's scores are read from TMEM once and stay in registers --------------------
+        float v0[32], v1[32];                    // v1: columns 32..63, used when WPR == 1
         float mx = -INFINITY;
         if (!warp_dead) {
-            tmem_ld32(s_addr, v0);
-            tmem_ld32(s_addr + 32, v1);
+            tmem_ld32(s_addr + half * CW, v0);
+            if (WPR == 1) tmem_ld32(s_addr + 32, v1);
             tmem_wait_ld();
             if (need_mask) {
                 // a masked score becomes -inf: its exponential below is exactly 0
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     v0[c] = (c < nvalid) ? v0[c] : -INFINITY;
-                    v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
+                    if (WPR == 1) v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
                 }
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
                 m4[(c >> 1) & 1] = fmaxf(m4[(c >> 1) & 1], fmaxf(v0[c], v0[c + 1]));
-                m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
+                if (WPR == 1) m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
             }
             mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            if (WPR == 2) {
+                // the row maximum over both halves; the partner has read its scores when it arrives,
+                // so P may be written over S afterwards
+                xch[t & 1][half][rloc] = mx;
+                pair_sync();
+                mx = fmaxf(mx, xch[t & 1][half ^ 1][rloc]);
+            }
         }
         const float mxs = mx * cscale;               // cscale > 0; -inf stays -inf (a row that sees nothing of this tile)
         if (t == 0) {
@@ -298,7 +318,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 wait(&o_done[(t - 1) & 1], (uint32_t)(((t - 1) >> 1) & 1), 2);   // P V(t-1) has completed
                 tc_fence_after();
 #pragma unroll
-                for (int hh = 0; hh < D / 16; ++hh) {
+                for (int hh = half * (D / 16 / WPR); hh < (half + 1) * (D / 16 / WPR); ++hh) {
                     float a[16];
                     tmem_ld16(o_addr + hh * 16, a);
                     tmem_wait_ld();
@@ -315,21 +335,21 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
             uint32_t zz[16];
 #pragma unroll
             for (int c = 0; c < 16; ++c) zz[c] = 0u;
-            tmem_st16_u32(s_addr, zz);
-            tmem_st16_u32(s_addr + 16, zz);
+            tmem_st16_u32(s_addr + half * 16, zz);
+            if (WPR == 1) tmem_st16_u32(s_addr + 16, zz);
         } else {
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
+            for (int k = 0; k < 2 / WPR; ++k) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    const float s0 = k ? v1[c] : v0[c], s1 = k ? v1[c + 1] : v0[c + 1];
+                    const float s0 = (WPR == 1 && k) ? v1[c] : v0[c], s1 = (WPR == 1 && k) ? v1[c + 1] : v0[c + 1];
                     const float p0 = ex2_approx(fmaf(s0, cscale, -m_ref));
                     const float p1 = ex2_approx(fmaf(s1, cscale, -m_ref));
                     ps4[(c >> 1) & 3] += p0 + p1;
                     pk[c >> 1] = pack_bf16(p0, p1);
                 }
-                tmem_st16_u32(s_addr + k * 16, pk);        // columns [16k, 16k+16): all 64 scores are in registers already
+                tmem_st16_u32(s_addr + (k + half) * 16, pk);   // packed pairs: 16 columns per 32 keys; every score they overwrite is in registers
             }
         }
         l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
@@ -341,11 +361,16 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     {
         wait(&o_done[(nt - 1) & 1], (uint32_t)(((nt - 1) >> 1) & 1), 3);
         tc_fence_after();
+        if (WPR == 2) {
+            lx[half][rloc] = l;
+            pair_sync();
+            l += lx[half ^ 1][rloc];
+        }
         const float inv = 1.0f / fmaxf(l, 1e-20f);
         const bool store = !abort_flag && row < S;
         uint4 *dst = reinterpret_cast<uint4 *>(O + (tok0 + (row < S ? row : 0)) * (size_t)E + hcol);
 #pragma unroll
-        for (int hh = 0; hh < D / 32; ++hh) {
+        for (int hh = half * (D / 32 / WPR); hh < (half + 1) * (D / 32 / WPR); ++hh) {
             float a[32];
             tmem_ld32(o_addr + hh * 32, a);
             tmem_wait_ld();
@@ -361,11 +386,11 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     __syncthreads();
 }
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, int WPR>
 int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, cudaStream_t st)
 {
     using C = Bf16Cfg<D>;
-    auto kern = mha_bf16_kernel<D, CAUSAL>;
+    auto kern = mha_bf16_kernel<D, CAUSAL, WPR>;
     // at least 100 KB: at most two blocks share an SM, so their 256-column TMEM allocations always fit in the 512 columns
     size_t smem = C::kSmemBytes + 1024;
     if (smem < 100 * 1024) smem = 100 * 1024;
@@ -375,7 +400,7 @@ int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int 
     const long long blocks = (long long)B * H * nqblk;
     if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
     const float cscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<(unsigned)blocks, kThreads, smem, st>>>(static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
+    kern<<<(unsigned)blocks, threads_of<WPR>(), smem, st>>>(static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
                                                     static_cast<const __nv_bfloat16 *>(v), static_cast<__nv_bfloat16 *>(out), S, E, H, B * H,
                                                     nqblk, cscale);
     return check_launch("mha_bf16_kernel");
@@ -385,12 +410,17 @@ int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int 
 
 bool mha_bf16_supports(int D) { return D == 64; }
 
-int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st)
+// variant: 0 = default, 1 = one worker per query row, 2 = two workers per query row
+int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st, int variant)
 {
     const int D = E / H;
     if (!mha_bf16_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "bf16 attention supports head_dim 64, got %d", D);
+    if (variant < 0 || variant > 2) return fail(HIPGPT_ERR_BAD_ARG, "bf16 attention: unknown variant %d", variant);
     if (B == 0 || S == 0) return HIPGPT_OK;
-    return causal ? launch_bf16_cfg<64, true>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false>(q, k, v, out, B, S, E, H, st);
+    if (variant == 0) variant = kDefaultWorkersPerRow;
+    if (variant == 2)
+        return causal ? launch_bf16_cfg<64, true, 2>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 2>(q, k, v, out, B, S, E, H, st);
+    return causal ? launch_bf16_cfg<64, true, 1>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 1>(q, k, v, out, B, S, E, H, st);
 }
 
 int bf16_status_fetch(int *status)

@@ -135,6 +135,12 @@ int hipgpt_mha_forward_planes(const float *d_qkv, float *d_out, float *d_probs,
 int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const void *d_v, void *d_out,
                             int B, int S, int E, int H, int causal, void *stream)
 {
+    return hipgpt_mha_forward_bf16_ex(d_q, d_k, d_v, d_out, B, S, E, H, causal, 0, stream);
+}
+
+int hipgpt_mha_forward_bf16_ex(const void *d_q, const void *d_k, const void *d_v, void *d_out,
+                               int B, int S, int E, int H, int causal, int variant, void *stream)
+{
     if (B < 0 || S < 0 || E < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: B=%d S=%d E=%d", B, S, E);
     if (H <= 0 || E % H != 0) return fail(HIPGPT_ERR_BAD_ARG, "Bad MHA config: E=%d H=%d", E, H);
     if (B == 0 || S == 0 || E == 0) return HIPGPT_OK;
@@ -142,7 +148,7 @@ int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const void *d_v, v
     if ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v) |
          reinterpret_cast<uintptr_t>(d_out)) & 15)
         return fail(HIPGPT_ERR_BAD_ARG, "bf16 planes must be 16-byte aligned");
-    return launch_mha_bf16(d_q, d_k, d_v, d_out, B, S, E, H, causal, static_cast<cudaStream_t>(stream));
+    return launch_mha_bf16(d_q, d_k, d_v, d_out, B, S, E, H, causal, static_cast<cudaStream_t>(stream), variant);
 }
 
 // Host buffers in, host buffers out, for planes of `esz`-byte elements (4: fp32, 2: bf16; the

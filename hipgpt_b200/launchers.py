@@ -42,7 +42,7 @@ def mha_forward(q, k, v, out, probs, B: int, S: int, E: int, H: int, *, causal: 
                                                   B, S, E, H, int(causal), algo, warps, _stream()))
 
 
-def mha_forward_bf16(d_qkv, d_output, B: int, S: int, E: int, H: int, *, causal: bool = False):
+def mha_forward_bf16(d_qkv, d_output, B: int, S: int, E: int, H: int, *, causal: bool = False, variant: int = 0):
     """The launcher's contract with bf16 storage: d_qkv = three stacked [B*S, E] bf16 planes, d_output
     [B*S, E] bf16 (head_dim 64), fp32 accumulation."""
     for t in (d_qkv, d_output):
@@ -50,7 +50,8 @@ def mha_forward_bf16(d_qkv, d_output, B: int, S: int, E: int, H: int, *, causal:
             raise ValueError("expected a contiguous CUDA bfloat16 tensor")
     plane = B * S * E * 2                                   # bytes
     p = d_qkv.data_ptr()
-    _capi.check(_capi.lib().hipgpt_mha_forward_bf16(p, p + plane, p + 2 * plane, d_output.data_ptr(), B, S, E, H, int(causal), _stream()))
+    _capi.check(_capi.lib().hipgpt_mha_forward_bf16_ex(p, p + plane, p + 2 * plane, d_output.data_ptr(), B, S, E, H, int(causal),
+                                                       int(variant), _stream()))
 
 
 def launch_scaled_dot_product(Q, K, scores, B: int, S: int, D: int):

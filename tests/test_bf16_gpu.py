@@ -22,11 +22,11 @@ def _status():
     return st.value
 
 
-def _run(qkv_f32: np.ndarray, B, S, E, H, causal):
+def _run(qkv_f32: np.ndarray, B, S, E, H, causal, variant=0):
     """-> (kernel output as float32 numpy, the bf16-rounded inputs as float32 numpy)"""
     d = torch.from_numpy(qkv_f32.reshape(3, B * S, E)).cuda().bfloat16()
     out = torch.full((B * S, E), float("nan"), dtype=torch.bfloat16, device="cuda")
-    launchers.mha_forward_bf16(d, out, B, S, E, H, causal=causal)
+    launchers.mha_forward_bf16(d, out, B, S, E, H, causal=causal, variant=variant)
     torch.cuda.synchronize()
     return out.float().cpu().numpy(), d.float().cpu().numpy()
 
@@ -38,10 +38,11 @@ SHAPES = [(1, 1, 1, 64), (2, 2, 7, 64), (1, 2, 64, 64), (1, 1, 128, 64), (1, 3, 
 
 @pytest.mark.parametrize("shape", SHAPES)
 @pytest.mark.parametrize("causal", [False, True])
-def test_bf16_kernel_matches_oracle(shape, causal):
+@pytest.mark.parametrize("variant", [1, 2])          # one or two worker threads per query row
+def test_bf16_kernel_matches_oracle(shape, causal, variant):
     B, H, S, D = shape
     E = H * D
-    out, rounded = _run(synth.qkv_planes(3000 + S, B, S, E), B, S, E, H, causal)
+    out, rounded = _run(synth.qkv_planes(3000 + S, B, S, E), B, S, E, H, causal, variant)
     ref_out, _ = ob.mha(rounded, B, S, E, H, causal=causal)
     assert _status() == 0
     assert np.isfinite(out).all()
@@ -57,8 +58,8 @@ def test_bf16_rows_whose_maximum_grows_late():
     ramp = (1.0 + np.arange(S, dtype=np.float32) / 40.0)[:, None]
     qkv[1] = np.sign(qkv[0][:1]) * ramp          # K rows grow along the sequence, aligned with the first query
     qkv[0] = np.abs(qkv[0]) * np.sign(qkv[0][:1])
-    for causal in (False, True):
-        out, rounded = _run(qkv, B, S, E, H, causal)
+    for causal, variant in [(False, 1), (True, 1), (False, 2), (True, 2)]:
+        out, rounded = _run(qkv, B, S, E, H, causal, variant)
         ref_out, _ = ob.mha(rounded, B, S, E, H, causal=causal)
         assert _status() == 0
         assert float(np.abs(out - ref_out).max()) <= TOL
