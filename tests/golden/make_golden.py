@@ -1,6 +1,6 @@
 """Writes tests/golden/attn_golden.npz from the REFERENCE's own attention launchers.
 
-Run it in a container where the HipGPT source tree is mounted (default /root/reference):
+Run it where the HipGPT source tree is mounted (oracle/Makefile's REF names the place):
 
     make -C oracle && python tests/golden/make_golden.py
 

@@ -100,7 +100,7 @@ def test_decode_scratch_size_query():
     assert lib.hipgpt_mha_decode_scratch_bytes(0, 8, 32, 256) == 0
 
 
-REFERENCE = os.environ.get("HIPGPT_REFERENCE", "/root/reference")   # the HipGPT tree, where it is mounted
+REFERENCE = os.environ.get("HIPGPT_REFERENCE", "/root/reference")   # the HipGPT tree
 
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE, "src", "transformer_layer.cpp")), reason="reference tree not mounted")
