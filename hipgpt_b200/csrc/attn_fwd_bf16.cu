@@ -100,7 +100,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     uint8_t *q_s = base;                             // [128][D] bf16, row r chunk c at r*128 + ((c ^ (r & 7)) * 16)
     uint8_t *k_s = q_s + C::kQBytes;                 // [stage][64 keys][D], the same layout (K-major operand)
     uint8_t *v_s = k_s + kStages * TILE;             // [stage][64 keys][D], the same bytes read as an N-major operand
-    __shared__ uint64_t k_full[kStages], k_free[kStages], v_full[kStages], v_free[kStages], s_full[2], p_full[2], o_done[2];
+    __shared__ uint64_t k_full[kStages], v_full[kStages], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ float xch[2][2][kRows];               // WPR == 2: row maxima of the two halves, by tile parity
@@ -122,8 +122,6 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&k_full[i], 1);                // the K warp
             mbar_init(&v_full[i], 1);                // the V warp
-            mbar_init(&k_free[i], 1);                // tcgen05.commit
-            mbar_init(&v_free[i], 1);
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -163,8 +161,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k)         // 16 bf16 = 32 bytes per instruction
                     mma_f16_ss(tmem + kColX + buf * kKeys, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
-                tc_commit(&s_full[buf]);
-                tc_commit(&k_free[stage]);
+                tc_commit(&s_full[buf]);             // S is ready; it also tells the K warp that this product no longer reads its stage
             };
             auto issue_pv = [&](int buf, int stage, bool first) {
                 // N-major B: 16 keys (two groups of 8 rows of 128 bytes) per instruction = 2048 bytes
@@ -173,8 +170,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 for (int k = 0; k < kKeys / 16; ++k)
                     mma_f16_ts(tmem + kColO, tmem + kColX + buf * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 128), idesc_pv,
                                (first && k == 0) ? 0u : 1u);
-                tc_commit(&o_done[buf]);
-                tc_commit(&v_free[stage]);
+                tc_commit(&o_done[buf]);             // O is up to date; it also tells the V warp that this product no longer reads its stage
             };
             wait(&k_full[0], 0, 4);
             tc_fence_after();
@@ -206,7 +202,8 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         const bool is_v = warp == kWorkers / 32 + 2;
         const __nv_bfloat16 *__restrict__ plane = is_v ? V : K;
         uint8_t *ring = is_v ? v_s : k_s;
-        uint64_t *full = is_v ? v_full : k_full, *freeb = is_v ? v_free : k_free;
+        uint64_t *full = is_v ? v_full : k_full;
+        uint64_t *done = is_v ? o_done : s_full;     // completion of the product that read a stage, by tile parity
         const int sc = lane % CPR, sr0 = lane / CPR;     // chunk of a row, first row
         constexpr int RPP = 32 / CPR;                    // rows per pass
         auto copy = [&](int u) {
@@ -226,12 +223,17 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         for (int u = 0; u < kStages - 1; ++u) copy(u);
         __syncthreads();                             // matches the block-wide barrier after Q staging
         for (int u = 0; u < nt; ++u) {
-            const int w = u + kStages - 1;           // the tile whose copy is issued now
-            if (w < nt && w >= kStages) wait(&freeb[w % kStages], (uint32_t)(((w / kStages) - 1) & 1), is_v ? 8 : 7);
-            copy(w);
-            cp_async_wait<kStages - 1>();            // tile u has landed
+            // tile u is published first: the wait for a free stage below ends only when a product two tiles
+            // back has completed, and the consumer of tile u must not stand behind that
+            cp_async_wait<kStages - 2>();            // the copies of tiles u+1, u+2 may be in flight: tile u has landed
             proxy_fence();                           // generic-proxy writes -> visible to the tensor core
             arrive(&full[u % kStages]);
+            const int w = u + kStages - 1;           // the tile whose copy is issued now
+            // stage w mod 4 held tile w - 4 = u - 1: free once Q K(u-1)^T (for V: P V(u-1)) has completed.  A commit
+            // costs the issuing lane about as much as a tensor-core instruction, so the stages have no barriers of
+            // their own; the later product on the same barrier, u + 1, cannot complete before tile u + 1 is published
+            if (w < nt && w >= kStages) wait(&done[(u - 1) & 1], (uint32_t)(((u - 1) >> 1) & 1), is_v ? 8 : 7);
+            copy(w);
         }
         cp_async_wait<0>();
         __syncthreads();
