@@ -69,7 +69,7 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="run only the greedy-generation leg and print its JSON")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--bf16-variant", type=int, default=0, help="--dtype bf16: 0 default, 1 one worker per query row, 2 two workers")
+    ap.add_argument("--bf16-variant", type=int, default=0, help="--dtype bf16: 0 default, 1 one worker per query row, 2 two workers, 3 two workers and 128-key tiles")
     return ap.parse_args()
 
 

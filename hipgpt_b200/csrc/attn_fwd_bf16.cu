@@ -7,7 +7,8 @@
 // = TMEM lane), one warp whose elected lane issues the tensor-core instructions, one warp that
 // copies K tiles and one that copies V tiles.  Two blocks per SM.  Per tile of 64 keys:
 //   copy     cp.async brings the bf16 K / V tile straight into its 128-byte-swizzled operand
-//            layout (no conversion), four stages each, rings of full / free mbarriers;
+//            layout (no conversion), four stages each; a stage is free again when the product that read
+//            it has completed (the S-ready barrier for K, the O-done barrier for V);
 //   S        = Q K^T (M=128, N=64, 4 instructions of K=16) into one of two TMEM buffers, issued one
 //            tile ahead of the softmax;
 //   softmax  the worker reads its 64 scores from TMEM once; maximum, exponentials (scale folded into
@@ -18,6 +19,8 @@
 //            row's maximum grew by more than 2^8 since the last rescale; until then exponentials may
 //            reach 2^8, harmless in bf16 / fp32.  The worker therefore goes from tile t straight to
 //            tile t+1 while P V(t) runs.
+// The template also holds two schedules that were measured slower and are kept selectable: two workers
+// per row (WPR = 2), and tiles of 128 keys with one S / P buffer (KEYS = 128).
 // Every wait is bounded: on expiry the block raises a flag that cuts all later waits short,
 // records a status code, skips its stores, frees its TMEM and returns.
 #include "tc_primitives.cuh"
@@ -29,13 +32,11 @@ namespace hipgpt {
 namespace {
 
 constexpr int kRows = 128;        // query rows per block
-constexpr int kKeys = 64;         // keys per tile
 // WPR = workers per query row: 1 (a worker owns the 64 scores of its row) or 2 (two workers, in warps w and
 // w + 4 that share a TMEM lane quadrant, own 32 scores each and exchange the row maximum through shared
 // memory once per tile): twice the warps to hide the latencies of the softmax behind.
 template <int WPR> __host__ __device__ constexpr int workers_of() { return kRows * WPR; }
 template <int WPR> __host__ __device__ constexpr int threads_of() { return workers_of<WPR>() + 32 + 64; }     // workers, the issuing warp, the K warp, the V warp
-constexpr int kStages = 4;        // K and V tiles in flight
 constexpr int kDefaultWorkersPerRow = 1;
 constexpr float kRescaleStep = 8.0f;     // log2 of the growth of a row maximum that forces a rescale
 constexpr uint32_t kColX = 0, kColO = 128, kTmemCols = 256;
@@ -76,14 +77,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int D>
+// KEYS = keys per tile: 64 (two S / P buffers in TMEM, Q K^T one tile ahead of the softmax, four stages of K and
+// V) or 128 (one S / P buffer of 128 columns, two stages; Q K^T with N = 128 costs the tensor pipe what N = 64
+// costs, so a tile of twice the keys takes 14 instead of 20 tensor-core operations)
+template <int D, int KEYS>
 struct Bf16Cfg {
+    static constexpr int kStages = KEYS == 64 ? 4 : 2;          // K and V tiles in flight
     static constexpr int kQBytes = kRows * D * 2;               // the Q tile
-    static constexpr int kTileBytes = kKeys * D * 2;            // one K or V tile
+    static constexpr int kTileBytes = KEYS * D * 2;             // one K or V tile
     static constexpr size_t kSmemBytes = (size_t)kQBytes + 2 * kStages * kTileBytes;
 };
 
-template <int D, bool CAUSAL, int WPR>
+template <int D, bool CAUSAL, int WPR, int KEYS>
 __global__ void __launch_bounds__(threads_of<WPR>(), 2)
 mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__restrict__ K, const __nv_bfloat16 *__restrict__ V,
                 __nv_bfloat16 *__restrict__ O, int S, int E, int H, int BH, int nqblk, float cscale)
@@ -91,8 +96,12 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     static_assert(D == 64, "rows of the operand tiles are 128 bytes");
     static_assert(WPR == 1 || WPR == 2, "one or two workers per row");
     constexpr int kWorkers = workers_of<WPR>();
-    constexpr int CW = kKeys / WPR;                  // score columns per worker and tile
-    using C = Bf16Cfg<D>;
+    static_assert(KEYS == 64 || (KEYS == 128 && WPR == 2), "128-key tiles need two workers per row");
+    constexpr int kKeys = KEYS, kStages = Bf16Cfg<D, KEYS>::kStages;
+    constexpr int CW = kKeys / WPR;                  // score columns per worker and tile: 64 or 32
+    constexpr bool TWO = CW == 64;                   // a worker holds two arrays of 32 scores
+    constexpr int XB = KEYS == 64 ? 2 : 1;           // S / P buffers in TMEM
+    using C = Bf16Cfg<D, KEYS>;
     constexpr int CPR = D / 8;                       // 16-byte chunks per row
     constexpr int TILE = C::kTileBytes;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -160,7 +169,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 const uint64_t dk = make_desc(smem_u32(k_s + stage * TILE), 16, 1024, 2);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k)         // 16 bf16 = 32 bytes per instruction
-                    mma_f16_ss(tmem + kColX + buf * kKeys, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
+                    mma_f16_ss(tmem + kColX + (XB == 2 ? buf * kKeys : 0), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
                 tc_commit(&s_full[buf]);             // S is ready; it also tells the K warp that this product no longer reads its stage
             };
             auto issue_pv = [&](int buf, int stage, bool first) {
@@ -168,7 +177,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 const uint64_t dv = make_desc(smem_u32(v_s + stage * TILE), 1024, 1024, 2);
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)
-                    mma_f16_ts(tmem + kColO, tmem + kColX + buf * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 128), idesc_pv,
+                    mma_f16_ts(tmem + kColO, tmem + kColX + (XB == 2 ? buf * kKeys : 0) + (uint32_t)(k * 8), dv + (uint64_t)(k * 128), idesc_pv,
                                (first && k == 0) ? 0u : 1u);
                 tc_commit(&o_done[buf]);             // O is up to date; it also tells the V warp that this product no longer reads its stage
             };
@@ -176,8 +185,8 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
             tc_fence_after();
             issue_qk(0, 0);
             for (int t = 0; t < nt; ++t) {
-                const int buf = t & 1;
-                if (t + 1 < nt) {
+                const int buf = t & 1;               // barrier slot of tile t (and its S / P buffer when there are two)
+                if (XB == 2 && t + 1 < nt) {
                     wait(&k_full[(t + 1) % kStages], (uint32_t)(((t + 1) / kStages) & 1), 4);    // K(t+1) is in shared memory
                     tc_fence_after();
                     issue_qk(buf ^ 1, (t + 1) % kStages);    // its buffer held P(t-1): P V(t-1) was issued before, instructions run in order
@@ -186,6 +195,12 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 wait(&v_full[t % kStages], (uint32_t)((t / kStages) & 1), 6);            // V(t) is in shared memory
                 tc_fence_after();
                 issue_pv(buf, t % kStages, t == 0);
+                if (XB == 1 && t + 1 < nt) {
+                    // one buffer: S(t+1) overwrites P(t), which the product just issued reads first (instructions run in order)
+                    wait(&k_full[(t + 1) % kStages], (uint32_t)(((t + 1) / kStages) & 1), 4);
+                    tc_fence_after();
+                    issue_qk(buf ^ 1, (t + 1) % kStages);
+                }
             }
         }
         __syncwarp();
@@ -267,7 +282,7 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     for (int t = 0; t < nt; ++t) {
         const int buf = t & 1;
         const int j0 = t * kKeys;
-        const uint32_t s_addr = lane_base + kColX + buf * kKeys;
+        const uint32_t s_addr = lane_base + kColX + (XB == 2 ? buf * kKeys : 0);
         wait(&s_full[buf], (uint32_t)((t >> 1) & 1), 1);   // S(t) is in TMEM
         tc_fence_after();
         const int wrow0 = q0 + wq * 32;              // first row of this warp
@@ -277,25 +292,25 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : kKeys) - half * CW;
 
         // ---- the worker's scores are read from TMEM once and stay in registers --------------------
-        float v0[32], v1[32];                    // v1: columns 32..63, used when WPR == 1
+        float v0[32], v1[32];                    // v1: the worker's columns 32..63, used when it owns 64
         float mx = -INFINITY;
         if (!warp_dead) {
             tmem_ld32(s_addr + half * CW, v0);
-            if (WPR == 1) tmem_ld32(s_addr + 32, v1);
+            if (TWO) tmem_ld32(s_addr + half * CW + 32, v1);
             tmem_wait_ld();
             if (need_mask) {
                 // a masked score becomes -inf: its exponential below is exactly 0
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     v0[c] = (c < nvalid) ? v0[c] : -INFINITY;
-                    if (WPR == 1) v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
+                    if (TWO) v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
                 }
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
                 m4[(c >> 1) & 1] = fmaxf(m4[(c >> 1) & 1], fmaxf(v0[c], v0[c + 1]));
-                if (WPR == 1) m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
+                if (TWO) m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
             }
             mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             if (WPR == 2) {
@@ -337,21 +352,21 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
             uint32_t zz[16];
 #pragma unroll
             for (int c = 0; c < 16; ++c) zz[c] = 0u;
-            tmem_st16_u32(s_addr + half * 16, zz);
-            if (WPR == 1) tmem_st16_u32(s_addr + 16, zz);
+            tmem_st16_u32(s_addr + half * (CW / 2), zz);
+            if (TWO) tmem_st16_u32(s_addr + half * (CW / 2) + 16, zz);
         } else {
 #pragma unroll
-            for (int k = 0; k < 2 / WPR; ++k) {
+            for (int k = 0; k < CW / 32; ++k) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    const float s0 = (WPR == 1 && k) ? v1[c] : v0[c], s1 = (WPR == 1 && k) ? v1[c + 1] : v0[c + 1];
+                    const float s0 = (TWO && k) ? v1[c] : v0[c], s1 = (TWO && k) ? v1[c + 1] : v0[c + 1];
                     const float p0 = ex2_approx(fmaf(s0, cscale, -m_ref));
                     const float p1 = ex2_approx(fmaf(s1, cscale, -m_ref));
                     ps4[(c >> 1) & 3] += p0 + p1;
                     pk[c >> 1] = pack_bf16(p0, p1);
                 }
-                tmem_st16_u32(s_addr + (k + half) * 16, pk);   // packed pairs: 16 columns per 32 keys; every score they overwrite is in registers
+                tmem_st16_u32(s_addr + half * (CW / 2) + k * 16, pk);   // packed pairs: 16 columns per 32 keys; every score they overwrite is in registers
             }
         }
         l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
@@ -388,11 +403,11 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     __syncthreads();
 }
 
-template <int D, bool CAUSAL, int WPR>
+template <int D, bool CAUSAL, int WPR, int KEYS>
 int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, cudaStream_t st)
 {
-    using C = Bf16Cfg<D>;
-    auto kern = mha_bf16_kernel<D, CAUSAL, WPR>;
+    using C = Bf16Cfg<D, KEYS>;
+    auto kern = mha_bf16_kernel<D, CAUSAL, WPR, KEYS>;
     // at least 100 KB: at most two blocks share an SM, so their 256-column TMEM allocations always fit in the 512 columns
     size_t smem = C::kSmemBytes + 1024;
     if (smem < 100 * 1024) smem = 100 * 1024;
@@ -412,17 +427,19 @@ int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int 
 
 bool mha_bf16_supports(int D) { return D == 64; }
 
-// variant: 0 = default, 1 = one worker per query row, 2 = two workers per query row
+// variant: 0 = default, 1 = one worker per query row, 2 = two workers per query row, 3 = two workers and 128-key tiles
 int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st, int variant)
 {
     const int D = E / H;
     if (!mha_bf16_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "bf16 attention supports head_dim 64, got %d", D);
-    if (variant < 0 || variant > 2) return fail(HIPGPT_ERR_BAD_ARG, "bf16 attention: unknown variant %d", variant);
+    if (variant < 0 || variant > 3) return fail(HIPGPT_ERR_BAD_ARG, "bf16 attention: unknown variant %d", variant);
     if (B == 0 || S == 0) return HIPGPT_OK;
     if (variant == 0) variant = kDefaultWorkersPerRow;
+    if (variant == 3)
+        return causal ? launch_bf16_cfg<64, true, 2, 128>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 2, 128>(q, k, v, out, B, S, E, H, st);
     if (variant == 2)
-        return causal ? launch_bf16_cfg<64, true, 2>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 2>(q, k, v, out, B, S, E, H, st);
-    return causal ? launch_bf16_cfg<64, true, 1>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 1>(q, k, v, out, B, S, E, H, st);
+        return causal ? launch_bf16_cfg<64, true, 2, 64>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 2, 64>(q, k, v, out, B, S, E, H, st);
+    return causal ? launch_bf16_cfg<64, true, 1, 64>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 1, 64>(q, k, v, out, B, S, E, H, st);
 }
 
 int bf16_status_fetch(int *status)
