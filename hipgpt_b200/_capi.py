@@ -13,6 +13,7 @@ from . import build as _build
 OK = 0
 ERR_BAD_ARG, ERR_NULL, ERR_UNSUPPORTED, ERR_CUDA, ERR_SCRATCH = -1, -2, -3, -4, -5
 ALGO_AUTO, ALGO_GENERIC, ALGO_ROWS, ALGO_TENSOR = 0, 1, 2, 3
+TENSOR_DEFAULT, TENSOR_SPLIT_TF32, TENSOR_TILED, TENSOR_WHOLE_HEAD = 0, 1, 5, 6
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 
@@ -40,6 +41,10 @@ SIGNATURES = {
     "hipgpt_shard_range": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     "hipgpt_probe_fma": (_i, [_vp, _i, _i, C.POINTER(C.c_double), _vp]),
     "hipgpt_kernel_status": (_i, [C.POINTER(_i)]),
+    "hipgpt_accuracy_notice": (_i, [C.POINTER(_i)]),
+    "hipgpt_set_full_range": (_i, [_i]),
+    "hipgpt_debug_wait_expiry": (_i, [_vp, _i, C.c_longlong, _vp]),
+    "hipgpt_gpt_debug_stall_barrier": (_i, [_vp, C.c_longlong]),
     "hipgpt_last_error": (C.c_char_p, []),
     "hipgpt_version": (_i, []),
 }

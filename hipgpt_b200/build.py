@@ -20,7 +20,7 @@ LIBDIR = os.path.join(PKG, "_lib")
 LIB = os.path.join(LIBDIR, "libhipgpt_attn.so")
 OBJDIR = os.path.join(LIBDIR, "obj")
 
-SOURCES = ["attn_fwd_rows.cu", "attn_fwd_tc.cu", "attn_fwd_bf16.cu", "attn_fwd_tc_pair.cu", "attn_fwd_tc16.cu", "attn_fwd_generic.cu", "attn_unfused.cu", "attn_decode.cu", "gpt_decode.cu", "probe.cu", "capi.cu",
+SOURCES = ["attn_fwd_rows.cu", "attn_fwd_tc.cu", "attn_fwd_bf16.cu", "attn_fwd_tc16.cu", "attn_fwd_head.cu", "attn_fwd_generic.cu", "attn_unfused.cu", "attn_decode.cu", "gpt_decode.cu", "probe.cu", "wait_probe.cu", "capi.cu",
            "compat_launchers.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
@@ -54,10 +54,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJDIR, exist_ok=True)
     cc = nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
-    if os.environ.get("HIPGPT_TC_TRACE"):        # phase tracing of the tensor-core kernel (see attn_fwd_tc.cu)
-        extra.append("-DHIPGPT_TC_TRACE")
-    if os.environ.get("HIPGPT_EXTRA_DEFS"):      # experiments: extra -D flags, space separated
-        extra += os.environ["HIPGPT_EXTRA_DEFS"].split()
 
     def compile_one(src: str) -> str:
         obj = os.path.join(OBJDIR, os.path.splitext(src)[0] + ".o")

@@ -39,16 +39,20 @@ int launch_mha_rows(const float *q, const float *k, const float *v, float *out, 
                     int B, int S, int E, int H, int causal, int warps, cudaStream_t st);
 bool mha_rows_supports(int D);
 int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
-                  int B, int S, int E, int H, int causal, cudaStream_t st, int variant = 0);
+                  int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_tc_supports(int D);
 int tc_status_fetch(int *status);
-int launch_mha_tc_pair(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st);
-bool mha_tc_pair_supports(int head_dim);
-int tc_pair_status_fetch(int *status);
 int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, float *probs,
                     int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_tc16_supports(int head_dim);
 int tc16_status_fetch(int *status);
+int tc16_notice_fetch(int *notice);
+// whole-head kernel (head_dim 32, S <= 256): TMA loads, 128-key products, all score tiles of a head in TMEM
+int launch_mha_head(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st);
+bool mha_head_supports(int head_dim, int S, int E, const void *q, const void *k, const void *v, const void *out);
+int head_status_fetch(int *status);
+int head_notice_fetch(int *notice);
+int probe_status_fetch(int *status);
 int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st,
                     int variant = 0);
 bool mha_bf16_supports(int D);

@@ -14,7 +14,6 @@
 
 #include <math.h>
 
-#include <mutex>
 
 namespace hipgpt {
 namespace {
@@ -285,8 +284,10 @@ int launch_decode(const float *q, const float *kc, const float *vc, float *out, 
 //     GPU (different streams, no dependency between them) race on it; serialise them.
 //   * The array keeps what the last call left.  Nothing needs clearing: the first kernel
 //     writes every partial record the second one reads.
-//   * The first call on each device looks the array's device address up (a lookup, not an
-//     allocation).  Make that first call before any stream capture begins on that device.
+//   * Every call looks the array's device address up with the device current (a lookup, not an
+//     allocation; nothing is cached, so the entry point stays valid after a cudaDeviceReset).
+//     The first lookup on a device loads the library's module there: make that first call
+//     before any stream capture begins on that device.
 // ---------------------------------------------------------------------------------------------
 namespace hipgpt {
 namespace {
@@ -294,30 +295,18 @@ namespace {
 constexpr size_t kNoAllocFloats = HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES / sizeof(float);
 static __device__ __align__(256) float g_decode_scratch[kNoAllocFloats];
 
-constexpr int kMaxDevices = 64;
-float *g_decode_scratch_addr[kMaxDevices];     // device address of the array, per device ordinal
-bool g_decode_scratch_known[kMaxDevices];
-std::mutex g_decode_scratch_mu;
-
 // Device address of g_decode_scratch on the current device.  In host code the array's name is
 // only a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress,
-// asked once per device while that device is current.
+// asked while the device that will run the kernel is current.  It is asked on every call and
+// never kept: after the first call on a device it is a table lookup, and an address kept across a
+// cudaDeviceReset (or the loss of the primary context) would point into memory that is gone.
 int decode_scratch_address(float **addr)
 {
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-    if (dev < 0 || dev >= kMaxDevices) return fail(HIPGPT_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-    std::lock_guard<std::mutex> lock(g_decode_scratch_mu);
-    if (!g_decode_scratch_known[dev]) {
-        void *p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_decode_scratch);
-        if (e != cudaSuccess || p == nullptr)
-            return fail(HIPGPT_ERR_CUDA, "cudaGetSymbolAddress(decode scratch): %s", cudaGetErrorString(e));
-        g_decode_scratch_addr[dev] = static_cast<float *>(p);
-        g_decode_scratch_known[dev] = true;
-    }
-    *addr = g_decode_scratch_addr[dev];
+    void *p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr)
+        return fail(HIPGPT_ERR_CUDA, "cudaGetSymbolAddress(decode scratch): %s", cudaGetErrorString(e));
+    *addr = static_cast<float *>(p);
     return HIPGPT_OK;
 }
 
@@ -343,8 +332,9 @@ extern "C" int hipgpt_mha_decode_noalloc(const float *d_q, const float *d_kcache
     float *scratch = nullptr;
     const int rc = decode_scratch_address(&scratch);
     if (rc != HIPGPT_OK) return rc;
-    if (D % 4 == 0 && ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_kcache) |
-                        reinterpret_cast<uintptr_t>(d_vcache) | reinterpret_cast<uintptr_t>(d_out)) & 15) != 0)
+    // only the vector kernels (head_dim % 4 == 0, up to 128) move 16 bytes at a time
+    if (D % 4 == 0 && D <= 128 && ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_kcache) |
+                                    reinterpret_cast<uintptr_t>(d_vcache) | reinterpret_cast<uintptr_t>(d_out)) & 15) != 0)
         return fail(HIPGPT_ERR_BAD_ARG, "decode needs 16-byte aligned pointers");
     return launch_decode(d_q, d_kcache, d_vcache, d_out, scratch, B, H, D, ctx, cap, ns, static_cast<cudaStream_t>(stream));
 }

@@ -427,16 +427,14 @@ int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int 
 
 bool mha_bf16_supports(int D) { return D == 64; }
 
-// variant: 0 = default, 1 = one worker per query row, 2 = two workers per query row, 3 = two workers and 128-key tiles
+// variant: 0 = default, 1 = one worker per query row, 2 = two workers per query row
 int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int B, int S, int E, int H, int causal, cudaStream_t st, int variant)
 {
     const int D = E / H;
     if (!mha_bf16_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "bf16 attention supports head_dim 64, got %d", D);
-    if (variant < 0 || variant > 3) return fail(HIPGPT_ERR_BAD_ARG, "bf16 attention: unknown variant %d", variant);
+    if (variant < 0 || variant > 2) return fail(HIPGPT_ERR_BAD_ARG, "bf16 attention: unknown variant %d", variant);
     if (B == 0 || S == 0) return HIPGPT_OK;
     if (variant == 0) variant = kDefaultWorkersPerRow;
-    if (variant == 3)
-        return causal ? launch_bf16_cfg<64, true, 2, 128>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 2, 128>(q, k, v, out, B, S, E, H, st);
     if (variant == 2)
         return causal ? launch_bf16_cfg<64, true, 2, 64>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 2, 64>(q, k, v, out, B, S, E, H, st);
     return causal ? launch_bf16_cfg<64, true, 1, 64>(q, k, v, out, B, S, E, H, st) : launch_bf16_cfg<64, false, 1, 64>(q, k, v, out, B, S, E, H, st);

@@ -1,0 +1,632 @@
+// Fused attention forward for the shape HipGPT's default model runs (head_dim 32, up to 256 tokens):
+// one thread block owns a whole (batch, head), so K and V are fetched and converted once for both
+// query tiles, every score tile of the head sits in tensor memory at the same time (no online
+// rescaling: a row's true maximum is known before its exponentials are taken), and a block that
+// has more than one head to do fetches the next head's operands while it finishes the current one.
+//
+// Replaces flash_attention_kernel<32> behind launch_multihead_attention for S <= 256
+// (HipGPT src/hip_kernels.cpp:263-325, dispatch :404-451); same arithmetic contract as the other
+// fp32-grade kernels here: results within 1e-5 of the scalar fp32 arithmetic on unit-scale data.
+//
+// Data movement: Q, K and V tiles of [128 rows][32 floats] arrive by TMA (cp.async.bulk.tensor, rank-3
+// maps {E, S, B} over this GPU's own memory, 128-byte swizzle, rows past S filled with zeros, no
+// multicast), six copies per head issued by one lane, completion counted on mbarriers.
+//
+// Products (tcgen05.mma, M = 128, accumulators in TMEM, issued by one lane):
+//   S = Q K^T, N = 128 keys:  the landed fp32 tiles ARE the TF32 operands (the tensor core ignores the
+//       13 low mantissa bits): 4 kind::tf32 instructions; the correction terms Q_lo K_hi + Q K_lo
+//       run as 4 kind::f16 instructions on fp16 copies [Q_lo | Q] x [K_hi | K_lo] concatenated along
+//       the reduction dimension.  8 instructions per 128 x 128 score tile.
+//   O = P V:  P = 2^(s c - m c + 8) is cut into fp16 P_hi (11 bits, exact) and P_lo, V (scaled by a
+//       power of two per head so that its largest magnitude sits near 2^14) into fp16 V_hi and V_lo:
+//       P_hi [V_hi | V_lo] (N = 64) and P_lo V_hi (N = 32, added to the second half), A operand from
+//       TMEM, 16 instructions per 128 keys.  The dropped P_lo V_lo is below 2^-22 relative.
+// TMEM (512 columns): three score/probability buffers of 128 columns (P_hi and P_lo overwrite S in
+// place as packed fp16), two output accumulators of 64 columns (one per query tile).
+// Tiles of a head: causal (q0,k0) (q1,k0) (q1,k1); unmasked (q0,k0) (q0,k1) (q1,k0) (q1,k1), the fourth
+// reusing the first buffer once its P V product has been issued.
+// Threads: three groups of 128 workers (thread = query row = TMEM lane) and one control warp.  A group
+// first converts one operand (K, Q or V) for the whole head, then owns one score tile (two for group 0
+// of an unmasked head): row maximum, exchange of the maximum with the group that holds the other key
+// tile of the same rows (shared memory + mbarrier), exponentials, P to TMEM; at the end the groups of a
+// query tile share its output columns.  The control lane issues the copies and every product in a fixed
+// order, so results do not depend on timing.
+// Every wait is bounded: on expiry the block raises a flag that cuts all later waits short, records a
+// site code for hipgpt_kernel_status, skips its stores, frees its TMEM and returns.
+#include "tc_primitives.cuh"
+
+#include <cuda.h>
+#include <math.h>
+
+#include <mutex>
+
+namespace hipgpt {
+namespace {
+
+constexpr int kTile = 128;                       // rows of a query tile = keys of a key tile
+constexpr int kHeadWorkers = 3 * kTile;
+constexpr int kHeadThreads = kHeadWorkers + 32;
+constexpr uint32_t kTileBytes = kTile * 128;     // one [128][128 byte] operand block
+constexpr uint32_t kOffQraw = 0, kOffKraw = 2 * kTileBytes, kOffVraw = 4 * kTileBytes;
+constexpr uint32_t kOffQ16 = 6 * kTileBytes, kOffK16 = 8 * kTileBytes, kOffV16 = 10 * kTileBytes;
+constexpr uint32_t kHeadSmemBytes = 12 * kTileBytes;
+constexpr uint32_t kColO = 384;                  // after three buffers of 128 columns
+constexpr float kPShift = 8.0f;                  // P carries a factor 2^8: small probabilities stay normal fp16 numbers
+constexpr long long kHeadCycleLimit = 1LL << 28; // per wait, about 0.14 s
+constexpr long long kHeadPollLimit = 1LL << 22;
+
+__device__ int g_head_status = 0;                // first wait site that ran out (0 = none)
+__device__ int g_head_notice = 0;                // bit 0: Q or K left the range in which the fp16 correction terms are exact
+
+struct HeadMaps {
+    CUtensorMap q, k, v;
+};
+
+template <bool CAUSAL>
+__global__ void __launch_bounds__(kHeadThreads, 1)
+mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, int S, int E, int H, int BH, float cscale)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_raw = base + kOffQraw, *k_raw = base + kOffKraw, *v_raw = base + kOffVraw;
+    uint8_t *q_16 = base + kOffQ16;              // per query tile: rows of [Q_lo (32) | Q (32)] fp16, K-major, 128-byte swizzle
+    uint8_t *k_16 = base + kOffK16;              // per key tile:   rows of [K_hi (32) | K_lo (32)]
+    uint8_t *v_16 = base + kOffV16;              // [V_hi | V_lo] (64 columns) fp16, N-major without swizzle: 8 keys x 8 columns
+                                                 // form one 128-byte core matrix, column blocks 128 bytes apart, key groups 1024
+    __shared__ uint64_t ld_q[2], ld_k[2], ld_v[2], cv_q[2], cv_k[2], cv_v[2];
+    __shared__ uint64_t s_full[3], p_full[4], o_done[2], xm[2], xs[2], epi_done, vx;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+    __shared__ float xmax[2][2][2][kTile];       // [head parity][query tile][slot][row]
+    __shared__ float xsum[2][2][2][kTile];
+    __shared__ float vmaxw[2][4];                // [head parity][warp of the V group]
+    __shared__ float s_vinv[2];                  // 1 / (V's power-of-two scale), by head parity
+    __shared__ unsigned s_amax[2];               // bit patterns of max |Q| and max |K| of the current head
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nq = S > kTile ? 2 : 1;            // query tiles = key tiles of a head
+
+    // site codes: 1 Q/K/V landed, 2 operand converted, 3 S ready, 4 P written, 5 output complete,
+    // 6 row maxima exchanged, 7 row sums exchanged, 8 previous head's output read, 9 V maximum exchanged
+    auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
+        if (abort_flag) return;
+        if (!mbar_wait_for(bar, parity, kHeadCycleLimit, kHeadPollLimit)) { abort_flag = 1; atomicCAS(&g_head_status, 0, site); }
+    };
+    auto arrive = [&](uint64_t *bar) {           // one arrival per warp, after every lane's writes
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+    };
+
+    if (warp == kHeadWorkers / 32) {
+        // ================= the control warp ==========================================================
+        auto load_qk = [&](int hd) {
+            const int b = hd / H, c0 = (hd % H) * 32;
+            for (int t = 0; t < nq; ++t) {
+                mbar_arrive_expect_tx(&ld_k[t], kTileBytes);
+                tma_load_3d(k_raw + t * kTileBytes, &maps.k, c0, t * kTile, b, &ld_k[t]);
+                mbar_arrive_expect_tx(&ld_q[t], kTileBytes);
+                tma_load_3d(q_raw + t * kTileBytes, &maps.q, c0, t * kTile, b, &ld_q[t]);
+            }
+        };
+        auto load_v = [&](int hd) {
+            const int b = hd / H, c0 = (hd % H) * 32;
+            for (int t = 0; t < nq; ++t) {
+                mbar_arrive_expect_tx(&ld_v[t], kTileBytes);
+                tma_load_3d(v_raw + t * kTileBytes, &maps.v, c0, t * kTile, b, &ld_v[t]);
+            }
+        };
+        if (lane == 0) {
+            abort_flag = 0;
+            s_amax[0] = s_amax[1] = 0u;
+            for (int i = 0; i < 2; ++i) {
+                mbar_init(&ld_q[i], 1); mbar_init(&ld_k[i], 1); mbar_init(&ld_v[i], 1);
+                mbar_init(&cv_q[i], 4); mbar_init(&cv_k[i], 4); mbar_init(&cv_v[i], 4);
+                mbar_init(&o_done[i], 1);
+                mbar_init(&xm[i], 8); mbar_init(&xs[i], 8);
+            }
+            for (int i = 0; i < 3; ++i) mbar_init(&s_full[i], 1);
+            for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 4);
+            mbar_init(&epi_done, kHeadWorkers / 32);
+            mbar_init(&vx, 4);
+            if ((int)blockIdx.x < BH) { load_qk(blockIdx.x); load_v(blockIdx.x); }
+        }
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncthreads();                             // barriers initialised, TMEM allocated
+        tc_fence_after();
+        const uint32_t tmem = tmem_base_slot;
+        if (lane == 0) {
+            constexpr uint32_t id_qk_h = idesc_f16(kTile, kTile);             // [Q_lo | Q] x [K_hi | K_lo], fp16
+            constexpr uint32_t id_qk_t = make_idesc(kTile, kTile, 0);         // Q x K, tf32
+            constexpr uint32_t id_pv_a = idesc_f16(kTile, 64) | (1u << 16);   // P_hi x [V_hi | V_lo], B N-major
+            constexpr uint32_t id_pv_b = idesc_f16(kTile, 32) | (1u << 16);   // P_lo x V_hi
+            auto issue_qk = [&](int q, int k, int buf) {
+                const uint32_t d = tmem + (uint32_t)(buf * kTile);
+                const uint64_t dq16 = make_desc(smem_u32(q_16 + q * kTileBytes), 16, 1024, 2);
+                const uint64_t dk16 = make_desc(smem_u32(k_16 + k * kTileBytes), 16, 1024, 2);
+                // the correction terms first: the accumulator is still tiny while they are added
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)       // 16 fp16 = 32 bytes per instruction
+                    mma_h_ss(d, dq16 + (uint64_t)(ks * 2), dk16 + (uint64_t)(ks * 2), id_qk_h, ks ? 1u : 0u);
+                const uint64_t dq = make_desc(smem_u32(q_raw + q * kTileBytes), 16, 1024, 2);
+                const uint64_t dk = make_desc(smem_u32(k_raw + k * kTileBytes), 16, 1024, 2);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)       // 8 floats = 32 bytes per instruction
+                    mma_ss(d, dq + (uint64_t)(ks * 2), dk + (uint64_t)(ks * 2), id_qk_t, 1u);
+                tc_commit(&s_full[buf]);
+            };
+            auto issue_pv = [&](int q, int k, int buf, bool first) {
+                const uint32_t d = tmem + kColO + (uint32_t)(q * 64);
+                const uint32_t a_hi = tmem + (uint32_t)(buf * kTile), a_lo = a_hi + 64;
+                const uint64_t dv = make_desc(smem_u32(v_16 + k * kTileBytes), 1024, 128, 0);
+                const int nks = (min(kTile, S - k * kTile) + 15) >> 4;        // 16 keys per instruction; keys past S hold zeros
+                for (int ks = 0; ks < nks; ++ks)     // 16 keys = 8 TMEM columns of packed fp16 = two key groups of V
+                    mma_h_ts(d, a_hi + (uint32_t)(ks * 8), dv + (uint64_t)(ks * 128), id_pv_a, (first && ks == 0) ? 0u : 1u);
+                for (int ks = 0; ks < nks; ++ks)
+                    mma_h_ts(d + 32, a_lo + (uint32_t)(ks * 8), dv + (uint64_t)(ks * 128), id_pv_b, 1u);
+            };
+            int it = 0;
+            for (int hd = blockIdx.x; hd < BH; hd += gridDim.x, ++it) {
+                const uint32_t par = (uint32_t)(it & 1);
+                const int next = hd + (int)gridDim.x;
+                const bool has_next = next < BH;
+                // ---- Q K^T of every tile whose buffer is free ---------------------------------------
+                wait(&cv_k[0], par, 2);
+                wait(&cv_q[0], par, 2);
+                tc_fence_after();
+                issue_qk(0, 0, 0);
+                if (nq == 2) {
+                    if (CAUSAL) {
+                        wait(&cv_q[1], par, 2); tc_fence_after(); issue_qk(1, 0, 1);
+                        wait(&cv_k[1], par, 2); tc_fence_after(); issue_qk(1, 1, 2);
+                    } else {
+                        wait(&cv_k[1], par, 2); tc_fence_after(); issue_qk(0, 1, 1);
+                        wait(&cv_q[1], par, 2); tc_fence_after(); issue_qk(1, 0, 2);
+                    }
+                }
+                // ---- the operands' range (see g_head_notice) ------------------------------------------
+                {
+                    const float aq = __uint_as_float(s_amax[0]), ak = __uint_as_float(s_amax[1]);
+                    s_amax[0] = 0u;
+                    s_amax[1] = 0u;
+                    // beyond fp16's largest number the correction terms saturate; below its smallest normal
+                    // numbers they are flushed, an absolute error of up to 2^-25 per fp16 value, which matters
+                    // when it is neither small in itself nor small beside the scores it is added to
+                    const bool over = !(aq <= 65504.0f) || !(ak <= 65504.0f);
+                    const float flush = 32.0f * cscale * 2.98e-8f * (aq + ak);
+                    if (over || (flush > 3.8e-6f && (aq + ak) > 8.0f * aq * ak)) atomicOr(&g_head_notice, 1);
+                }
+                const bool tail_qk = !CAUSAL && nq == 2;    // the fourth tile's Q K^T comes after the first two P V products
+                if (has_next && !tail_qk) {
+                    // the raw Q and K tiles and their fp16 copies are free once every Q K^T has completed
+                    wait(&s_full[0], par, 3);
+                    if (nq == 2) { wait(&s_full[1], par, 3); wait(&s_full[2], par, 3); }
+                    load_qk(next);
+                }
+                wait(&cv_v[0], par, 2);
+                if (nq == 2) wait(&cv_v[1], par, 2);
+                if (has_next) load_v(next);              // the raw V tiles have been read
+                if (it > 0) wait(&epi_done, (uint32_t)((it - 1) & 1), 8);     // the previous head's output has left TMEM
+                // ---- P V, in a fixed order ------------------------------------------------------------
+                wait(&p_full[0], par, 4);
+                tc_fence_after();
+                issue_pv(0, 0, 0, true);
+                if (nq == 1 || CAUSAL) tc_commit(&o_done[0]);
+                if (nq == 2) {
+                    if (CAUSAL) {
+                        wait(&p_full[2], par, 4); tc_fence_after(); issue_pv(1, 1, 2, true);
+                        wait(&p_full[1], par, 4); tc_fence_after(); issue_pv(1, 0, 1, false);
+                        tc_commit(&o_done[1]);
+                    } else {
+                        wait(&p_full[1], par, 4); tc_fence_after(); issue_pv(0, 1, 1, false);
+                        tc_commit(&o_done[0]);
+                        // (q1, k1) into the first buffer: its P has been consumed by the product issued above
+                        // (instructions run in order) and its workers have arrived at p_full[0]
+                        issue_qk(1, 1, 0);
+                        if (has_next) {
+                            wait(&s_full[0], 1u, 3);     // second completion of this barrier in this head
+                            wait(&s_full[1], par, 3);
+                            wait(&s_full[2], par, 3);
+                            load_qk(next);
+                        }
+                        wait(&p_full[2], par, 4); tc_fence_after(); issue_pv(1, 0, 2, true);
+                        wait(&p_full[3], par, 4); tc_fence_after(); issue_pv(1, 1, 0, false);
+                        tc_commit(&o_done[1]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        tc_fence_before();
+        __syncthreads();                             // the workers have read their last output
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+        return;
+    }
+
+    // ===================== the workers ===============================================================
+    const int grp = warp >> 2;                       // 0: converts K, 1: converts Q, 2: converts V
+    const int wq = warp & 3;                         // TMEM lane quadrant of this warp
+    const int rloc = wq * 32 + lane;                 // row inside a tile = TMEM lane
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t lane_base = tmem_base_slot + ((uint32_t)(wq * 32) << 16);
+
+    int it = 0;
+    for (int hd = blockIdx.x; hd < BH; hd += gridDim.x, ++it) {
+        const uint32_t par = (uint32_t)(it & 1);
+        const int b = hd / H, h = hd % H;
+
+        // ---- operand conversion: thread = one row of each tile ------------------------------------------
+        if (grp < 2) {
+            // K: [K_hi | K_lo];  Q: [Q_lo | Q].  hi = the 11 leading bits (exact in fp16), lo = x - hi.
+            uint8_t *raw = grp == 0 ? k_raw : q_raw, *dst16 = grp == 0 ? k_16 : q_16;
+            uint64_t *ld = grp == 0 ? ld_k : ld_q, *cv = grp == 0 ? cv_k : cv_q;
+            float amax = 0.0f;
+            for (int t = 0; t < nq; ++t) {
+                wait(&ld[t], par, 1);
+                const uint8_t *src = raw + t * kTileBytes;
+                uint8_t *dst = dst16 + t * kTileBytes;
+                float4 x[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) x[c] = *reinterpret_cast<const float4 *>(src + sw128(rloc, c));
+#pragma unroll
+                for (int pc = 0; pc < 4; ++pc) {
+                    const float4 a = x[2 * pc], c4 = x[2 * pc + 1];
+                    const float4 ah = hi4(a), ch = hi4(c4);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                                             fmaxf(fmaxf(fabsf(c4.x), fabsf(c4.y)), fmaxf(fabsf(c4.z), fabsf(c4.w)))));
+                    const uint4 lo = make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
+                                                pack_f16(c4.x - ch.x, c4.y - ch.y), pack_f16(c4.z - ch.z, c4.w - ch.w));
+                    if (grp == 0) {
+                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, pc)) =
+                            make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, 4 + pc)) = lo;
+                    } else {
+                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, pc)) = lo;
+                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, 4 + pc)) =
+                            make_uint4(pack_f16(a.x, a.y), pack_f16(a.z, a.w), pack_f16(c4.x, c4.y), pack_f16(c4.z, c4.w));
+                    }
+                }
+                if (t == nq - 1) {
+                    // a NaN compares false everywhere: its bit pattern is what reaches the range test
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    if (lane == 0) atomicMax(&s_amax[grp == 0 ? 1 : 0], __float_as_uint(amax));
+                }
+                proxy_fence();                       // generic-proxy writes -> visible to the tensor core
+                arrive(&cv[t]);
+            }
+        } else {
+            // V: scaled by a power of two so that the head's largest magnitude lies in [2^14, 2^15), then
+            // [V_hi | V_lo].  The previous head's P V products must have completed before V16 is overwritten.
+            if (it > 0) {
+                wait(&o_done[0], (uint32_t)((it - 1) & 1), 5);
+                if (nq == 2) wait(&o_done[1], (uint32_t)((it - 1) & 1), 5);
+            }
+            float4 x[2][8];
+            float amax = 0.0f;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                if (t < nq) {
+                    wait(&ld_v[t], par, 1);
+                    const uint8_t *src = v_raw + t * kTileBytes;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        x[t][c] = *reinterpret_cast<const float4 *>(src + sw128(rloc, c));
+                        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(x[t][c].x), fabsf(x[t][c].y)), fmaxf(fabsf(x[t][c].z), fabsf(x[t][c].w))));
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (lane == 0) vmaxw[par][wq] = amax;
+            arrive(&vx);
+            wait(&vx, par, 9);
+            const float vm = fmaxf(fmaxf(vmaxw[par][0], vmaxw[par][1]), fmaxf(vmaxw[par][2], vmaxw[par][3]));
+            float sc = 1.0f, inv = 1.0f;
+            if (vm > 0.0f && vm <= 3.0e38f) {
+                const int e = (int)((__float_as_uint(vm) >> 23) & 0xffu) - 127;
+                const int sh = min(14 - e, 126);
+                sc = __uint_as_float((uint32_t)(127 + sh) << 23);
+                inv = __uint_as_float((uint32_t)(127 - sh) << 23);
+            }
+            if (tid == 2 * kTile) s_vinv[par] = inv;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                if (t < nq) {
+                    const int key = t * kTile + rloc;
+                    uint8_t *dst = v_16 + (key >> 3) * 1024 + (key & 7) * 16;
+#pragma unroll
+                    for (int pc = 0; pc < 4; ++pc) {
+                        float4 a = x[t][2 * pc], c4 = x[t][2 * pc + 1];
+                        a.x *= sc; a.y *= sc; a.z *= sc; a.w *= sc;
+                        c4.x *= sc; c4.y *= sc; c4.z *= sc; c4.w *= sc;
+                        const float4 ah = hi4(a), ch = hi4(c4);
+                        *reinterpret_cast<uint4 *>(dst + pc * 128) =
+                            make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+                        *reinterpret_cast<uint4 *>(dst + (4 + pc) * 128) =
+                            make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
+                                       pack_f16(c4.x - ch.x, c4.y - ch.y), pack_f16(c4.z - ch.z, c4.w - ch.w));
+                    }
+                    proxy_fence();
+                    arrive(&cv_v[t]);
+                }
+            }
+        }
+
+        // ---- one score tile: row maximum, exponentials, P_hi and P_lo over S in place ------------------
+        // `spar`: parity of s_full[buf] for this tile; `ptile`: index of its p_full barrier; `paired`: another
+        // group holds the other key tile of the same rows, `slot` tells the two apart.  Returns the row's
+        // partial sum of P.
+        auto softmax_tile = [&](int q, int k, int buf, uint32_t spar, int ptile, bool paired, int slot) -> float {
+            const uint32_t s_addr = lane_base + (uint32_t)(buf * kTile);
+            const int ncols = min(kTile, S - k * kTile);                      // keys of this tile that exist
+            const bool diag = CAUSAL && q == k;
+            const int nvalid = diag ? min(ncols, rloc + 1) : ncols;           // keys this row sees
+            const int nwarp = diag ? min(ncols, wq * 32 + 32) : ncols;        // ... the warp's last row sees
+            const int nmin = diag ? min(ncols, wq * 32 + 1) : ncols;          // ... its first row sees
+            const int nch = (nwarp + 31) >> 5;                                // 32-column chunks with any visible key
+            wait(&s_full[buf], spar, 3);
+            tc_fence_after();
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (c < nch) {
+                    float v[32];
+                    tmem_ld32(s_addr + c * 32, v);
+                    tmem_wait_ld();
+                    if (c * 32 + 32 > nmin) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j < nvalid) ? v[j] : -INFINITY;
+                    }
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        m4[0] = fmaxf(m4[0], v[j]); m4[1] = fmaxf(m4[1], v[j + 1]);
+                        m4[2] = fmaxf(m4[2], v[j + 2]); m4[3] = fmaxf(m4[3], v[j + 3]);
+                    }
+                    mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+                }
+            }
+            if (paired) {
+                xmax[par][q][slot][rloc] = mx;
+                arrive(&xm[q]);
+                wait(&xm[q], par, 6);
+                mx = fmaxf(mx, xmax[par][q][slot ^ 1][rloc]);
+            }
+            mx = fmaxf(mx, -1e30f);
+            const float nmc = kPShift - mx * cscale;     // p = 2^(s c - m c + 8)
+            float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t held[32];                           // P_lo of two chunks, kept until their columns have been read
+            // chunk c: scores in columns [32c, 32c+32); P_hi goes to [16c, 16c+16), P_lo to [64+16c, 64+16c+16)
+            auto chunk = [&](int c, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+                if (c < nch) {
+                    float v[32];
+                    tmem_ld32(s_addr + c * 32, v);
+                    tmem_wait_ld();
+                    if (c * 32 + 32 > nmin) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j < nvalid) ? v[j] : -INFINITY;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float p0 = ex2_approx(fmaf(v[j], cscale, nmc)), p1 = ex2_approx(fmaf(v[j + 1], cscale, nmc));
+                        ps[j & 3] += p0;
+                        ps[(j + 1) & 3] += p1;
+                        const float h0 = tf32_hi(p0), h1 = tf32_hi(p1);
+                        hi[j >> 1] = pack_f16(h0, h1);
+                        lo[j >> 1] = pack_f16(p0 - h0, p1 - h1);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) hi[j] = lo[j] = 0u;
+                }
+            };
+            {
+                uint32_t hi[16], lo[16];
+                chunk(0, hi, lo);
+                tmem_st16_u32(s_addr + 0, hi);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) held[j] = lo[j];
+                chunk(1, hi, lo);
+                tmem_st16_u32(s_addr + 16, hi);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) held[16 + j] = lo[j];
+                chunk(2, hi, lo);                        // columns 64..95 have been read
+                tmem_st16_u32(s_addr + 32, hi);
+                {
+                    uint32_t l0[16], l1[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) { l0[j] = held[j]; l1[j] = held[16 + j]; }
+                    tmem_st16_u32(s_addr + 64, l0);
+                    tmem_st16_u32(s_addr + 80, l1);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) held[j] = lo[j];
+                chunk(3, hi, lo);                        // columns 96..127 have been read
+                tmem_st16_u32(s_addr + 48, hi);
+                {
+                    uint32_t l2[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) l2[j] = held[j];
+                    tmem_st16_u32(s_addr + 96, l2);
+                }
+                tmem_st16_u32(s_addr + 112, lo);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            arrive(&p_full[ptile]);
+            const float l = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+            if (paired) {
+                xsum[par][q][slot][rloc] = l;
+                arrive(&xs[q]);
+            }
+            return l;
+        };
+        // ---- output columns [c0, c0 + nc) of query tile q: (P_hi V_hi + corrections) / (l * V's scale) ----
+        auto epilogue = [&](int q, int c0, int nc, bool paired, int slot, float l) {
+            if (paired) {
+                wait(&xs[q], par, 7);
+                l += xsum[par][q][slot ^ 1][rloc];
+            }
+            wait(&o_done[q], par, 5);
+            tc_fence_after();
+            const float inv = (1.0f / fmaxf(l, 1e-20f)) * s_vinv[par];
+            const int row = q * kTile + rloc;
+            const bool store = !abort_flag && row < S;
+            float4 *dst = reinterpret_cast<float4 *>(O + ((size_t)b * S + (row < S ? row : 0)) * (size_t)E + (size_t)h * 32);
+            const uint32_t o_addr = lane_base + kColO + (uint32_t)(q * 64);
+            for (int cc = c0; cc < c0 + nc; cc += 16) {
+                float a[16], c2[16];
+                tmem_ld16(o_addr + cc, a);
+                tmem_ld16(o_addr + 32 + cc, c2);
+                tmem_wait_ld();
+                if (store) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        dst[(cc >> 2) + j] = make_float4((a[4 * j] + c2[4 * j]) * inv, (a[4 * j + 1] + c2[4 * j + 1]) * inv,
+                                                         (a[4 * j + 2] + c2[4 * j + 2]) * inv, (a[4 * j + 3] + c2[4 * j + 3]) * inv);
+                }
+            }
+        };
+
+        if (nq == 1) {
+            if (grp == 0) {
+                const float l = softmax_tile(0, 0, 0, par, 0, false, 0);
+                epilogue(0, 0, 32, false, 0, l);
+            }
+        } else if (CAUSAL) {
+            if (grp == 0) {
+                const float l = softmax_tile(0, 0, 0, par, 0, false, 0);
+                epilogue(0, 0, 32, false, 0, l);
+            } else if (grp == 1) {
+                const float l = softmax_tile(1, 0, 1, par, 1, true, 0);
+                epilogue(1, 0, 16, true, 0, l);
+            } else {
+                const float l = softmax_tile(1, 1, 2, par, 2, true, 1);
+                epilogue(1, 16, 16, true, 1, l);
+            }
+        } else {
+            if (grp == 0) {
+                // s_full[0] completes twice per head here: parity 0 for (q0, k0), 1 for (q1, k1)
+                const float l0 = softmax_tile(0, 0, 0, 0u, 0, true, 0);
+                const float l3 = softmax_tile(1, 1, 0, 1u, 3, true, 1);
+                epilogue(0, 0, 16, true, 0, l0);
+                epilogue(1, 16, 16, true, 1, l3);
+            } else if (grp == 1) {
+                const float l = softmax_tile(0, 1, 1, par, 1, true, 1);
+                epilogue(0, 16, 16, true, 1, l);
+            } else {
+                const float l = softmax_tile(1, 0, 2, par, 2, true, 0);
+                epilogue(1, 0, 16, true, 0, l);
+            }
+        }
+        tc_fence_before();
+        arrive(&epi_done);
+    }
+    tc_fence_before();
+    __syncthreads();
+}
+
+// ---- host side: tensor maps and the launch ---------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Rank-3 map {E, S, B} over one fp32 plane; a box is [1][128 rows][32 floats], 128-byte swizzled, rows
+// past S read as zeros.
+int make_plane_map(CUtensorMap *m, const float *plane, int B, int S, int E)
+{
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(HIPGPT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {(cuuint64_t)E, (cuuint64_t)S, (cuuint64_t)B};
+    const cuuint64_t strides[2] = {(cuuint64_t)E * 4, (cuuint64_t)S * E * 4};
+    const cuuint32_t box[3] = {32, (cuuint32_t)kTile, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(plane), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(HIPGPT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return HIPGPT_OK;
+}
+
+template <bool CAUSAL>
+int launch_head_cfg(const HeadMaps &maps, float *out, int B, int S, int E, int H, cudaStream_t st)
+{
+    auto kern = mha_head_kernel<CAUSAL>;
+    const size_t smem = kHeadSmemBytes + 1024;
+    static bool attr_set = false;                    // per instantiation; setting it twice is harmless
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        sms = 148;
+    const long long bh = (long long)B * H;
+    if (bh > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "%lld (batch, head) pairs are too many", bh);
+    const unsigned grid = (unsigned)(bh < sms ? bh : sms);
+    const float cscale = (1.0f / sqrtf(32.0f)) * kLog2e;
+    kern<<<grid, kHeadThreads, smem, st>>>(maps, out, S, E, H, (int)bh, cscale);
+    return check_launch("mha_head_kernel");
+}
+
+}  // namespace
+
+// head_dim 32, at most 256 tokens, planes whose rows TMA can address (16-byte aligned base and row pitch)
+bool mha_head_supports(int head_dim, int S, int E, const void *q, const void *k, const void *v, const void *out)
+{
+    return head_dim == 32 && S >= 1 && S <= 2 * kTile && (E % 4) == 0 &&
+           ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+             reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+           encode_fn() != nullptr;
+}
+
+int launch_mha_head(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st)
+{
+    if (E / H != 32 || S > 2 * kTile) return fail(HIPGPT_ERR_UNSUPPORTED, "whole-head kernel: head_dim %d, S %d", E / H, S);
+    if (B == 0 || S == 0) return HIPGPT_OK;
+    HeadMaps maps;
+    int rc = make_plane_map(&maps.q, q, B, S, E);
+    if (rc == HIPGPT_OK) rc = make_plane_map(&maps.k, k, B, S, E);
+    if (rc == HIPGPT_OK) rc = make_plane_map(&maps.v, v, B, S, E);
+    if (rc != HIPGPT_OK) return rc;
+    return causal ? launch_head_cfg<true>(maps, out, B, S, E, H, st) : launch_head_cfg<false>(maps, out, B, S, E, H, st);
+}
+
+// Reads and clears a status word of this file.
+static int fetch_word(int &sym, int *value)
+{
+    int s = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&s, sym, sizeof(int));
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+    if (s != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(sym, &zero, sizeof(int));
+    }
+    *value = s;
+    return HIPGPT_OK;
+}
+int head_status_fetch(int *status) { return fetch_word(g_head_status, status); }
+int head_notice_fetch(int *notice) { return fetch_word(g_head_notice, notice); }
+
+}  // namespace hipgpt

@@ -46,23 +46,6 @@ constexpr int kM = 128;          // query rows per block
 
 __device__ int g_tc_status = 0;   // 0 ok; otherwise the site code of the first wait that ran out
 
-// Optional phase trace (build with -DHIPGPT_TC_TRACE): thread 0 and the issuing lane of block 0
-// store SM cycle counters at the marked points into a buffer given by hipgpt_debug_trace().
-// Layout: [0] start, [1] prologue done, [2 + 8*t + k] worker marks of tile t, [100 + 4*t + k]
-// issuing-lane marks, [99] end.  Compiled out by default.
-#ifdef HIPGPT_TC_TRACE
-__device__ long long *g_trace = nullptr;
-#define TC_TRACE_AT(i) do { if (g_trace && blockIdx.x == 0) g_trace[(i)] = clock64(); } while (0)
-// per block: [256 + 4*b] start ns, [+1] end ns, [+2] SM id
-__device__ __forceinline__ long long tc_gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ int tc_smid() { int r; asm volatile("mov.u32 %0, %%smid;" : "=r"(r)); return r; }
-#define TC_TRACE_BLOCK(k) do { if (g_trace && tid == 0) { g_trace[256 + 4 * blockIdx.x + (k)] = tc_gtime(); g_trace[256 + 4 * blockIdx.x + 2] = tc_smid(); } } while (0)
-#else
-#define TC_TRACE_BLOCK(k) do { } while (0)
-#define TC_TRACE_AT(i) do { } while (0)
-#endif
-#define TC_TRACE_W(k) do { if (tid == 0 && t < 12) TC_TRACE_AT(2 + 8 * t + (k)); } while (0)
-#define TC_TRACE_M(k) do { if (t < 12) TC_TRACE_AT(100 + 4 * t + (k)); } while (0)
 
 // Shape of one kernel variant.
 //   D        head_dim (32 or 64)
@@ -122,7 +105,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     const int kend = CAUSAL ? min(S, q0 + kM) : S;
     const int ntiles = (kend + KN - 1) / KN;
 
-    TC_TRACE_BLOCK(0);
     if (tid == 0) {
         abort_flag = 0;
         mbar_init(&mbar_s[0], 1);                // tcgen05.commit after Q K^T into S buffer 0 / 1
@@ -193,18 +175,14 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             };
             if (ntiles > 0) issue_qk(0);
             for (int t = 0; t < ntiles; ++t) {
-                TC_TRACE_M(0);
                 wait(&mbar_k, (uint32_t)(t & 1), 3);     // K(t+1) is in shared memory
                 tc_fence_after();
                 // MMAs of one thread execute in issue order: P V(t-1), which still reads P_hi from
                 // this S buffer, was issued before
-                TC_TRACE_M(1);
                 if (t + 1 < ntiles) issue_qk((t + 1) & 1);
-                TC_TRACE_M(2);
                 wait(&mbar_p, (uint32_t)(t & 1), 5);                    // P(t) is in TMEM
                 wait(&mbar_v[t & 1], (uint32_t)((t >> 1) & 1), 6);      // V(t) is in shared memory
                 tc_fence_after();
-                TC_TRACE_M(3);
                 issue_pv(t & 1);
             }
         }
@@ -285,7 +263,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     const int wq = warp & 3;                     // TMEM lane quadrant of this warp
     const int rloc = wq * 32 + lane;             // row inside the block = TMEM lane
     const int row = q0 + rloc;                   // this worker's query row
-    if (tid == 0) TC_TRACE_AT(0);
     {
         // Q: the workers of a row share its chunks
         constexpr int QC = CPR / HALVES;
@@ -306,7 +283,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     const uint32_t tmem = tmem_base_slot;
     const uint32_t lane_base = tmem + ((uint32_t)(wq * 32) << 16);   // this warp's 32 TMEM lanes
 
-    if (tid == 0) TC_TRACE_AT(1);
     float o[DW];
 #pragma unroll
     for (int d = 0; d < DW; ++d) o[d] = 0.0f;
@@ -337,10 +313,8 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     for (int t = 0; t < ntiles; ++t) {
         const int buf = t & 1;
         const int j0 = t * KN + half * 64;            // first key of this worker's 64 columns
-        TC_TRACE_W(0);
         wait(&mbar_s[buf], (uint32_t)((t >> 1) & 1), 1);     // S(t) is in TMEM
         tc_fence_after();
-        TC_TRACE_W(1);
 
         // ---- softmax of this worker's 64 scores (tcgen05 ops are warp-wide: uniform control flow) ----
         // Two sweeps over the scores in TMEM, so that only a few of them are in registers at
@@ -383,7 +357,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         const float mn = fmaxf(m, mx);            // m is finite (-1e30f at worst), so is mn
         const float alpha = ex2_approx(m - mn);
         m = mn;
-        TC_TRACE_W(3);
 
         // ---- the previous tile's P V: collect it; P_lo is free afterwards ----------------------
         if (t > 0) {
@@ -392,7 +365,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
             collect_o();
         }
         alpha_prev = alpha;
-        TC_TRACE_W(4);
 
         float psum = 0.0f;
         if (warp_dead) {
@@ -450,7 +422,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         }
         l = fmaf(l, alpha, psum);
         tmem_wait_st();
-        TC_TRACE_W(6);
         tc_fence_before();
         arrive(&mbar_p);
     }
@@ -467,8 +438,6 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
         asm volatile("bar.sync %0, 64;" ::"r"(1 + wq) : "memory");
         l += xchg[0][half ^ 1][rloc];
     }
-    if (tid == 0) TC_TRACE_AT(99);
-    TC_TRACE_BLOCK(1);
     if (!abort_flag && row < S) {
         const float inv = 1.0f / fmaxf(l, 1e-20f);
         float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + row) * (size_t)E + hcol + half * DW);
@@ -500,507 +469,21 @@ int launch_tc_cfg(const float *q, const float *k, const float *v, float *out, in
     return check_launch("mha_tc_kernel");
 }
 
-// =================================================================================================
-// Persistent variant: each block walks a list of (batch*head, query block) items and treats their
-// key tiles as one stream, so that the fixed cost of an item (fetching and staging Q, K(0), V(0);
-// the last P V and the output store) overlaps with its neighbours' work instead of leaving the
-// SM idle.  At S=256 that fixed cost is larger than the tile work itself.
-//   * the grid is (blocks per SM) x (number of SMs), or the number of items if that is smaller;
-//     block c takes items c, c+G, c+2G, ... of the heaviest-first order;
-//   * producers stage Q too (raw buffer by cp.async, then split), as soon as the last Q K^T of the
-//     previous item has completed; K tile T+1 follows Q K(T)^T, V tile T+1 follows P V(T) (one K
-//     and one V buffer);
-//   * workers finish an item (collect the last O_ext, normalise, store) inside the first tile of
-//     the next one;
-//   * every mbarrier is indexed by the running tile number (or item number for Q), and each wait
-//     site is at most one phase behind its barrier (argument in the comments at the waits).
-// =================================================================================================
-template <int D, int PRODUCERS>
-struct TcpCfg {
-    static constexpr int KN = 64;
-    static constexpr int WORKERS = kM;
-    static constexpr int THREADS = WORKERS + 32 + PRODUCERS;
-    static constexpr int DB = D / 32;
-    static constexpr int QBLK = kM * 32;
-    static constexpr int KBLK = KN * 32;
-    static constexpr uint32_t kColS = 0, kColPlo = 2 * KN, kColO = 3 * KN;
-    static constexpr uint32_t kTmemCols = (3 * KN + 2 * D) <= 256 ? 256 : 512;
-    static constexpr int BLOCKS_PER_SM = kTmemCols == 256 ? 2 : 1;
-    // Q hi/lo, K hi/lo, V hi/lo, raw Q, K, V
-    static constexpr size_t kSmemFloats = (size_t)2 * DB * QBLK + 2 * DB * KBLK + 2 * DB * KBLK + kM * D + 2 * KN * D;
-};
-
-// Position in a block's stream of tiles: item n of its list (bh, q0, nt tiles), tile t of that item.
-struct TileCursor {
-    int n, bh, q0, nt, t;
-    bool valid;
-};
-
-template <bool CAUSAL>
-__device__ __forceinline__ void cursor_load(TileCursor &c, int n, int first, int stride, int nitems, int BH, int nqblk, int S, int KN)
-{
-    const int i = first + n * stride;
-    c.n = n;
-    c.t = 0;
-    c.valid = i < nitems;
-    if (!c.valid) { c.bh = 0; c.q0 = 0; c.nt = 0; return; }
-    c.bh = i % BH;
-    const int qblk = CAUSAL ? (nqblk - 1 - i / BH) : (i / BH);          // heaviest first
-    c.q0 = qblk * kM;
-    const int kend = CAUSAL ? min(S, c.q0 + kM) : S;
-    c.nt = (kend + KN - 1) / KN;
-}
-template <bool CAUSAL>
-__device__ __forceinline__ void cursor_next(TileCursor &c, int first, int stride, int nitems, int BH, int nqblk, int S, int KN)
-{
-    if (++c.t >= c.nt) cursor_load<CAUSAL>(c, c.n + 1, first, stride, nitems, BH, nqblk, S, KN);
-}
-
-template <int D, int PRODUCERS, bool CAUSAL>
-__global__ void __launch_bounds__(TcpCfg<D, PRODUCERS>::THREADS, TcpCfg<D, PRODUCERS>::BLOCKS_PER_SM)
-mha_tcp_kernel(const float *__restrict__ Q, const float *__restrict__ K, const float *__restrict__ V,
-               float *__restrict__ O, int S, int E, int H, int BH, int nqblk, int nitems, float qscale)
-{
-    using C = TcpCfg<D, PRODUCERS>;
-    constexpr int KN = C::KN, DB = C::DB, QBLK = C::QBLK, KBLK = C::KBLK, WORKERS = C::WORKERS;
-    constexpr int CPR = D / 4;
-    constexpr uint32_t kColS = C::kColS, kColPlo = C::kColPlo, kColO = C::kColO;
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    float *base = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    float *q_hi = base, *q_lo = q_hi + DB * QBLK;
-    float *k_hi = q_lo + DB * QBLK, *k_lo = k_hi + DB * KBLK;
-    float *v_s = k_lo + DB * KBLK;               // [hi, lo][DB][KN][32]
-    float *q_raw = v_s + 2 * DB * KBLK;          // [128][D]
-    float *k_raw = q_raw + kM * D;               // [KN][D]
-    float *v_raw = k_raw + KN * D;
-    __shared__ uint64_t mbar_s[2], mbar_q, mbar_k, mbar_v, mbar_p, mbar_o;
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ volatile int abort_flag;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int first = blockIdx.x, stride = gridDim.x;
-
-    if (tid == 0) {
-        abort_flag = 0;
-        mbar_init(&mbar_s[0], 1);
-        mbar_init(&mbar_s[1], 1);
-        mbar_init(&mbar_q, PRODUCERS);
-        mbar_init(&mbar_k, PRODUCERS);
-        mbar_init(&mbar_v, PRODUCERS);
-        mbar_init(&mbar_p, WORKERS);
-        mbar_init(&mbar_o, 1);
-    }
-    if (warp == WORKERS / 32) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();                             // barriers initialised, TMEM allocated
-    tc_fence_after();
-    const uint32_t tmem = tmem_base_slot;
-
-    // site codes of the status word: 1 S ready (worker), 2 O ready (worker), 3 K staged, 4 Q staged,
-    // 5 P written, 6 V staged, 7 K buffer free (producer), 8 V buffer free (producer)
-    auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
-        if (abort_flag) return;
-        if (!mbar_wait(bar, parity)) { abort_flag = 1; atomicCAS(&g_tc_status, 0, 10 + site); }
-    };
-    auto arrive = [&](uint64_t *bar) {
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-    };
-    auto load_cursor = [&](TileCursor &c, int n) { cursor_load<CAUSAL>(c, n, first, stride, nitems, BH, nqblk, S, KN); };
-    auto next_tile = [&](TileCursor &c) { cursor_next<CAUSAL>(c, first, stride, nitems, BH, nqblk, S, KN); };
-
-    if (warp == WORKERS / 32) {
-        // ================= the issuing lane ========================================================
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = make_idesc(kM, KN, 0);
-            constexpr uint32_t idesc_pv1 = make_idesc(kM, 2 * D, 1);
-            constexpr uint32_t idesc_pv2 = make_idesc(kM, D, 1);
-            auto issue_qk = [&](int buf) {
-                uint32_t acc = 0;
-#pragma unroll
-                for (int pass = 0; pass < 3; ++pass) {
-                    const float *qa = pass == 0 ? q_lo : q_hi;       // correction terms first
-                    const float *kb = pass == 1 ? k_lo : k_hi;
-#pragma unroll
-                    for (int db = 0; db < DB; ++db) {
-                        const uint64_t da = make_desc(smem_u32(qa + db * QBLK), 16, 1024, 2);
-                        const uint64_t dk = make_desc(smem_u32(kb + db * KBLK), 16, 1024, 2);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            mma_ss(tmem + kColS + buf * KN, da + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, acc);
-                            acc = 1;
-                        }
-                    }
-                }
-                tc_commit(&mbar_s[buf]);
-            };
-            auto issue_pv = [&](int buf) {
-                const uint64_t dv = make_desc(smem_u32(v_s), KBLK * 4, 512, 1);
-#pragma unroll
-                for (int k = 0; k < KN / 8; ++k)
-                    mma_ts(tmem + kColO, tmem + kColS + buf * KN + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv1, k ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < KN / 8; ++k)
-                    mma_ts(tmem + kColO + D, tmem + kColPlo + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), idesc_pv2, 1);
-                tc_commit(&mbar_o);
-            };
-            TileCursor c;                        // the tile whose Q K^T is issued next
-            load_cursor(c, 0);
-            int T = 0;                           // running tile number of the tile whose P V comes next
-            if (c.valid) {
-                wait(&mbar_q, 0, 4);
-                wait(&mbar_k, 0, 3);
-                tc_fence_after();
-                issue_qk(0);
-                next_tile(c);
-            }
-            TileCursor pv;                       // the tile whose P V is issued next
-            load_cursor(pv, 0);
-            while (pv.valid) {
-                if (c.valid) {
-                    // Q K(T+1)^T.  Its S buffer held P_hi(T-1): P V(T-1) was issued before, and MMAs of
-                    // one thread execute in issue order.
-                    if (c.t == 0) wait(&mbar_q, (uint32_t)(c.n & 1), 4);       // Q of a new item
-                    wait(&mbar_k, (uint32_t)((T + 1) & 1), 3);
-                    tc_fence_after();
-                    issue_qk((T + 1) & 1);
-                    next_tile(c);
-                }
-                wait(&mbar_p, (uint32_t)(T & 1), 5);
-                wait(&mbar_v, (uint32_t)(T & 1), 6);
-                tc_fence_after();
-                issue_pv(T & 1);
-                next_tile(pv);
-                ++T;
-            }
-        }
-        __syncwarp();
-        tc_fence_before();
-        __syncthreads();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
-        return;
-    }
-
-    if (warp > WORKERS / 32) {
-        // ================= the producers ============================================================
-        constexpr int RPP = PRODUCERS / CPR;
-        constexpr int NPK = KN / RPP, NPQ = kM / RPP;
-        const int ptid = tid - WORKERS - 32;
-        const int sc = ptid % CPR, sr0 = ptid / CPR;
-        auto fetch_rows = [&](const float *__restrict__ plane, float *raw, int bh, int row0, int passes, bool live) {
-            const size_t tok0 = (size_t)(bh / H) * S;
-            const size_t hcol = (size_t)(bh % H) * D;
-            for (int p = 0; p < passes; ++p) {
-                const int r = sr0 + p * RPP;
-                const int j = row0 + r;
-                const bool ok = live && j < S;
-                cp_async16(raw + r * D + sc * 4, plane + (tok0 + (ok ? j : 0)) * (size_t)E + hcol + sc * 4, ok);
-            }
-            cp_async_commit();
-        };
-        auto store_q = [&]() {
-#pragma unroll
-            for (int p = 0; p < NPQ; ++p) {
-                const int r = sr0 + p * RPP;
-                float4 x = *reinterpret_cast<const float4 *>(q_raw + r * D + sc * 4);
-                x.x *= qscale; x.y *= qscale; x.z *= qscale; x.w *= qscale;
-                store_split(q_hi + (sc >> 3) * QBLK, q_lo + (sc >> 3) * QBLK, r, sc & 7, x);
-            }
-        };
-        auto store_k = [&]() {
-#pragma unroll
-            for (int p = 0; p < NPK; ++p) {
-                const int r = sr0 + p * RPP;
-                store_split(k_hi + (sc >> 3) * KBLK, k_lo + (sc >> 3) * KBLK, r, sc & 7,
-                            *reinterpret_cast<const float4 *>(k_raw + r * D + sc * 4));
-            }
-        };
-        auto store_v = [&]() {
-            float *blk = v_s + (sc >> 3) * KBLK;
-#pragma unroll
-            for (int p = 0; p < NPK; ++p) {
-                const int r = sr0 + p * RPP;
-                store_split_nmajor(blk, blk + DB * KBLK, r, sc & 7, *reinterpret_cast<const float4 *>(v_raw + r * D + sc * 4));
-            }
-        };
-        TileCursor cur, nxt;                     // tile T and tile T+1
-        load_cursor(cur, 0);
-        nxt = cur;
-        if (cur.valid) {
-            fetch_rows(Q, q_raw, cur.bh, cur.q0, NPQ, true);
-            fetch_rows(K, k_raw, cur.bh, 0, NPK, true);
-            fetch_rows(V, v_raw, cur.bh, 0, NPK, true);
-            cp_async_wait_all();
-            store_q();
-            store_k();
-            store_v();
-            proxy_fence();
-            arrive(&mbar_q);                     // phase 0: Q of item 0
-            arrive(&mbar_k);                     // phase 0: K of tile 0
-            arrive(&mbar_v);                     // phase 0: V of tile 0
-            next_tile(nxt);
-            // in flight from here on: K and V of tile T+1, and Q of the next item when tile T+1 opens it
-            if (nxt.valid) {
-                if (nxt.t == 0) fetch_rows(Q, q_raw, nxt.bh, nxt.q0, NPQ, true);
-                fetch_rows(K, k_raw, nxt.bh, nxt.t * KN, NPK, true);
-                fetch_rows(V, v_raw, nxt.bh, nxt.t * KN, NPK, true);
-            }
-        }
-        for (int T = 0; cur.valid; ++T) {
-            // Q K(T)^T has completed: the K buffer is free, and so is Q if tile T closed its item.
-            // (S barrier T&1 completes next for tile T+2, which is issued only after this thread
-            // has arrived for K(T+2), i.e. after this wait.)
-            wait(&mbar_s[T & 1], (uint32_t)((T >> 1) & 1), 7);
-            cp_async_wait_all();
-            if (nxt.valid) {
-                if (nxt.t == 0) { store_q(); proxy_fence(); arrive(&mbar_q); }
-                store_k();
-            }
-            proxy_fence();
-            arrive(&mbar_k);                     // phase T+1
-            // P V(T) has completed: the V buffer is free.  (O barrier completes next for tile T+1,
-            // which needs V(T+1) from this thread, i.e. after this wait.)
-            wait(&mbar_o, (uint32_t)(T & 1), 8);
-            if (nxt.valid) store_v();
-            proxy_fence();
-            arrive(&mbar_v);                     // phase T+1
-            cur = nxt;
-            next_tile(nxt);
-            if (nxt.valid) {
-                if (nxt.t == 0) fetch_rows(Q, q_raw, nxt.bh, nxt.q0, NPQ, true);
-                fetch_rows(K, k_raw, nxt.bh, nxt.t * KN, NPK, true);
-                fetch_rows(V, v_raw, nxt.bh, nxt.t * KN, NPK, true);
-            }
-        }
-        cp_async_wait_all();
-        __syncthreads();
-        return;
-    }
-
-    // ===================== the workers ===============================================================
-    const int rloc = warp * 32 + lane;           // row inside the block = TMEM lane
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    float o[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.0f;
-    float m = -1e30f, l = 0.0f, alpha_prev = 1.0f;
-
-    auto collect_o = [&]() {
-#pragma unroll
-        for (int g = 0; g < D / 32; ++g) {
-            float a[32], c[32];
-            tmem_ld32(lane_base + kColO + g * 32, a);
-            tmem_ld32(lane_base + kColO + D + g * 32, c);
-            tmem_wait_ld();
-#pragma unroll
-            for (int d = 0; d < 32; ++d) o[g * 32 + d] = fmaf(o[g * 32 + d], alpha_prev, a[d] + c[d]);
-        }
-    };
-    // normalise and store the finished item, then start the accumulators afresh
-    auto finish_item = [&](int bh, int q0) {
-        const int row = q0 + rloc;
-        if (!abort_flag && row < S) {
-            const float inv = 1.0f / fmaxf(l, 1e-20f);
-            float4 *dst = reinterpret_cast<float4 *>(O + ((size_t)(bh / H) * S + row) * (size_t)E + (size_t)(bh % H) * D);
-#pragma unroll
-            for (int c = 0; c < D / 4; ++c)
-                dst[c] = make_float4(o[c * 4 + 0] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
-        }
-#pragma unroll
-        for (int d = 0; d < D; ++d) o[d] = 0.0f;
-        l = 0.0f;
-    };
-
-    TileCursor cur;
-    load_cursor(cur, 0);
-    int prev_bh = 0, prev_q0 = 0;
-    int T = 0;
-    for (; cur.valid; ++T) {
-        const int buf = T & 1;
-        const int q0 = cur.q0;
-        const int row = q0 + rloc;
-        const int j0 = cur.t * KN;
-        if (cur.t == 0) m = -1e30f;              // a new item: fresh maximum (its sum and output are reset in finish_item)
-        // S(T) is in TMEM.  (S barrier T&1 completes next for tile T+2, issued after P V(T), which
-        // waits for this thread's arrival at the end of this iteration.)
-        wait(&mbar_s[buf], (uint32_t)((T >> 1) & 1), 1);
-        tc_fence_after();
-
-        const bool warp_dead = CAUSAL && j0 > q0 + warp * 32 + 31;
-        const bool need_mask = (CAUSAL && j0 + KN - 1 > q0 + warp * 32) || j0 + KN > S;
-        const int nvalid = min(S - j0, CAUSAL ? row - j0 + 1 : KN);
-        const uint32_t s_addr = lane_base + kColS + buf * KN;
-        float mx = -INFINITY;
-        if (!warp_dead) {
-            float v0[32], v1[32];
-            tmem_ld32(s_addr, v0);
-            tmem_ld32(s_addr + 32, v1);
-            tmem_wait_ld();
-            if (need_mask) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    v0[c] = (c < nvalid) ? v0[c] : -INFINITY;
-                    v1[c] = (32 + c < nvalid) ? v1[c] : -INFINITY;
-                }
-            }
-            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                m4[(c >> 1) & 1] = fmaxf(m4[(c >> 1) & 1], fmaxf(v0[c], v0[c + 1]));
-                m4[2 + ((c >> 1) & 1)] = fmaxf(m4[2 + ((c >> 1) & 1)], fmaxf(v1[c], v1[c + 1]));
-            }
-            mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        }
-        const float mn = fmaxf(m, mx);
-        const float alpha = cur.t == 0 ? 1.0f : ex2_approx(m - mn);
-        m = mn;
-
-        // the previous tile's P V (possibly the last one of the previous item): collect it; P_lo is
-        // free afterwards.  (O barrier completes next for tile T, which waits for this thread's
-        // arrival below.)
-        if (T > 0) {
-            wait(&mbar_o, (uint32_t)((T - 1) & 1), 2);
-            tc_fence_after();
-            collect_o();
-            if (cur.t == 0) finish_item(prev_bh, prev_q0);
-        }
-        alpha_prev = alpha;
-
-        float psum = 0.0f;
-        if (warp_dead) {
-            float z[16];
-#pragma unroll
-            for (int c = 0; c < 16; ++c) z[c] = 0.0f;
-#pragma unroll
-            for (int g = 0; g < KN / 16; ++g) {
-                tmem_st16(s_addr + g * 16, z);
-                tmem_st16(lane_base + kColPlo + g * 16, z);
-            }
-        } else if (need_mask) {
-#pragma unroll
-            for (int g = 0; g < KN / 16; ++g) {
-                float v[16], lo[16];
-                tmem_ld16(s_addr + g * 16, v);
-                tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const float p = (g * 16 + c < nvalid) ? ex2_approx(v[c] - mn) : 0.0f;
-                    psum += p;
-                    v[c] = tf32_hi(p);
-                    lo[c] = p - v[c];
-                }
-                tmem_st16(s_addr + g * 16, v);
-                tmem_st16(lane_base + kColPlo + g * 16, lo);
-            }
-        } else {
-            float curv[16], nxtv[16];
-            float ps4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            tmem_ld16(s_addr, curv);
-#pragma unroll
-            for (int g = 0; g < KN / 16; ++g) {
-                tmem_wait_ld();
-                if (g + 1 < KN / 16) tmem_ld16(s_addr + (g + 1) * 16, nxtv);
-                float lo[16];
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const float p = ex2_approx(curv[c] - mn);
-                    ps4[c & 3] += p;
-                    curv[c] = tf32_hi(p);
-                    lo[c] = p - curv[c];
-                }
-                tmem_st16(s_addr + g * 16, curv);
-                tmem_st16(lane_base + kColPlo + g * 16, lo);
-                if (g + 1 < KN / 16) {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) curv[c] = nxtv[c];
-                }
-            }
-            psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-        }
-        l = fmaf(l, alpha, psum);
-        tmem_wait_st();
-        tc_fence_before();
-        arrive(&mbar_p);                         // phase T
-        prev_bh = cur.bh;
-        prev_q0 = q0;
-        next_tile(cur);
-    }
-    if (T > 0) {
-        wait(&mbar_o, (uint32_t)((T - 1) & 1), 2);
-        tc_fence_after();
-        collect_o();
-        finish_item(prev_bh, prev_q0);
-    }
-    tc_fence_before();
-    __syncthreads();
-}
-
-template <int D, int PRODUCERS, bool CAUSAL>
-int launch_tcp_cfg(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, cudaStream_t st)
-{
-    using C = TcpCfg<D, PRODUCERS>;
-    auto kern = mha_tcp_kernel<D, PRODUCERS, CAUSAL>;
-    size_t smem = C::kSmemFloats * sizeof(float) + 1024;
-    if (C::BLOCKS_PER_SM == 2 && smem < 100 * 1024) smem = 100 * 1024;     // at most two blocks per SM (256 TMEM columns each)
-    if (C::BLOCKS_PER_SM == 1 && smem < 120 * 1024) smem = 120 * 1024;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-    }
-    const int nqblk = (S + kM - 1) / kM;
-    const long long nitems = (long long)B * H * nqblk;
-    if (nitems > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "%lld work items are too many", nitems);
-    const long long slots = (long long)sm_count * C::BLOCKS_PER_SM;
-    const unsigned grid = (unsigned)(nitems < slots ? nitems : slots);
-    const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<grid, C::THREADS, smem, st>>>(q, k, v, out, S, E, H, B * H, nqblk, (int)nitems, qscale);
-    return check_launch("mha_tcp_kernel");
-}
-
 }  // namespace
 
 bool mha_tc_supports(int D) { return D == 32 || D == 64; }
 
-// variant: 0 = default, 1 = 64-key tiles (two blocks per SM for head_dim 32), 2 = 128-key tiles with
-// two workers per row (head_dim 32 only, one block per SM), 3 = persistent blocks over a stream of tiles
+// The full-range split-TF32 kernel: 64-key tiles, one worker per query row.
 int launch_mha_tc(const float *q, const float *k, const float *v, float *out,
-                  int B, int S, int E, int H, int causal, cudaStream_t st, int variant)
+                  int B, int S, int E, int H, int causal, cudaStream_t st)
 {
     const int D = E / H;
-    if (variant == 4) return launch_mha_tc_pair(q, k, v, out, B, S, E, H, causal, st);
-    // default: fewer tensor-core instructions per tile and a softmax that runs ahead of the P V
-    // products; measured faster than variant 1 at every benchmark shape
-    if (variant == 5 || variant == 0) return launch_mha_tc16(q, k, v, out, nullptr, B, S, E, H, causal, st);
-    if (variant == 3) {
-        if (D == 32) return causal ? launch_tcp_cfg<32, 64, true>(q, k, v, out, B, S, E, H, st)
-                                   : launch_tcp_cfg<32, 64, false>(q, k, v, out, B, S, E, H, st);
-        if (D == 64) return causal ? launch_tcp_cfg<64, 64, true>(q, k, v, out, B, S, E, H, st)
-                                   : launch_tcp_cfg<64, 64, false>(q, k, v, out, B, S, E, H, st);
-    }
-    if (D == 32) {
-        const bool wide = variant == 2;
-        if (wide) return causal ? launch_tc_cfg<32, 128, 128, true>(q, k, v, out, B, S, E, H, st)
-                                : launch_tc_cfg<32, 128, 128, false>(q, k, v, out, B, S, E, H, st);
-        return causal ? launch_tc_cfg<32, 64, 64, true>(q, k, v, out, B, S, E, H, st)
-                      : launch_tc_cfg<32, 64, 64, false>(q, k, v, out, B, S, E, H, st);
-    }
+    if (D == 32) return causal ? launch_tc_cfg<32, 64, 64, true>(q, k, v, out, B, S, E, H, st)
+                               : launch_tc_cfg<32, 64, 64, false>(q, k, v, out, B, S, E, H, st);
     if (D == 64) return causal ? launch_tc_cfg<64, 64, 64, true>(q, k, v, out, B, S, E, H, st)
                                : launch_tc_cfg<64, 64, 64, false>(q, k, v, out, B, S, E, H, st);
     return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
 }
-
-#ifdef HIPGPT_TC_TRACE
-extern "C" __attribute__((visibility("default"))) int hipgpt_debug_trace(long long *d_buf)
-{
-    return (int)cudaMemcpyToSymbol(g_trace, &d_buf, sizeof(d_buf));
-}
-#endif
 
 // Reads and clears the status word of the tensor-core kernels (synchronises the device).
 int tc_status_fetch(int *status)

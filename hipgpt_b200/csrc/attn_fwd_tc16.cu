@@ -71,61 +71,20 @@ struct Tc16Cfg {
 };
 
 __device__ int g_tc16_status = 0;
+__device__ int g_tc16_notice = 0;                // bit 0: an operand left the range in which the fp16 correction terms are exact
 
-// Optional timeline (build with -DHIPGPT_TC_TRACE): worker 0 of every block stores nanosecond
-// timestamps: [0] start, [1] prologue done, [2 + t] P(t) written (t < 6), [8] end, [9] SM id.
-#ifdef HIPGPT_TC_TRACE
-__device__ long long *g_trace16 = nullptr;
-__device__ __forceinline__ long long t16_now() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define T16(i) do { if (trace && tid == 0) trace[(i)] = t16_now(); } while (0)
-// cycle counter marks of worker 0 ([10 + 4t + k]) and of the issuing lane ([34 + 4t + k]), t < 6; [60] cycle counter at start
-#define C16(i) do { if (trace) trace[(i)] = clock64(); } while (0)
-#else
-#define T16(i) do { } while (0)
-#define C16(i) do { } while (0)
-#endif
-
-// fp32 accumulator, fp16 A and B, both K-major
-__host__ __device__ constexpr uint32_t idesc_f16(int m, int n)
+__device__ __forceinline__ float amax8(float m, float4 a, float4 c)
 {
-    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+    return fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                          fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w)))));
 }
-
-__device__ __forceinline__ void mma_h_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+// The warp's largest magnitude into a shared word (as a bit pattern: non-negative floats order like integers).
+__device__ __forceinline__ void publish_amax(unsigned *slot, float m)
 {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(slot, __float_as_uint(m));
 }
-__device__ __forceinline__ void mma_h_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-// two floats -> one word of two fp16 (round to nearest, saturating), `lo` in the low half
-__device__ __forceinline__ uint32_t pack_f16(float lo, float hi)
-{
-    uint32_t r;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-
-__device__ __forceinline__ void tmem_st8_u32(uint32_t addr, const uint32_t (&v)[8])
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
-}
-
-__device__ __forceinline__ float4 hi4(float4 x) { return make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w)); }
-
-// byte offset of 16-byte chunk c of row r in a tile of 128-byte rows, SWIZZLE_128B
-__device__ __forceinline__ int sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
 
 // Which pieces of a 64-row tile a staging thread owns.  A piece is 32 bytes (8 floats) of a row; a
 // thread owns pieces of pairs of adjacent rows.  PT = threads that stage this operand, PPR = pieces per row.
@@ -156,14 +115,9 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     __shared__ uint64_t k_full[2], v_full[2], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
+    __shared__ unsigned s_amax[3];                   // largest |Q| (scaled), |K|, |V| this block has seen
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef HIPGPT_TC_TRACE
-    long long *trace = g_trace16 ? g_trace16 + 128 * (size_t)blockIdx.x : nullptr;
-    if (trace && tid == 0) { int sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); trace[9] = sm; }
-#endif
-    T16(0);
-    if (tid == 0) C16(60);
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);     // heaviest first
     const int b = bh / H, h = bh % H;
@@ -179,6 +133,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
 
     if (tid == 0) {
         abort_flag = 0;
+        s_amax[0] = s_amax[1] = s_amax[2] = 0u;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], PWK);              // one arrival per K warp
@@ -256,24 +211,18 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             };
             wait(&k_full[0], 0, 4);
             tc_fence_after();
-            C16(58);
             issue_qk(0, 0);
-            C16(59);
             for (int t = 0; t < nt; ++t) {
                 const int st = t & 1;
                 if (t + 1 < nt) {
                     wait(&k_full[st ^ 1], (uint32_t)(((t + 1) >> 1) & 1), 4);    // K(t+1) is in shared memory
                     tc_fence_after();
-                    if (t < 6) C16(34 + 4 * t);
                     issue_qk(st ^ 1, st ^ 1);        // its buffer held P(t-1): P V(t-1) was issued before, instructions run in order
-                    if (t < 6) C16(35 + 4 * t);
                 }
                 wait(&p_full[st], (uint32_t)((t >> 1) & 1), 5);                  // P(t) is in TMEM
                 wait(&v_full[st], (uint32_t)((t >> 1) & 1), 6);                  // V(t) is in shared memory
                 tc_fence_after();
-                if (t < 6) C16(36 + 4 * t);
                 issue_pv(st, st, t == 0);
-                if (t < 6) C16(37 + 4 * t);
             }
             if (PROBS) {
                 // X[u & 1] held P(u-2) (consumed by P V(u-2), issued before) or, from the third tile of
@@ -321,6 +270,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             }
             cp_async_commit();
         };
+        float amax = 0.0f;
         auto convert_k = [&](int stage) {
             uint8_t *khi = k_st + stage * kKStage + pblk * kKBlk, *k16 = k_st + stage * kKStage + C::kKhiBytes;
 #pragma unroll
@@ -336,6 +286,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                 for (int i = 0; i < BATCH; ++i) {
                     const int r = piece_row(half * BATCH + i);
                     const float4 ah = hi4(a[i]), ch = hi4(c[i]);
+                    amax = amax8(amax, a[i], c[i]);
                     *reinterpret_cast<uint4 *>(k16 + off16(r, pc, kKBlk)) =
                         make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
                     *reinterpret_cast<uint4 *>(k16 + off16(r, PPR + pc, kKBlk)) =
@@ -348,7 +299,6 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         __syncthreads();                             // matches the block-wide barrier after Q staging
         for (int u = 0; u < nk; ++u) {
             const int st = u & 1;
-            if (lane == 0 && u < 6) C16(64 + 4 * u);
             if (u + 1 < nk) {
                 if (u >= 1) wait(&s_full[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 7);   // Q K(u-1)^T has completed
                 copy_k(u + 1 < nt ? u + 1 : u + 1 - nt, st ^ 1);
@@ -356,13 +306,11 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                 cp_async_commit();                   // keeps the group count of the wait below
             }
             cp_async_wait_1();                       // K(u) has landed
-            if (lane == 0 && u < 6) C16(66 + 4 * u);
             convert_k(st);
-            if (lane == 0 && u < 6) C16(65 + 4 * u);
             proxy_fence();                           // generic-proxy writes -> visible to the tensor core
             arrive(&k_full[st]);
-            if (lane == 0 && u < 6) C16(67 + 4 * u);
         }
+        publish_amax(&s_amax[1], amax);
         cp_async_wait_all();
         __syncthreads();
         return;
@@ -384,6 +332,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             }
             cp_async_commit();
         };
+        float amax = 0.0f;
         auto convert_v = [&](int stage) {
             uint8_t *vhi = v_st + stage * kVStage + pblk * kKBlk, *vlo = vhi + DB * kKBlk, *v16 = v_st + stage * kVStage + C::kVhlBytes;
 #pragma unroll
@@ -399,6 +348,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                 for (int i = 0; i < BATCH; ++i) {
                     const int r = piece_row(half * BATCH + i);
                     const float4 ah = hi4(a[i]), ch = hi4(c[i]);
+                    amax = amax8(amax, a[i], c[i]);
                     *reinterpret_cast<float4 *>(vlo + nmaj(r, pch)) = make_float4(a[i].x - ah.x, a[i].y - ah.y, a[i].z - ah.z, a[i].w - ah.w);
                     *reinterpret_cast<float4 *>(vlo + nmaj(r, pch + 1)) = make_float4(c[i].x - ch.x, c[i].y - ch.y, c[i].z - ch.z, c[i].w - ch.w);
                     // fp16 copy, N-major without swizzle: 8 keys x 8 columns form one 128-byte core matrix (key i of
@@ -412,20 +362,17 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         __syncthreads();
         for (int u = 0; u < nt; ++u) {
             const int st = u & 1;
-            if (lane == 0 && u < 6) C16(96 + 4 * u);
             cp_async_wait_all();                     // V(u) has landed
-            if (lane == 0 && u < 6) C16(97 + 4 * u);
             convert_v(st);
             proxy_fence();
             arrive(&v_full[st]);
-            if (lane == 0 && u < 6) C16(98 + 4 * u);
             if (u + 1 < nt) {
                 // the stage of V(u+1) held V(u-1); V(u) is published before this warp waits for that product
                 if (u >= 1) wait(&o_done[st ^ 1], (uint32_t)(((u - 1) >> 1) & 1), 8);   // P V(u-1) has completed
                 copy_v(u + 1, st ^ 1);
             }
-            if (lane == 0 && u < 6) C16(99 + 4 * u);
         }
+        publish_amax(&s_amax[2], amax);
         cp_async_wait_all();
         __syncthreads();
         return;
@@ -436,6 +383,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     const int rloc = wq * 32 + lane;                 // row inside the block = TMEM lane
     const int row = q0 + rloc;
     {
+        float amax = 0.0f;
         const bool ok = row < S;
         const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
 #pragma unroll
@@ -445,6 +393,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             a.x *= qscale; a.y *= qscale; a.z *= qscale; a.w *= qscale;     // scores come out in the log2 domain
             c.x *= qscale; c.y *= qscale; c.z *= qscale; c.w *= qscale;
             const float4 ah = hi4(a), ch = hi4(c);
+            amax = amax8(amax, a, c);
             uint8_t *qb = q_hi + (j >> 2) * kQBlk;
             *reinterpret_cast<float4 *>(qb + sw128(rloc, 2 * (j & 3))) = ah;
             *reinterpret_cast<float4 *>(qb + sw128(rloc, 2 * (j & 3) + 1)) = ch;
@@ -454,6 +403,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             *reinterpret_cast<uint4 *>(q_16 + off16(rloc, PPR + j, kQBlk)) =
                 make_uint4(pack_f16(a.x, a.y), pack_f16(a.z, a.w), pack_f16(c.x, c.y), pack_f16(c.z, c.w));
         }
+        publish_amax(&s_amax[0], amax);
     }
     proxy_fence();
     tc_fence_before();
@@ -461,7 +411,6 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     tc_fence_after();
     const uint32_t lane_base = tmem_base_slot + ((uint32_t)(wq * 32) << 16);
     const uint32_t o_addr = lane_base + kColO;
-    T16(1);
 
     float m_ref = 0.0f, l = 0.0f;                    // reference maximum (log2 domain) and row sum
     for (int t = 0; t < nt; ++t) {
@@ -470,7 +419,6 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         const uint32_t s_addr = lane_base + kColX + buf * kKeys, l_addr = lane_base + kColL + buf * 32;
         wait(&s_full[buf], (uint32_t)((t >> 1) & 1), 1);   // S(t) is in TMEM
         tc_fence_after();
-        if (tid == 0 && t < 6) C16(10 + 4 * t);
         const int wrow0 = q0 + wq * 32;              // first row of this warp
         const bool warp_dead = CAUSAL && j0 > wrow0 + 31;          // these columns are above the diagonal for the whole warp
         const bool need_mask = (CAUSAL && j0 + kKeys - 1 > wrow0) || j0 + kKeys > S;
@@ -523,7 +471,6 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             }
         }
 
-        if (tid == 0 && t < 6) C16(11 + 4 * t);
         // ---- exponentials; P_hi over S in place, P_lo as packed fp16 ---------------------------------
         float psum = 0.0f;
         if (warp_dead) {
@@ -564,14 +511,11 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         tmem_wait_st();
         tc_fence_before();
         arrive(&p_full[buf]);
-        if (t < 6) T16(2 + t);
-        if (tid == 0 && t < 6) C16(12 + 4 * t);
     }
 
     {
         wait(&o_done[(nt - 1) & 1], (uint32_t)(((nt - 1) >> 1) & 1), 3);
         tc_fence_after();
-        if (tid == 0) C16(62);
         const float inv = 1.0f / fmaxf(l, 1e-20f);
         const bool store = !abort_flag && row < S;
         float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + (row < S ? row : 0)) * (size_t)E + hcol);
@@ -661,10 +605,17 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
             }
         }
     }
-    T16(8);
-    if (tid == 0) C16(61);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) {
+        // Range of the fp16 copies: beyond fp16's largest number a correction term saturates; below its smallest
+        // normal numbers it is flushed, an absolute error of up to 2^-25 per fp16 value, which matters when it is
+        // neither small in itself nor small beside the scores it is added to.  (Q carries the softmax scale here.)
+        const float aq = __uint_as_float(s_amax[0]), ak = __uint_as_float(s_amax[1]), av = __uint_as_float(s_amax[2]);
+        const bool over = !(aq <= 65504.0f) || !(ak <= 65504.0f) || !(av <= 65504.0f);
+        const float flush = (float)D * 2.98e-8f * (aq + ak);
+        if (over || (flush > 3.8e-6f && (aq + ak) > 8.0f * aq * ak)) atomicOr(&g_tc16_notice, 1);
+    }
 }
 
 template <int D, bool CAUSAL, bool PROBS>
@@ -711,15 +662,6 @@ int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, 
     }
 }
 
-#ifdef HIPGPT_TC_TRACE
-}  // namespace hipgpt
-extern "C" __attribute__((visibility("default"))) void hipgpt_debug_trace16(long long *buf)
-{
-    cudaMemcpyToSymbol(hipgpt::g_trace16, &buf, sizeof(buf));
-}
-namespace hipgpt {
-#endif
-
 int tc16_status_fetch(int *status)
 {
     int s = 0;
@@ -730,6 +672,19 @@ int tc16_status_fetch(int *status)
         cudaMemcpyToSymbol(g_tc16_status, &zero, sizeof(int));
     }
     *status = s;
+    return HIPGPT_OK;
+}
+
+int tc16_notice_fetch(int *notice)
+{
+    int s = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&s, g_tc16_notice, sizeof(int));
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+    if (s != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tc16_notice, &zero, sizeof(int));
+    }
+    *notice = s;
     return HIPGPT_OK;
 }
 

@@ -7,6 +7,9 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <stdlib.h>
+
+#include <atomic>
 #include <mutex>
 
 namespace hipgpt {
@@ -33,6 +36,21 @@ int check_launch(const char *what)
 
 namespace {
 
+// 0: fp32-grade kernels with fp16 correction terms (exact for operands within fp16's range);
+// 1: kernels whose accuracy holds over the whole fp32 range.  -1 until first read.
+std::atomic<int> g_full_range{-1};
+
+bool full_range()
+{
+    int v = g_full_range.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char *e = getenv("HIPGPT_FULL_RANGE");
+        v = (e && e[0] && e[0] != '0') ? 1 : 0;
+        g_full_range.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+
 int check_mha_args(const void *q, const void *k, const void *v, const void *out, int B, int S, int E, int H)
 {
     if (H <= 0 || E <= 0 || (E % H) != 0) return fail(HIPGPT_ERR_BAD_ARG, "Bad MHA config: E=%d H=%d", E, H);
@@ -52,12 +70,19 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
     const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                            reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                          (probs == nullptr || (reinterpret_cast<uintptr_t>(probs) & 15) == 0);
+    const bool tensor_ok = aligned && (D == 32 || D == 64);
     switch (algo) {
     case HIPGPT_ALGO_AUTO:
-        // tensor pipe when it applies (fp32-grade TF32 + FP16 products; with the probabilities
-        // it sweeps the key tiles twice); FFMA rows kernel for head_dim 128; generic kernel for everything else
-        if (mha_tc16_supports(D) && aligned && probs != nullptr) return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
-        if (mha_tc_supports(D) && aligned) return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
+        if (tensor_ok && full_range()) {
+            // operands of any fp32 magnitude: split-TF32 products; with the probabilities the exact FFMA kernel
+            if (!probs) return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
+            return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
+        }
+        // tensor pipe when it applies (fp32-grade TF32 + FP16 products): the whole-head kernel for the default
+        // model's shape, the tiled kernel otherwise (it also stores the probabilities, by a second sweep);
+        // FFMA rows kernel for head_dim 128; generic kernel for everything else
+        if (!probs && mha_head_supports(D, S, E, q, k, v, out)) return launch_mha_head(q, k, v, out, B, S, E, H, causal, st);
+        if (tensor_ok) return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
         if (mha_rows_supports(D) && aligned) return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
         return launch_mha_generic(q, k, v, out, probs, B, S, E, H, causal, st);
     case HIPGPT_ALGO_GENERIC:
@@ -67,12 +92,24 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
         return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
     case HIPGPT_ALGO_TENSOR:
         if (!aligned) return fail(HIPGPT_ERR_BAD_ARG, "tensor-core kernel needs 16-byte aligned pointers");
-        if (!mha_tc_supports(D)) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
-        if (probs) {
-            if (warps != 0 && warps != 5) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: only the default variant stores probabilities");
+        if (!tensor_ok) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
+        switch (warps) {                             // `warps` selects the kernel here
+        case HIPGPT_TENSOR_DEFAULT:
+            if (!probs && mha_head_supports(D, S, E, q, k, v, out)) return launch_mha_head(q, k, v, out, B, S, E, H, causal, st);
             return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
+        case HIPGPT_TENSOR_SPLIT_TF32:
+            if (probs) return fail(HIPGPT_ERR_UNSUPPORTED, "split-TF32 kernel stores no probabilities");
+            return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st);
+        case HIPGPT_TENSOR_TILED:
+            return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
+        case HIPGPT_TENSOR_WHOLE_HEAD:
+            if (probs) return fail(HIPGPT_ERR_UNSUPPORTED, "whole-head kernel stores no probabilities");
+            if (!mha_head_supports(D, S, E, q, k, v, out))
+                return fail(HIPGPT_ERR_UNSUPPORTED, "whole-head kernel: needs head_dim 32 and S <= 256 (head_dim %d, S %d)", D, S);
+            return launch_mha_head(q, k, v, out, B, S, E, H, causal, st);
+        default:
+            return fail(HIPGPT_ERR_BAD_ARG, "unknown tensor-core kernel %d", warps);
         }
-        return launch_mha_tc(q, k, v, out, B, S, E, H, causal, st, warps);   // `warps` selects the tile variant here
     default:
         return fail(HIPGPT_ERR_BAD_ARG, "unknown algo %d", algo);
     }
@@ -104,6 +141,22 @@ Workspace g_ws;
 }  // namespace hipgpt
 
 using namespace hipgpt;
+
+// First non-zero status word of the tensor-core kernels, as hipgpt_kernel_status reports it.
+static int fetch_status_words(int *status)
+{
+    int a = 0, b = 0, d = 0, h = 0;
+    int rc = tc_status_fetch(&a);
+    if (rc == HIPGPT_OK) rc = bf16_status_fetch(&b);
+    if (rc == HIPGPT_OK) rc = tc16_status_fetch(&d);
+    if (rc == HIPGPT_OK) rc = head_status_fetch(&h);
+    int pr = 0;
+    if (rc == HIPGPT_OK) rc = probe_status_fetch(&pr);
+    if (rc != HIPGPT_OK) return rc;
+    *status = a ? a : (b ? 100 + b : (d ? 300 + d : (h ? 400 + h : (pr ? 900 + pr : 0))));
+    return HIPGPT_OK;
+}
+
 
 extern "C" {
 
@@ -234,6 +287,11 @@ static int mha_forward_host_impl(const void *h_qkv_v, void *h_out_v, float *h_pr
     }
     e = cudaStreamSynchronize(s_out);                // its last copy waits for the last kernel, which waits for the last copy in
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "host-buffer call: %s", cudaGetErrorString(e));
+    // a block whose bounded wait ran out stored nothing: the output would be stale
+    int status = 0;
+    const int src = fetch_status_words(&status);
+    if (src != HIPGPT_OK) return src;
+    if (status != 0) return fail(HIPGPT_ERR_CUDA, "a bounded wait inside a kernel ran out (status %d); the output is incomplete", status);
     return HIPGPT_OK;
 }
 
@@ -308,9 +366,10 @@ int hipgpt_mha_decode(const float *d_q, const float *d_kcache, const float *d_vc
     const size_t need = hipgpt_mha_decode_scratch_bytes(B, H, D, ctx);
     if (need > 0 && (!d_scratch || scratch_bytes < need))
         return fail(HIPGPT_ERR_SCRATCH, "scratch of %zu bytes needed, %zu given", need, d_scratch ? scratch_bytes : (size_t)0);
-    if (D % 4 == 0 && ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_kcache) |
-                        reinterpret_cast<uintptr_t>(d_vcache) | reinterpret_cast<uintptr_t>(d_out) |
-                        reinterpret_cast<uintptr_t>(d_scratch)) & 15) != 0)
+    // only the vector kernels (head_dim % 4 == 0, up to 128) move 16 bytes at a time
+    if (D % 4 == 0 && D <= 128 && ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_kcache) |
+                                    reinterpret_cast<uintptr_t>(d_vcache) | reinterpret_cast<uintptr_t>(d_out) |
+                                    reinterpret_cast<uintptr_t>(d_scratch)) & 15) != 0)
         return fail(HIPGPT_ERR_BAD_ARG, "decode needs 16-byte aligned pointers");
     const int ns = need > 0 ? decode_splits(B, H, D, ctx) : 1;
     return launch_decode(d_q, d_kcache, d_vcache, d_out, d_scratch, B, H, D, ctx, cap, ns, static_cast<cudaStream_t>(stream));
@@ -331,18 +390,27 @@ int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end)
 int hipgpt_kernel_status(int *status)
 {
     if (!status) return fail(HIPGPT_ERR_NULL, "status must not be NULL");
-    int a = 0, b = 0, c = 0;
-    int rc = tc_status_fetch(&a);
+    const cudaError_t e = cudaDeviceSynchronize();   // the kernels may run on non-blocking streams
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    return fetch_status_words(status);
+}
+
+int hipgpt_accuracy_notice(int *notice)
+{
+    if (!notice) return fail(HIPGPT_ERR_NULL, "notice must not be NULL");
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    int n16 = 0, nh = 0;
+    int rc = tc16_notice_fetch(&n16);
+    if (rc == HIPGPT_OK) rc = head_notice_fetch(&nh);
     if (rc != HIPGPT_OK) return rc;
-    rc = bf16_status_fetch(&b);
-    if (rc != HIPGPT_OK) return rc;
-    rc = tc_pair_status_fetch(&c);
-    if (rc != HIPGPT_OK) return rc;
-    int d = 0;
-    rc = tc16_status_fetch(&d);
-    if (rc != HIPGPT_OK) return rc;
-    // 1xx: the bf16 kernel's wait sites, 2xx: the paired kernel's, 3xx: the tf32+fp16 kernel's
-    *status = a ? a : (b ? 100 + b : (c ? 200 + c : (d ? 300 + d : 0)));
+    *notice = n16 | nh;
+    return HIPGPT_OK;
+}
+
+int hipgpt_set_full_range(int on)
+{
+    g_full_range.store(on ? 1 : 0, std::memory_order_relaxed);
     return HIPGPT_OK;
 }
 

@@ -251,6 +251,7 @@ struct FusedArgs {
     const int *prompts;
     int B, n_prompt, n_new, nsteps, ns;
     unsigned *bar;                   // [0] arrivals, [1] generation
+    long long bar_limit;             // SM cycles a block waits at the barrier before it gives up
     unsigned *cnt;                   // [B*H] splits of a (batch, head) that have finished, zero between phases
     int *err;
 };
@@ -278,7 +279,7 @@ __device__ __forceinline__ bool grid_barrier(const FusedArgs &a, unsigned &gen, 
                 if (seen == target) break;
                 if ((++spins & 63u) == 0u) {
                     if (*reinterpret_cast<volatile int *>(a.err) != 0) { ok = 0; break; }
-                    if (clock64() - t0 > kBarrierLimitCycles) { atomicExch(a.err, 1); ok = 0; break; }
+                    if (clock64() - t0 > a.bar_limit) { atomicExch(a.err, 1); ok = 0; break; }
                 }
             }
         }
@@ -550,6 +551,11 @@ struct GptDecoder {
     bool persistent_ok = false;                      // head_dim, shared memory and co-residency allow it
     int grid_blocks = 0;
     size_t fused_smem = 0;
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};   // start, prompt done, all done
+    // test hook (hipgpt_gpt_debug_stall_barrier): the next persistent call starts with an arrival counter
+    // that can never complete and this wait limit, so that the barrier's give-up path runs
+    bool stall_next = false;
+    long long stall_limit = 0;
 };
 
 namespace {
@@ -745,8 +751,9 @@ int hipgpt_gpt_generate(hipgpt_gpt *handle, const int *h_prompts, int B, int n_p
     if (rc != HIPGPT_OK) return rc;
     CUDA_OK(cudaMemcpyAsync(g->d_prompts, h_prompts, (size_t)B * n_prompt * sizeof(int), cudaMemcpyHostToDevice, g->stream));
     CUDA_OK(cudaMemsetAsync(g->d_pos, 0, sizeof(int), g->stream));
-    cudaEvent_t e0, e1, e2;
-    CUDA_OK(cudaEventCreate(&e0)); CUDA_OK(cudaEventCreate(&e1)); CUDA_OK(cudaEventCreate(&e2));
+    for (cudaEvent_t &ev : g->ev)
+        if (!ev) CUDA_OK(cudaEventCreate(&ev));
+    const cudaEvent_t e0 = g->ev[0], e1 = g->ev[1], e2 = g->ev[2];
     CUDA_OK(cudaEventRecord(e0, g->stream));
     if (persistent) {
         FusedArgs a{};
@@ -757,6 +764,15 @@ int hipgpt_gpt_generate(hipgpt_gpt *handle, const int *h_prompts, int B, int n_p
         a.ids = g->d_ids; a.out_ids = g->d_out; a.pos_ptr = g->d_pos; a.prompts = g->d_prompts;
         a.B = B; a.n_prompt = n_prompt; a.n_new = n_new; a.ns = decode_splits(B, g->H, g->E / g->H, g->S);
         a.bar = g->d_bar; a.cnt = g->d_cnt; a.err = g->d_err;
+        a.bar_limit = kBarrierLimitCycles;
+        if (g->stall_next) {
+            // arrivals start at the grid size: no block ever sees itself as the last one
+            const unsigned poisoned = (unsigned)g->grid_blocks;
+            CUDA_OK(cudaMemcpyAsync(g->d_bar, &poisoned, sizeof(unsigned), cudaMemcpyHostToDevice, g->stream));
+            CUDA_OK(cudaStreamSynchronize(g->stream));
+            a.bar_limit = g->stall_limit;
+            g->stall_next = false;
+        }
         void *params[] = {&a};
         a.nsteps = n_prompt;                         // the prompt positions, then the remaining new tokens
         CUDA_OK(cudaLaunchCooperativeKernel((const void *)gpt_steps_kernel, dim3(g->grid_blocks), dim3(32 * kSeg), params, g->fused_smem, g->stream));
@@ -788,7 +804,6 @@ int hipgpt_gpt_generate(hipgpt_gpt *handle, const int *h_prompts, int B, int n_p
     cudaEventElapsedTime(&b, e1, e2);
     if (ms_prompt) *ms_prompt = a;
     if (ms_decode) *ms_decode = b;
-    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
     return rc;
 }
 
@@ -800,6 +815,17 @@ int hipgpt_gpt_set_mode(hipgpt_gpt *handle, int mode)
     if (mode == HIPGPT_GPT_MODE_PERSISTENT && !g->persistent_ok)
         return fail(HIPGPT_ERR_UNSUPPORTED, "persistent form needs head_dim %% 4 == 0, head_dim <= 128 and cooperative launch");
     g->mode = mode;
+    return HIPGPT_OK;
+}
+
+int hipgpt_gpt_debug_stall_barrier(hipgpt_gpt *handle, long long limit_cycles)
+{
+    GptDecoder *g = reinterpret_cast<GptDecoder *>(handle);
+    if (!g) return fail(HIPGPT_ERR_NULL, "handle must not be NULL");
+    if (limit_cycles <= 0 || limit_cycles > kBarrierLimitCycles) return fail(HIPGPT_ERR_BAD_ARG, "limit of %lld cycles out of range", limit_cycles);
+    if (!(g->mode == HIPGPT_GPT_MODE_PERSISTENT && g->persistent_ok)) return fail(HIPGPT_ERR_UNSUPPORTED, "the handle is not in the persistent mode");
+    g->stall_next = true;
+    g->stall_limit = limit_cycles;
     return HIPGPT_OK;
 }
 
@@ -818,6 +844,7 @@ void hipgpt_gpt_destroy(hipgpt_gpt *handle)
     if (g->d_bar) cudaFree(g->d_bar);
     if (g->d_cnt) cudaFree(g->d_cnt);
     if (g->d_err) cudaFree(g->d_err);
+    for (cudaEvent_t ev : g->ev) if (ev) cudaEventDestroy(ev);
     if (g->stream) cudaStreamDestroy(g->stream);
     delete g;
 }

@@ -28,9 +28,10 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity)
     return done != 0;
 }
 
-// Bounded wait for the phase with the given parity; false when the limit ran out.  A phase that
-// has already completed is recognised by one non-blocking test, without reading the clock.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+// Bounded wait for the phase with the given parity; false when the limit (SM cycles, and a number of
+// polls) ran out.  A phase that has already completed is recognised by one non-blocking test,
+// without reading the clock.
+__device__ __forceinline__ bool mbar_wait_for(uint64_t *bar, uint32_t parity, long long cycle_limit, long long poll_limit)
 {
     const uint32_t addr = smem_u32(bar);
     uint32_t done;
@@ -40,8 +41,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
-    const long long deadline = clock64() + kCycleLimit;
-    for (long long i = 0; i < kSpinLimit; ++i) {
+    const long long deadline = clock64() + cycle_limit;
+    for (long long i = 0; i < poll_limit; ++i) {
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -51,6 +52,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
         if ((i & 15) == 15 && clock64() > deadline) break;
     }
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) { return mbar_wait_for(bar, parity, kCycleLimit, kSpinLimit); }
+
+// One arrival that also announces `bytes` of asynchronous copies which will complete on this barrier.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// TMA: one box of a rank-3 tensor map (this GPU's own memory; no multicast) into shared memory; the
+// bytes count towards `bar`.  c0 is the innermost coordinate: c0 * element size must be a multiple
+// of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tensor_map, int c0, int c1, int c2, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -163,5 +181,49 @@ __device__ __forceinline__ void store_split_nmajor(float *hi_blk, float *lo_blk,
     *reinterpret_cast<float4 *>(hi_blk + off) = h;
     *reinterpret_cast<float4 *>(lo_blk + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
 }
+
+// ---- fp16 products (kind::f16) used for the correction terms and the all-fp16 P V product ----
+
+// fp32 accumulator, fp16 A and B, both K-major
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n)
+{
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_h_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_h_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// two floats -> one word of two fp16 (round to nearest, saturating), `lo` in the low half
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ void tmem_st8_u32(uint32_t addr, const uint32_t (&v)[8])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
+__device__ __forceinline__ float4 hi4(float4 x) { return make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w)); }
+
+// byte offset of 16-byte chunk c of row r in a tile of 128-byte rows, SWIZZLE_128B
+__device__ __forceinline__ int sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
 
 }  // namespace hipgpt

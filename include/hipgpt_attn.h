@@ -46,11 +46,21 @@ extern "C" {
 
 /* Kernel selector of hipgpt_mha_forward_ex (profiling and tests; 0 is what every other
  * entry point uses). */
-#define HIPGPT_ALGO_AUTO     0   /* tensor kernel (head_dim 32/64, no probabilities), else rows
-                                    kernel (head_dim 32/64/128), else generic kernel               */
+#define HIPGPT_ALGO_AUTO     0   /* tensor-core kernels for head_dim 32/64 (with or without the
+                                    probabilities), FFMA rows kernel for head_dim 128, generic kernel
+                                    for every other head_dim                                        */
 #define HIPGPT_ALGO_GENERIC  1   /* one warp per query row, any head_dim <= 512                    */
-#define HIPGPT_ALGO_ROWS     2   /* register-resident query rows, shared-memory K/V tiles          */
-#define HIPGPT_ALGO_TENSOR   3   /* tcgen05 split-TF32 kernel, head_dim 32/64, no probabilities    */
+#define HIPGPT_ALGO_ROWS     2   /* exact fp32 FFMA: register-resident query rows, shared-memory K/V */
+#define HIPGPT_ALGO_TENSOR   3   /* tcgen05 kernels, head_dim 32/64; `warps` picks one of HIPGPT_TENSOR_* */
+
+/* Tensor-core kernels (the `warps` argument of hipgpt_mha_forward_ex with HIPGPT_ALGO_TENSOR). */
+#define HIPGPT_TENSOR_DEFAULT     0   /* what HIPGPT_ALGO_AUTO runs: WHOLE_HEAD where it applies, else TILED */
+#define HIPGPT_TENSOR_SPLIT_TF32  1   /* three TF32 products per product: 1e-5 accuracy over the whole fp32 range;
+                                         stores no probabilities                                                */
+#define HIPGPT_TENSOR_TILED       5   /* TF32 main products + FP16 correction products, 64-key tiles, any S;
+                                         stores the probabilities by a second sweep when asked                  */
+#define HIPGPT_TENSOR_WHOLE_HEAD  6   /* head_dim 32, S <= 256: one block per (batch, head), TMA loads, 128-key
+                                         products, every score tile of the head in tensor memory                */
 
 /*
  * Fused multi-head attention forward:  out = softmax(Q K^T / sqrt(D)) V  per (batch, head).
@@ -68,15 +78,12 @@ HIPGPT_API int hipgpt_mha_forward(const float *d_q, const float *d_k, const floa
                        int B, int S, int E, int H, int causal, void *stream);
 
 /* The same with an explicit kernel selector (HIPGPT_ALGO_*).  `warps`: for HIPGPT_ALGO_ROWS the
- * number of warps per thread block (0 = default); for HIPGPT_ALGO_TENSOR the schedule variant
- * (profiling and tests): 0 default (= variant 5), 1 = split-TF32
- * with 64-key tiles, 2 = 128-key tiles with two workers per row (head_dim 32),
- * 3 = persistent blocks over a stream of tiles, 4 = two query tiles per block with the output
- * accumulated in tensor memory (head_dim 32), 5 = TF32 main products with FP16 correction
- * products and a softmax that runs ahead of the P V products.  All variants hold the same 1e-5
- * accuracy on unit-scale data; variant 5 keeps it for operand magnitudes within fp16's normal range
- * (about 1e-4 .. 6e4) and falls to plain TF32 grade (~3e-4 relative) beyond, variant 1 has the full
- * fp32 range. */
+ * number of warps per thread block (0 = default); for HIPGPT_ALGO_TENSOR one of HIPGPT_TENSOR_*.
+ * Every kernel holds 1e-5 on unit-scale data.  TILED and WHOLE_HEAD keep that accuracy while Q, K (and for
+ * TILED, V) stay within fp16's range (about 1e-4 .. 6e4; WHOLE_HEAD rescales V by a power of two per head,
+ * so V may have any magnitude); outside it their correction terms saturate or are flushed, the result
+ * falls to plain TF32 grade (~3e-4 relative), and the launch raises the flag that
+ * hipgpt_accuracy_notice() reports.  SPLIT_TF32 and the FFMA kernels have the full fp32 range. */
 HIPGPT_API int hipgpt_mha_forward_ex(const float *d_q, const float *d_k, const float *d_v,
                           float *d_out, float *d_probs,
                           int B, int S, int E, int H, int causal,
@@ -99,8 +106,7 @@ HIPGPT_API int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const v
                             int B, int S, int E, int H, int causal, void *stream);
 /* The same with the kernel's schedule exposed: variant 0 = the default, 1 = one worker thread per query
  * row (it owns the 64 scores of a tile), 2 = two worker threads per query row (32 scores each; twice the
- * warps per SM), 3 = two workers per row and tiles of 128 keys.  Same results to the stated tolerance; the row
- * sums differ in summation order. */
+ * warps per SM).  Same results to the stated tolerance; the row sums differ in summation order. */
 HIPGPT_API int hipgpt_mha_forward_bf16_ex(const void *d_q, const void *d_k, const void *d_v, void *d_out,
                                int B, int S, int E, int H, int causal, int variant, void *stream);
 
@@ -154,8 +160,10 @@ HIPGPT_API int hipgpt_mha_decode(const float *d_q, const float *d_kcache, const 
  * (HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES on every GPU that loads the library, until exit).
  *   - a call whose partial results do not fit returns HIPGPT_ERR_SCRATCH;
  *   - all calls on a GPU share that array: calls that may overlap on the GPU race, order them;
- *   - nothing is allocated or freed; the first call on each device looks up the array's
- *     device address, so make that call before any stream capture starts on the device.
+ *   - nothing is allocated or freed; every call looks up the array's device address (nothing is
+ *     cached, so the entry point stays valid across a cudaDeviceReset); the first lookup on a
+ *     device loads the library's module there, so make that call before any stream capture
+ *     starts on the device.
  */
 #define HIPGPT_DECODE_NOALLOC_SCRATCH_BYTES (1u << 20)
 HIPGPT_API int hipgpt_mha_decode_noalloc(const float *d_q, const float *d_kcache, const float *d_vcache, float *d_out,
@@ -215,12 +223,42 @@ HIPGPT_API int hipgpt_probe_fma(float *d_sink, int blocks, int iters, double *fl
 /*
  * Device-side status of the tensor-core kernels (no counterpart in the reference).  Their
  * waits on hardware barriers are bounded; a block whose wait runs out stores nothing and records
- * which wait it was: 1..8 for the split-TF32 kernel, 100 + site for the bf16 kernel, 200 + site
- * and 300 + site for the two other fp32 tensor-core variants.  This call waits for the device,
- * stores the status word in *status and clears it.  0 means every launch since the last call
- * completed normally.
+ * which wait it was: 1..8 for the split-TF32 kernel, 100 + site for the bf16 kernel, 300 + site
+ * for the tiled fp32 kernel, 400 + site for the whole-head kernel, 900 + site for the test hook
+ * hipgpt_debug_wait_expiry.  This call waits for the whole
+ * device (cudaDeviceSynchronize), stores the status word in *status and clears it.  0 means every
+ * launch since the last call completed normally.  Callers of the device-pointer entry points
+ * that need to know must poll this; hipgpt_mha_forward_host does it itself and returns
+ * HIPGPT_ERR_CUDA when the word is set.
  */
 HIPGPT_API int hipgpt_kernel_status(int *status);
+
+/*
+ * Accuracy notice of the default fp32 tensor-core kernels (no counterpart in the reference: its kernels
+ * are plain fp32).  Bit 0 of *notice is set when, since the last call, some launch met Q, K or V values
+ * outside the range in which its fp16 correction terms are exact (beyond +-65504, or so small beside the
+ * other operand that the flushed bits matter): that launch's result is TF32-grade (~3e-4 relative), not
+ * 1e-5-grade.  Waits for the device, then reads and clears the flag.
+ * hipgpt_set_full_range(1) (or the environment variable HIPGPT_FULL_RANGE=1, read at the first call)
+ * makes every entry point, the reference-named launchers included, use the kernels whose accuracy does
+ * not depend on magnitude (split-TF32; exact FFMA when the probabilities are stored).
+ */
+HIPGPT_API int hipgpt_accuracy_notice(int *notice);
+HIPGPT_API int hipgpt_set_full_range(int on);
+
+/*
+ * Test hooks for the give-up paths (no counterpart in the reference).  Nothing here traps, faults or
+ * spins without a limit.
+ *   hipgpt_debug_wait_expiry  launches two small blocks that run the tensor-core kernels' wait protocol
+ *       (bounded mbarrier wait, abort flag, status word, stores skipped) on a barrier at which nothing
+ *       arrives, with a limit of `limit_cycles` SM cycles (at most 2^24, a few milliseconds).  Afterwards
+ *       hipgpt_kernel_status() reports 907 and d_canary[0..n) is untouched.
+ *   hipgpt_gpt_debug_stall_barrier  makes the NEXT persistent-mode hipgpt_gpt_generate call start with a
+ *       grid-barrier counter that cannot complete and a wait limit of `limit_cycles`: every block gives up
+ *       at its first barrier, the call returns HIPGPT_ERR_CUDA, and the handle stays usable.
+ */
+HIPGPT_API int hipgpt_debug_wait_expiry(float *d_canary, int n, long long limit_cycles, void *stream);
+HIPGPT_API int hipgpt_gpt_debug_stall_barrier(hipgpt_gpt *g, long long limit_cycles);
 
 /* Text of the calling thread's most recent failure ("" if none). */
 HIPGPT_API const char *hipgpt_last_error(void);

@@ -38,7 +38,7 @@ SHAPES = [(1, 1, 1, 64), (2, 2, 7, 64), (1, 2, 64, 64), (1, 1, 128, 64), (1, 3, 
 
 @pytest.mark.parametrize("shape", SHAPES)
 @pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("variant", [1, 2, 3])       # one or two worker threads per query row; 3: two workers and 128-key tiles
+@pytest.mark.parametrize("variant", [1, 2])       # one or two worker threads per query row
 def test_bf16_kernel_matches_oracle(shape, causal, variant):
     B, H, S, D = shape
     E = H * D
@@ -58,7 +58,7 @@ def test_bf16_rows_whose_maximum_grows_late():
     ramp = (1.0 + np.arange(S, dtype=np.float32) / 40.0)[:, None]
     qkv[1] = np.sign(qkv[0][:1]) * ramp          # K rows grow along the sequence, aligned with the first query
     qkv[0] = np.abs(qkv[0]) * np.sign(qkv[0][:1])
-    for causal, variant in [(False, 1), (True, 1), (False, 2), (True, 2), (False, 3), (True, 3)]:
+    for causal, variant in [(False, 1), (True, 1), (False, 2), (True, 2)]:
         out, rounded = _run(qkv, B, S, E, H, causal, variant)
         ref_out, _ = ob.mha(rounded, B, S, E, H, causal=causal)
         assert _status() == 0

@@ -10,6 +10,7 @@ import numpy as np
 import pytest
 
 from hipgpt_b200 import _capi, synth
+from oracle import bindings as ob
 
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
@@ -33,6 +34,10 @@ def _call_pair(lib, B, H, D, ctx, cap, seed):
     _capi.check(lib.hipgpt_mha_decode_noalloc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), got.data_ptr(),
                                               B, H, D, ctx, cap, st))
     torch.cuda.synchronize()
+    # the CPU oracle's single-row attention on the same inputs: the entry point is checked against the
+    # reference arithmetic too, not only against its sibling kernel launch
+    ref = ob.decode_row(q.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), B, H, D, ctx, cap)
+    assert float(np.abs(got.cpu().numpy() - ref).max()) <= TOL
     return want.cpu().numpy(), got.cpu().numpy(), nbytes
 
 
