@@ -58,6 +58,60 @@ constexpr long long kHeadPollLimit = 1LL << 22;
 __device__ int g_head_status = 0;                // first wait site that ran out (0 = none)
 __device__ int g_head_notice = 0;                // bit 0: Q or K left the range in which the fp16 correction terms are exact
 
+// Largest score of one 32-column chunk; columns from `nvalid` on (counted from the tile's first column) are hidden.
+__device__ __forceinline__ float chunk_max(float (&v)[32], int col0, int nvalid, bool need_mask)
+{
+    if (need_mask) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (col0 + j < nvalid) ? v[j] : -INFINITY;
+    }
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        m4[0] = fmaxf(m4[0], v[j]); m4[1] = fmaxf(m4[1], v[j + 1]);
+        m4[2] = fmaxf(m4[2], v[j + 2]); m4[3] = fmaxf(m4[3], v[j + 3]);
+    }
+    return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+}
+
+// One chunk of scores -> P = 2^(s c + nmc), cut into fp16 hi and lo, written over the chunk's own 32 TMEM
+// columns (16 of packed P_hi, then 16 of packed P_lo).  Returns the sum of P.
+__device__ __forceinline__ float chunk_exp(float (&v)[32], uint32_t addr, int col0, int nvalid, bool need_mask, float cscale, float nmc)
+{
+    if (need_mask) {
+        // a hidden score becomes -inf: its exponential is exactly 0
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (col0 + j < nvalid) ? v[j] : -INFINITY;
+    }
+    float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+            const float s0 = v[16 * half + j], s1 = v[16 * half + j + 1];
+            const float p0 = ex2_approx(fmaf(s0, cscale, nmc)), p1 = ex2_approx(fmaf(s1, cscale, nmc));
+            ps[j & 3] += p0;
+            ps[(j + 1) & 3] += p1;
+            const float h0 = tf32_hi(p0), h1 = tf32_hi(p1);      // 11 leading bits: exact in fp16
+            hi[j >> 1] = pack_f16(h0, h1);
+            lo[j >> 1] = pack_f16(p0 - h0, p1 - h1);
+        }
+        tmem_st8_u32(addr + 8 * half, hi);
+        tmem_st8_u32(addr + 16 + 8 * half, lo);
+    }
+    return (ps[0] + ps[1]) + (ps[2] + ps[3]);
+}
+
+__device__ __forceinline__ void chunk_zero(uint32_t addr)
+{
+    uint32_t z[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) z[j] = 0u;
+    tmem_st16_u32(addr, z);
+    tmem_st16_u32(addr + 16, z);
+}
+
 struct HeadMaps {
     CUtensorMap q, k, v;
 };
@@ -159,13 +213,14 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
             };
             auto issue_pv = [&](int q, int k, int buf, bool first) {
                 const uint32_t d = tmem + kColO + (uint32_t)(q * 64);
-                const uint32_t a_hi = tmem + (uint32_t)(buf * kTile), a_lo = a_hi + 64;
+                // keys 32c .. 32c+31 of the tile: P_hi in columns [32c, 32c+16) of the buffer, P_lo in [32c+16, 32c+32)
+                const uint32_t a0 = tmem + (uint32_t)(buf * kTile);
                 const uint64_t dv = make_desc(smem_u32(v_16 + k * kTileBytes), 1024, 128, 0);
                 const int nks = (min(kTile, S - k * kTile) + 15) >> 4;        // 16 keys per instruction; keys past S hold zeros
                 for (int ks = 0; ks < nks; ++ks)     // 16 keys = 8 TMEM columns of packed fp16 = two key groups of V
-                    mma_h_ts(d, a_hi + (uint32_t)(ks * 8), dv + (uint64_t)(ks * 128), id_pv_a, (first && ks == 0) ? 0u : 1u);
+                    mma_h_ts(d, a0 + (uint32_t)(32 * (ks >> 1) + 8 * (ks & 1)), dv + (uint64_t)(ks * 128), id_pv_a, (first && ks == 0) ? 0u : 1u);
                 for (int ks = 0; ks < nks; ++ks)
-                    mma_h_ts(d + 32, a_lo + (uint32_t)(ks * 8), dv + (uint64_t)(ks * 128), id_pv_b, 1u);
+                    mma_h_ts(d + 32, a0 + (uint32_t)(32 * (ks >> 1) + 8 * (ks & 1) + 16), dv + (uint64_t)(ks * 128), id_pv_b, 1u);
             };
             int it = 0;
             for (int hd = blockIdx.x; hd < BH; hd += gridDim.x, ++it) {
@@ -254,70 +309,95 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
     tc_fence_after();
     const uint32_t lane_base = tmem_base_slot + ((uint32_t)(wq * 32) << 16);
 
+    // The score tiles this group owns, packed: bit 0 query tile, 1 key tile, 2-3 S/P buffer, 4-5 index of the
+    // p_full barrier, 6 slot in the exchange with the group that holds the other key tile of the same rows,
+    // 7 whether there is such a group, 8-9 parity of s_full[buffer] (0: the head's parity, 1: always 0, 2: always 1).
+    auto mk = [](int q, int k, int buf, int ptile, int slot, int paired, int sp) {
+        return (uint32_t)(q | (k << 1) | (buf << 2) | (ptile << 4) | (slot << 6) | (paired << 7) | (sp << 8));
+    };
+    uint32_t job0 = 0, job1 = 0;
+    int njobs = 0;
+    if (nq == 1) {
+        if (grp == 0) { job0 = mk(0, 0, 0, 0, 0, 0, 0); njobs = 1; }
+    } else if (CAUSAL) {
+        njobs = 1;
+        job0 = grp == 0 ? mk(0, 0, 0, 0, 0, 0, 0) : grp == 1 ? mk(1, 0, 1, 1, 0, 1, 0) : mk(1, 1, 2, 2, 1, 1, 0);
+    } else {
+        // s_full[0] completes twice per head here: first for (q0, k0), then for (q1, k1)
+        njobs = grp == 0 ? 2 : 1;
+        job0 = grp == 0 ? mk(0, 0, 0, 0, 0, 1, 1) : grp == 1 ? mk(0, 1, 1, 1, 1, 1, 0) : mk(1, 0, 2, 2, 0, 1, 0);
+        job1 = mk(1, 1, 0, 3, 1, 1, 2);
+    }
+
+    // ---- conversion of K (group 0) or Q (group 1) for the head this block takes `itn`-th: thread = one row of each tile ----
+    auto convert_kq = [&](int itn) {
+        const uint32_t parn = (uint32_t)(itn & 1);
+        // K: [K_hi | K_lo];  Q: [Q_lo | Q].  hi = the 11 leading bits (exact in fp16), lo = x - hi.
+        uint8_t *raw = grp == 0 ? k_raw : q_raw, *dst16 = grp == 0 ? k_16 : q_16;
+        uint64_t *ld = grp == 0 ? ld_k : ld_q, *cv = grp == 0 ? cv_k : cv_q;
+        float amax = 0.0f;
+        for (int t = 0; t < nq; ++t) {
+            wait(&ld[t], parn, 1);
+            const uint8_t *src = raw + t * kTileBytes;
+            uint8_t *dst = dst16 + t * kTileBytes;
+            float4 x[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) x[c] = *reinterpret_cast<const float4 *>(src + sw128(rloc, c));
+#pragma unroll
+            for (int pc = 0; pc < 4; ++pc) {
+                const float4 a = x[2 * pc], c4 = x[2 * pc + 1];
+                const float4 ah = hi4(a), ch = hi4(c4);
+                amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                                         fmaxf(fmaxf(fabsf(c4.x), fabsf(c4.y)), fmaxf(fabsf(c4.z), fabsf(c4.w)))));
+                const uint4 lo = make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
+                                            pack_f16(c4.x - ch.x, c4.y - ch.y), pack_f16(c4.z - ch.z, c4.w - ch.w));
+                if (grp == 0) {
+                    *reinterpret_cast<uint4 *>(dst + sw128(rloc, pc)) =
+                        make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+                    *reinterpret_cast<uint4 *>(dst + sw128(rloc, 4 + pc)) = lo;
+                } else {
+                    *reinterpret_cast<uint4 *>(dst + sw128(rloc, pc)) = lo;
+                    *reinterpret_cast<uint4 *>(dst + sw128(rloc, 4 + pc)) =
+                        make_uint4(pack_f16(a.x, a.y), pack_f16(a.z, a.w), pack_f16(c4.x, c4.y), pack_f16(c4.z, c4.w));
+                }
+            }
+            if (t == nq - 1) {
+                // a NaN compares false everywhere: its bit pattern is what reaches the range test
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                if (lane == 0) atomicMax(&s_amax[grp == 0 ? 1 : 0], __float_as_uint(amax));
+            }
+            proxy_fence();                       // generic-proxy writes -> visible to the tensor core
+            arrive(&cv[t]);
+        }
+    };
+    if (grp < 2 && (int)blockIdx.x < BH) convert_kq(0);
+
     int it = 0;
     for (int hd = blockIdx.x; hd < BH; hd += gridDim.x, ++it) {
         const uint32_t par = (uint32_t)(it & 1);
         const int b = hd / H, h = hd % H;
 
-        // ---- operand conversion: thread = one row of each tile ------------------------------------------
-        if (grp < 2) {
-            // K: [K_hi | K_lo];  Q: [Q_lo | Q].  hi = the 11 leading bits (exact in fp16), lo = x - hi.
-            uint8_t *raw = grp == 0 ? k_raw : q_raw, *dst16 = grp == 0 ? k_16 : q_16;
-            uint64_t *ld = grp == 0 ? ld_k : ld_q, *cv = grp == 0 ? cv_k : cv_q;
-            float amax = 0.0f;
-            for (int t = 0; t < nq; ++t) {
-                wait(&ld[t], par, 1);
-                const uint8_t *src = raw + t * kTileBytes;
-                uint8_t *dst = dst16 + t * kTileBytes;
-                float4 x[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) x[c] = *reinterpret_cast<const float4 *>(src + sw128(rloc, c));
-#pragma unroll
-                for (int pc = 0; pc < 4; ++pc) {
-                    const float4 a = x[2 * pc], c4 = x[2 * pc + 1];
-                    const float4 ah = hi4(a), ch = hi4(c4);
-                    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
-                                             fmaxf(fmaxf(fabsf(c4.x), fabsf(c4.y)), fmaxf(fabsf(c4.z), fabsf(c4.w)))));
-                    const uint4 lo = make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
-                                                pack_f16(c4.x - ch.x, c4.y - ch.y), pack_f16(c4.z - ch.z, c4.w - ch.w));
-                    if (grp == 0) {
-                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, pc)) =
-                            make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
-                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, 4 + pc)) = lo;
-                    } else {
-                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, pc)) = lo;
-                        *reinterpret_cast<uint4 *>(dst + sw128(rloc, 4 + pc)) =
-                            make_uint4(pack_f16(a.x, a.y), pack_f16(a.z, a.w), pack_f16(c4.x, c4.y), pack_f16(c4.z, c4.w));
-                    }
-                }
-                if (t == nq - 1) {
-                    // a NaN compares false everywhere: its bit pattern is what reaches the range test
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                    if (lane == 0) atomicMax(&s_amax[grp == 0 ? 1 : 0], __float_as_uint(amax));
-                }
-                proxy_fence();                       // generic-proxy writes -> visible to the tensor core
-                arrive(&cv[t]);
-            }
-        } else {
+        // ---- conversion of V (group 2): scaled by a power of two so that the head's largest magnitude lies in
+        // [2^14, 2^15), then [V_hi | V_lo], before the group turns to its score tile.  (Placed between the
+        // group's two sweeps it ran beside the other groups' exponentials and took longer: measured slower.)
+        // K and Q of this head were converted before the loop (first head) or behind the previous head's
+        // exponentials.
+        auto convert_v = [&]() {
             // V: scaled by a power of two so that the head's largest magnitude lies in [2^14, 2^15), then
             // [V_hi | V_lo].  The previous head's P V products must have completed before V16 is overwritten.
             if (it > 0) {
                 wait(&o_done[0], (uint32_t)((it - 1) & 1), 5);
                 if (nq == 2) wait(&o_done[1], (uint32_t)((it - 1) & 1), 5);
             }
-            float4 x[2][8];
             float amax = 0.0f;
+            for (int t = 0; t < nq; ++t) {
+                wait(&ld_v[t], par, 1);
+                const uint8_t *src = v_raw + t * kTileBytes;
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                if (t < nq) {
-                    wait(&ld_v[t], par, 1);
-                    const uint8_t *src = v_raw + t * kTileBytes;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        x[t][c] = *reinterpret_cast<const float4 *>(src + sw128(rloc, c));
-                        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(x[t][c].x), fabsf(x[t][c].y)), fmaxf(fabsf(x[t][c].z), fabsf(x[t][c].w))));
-                    }
+                for (int c = 0; c < 8; ++c) {
+                    const float4 x = *reinterpret_cast<const float4 *>(src + sw128(rloc, c));
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
                 }
             }
 #pragma unroll
@@ -334,34 +414,42 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                 inv = __uint_as_float((uint32_t)(127 - sh) << 23);
             }
             if (tid == 2 * kTile) s_vinv[par] = inv;
+            for (int t = 0; t < nq; ++t) {
+                const int key = t * kTile + rloc;
+                const uint8_t *src = v_raw + t * kTileBytes;
+                uint8_t *dst = v_16 + (key >> 3) * 1024 + (key & 7) * 16;
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                if (t < nq) {
-                    const int key = t * kTile + rloc;
-                    uint8_t *dst = v_16 + (key >> 3) * 1024 + (key & 7) * 16;
-#pragma unroll
-                    for (int pc = 0; pc < 4; ++pc) {
-                        float4 a = x[t][2 * pc], c4 = x[t][2 * pc + 1];
-                        a.x *= sc; a.y *= sc; a.z *= sc; a.w *= sc;
-                        c4.x *= sc; c4.y *= sc; c4.z *= sc; c4.w *= sc;
-                        const float4 ah = hi4(a), ch = hi4(c4);
-                        *reinterpret_cast<uint4 *>(dst + pc * 128) =
-                            make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
-                        *reinterpret_cast<uint4 *>(dst + (4 + pc) * 128) =
-                            make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
-                                       pack_f16(c4.x - ch.x, c4.y - ch.y), pack_f16(c4.z - ch.z, c4.w - ch.w));
-                    }
-                    proxy_fence();
-                    arrive(&cv_v[t]);
+                for (int pc = 0; pc < 4; ++pc) {
+                    float4 a = *reinterpret_cast<const float4 *>(src + sw128(rloc, 2 * pc));
+                    float4 c4 = *reinterpret_cast<const float4 *>(src + sw128(rloc, 2 * pc + 1));
+                    a.x *= sc; a.y *= sc; a.z *= sc; a.w *= sc;
+                    c4.x *= sc; c4.y *= sc; c4.z *= sc; c4.w *= sc;
+                    const float4 ah = hi4(a), ch = hi4(c4);
+                    *reinterpret_cast<uint4 *>(dst + pc * 128) =
+                        make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+                    *reinterpret_cast<uint4 *>(dst + (4 + pc) * 128) =
+                        make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
+                                   pack_f16(c4.x - ch.x, c4.y - ch.y), pack_f16(c4.z - ch.z, c4.w - ch.w));
                 }
+                proxy_fence();
+                arrive(&cv_v[t]);
             }
-        }
+        
+        };
+        if (grp == 2) convert_v();
 
-        // ---- one score tile: row maximum, exponentials, P_hi and P_lo over S in place ------------------
-        // `spar`: parity of s_full[buf] for this tile; `ptile`: index of its p_full barrier; `paired`: another
-        // group holds the other key tile of the same rows, `slot` tells the two apart.  Returns the row's
-        // partial sum of P.
-        auto softmax_tile = [&](int q, int k, int buf, uint32_t spar, int ptile, bool paired, int slot) -> float {
+        // ---- score tiles of this group --------------------------------------------------------------------
+        // Per tile: row maximum (first sweep over the tile's columns in TMEM), exchange of the maximum with
+        // the group that holds the other key tile of the same rows, exponentials (second sweep), P_hi and
+        // P_lo over S in place.  Chunk c = score columns [32c, 32c+32): its P_hi (packed fp16) goes to
+        // columns [32c, 32c+16), its P_lo to [32c+16, 32c+32), so a chunk is rewritten where it was read.
+        float lsum[2] = {0.0f, 0.0f};
+#pragma unroll 1
+        for (int ji = 0; ji < njobs; ++ji) {
+            const uint32_t job = ji ? job1 : job0;
+            const int q = job & 1, k = (job >> 1) & 1, buf = (job >> 2) & 3, ptile = (job >> 4) & 3, slot = (job >> 6) & 1;
+            const bool paired = (job >> 7) & 1;
+            const uint32_t spar = ((job >> 8) & 3) == 0 ? par : ((job >> 8) & 3) - 1;   // parity of s_full[buf] for this tile
             const uint32_t s_addr = lane_base + (uint32_t)(buf * kTile);
             const int ncols = min(kTile, S - k * kTile);                      // keys of this tile that exist
             const bool diag = CAUSAL && q == k;
@@ -371,26 +459,23 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
             const int nch = (nwarp + 31) >> 5;                                // 32-column chunks with any visible key
             wait(&s_full[buf], spar, 3);
             tc_fence_after();
+            // Both sweeps keep one TMEM load in flight while the chunk before it is worked on: the load of
+            // chunk c+1 is issued as soon as chunk c has arrived (tcgen05.wait::ld waits for every earlier load).
             float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (c < nch) {
-                    float v[32];
-                    tmem_ld32(s_addr + c * 32, v);
+            float va[32], vb[32];
+            tmem_ld32(s_addr, va);                                            // nch >= 1: a tile has at least one key
+#pragma unroll 1
+            for (int c0 = 0; c0 < nch; c0 += 2) {
+                tmem_wait_ld();
+                if (c0 + 1 < nch) tmem_ld32(s_addr + c0 * 32 + 32, vb);
+                mx = fmaxf(mx, chunk_max(va, c0 * 32, nvalid, c0 * 32 + 32 > nmin));
+                if (c0 + 1 < nch) {
                     tmem_wait_ld();
-                    if (c * 32 + 32 > nmin) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j < nvalid) ? v[j] : -INFINITY;
-                    }
-                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        m4[0] = fmaxf(m4[0], v[j]); m4[1] = fmaxf(m4[1], v[j + 1]);
-                        m4[2] = fmaxf(m4[2], v[j + 2]); m4[3] = fmaxf(m4[3], v[j + 3]);
-                    }
-                    mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+                    if (c0 + 2 < nch) tmem_ld32(s_addr + c0 * 32 + 64, va);
+                    mx = fmaxf(mx, chunk_max(vb, c0 * 32 + 32, nvalid, c0 * 32 + 64 > nmin));
                 }
             }
+            tmem_ld32(s_addr, va);                                            // the second sweep's first chunk: on its way during the exchange below
             if (paired) {
                 xmax[par][q][slot][rloc] = mx;
                 arrive(&xm[q]);
@@ -399,75 +484,39 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
             }
             mx = fmaxf(mx, -1e30f);
             const float nmc = kPShift - mx * cscale;     // p = 2^(s c - m c + 8)
-            float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t held[32];                           // P_lo of two chunks, kept until their columns have been read
-            // chunk c: scores in columns [32c, 32c+32); P_hi goes to [16c, 16c+16), P_lo to [64+16c, 64+16c+16)
-            auto chunk = [&](int c, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
-                if (c < nch) {
-                    float v[32];
-                    tmem_ld32(s_addr + c * 32, v);
+            float ps = 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < nch; c0 += 2) {
+                tmem_wait_ld();
+                if (c0 + 1 < nch) tmem_ld32(s_addr + c0 * 32 + 32, vb);
+                ps += chunk_exp(va, s_addr + c0 * 32, c0 * 32, nvalid, c0 * 32 + 32 > nmin, cscale, nmc);
+                if (c0 + 1 < nch) {
                     tmem_wait_ld();
-                    if (c * 32 + 32 > nmin) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j < nvalid) ? v[j] : -INFINITY;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const float p0 = ex2_approx(fmaf(v[j], cscale, nmc)), p1 = ex2_approx(fmaf(v[j + 1], cscale, nmc));
-                        ps[j & 3] += p0;
-                        ps[(j + 1) & 3] += p1;
-                        const float h0 = tf32_hi(p0), h1 = tf32_hi(p1);
-                        hi[j >> 1] = pack_f16(h0, h1);
-                        lo[j >> 1] = pack_f16(p0 - h0, p1 - h1);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) hi[j] = lo[j] = 0u;
+                    if (c0 + 2 < nch) tmem_ld32(s_addr + c0 * 32 + 64, va);
+                    ps += chunk_exp(vb, s_addr + c0 * 32 + 32, c0 * 32 + 32, nvalid, c0 * 32 + 64 > nmin, cscale, nmc);
                 }
-            };
-            {
-                uint32_t hi[16], lo[16];
-                chunk(0, hi, lo);
-                tmem_st16_u32(s_addr + 0, hi);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) held[j] = lo[j];
-                chunk(1, hi, lo);
-                tmem_st16_u32(s_addr + 16, hi);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) held[16 + j] = lo[j];
-                chunk(2, hi, lo);                        // columns 64..95 have been read
-                tmem_st16_u32(s_addr + 32, hi);
-                {
-                    uint32_t l0[16], l1[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) { l0[j] = held[j]; l1[j] = held[16 + j]; }
-                    tmem_st16_u32(s_addr + 64, l0);
-                    tmem_st16_u32(s_addr + 80, l1);
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) held[j] = lo[j];
-                chunk(3, hi, lo);                        // columns 96..127 have been read
-                tmem_st16_u32(s_addr + 48, hi);
-                {
-                    uint32_t l2[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) l2[j] = held[j];
-                    tmem_st16_u32(s_addr + 96, l2);
-                }
-                tmem_st16_u32(s_addr + 112, lo);
             }
+            for (int c = nch; c < 4; ++c) chunk_zero(s_addr + c * 32);       // chunks that no row of this warp sees
             tmem_wait_st();
             tc_fence_before();
             arrive(&p_full[ptile]);
-            const float l = (ps[0] + ps[1]) + (ps[2] + ps[3]);
             if (paired) {
-                xsum[par][q][slot][rloc] = l;
+                xsum[par][q][slot][rloc] = ps;
                 arrive(&xs[q]);
             }
-            return l;
-        };
-        // ---- output columns [c0, c0 + nc) of query tile q: (P_hi V_hi + corrections) / (l * V's scale) ----
-        auto epilogue = [&](int q, int c0, int nc, bool paired, int slot, float l) {
+            if (ji) lsum[1] = ps; else lsum[0] = ps;
+        }
+        // the next head's K and Q have landed by now (their copies were issued when this head's Q K^T had
+        // completed): converting them here lets its Q K^T run while this head's output is stored
+        if (grp < 2 && hd + (int)gridDim.x < BH) convert_kq(it + 1);
+        // ---- output: (P_hi V_hi + corrections) / (l * V's scale); the groups of a query tile share its columns ----
+#pragma unroll 1
+        for (int ji = 0; ji < njobs; ++ji) {
+            const uint32_t job = ji ? job1 : job0;
+            const int q = job & 1, slot = (job >> 6) & 1;
+            const bool paired = (job >> 7) & 1;
+            const int c0 = paired ? 16 * slot : 0, nc = paired ? 16 : 32;
+            float l = ji ? lsum[1] : lsum[0];
             if (paired) {
                 wait(&xs[q], par, 7);
                 l += xsum[par][q][slot ^ 1][rloc];
@@ -479,6 +528,7 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
             const bool store = !abort_flag && row < S;
             float4 *dst = reinterpret_cast<float4 *>(O + ((size_t)b * S + (row < S ? row : 0)) * (size_t)E + (size_t)h * 32);
             const uint32_t o_addr = lane_base + kColO + (uint32_t)(q * 64);
+#pragma unroll 1
             for (int cc = c0; cc < c0 + nc; cc += 16) {
                 float a[16], c2[16];
                 tmem_ld16(o_addr + cc, a);
@@ -490,38 +540,6 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                         dst[(cc >> 2) + j] = make_float4((a[4 * j] + c2[4 * j]) * inv, (a[4 * j + 1] + c2[4 * j + 1]) * inv,
                                                          (a[4 * j + 2] + c2[4 * j + 2]) * inv, (a[4 * j + 3] + c2[4 * j + 3]) * inv);
                 }
-            }
-        };
-
-        if (nq == 1) {
-            if (grp == 0) {
-                const float l = softmax_tile(0, 0, 0, par, 0, false, 0);
-                epilogue(0, 0, 32, false, 0, l);
-            }
-        } else if (CAUSAL) {
-            if (grp == 0) {
-                const float l = softmax_tile(0, 0, 0, par, 0, false, 0);
-                epilogue(0, 0, 32, false, 0, l);
-            } else if (grp == 1) {
-                const float l = softmax_tile(1, 0, 1, par, 1, true, 0);
-                epilogue(1, 0, 16, true, 0, l);
-            } else {
-                const float l = softmax_tile(1, 1, 2, par, 2, true, 1);
-                epilogue(1, 16, 16, true, 1, l);
-            }
-        } else {
-            if (grp == 0) {
-                // s_full[0] completes twice per head here: parity 0 for (q0, k0), 1 for (q1, k1)
-                const float l0 = softmax_tile(0, 0, 0, 0u, 0, true, 0);
-                const float l3 = softmax_tile(1, 1, 0, 1u, 3, true, 1);
-                epilogue(0, 0, 16, true, 0, l0);
-                epilogue(1, 16, 16, true, 1, l3);
-            } else if (grp == 1) {
-                const float l = softmax_tile(0, 1, 1, par, 1, true, 1);
-                epilogue(0, 16, 16, true, 1, l);
-            } else {
-                const float l = softmax_tile(1, 0, 2, par, 2, true, 0);
-                epilogue(1, 0, 16, true, 0, l);
             }
         }
         tc_fence_before();
