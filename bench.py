@@ -38,9 +38,11 @@ sys.path.insert(0, ROOT)
 from hipgpt_b200 import synth  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in profiles/
-# (workload, tensor kernel?) -> bytes
-TRAFFIC = {("c2", True): 25.23e6, ("c2", False): 25.21e6, ("c3", True): 129.9e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture that the named summary under
+# profiles/ records: (workload, kernel) -> (bytes, summary).  A kernel without a capture of its own reports null.
+TRAFFIC = {("c2", "mha_head_kernel"): (25.32e6, "profiles/mha_head_kernel_c2_causal.md"),
+           ("c2", "mha_tc16_kernel"): (25.23e6, "profiles/mha_tc16_kernel_c2_causal.md"),
+           ("c3", "mha_tc16_kernel"): (129.9e6, "profiles/mha_tc16_kernel_c3_causal.md")}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -69,6 +71,7 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="run only the greedy-generation leg and print its JSON")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-scaling", action="store_true", help="skip the C5 sharded leg (key scaling_c5)")
     ap.add_argument("--bf16-variant", type=int, default=0, help="--dtype bf16: 0 default, 1 one worker per query row, 2 two workers, 3 two workers and 128-key tiles")
     return ap.parse_args()
 
@@ -211,21 +214,85 @@ def run_reference(args):
     line = {"impl": "reference", "metric": "causal_attn_fwd_tflops", "value": tf, "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": info["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": dict(workload_config(args, cfg, 1), l2="host cores: inputs in host memory, no GPU cache involved",
-                           parallelism="rank 0 only, all host threads"),
+            "config": workload_config(args, cfg),
+            "timing": {"l2": "host cores: inputs in host memory, no GPU cache involved", "parallelism": "rank 0 only, all host threads"},
             "cpu_baseline": info,
             "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     emit(line)
 
 
-def workload_config(args, cfg, sets):
-    return {"workload": f"{args.workload}: causal MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} {args.dtype}"
-                        if args.causal else f"{args.workload}: full MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} {args.dtype}",
+def workload_config(args, cfg):
+    """What is computed, in words both arms share (how each arm steps through it is reported beside it, not here)."""
+    kind = "causal" if args.causal else "full"
+    return {"workload": f"{args.workload}: {kind} MHA forward B={cfg['B']} H={cfg['H']} S={cfg['S']} head_dim={cfg['D']} {args.dtype}",
             "B": cfg["B"], "H": cfg["H"], "S": cfg["S"], "head_dim": cfg["D"], "causal": int(args.causal),
-            "probs_stored": int(args.probs), "batches_per_step": sets,
-            "l2": f"{sets} distinct input batches per step, {sets * bytes_of(cfg['B'], cfg['H'], cfg['S'], cfg['D'], args.probs) * (2 if args.dtype == 'bf16' else 4) // 4 / 1e6:.0f} MB > 126 MB L2",
-            "parallelism": f"batch-major shards x{args.gpus}" + (", NCCL all-gather of outputs in chunks, overlapped" if args.gather else ", no collective")}
+            "probs_stored": int(args.probs)}
+
+
+def scaling_c5_leg(world, rank, lib):
+    """BASELINE.json's scaling configuration (B=64 H=16 S=2048 head_dim=64, causal, fp32 and bf16 storage) with its
+    batches split over the ranks by the library's own driver (hipgpt_mha_forward_sharded): compute only, and with the
+    NCCL all-gather of the outputs, chunk by chunk behind the arithmetic.  Device time per call from CUDA events,
+    max over ranks; L2 is flushed between calls (at 8 ranks a rank's bf16 inputs are smaller than L2)."""
+    import torch
+    import torch.distributed as dist
+    from hipgpt_b200 import sharding
+    c = synth.CONFIGS["c5"]
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    E = H * D
+    if B % world:
+        return {"skipped": f"{B} batches do not split over {world} ranks"}
+    Bl = B // world
+    chunks = next(ch for ch in (16, 8, 4, 2, 1) if Bl % ch == 0)
+    sh = sharding.ShardedAttention()
+    stream = torch.cuda.current_stream()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    out = {"config": f"c5: causal MHA forward B={B} H={H} S={S} head_dim={D}, batches split over {world} rank(s)",
+           "flops_per_call": flops_of(B, H, S, D, True), "nccl_version": int(lib.hipgpt_shard_nccl_version()),
+           "gather_chunks": chunks, "reps": 5}
+    for name, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(4 + rank)
+        loc = torch.randn((3, Bl * S, E), device="cuda", generator=g, dtype=torch.float32).to(dtype)
+        full = torch.empty((B * S, E), device="cuda", dtype=dtype)
+
+        def call(ch, gather):
+            sh.forward(loc[0], loc[1], loc[2], full, B, S, E, H, causal=True, chunks=ch, gather=gather)
+
+        def timed(ch, gather, reps=5):
+            for _ in range(2):
+                call(ch, gather)
+            total = 0.0
+            for _ in range(reps):
+                flush.fill_(1)
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                call(ch, gather)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1)
+                if world > 1:
+                    tt = torch.tensor([ms], device="cuda")
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                    ms = float(tt.item())
+                total += ms
+            return total / reps
+        res = {}
+        for label, ch, gather in (("compute_only", 1, False), ("compute_chunked", chunks, False), ("with_gather", chunks, True)):
+            if label == "with_gather" and world == 1:
+                continue
+            ms = timed(ch, gather)
+            res[label] = {"ms": ms, "tflops": flops_of(B, H, S, D, True) / (ms * 1e-3) / 1e12}
+        res["gathered_bytes_per_rank"] = int((B - Bl) * S * E * full.element_size()) if world > 1 else 0
+        out[name] = res
+        del loc, full
+    sh.close()
+    return out
 
 
 # ----------------------------------------------------------------------------- GPU arm ----
@@ -403,8 +470,11 @@ def run_ours(args):
     else:
         roofline = {"bound": "fma", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s", "frac": achieved / fma_peak,
                     "peak_source": "fp32 FFMA loop timed in this run"}
-    roofline.update({"kernel": "mha_bf16_kernel" if bf16 else "mha_tc16_kernel" if tc16 else "mha_tc_kernel" if tensor_kernel else "mha_rows_kernel",
-                     "traffic": None if (bf16 or args.probs) else TRAFFIC.get((args.workload, tensor_kernel)),
+    kernel = ("mha_bf16_kernel" if bf16 else
+              "mha_head_kernel" if (D == 32 and S <= 256 and not args.probs) else
+              "mha_tc16_kernel" if tensor_kernel else "mha_rows_kernel" if D == 128 else "mha_generic_kernel")
+    traffic = TRAFFIC.get((args.workload, kernel)) if (args.causal and not args.probs and not bf16) else None
+    roofline.update({"kernel": kernel, "traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None,
                      "us_per_launch": launch_ms * 1e3, "algorithmic_bytes_per_launch": per_batch_bytes,
                      "algorithmic_flops_per_launch": flops_launch,
                      "vs_fp32_fma_ceiling": {"achieved_tflops": achieved, "ffma_peak_tflops": fma_peak, "ratio": achieved / fma_peak,
@@ -414,8 +484,18 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong" if (args.strong and world > 1) else "weak", "vs_baseline": None,
             "dtype": "bf16 storage, fp32 accumulate" if bf16 else "f32", "data": "synthetic",
-            "config": workload_config(args, cfg, sets), "clocks": clocks.summary(), "roofline": roofline,
+            "config": workload_config(args, dict(cfg, B=B_total)),
+            "timing": {"batches_per_step": sets,
+                       "l2": f"{sets} distinct input batches per step, {sets * per_batch_bytes / 1e6:.0f} MB > 126 MB L2",
+                       "parallelism": f"batch-major shards x{world}" + (", NCCL all-gather of outputs in chunks, overlapped" if args.gather else ", no collective")},
+            "clocks": clocks.summary(), "roofline": roofline,
             "gpu_launches": args.steps * sets}
+
+    # the scaling configuration through the library's sharded driver (every N, the default workload only)
+    if args.workload == "c2" and not args.no_scaling and not bf16:
+        del d_in, d_out
+        torch.cuda.empty_cache()
+        line["scaling_c5"] = scaling_c5_leg(world, rank, lib)
 
     # end to end through the host-buffer entry point: pinned host memory in, host memory out
     if not args.no_e2e:

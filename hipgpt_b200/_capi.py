@@ -30,6 +30,15 @@ SIGNATURES = {
     "hipgpt_scaled_dot_product": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "hipgpt_softmax": (_i, [_vp, _vp, _i, _i, _vp]),
     "hipgpt_attention_weighted_sum": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hipgpt_mha_backward_scratch_bytes": (_sz, [_i, _i, _i]),
+    "hipgpt_mha_backward": (_i, [_vp] * 9 + [_sz, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_mha_backward_planes": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_matmul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hipgpt_layer_norm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "hipgpt_dropout": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
+    "hipgpt_add_inplace": (_i, [_vp, _vp, C.c_longlong, _vp]),
+    "hipgpt_relu": (_i, [_vp, C.c_longlong, _vp]),
+    "hipgpt_embedding_lookup": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_decode_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "hipgpt_mha_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -37,8 +46,19 @@ SIGNATURES = {
     "hipgpt_gpt_create": (_i, [C.POINTER(_vp), _vp, _i, _i, _i, _i, _i, _i, _i]),
     "hipgpt_gpt_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "hipgpt_gpt_destroy": (None, [_vp]),
+    "hipgpt_checkpoint_header": (_i, [C.c_char_p] + [C.POINTER(_i)] * 6),
+    "hipgpt_checkpoint_weights": (_i, [C.c_char_p, _vp, C.c_longlong]),
+    "hipgpt_run_config": (_i, [C.c_char_p] + [C.POINTER(_i)] * 6 + [C.c_char_p, _sz, C.c_char_p, _sz]),
+    "hipgpt_gpt_create_from_checkpoint": (_i, [C.POINTER(_vp), C.c_char_p, _i]),
+    "hipgpt_gpt_create_from_run": (_i, [C.POINTER(_vp), C.c_char_p, _i]),
     "hipgpt_gpt_set_mode": (_i, [_vp, _i]),
     "hipgpt_shard_range": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "hipgpt_shard_chunk_range": (_i, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "hipgpt_shard_unique_id": (_i, [_vp]),
+    "hipgpt_shard_create": (_i, [C.POINTER(_vp), _vp, _i, _i]),
+    "hipgpt_shard_destroy": (None, [_vp]),
+    "hipgpt_mha_forward_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_shard_nccl_version": (_i, []),
     "hipgpt_probe_fma": (_i, [_vp, _i, _i, C.POINTER(C.c_double), _vp]),
     "hipgpt_kernel_status": (_i, [C.POINTER(_i)]),
     "hipgpt_accuracy_notice": (_i, [C.POINTER(_i)]),
@@ -54,6 +74,14 @@ CXX_LAUNCHERS = {
     "launch_scaled_dot_product": "_Z25launch_scaled_dot_productPKfS0_Pfiii",
     "launch_softmax": "_Z14launch_softmaxPKfPfii",
     "launch_attention_weighted_sum": "_Z29launch_attention_weighted_sumPKfS0_Pfiii",
+    "launch_multihead_attention_backward": "_Z35launch_multihead_attention_backwardPKfS0_S0_Pfiiii",
+    "launch_matmul": "_Z13launch_matmulPKfS0_Pfiii",
+    "launch_matmul_add_bias": "_Z22launch_matmul_add_biasPKfS0_S0_Pfiii",
+    "launch_layer_norm_forward": "_Z25launch_layer_norm_forwardPKfPfS0_S0_ii",
+    "launch_dropout_forward": "_Z22launch_dropout_forwardPKfPfS1_fii",
+    "launch_add_inplace": "_Z18launch_add_inplacePfPKfi",
+    "launch_relu": "_Z11launch_reluPfi",
+    "launch_embedding_lookup": "_Z23launch_embedding_lookupPKiPKfS2_Pfiiii",
 }
 
 _lib = None

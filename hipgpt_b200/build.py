@@ -20,8 +20,8 @@ LIBDIR = os.path.join(PKG, "_lib")
 LIB = os.path.join(LIBDIR, "libhipgpt_attn.so")
 OBJDIR = os.path.join(LIBDIR, "obj")
 
-SOURCES = ["attn_fwd_rows.cu", "attn_fwd_tc.cu", "attn_fwd_bf16.cu", "attn_fwd_tc16.cu", "attn_fwd_head.cu", "attn_fwd_generic.cu", "attn_unfused.cu", "attn_decode.cu", "gpt_decode.cu", "probe.cu", "wait_probe.cu", "capi.cu",
-           "compat_launchers.cpp"]
+SOURCES = ["attn_fwd_rows.cu", "attn_fwd_tc.cu", "attn_fwd_bf16.cu", "attn_fwd_tc16.cu", "attn_fwd_head.cu", "attn_fwd_generic.cu", "attn_unfused.cu", "attn_bwd.cu", "layer_ops.cu", "attn_decode.cu", "gpt_decode.cu", "probe.cu", "wait_probe.cu", "capi.cu",
+           "compat_launchers.cpp", "checkpoint.cpp", "sharded.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "-I", os.path.join(ROOT, "include"), "-I", CSRC]
@@ -67,7 +67,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
         objs = list(pool.map(compile_one, SOURCES))
-    cmd = [cc, *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC"]
+    cmd = [cc, *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)

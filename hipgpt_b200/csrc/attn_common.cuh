@@ -57,6 +57,12 @@ int launch_mha_bf16(const void *q, const void *k, const void *v, void *out, int 
                     int variant = 0);
 bool mha_bf16_supports(int D);
 int bf16_status_fetch(int *status);
+// attention backward (attn_bwd.cu): scratch = 2 B H S floats (row sums w_i, then log-sum-exp of the rows)
+size_t mha_backward_scratch_bytes(int B, int H, int S);
+int launch_mha_backward(const float *g, const float *q, const float *k, const float *v, const float *probs,
+                        float *dq, float *dk, float *dv, float *scratch, int B, int S, int E, int H, int causal, cudaStream_t st);
+// the launchers either side of attention (layer_ops.cu)
+int launch_matmul_exact(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st);
 int launch_mha_generic(const float *q, const float *k, const float *v, float *out, float *probs,
                        int B, int S, int E, int H, int causal, cudaStream_t st);
 int launch_sdp(const float *Q, const float *K, float *scores, int B, int S, int D, cudaStream_t st);

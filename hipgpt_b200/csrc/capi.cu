@@ -375,6 +375,60 @@ int hipgpt_mha_decode(const float *d_q, const float *d_kcache, const float *d_vc
     return launch_decode(d_q, d_kcache, d_vcache, d_out, d_scratch, B, H, D, ctx, cap, ns, static_cast<cudaStream_t>(stream));
 }
 
+size_t hipgpt_mha_backward_scratch_bytes(int B, int H, int S)
+{
+    if (B <= 0 || H <= 0 || S <= 0) return 0;
+    return mha_backward_scratch_bytes(B, H, S);
+}
+
+int hipgpt_mha_backward(const float *d_grad_out, const float *d_q, const float *d_k, const float *d_v, const float *d_probs,
+                        float *d_grad_q, float *d_grad_k, float *d_grad_v, float *d_scratch, size_t scratch_bytes,
+                        int B, int S, int E, int H, int causal, void *stream)
+{
+    const int rc = check_mha_args(d_q, d_k, d_v, d_grad_out, B, S, E, H);
+    if (rc != HIPGPT_OK) return rc > 0 ? HIPGPT_OK : rc;
+    if (!d_grad_q || !d_grad_k || !d_grad_v) return fail(HIPGPT_ERR_NULL, "the three gradient outputs must not be NULL");
+    const size_t need = mha_backward_scratch_bytes(B, H, S);
+    if (!d_scratch || scratch_bytes < need)
+        return fail(HIPGPT_ERR_SCRATCH, "scratch of %zu bytes needed, %zu given", need, d_scratch ? scratch_bytes : (size_t)0);
+    return launch_mha_backward(d_grad_out, d_q, d_k, d_v, d_probs, d_grad_q, d_grad_k, d_grad_v, d_scratch, B, S, E, H, causal,
+                               static_cast<cudaStream_t>(stream));
+}
+
+// The reference's launcher has no scratch argument (include/hip_kernels.h:59-62): its drop-in form keeps the row
+// sums in a buffer of the library that grows to the largest call on the current device.
+int hipgpt_mha_backward_planes(const float *d_grad_out, const float *d_qkv, const float *d_probs, float *d_grad_qkv,
+                               int B, int S, int E, int H, int causal, void *stream)
+{
+    if (B < 0 || S < 0 || E < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: B=%d S=%d E=%d", B, S, E);
+    if (H <= 0 || E % H != 0) return fail(HIPGPT_ERR_BAD_ARG, "Bad MHA config: E=%d H=%d", E, H);
+    if (B == 0 || S == 0 || E == 0) return HIPGPT_OK;
+    if (!d_grad_out || !d_qkv || !d_grad_qkv) return fail(HIPGPT_ERR_NULL, "grad_out, qkv and grad_qkv must not be NULL");
+    static std::mutex mu;
+    static float *buf[64] = {};
+    static size_t cap[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    const size_t need = mha_backward_scratch_bytes(B, H, S);
+    float *scratch;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (cap[dev] < need) {
+            if (buf[dev]) cudaFree(buf[dev]);
+            buf[dev] = nullptr;
+            cap[dev] = 0;
+            e = cudaMalloc(&buf[dev], need);
+            if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMalloc(%zu): %s", need, cudaGetErrorString(e));
+            cap[dev] = need;
+        }
+        scratch = buf[dev];
+    }
+    const size_t plane = (size_t)B * S * E;
+    return launch_mha_backward(d_grad_out, d_qkv, d_qkv + plane, d_qkv + 2 * plane, d_probs, d_grad_qkv, d_grad_qkv + plane,
+                               d_grad_qkv + 2 * plane, scratch, B, S, E, H, causal, static_cast<cudaStream_t>(stream));
+}
+
 int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end)
 {
     if (B < 0 || world <= 0 || rank < 0 || rank >= world)

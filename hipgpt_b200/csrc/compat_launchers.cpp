@@ -1,7 +1,10 @@
 // Reference-named entry points over the C ABI (declared in include/hipgpt_launchers.hpp).
 // Each one stands where HipGPT's own definition stood: launch_multihead_attention
 // (src/hip_kernels.cpp:404-451), launch_scaled_dot_product (:468-473), launch_softmax
-// (:506-511), launch_attention_weighted_sum (:527-532).
+// (:506-511), launch_attention_weighted_sum (:527-532); and the launchers either side of attention in
+// TransformerLayer::forward / GPTModel::forward: launch_matmul (:102-109), launch_matmul_add_bias (:147-154),
+// launch_layer_norm_forward (:838-848), launch_dropout_forward (:966-970), launch_add_inplace (:726-730),
+// launch_relu (:254-258), launch_embedding_lookup (:583-599); and launch_multihead_attention_backward (:1242-1272).
 #include "hipgpt_launchers.hpp"
 
 #include <cstdio>
@@ -42,4 +45,48 @@ void launch_softmax(const float* scores, float* softmax_out, int B, int S)
 void launch_attention_weighted_sum(const float* softmax, const float* V, float* output, int B, int S, int D)
 {
     die_on(hipgpt_attention_weighted_sum(softmax, V, output, B, S, D, nullptr), "launch_attention_weighted_sum");
+}
+
+void launch_matmul(const float* A, const float* B, float* C, int M, int N, int K)
+{
+    die_on(hipgpt_matmul(A, B, nullptr, C, M, N, K, nullptr), "launch_matmul");
+}
+
+void launch_matmul_add_bias(const float* A, const float* B, const float* bias, float* C, int M, int N, int K)
+{
+    die_on(hipgpt_matmul(A, B, bias, C, M, N, K, nullptr), "launch_matmul_add_bias");
+}
+
+void launch_layer_norm_forward(const float* input, float* output, const float* gamma, const float* beta, int N, int E)
+{
+    die_on(hipgpt_layer_norm(input, output, gamma, beta, N, E, nullptr), "launch_layer_norm_forward");
+}
+
+void launch_dropout_forward(const float* input, float* output, float* mask, float p, int N, int E)
+{
+    die_on(hipgpt_dropout(input, output, mask, p, N, E, nullptr), "launch_dropout_forward");
+}
+
+void launch_add_inplace(float* a, const float* b, int n)
+{
+    die_on(hipgpt_add_inplace(a, b, n, nullptr), "launch_add_inplace");
+}
+
+void launch_relu(float* A, int size)
+{
+    die_on(hipgpt_relu(A, size, nullptr), "launch_relu");
+}
+
+void launch_embedding_lookup(const int* d_token_ids, const float* d_token_embed, const float* d_pos_embed,
+                             float* d_output, int batch_size, int seq_len, int vocab_size, int embed_dim)
+{
+    die_on(hipgpt_embedding_lookup(d_token_ids, d_token_embed, d_pos_embed, d_output, batch_size, seq_len, vocab_size, embed_dim, nullptr),
+           "launch_embedding_lookup");
+}
+
+void launch_multihead_attention_backward(const float* d_grad_attn_output, const float* d_qkv, const float* d_softmax,
+                                         float* d_grad_qkv, int B, int S, int E, int H)
+{
+    die_on(hipgpt_mha_backward_planes(d_grad_attn_output, d_qkv, d_softmax, d_grad_qkv, B, S, E, H, /*causal=*/0, nullptr),
+           "launch_multihead_attention_backward");
 }

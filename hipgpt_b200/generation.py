@@ -28,6 +28,26 @@ class GptDecoder:
         if mode is not None:
             self.set_mode(mode)
 
+    @classmethod
+    def from_checkpoint(cls, path: str, max_batch: int = 8, mode: int | None = None):
+        """A HipGPT checkpoint file (GPTModel::save_checkpoint's layout) or, for a path ending in .json, the run
+        configuration that names it (src/train_gpt.cpp:60-102); read by the library's native reader."""
+        import os
+        from . import checkpoint
+        lib = _capi.lib()
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        if path.endswith(".json"):
+            cfg = checkpoint.read_run_config(path)
+            _capi.check(lib.hipgpt_gpt_create_from_run(C.byref(self._h), os.fsencode(path), max_batch))
+        else:
+            cfg = checkpoint.read_header(path)
+            _capi.check(lib.hipgpt_gpt_create_from_checkpoint(C.byref(self._h), os.fsencode(path), max_batch))
+        self.shape = (cfg["V"], cfg["S"], cfg["E"], cfg["L"], cfg["H"], cfg["F"])
+        if mode is not None:
+            self.set_mode(mode)
+        return self
+
     def set_mode(self, mode: int):
         _capi.check(_capi.lib().hipgpt_gpt_set_mode(self._h, int(mode)))
 

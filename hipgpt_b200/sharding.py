@@ -74,3 +74,56 @@ def sharded_forward(qkv_local: torch.Tensor, B: int, S: int, E: int, H: int, *, 
     if not gather or world == 1:
         return out_local
     return all_gather_output(out_local, B, S, E, group)
+
+
+# ---- the library's own multi-GPU driver (hipgpt_mha_forward_sharded in include/hipgpt_attn.h) -------------------
+def chunk_range(B: int, world: int, rank: int, chunks: int, chunk: int) -> Tuple[int, int]:
+    """Global batches [b0, b1) that `rank` owns in chunk `chunk` (B a multiple of world * chunks)."""
+    b0, b1 = C.c_int(), C.c_int()
+    _capi.check(_capi.lib().hipgpt_shard_chunk_range(B, world, rank, chunks, chunk, C.byref(b0), C.byref(b1)))
+    return b0.value, b1.value
+
+
+def local_planes_chunked(qkv: torch.Tensor, B: int, S: int, E: int, world: int, rank: int, chunks: int) -> torch.Tensor:
+    """This rank's batches of three stacked [B*S, E] planes in the order the driver wants them: chunk after chunk."""
+    view = qkv.view(3, B, S, E)
+    parts = [view[:, slice(*chunk_range(B, world, rank, chunks, c))] for c in range(chunks)]
+    return torch.cat(parts, dim=1).reshape(3, (B // world) * S, E).contiguous()
+
+
+class ShardedAttention:
+    """One per process (= per GPU): an NCCL communicator of the library's own, a high-priority communication stream
+    and the per-chunk events.  torch.distributed only carries the 128-byte id from rank 0 to the other ranks."""
+
+    def __init__(self, group=None):
+        lib = _capi.lib()
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        ident = (C.c_char * 128)()
+        if self.world > 1:
+            if self.rank == 0:
+                _capi.check(lib.hipgpt_shard_unique_id(ident))
+            box = [bytes(ident)]
+            dist.broadcast_object_list(box, src=0, group=group)
+            ident = (C.c_char * 128).from_buffer_copy(box[0])
+        self._h = C.c_void_p()
+        _capi.check(lib.hipgpt_shard_create(C.byref(self._h), ident, self.rank, self.world))
+
+    def forward(self, q, k, v, out, B: int, S: int, E: int, H: int, *, causal: bool = False, chunks: int = 1, gather: bool = True):
+        """q, k, v: this rank's batches (local_planes_chunked order), fp32 or bf16 CUDA tensors (or raw addresses with
+        elem_bytes given by `out`'s dtype); out: the whole [B*S, E] output.  Asynchronous on torch's current stream."""
+        esz = out.element_size()
+        ptr = lambda t: t if isinstance(t, int) else t.data_ptr()
+        _capi.check(_capi.lib().hipgpt_mha_forward_sharded(self._h, ptr(q), ptr(k), ptr(v), out.data_ptr(), B, S, E, H, int(causal),
+                                                           esz, chunks, int(gather), torch.cuda.current_stream().cuda_stream))
+
+    def close(self):
+        if self._h:
+            _capi.lib().hipgpt_shard_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -94,3 +94,19 @@ def gpt_weights(seed: int, V: int, S: int, E: int, L: int, H: int, F: int, std: 
         parts += [np.ones(E, np.float32), np.zeros(E, np.float32), np.ones(E, np.float32), np.zeros(E, np.float32)]
     parts.append(mat(E, V))
     return np.ascontiguousarray(np.concatenate(parts), dtype=np.float32)
+
+
+def layer_weights(seed: int, E: int, H: int, F: int, std: float = 0.05) -> np.ndarray:
+    """One layer's tensors in checkpoint order (src/transformer_layer.cpp:312-344), every one of them random:
+    matrices N(0, std^2), biases N(0, 0.1^2), layer-norm gamma 1 + N(0, 0.1^2), beta N(0, 0.1^2)."""
+    del H
+    s = [0]
+
+    def rnd(n, scale, shift=0.0):
+        s[0] += 1
+        return (normal(seed, (n,), scale, stream=s[0]) + np.float32(shift)).astype(np.float32)
+
+    parts = [rnd(E * 3 * E, std), rnd(E * E, std), rnd(E * F, std), rnd(F * E, std),
+             rnd(3 * E, 0.1), rnd(E, 0.1), rnd(F, 0.1), rnd(E, 0.1),
+             rnd(E, 0.1, 1.0), rnd(E, 0.1), rnd(E, 0.1, 1.0), rnd(E, 0.1)]
+    return np.ascontiguousarray(np.concatenate(parts), dtype=np.float32)

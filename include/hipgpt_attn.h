@@ -137,6 +137,55 @@ HIPGPT_API int hipgpt_attention_weighted_sum(const float *d_softmax, const float
                                   int B, int S, int D, void *stream);
 
 /*
+ * Attention backward: gradients of Q, K, V from the gradient of the attention output.  Replaces
+ * launch_multihead_attention_backward (src/hip_kernels.cpp:1162-1272, declared include/hip_kernels.h:59-62,
+ * called at src/transformer_layer.cpp:285-286).
+ *   d_grad_out     [B*S][E]   dL/d(output); d_q, d_k, d_v as in hipgpt_mha_forward
+ *   d_probs        [B][H][S][S] as hipgpt_mha_forward stored them, or NULL: the probabilities are then formed
+ *                  again from Q and K (row maxima and sums recomputed first), so the forward need not have
+ *                  written them at all
+ *   d_grad_q/k/v   [B*S][E], fully overwritten
+ *   d_scratch      hipgpt_mha_backward_scratch_bytes(B, H, S) bytes (2 B H S floats)
+ * No atomics: a key row's gradients add its queries in ascending order, so results are reproducible run to
+ * run (the reference's atomicAdd order is not); they agree with the reference's arithmetic to rounding.
+ * hipgpt_mha_backward_planes is the launcher's own view (three stacked planes in d_qkv and d_grad_qkv) with
+ * the scratch kept in a buffer of the library, which grows with cudaMalloc to the largest call per device.
+ */
+HIPGPT_API size_t hipgpt_mha_backward_scratch_bytes(int B, int H, int S);
+HIPGPT_API int hipgpt_mha_backward(const float *d_grad_out, const float *d_q, const float *d_k, const float *d_v, const float *d_probs,
+                        float *d_grad_q, float *d_grad_k, float *d_grad_v, float *d_scratch, size_t scratch_bytes,
+                        int B, int S, int E, int H, int causal, void *stream);
+HIPGPT_API int hipgpt_mha_backward_planes(const float *d_grad_out, const float *d_qkv, const float *d_probs, float *d_grad_qkv,
+                               int B, int S, int E, int H, int causal, void *stream);
+
+/*
+ * The launchers either side of attention in the reference's layer and model forward, restated with the
+ * reference's arithmetic (device pointers, explicit stream):
+ *   hipgpt_matmul            C[M][K] = A[M][N] B[N][K] (+ bias[K] when d_bias is not NULL); the reference's
+ *                            argument order, N being the inner dimension.  Replaces launch_matmul and
+ *                            launch_matmul_add_bias (src/hip_kernels.cpp:69-154): one accumulator per output,
+ *                            k ascending, fused multiply-add, bias added once at the end, so bit-identical to
+ *                            that arithmetic.  d_A == d_C (the reference's in-place output projection,
+ *                            src/transformer_layer.cpp:220) is allowed when K <= 256 and K % 4 == 0.
+ *   hipgpt_layer_norm        replaces launch_layer_norm_forward (src/hip_kernels.cpp:757-848), eps 1e-5;
+ *                            agrees with the reference's 64-lane reduction order to rounding (~1e-7).
+ *   hipgpt_dropout           replaces launch_dropout_forward (src/hip_kernels.cpp:944-970): the mask depends
+ *                            on the element index only (generator at :24-42); bit-identical; d_mask may be
+ *                            NULL; in place (d_in == d_out) allowed.
+ *   hipgpt_add_inplace       a += b           (launch_add_inplace, src/hip_kernels.cpp:721-730)
+ *   hipgpt_relu              a = max(0, a)    (launch_relu, src/hip_kernels.cpp:248-258)
+ *   hipgpt_embedding_lookup  out[t] = tok[id_t] + pos[t mod S], zeros for an id outside [0, V)
+ *                            (launch_embedding_lookup, src/hip_kernels.cpp:537-599)
+ */
+HIPGPT_API int hipgpt_matmul(const float *d_A, const float *d_B, const float *d_bias, float *d_C, int M, int N, int K, void *stream);
+HIPGPT_API int hipgpt_layer_norm(const float *d_in, float *d_out, const float *d_gamma, const float *d_beta, int rows, int E, void *stream);
+HIPGPT_API int hipgpt_dropout(const float *d_in, float *d_out, float *d_mask, float p, int rows, int E, void *stream);
+HIPGPT_API int hipgpt_add_inplace(float *d_a, const float *d_b, long long n, void *stream);
+HIPGPT_API int hipgpt_relu(float *d_a, long long n, void *stream);
+HIPGPT_API int hipgpt_embedding_lookup(const int *d_ids, const float *d_tok, const float *d_pos, float *d_out,
+                            int B, int S, int V, int E, void *stream);
+
+/*
  * Single-query-row attention over a key/value cache, split over the context (extension; the
  * reference's generation loop, src/gpt_model.cpp:261-280, re-runs the whole window instead).
  *   d_q, d_out       [B][E]          the new token's query / the attention output
@@ -191,6 +240,24 @@ HIPGPT_API int hipgpt_gpt_generate(hipgpt_gpt *g, const int *h_prompts, int B, i
                         float *h_logits_last, float *ms_prompt, float *ms_decode);
 HIPGPT_API void hipgpt_gpt_destroy(hipgpt_gpt *g);
 /*
+ * HipGPT's own files (host code): the checkpoint written by GPTModel::save_checkpoint (src/gpt_model.cpp:355-388;
+ * per layer src/transformer_layer.cpp:312-344; read back at src/gpt_model.cpp:390-420) and the run configuration
+ * written by save_config (src/train_gpt.cpp:60-102; read at src/generate.cpp:90-103).
+ *   hipgpt_checkpoint_header   V, S, E, L from the file's header, H and F from the first layer's
+ *   hipgpt_checkpoint_weights  the tensors in file order without the integer headers (what hipgpt_gpt_create takes):
+ *                              `count` must be hipgpt_gpt_weight_count(V, S, E, L, H, F); every layer's header is checked
+ *   hipgpt_run_config          the six "model" numbers and, when asked, "checkpoint"."latest" and "tokenizer"."path"
+ *                              (file names relative to the configuration's own directory)
+ *   hipgpt_gpt_create_from_checkpoint / _from_run   the generation driver for such a file
+ */
+HIPGPT_API int hipgpt_checkpoint_header(const char *path, int *V, int *S, int *E, int *L, int *H, int *F);
+HIPGPT_API int hipgpt_checkpoint_weights(const char *path, float *h_weights, long long count);
+HIPGPT_API int hipgpt_run_config(const char *json_path, int *V, int *S, int *E, int *H, int *F, int *L,
+                      char *ckpt_name, size_t ckpt_cap, char *tok_name, size_t tok_cap);
+HIPGPT_API int hipgpt_gpt_create_from_checkpoint(hipgpt_gpt **out, const char *path, int max_batch);
+HIPGPT_API int hipgpt_gpt_create_from_run(hipgpt_gpt **out, const char *json_path, int max_batch);
+
+/*
  * Two forms of the same token step, same arithmetic and the same ids (extension, like the driver itself):
  *   HIPGPT_GPT_MODE_GRAPH (default): one step = 52 kernel launches captured once as a CUDA graph and replayed
  *     per token.
@@ -205,12 +272,34 @@ HIPGPT_API void hipgpt_gpt_destroy(hipgpt_gpt *g);
 HIPGPT_API int hipgpt_gpt_set_mode(hipgpt_gpt *g, int mode);
 
 /*
- * Batch-major sharding of the (batch x head) space over the GPUs of one box: rank r of
- * `world` owns batches [*b_begin, *b_end), a contiguous slab of every [B*S][E] plane and of
- * the output.  Every (batch, head) pair is independent (src/hip_kernels.cpp:269-277), so the
- * kernels exchange nothing; the outputs are all-gathered afterwards by the caller.
+ * Sharding of the (batch x head) space over the GPUs of one box (no counterpart in the reference, which runs on one
+ * GPU).  Every (batch, head) pair is independent (src/hip_kernels.cpp:269-277), so the kernels exchange nothing: a rank
+ * computes its own batches from its own memory, and the only collective is the all-gather of the outputs.
+ *
+ *   hipgpt_shard_range        contiguous split: rank r of `world` owns batches [*b_begin, *b_end) (sizes differ by <= 1).
+ *   hipgpt_shard_chunk_range  the split the driver below uses, for B a multiple of world * chunks: chunk c covers
+ *                             batches [c*world*k, (c+1)*world*k), k = B / (world*chunks), and rank r owns the r-th run
+ *                             of k batches inside it.  In the output every chunk is then one contiguous block with the
+ *                             ranks' parts in rank order, the in-place form of ncclAllGather.
+ *   hipgpt_shard_unique_id    128 bytes made by rank 0 and handed to every rank (by the job's own means);
+ *   hipgpt_shard_create       collective over the ranks, each with its own GPU current: an NCCL communicator (NCCL is
+ *                             loaded at run time, libnccl.so.2), a communication stream of the highest priority, events;
+ *   hipgpt_mha_forward_sharded  d_q, d_k, d_v hold THIS rank's batches, chunk after chunk; d_out is the whole
+ *                             [B*S][E] output.  Per chunk the attention kernels run on `stream`, then that chunk is
+ *                             all-gathered in place on the communication stream while the next chunk computes; `stream`
+ *                             finally waits for the last gather.  gather = 0 leaves only this rank's batches valid.
+ *                             elem_bytes 4 = fp32 planes, 2 = bf16 planes (head_dim 64).  Results are the bits of the
+ *                             unsharded call.
  */
+typedef struct hipgpt_shard_ctx hipgpt_shard_ctx;
 HIPGPT_API int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end);
+HIPGPT_API int hipgpt_shard_chunk_range(int B, int world, int rank, int chunks, int chunk, int *b_begin, int *b_end);
+HIPGPT_API int hipgpt_shard_unique_id(void *id128);
+HIPGPT_API int hipgpt_shard_create(hipgpt_shard_ctx **out, const void *id128, int rank, int world);
+HIPGPT_API void hipgpt_shard_destroy(hipgpt_shard_ctx *ctx);
+HIPGPT_API int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *ctx, const void *d_q, const void *d_k, const void *d_v, void *d_out,
+                               int B, int S, int E, int H, int causal, int elem_bytes, int chunks, int gather, void *stream);
+HIPGPT_API int hipgpt_shard_nccl_version(void);
 
 /*
  * Measurement helper (no counterpart in the reference): enqueues a register-resident fp32

@@ -10,6 +10,7 @@
  *   oracle_sdp              src/hip_kernels.cpp:455-473  scaled_dot_product_kernel
  *   oracle_softmax          src/hip_kernels.cpp:478-511  softmax_kernel
  *   oracle_weighted_sum     src/hip_kernels.cpp:514-532  attention_weighted_sum_kernel
+ *   oracle_mha_backward     src/hip_kernels.cpp:1162-1272  multihead_attention_backward_kernel
  *   oracle_decode_row       (extension) one query row over a key/value cache, same
  *                           arithmetic as the flash kernel restricted to one row.
  *
@@ -24,7 +25,7 @@
  * With causal == 0 the functions are the reference's semantics (no mask at all).
  *
  * Parity pin: oracle/Makefile compiles the reference's own hip_kernels.cpp, where it is
- * mounted, into oracle/_ref/libhipgpt_ref.so; tests/test_oracle_vs_reference.py asserts
+ * mounted, into oracle/_ref/libhipgpt_ref.so; tests/test_oracle.py asserts
  * bit equality, and tests/golden/ holds outputs of that reference build.
  *
  * Only tests/, the smoke check and bench.py's CPU-baseline leg may call this file.
@@ -319,4 +320,63 @@ ORACLE_API void oracle_set_num_threads(int n)
 #else
     (void)n;
 #endif
+}
+
+/* dQ, dK, dV as three stacked planes (launcher view, src/hip_kernels.cpp:1242-1255), from dO, the stacked
+ * Q, K, V planes and the stored probabilities.  Loop order of the kernel (:1190-1239): per (token, head) first
+ * w = sum_j p_ij (g . V_j), then for j ascending: dV_j += p_ij g; dQ_i += ds k_j / sqrt(D); dK_j += ds q_i / sqrt(D)
+ * with ds = p_ij ((g . V_j) - w).  The reference's threads add into dK and dV with atomicAdd in whatever
+ * order they run; here queries are visited in ascending order, which is also what the reference source
+ * does when it is run on one host thread through the host stand-in (the pin in tests/test_oracle.py).
+ * `probs` NULL (extension): the probabilities are formed from Q and K by the flash arithmetic above.
+ * `causal` (extension): keys j > i are skipped. */
+ORACLE_API int oracle_mha_backward(const float *gout, const float *qkv, const float *probs, float *gqkv,
+                                   int B, int S, int E, int H, int causal)
+{
+    if (H <= 0 || (E % H) != 0) return -1;
+    const int D = E / H;
+    const size_t plane = (size_t)B * S * E;
+    const float *Q = qkv, *K = qkv + plane, *V = qkv + 2 * plane;
+    float *dQ = gqkv, *dK = gqkv + plane, *dV = gqkv + 2 * plane;
+    const float inv = inv_sqrtf((float)D);
+    memset(gqkv, 0, 3 * plane * sizeof(float));
+    float *prow = probs ? NULL : (float *)malloc(sizeof(float) * (size_t)S);
+    float *scratch = probs ? NULL : (float *)malloc(sizeof(float) * plane);      /* the forward output, unused */
+    for (int h = 0; h < H; ++h)
+        for (long long t = 0; t < (long long)B * S; ++t) {
+            const int b = (int)(t / S), i = (int)(t % S);
+            const float *q = Q + (size_t)t * E + (size_t)h * D, *g = gout + (size_t)t * E + (size_t)h * D;
+            float *dq = dQ + (size_t)t * E + (size_t)h * D;
+            const float *p;
+            if (probs) {
+                p = probs + (((size_t)b * H + h) * (size_t)S + (size_t)i) * (size_t)S;
+            } else {
+                flash_row(Q, K, V, scratch, NULL, prow, S, E, D, (size_t)b * S, i, h, causal);
+                for (int j = causal ? i + 1 : S; j < S; ++j) prow[j] = 0.0f;
+                p = prow;
+            }
+            const int jend = causal ? i + 1 : S;
+            float w = 0.0f;
+            for (int j = 0; j < jend; ++j) {
+                const float *v = V + ((size_t)b * S + j) * E + (size_t)h * D;
+                float vdot = 0.0f;
+                for (int d = 0; d < D; ++d) vdot = MAC(vdot, g[d], v[d]);
+                w = MAC(w, p[j], vdot);
+            }
+            for (int d = 0; d < D; ++d) dq[d] = 0.0f;
+            for (int j = 0; j < jend; ++j) {
+                const float pij = p[j];
+                const float *k = K + ((size_t)b * S + j) * E + (size_t)h * D, *v = V + ((size_t)b * S + j) * E + (size_t)h * D;
+                float *dk = dK + ((size_t)b * S + j) * E + (size_t)h * D, *dv = dV + ((size_t)b * S + j) * E + (size_t)h * D;
+                float vdot = 0.0f;
+                for (int d = 0; d < D; ++d) vdot = MAC(vdot, g[d], v[d]);
+                const float ds = pij * (vdot - w);
+                for (int d = 0; d < D; ++d) dv[d] = MAC(dv[d], pij, g[d]);
+                for (int d = 0; d < D; ++d) dq[d] += ds * k[d] * inv;
+                for (int d = 0; d < D; ++d) dk[d] += ds * q[d] * inv;
+            }
+        }
+    free(prow);
+    free(scratch);
+    return 0;
 }

@@ -211,3 +211,74 @@ def dropout_oracle(x: np.ndarray, p: float):
     lib.oracle_dropout.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_float]
     lib.oracle_dropout(_f(x), _f(out), x.size, p)
     return out
+
+
+# ---- the launchers either side of attention (layer norm, projections, embedding, the whole block) ----
+def matmul(A: np.ndarray, W: np.ndarray, bias, M: int, N: int, K: int, fma: bool = True) -> np.ndarray:
+    """C[M][K] = A[M][N] W[N][K] (+ bias): one accumulator per output, k ascending (fused multiply-add when fma)."""
+    out = np.empty((M, K), dtype=np.float32)
+    lib = oracle_lib(fma)
+    lib.oracle_matmul.restype = None
+    lib.oracle_matmul.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3
+    lib.oracle_matmul(_f(A), _f(W), _f(bias) if bias is not None else None, _f(out), M, N, K)
+    return out
+
+
+def layer_norm(x: np.ndarray, g: np.ndarray, b: np.ndarray, rows: int, E: int, ref_order: bool = False) -> np.ndarray:
+    out = np.empty((rows, E), dtype=np.float32)
+    lib = oracle_lib(False)
+    lib.oracle_layer_norm.restype = None
+    lib.oracle_layer_norm.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3
+    lib.oracle_layer_norm(_f(x), _f(out), _f(g), _f(b), rows, E, int(ref_order))
+    return out
+
+
+def embedding(ids: np.ndarray, tok: np.ndarray, pos: np.ndarray, B: int, S: int, V: int, E: int) -> np.ndarray:
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    out = np.empty((B * S, E), dtype=np.float32)
+    lib = oracle_lib(False)
+    lib.oracle_embedding.restype = None
+    lib.oracle_embedding.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
+    lib.oracle_embedding(_i(ids), _f(tok), _f(pos), _f(out), B, S, V, E)
+    return out
+
+
+def layer_forward(x: np.ndarray, w: np.ndarray, B: int, S: int, E: int, H: int, F: int, dropout_p: float = 0.1,
+                  fma: bool = True) -> np.ndarray:
+    """One HipGPT block (TransformerLayer::forward) on [B*S][E] activations; w = the layer's tensors in checkpoint order."""
+    out = np.empty((B * S, E), dtype=np.float32)
+    lib = oracle_lib(fma)
+    lib.oracle_layer_forward.restype = C.c_int
+    lib.oracle_layer_forward.argtypes = [C.c_void_p] * 3 + [C.c_int] * 5 + [C.c_float]
+    if lib.oracle_layer_forward(_f(x), _f(w), _f(out), B, S, E, H, F, dropout_p) < 0:
+        raise ValueError("oracle rejected the layer")
+    return out
+
+
+# ---- attention backward --------------------------------------------------------------------------------
+def mha_backward(gout: np.ndarray, qkv: np.ndarray, probs, B: int, S: int, E: int, H: int, causal: bool = False,
+                 fma: bool = False) -> np.ndarray:
+    """dQ, dK, dV as three stacked [B*S][E] planes; probs [B][H][S][S] or None (recomputed from Q and K)."""
+    out = np.zeros(3 * B * S * E, dtype=np.float32)
+    lib = oracle_lib(fma)
+    lib.oracle_mha_backward.restype = C.c_int
+    lib.oracle_mha_backward.argtypes = [C.c_void_p] * 4 + [C.c_int] * 5
+    rc = lib.oracle_mha_backward(_f(gout), _f(qkv), _f(probs) if probs is not None else None, _f(out), B, S, E, H, int(causal))
+    if rc < 0:
+        raise ValueError("oracle rejected the configuration")
+    return out
+
+
+def ref_mha_backward(gout: np.ndarray, qkv: np.ndarray, probs: np.ndarray, B: int, S: int, E: int, H: int) -> np.ndarray:
+    """The reference's own backward launcher on ONE host thread (its atomicAdd is a plain add in the stand-in)."""
+    out = np.zeros(3 * B * S * E, dtype=np.float32)
+    lib = ref_lib()
+    before = lib.ref_num_threads()
+    lib.ref_set_num_threads(1)
+    try:
+        lib.ref_mha_backward.restype = None
+        lib.ref_mha_backward.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
+        lib.ref_mha_backward(_f(gout), _f(qkv), _f(probs), _f(out), B, S, E, H)
+    finally:
+        lib.ref_set_num_threads(before)
+    return out

@@ -334,3 +334,111 @@ ORACLE_API int oracle_gpt_generate_window(const float *weights, int V, int S, in
     free(x); free(h); free(x1); free(qkv); free(att); free(proj); free(probs); free(ff); free(logits); free(seq); free(ids); free(lw);
     return 0;
 }
+
+/* ---- the launchers either side of attention, for the parity tests of the library's own versions ---------- */
+
+/* C[M][K] = A[M][N] W[N][K] (+ bias), the reference's argument order and summation order
+ * (src/hip_kernels.cpp:69-154: one accumulator, k ascending, bias once at the end). */
+ORACLE_API void oracle_matmul(const float *A, const float *W, const float *bias, float *C, int M, int N, int K)
+{
+    matmul_rows(A, W, bias, C, M, N, K, 0);
+}
+
+/* Sum in the order of the reference's layer-norm kernel (src/hip_kernels.cpp:775-801): `threads` lanes add
+ * strided elements ascending, every 64-lane wave folds itself with offsets 32 .. 1, the wave leaders' sums are
+ * folded with offsets 16 .. 1.  A launch of fewer than 64 threads leaves lanes of the wave inactive, and what
+ * __shfl_down returns from them is not defined; they count as 0 here (only lane 0's result is used, and with
+ * 64 threads or more lane 0 never reads past its wave). */
+static float wave64_order_sum(const float *x, int n, int threads, float shift, int square)
+{
+    float lane[1024], wave[32];
+    for (int t = 0; t < threads; ++t) {
+        float s = 0.0f;
+        for (int e = t; e < n; e += threads) {
+            const float v = x[e] - shift;
+            s += square ? v * v : v;
+        }
+        lane[t] = s;
+    }
+    const int nwaves = (threads + 63) / 64;
+    for (int w = 0; w < nwaves; ++w) {
+        float *v = lane + 64 * w;
+        const int width = threads - 64 * w < 64 ? threads - 64 * w : 64;
+        for (int off = 32; off > 0; off >>= 1) {
+            float t[64];
+            for (int l = 0; l < width; ++l) t[l] = v[l] + (l + off < width ? v[l + off] : 0.0f);
+            memcpy(v, t, sizeof(float) * width);
+        }
+        wave[w] = v[0];
+    }
+    for (int w = nwaves; w < 32; ++w) wave[w] = 0.0f;
+    for (int off = 16; off > 0; off >>= 1) {
+        float t[32];
+        for (int l = 0; l < 32; ++l) t[l] = wave[l] + (l + off < 32 ? wave[l + off] : 0.0f);
+        memcpy(wave, t, sizeof(t));
+    }
+    return wave[0];
+}
+
+/* ref_order = 0: sums in the order of a 32-lane strided partial sum and a butterfly (what the library's kernel
+ * does); 1: in the order of the reference's kernel launched with its own thread count (the power of two at or
+ * above min(E, 1024), src/hip_kernels.cpp:838-848).  The two differ by rounding only. */
+ORACLE_API void oracle_layer_norm(const float *x, float *y, const float *g, const float *b, int rows, int E, int ref_order)
+{
+    int threads = 1;
+    while (threads < (E < 1024 ? E : 1024)) threads <<= 1;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const float *xr = x + (size_t)r * E;
+        float *yr = y + (size_t)r * E;
+        if (!ref_order) { layer_norm(xr, yr, g, b, E); continue; }
+        const float mean = wave64_order_sum(xr, E, threads, 0.0f, 0) / (float)E;
+        const float var = wave64_order_sum(xr, E, threads, mean, 1) / (float)E;
+        const float inv = 1.0f / sqrtf(var + 1e-5f);
+        for (int e = 0; e < E; ++e) yr[e] = g[e] * (xr[e] - mean) * inv + b[e];
+    }
+}
+
+/* out[t][e] = tok[id_t][e] + pos[t mod S][e], zeros for an id outside [0, V) (src/hip_kernels.cpp:537-581). */
+ORACLE_API void oracle_embedding(const int *ids, const float *tok, const float *pos, float *out, int B, int S, int V, int E)
+{
+    for (long long t = 0; t < (long long)B * S; ++t) {
+        const int id = ids[t];
+        for (int e = 0; e < E; ++e)
+            out[t * E + e] = (id < 0 || id >= V) ? 0.0f : tok[(size_t)id * E + e] + pos[(size_t)(t % S) * E + e];
+    }
+}
+
+/* One pre-LN block as TransformerLayer::forward runs it (src/transformer_layer.cpp:232-253) on B*S tokens:
+ * layer norm, QKV projection whose [T][3E] output the attention launcher reads as three stacked [T][E] planes
+ * (src/hip_kernels.cpp:415-417), attention without mask, output projection, dropout, residual; layer norm,
+ * FF1, ReLU, FF2, dropout, residual.  `w` holds the layer's tensors in checkpoint order
+ * (src/transformer_layer.cpp:312-344): Wqkv, Wo, W1, W2, bqkv, bo, b1, b2, attn gamma, beta, ffn gamma, beta. */
+ORACLE_API int oracle_layer_forward(const float *x, const float *w, float *out, int B, int S, int E, int H, int F, float dropout_p)
+{
+    if (B < 0 || S <= 0 || E <= 0 || H <= 0 || F <= 0 || E % H) return -1;
+    const float *p = w;
+    layer_w lw;
+    lw.wqkv = take(&p, (long long)E * 3 * E); lw.wo = take(&p, (long long)E * E);
+    lw.w1 = take(&p, (long long)E * F); lw.w2 = take(&p, (long long)F * E);
+    lw.bqkv = take(&p, 3LL * E); lw.bo = take(&p, E); lw.b1 = take(&p, F); lw.b2 = take(&p, E);
+    lw.g1 = take(&p, E); lw.be1 = take(&p, E); lw.g2 = take(&p, E); lw.be2 = take(&p, E);
+    const size_t T = (size_t)B * S, TE = T * E;
+    float *h = (float *)malloc(sizeof(float) * TE), *x1 = (float *)malloc(sizeof(float) * TE);
+    float *qkv = (float *)malloc(sizeof(float) * 3 * TE), *att = (float *)malloc(sizeof(float) * TE), *proj = (float *)malloc(sizeof(float) * TE);
+    float *ff = (float *)malloc(sizeof(float) * T * F);
+    int rc = 0;
+#pragma omp parallel for schedule(static)
+    for (long long t = 0; t < (long long)T; ++t) layer_norm(x + (size_t)t * E, h + (size_t)t * E, lw.g1, lw.be1, E);
+    matmul_rows(h, lw.wqkv, lw.bqkv, qkv, (int)T, E, 3 * E, 0);
+    if (oracle_mha_dispatch(qkv, att, NULL, B, S, E, H, 0) < 0) rc = -1;
+    matmul_rows(att, lw.wo, lw.bo, proj, (int)T, E, E, 0);
+    for (size_t i = 0; i < TE; ++i) x1[i] = x[i] + dropout_one(proj[i], (unsigned int)i, dropout_p);
+#pragma omp parallel for schedule(static)
+    for (long long t = 0; t < (long long)T; ++t) layer_norm(x1 + (size_t)t * E, h + (size_t)t * E, lw.g2, lw.be2, E);
+    matmul_rows(h, lw.w1, lw.b1, ff, (int)T, E, F, 1);
+    matmul_rows(ff, lw.w2, lw.b2, proj, (int)T, F, E, 0);
+    for (size_t i = 0; i < TE; ++i) out[i] = x1[i] + dropout_one(proj[i], (unsigned int)i, dropout_p);
+    free(h); free(x1); free(qkv); free(att); free(proj); free(ff);
+    return rc;
+}

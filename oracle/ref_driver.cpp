@@ -64,6 +64,15 @@ void ref_embedding_lookup(const int *ids, const float *tok, const float *pos, fl
     launch_embedding_lookup(ids, tok, pos, out, B, S, V, E);
 }
 
+/* The attention backward launcher (src/hip_kernels.cpp:1242-1272).  Its kernel adds into dK and dV with
+ * atomicAdd, which the host stand-in runs as a plain add: call it with ONE host thread (ref_set_num_threads(1)),
+ * where the order of those additions is ascending in the query index. */
+__attribute__((visibility("default")))
+void ref_mha_backward(const float *gout, const float *qkv, const float *probs, float *gqkv, int B, int S, int E, int H)
+{
+    launch_multihead_attention_backward(gout, qkv, probs, gqkv, B, S, E, H);
+}
+
 __attribute__((visibility("default")))
 int ref_num_threads(void)
 {

@@ -64,3 +64,30 @@ def test_local_planes_are_contiguous_slabs():
     loc = sharding.local_planes(qkv, B, S, E, 1, 3)
     assert loc.shape == (3, 2 * S, E) and loc.is_contiguous()
     assert torch.equal(loc[1], qkv[1, S:3 * S])
+
+
+@pytest.mark.parametrize("B,world,chunks", [(64, 8, 4), (32, 2, 16), (8, 2, 2), (6, 3, 1), (4, 4, 1)])
+def test_chunk_ranges_tile_the_batches_in_gather_order(B, world, chunks):
+    """Chunk c of the output must be one contiguous block holding the ranks' parts in rank order: that is what lets
+    ncclAllGather work in place (sendbuff = recvbuff + rank * count)."""
+    k = B // (world * chunks)
+    seen = []
+    for c in range(chunks):
+        for r in range(world):
+            b0, b1 = sharding.chunk_range(B, world, r, chunks, c)
+            assert b1 - b0 == k and b0 == c * world * k + r * k
+            seen += list(range(b0, b1))
+    assert seen == list(range(B))
+    qkv = torch.arange(3 * B * 2 * 4, dtype=torch.float32).view(3, B * 2, 4)
+    for r in range(world):
+        loc = sharding.local_planes_chunked(qkv, B, 2, 4, world, r, chunks)
+        want = torch.cat([qkv.view(3, B, 2, 4)[:, slice(*sharding.chunk_range(B, world, r, chunks, c))] for c in range(chunks)], dim=1)
+        assert torch.equal(loc, want.reshape(3, -1, 4))
+
+
+def test_chunk_range_refuses_uneven_splits():
+    from hipgpt_b200 import _capi
+    with pytest.raises(_capi.HipGPTError, match="not a multiple"):
+        sharding.chunk_range(10, 4, 0, 1, 0)
+    with pytest.raises(_capi.HipGPTError):
+        sharding.chunk_range(8, 2, 0, 2, 2)

@@ -53,7 +53,7 @@ def test_tensor_kernel_probabilities_match_oracle(shape, causal):
     E = H * D
     qkv = synth.qkv_planes(2500 + S + D, B, S, E)
     ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=True)
-    out, probs = gpu_mha(qkv, B, S, E, H, causal, True, algo=_capi.ALGO_TENSOR)
+    out, probs = gpu_mha(qkv, B, S, E, H, causal, True, algo=_capi.ALGO_TENSOR, warps=_capi.TENSOR_TILED)
     assert _status() == 0
     assert np.isfinite(out).all() and np.isfinite(probs).all()      # the buffers were pre-filled with NaN
     assert float(np.abs(out - ref_out).max()) <= TOL
@@ -61,7 +61,7 @@ def test_tensor_kernel_probabilities_match_oracle(shape, causal):
     if causal:
         assert np.all(np.triu(probs, 1) == 0.0)
     # the same call without probabilities gives the same output bits: the second sweep only adds stores
-    out2, _ = gpu_mha(qkv, B, S, E, H, causal, False, algo=_capi.ALGO_TENSOR)
+    out2, _ = gpu_mha(qkv, B, S, E, H, causal, False, algo=_capi.ALGO_TENSOR, warps=_capi.TENSOR_TILED)
     assert np.array_equal(out, out2)
 
 
