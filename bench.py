@@ -244,18 +244,24 @@ def scaling_c5_leg(world, rank, lib):
     if B % world:
         return {"skipped": f"{B} batches do not split over {world} ranks"}
     Bl = B // world
-    chunks = next(ch for ch in (16, 8, 4, 2, 1) if Bl % ch == 0)
+
+    def chunks_for(esz):
+        # a chunk should carry at least ~16 MB of output: below that the per-chunk launches and collectives cost
+        # more than their overlap saves
+        want = max(1, min(16, int(Bl * S * E * esz) // (16 << 20)))
+        return next(ch for ch in range(want, 0, -1) if Bl % ch == 0)
     sh = sharding.ShardedAttention()
     stream = torch.cuda.current_stream()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     out = {"config": f"c5: causal MHA forward B={B} H={H} S={S} head_dim={D}, batches split over {world} rank(s)",
            "flops_per_call": flops_of(B, H, S, D, True), "nccl_version": int(lib.hipgpt_shard_nccl_version()),
-           "gather_chunks": chunks, "reps": 5}
+           "reps": 5}
     for name, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
         g = torch.Generator(device="cuda")
         g.manual_seed(4 + rank)
         loc = torch.randn((3, Bl * S, E), device="cuda", generator=g, dtype=torch.float32).to(dtype)
         full = torch.empty((B * S, E), device="cuda", dtype=dtype)
+        chunks = chunks_for(full.element_size())
 
         def call(ch, gather):
             sh.forward(loc[0], loc[1], loc[2], full, B, S, E, H, causal=True, chunks=ch, gather=gather)
@@ -288,6 +294,7 @@ def scaling_c5_leg(world, rank, lib):
                 continue
             ms = timed(ch, gather)
             res[label] = {"ms": ms, "tflops": flops_of(B, H, S, D, True) / (ms * 1e-3) / 1e12}
+        res["gather_chunks"] = chunks
         res["gathered_bytes_per_rank"] = int((B - Bl) * S * E * full.element_size()) if world > 1 else 0
         out[name] = res
         del loc, full

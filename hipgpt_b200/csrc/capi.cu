@@ -287,9 +287,14 @@ static int mha_forward_host_impl(const void *h_qkv_v, void *h_out_v, float *h_pr
     }
     e = cudaStreamSynchronize(s_out);                // its last copy waits for the last kernel, which waits for the last copy in
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "host-buffer call: %s", cudaGetErrorString(e));
-    // a block whose bounded wait ran out stored nothing: the output would be stale
-    int status = 0;
-    const int src = fetch_status_words(&status);
+    // a block whose bounded wait ran out stored nothing: the output would be stale.  Only the status word of the
+    // kernel this call ran is read (one small copy; the words of the other kernels stay for hipgpt_kernel_status).
+    int status = 0, src = HIPGPT_OK;
+    const int D = E / H;
+    if (esz == 2) src = bf16_status_fetch(&status);
+    else if ((D == 32 || D == 64) && full_range()) src = h_probs ? HIPGPT_OK : tc_status_fetch(&status);
+    else if (!h_probs && D == 32 && S <= 256) src = head_status_fetch(&status), status = status ? 400 + status : 0;
+    else if (D == 32 || D == 64) src = tc16_status_fetch(&status), status = status ? 300 + status : 0;
     if (src != HIPGPT_OK) return src;
     if (status != 0) return fail(HIPGPT_ERR_CUDA, "a bounded wait inside a kernel ran out (status %d); the output is incomplete", status);
     return HIPGPT_OK;
