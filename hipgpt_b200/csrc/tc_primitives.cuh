@@ -7,6 +7,7 @@ namespace hipgpt {
 
 constexpr long long kSpinLimit = 1LL << 24;      // polls per wait, and
 constexpr long long kCycleLimit = 1LL << 31;     // SM cycles per wait (about one second)
+constexpr uint32_t kSuspendHintNs = 20000;       // how long one try_wait may sleep before it returns unsatisfied
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -43,13 +44,14 @@ __device__ __forceinline__ bool mbar_wait_for(uint64_t *bar, uint32_t parity, lo
     if (done) return true;
     const long long deadline = clock64() + cycle_limit;
     for (long long i = 0; i < poll_limit; ++i) {
+        // the thread sleeps inside the instruction until the phase completes or the hinted time (ns) has passed
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+            : "=r"(done) : "r"(addr), "r"(parity), "r"(kSuspendHintNs) : "memory");
         if (done) return true;
-        if ((i & 15) == 15 && clock64() > deadline) break;
+        if ((i & 3) == 3 && clock64() > deadline) break;
     }
     return false;
 }
