@@ -48,7 +48,7 @@ bool mha_tc16_supports(int head_dim);
 int tc16_status_fetch(int *status);
 int tc16_notice_fetch(int *notice);
 // whole-head kernel (head_dim 32, S <= 256): TMA loads, 128-key products, all score tiles of a head in TMEM
-int launch_mha_head(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st);
+int launch_mha_head(const float *q, const float *k, const float *v, float *out, float *probs, int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_head_supports(int head_dim, int S, int E, const void *q, const void *k, const void *v, const void *out);
 int head_status_fetch(int *status);
 int head_notice_fetch(int *notice);

@@ -31,11 +31,14 @@
 // tile of the same rows (shared memory + mbarrier), exponentials, P to TMEM; at the end the groups of a
 // query tile share its output columns.  The control lane issues the copies and every product in a fixed
 // order, so results do not depend on timing.
+// Probabilities (when asked for): a row's sum is known once all its tiles have been through the exponentials;
+// the workers then read P_hi + P_lo back from TMEM, divide by the sum and store [B][H][S][S]: no second Q K^T.
 // Every wait is bounded: on expiry the block raises a flag that cuts all later waits short, records a
 // site code for hipgpt_kernel_status, skips its stores, frees its TMEM and returns.
 #include "tc_primitives.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <math.h>
 
 #include <mutex>
@@ -116,9 +119,9 @@ struct HeadMaps {
     CUtensorMap q, k, v;
 };
 
-template <bool CAUSAL>
+template <bool CAUSAL, bool PROBS>
 __global__ void __launch_bounds__(kHeadThreads, 1)
-mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, int S, int E, int H, int BH, float cscale)
+mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, float *__restrict__ P, int S, int E, int H, int BH, float cscale)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -128,7 +131,7 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
     uint8_t *v_16 = base + kOffV16;              // [V_hi | V_lo] (64 columns) fp16, N-major without swizzle: 8 keys x 8 columns
                                                  // form one 128-byte core matrix, column blocks 128 bytes apart, key groups 1024
     __shared__ uint64_t ld_q[2], ld_k[2], ld_v[2], cv_q[2], cv_k[2], cv_v[2];
-    __shared__ uint64_t s_full[3], p_full[4], o_done[2], xm[2], xs[2], epi_done, vx;
+    __shared__ uint64_t s_full[3], p_full[4], o_done[2], xm[2], xs[2], epi_done, vx, pr_done;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ float xmax[2][2][2][kTile];       // [head parity][query tile][slot][row]
@@ -141,7 +144,8 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
     const int nq = S > kTile ? 2 : 1;            // query tiles = key tiles of a head
 
     // site codes: 1 Q/K/V landed, 2 operand converted, 3 S ready, 4 P written, 5 output complete,
-    // 6 row maxima exchanged, 7 row sums exchanged, 8 previous head's output read, 9 V maximum exchanged
+    // 6 row maxima exchanged, 7 row sums exchanged, 8 previous head's output read, 9 V maximum exchanged,
+    // 10 probabilities of the first tile read back
     auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
         if (abort_flag) return;
         if (!mbar_wait_for(bar, parity, kHeadCycleLimit, kHeadPollLimit)) { abort_flag = 1; atomicCAS(&g_head_status, 0, site); }
@@ -182,6 +186,7 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
             for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 4);
             mbar_init(&epi_done, kHeadWorkers / 32);
             mbar_init(&vx, 4);
+            mbar_init(&pr_done, 4);
             if ((int)blockIdx.x < BH) { load_qk(blockIdx.x); load_v(blockIdx.x); }
         }
         __syncwarp();
@@ -228,6 +233,12 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                 const int next = hd + (int)gridDim.x;
                 const bool has_next = next < BH;
                 // ---- Q K^T of every tile whose buffer is free ---------------------------------------
+                // (with the probabilities stored, the workers read P back from these buffers until their output is out,
+                // and stage them in the Q and K areas of shared memory, so this head's Q and K are fetched only now)
+                if (PROBS && it > 0) {
+                    wait(&epi_done, (uint32_t)((it - 1) & 1), 8);
+                    load_qk(hd);
+                }
                 wait(&cv_k[0], par, 2);
                 wait(&cv_q[0], par, 2);
                 tc_fence_after();
@@ -254,7 +265,7 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                     if (over || (flush > 3.8e-6f && (aq + ak) > 8.0f * aq * ak)) atomicOr(&g_head_notice, 1);
                 }
                 const bool tail_qk = !CAUSAL && nq == 2;    // the fourth tile's Q K^T comes after the first two P V products
-                if (has_next && !tail_qk) {
+                if (has_next && !tail_qk && !PROBS) {
                     // the raw Q and K tiles and their fp16 copies are free once every Q K^T has completed
                     wait(&s_full[0], par, 3);
                     if (nq == 2) { wait(&s_full[1], par, 3); wait(&s_full[2], par, 3); }
@@ -263,7 +274,7 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                 wait(&cv_v[0], par, 2);
                 if (nq == 2) wait(&cv_v[1], par, 2);
                 if (has_next) load_v(next);              // the raw V tiles have been read
-                if (it > 0) wait(&epi_done, (uint32_t)((it - 1) & 1), 8);     // the previous head's output has left TMEM
+                if (!PROBS && it > 0) wait(&epi_done, (uint32_t)((it - 1) & 1), 8);     // the previous head's output has left TMEM
                 // ---- P V, in a fixed order ------------------------------------------------------------
                 wait(&p_full[0], par, 4);
                 tc_fence_after();
@@ -278,9 +289,11 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                         wait(&p_full[1], par, 4); tc_fence_after(); issue_pv(0, 1, 1, false);
                         tc_commit(&o_done[0]);
                         // (q1, k1) into the first buffer: its P has been consumed by the product issued above
-                        // (instructions run in order) and its workers have arrived at p_full[0]
+                        // (instructions run in order) and its workers have arrived at p_full[0]; with the probabilities
+                        // stored they have also read that P back
+                        if (PROBS) wait(&pr_done, par, 10);
                         issue_qk(1, 1, 0);
-                        if (has_next) {
+                        if (has_next && !PROBS) {
                             wait(&s_full[0], 1u, 3);     // second completion of this barrier in this head
                             wait(&s_full[1], par, 3);
                             wait(&s_full[2], par, 3);
@@ -443,6 +456,74 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
         // the group that holds the other key tile of the same rows, exponentials (second sweep), P_hi and
         // P_lo over S in place.  Chunk c = score columns [32c, 32c+32): its P_hi (packed fp16) goes to
         // columns [32c, 32c+16), its P_lo to [32c+16, 32c+32), so a chunk is rewritten where it was read.
+        // The probabilities of one tile, normalised: P_hi + P_lo read back from TMEM, divided by the row's sum over all
+        // of its tiles (P carries a factor 2^8, and so does the sum).  A worker holds a row, so its own stores would be
+        // 16-byte pieces S floats apart; the warp turns each 32 x 32 chunk through shared memory instead and stores four
+        // rows of 128 contiguous bytes per instruction.  The scratch is the first tile of the raw Q (group 0), of the fp16
+        // Q (group 1) or of the raw K (group 2): free once the products that read them have completed, which the caller
+        // has made sure of.  Chunks that no row of the warp sees are zeros.
+        auto store_probs = [&](uint32_t job, float l_total) {
+            const int q = job & 1, k = (job >> 1) & 1, buf = (job >> 2) & 3;
+            const uint32_t s_addr = lane_base + (uint32_t)(buf * kTile);
+            const int ncols = min(kTile, S - k * kTile);
+            const bool diag = CAUSAL && q == k;
+            const int nwarp = diag ? min(ncols, wq * 32 + 32) : ncols;
+            const int nch = (nwarp + 31) >> 5;
+            const int wrow0 = q * kTile + wq * 32;              // first row of this warp
+            const float inv = 1.0f / fmaxf(l_total, 1e-20f);
+            uint8_t *tb = (grp == 0 ? q_raw : grp == 1 ? q_16 : k_raw) + wq * 4096;   // [32 rows][128 bytes], 16-byte chunks swizzled by the row
+            float *pw = P + ((size_t)hd * S + wrow0) * (size_t)S + (size_t)k * kTile;
+            const bool vec = (S & 3) == 0;                      // then every group of four columns is 16-byte aligned
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                const int nleft = ncols - c * 32;               // columns of this chunk that exist
+                if (nleft <= 0) break;
+                if (c < nch) {
+                    float w[32];
+                    tmem_ld32(s_addr + c * 32, w);              // 16 words of packed P_hi, then 16 of packed P_lo
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float o[4];
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const __half2 hh = *reinterpret_cast<const __half2 *>(&w[2 * j + i]), ll = *reinterpret_cast<const __half2 *>(&w[16 + 2 * j + i]);
+                            o[2 * i] = (__low2float(hh) + __low2float(ll)) * inv;
+                            o[2 * i + 1] = (__high2float(hh) + __high2float(ll)) * inv;
+                        }
+                        *reinterpret_cast<float4 *>(tb + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4 *>(tb + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                __syncwarp();
+                if (!abort_flag) {
+                    if (vec) {
+                        const int ch = lane & 7;                // 16-byte piece of a row
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = 4 * i + (lane >> 3);
+                            const float4 val = *reinterpret_cast<const float4 *>(tb + rr * 128 + ((ch ^ (rr & 7)) << 4));
+                            if (wrow0 + rr < S && 4 * ch < nleft) *reinterpret_cast<float4 *>(pw + (size_t)rr * S + c * 32 + 4 * ch) = val;
+                        }
+                    } else {
+                        for (int rr = 0; rr < 32 && wrow0 + rr < S; ++rr)
+                            if (lane < nleft)
+                                pw[(size_t)rr * S + c * 32 + lane] = *reinterpret_cast<const float *>(tb + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
+                    }
+                }
+                __syncwarp();                                   // the chunk is out before the next one is staged
+            }
+            // a causal head's first query tile has no second key tile: those columns are zeros
+            if (CAUSAL && q == 0 && k == 0 && !abort_flag)
+                for (int rr = 0; rr < 32 && wrow0 + rr < S; ++rr) {
+                    float *pr = P + ((size_t)hd * S + wrow0 + rr) * (size_t)S;
+                    if (vec) for (int col = kTile + 4 * lane; col < S; col += 128) *reinterpret_cast<float4 *>(pr + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    else for (int col = kTile + lane; col < S; col += 32) pr[col] = 0.0f;
+                }
+        };
         float lsum[2] = {0.0f, 0.0f};
 #pragma unroll 1
         for (int ji = 0; ji < njobs; ++ji) {
@@ -505,10 +586,17 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                 arrive(&xs[q]);
             }
             if (ji) lsum[1] = ps; else lsum[0] = ps;
+            if (PROBS && !CAUSAL && njobs == 2 && ji == 0) {
+                // this tile's buffer is taken by the group's second tile: its probabilities leave now
+                wait(&xs[q], par, 7);
+                store_probs(job, ps + xsum[par][q][slot ^ 1][rloc]);
+                tc_fence_before();
+                arrive(&pr_done);
+            }
         }
         // the next head's K and Q have landed by now (their copies were issued when this head's Q K^T had
         // completed): converting them here lets its Q K^T run while this head's output is stored
-        if (grp < 2 && hd + (int)gridDim.x < BH) convert_kq(it + 1);
+        if (!PROBS && grp < 2 && hd + (int)gridDim.x < BH) convert_kq(it + 1);
         // ---- output: (P_hi V_hi + corrections) / (l * V's scale); the groups of a query tile share its columns ----
 #pragma unroll 1
         for (int ji = 0; ji < njobs; ++ji) {
@@ -521,8 +609,9 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
                 wait(&xs[q], par, 7);
                 l += xsum[par][q][slot ^ 1][rloc];
             }
-            wait(&o_done[q], par, 5);
+            wait(&o_done[q], par, 5);                    // every product of this head issued so far has completed
             tc_fence_after();
+            if (PROBS && !(!CAUSAL && njobs == 2 && ji == 0)) store_probs(job, l);
             const float inv = (1.0f / fmaxf(l, 1e-20f)) * s_vinv[par];
             const int row = q * kTile + rloc;
             const bool store = !abort_flag && row < S;
@@ -544,6 +633,8 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, in
         }
         tc_fence_before();
         arrive(&epi_done);
+        // with the probabilities stored, shared memory of this head served as their staging area until now
+        if (PROBS && grp < 2 && hd + (int)gridDim.x < BH) convert_kq(it + 1);
     }
     tc_fence_before();
     __syncthreads();
@@ -586,10 +677,10 @@ int make_plane_map(CUtensorMap *m, const float *plane, int B, int S, int E)
     return HIPGPT_OK;
 }
 
-template <bool CAUSAL>
-int launch_head_cfg(const HeadMaps &maps, float *out, int B, int S, int E, int H, cudaStream_t st)
+template <bool CAUSAL, bool PROBS>
+int launch_head_cfg(const HeadMaps &maps, float *out, float *probs, int B, int S, int E, int H, cudaStream_t st)
 {
-    auto kern = mha_head_kernel<CAUSAL>;
+    auto kern = mha_head_kernel<CAUSAL, PROBS>;
     const size_t smem = kHeadSmemBytes + 1024;
     static bool attr_set = false;                    // per instantiation; setting it twice is harmless
     if (!attr_set) {
@@ -604,7 +695,7 @@ int launch_head_cfg(const HeadMaps &maps, float *out, int B, int S, int E, int H
     if (bh > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "%lld (batch, head) pairs are too many", bh);
     const unsigned grid = (unsigned)(bh < sms ? bh : sms);
     const float cscale = (1.0f / sqrtf(32.0f)) * kLog2e;
-    kern<<<grid, kHeadThreads, smem, st>>>(maps, out, S, E, H, (int)bh, cscale);
+    kern<<<grid, kHeadThreads, smem, st>>>(maps, out, probs, S, E, H, (int)bh, cscale);
     return check_launch("mha_head_kernel");
 }
 
@@ -619,7 +710,7 @@ bool mha_head_supports(int head_dim, int S, int E, const void *q, const void *k,
            encode_fn() != nullptr;
 }
 
-int launch_mha_head(const float *q, const float *k, const float *v, float *out, int B, int S, int E, int H, int causal, cudaStream_t st)
+int launch_mha_head(const float *q, const float *k, const float *v, float *out, float *probs, int B, int S, int E, int H, int causal, cudaStream_t st)
 {
     if (E / H != 32 || S > 2 * kTile) return fail(HIPGPT_ERR_UNSUPPORTED, "whole-head kernel: head_dim %d, S %d", E / H, S);
     if (B == 0 || S == 0) return HIPGPT_OK;
@@ -628,7 +719,8 @@ int launch_mha_head(const float *q, const float *k, const float *v, float *out, 
     if (rc == HIPGPT_OK) rc = make_plane_map(&maps.k, k, B, S, E);
     if (rc == HIPGPT_OK) rc = make_plane_map(&maps.v, v, B, S, E);
     if (rc != HIPGPT_OK) return rc;
-    return causal ? launch_head_cfg<true>(maps, out, B, S, E, H, st) : launch_head_cfg<false>(maps, out, B, S, E, H, st);
+    if (probs) return causal ? launch_head_cfg<true, true>(maps, out, probs, B, S, E, H, st) : launch_head_cfg<false, true>(maps, out, probs, B, S, E, H, st);
+    return causal ? launch_head_cfg<true, false>(maps, out, nullptr, B, S, E, H, st) : launch_head_cfg<false, false>(maps, out, nullptr, B, S, E, H, st);
 }
 
 // Reads and clears a status word of this file.

@@ -81,7 +81,7 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
         // tensor pipe when it applies (fp32-grade TF32 + FP16 products): the whole-head kernel for the default
         // model's shape, the tiled kernel otherwise (it also stores the probabilities, by a second sweep);
         // FFMA rows kernel for head_dim 128; generic kernel for everything else
-        if (!probs && mha_head_supports(D, S, E, q, k, v, out)) return launch_mha_head(q, k, v, out, B, S, E, H, causal, st);
+        if (mha_head_supports(D, S, E, q, k, v, out)) return launch_mha_head(q, k, v, out, probs, B, S, E, H, causal, st);
         if (tensor_ok) return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
         if (mha_rows_supports(D) && aligned) return launch_mha_rows(q, k, v, out, probs, B, S, E, H, causal, warps, st);
         return launch_mha_generic(q, k, v, out, probs, B, S, E, H, causal, st);
@@ -95,7 +95,7 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
         if (!tensor_ok) return fail(HIPGPT_ERR_UNSUPPORTED, "tensor-core kernel: head_dim %d is not 32 or 64", D);
         switch (warps) {                             // `warps` selects the kernel here
         case HIPGPT_TENSOR_DEFAULT:
-            if (!probs && mha_head_supports(D, S, E, q, k, v, out)) return launch_mha_head(q, k, v, out, B, S, E, H, causal, st);
+            if (mha_head_supports(D, S, E, q, k, v, out)) return launch_mha_head(q, k, v, out, probs, B, S, E, H, causal, st);
             return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
         case HIPGPT_TENSOR_SPLIT_TF32:
             if (probs) return fail(HIPGPT_ERR_UNSUPPORTED, "split-TF32 kernel stores no probabilities");
@@ -103,10 +103,9 @@ int mha_dispatch(const float *q, const float *k, const float *v, float *out, flo
         case HIPGPT_TENSOR_TILED:
             return launch_mha_tc16(q, k, v, out, probs, B, S, E, H, causal, st);
         case HIPGPT_TENSOR_WHOLE_HEAD:
-            if (probs) return fail(HIPGPT_ERR_UNSUPPORTED, "whole-head kernel stores no probabilities");
             if (!mha_head_supports(D, S, E, q, k, v, out))
                 return fail(HIPGPT_ERR_UNSUPPORTED, "whole-head kernel: needs head_dim 32 and S <= 256 (head_dim %d, S %d)", D, S);
-            return launch_mha_head(q, k, v, out, B, S, E, H, causal, st);
+            return launch_mha_head(q, k, v, out, probs, B, S, E, H, causal, st);
         default:
             return fail(HIPGPT_ERR_BAD_ARG, "unknown tensor-core kernel %d", warps);
         }
@@ -293,7 +292,7 @@ static int mha_forward_host_impl(const void *h_qkv_v, void *h_out_v, float *h_pr
     const int D = E / H;
     if (esz == 2) src = bf16_status_fetch(&status);
     else if ((D == 32 || D == 64) && full_range()) src = h_probs ? HIPGPT_OK : tc_status_fetch(&status);
-    else if (!h_probs && D == 32 && S <= 256) src = head_status_fetch(&status), status = status ? 400 + status : 0;
+    else if (D == 32 && S <= 256) src = head_status_fetch(&status), status = status ? 400 + status : 0;
     else if (D == 32 || D == 64) src = tc16_status_fetch(&status), status = status ? 300 + status : 0;
     if (src != HIPGPT_OK) return src;
     if (status != 0) return fail(HIPGPT_ERR_CUDA, "a bounded wait inside a kernel ran out (status %d); the output is incomplete", status);
