@@ -116,11 +116,16 @@ weighted_sum_kernel(const float *__restrict__ P, const float *__restrict__ V, fl
 
 int launch_sdp(const float *Q, const float *K, float *scores, int B, int S, int D, cudaStream_t st)
 {
-    if (B > 65535) return fail(HIPGPT_ERR_BAD_ARG, "B' = %d exceeds 65535 batch items per launch", B);
-    const dim3 grid((S + kTile - 1) / kTile, (S + kTile - 1) / kTile, B), block(kTile, 8);
     const float inv = 1.0f / sqrtf((float)D);              // IEEE divide and sqrt: the host's value
-    sdp_kernel<<<grid, block, 0, st>>>(Q, K, scores, S, D, inv);
-    return check_launch("sdp_kernel");
+    // the batch index rides on grid.z, which holds 65535 at most: more batch items take several launches
+    for (int b0 = 0; b0 < B; b0 += 65535) {
+        const int nb = B - b0 < 65535 ? B - b0 : 65535;
+        const dim3 grid((S + kTile - 1) / kTile, (S + kTile - 1) / kTile, nb), block(kTile, 8);
+        sdp_kernel<<<grid, block, 0, st>>>(Q + (size_t)b0 * S * D, K + (size_t)b0 * S * D, scores + (size_t)b0 * S * S, S, D, inv);
+        const int rc = check_launch("sdp_kernel");
+        if (rc != HIPGPT_OK) return rc;
+    }
+    return HIPGPT_OK;
 }
 
 int launch_softmax_rows(const float *scores, float *out, int B, int S, cudaStream_t st)
@@ -134,10 +139,14 @@ int launch_softmax_rows(const float *scores, float *out, int B, int S, cudaStrea
 
 int launch_weighted_sum(const float *P, const float *V, float *out, int B, int S, int D, cudaStream_t st)
 {
-    if (B > 65535) return fail(HIPGPT_ERR_BAD_ARG, "B' = %d exceeds 65535 batch items per launch", B);
-    const dim3 grid((D + kTile - 1) / kTile, (S + kTile - 1) / kTile, B), block(kTile, 8);
-    weighted_sum_kernel<<<grid, block, 0, st>>>(P, V, out, S, D);
-    return check_launch("weighted_sum_kernel");
+    for (int b0 = 0; b0 < B; b0 += 65535) {
+        const int nb = B - b0 < 65535 ? B - b0 : 65535;
+        const dim3 grid((D + kTile - 1) / kTile, (S + kTile - 1) / kTile, nb), block(kTile, 8);
+        weighted_sum_kernel<<<grid, block, 0, st>>>(P + (size_t)b0 * S * S, V + (size_t)b0 * S * D, out + (size_t)b0 * S * D, S, D);
+        const int rc = check_launch("weighted_sum_kernel");
+        if (rc != HIPGPT_OK) return rc;
+    }
+    return HIPGPT_OK;
 }
 
 }  // namespace hipgpt

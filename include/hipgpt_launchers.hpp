@@ -8,6 +8,8 @@
 // the call is asynchronous on the legacy default stream (the reference launches with stream
 // 0); nothing is returned; a head configuration with H <= 0 or E % H != 0 prints
 // "Bad MHA config: E=.. H=.." to stderr and aborts (src/hip_kernels.cpp:410-413).
+// Narrower than the reference: head_dim (E / H) up to 512 (the reference's fallback kernel takes any), and at most
+// 65535 (batch, head) rows per call of the decode and backward entry points.
 // Behaviour added: d_attn_probs may be nullptr on every path (the probabilities are then not
 // written); any other failure prints the library's error text to stderr and aborts, where the
 // reference would have continued silently.

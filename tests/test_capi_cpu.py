@@ -39,8 +39,11 @@ def test_reference_objects_would_resolve_against_the_library():
     declarations in include/hip_kernels.h:39-46; check with the compiler, not by hand."""
     import subprocess
     import tempfile
-    src = '#include "hipgpt_launchers.hpp"\nvoid f(const float* a, float* b){launch_multihead_attention(a,b,b,1,1,1,1);' \
-          'launch_scaled_dot_product(a,a,b,1,1,1);launch_softmax(a,b,1,1);launch_attention_weighted_sum(a,a,b,1,1,1);}\n'
+    src = '#include "hipgpt_launchers.hpp"\nvoid f(const float* a, float* b, const int* i){launch_multihead_attention(a,b,b,1,1,1,1);' \
+          'launch_scaled_dot_product(a,a,b,1,1,1);launch_softmax(a,b,1,1);launch_attention_weighted_sum(a,a,b,1,1,1);' \
+          'launch_multihead_attention_backward(a,a,a,b,1,1,1,1);launch_matmul(a,a,b,1,1,1);launch_matmul_add_bias(a,a,a,b,1,1,1);' \
+          'launch_layer_norm_forward(a,b,a,a,1,1);launch_dropout_forward(a,b,b,0.1f,1,1);launch_add_inplace(b,a,1);launch_relu(b,1);' \
+          'launch_embedding_lookup(i,a,a,b,1,1,1,1);}\n'
     with tempfile.TemporaryDirectory() as td:
         cpp = os.path.join(td, "t.cpp")
         open(cpp, "w").write(src)
@@ -102,36 +105,35 @@ def test_decode_scratch_size_query():
 
 REFERENCE = os.environ.get("HIPGPT_REFERENCE", "/root/reference")   # the HipGPT tree
 
+# launchers that HipGPT's layer and model sources name but only its training path calls: outside this library
+TRAINING_ONLY = {"launch_matmul_backward_bias", "launch_matmul_transpose_A", "launch_matmul_transpose_B", "launch_backprop_activation",
+                 "launch_embedding_backward", "launch_adam_update", "launch_layer_norm_backward", "launch_dropout_backward",
+                 "launch_l2_accumulate", "launch_scale_inplace"}
+
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE, "src", "transformer_layer.cpp")), reason="reference tree not mounted")
-def test_reference_transformer_layer_links_against_the_library():
-    """HipGPT's own src/transformer_layer.cpp, compiled where it lies (host stand-in for the HIP
-    runtime), refers to launch_multihead_attention by exactly the symbol this library exports, and
-    links with it when every other launcher it needs is stubbed (src/transformer_layer.cpp:218 is
-    the only call site)."""
+def test_reference_layer_and_model_resolve_their_forward_path_against_the_library():
+    """HipGPT's own src/transformer_layer.cpp and src/gpt_model.cpp, compiled where they lie: every launch_* symbol
+    they leave undefined is either exported by this library under exactly that mangled name, or belongs to the
+    training path (backward passes, Adam, clipping).  oracle/Makefile links the two objects with the library into
+    oracle/_ref/ref_model_run, the program the GPU tests run; nothing is stubbed with an empty function."""
     import subprocess
     import tempfile
-    shim = os.path.join(ROOT, "oracle", "ref_shim")
-    libdir = os.path.dirname(_capi.lib_path())
+    shim = os.path.join(ROOT, "oracle", "ref_shim_cuda")
+    exported = subprocess.run(["nm", "-D", "--defined-only", _capi.lib_path()], check=True, capture_output=True, text=True).stdout
     with tempfile.TemporaryDirectory() as td:
-        obj = os.path.join(td, "transformer_layer.o")
-        subprocess.run(["g++", "-std=c++17", "-O1", "-fPIC", "-I", shim, "-I", os.path.join(REFERENCE, "include"), "-c",
-                        os.path.join(REFERENCE, "src", "transformer_layer.cpp"), "-o", obj], check=True)
-        undefined = subprocess.run(["nm", "-u", obj], check=True, capture_output=True, text=True).stdout.split()
-        wanted = [u for u in undefined if "launch_" in u]
-        attention = _capi.CXX_LAUNCHERS["launch_multihead_attention"]
-        assert attention in wanted
-        exported = subprocess.run(["nm", "-D", "--defined-only", _capi.lib_path()], check=True, capture_output=True, text=True).stdout
-        assert attention in exported
-        # every other launcher (and the shim's thread-index globals) as an empty definition: the link must then close
-        others = [u for u in wanted if u != attention and u not in exported]
-        stub = os.path.join(td, "stubs.s")
-        with open(stub, "w") as f:
-            for name in others:
-                f.write(f".globl {name}\n.type {name}, @function\n{name}:\n ret\n")
-        out = os.path.join(td, "liblayer.so")
-        r = subprocess.run(["g++", "-shared", "-o", out, obj, stub, "-L", libdir, "-lhipgpt_attn", "-Wl,--no-undefined",
-                            "-Wl,-rpath," + libdir], capture_output=True, text=True)
-        assert r.returncode == 0, r.stderr
-        needed = subprocess.run(["readelf", "-d", out], check=True, capture_output=True, text=True).stdout
-        assert "libhipgpt_attn.so" in needed
+        for name in ("transformer_layer", "gpt_model"):
+            obj = os.path.join(td, name + ".o")
+            subprocess.run(["g++", "-std=c++17", "-O1", "-w", "-I", shim, "-I", os.path.join(REFERENCE, "include"), "-I", "/usr/local/cuda/include",
+                            "-c", os.path.join(REFERENCE, "src", name + ".cpp"), "-o", obj], check=True)
+            undefined = subprocess.run(["nm", "-u", obj], check=True, capture_output=True, text=True).stdout.split()
+            wanted = [u for u in undefined if "launch_" in u]
+            assert wanted
+            for sym in wanted:
+                plain = subprocess.run(["c++filt", sym], check=True, capture_output=True, text=True).stdout.split("(")[0].strip()
+                assert sym in exported or plain in TRAINING_ONLY, f"{name}.cpp needs {plain}, which the library does not export"
+            if name == "transformer_layer":
+                for must in ("launch_multihead_attention", "launch_matmul_add_bias", "launch_layer_norm_forward", "launch_dropout_forward",
+                             "launch_multihead_attention_backward"):
+                    assert _capi.CXX_LAUNCHERS[must] in wanted and _capi.CXX_LAUNCHERS[must] in exported
+    assert os.path.exists(os.path.join(ROOT, "oracle", "_ref", "ref_model_run")), "run `make -C oracle` (or __graft_entry__.build())"

@@ -7,7 +7,7 @@ from hipgpt_b200 import synth
 from oracle import bindings as ob
 
 
-def _numpy_generate(w, V, S, E, L, H, F, prompts, n_new):
+def _numpy_generate(w, V, S, E, L, H, F, prompts, n_new, margins=None):
     """Independent float64 restatement: full causal recompute per step, no cache."""
     D = E // H
     off = 0
@@ -50,6 +50,9 @@ def _numpy_generate(w, V, S, E, L, H, F, prompts, n_new):
             logits = x[-1] @ wout
             nxt = int(np.argmax(logits))
             out[bi, i] = nxt
+            if margins is not None:
+                top2 = np.partition(logits, -2)[-2:]
+                margins.append(float(top2[1] - top2[0]))
             seq.append(nxt)
     return out
 
@@ -63,6 +66,22 @@ def test_oracle_generation_matches_numpy_on_a_tiny_model():
         ids, logits = ob.gpt_generate(w, **cfg, prompts=prompts, n_new=12, fma=fma)
         assert np.array_equal(ids, _numpy_generate(w, **cfg, prompts=prompts, n_new=12))
         assert np.isfinite(logits).all()
+
+
+def test_oracle_generation_matches_numpy_on_the_default_model():
+    """The benchmark's whole generation case (E=256 L=8 H=8 F=1024 V=5000 S=256, weights N(0, 0.02) seed 3, 8 prompts
+    of 16 ids, 128 new tokens): all 1024 ids of the fp32 oracle against float64 arithmetic that shares nothing with it,
+    with the gap between the two largest logits of every step: the room an fp32 rounding difference (about 1e-6 here)
+    has before it changes an id.  Measured: smallest gap 2.9e-5, 4 steps below 1e-4, median 2.4e-2."""
+    cfg = dict(synth.GPT_DEFAULT)
+    w = synth.gpt_weights(3, **cfg)
+    prompts = synth.token_ids(3, (8, 16), cfg["V"])
+    n_new = 128
+    margins = []
+    want = _numpy_generate(w, **cfg, prompts=prompts, n_new=n_new, margins=margins)
+    ids, _ = ob.gpt_generate(w, **cfg, prompts=prompts, n_new=n_new, fma=True)
+    assert len(margins) == 1024 and min(margins) > 1e-5, f"a step of this seed is decided by {min(margins):.2e}: below fp32 noise"
+    assert np.array_equal(ids, want)
 
 
 def test_oracle_rejects_requests_past_the_position_table():

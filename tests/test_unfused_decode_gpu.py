@@ -37,6 +37,23 @@ def test_unfused_chain(shape):
     assert np.array_equal(d_scores.cpu().numpy(), sm)
 
 
+def test_unfused_chain_takes_more_batch_items_than_one_grid_holds():
+    """The reference's kernels index threads by B' * S and take any B'; here the batch index rides on grid.z
+    (65535 at most), so larger counts are split over several launches."""
+    Bp, S, D = 65535 + 70, 4, 8
+    Q, K, V = (synth.normal(80 + i, (Bp, S, D)) for i in range(3))
+    dQ, dK, dV = dev(Q), dev(K), dev(V)
+    d_scores = torch.full((Bp, S, S), float("nan"), device="cuda")
+    d_o = torch.full((Bp, S, D), float("nan"), device="cuda")
+    launchers.launch_scaled_dot_product(dQ, dK, d_scores, Bp, S, D)
+    launchers.launch_softmax(d_scores, d_scores, Bp, S)
+    launchers.launch_attention_weighted_sum(d_scores, dV, d_o, Bp, S, D)
+    sm = ob.softmax(ob.sdp(Q, K, Bp, S, D, fma=True), Bp, S)
+    got = d_o.cpu().numpy()
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got, ob.weighted_sum(sm, V, Bp, S, D, fma=True), atol=1e-6, rtol=0)
+
+
 def test_unfused_chain_matches_reference_golden():
     Bp, S, D = (int(x) for x in GOLDEN["trio.shape"])
     dQ, dK, dV = dev(GOLDEN["trio.Q"]), dev(GOLDEN["trio.K"]), dev(GOLDEN["trio.V"])
