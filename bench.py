@@ -3,6 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload c2|c3|c5] [--causal 0|1] [--probs 0|1] [--gather 0|1]
+                    [--kernel auto|whole_head|tiled|split_tf32|rows|generic] [--dtype f32|bf16]
 
 One JSON line on stdout (rank 0).  A *step* is one pass of the attention forward over SETS
 different input batches of the workload's shape, one kernel launch per batch; the SETS batches
@@ -13,7 +14,12 @@ Default workload: B=32 H=8 S=256 head_dim=32, fp32, causal, probabilities not st
             CUDA events around the K timed steps, max over ranks
   e2e       the same metric through the host-buffer C-ABI call (pinned host memory in, host
             memory out), copies inside the timed region
-  roofline  the attention kernel against the fp32 FMA-pipe ceiling measured in the same run
+  roofline  the attention kernel against the roofline that binds it: the measured HBM copy rate when
+            moving the algorithmic bytes takes longer than the tensor pipe needs for the products
+            (workload c2), else the measured tensor rate; the fp32 FFMA ceiling timed in the same
+            run is reported beside it
+  scaling_c5  (default run) the largest workload through the sharded C-ABI driver: compute alone,
+            compute in chunks, and with the overlapped all-gather of the outputs when N > 1
   cpu_baseline  the CPU oracle (a port of the reference arithmetic) on this box's host cores
 
 With N > 1 (torchrun, one rank per GPU) every rank runs the same step on its own batches
@@ -40,10 +46,13 @@ from hipgpt_b200 import synth  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture that the named summary under
 # profiles/ records: (workload, kernel) -> (bytes, summary).  A kernel without a capture of its own reports null.
-TRAFFIC = {("c2", "mha_head_kernel"): (25.32e6, "profiles/mha_head_kernel_c2_causal.md"),
+TRAFFIC = {("c2", "mha_head_kernel"): (25.25e6, "profiles/mha_head_kernel_c2_causal.md"),
            ("c2", "mha_tc16_kernel"): (25.23e6, "profiles/mha_tc16_kernel_c2_causal.md"),
-           ("c3", "mha_tc16_kernel"): (129.9e6, "profiles/mha_tc16_kernel_c3_causal.md")}
+           ("c3", "mha_tc16_kernel"): (130.6e6, "profiles/mha_tc16_kernel_c3_causal.md")}
 FALLBACK_HBM_GBS = 6650.0
+# --kernel: name -> (algo, tensor-kernel selector) of hipgpt_mha_forward_ex, and the kernel's name in a launch list
+KERNELS = {"auto": None, "whole_head": (3, 6, "mha_head_kernel"), "tiled": (3, 5, "mha_tc16_kernel"),
+           "split_tf32": (3, 1, "mha_tc_kernel"), "rows": (2, 0, "mha_rows_kernel"), "generic": (1, 0, "mha_generic_kernel")}
 
 
 def flops_of(B, H, S, D, causal):
@@ -72,6 +81,8 @@ def parse():
     ap.add_argument("--decode-only", action="store_true", help="run only the greedy-generation leg and print its JSON")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-scaling", action="store_true", help="skip the C5 sharded leg (key scaling_c5)")
+    ap.add_argument("--kernel", default="auto", choices=sorted(KERNELS),
+                    help="fp32 attention kernel: auto is what hipgpt_mha_forward picks; the others go through hipgpt_mha_forward_ex")
     ap.add_argument("--bf16-variant", type=int, default=0, help="--dtype bf16: 0 default, 1 one worker per query row, 2 two workers, 3 two workers and 128-key tiles")
     return ap.parse_args()
 
@@ -374,8 +385,13 @@ def run_ours(args):
     if bf16:
         def fwd(q, k, v, out, probs, B_, S_, E_, H_, causal, st_):
             return lib.hipgpt_mha_forward_bf16_ex(q, k, v, out, B_, S_, E_, H_, causal, args.bf16_variant, st_)
-    else:
+    elif KERNELS[args.kernel] is None:
         fwd = lib.hipgpt_mha_forward
+    else:
+        algo, which = KERNELS[args.kernel][:2]
+
+        def fwd(q, k, v, out, probs, B_, S_, E_, H_, causal, st_):
+            return lib.hipgpt_mha_forward_ex(q, k, v, out, probs, B_, S_, E_, H_, causal, algo, which, st_)
 
     def step():
         handles = []
@@ -452,7 +468,7 @@ def run_ours(args):
     # split-TF32 (three TF32 products per fp32 product); TF32 runs at half the measured dense bf16
     # rate.  With the probabilities stored the kernel forms Q K^T twice (1.5 times the tensor work)
     # and writes B H S S floats more.  Other head dims run the FFMA kernel, measured against the FFMA ceiling.
-    tensor_kernel = D in (32, 64)
+    tensor_kernel = D in (32, 64) and (KERNELS[args.kernel] is None or KERNELS[args.kernel][0] == 3)
     flops_launch = flops_of(B, H, S, D, args.causal)
     # a kernel timed back to back for seconds is compared with the sustained figure
     bf16_peak = float(peaks.get("bf16_tflops_sustained" if bf16 else "bf16_tflops", 1400.0 if bf16 else 1590.0))
@@ -461,7 +477,7 @@ def run_ours(args):
     # tensor work per fp32 product, in TF32 products: the default kernel runs one TF32 product and two FP16
     # products (twice the TF32 rate); 3 would be the figure of the split-TF32 variant
     tc16 = tensor_kernel and not bf16
-    tf32_products = (2.0 if tc16 else 3.0) * (1.5 if args.probs else 1.0)
+    tf32_products = (2.0 if (tc16 and args.kernel != "split_tf32") else 3.0) * (1.5 if args.probs else 1.0)
     t_pipe = (flops_launch / (bf16_peak * 1e12)) if bf16 else (tf32_products * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
     src = "measured" if peaks else "fallback"
     if bf16 and t_hbm < t_pipe:
@@ -478,7 +494,8 @@ def run_ours(args):
         roofline = {"bound": "fma", "achieved": achieved, "peak": fma_peak, "unit": "TFLOP/s", "frac": achieved / fma_peak,
                     "peak_source": "fp32 FFMA loop timed in this run"}
     kernel = ("mha_bf16_kernel" if bf16 else
-              "mha_head_kernel" if (D == 32 and S <= 256 and not args.probs) else
+              KERNELS[args.kernel][2] if KERNELS[args.kernel] else
+              "mha_head_kernel" if (D == 32 and S <= 256) else
               "mha_tc16_kernel" if tensor_kernel else "mha_rows_kernel" if D == 128 else "mha_generic_kernel")
     traffic = TRAFFIC.get((args.workload, kernel)) if (args.causal and not args.probs and not bf16) else None
     roofline.update({"kernel": kernel, "traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None,
