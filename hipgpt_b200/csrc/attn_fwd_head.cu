@@ -25,12 +25,12 @@
 // place as packed fp16), two output accumulators of 64 columns (one per query tile).
 // Tiles of a head: causal (q0,k0) (q1,k0) (q1,k1); unmasked (q0,k0) (q0,k1) (q1,k0) (q1,k1), the fourth
 // reusing the first buffer once its P V product has been issued.
-// Threads: three groups of 128 workers (thread = query row = TMEM lane) and one control warp.  A group
+// Threads: three groups of 128 workers (thread = query row = TMEM lane) and three issuing warps.  A group
 // first converts one operand (K, Q or V) for the whole head, then owns one score tile (two for group 0
 // of an unmasked head): row maximum, exchange of the maximum with the group that holds the other key
 // tile of the same rows (shared memory + mbarrier), exponentials, P to TMEM; at the end the groups of a
-// query tile share its output columns.  The control lane issues the copies and every product in a fixed
-// order, so results do not depend on timing.
+// query tile share its output columns.  One issuing warp issues the copies and every Q K^T, the other two the
+// P V products of one query tile each, in a fixed order, so results do not depend on timing.
 // Probabilities (when asked for): a row's sum is known once all its tiles have been through the exponentials;
 // the workers then read P_hi + P_lo back from TMEM, divide by the sum and store [B][H][S][S]: no second Q K^T.
 // Every wait is bounded: on expiry the block raises a flag that cuts all later waits short, records a
@@ -48,7 +48,8 @@ namespace {
 
 constexpr int kTile = 128;                       // rows of a query tile = keys of a key tile
 constexpr int kHeadWorkers = 3 * kTile;
-constexpr int kHeadThreads = kHeadWorkers + 32;
+constexpr int kHeadIssuers = 3;                  // warps that issue copies and tensor-core instructions
+constexpr int kHeadThreads = kHeadWorkers + 32 * kHeadIssuers;
 constexpr uint32_t kTileBytes = kTile * 128;     // one [128][128 byte] operand block
 constexpr uint32_t kOffQraw = 0, kOffKraw = 2 * kTileBytes, kOffVraw = 4 * kTileBytes;
 constexpr uint32_t kOffQ16 = 6 * kTileBytes, kOffK16 = 8 * kTileBytes, kOffV16 = 10 * kTileBytes;
@@ -60,6 +61,15 @@ constexpr long long kHeadPollLimit = 1LL << 22;
 
 __device__ int g_head_status = 0;                // first wait site that ran out (0 = none)
 __device__ int g_head_notice = 0;                // bit 0: Q or K left the range in which the fp16 correction terms are exact
+
+// The polling part of a bounded wait; on expiry the block's abort flag is raised and the site recorded.
+__device__ __noinline__ void head_wait_slow(uint64_t *bar, uint32_t parity, int site, volatile int *abort_flag)
+{
+    if (!mbar_wait_for(bar, parity, kHeadCycleLimit, kHeadPollLimit)) {
+        *abort_flag = 1;
+        atomicCAS(&g_head_status, 0, site);
+    }
+}
 
 // Largest score of one 32-column chunk; columns from `nvalid` on (counted from the tile's first column) are hidden.
 __device__ __forceinline__ float chunk_max(float (&v)[32], int col0, int nvalid, bool need_mask)
@@ -131,7 +141,7 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
     uint8_t *v_16 = base + kOffV16;              // [V_hi | V_lo] (64 columns) fp16, N-major without swizzle: 8 keys x 8 columns
                                                  // form one 128-byte core matrix, column blocks 128 bytes apart, key groups 1024
     __shared__ uint64_t ld_q[2], ld_k[2], ld_v[2], cv_q[2], cv_k[2], cv_v[2];
-    __shared__ uint64_t s_full[3], p_full[4], o_done[2], xm[2], xs[2], epi_done, vx, pr_done;
+    __shared__ uint64_t s_full[3], p_full[4], o_done[2], xm[2], xs[2], epi_done, vx, pr_done, b0_free;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ float xmax[2][2][2][kTile];       // [head parity][query tile][slot][row]
@@ -140,67 +150,87 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
     __shared__ float s_vinv[2];                  // 1 / (V's power-of-two scale), by head parity
     __shared__ unsigned s_amax[2];               // bit patterns of max |Q| and max |K| of the current head
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // the warp's number, read from one lane so that the compiler knows it (and the role, tile and buffer numbers
+    // that follow from it) to be the same for the whole warp: descriptors then live in uniform registers
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int nq = S > kTile ? 2 : 1;            // query tiles = key tiles of a head
 
     // site codes: 1 Q/K/V landed, 2 operand converted, 3 S ready, 4 P written, 5 output complete,
     // 6 row maxima exchanged, 7 row sums exchanged, 8 previous head's output read, 9 V maximum exchanged,
-    // 10 probabilities of the first tile read back
+    // 10 probabilities of the first tile read back, 11 first product of an unmasked head complete
+    // (the kernel's instructions are fetched cold by every SM, so the code is kept small: the polling loop of a
+    // wait exists once, out of line, behind a one-instruction test that is all an already completed phase costs)
     auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
-        if (abort_flag) return;
-        if (!mbar_wait_for(bar, parity, kHeadCycleLimit, kHeadPollLimit)) { abort_flag = 1; atomicCAS(&g_head_status, 0, site); }
+        if (abort_flag || mbar_test(bar, parity)) return;
+        head_wait_slow(bar, parity, site, &abort_flag);
     };
     auto arrive = [&](uint64_t *bar) {           // one arrival per warp, after every lane's writes
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
     };
 
-    if (warp == kHeadWorkers / 32) {
-        // ================= the control warp ==========================================================
+    if (warp >= kHeadWorkers / 32) {
+        // ================= the three issuing warps =====================================================
+        // role 0: the copies and every Q K^T; role 1: the P V products of query tile 0; role 2: those of query
+        // tile 1.  A tcgen05.mma costs the thread that issues it far more than it costs the tensor pipe (measured:
+        // about 100 cycles per instruction from one lane of a diverged warp, 55 - 85 from a converged warp that
+        // elects the lane per instruction, and two warps issue side by side at that rate each), so the warps stay
+        // converged, compute the descriptors warp-uniformly and share the head's 72 - 96 instructions between them.
+        // Instructions of one thread run in order; between the warps the order is made by mbarriers, and each
+        // accumulator is written by one warp only, in a fixed order: results do not depend on timing.
+        const int role = warp - kHeadWorkers / 32;
         auto load_qk = [&](int hd) {
-            const int b = hd / H, c0 = (hd % H) * 32;
-            for (int t = 0; t < nq; ++t) {
-                mbar_arrive_expect_tx(&ld_k[t], kTileBytes);
-                tma_load_3d(k_raw + t * kTileBytes, &maps.k, c0, t * kTile, b, &ld_k[t]);
-                mbar_arrive_expect_tx(&ld_q[t], kTileBytes);
-                tma_load_3d(q_raw + t * kTileBytes, &maps.q, c0, t * kTile, b, &ld_q[t]);
+            if (lane == 0) {
+                const int b = hd / H, c0 = (hd % H) * 32;
+                for (int t = 0; t < nq; ++t) {
+                    mbar_arrive_expect_tx(&ld_k[t], kTileBytes);
+                    tma_load_3d(k_raw + t * kTileBytes, &maps.k, c0, t * kTile, b, &ld_k[t]);
+                    mbar_arrive_expect_tx(&ld_q[t], kTileBytes);
+                    tma_load_3d(q_raw + t * kTileBytes, &maps.q, c0, t * kTile, b, &ld_q[t]);
+                }
             }
+            __syncwarp();
         };
         auto load_v = [&](int hd) {
-            const int b = hd / H, c0 = (hd % H) * 32;
-            for (int t = 0; t < nq; ++t) {
-                mbar_arrive_expect_tx(&ld_v[t], kTileBytes);
-                tma_load_3d(v_raw + t * kTileBytes, &maps.v, c0, t * kTile, b, &ld_v[t]);
+            if (lane == 0) {
+                const int b = hd / H, c0 = (hd % H) * 32;
+                for (int t = 0; t < nq; ++t) {
+                    mbar_arrive_expect_tx(&ld_v[t], kTileBytes);
+                    tma_load_3d(v_raw + t * kTileBytes, &maps.v, c0, t * kTile, b, &ld_v[t]);
+                }
             }
+            __syncwarp();
         };
-        if (lane == 0) {
-            abort_flag = 0;
-            s_amax[0] = s_amax[1] = 0u;
-            for (int i = 0; i < 2; ++i) {
-                mbar_init(&ld_q[i], 1); mbar_init(&ld_k[i], 1); mbar_init(&ld_v[i], 1);
-                mbar_init(&cv_q[i], 4); mbar_init(&cv_k[i], 4); mbar_init(&cv_v[i], 4);
-                mbar_init(&o_done[i], 1);
-                mbar_init(&xm[i], 8); mbar_init(&xs[i], 8);
+        if (role == 0) {
+            if (lane == 0) {
+                abort_flag = 0;
+                s_amax[0] = s_amax[1] = 0u;
+                for (int i = 0; i < 2; ++i) {
+                    mbar_init(&ld_q[i], 1); mbar_init(&ld_k[i], 1); mbar_init(&ld_v[i], 1);
+                    mbar_init(&cv_q[i], 4); mbar_init(&cv_k[i], 4); mbar_init(&cv_v[i], 4);
+                    mbar_init(&o_done[i], 1);
+                    mbar_init(&xm[i], 8); mbar_init(&xs[i], 8);
+                }
+                for (int i = 0; i < 3; ++i) mbar_init(&s_full[i], 1);
+                for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 4);
+                mbar_init(&epi_done, kHeadWorkers / 32);
+                mbar_init(&vx, 4);
+                mbar_init(&pr_done, 4);
+                mbar_init(&b0_free, 1);
             }
-            for (int i = 0; i < 3; ++i) mbar_init(&s_full[i], 1);
-            for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 4);
-            mbar_init(&epi_done, kHeadWorkers / 32);
-            mbar_init(&vx, 4);
-            mbar_init(&pr_done, 4);
+            __syncwarp();
             if ((int)blockIdx.x < BH) { load_qk(blockIdx.x); load_v(blockIdx.x); }
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
-        __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncthreads();                             // barriers initialised, TMEM allocated
         tc_fence_after();
         const uint32_t tmem = tmem_base_slot;
-        if (lane == 0) {
+        if (role == 0) {
             constexpr uint32_t id_qk_h = idesc_f16(kTile, kTile);             // [Q_lo | Q] x [K_hi | K_lo], fp16
             constexpr uint32_t id_qk_t = make_idesc(kTile, kTile, 0);         // Q x K, tf32
-            constexpr uint32_t id_pv_a = idesc_f16(kTile, 64) | (1u << 16);   // P_hi x [V_hi | V_lo], B N-major
-            constexpr uint32_t id_pv_b = idesc_f16(kTile, 32) | (1u << 16);   // P_lo x V_hi
             auto issue_qk = [&](int q, int k, int buf) {
                 const uint32_t d = tmem + (uint32_t)(buf * kTile);
                 const uint64_t dq16 = make_desc(smem_u32(q_16 + q * kTileBytes), 16, 1024, 2);
@@ -208,52 +238,45 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
                 // the correction terms first: the accumulator is still tiny while they are added
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)       // 16 fp16 = 32 bytes per instruction
-                    mma_h_ss(d, dq16 + (uint64_t)(ks * 2), dk16 + (uint64_t)(ks * 2), id_qk_h, ks ? 1u : 0u);
+                    if (elect_one()) mma_h_ss(d, dq16 + (uint64_t)(ks * 2), dk16 + (uint64_t)(ks * 2), id_qk_h, ks ? 1u : 0u);
                 const uint64_t dq = make_desc(smem_u32(q_raw + q * kTileBytes), 16, 1024, 2);
                 const uint64_t dk = make_desc(smem_u32(k_raw + k * kTileBytes), 16, 1024, 2);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)       // 8 floats = 32 bytes per instruction
-                    mma_ss(d, dq + (uint64_t)(ks * 2), dk + (uint64_t)(ks * 2), id_qk_t, 1u);
-                tc_commit(&s_full[buf]);
+                    if (elect_one()) mma_ss(d, dq + (uint64_t)(ks * 2), dk + (uint64_t)(ks * 2), id_qk_t, 1u);
+                if (elect_one()) tc_commit(&s_full[buf]);
             };
-            auto issue_pv = [&](int q, int k, int buf, bool first) {
-                const uint32_t d = tmem + kColO + (uint32_t)(q * 64);
-                // keys 32c .. 32c+31 of the tile: P_hi in columns [32c, 32c+16) of the buffer, P_lo in [32c+16, 32c+32)
-                const uint32_t a0 = tmem + (uint32_t)(buf * kTile);
-                const uint64_t dv = make_desc(smem_u32(v_16 + k * kTileBytes), 1024, 128, 0);
-                const int nks = (min(kTile, S - k * kTile) + 15) >> 4;        // 16 keys per instruction; keys past S hold zeros
-                for (int ks = 0; ks < nks; ++ks)     // 16 keys = 8 TMEM columns of packed fp16 = two key groups of V
-                    mma_h_ts(d, a0 + (uint32_t)(32 * (ks >> 1) + 8 * (ks & 1)), dv + (uint64_t)(ks * 128), id_pv_a, (first && ks == 0) ? 0u : 1u);
-                for (int ks = 0; ks < nks; ++ks)
-                    mma_h_ts(d + 32, a0 + (uint32_t)(32 * (ks >> 1) + 8 * (ks & 1) + 16), dv + (uint64_t)(ks * 128), id_pv_b, 1u);
-            };
+            const int nfirst = nq == 1 ? 1 : 3;      // tiles whose buffers are free at the start of a head
             int it = 0;
+#pragma unroll 1
             for (int hd = blockIdx.x; hd < BH; hd += gridDim.x, ++it) {
-                const uint32_t par = (uint32_t)(it & 1);
+                const uint32_t par = (uint32_t)(it & 1), ppar = (uint32_t)((it - 1) & 1);
                 const int next = hd + (int)gridDim.x;
                 const bool has_next = next < BH;
                 // ---- Q K^T of every tile whose buffer is free ---------------------------------------
                 // (with the probabilities stored, the workers read P back from these buffers until their output is out,
                 // and stage them in the Q and K areas of shared memory, so this head's Q and K are fetched only now)
                 if (PROBS && it > 0) {
-                    wait(&epi_done, (uint32_t)((it - 1) & 1), 8);
+                    wait(&epi_done, ppar, 8);
                     load_qk(hd);
                 }
-                wait(&cv_k[0], par, 2);
-                wait(&cv_q[0], par, 2);
-                tc_fence_after();
-                issue_qk(0, 0, 0);
-                if (nq == 2) {
-                    if (CAUSAL) {
-                        wait(&cv_q[1], par, 2); tc_fence_after(); issue_qk(1, 0, 1);
-                        wait(&cv_k[1], par, 2); tc_fence_after(); issue_qk(1, 1, 2);
-                    } else {
-                        wait(&cv_k[1], par, 2); tc_fence_after(); issue_qk(0, 1, 1);
-                        wait(&cv_q[1], par, 2); tc_fence_after(); issue_qk(1, 0, 2);
+                // tile t: causal (q0,k0) (q1,k0) (q1,k1), unmasked (q0,k0) (q0,k1) (q1,k0), into buffer t.  A buffer still
+                // holds the previous head's P until the P V products that read it have completed: the first buffer is
+                // read by query tile 0 only in a causal head, every other case waits for both accumulators.
+#pragma unroll 1
+                for (int t = 0; t < nfirst; ++t) {
+                    const int q = CAUSAL ? (t > 0) : (t >> 1), k = CAUSAL ? (t > 1) : (t & 1);
+                    if (it > 0) {
+                        if (t == 0) wait(&o_done[0], ppar, 5);
+                        if (nq == 2 && t == (CAUSAL ? 1 : 0)) wait(&o_done[1], ppar, 5);
                     }
+                    wait(&cv_k[k], par, 2);
+                    wait(&cv_q[q], par, 2);
+                    tc_fence_after();
+                    issue_qk(q, k, t);
                 }
                 // ---- the operands' range (see g_head_notice) ------------------------------------------
-                {
+                if (lane == 0) {
                     const float aq = __uint_as_float(s_amax[0]), ak = __uint_as_float(s_amax[1]);
                     s_amax[0] = 0u;
                     s_amax[1] = 0u;
@@ -264,7 +287,8 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
                     const float flush = 32.0f * cscale * 2.98e-8f * (aq + ak);
                     if (over || (flush > 3.8e-6f && (aq + ak) > 8.0f * aq * ak)) atomicOr(&g_head_notice, 1);
                 }
-                const bool tail_qk = !CAUSAL && nq == 2;    // the fourth tile's Q K^T comes after the first two P V products
+                __syncwarp();
+                const bool tail_qk = !CAUSAL && nq == 2;    // the fourth tile's Q K^T comes after the first P V product
                 if (has_next && !tail_qk && !PROBS) {
                     // the raw Q and K tiles and their fp16 copies are free once every Q K^T has completed
                     wait(&s_full[0], par, 3);
@@ -274,42 +298,65 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
                 wait(&cv_v[0], par, 2);
                 if (nq == 2) wait(&cv_v[1], par, 2);
                 if (has_next) load_v(next);              // the raw V tiles have been read
-                if (!PROBS && it > 0) wait(&epi_done, (uint32_t)((it - 1) & 1), 8);     // the previous head's output has left TMEM
-                // ---- P V, in a fixed order ------------------------------------------------------------
-                wait(&p_full[0], par, 4);
-                tc_fence_after();
-                issue_pv(0, 0, 0, true);
-                if (nq == 1 || CAUSAL) tc_commit(&o_done[0]);
-                if (nq == 2) {
-                    if (CAUSAL) {
-                        wait(&p_full[2], par, 4); tc_fence_after(); issue_pv(1, 1, 2, true);
-                        wait(&p_full[1], par, 4); tc_fence_after(); issue_pv(1, 0, 1, false);
-                        tc_commit(&o_done[1]);
-                    } else {
-                        wait(&p_full[1], par, 4); tc_fence_after(); issue_pv(0, 1, 1, false);
-                        tc_commit(&o_done[0]);
-                        // (q1, k1) into the first buffer: its P has been consumed by the product issued above
-                        // (instructions run in order) and its workers have arrived at p_full[0]; with the probabilities
-                        // stored they have also read that P back
-                        if (PROBS) wait(&pr_done, par, 10);
-                        issue_qk(1, 1, 0);
-                        if (has_next && !PROBS) {
-                            wait(&s_full[0], 1u, 3);     // second completion of this barrier in this head
-                            wait(&s_full[1], par, 3);
-                            wait(&s_full[2], par, 3);
-                            load_qk(next);
-                        }
-                        wait(&p_full[2], par, 4); tc_fence_after(); issue_pv(1, 0, 2, true);
-                        wait(&p_full[3], par, 4); tc_fence_after(); issue_pv(1, 1, 0, false);
-                        tc_commit(&o_done[1]);
+                if (tail_qk) {
+                    // (q1, k1) into the first buffer, once the product that reads (q0, k0)'s P from it has completed;
+                    // with the probabilities stored its workers must also have read that P back
+                    wait(&b0_free, par, 11);
+                    if (PROBS) wait(&pr_done, par, 10);
+                    tc_fence_after();
+                    issue_qk(1, 1, 0);
+                    if (has_next && !PROBS) {
+                        wait(&s_full[0], 1u, 3);         // second completion of this barrier in this head
+                        wait(&s_full[1], par, 3);
+                        wait(&s_full[2], par, 3);
+                        load_qk(next);
                     }
                 }
+            }
+        } else if (role - 1 < nq) {
+            // ---- P V of one query tile, in a fixed order ----------------------------------------------
+            const int q = role - 1;
+            constexpr uint32_t id_pv_a = idesc_f16(kTile, 64) | (1u << 16);   // P_hi x [V_hi | V_lo], B N-major
+            constexpr uint32_t id_pv_b = idesc_f16(kTile, 32) | (1u << 16);   // P_lo x V_hi
+            // the tiles of this query tile in the order of their products, packed: bit 0 key tile, 1-2 buffer, 3-4 p_full barrier
+            auto pk = [](int k, int buf, int ptile) { return (uint32_t)(k | (buf << 1) | (ptile << 3)); };
+            const uint32_t pj0 = (nq == 1 || q == 0) ? pk(0, 0, 0) : CAUSAL ? pk(1, 2, 2) : pk(0, 2, 2);
+            const uint32_t pj1 = q == 0 ? pk(1, 1, 1) : CAUSAL ? pk(0, 1, 1) : pk(1, 0, 3);
+            const int npv = (nq == 1 || (CAUSAL && q == 0)) ? 1 : 2;
+            const uint32_t d = tmem + kColO + (uint32_t)(q * 64);
+            int it = 0;
+#pragma unroll 1
+            for (int hd = blockIdx.x; hd < BH; hd += gridDim.x, ++it) {
+                const uint32_t par = (uint32_t)(it & 1);
+                if (it > 0) wait(&epi_done, (uint32_t)((it - 1) & 1), 8);     // the previous head's output has left TMEM
+#pragma unroll 1
+                for (int j = 0; j < npv; ++j) {
+                    const uint32_t pj = j ? pj1 : pj0;
+                    const int k = pj & 1, buf = (pj >> 1) & 3, ptile = (pj >> 3) & 3;
+                    wait(&cv_v[k], par, 2);
+                    wait(&p_full[ptile], par, 4);
+                    tc_fence_after();
+                    // keys 32c .. 32c+31 of the tile: P_hi in columns [32c, 32c+16) of the buffer, P_lo in [32c+16, 32c+32)
+                    const uint32_t a0 = tmem + (uint32_t)(buf * kTile);
+                    const uint64_t dv = make_desc(smem_u32(v_16 + k * kTileBytes), 1024, 128, 0);
+                    const int nks = (min(kTile, S - k * kTile) + 15) >> 4;        // 16 keys per instruction; keys past S hold zeros
+                    // (unrolled: a rolled loop's address arithmetic between the instructions was measured to double their cost)
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)       // 16 keys = 8 TMEM columns of packed fp16 = two key groups of V
+                        if (ks < nks && elect_one()) mma_h_ts(d, a0 + (uint32_t)(32 * (ks >> 1) + 8 * (ks & 1)), dv + (uint64_t)(ks * 128), id_pv_a, (j == 0 && ks == 0) ? 0u : 1u);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        if (ks < nks && elect_one()) mma_h_ts(d + 32, a0 + (uint32_t)(32 * (ks >> 1) + 8 * (ks & 1) + 16), dv + (uint64_t)(ks * 128), id_pv_b, 1u);
+                    // an unmasked head's fourth score tile goes into the first buffer once this product has read it
+                    if (!CAUSAL && nq == 2 && q == 0 && j == 0 && elect_one()) tc_commit(&b0_free);
+                }
+                if (elect_one()) tc_commit(&o_done[q]);
             }
         }
         __syncwarp();
         tc_fence_before();
         __syncthreads();                             // the workers have read their last output
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+        if (role == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
         return;
     }
 
@@ -540,23 +587,16 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
             const int nch = (nwarp + 31) >> 5;                                // 32-column chunks with any visible key
             wait(&s_full[buf], spar, 3);
             tc_fence_after();
-            // Both sweeps keep one TMEM load in flight while the chunk before it is worked on: the load of
-            // chunk c+1 is issued as soon as chunk c has arrived (tcgen05.wait::ld waits for every earlier load).
+            // One chunk of 32 columns at a time, one copy of the code per sweep: the loads' latency is covered by
+            // the SM's other warps, and the instruction footprint matters more than the overlap inside a warp.
             float mx = -INFINITY;
-            float va[32], vb[32];
-            tmem_ld32(s_addr, va);                                            // nch >= 1: a tile has at least one key
+            float v[32];
 #pragma unroll 1
-            for (int c0 = 0; c0 < nch; c0 += 2) {
+            for (int c = 0; c < nch; ++c) {
+                tmem_ld32(s_addr + c * 32, v);
                 tmem_wait_ld();
-                if (c0 + 1 < nch) tmem_ld32(s_addr + c0 * 32 + 32, vb);
-                mx = fmaxf(mx, chunk_max(va, c0 * 32, nvalid, c0 * 32 + 32 > nmin));
-                if (c0 + 1 < nch) {
-                    tmem_wait_ld();
-                    if (c0 + 2 < nch) tmem_ld32(s_addr + c0 * 32 + 64, va);
-                    mx = fmaxf(mx, chunk_max(vb, c0 * 32 + 32, nvalid, c0 * 32 + 64 > nmin));
-                }
+                mx = fmaxf(mx, chunk_max(v, c * 32, nvalid, c * 32 + 32 > nmin));
             }
-            tmem_ld32(s_addr, va);                                            // the second sweep's first chunk: on its way during the exchange below
             if (paired) {
                 xmax[par][q][slot][rloc] = mx;
                 arrive(&xm[q]);
@@ -567,16 +607,12 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
             const float nmc = kPShift - mx * cscale;     // p = 2^(s c - m c + 8)
             float ps = 0.0f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < nch; c0 += 2) {
+            for (int c = 0; c < nch; ++c) {
+                tmem_ld32(s_addr + c * 32, v);
                 tmem_wait_ld();
-                if (c0 + 1 < nch) tmem_ld32(s_addr + c0 * 32 + 32, vb);
-                ps += chunk_exp(va, s_addr + c0 * 32, c0 * 32, nvalid, c0 * 32 + 32 > nmin, cscale, nmc);
-                if (c0 + 1 < nch) {
-                    tmem_wait_ld();
-                    if (c0 + 2 < nch) tmem_ld32(s_addr + c0 * 32 + 64, va);
-                    ps += chunk_exp(vb, s_addr + c0 * 32 + 32, c0 * 32 + 32, nvalid, c0 * 32 + 64 > nmin, cscale, nmc);
-                }
+                ps += chunk_exp(v, s_addr + c * 32, c * 32, nvalid, c * 32 + 32 > nmin, cscale, nmc);
             }
+#pragma unroll 1
             for (int c = nch; c < 4; ++c) chunk_zero(s_addr + c * 32);       // chunks that no row of this warp sees
             tmem_wait_st();
             tc_fence_before();
