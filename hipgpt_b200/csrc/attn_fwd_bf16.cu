@@ -115,7 +115,9 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
     __shared__ float xch[2][2][kRows];               // WPR == 2: row maxima of the two halves, by tile parity
     __shared__ float lx[2][kRows];                   // WPR == 2: row sums of the two halves
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // read from one lane, so that the compiler knows the warp's number (and every role that follows from it) to be warp-uniform
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);     // heaviest first
     const int b = bh / H, h = bh % H;

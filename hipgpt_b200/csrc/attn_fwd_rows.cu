@@ -135,7 +135,9 @@ mha_rows_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
     float *ks = smem;                  // [2][KT][D]
     float *vs = smem + 2 * KT * D;     // [2][KT][D]
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // read from one lane, so that the compiler knows the warp's number (and every role that follows from it) to be warp-uniform
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int grp = lane / NT, part = lane % NT;
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);   // heaviest first

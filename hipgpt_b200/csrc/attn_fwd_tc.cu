@@ -94,7 +94,9 @@ mha_tc_kernel(const float *__restrict__ Q, const float *__restrict__ K, const fl
     __shared__ volatile int abort_flag;
     __shared__ float xchg[2][2][kM];             // [tile parity][half][row]: row maxima, at the end row sums
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // read from one lane, so that the compiler knows the warp's number (and every role that follows from it) to be warp-uniform
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int bh = blockIdx.x % BH;
     const int qblk = CAUSAL ? (nqblk - 1 - blockIdx.x / BH) : (blockIdx.x / BH);   // heaviest first
     const int b = bh / H, h = bh % H;
