@@ -163,7 +163,9 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
         __syncthreads();                             // Q staged; TMEM allocated
         tc_fence_after();
         const uint32_t tmem = tmem_base_slot;
-        if (lane == 0) {
+        // The warp stays converged and elects the issuing lane per instruction: descriptors are then computed
+        // warp-uniformly (uniform registers), which roughly halves what an instruction costs its issuer.
+        {
             constexpr uint32_t idesc_qk = idesc_bf16(kRows, kKeys, 0);
             constexpr uint32_t idesc_pv = idesc_bf16(kRows, D, 1);
             const uint64_t dq = make_desc(smem_u32(q_s), 16, 1024, 2);
@@ -171,17 +173,17 @@ mha_bf16_kernel(const __nv_bfloat16 *__restrict__ Q, const __nv_bfloat16 *__rest
                 const uint64_t dk = make_desc(smem_u32(k_s + stage * TILE), 16, 1024, 2);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k)         // 16 bf16 = 32 bytes per instruction
-                    mma_f16_ss(tmem + kColX + (XB == 2 ? buf * kKeys : 0), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
-                tc_commit(&s_full[buf]);             // S is ready; it also tells the K warp that this product no longer reads its stage
+                    if (elect_one()) mma_f16_ss(tmem + kColX + (XB == 2 ? buf * kKeys : 0), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
+                if (elect_one()) tc_commit(&s_full[buf]);             // S is ready; it also tells the K warp that this product no longer reads its stage
             };
             auto issue_pv = [&](int buf, int stage, bool first) {
                 // N-major B: 16 keys (two groups of 8 rows of 128 bytes) per instruction = 2048 bytes
                 const uint64_t dv = make_desc(smem_u32(v_s + stage * TILE), 1024, 1024, 2);
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)
-                    mma_f16_ts(tmem + kColO, tmem + kColX + (XB == 2 ? buf * kKeys : 0) + (uint32_t)(k * 8), dv + (uint64_t)(k * 128), idesc_pv,
+                    if (elect_one()) mma_f16_ts(tmem + kColO, tmem + kColX + (XB == 2 ? buf * kKeys : 0) + (uint32_t)(k * 8), dv + (uint64_t)(k * 128), idesc_pv,
                                (first && k == 0) ? 0u : 1u);
-                tc_commit(&o_done[buf]);             // O is up to date; it also tells the V warp that this product no longer reads its stage
+                if (elect_one()) tc_commit(&o_done[buf]);             // O is up to date; it also tells the V warp that this product no longer reads its stage
             };
             wait(&k_full[0], 0, 4);
             tc_fence_after();

@@ -171,7 +171,9 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
         __syncthreads();                             // Q staged; TMEM allocated
         tc_fence_after();
         const uint32_t tmem = tmem_base_slot;
-        if (lane == 0) {
+        // The warp stays converged and elects the issuing lane per instruction: descriptors are then computed
+        // warp-uniformly (uniform registers), which roughly halves what an instruction costs its issuer.
+        {
             constexpr uint32_t id_qk_h = idesc_f16(kRows, kKeys);            // [Q_lo | Q] x [K_hi | K_lo], fp16
             constexpr uint32_t id_qk_t = make_idesc(kRows, kKeys, 0);        // Q_hi x K_hi, tf32
             constexpr uint32_t id_pv_t = make_idesc(kRows, 2 * D, 1);        // P_hi x [V_hi | V_lo], tf32, B N-major
@@ -185,7 +187,7 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                     const uint64_t dk = make_desc(smem_u32(k_st + stage * kKStage + C::kKhiBytes + hb * kKBlk), 16, 1024, 2);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)      // 16 fp16 = 32 bytes per instruction
-                        mma_h_ss(d, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_qk_h, (hb | k) ? 1u : 0u);
+                        if (elect_one()) mma_h_ss(d, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_qk_h, (hb | k) ? 1u : 0u);
                 }
 #pragma unroll
                 for (int db = 0; db < DB; ++db) {
@@ -193,9 +195,9 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                     const uint64_t dk = make_desc(smem_u32(k_st + stage * kKStage + db * kKBlk), 16, 1024, 2);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)      // 8 floats = 32 bytes per instruction
-                        mma_ss(d, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_qk_t, 1);
+                        if (elect_one()) mma_ss(d, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), id_qk_t, 1);
                 }
-                tc_commit(&s_full[buf]);             // also tells the K warp that this stage (same parity as buf) is free
+                if (elect_one()) tc_commit(&s_full[buf]);             // also tells the K warp that this stage (same parity as buf) is free
             };
             auto issue_pv = [&](int buf, int stage, bool first) {
                 // fp32 N-major B: 8 keys of 128 bytes per instruction; lbo = bytes between 32-column blocks
@@ -205,11 +207,11 @@ mha_tc16_kernel(const float *__restrict__ Q, const float *__restrict__ K, const 
                 const uint64_t dvt = make_desc(smem_u32(v_st + stage * kVStage + C::kVhlBytes), D * 16, 128, 0);
 #pragma unroll
                 for (int k = 0; k < kKeys / 8; ++k)
-                    mma_ts(tmem + kColO, tmem + kColX + buf * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), id_pv_t, (first && k == 0) ? 0u : 1u);
+                    if (elect_one()) mma_ts(tmem + kColO, tmem + kColX + buf * kKeys + (uint32_t)(k * 8), dv + (uint64_t)(k * 64), id_pv_t, (first && k == 0) ? 0u : 1u);
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)  // 16 keys = 8 TMEM columns of packed fp16 = two key groups of the fp16 V
-                    mma_h_ts(tmem + kColO + D, tmem + kColL + buf * 32 + (uint32_t)(k * 8), dvt + (uint64_t)(k * 2 * D), id_pv_h, 1);
-                tc_commit(&o_done[buf]);             // also tells the V warp that this stage is free
+                    if (elect_one()) mma_h_ts(tmem + kColO + D, tmem + kColL + buf * 32 + (uint32_t)(k * 8), dvt + (uint64_t)(k * 2 * D), id_pv_h, 1);
+                if (elect_one()) tc_commit(&o_done[buf]);             // also tells the V warp that this stage is free
             };
             wait(&k_full[0], 0, 4);
             tc_fence_after();
