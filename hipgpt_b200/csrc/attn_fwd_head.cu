@@ -36,12 +36,10 @@
 // Every wait is bounded: on expiry the block raises a flag that cuts all later waits short, records a
 // site code for hipgpt_kernel_status, skips its stores, frees its TMEM and returns.
 #include "tc_primitives.cuh"
+#include "tma_host.cuh"
 
-#include <cuda.h>
 #include <cuda_fp16.h>
 #include <math.h>
-
-#include <mutex>
 
 namespace hipgpt {
 namespace {
@@ -678,41 +676,6 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
 
 // ---- host side: tensor maps and the launch ---------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// Rank-3 map {E, S, B} over one fp32 plane; a box is [1][128 rows][32 floats], 128-byte swizzled, rows
-// past S read as zeros.
-int make_plane_map(CUtensorMap *m, const float *plane, int B, int S, int E)
-{
-    EncodeTiledFn enc = encode_fn();
-    if (!enc) return fail(HIPGPT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const cuuint64_t dims[3] = {(cuuint64_t)E, (cuuint64_t)S, (cuuint64_t)B};
-    const cuuint64_t strides[2] = {(cuuint64_t)E * 4, (cuuint64_t)S * E * 4};
-    const cuuint32_t box[3] = {32, (cuuint32_t)kTile, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(plane), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(HIPGPT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return HIPGPT_OK;
-}
-
 template <bool CAUSAL, bool PROBS>
 int launch_head_cfg(const HeadMaps &maps, float *out, float *probs, int B, int S, int E, int H, cudaStream_t st)
 {
@@ -743,7 +706,7 @@ bool mha_head_supports(int head_dim, int S, int E, const void *q, const void *k,
     return head_dim == 32 && S >= 1 && S <= 2 * kTile && (E % 4) == 0 &&
            ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
              reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
-           encode_fn() != nullptr;
+           tma_encode_fn() != nullptr;
 }
 
 int launch_mha_head(const float *q, const float *k, const float *v, float *out, float *probs, int B, int S, int E, int H, int causal, cudaStream_t st)
@@ -751,9 +714,9 @@ int launch_mha_head(const float *q, const float *k, const float *v, float *out, 
     if (E / H != 32 || S > 2 * kTile) return fail(HIPGPT_ERR_UNSUPPORTED, "whole-head kernel: head_dim %d, S %d", E / H, S);
     if (B == 0 || S == 0) return HIPGPT_OK;
     HeadMaps maps;
-    int rc = make_plane_map(&maps.q, q, B, S, E);
-    if (rc == HIPGPT_OK) rc = make_plane_map(&maps.k, k, B, S, E);
-    if (rc == HIPGPT_OK) rc = make_plane_map(&maps.v, v, B, S, E);
+    int rc = tma_plane_map(&maps.q, q, B, S, E, kTile, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == HIPGPT_OK) rc = tma_plane_map(&maps.k, k, B, S, E, kTile, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == HIPGPT_OK) rc = tma_plane_map(&maps.v, v, B, S, E, kTile, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HIPGPT_OK) return rc;
     if (probs) return causal ? launch_head_cfg<true, true>(maps, out, probs, B, S, E, H, st) : launch_head_cfg<false, true>(maps, out, probs, B, S, E, H, st);
     return causal ? launch_head_cfg<true, false>(maps, out, nullptr, B, S, E, H, st) : launch_head_cfg<false, false>(maps, out, nullptr, B, S, E, H, st);
