@@ -42,7 +42,9 @@ constexpr int kWorkers = kRows;
 constexpr int kStages = 3;        // fp16 operand stages of K and of V
 constexpr float kRescaleStep = 8.0f;
 constexpr float kPShift = 6.0f;   // P carries a factor 2^6: with the lazy reference maximum it stays below 2^15
-constexpr uint32_t kColX = 0, kColO = 128, kTmemCols = 256;
+constexpr int kBufs = 3;          // S / P buffers in TMEM
+constexpr uint32_t kColX = 0, kColO = kBufs * kKeys;
+static_assert(kBufs == kStages, "the barriers of buffers and stages share the tile-mod-3 phase arithmetic");
 
 // Sizes that depend on head_dim.  An operand row is cut into blocks of 128 bytes (32 floats or 64
 // fp16 values); a block of a tile is [rows][128 bytes], 128-byte swizzled.
@@ -54,8 +56,9 @@ struct Tc16Cfg {
     static constexpr int PWK = D == 64 ? 4 : 1;               // warps that convert K
     static constexpr int PWV = D == 64 ? 4 : 2;               // warps that convert V
     static constexpr int NRAW = D == 64 ? 3 : 2;              // landing slots per operand
-    static constexpr int THREADS = kWorkers + 32 + (PWK + PWV) * 32;   // workers, the issuing warp, the K warps, the V warps
+    static constexpr int THREADS = kWorkers + 64 + (PWK + PWV) * 32;   // workers, the two issuing warps, the K warps, the V warps
     static constexpr int BLOCKS_PER_SM = D == 64 ? 1 : 2;
+    static constexpr uint32_t kTmemCols = (kColO + 2 * D) <= 256 ? 256 : 512;
     static constexpr int kQBlk = kRows * 128, kKBlk = kKeys * 128;      // bytes of one block of a Q / K tile
     static constexpr int kQ16Bytes = HB * kQBlk;
     static constexpr int kK16Stage = HB * kKBlk;              // [K_hi | K_lo] rows
@@ -161,7 +164,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     uint8_t *v_16 = k_raw + NRAW * C::kRawSlot;              // per stage: [V_hi | V_lo] fp16, N-major: 8 keys x 8 columns form one
                                                              // 128-byte core matrix, column blocks 128 bytes apart, key groups 32 D
     uint8_t *v_raw = v_16 + kStages * C::kV16Stage;          // landing slots (the second sweep's staging area starts at v_16)
-    __shared__ uint64_t k_land[NRAW], v_land[NRAW], k_full[kStages], v_full[kStages], s_full[kStages], o_done[kStages], p_full[2];
+    __shared__ uint64_t k_land[NRAW], v_land[NRAW], k_full[kStages], v_full[kStages], s_full[kStages], o_done[kStages], p_full[kBufs];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ unsigned s_amax[3];                   // largest |Q| (scaled), |K|, |V| this block has seen
@@ -195,8 +198,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             mbar_init(&s_full[i], 1);                // tcgen05.commit after Q K(t)^T, t mod 3 = i: S is ready, and the K stage is free
             mbar_init(&o_done[i], 1);                // tcgen05.commit after P V(t): O is up to date, and the V stage is free
         }
-        mbar_init(&p_full[0], kWorkers / 32);        // one arrival per worker warp
-        mbar_init(&p_full[1], kWorkers / 32);
+        for (int i = 0; i < kBufs; ++i) mbar_init(&p_full[i], kWorkers / 32);    // one arrival per worker warp
     }
     __syncthreads();
 
@@ -218,11 +220,19 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     // barrier slot and phase parity of tile t for the barriers that are indexed by tile mod 3
     auto ph3 = [](int t) { return (uint32_t)((t / kStages) & 1); };
 
-    if (warp == kWorkers / 32) {
-        // ================= the issuing warp =====================================================
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        // the first tiles are asked for before anything else happens
+    if (warp == kWorkers / 32 || warp == kWorkers / 32 + 1) {
+        // ================= the two issuing warps =================================================
+        // One issues the K copies and every Q K^T, the other the V copies and every P V: an instruction costs the warp
+        // that issues it 60 - 100 cycles, more than it costs the tensor pipe, and two warps issue side by side.  Each
+        // accumulator is written by one warp, in tile order; what one warp's products need from the other's is
+        // ordered by the tcgen05.commit barriers.  The warps stay converged and elect the issuing lane per instruction
+        // (descriptors are then computed warp-uniformly, in uniform registers).
+        const bool qk_role = warp == kWorkers / 32;
+        if (qk_role) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        // one lane asks the TMA unit for a whole raw tile; the first tiles are asked for before anything else happens
         auto copy_k = [&](int u) {                   // u counts staged K tiles: the second sweep reads the tiles again
             if (lane == 0 && u < nk) {
                 const int slot = u % NRAW, j0 = (u < nt ? u : u - nt) * kKeys;
@@ -243,19 +253,17 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             }
             __syncwarp();
         };
-        for (int u = 0; u < NRAW; ++u) copy_k(u);
-        for (int u = 0; u < NRAW; ++u) copy_v(u);
+        if (qk_role) {
+            for (int u = 0; u < NRAW; ++u) copy_k(u);
+        } else {
+            for (int u = 0; u < NRAW; ++u) copy_v(u);
+        }
         tc_fence_before();
         __syncthreads();                             // Q staged; TMEM allocated
         tc_fence_after();
         const uint32_t tmem = tmem_base_slot;
-        // The warp stays converged and elects the issuing lane per instruction: descriptors are then computed
-        // warp-uniformly (uniform registers), which roughly halves what an instruction costs its issuer.
-        {
+        if (qk_role) {
             constexpr uint32_t id_qk = idesc_f16(kRows, kKeys);                    // fp16 x fp16, both K-major
-            constexpr uint32_t id_pv_a = idesc_f16(kRows, 2 * D) | (1u << 16);     // P_hi x [V_hi | V_lo], B N-major
-            constexpr uint32_t id_pv_b = idesc_f16(kRows, D) | (1u << 16);         // P_lo x V_hi
-            // columns [c0, c0 + D) of a row of [hi | lo]: block and 16-byte offset of 16-value step k
             auto issue_qk = [&](int buf, int t) {
                 const uint32_t d = tmem + kColX + buf * kKeys;
                 const uint8_t *kst = k_16 + (t % kStages) * C::kK16Stage;
@@ -265,7 +273,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
                     const int qc = prod == 0 ? D : 0, kc = prod == 1 ? D : 0;      // Q_lo K_hi, Q_hi K_lo, Q_hi K_hi
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
-                        const int qa = qc + 16 * k, ka = kc + 16 * k;
+                        const int qa = qc + 16 * k, ka = kc + 16 * k;              // first of 16 columns of a row of [hi | lo]
                         const uint64_t dq = make_desc(smem_u32(q_16 + (qa >> 6) * kQBlk), 16, 1024, 2) + (uint64_t)(((qa & 63) >> 4) * 2);
                         const uint64_t dk = make_desc(smem_u32(kst + (ka >> 6) * kKBlk), 16, 1024, 2) + (uint64_t)(((ka & 63) >> 4) * 2);
                         if (elect_one()) mma_h_ss(d, dq, dk, id_qk, (prod | k) ? 1u : 0u);
@@ -273,7 +281,31 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
                 }
                 if (elect_one()) tc_commit(&s_full[t % kStages]);    // S is ready; it also tells the K warps that this stage is free
             };
-            auto issue_pv = [&](int buf, int t) {
+            wait(&k_full[0], 0, 4);
+            tc_fence_after();
+            issue_qk(0, 0);
+            for (int t = 0; t + 1 < nk; ++t) {
+                // the landing slot of K(t) was read when K(t) was converted, before Q K(t)^T was issued
+                copy_k(t + NRAW);
+                wait(&k_full[(t + 1) % kStages], ph3(t + 1), 4);                 // K(t+1) is in its stage
+                // the buffer of S(t+1) held P(t-2) (first sweep) or S(t-2) (second sweep): with three buffers the product
+                // runs up to two tiles ahead of the exponentials and never waits for the P V product before it
+                if (t >= 2) {
+                    if (t - 2 < nt) wait(&o_done[(t - 2) % kStages], ph3(t - 2), 2);          // P V(t-2) has read it
+                    else wait(&p_full[(t - 2) % kBufs], ph3(t - 2), 5);                       // the workers have read it
+                }
+                tc_fence_after();
+                issue_qk((t + 1) % kBufs, t + 1);
+            }
+        } else {
+            constexpr uint32_t id_pv_a = idesc_f16(kRows, 2 * D) | (1u << 16);     // P_hi x [V_hi | V_lo], B N-major
+            constexpr uint32_t id_pv_b = idesc_f16(kRows, D) | (1u << 16);         // P_lo x V_hi
+            for (int t = 0; t < nt; ++t) {
+                const int buf = t % kBufs;
+                wait(&p_full[buf], ph3(t), 5);                                   // P(t) is in TMEM
+                wait(&v_full[t % kStages], ph3(t), 6);                           // V(t) is in its stage: its landing slot has been read
+                copy_v(t + NRAW);
+                tc_fence_after();
                 const uint32_t a0 = tmem + kColX + buf * kKeys;
                 // N-major B without swizzle: lbo = bytes between groups of 8 keys, sbo = bytes between blocks of 8 columns
                 const uint64_t dv = make_desc(smem_u32(v_16 + (t % kStages) * C::kV16Stage), 32 * D, 128, 0);
@@ -283,43 +315,13 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)
                     if (elect_one()) mma_h_ts(tmem + kColO + D, a0 + (uint32_t)(32 * (k >> 1) + 8 * (k & 1) + 16), dv + (uint64_t)(k * 4 * D), id_pv_b, 1u);
-                if (elect_one()) tc_commit(&o_done[t % kStages]);    // O is up to date; it also tells the V warps that this stage is free
-            };
-            wait(&k_full[0], 0, 4);
-            tc_fence_after();
-            issue_qk(0, 0);
-            for (int t = 0; t < nt; ++t) {
-                const int buf = t & 1;
-                // the landing slot of K(t) was read when K(t) was converted, before Q K(t)^T was issued
-                copy_k(t + NRAW);
-                if (t + 1 < nt) {
-                    wait(&k_full[(t + 1) % kStages], ph3(t + 1), 4);             // K(t+1) is in its stage
-                    tc_fence_after();
-                    issue_qk(buf ^ 1, t + 1);        // its buffer held P(t-1): P V(t-1) was issued before, instructions run in order
-                }
-                wait(&p_full[buf], (uint32_t)((t >> 1) & 1), 5);                 // P(t) is in TMEM
-                wait(&v_full[t % kStages], ph3(t), 6);                           // V(t) is in its stage: its landing slot has been read
-                copy_v(t + NRAW);
-                tc_fence_after();
-                issue_pv(buf, t);
-            }
-            if (PROBS) {
-                // X[u & 1] held P(u-2) (consumed by P V(u-2), issued before) or, from the third tile of
-                // this sweep on, S(u-2), which the workers must have read
-                for (int u = nt; u < nk; ++u) {
-                    const int bf = u & 1;
-                    wait(&k_full[u % kStages], ph3(u), 4);
-                    copy_k(u + NRAW);                // the landing slot of K(u) has been read
-                    if (u - 2 >= nt) wait(&p_full[bf], (uint32_t)(((u - 2) >> 1) & 1), 5);
-                    tc_fence_after();
-                    issue_qk(bf, u);
-                }
+                if (elect_one()) tc_commit(&o_done[t % kStages]);    // O is up to date; the V warps may rewrite this stage, Q K^T this buffer
             }
         }
         __syncwarp();
         tc_fence_before();
         __syncthreads();                             // the workers have read the output
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        if (qk_role) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
         return;
     }
 
@@ -327,8 +329,8 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     // A raw fp32 tile lands in a slot by TMA; a thread reads its own 32-byte pieces (8 floats of pairs of adjacent
     // rows), cuts them into hi and lo and writes the fp16 operand stage.  The stage of tile u was read by the product
     // of tile u - 3.
-    if (warp > kWorkers / 32 && warp <= kWorkers / 32 + PWK) {
-        const PieceMap<32 * PWK, PPR> pm(tid - kWorkers - 32);
+    if (warp > kWorkers / 32 + 1 && warp <= kWorkers / 32 + 1 + PWK) {
+        const PieceMap<32 * PWK, PPR> pm(tid - kWorkers - 64);
         constexpr int NPC = pm.NPC, BATCH = pm.BATCH;
         const int pc = pm.pc, pblk = pm.pblk, pch = pm.pch;
         float amax = 0.0f;
@@ -366,8 +368,8 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
         __syncthreads();
         return;
     }
-    if (warp > kWorkers / 32 + PWK) {
-        const PieceMap<32 * PWV, PPR> pm(tid - kWorkers - 32 - 32 * PWK);
+    if (warp > kWorkers / 32 + 1 + PWK) {
+        const PieceMap<32 * PWV, PPR> pm(tid - kWorkers - 64 - 32 * PWK);
         constexpr int NPC = pm.NPC, BATCH = pm.BATCH;
         const int pc = pm.pc, pblk = pm.pblk, pch = pm.pch;
         float amax = 0.0f;
@@ -441,7 +443,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
 
     float m_ref = 0.0f, l = 0.0f;                    // reference maximum (log2 domain) and row sum (of P, which carries 2^6)
     for (int t = 0; t < nt; ++t) {
-        const int buf = t & 1;
+        const int buf = t % kBufs;
         const int j0 = t * kKeys;
         const uint32_t s_addr = lane_base + kColX + buf * kKeys;
         wait(&s_full[t % kStages], ph3(t), 1);       // S(t) is in TMEM
@@ -539,7 +541,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             float *pwarp = P + ((size_t)bh * S + wrow0) * (size_t)S;
             const bool vec = (S & 3) == 0;               // then every 4-column group of a row is 16-byte aligned
             for (int u = nt; u < nk; ++u) {
-                const int buf = u & 1, j0 = (u - nt) * kKeys;
+                const int buf = u % kBufs, j0 = (u - nt) * kKeys;
                 const uint32_t s_addr = lane_base + kColX + buf * kKeys;
                 wait(&s_full[u % kStages], ph3(u), 1);
                 tc_fence_after();
