@@ -46,6 +46,7 @@ int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, 
                     int B, int S, int E, int H, int causal, cudaStream_t st);
 bool mha_tc16_supports(int head_dim);
 int tc16_status_fetch(int *status);
+void tc16_release_scratch();
 int tc16_notice_fetch(int *notice);
 // whole-head kernel (head_dim 32, S <= 256): TMA loads, 128-key products, all score tiles of a head in TMEM
 int launch_mha_head(const float *q, const float *k, const float *v, float *out, float *probs, int B, int S, int E, int H, int causal, cudaStream_t st);

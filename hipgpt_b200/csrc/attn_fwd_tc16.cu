@@ -17,11 +17,14 @@
 // (steps of 6e-8), which the notice's test weighs against the scores it is added to.  The split-TF32 kernel
 // (attn_fwd_tc.cu) has the whole fp32 range.
 //
-// One block = 128 query rows of one (batch, head); two blocks per SM at head_dim 32, one at head_dim 64.
-//   Copies: one lane asks the TMA unit for whole raw tiles ([64 keys][32 floats] boxes, keys past S arrive as zeros)
-//   into a ring of landing slots, as many tiles ahead as there are slots; the K and V warps turn a landed tile into
-//   its fp16 operand stage (three stages) and publish it.  A stage is rewritten once the product that read it three
-//   tiles ago has completed (barriers indexed by tile mod 3, completed by tcgen05.commit).
+// Two kernels.  kv_pack_kernel cuts K and V into their fp16 pieces once per call and writes them, tile by tile, as
+// the exact shared-memory images of the operand stages (K: rows of [K_hi | K_lo], K-major, 128-byte swizzle; V:
+// [V_hi | V_lo], N-major) into a scratch buffer of the library: a 64-key tile is needed by every block of query rows
+// of its head (8 at S = 1024, 16 at S = 2048), and converting it in each of them was measured to be what paced the
+// attention kernel (no conversion: 1.4 x faster).  mha_tc16_kernel then fetches a stage with one bulk copy.
+// One block = 128 query rows of one (batch, head); two blocks per SM.
+//   Copies: one lane of an issuing warp asks for a whole operand stage (cp.async.bulk, completion counted on an
+//   mbarrier); a stage is refilled once the product that read it has completed (tcgen05.commit barriers).
 //   TMEM (256 columns): X0, X1 (64 each): S(t), overwritten in place by P(t);  O (2 D): [P_hi V_hi | P_hi V_lo + P_lo V_hi],
 //   accumulated over ALL tiles.  Workers (thread = query row = TMEM lane) never read O back per tile: the reference
 //   maximum only moves (and O is rescaled, by the whole warp) when a row's maximum grew by more than 2^8.
@@ -29,9 +32,12 @@
 // Every wait is bounded: on expiry the block raises a flag that cuts all later waits short,
 // records a status code, skips its stores, frees its TMEM and returns.
 #include "tc_primitives.cuh"
-#include "tma_host.cuh"
 
 #include <math.h>
+#include <stdlib.h>
+
+#include <mutex>
+#include <vector>
 
 namespace hipgpt {
 namespace {
@@ -39,49 +45,32 @@ namespace {
 constexpr int kRows = 128;        // query rows per block
 constexpr int kKeys = 64;         // keys per tile
 constexpr int kWorkers = kRows;
-constexpr int kStages = 3;        // fp16 operand stages of K and of V
 constexpr float kRescaleStep = 8.0f;
 constexpr float kPShift = 6.0f;   // P carries a factor 2^6: with the lazy reference maximum it stays below 2^15
-constexpr int kBufs = 3;          // S / P buffers in TMEM
-constexpr uint32_t kColX = 0, kColO = kBufs * kKeys;
-static_assert(kBufs == kStages, "the barriers of buffers and stages share the tile-mod-3 phase arithmetic");
+constexpr int kBufs = 2;          // S / P buffers in TMEM
+constexpr uint32_t kColX = 0, kColO = kBufs * kKeys, kTmemCols = 256;
+constexpr int kPackThreads = 128;
 
 // Sizes that depend on head_dim.  An operand row is cut into blocks of 128 bytes (32 floats or 64
 // fp16 values); a block of a tile is [rows][128 bytes], 128-byte swizzled.
 template <int D>
 struct Tc16Cfg {
-    static constexpr int DB = D / 32;                         // fp32 blocks per row
     static constexpr int HB = (2 * D) / 64;                   // fp16 blocks per row of [x_hi | x_lo]
-    static constexpr int PPR = D / 8;                         // 32-byte pieces per row
-    static constexpr int PWK = D == 64 ? 4 : 1;               // warps that convert K
-    static constexpr int PWV = D == 64 ? 4 : 2;               // warps that convert V
-    static constexpr int NRAW = D == 64 ? 3 : 2;              // landing slots per operand
-    static constexpr int THREADS = kWorkers + 64 + (PWK + PWV) * 32;   // workers, the two issuing warps, the K warps, the V warps
-    static constexpr int BLOCKS_PER_SM = D == 64 ? 1 : 2;
-    static constexpr uint32_t kTmemCols = (kColO + 2 * D) <= 256 ? 256 : 512;
+    static constexpr int PPR = D / 8;                         // 32-byte pieces (8 floats) per row
+    static constexpr int KST = D == 64 ? 2 : 3;               // operand stages of K
+    static constexpr int VST = D == 64 ? 2 : 4;               // ... of V (the second sweep stages 32 KB of probabilities there)
+    static constexpr int THREADS = kWorkers + 64;             // workers and the two issuing warps
+    static constexpr int BLOCKS_PER_SM = 2;
     static constexpr int kQBlk = kRows * 128, kKBlk = kKeys * 128;      // bytes of one block of a Q / K tile
     static constexpr int kQ16Bytes = HB * kQBlk;
     static constexpr int kK16Stage = HB * kKBlk;              // [K_hi | K_lo] rows
     static constexpr int kV16Stage = kKeys * 2 * D * 2;       // [V_hi | V_lo], N-major without swizzle
-    static constexpr int kRawSlot = DB * kKBlk;               // one raw fp32 tile
-    static constexpr size_t kSmemBytes = (size_t)kQ16Bytes + kStages * (kK16Stage + kV16Stage) + 2 * NRAW * kRawSlot;
+    static constexpr size_t kSmemBytes = (size_t)kQ16Bytes + KST * kK16Stage + VST * kV16Stage;
+    static_assert(VST * kV16Stage >= 4 * 32 * kKeys * 4, "the second sweep's staging area");
 };
 
 __device__ int g_tc16_status = 0;
-__device__ int g_tc16_notice = 0;                // bit 0: an operand left the range in which the fp16 pieces are exact
-
-__device__ __forceinline__ float amax8(float m, float4 a, float4 c)
-{
-    return fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
-                          fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w)))));
-}
-// The warp's largest magnitude into a shared word (as a bit pattern: non-negative floats order like integers).
-__device__ __forceinline__ void publish_amax(unsigned *slot, float m)
-{
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if ((threadIdx.x & 31) == 0) atomicMax(slot, __float_as_uint(m));
-}
+__device__ int g_tc16_notice = 0;                // never raised by this kernel: its operands are scaled into fp16's range
 
 // The polling part of a bounded wait; on expiry the block's abort flag is raised and the site recorded.
 __device__ __noinline__ void tc16_wait_slow(uint64_t *bar, uint32_t parity, int site, volatile int *abort_flag)
@@ -108,9 +97,9 @@ __device__ __forceinline__ float chunk_max(float (&v)[32], int col0, int nvalid,
     return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
 }
 
-// One chunk of scores (log2 domain) -> P = 2^(s + nm), cut into fp16 hi and lo, written over the chunk's own 32 TMEM
+// One chunk of scores (log2 domain, times 1 / sfac) -> P = 2^(s sfac + nm), cut into fp16 hi and lo, written over the chunk's own 32 TMEM
 // columns (16 of packed P_hi, then 16 of packed P_lo).  Returns the sum of P.
-__device__ __forceinline__ float chunk_exp(float (&v)[32], uint32_t addr, int col0, int nvalid, bool need_mask, float nm)
+__device__ __forceinline__ float chunk_exp(float (&v)[32], uint32_t addr, int col0, int nvalid, bool need_mask, float sfac, float nm)
 {
     if (need_mask) {
         // a hidden score becomes -inf: its exponential is exactly 0
@@ -123,7 +112,7 @@ __device__ __forceinline__ float chunk_exp(float (&v)[32], uint32_t addr, int co
         uint32_t hi[8], lo[8];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
-            const float p0 = ex2_approx(v[16 * half + j] + nm), p1 = ex2_approx(v[16 * half + j + 1] + nm);
+            const float p0 = ex2_approx(fmaf(v[16 * half + j], sfac, nm)), p1 = ex2_approx(fmaf(v[16 * half + j + 1], sfac, nm));
             ps[j & 3] += p0;
             ps[(j + 1) & 3] += p1;
             const float h0 = tf32_hi(p0), h1 = tf32_hi(p1);      // 11 leading bits: exact in fp16
@@ -136,38 +125,120 @@ __device__ __forceinline__ float chunk_exp(float (&v)[32], uint32_t addr, int co
     return (ps[0] + ps[1]) + (ps[2] + ps[3]);
 }
 
-// Which pieces of a 64-row tile a converting thread owns.  A piece is 32 bytes (8 floats) of a row; a
-// thread owns pieces of pairs of adjacent rows.  PT = threads that convert this operand, PPR = pieces per row.
-template <int PT, int PPR>
-struct PieceMap {
-    static constexpr int NPC = (kKeys * PPR) / PT;            // pieces per thread and tile
-    static constexpr int RPP = 2 * (PT / PPR);                // rows covered by a pair of passes
-    static constexpr int BATCH = NPC < 8 ? NPC : 8;           // pieces converted at a time
-    int pc, pq, pblk, pch;                                    // piece of a row, row pair, fp32 block and first 16-byte chunk of the piece
-    __device__ explicit PieceMap(int pid) : pc(pid % PPR), pq(pid / PPR), pblk((pid % PPR) >> 2), pch(2 * ((pid % PPR) & 3)) {}
-    __device__ int row(int p) const { return RPP * (p >> 1) + 2 * pq + (p & 1); }
-};
+// The power of two that brings a largest magnitude `amax` into [2^14, 2^15): fp16 then holds the 11 leading bits of
+// every value that matters beside the largest one.  1 for zero, infinite or NaN input.
+__device__ __forceinline__ float range_scale(float amax)
+{
+    if (!(amax > 0.0f && amax <= 3.0e38f)) return 1.0f;
+    const int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+    int sh = 14 - e;
+    sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+    return __uint_as_float((uint32_t)(127 + sh) << 23);
+}
+
+// log2 of a positive power of two (its exponent field)
+__device__ __forceinline__ float log2_of_pow2(float p) { return (float)((int)((__float_as_uint(p) >> 23) & 0xffu) - 127); }
+
+// ---- the pack kernel: K and V of one (batch, head, 64-key tile) -> the fp16 images of their operand stages ----
+// Thread pid owns 32-byte pieces (8 floats): piece pid % PPR of rows pid / PPR, + 128 / PPR, ...  A warp reads whole
+// rows (coalesced) and writes 16-byte chunks that fill whole 128-byte lines of the image.
+// Every tile is scaled by a power of two of its own (range_scale of the tile's largest magnitude), so that no operand
+// magnitude costs accuracy: the block holds its pieces in registers, finds the two maxima, converts.  The maxima go to
+// tmax[0][tile] (K) and tmax[1][tile] (V), V's largest over the whole head to hmax[bh] (zeroed before the launch;
+// non-negative floats order like their bit patterns): the attention kernel takes the factors out again.
+// K image: [HB blocks][64 rows][128 bytes], a row of block j holds values 64 j .. 64 j + 63 of [K_hi (D) | K_lo (D)],
+// 16-byte chunks swizzled by the row (the layout a K-major, 128-byte-swizzled operand has in shared memory).
+// V image: key r, column block cb (8 columns of [V_hi (D) | V_lo (D)]) at (r / 8) * 32 D + cb * 128 + (r % 8) * 16:
+// 8 keys x 8 columns form one 128-byte core matrix of an N-major operand without swizzle.  Keys past S are zeros.
+template <int D>
+__global__ void __launch_bounds__(kPackThreads)
+kv_pack_kernel(const float *__restrict__ K, const float *__restrict__ V, float *__restrict__ tmax, float *__restrict__ hmax,
+               uint8_t *__restrict__ kimg, uint8_t *__restrict__ vimg, int S, int E, int H, int ntk, int ntiles)
+{
+    using C = Tc16Cfg<D>;
+    constexpr int PPR = C::PPR, RPT = kPackThreads / PPR, NP = kKeys / RPT;      // rows covered per pass, pieces per thread
+    __shared__ float red[2][kPackThreads / 32];
+    const int kt = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / H, h = bh % H;
+    const int pid = threadIdx.x, pc = pid % PPR, r0 = pid / PPR;
+    const size_t tile = (size_t)bh * ntk + kt;
+    uint8_t *kout = kimg + tile * C::kK16Stage, *vout = vimg + tile * C::kV16Stage;
+    float4 ka[NP], kc[NP], va[NP], vc[NP];
+    float mk = 0.0f, mv = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        const int j = kt * kKeys + r0 + i * RPT;
+        const bool ok = j < S;
+        const size_t off = ((size_t)b * S + (ok ? j : 0)) * (size_t)E + (size_t)h * D + 8 * pc;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        ka[i] = ok ? __ldg(reinterpret_cast<const float4 *>(K + off)) : z;
+        kc[i] = ok ? __ldg(reinterpret_cast<const float4 *>(K + off) + 1) : z;
+        va[i] = ok ? __ldg(reinterpret_cast<const float4 *>(V + off)) : z;
+        vc[i] = ok ? __ldg(reinterpret_cast<const float4 *>(V + off) + 1) : z;
+        mk = fmaxf(mk, fmaxf(fmaxf(fmaxf(fabsf(ka[i].x), fabsf(ka[i].y)), fmaxf(fabsf(ka[i].z), fabsf(ka[i].w))),
+                             fmaxf(fmaxf(fabsf(kc[i].x), fabsf(kc[i].y)), fmaxf(fabsf(kc[i].z), fabsf(kc[i].w)))));
+        mv = fmaxf(mv, fmaxf(fmaxf(fmaxf(fabsf(va[i].x), fabsf(va[i].y)), fmaxf(fabsf(va[i].z), fabsf(va[i].w))),
+                             fmaxf(fmaxf(fabsf(vc[i].x), fabsf(vc[i].y)), fmaxf(fabsf(vc[i].z), fabsf(vc[i].w)))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+        mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+    }
+    if ((pid & 31) == 0) { red[0][pid >> 5] = mk; red[1][pid >> 5] = mv; }
+    __syncthreads();
+    mk = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
+    mv = fmaxf(fmaxf(red[1][0], red[1][1]), fmaxf(red[1][2], red[1][3]));
+    if (pid == 0) {
+        tmax[tile] = mk;
+        tmax[ntiles + tile] = mv;
+        atomicMax(reinterpret_cast<unsigned *>(hmax) + bh, __float_as_uint(mv));     // a NaN's pattern is "no scaling" too
+    }
+    const float sk = range_scale(mk), sv = range_scale(mv);
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        const int r = r0 + i * RPT;
+        float4 a = ka[i], c = kc[i];
+        a.x *= sk; a.y *= sk; a.z *= sk; a.w *= sk; c.x *= sk; c.y *= sk; c.z *= sk; c.w *= sk;
+        {
+            const float4 ah = hi4(a), ch = hi4(c);
+            // values 8 pc .. of the hi half, 8 (PPR + pc) .. of the lo half of the row
+            *reinterpret_cast<uint4 *>(kout + (pc >> 3) * C::kKBlk + sw128(r, pc & 7)) =
+                make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+            *reinterpret_cast<uint4 *>(kout + ((PPR + pc) >> 3) * C::kKBlk + sw128(r, (PPR + pc) & 7)) =
+                make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
+                           pack_f16(c.x - ch.x, c.y - ch.y), pack_f16(c.z - ch.z, c.w - ch.w));
+        }
+        a = va[i]; c = vc[i];
+        a.x *= sv; a.y *= sv; a.z *= sv; a.w *= sv; c.x *= sv; c.y *= sv; c.z *= sv; c.w *= sv;
+        {
+            const float4 ah = hi4(a), ch = hi4(c);
+            uint8_t *dst = vout + (r >> 3) * (32 * D) + (r & 7) * 16;
+            *reinterpret_cast<uint4 *>(dst + pc * 128) =
+                make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
+            *reinterpret_cast<uint4 *>(dst + (PPR + pc) * 128) =
+                make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
+                           pack_f16(c.x - ch.x, c.y - ch.y), pack_f16(c.z - ch.z, c.w - ch.w));
+        }
+    }
+}
 
 template <int D, bool CAUSAL, bool PROBS>
 __global__ void __launch_bounds__(Tc16Cfg<D>::THREADS, Tc16Cfg<D>::BLOCKS_PER_SM)
-mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const float *__restrict__ Q,
-                float *__restrict__ O, float *__restrict__ P, int S, int E, int H, int BH, int nqblk, float qscale)
+mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vimg, const float *__restrict__ tmax, const float *__restrict__ hmax, int ntiles, const float *__restrict__ Q,
+                float *__restrict__ O, float *__restrict__ P, int S, int E, int H, int BH, int nqblk, int ntk, float qscale)
 {
     using C = Tc16Cfg<D>;
-    constexpr int DB = C::DB, PPR = C::PPR, PWK = C::PWK, PWV = C::PWV, NRAW = C::NRAW;
+    constexpr int PPR = C::PPR, KST = C::KST, VST = C::VST;
     constexpr int kQBlk = C::kQBlk, kKBlk = C::kKBlk;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *q_16 = base;                                    // fp16 [HB][128][64]: a row is [Q_hi (D) | Q_lo (D)], K-major
     uint8_t *k_16 = q_16 + C::kQ16Bytes;                     // per stage: fp16 [HB][64][64]: [K_hi (D) | K_lo (D)]
-    uint8_t *k_raw = k_16 + kStages * C::kK16Stage;          // landing slots: fp32 [DB][64][32], 128-byte swizzled
-    uint8_t *v_16 = k_raw + NRAW * C::kRawSlot;              // per stage: [V_hi | V_lo] fp16, N-major: 8 keys x 8 columns form one
-                                                             // 128-byte core matrix, column blocks 128 bytes apart, key groups 32 D
-    uint8_t *v_raw = v_16 + kStages * C::kV16Stage;          // landing slots (the second sweep's staging area starts at v_16)
-    __shared__ uint64_t k_land[NRAW], v_land[NRAW], k_full[kStages], v_full[kStages], s_full[kStages], o_done[kStages], p_full[kBufs];
+    uint8_t *v_16 = k_16 + KST * C::kK16Stage;               // per stage: [V_hi | V_lo] fp16, N-major
+    __shared__ uint64_t k_full[KST], v_full[VST], s_full[KST], o_done[VST], p_full[kBufs];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
-    __shared__ unsigned s_amax[3];                   // largest |Q| (scaled), |K|, |V| this block has seen
 
     const int tid = threadIdx.x, lane = tid & 31;
     // read from one lane, so that the compiler knows the warp's number (and every role that follows from it) to be warp-uniform
@@ -187,23 +258,20 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
 
     if (tid == 0) {
         abort_flag = 0;
-        s_amax[0] = s_amax[1] = s_amax[2] = 0u;
-        for (int i = 0; i < NRAW; ++i) {
-            mbar_init(&k_land[i], 1);                // the copy of a tile: one announcement, then its bytes
-            mbar_init(&v_land[i], 1);
+        for (int i = 0; i < KST; ++i) {
+            mbar_init(&k_full[i], 1);                // the copy of a stage: one announcement, then its bytes
+            mbar_init(&s_full[i], 1);                // tcgen05.commit after Q K(t)^T, t mod KST = i: S is ready, and the K stage is free
         }
-        for (int i = 0; i < kStages; ++i) {
-            mbar_init(&k_full[i], PWK);              // one arrival per K warp
-            mbar_init(&v_full[i], PWV);              // one arrival per V warp
-            mbar_init(&s_full[i], 1);                // tcgen05.commit after Q K(t)^T, t mod 3 = i: S is ready, and the K stage is free
+        for (int i = 0; i < VST; ++i) {
+            mbar_init(&v_full[i], 1);
             mbar_init(&o_done[i], 1);                // tcgen05.commit after P V(t): O is up to date, and the V stage is free
         }
         for (int i = 0; i < kBufs; ++i) mbar_init(&p_full[i], kWorkers / 32);    // one arrival per worker warp
     }
     __syncthreads();
 
-    // site codes in the status word: 1 S ready, 2 O complete (rescale), 3 O complete (end), 4 K staged,
-    // 5 P written, 6 V staged, 7 K stage free, 8 V stage free, 9 K tile landed, 10 V tile landed
+    // site codes in the status word: 1 S ready, 2 O complete (rescale), 3 O complete (end), 4 K stage landed,
+    // 5 P written, 6 V stage landed, 7 K stage free, 8 V stage free
     // (the polling loop exists once, out of line: an already completed phase costs one test)
     auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
         if (abort_flag || mbar_test(bar, parity)) return;
@@ -217,46 +285,41 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     // byte offset, inside an fp16 operand of rows [hi (D) | lo (D)], of the 16-byte chunk holding values
     // 8 e8 .. 8 e8 + 7 of row r; blk = bytes of one 128-byte-row block of that operand
     auto off16 = [](int r, int e8, int blk) { return (e8 >> 3) * blk + sw128(r, e8 & 7); };
-    // barrier slot and phase parity of tile t for the barriers that are indexed by tile mod 3
-    auto ph3 = [](int t) { return (uint32_t)((t / kStages) & 1); };
+    // phase parity of tile t on a barrier that is indexed by tile mod n
+    auto phn = [](int t, int n) { return (uint32_t)((t / n) & 1); };
 
     if (warp == kWorkers / 32 || warp == kWorkers / 32 + 1) {
         // ================= the two issuing warps =================================================
-        // One issues the K copies and every Q K^T, the other the V copies and every P V: an instruction costs the warp
-        // that issues it 60 - 100 cycles, more than it costs the tensor pipe, and two warps issue side by side.  Each
-        // accumulator is written by one warp, in tile order; what one warp's products need from the other's is
-        // ordered by the tcgen05.commit barriers.  The warps stay converged and elect the issuing lane per instruction
-        // (descriptors are then computed warp-uniformly, in uniform registers).
+        // One fetches the K stages and issues every Q K^T, the other fetches the V stages and issues every P V: an
+        // instruction costs the warp that issues it 60 - 100 cycles, more than it costs the tensor pipe, and two warps
+        // issue side by side.  Each accumulator is written by one warp, in tile order; what one warp's products need
+        // from the other's is ordered by the tcgen05.commit barriers.  The warps stay converged and elect the issuing
+        // lane per instruction (descriptors are then computed warp-uniformly, in uniform registers).
         const bool qk_role = warp == kWorkers / 32;
         if (qk_role) {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(C::kTmemCols) : "memory");
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
-        // one lane asks the TMA unit for a whole raw tile; the first tiles are asked for before anything else happens
-        auto copy_k = [&](int u) {                   // u counts staged K tiles: the second sweep reads the tiles again
+        // one lane asks for a whole packed stage (u counts staged K tiles: the second sweep reads the tiles again)
+        auto copy_k = [&](int u) {
             if (lane == 0 && u < nk) {
-                const int slot = u % NRAW, j0 = (u < nt ? u : u - nt) * kKeys;
-                mbar_arrive_expect_tx(&k_land[slot], (uint32_t)C::kRawSlot);
-#pragma unroll
-                for (int db = 0; db < DB; ++db)
-                    tma_load_3d(k_raw + slot * C::kRawSlot + db * kKBlk, &kmap, (int)hcol + 32 * db, j0, b, &k_land[slot]);
+                const int kt = u < nt ? u : u - nt;
+                mbar_arrive_expect_tx(&k_full[u % KST], (uint32_t)C::kK16Stage);
+                bulk_load(k_16 + (u % KST) * C::kK16Stage, kimg + ((size_t)bh * ntk + kt) * C::kK16Stage, (uint32_t)C::kK16Stage, &k_full[u % KST]);
             }
             __syncwarp();
         };
         auto copy_v = [&](int u) {
             if (lane == 0 && u < nt) {
-                const int slot = u % NRAW;
-                mbar_arrive_expect_tx(&v_land[slot], (uint32_t)C::kRawSlot);
-#pragma unroll
-                for (int db = 0; db < DB; ++db)
-                    tma_load_3d(v_raw + slot * C::kRawSlot + db * kKBlk, &vmap, (int)hcol + 32 * db, u * kKeys, b, &v_land[slot]);
+                mbar_arrive_expect_tx(&v_full[u % VST], (uint32_t)C::kV16Stage);
+                bulk_load(v_16 + (u % VST) * C::kV16Stage, vimg + ((size_t)bh * ntk + u) * C::kV16Stage, (uint32_t)C::kV16Stage, &v_full[u % VST]);
             }
             __syncwarp();
         };
         if (qk_role) {
-            for (int u = 0; u < NRAW; ++u) copy_k(u);
+            for (int u = 0; u < KST; ++u) copy_k(u);
         } else {
-            for (int u = 0; u < NRAW; ++u) copy_v(u);
+            for (int u = 0; u < VST; ++u) copy_v(u);
         }
         tc_fence_before();
         __syncthreads();                             // Q staged; TMEM allocated
@@ -266,7 +329,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             constexpr uint32_t id_qk = idesc_f16(kRows, kKeys);                    // fp16 x fp16, both K-major
             auto issue_qk = [&](int buf, int t) {
                 const uint32_t d = tmem + kColX + buf * kKeys;
-                const uint8_t *kst = k_16 + (t % kStages) * C::kK16Stage;
+                const uint8_t *kst = k_16 + (t % KST) * C::kK16Stage;
                 // the correction terms first: the accumulator is still tiny while they are added
 #pragma unroll
                 for (int prod = 0; prod < 3; ++prod) {
@@ -279,134 +342,53 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
                         if (elect_one()) mma_h_ss(d, dq, dk, id_qk, (prod | k) ? 1u : 0u);
                     }
                 }
-                if (elect_one()) tc_commit(&s_full[t % kStages]);    // S is ready; it also tells the K warps that this stage is free
+                if (elect_one()) tc_commit(&s_full[t % KST]);        // S is ready, and this K stage may be refilled
             };
             wait(&k_full[0], 0, 4);
             tc_fence_after();
             issue_qk(0, 0);
             for (int t = 0; t + 1 < nk; ++t) {
-                // the landing slot of K(t) was read when K(t) was converted, before Q K(t)^T was issued
-                copy_k(t + NRAW);
-                wait(&k_full[(t + 1) % kStages], ph3(t + 1), 4);                 // K(t+1) is in its stage
-                // the buffer of S(t+1) held P(t-2) (first sweep) or S(t-2) (second sweep): with three buffers the product
-                // runs up to two tiles ahead of the exponentials and never waits for the P V product before it
-                if (t >= 2) {
-                    if (t - 2 < nt) wait(&o_done[(t - 2) % kStages], ph3(t - 2), 2);          // P V(t-2) has read it
-                    else wait(&p_full[(t - 2) % kBufs], ph3(t - 2), 5);                       // the workers have read it
+                wait(&k_full[(t + 1) % KST], phn(t + 1, KST), 4);                // K(t+1) is in its stage
+                // the buffer of S(t+1) held P(t-1) (first sweep) or S(t-1) (second sweep)
+                if (t >= 1) {
+                    if (t - 1 < nt) wait(&o_done[(t - 1) % VST], phn(t - 1, VST), 2);        // P V(t-1) has read it
+                    else wait(&p_full[(t - 1) % kBufs], phn(t - 1, kBufs), 5);               // the workers have read it
                 }
                 tc_fence_after();
                 issue_qk((t + 1) % kBufs, t + 1);
+                // Q K(t)^T was issued a whole step ago: it has completed, or does so before the product above
+                wait(&s_full[t % KST], phn(t, KST), 7);
+                copy_k(t + KST);
             }
         } else {
             constexpr uint32_t id_pv_a = idesc_f16(kRows, 2 * D) | (1u << 16);     // P_hi x [V_hi | V_lo], B N-major
             constexpr uint32_t id_pv_b = idesc_f16(kRows, D) | (1u << 16);         // P_lo x V_hi
             for (int t = 0; t < nt; ++t) {
                 const int buf = t % kBufs;
-                wait(&p_full[buf], ph3(t), 5);                                   // P(t) is in TMEM
-                wait(&v_full[t % kStages], ph3(t), 6);                           // V(t) is in its stage: its landing slot has been read
-                copy_v(t + NRAW);
+                wait(&p_full[buf], phn(t, kBufs), 5);                            // P(t) is in TMEM
+                wait(&v_full[t % VST], phn(t, VST), 6);                          // V(t) is in its stage
                 tc_fence_after();
                 const uint32_t a0 = tmem + kColX + buf * kKeys;
                 // N-major B without swizzle: lbo = bytes between groups of 8 keys, sbo = bytes between blocks of 8 columns
-                const uint64_t dv = make_desc(smem_u32(v_16 + (t % kStages) * C::kV16Stage), 32 * D, 128, 0);
+                const uint64_t dv = make_desc(smem_u32(v_16 + (t % VST) * C::kV16Stage), 32 * D, 128, 0);
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)  // 16 keys = 8 TMEM columns of packed fp16 = two key groups of V
                     if (elect_one()) mma_h_ts(tmem + kColO, a0 + (uint32_t)(32 * (k >> 1) + 8 * (k & 1)), dv + (uint64_t)(k * 4 * D), id_pv_a, (t == 0 && k == 0) ? 0u : 1u);
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)
                     if (elect_one()) mma_h_ts(tmem + kColO + D, a0 + (uint32_t)(32 * (k >> 1) + 8 * (k & 1) + 16), dv + (uint64_t)(k * 4 * D), id_pv_b, 1u);
-                if (elect_one()) tc_commit(&o_done[t % kStages]);    // O is up to date; the V warps may rewrite this stage, Q K^T this buffer
+                if (elect_one()) tc_commit(&o_done[t % VST]);        // O is up to date; this V stage may be refilled, Q K^T may take the buffer
+                // P V(t-1) was issued a whole step ago: its stage takes V(t-1+VST)
+                if (t >= 1) {
+                    wait(&o_done[(t - 1) % VST], phn(t - 1, VST), 8);
+                    copy_v(t - 1 + VST);
+                }
             }
         }
         __syncwarp();
         tc_fence_before();
         __syncthreads();                             // the workers have read the output
-        if (qk_role) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
-        return;
-    }
-
-    // ================= the converting warps ===========================================================
-    // A raw fp32 tile lands in a slot by TMA; a thread reads its own 32-byte pieces (8 floats of pairs of adjacent
-    // rows), cuts them into hi and lo and writes the fp16 operand stage.  The stage of tile u was read by the product
-    // of tile u - 3.
-    if (warp > kWorkers / 32 + 1 && warp <= kWorkers / 32 + 1 + PWK) {
-        const PieceMap<32 * PWK, PPR> pm(tid - kWorkers - 64);
-        constexpr int NPC = pm.NPC, BATCH = pm.BATCH;
-        const int pc = pm.pc, pblk = pm.pblk, pch = pm.pch;
-        float amax = 0.0f;
-        __syncthreads();                             // matches the block-wide barrier after Q staging
-        for (int u = 0; u < nk; ++u) {
-            const uint8_t *raw = k_raw + (u % NRAW) * C::kRawSlot + pblk * kKBlk;
-            uint8_t *k16 = k_16 + (u % kStages) * C::kK16Stage;
-            wait(&k_land[u % NRAW], (uint32_t)((u / NRAW) & 1), 9);              // the raw tile has landed
-            if (u >= kStages) wait(&s_full[u % kStages], ph3(u - kStages), 7);   // Q K(u-3)^T has completed
-#pragma unroll
-            for (int half = 0; half < NPC / BATCH; ++half) {
-                float4 a[BATCH], c[BATCH];
-#pragma unroll
-                for (int i = 0; i < BATCH; ++i) {
-                    const int r = pm.row(half * BATCH + i);
-                    a[i] = *reinterpret_cast<const float4 *>(raw + sw128(r, pch));
-                    c[i] = *reinterpret_cast<const float4 *>(raw + sw128(r, pch + 1));
-                }
-#pragma unroll
-                for (int i = 0; i < BATCH; ++i) {
-                    const int r = pm.row(half * BATCH + i);
-                    const float4 ah = hi4(a[i]), ch = hi4(c[i]);
-                    amax = amax8(amax, a[i], c[i]);
-                    *reinterpret_cast<uint4 *>(k16 + off16(r, pc, kKBlk)) =
-                        make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
-                    *reinterpret_cast<uint4 *>(k16 + off16(r, PPR + pc, kKBlk)) =
-                        make_uint4(pack_f16(a[i].x - ah.x, a[i].y - ah.y), pack_f16(a[i].z - ah.z, a[i].w - ah.w),
-                                   pack_f16(c[i].x - ch.x, c[i].y - ch.y), pack_f16(c[i].z - ch.z, c[i].w - ch.w));
-                }
-            }
-            proxy_fence();                           // generic-proxy writes -> visible to the tensor core
-            arrive(&k_full[u % kStages]);
-        }
-        publish_amax(&s_amax[1], amax);
-        __syncthreads();
-        return;
-    }
-    if (warp > kWorkers / 32 + 1 + PWK) {
-        const PieceMap<32 * PWV, PPR> pm(tid - kWorkers - 64 - 32 * PWK);
-        constexpr int NPC = pm.NPC, BATCH = pm.BATCH;
-        const int pc = pm.pc, pblk = pm.pblk, pch = pm.pch;
-        float amax = 0.0f;
-        __syncthreads();
-        for (int u = 0; u < nt; ++u) {
-            const uint8_t *raw = v_raw + (u % NRAW) * C::kRawSlot + pblk * kKBlk;
-            uint8_t *v16 = v_16 + (u % kStages) * C::kV16Stage;
-            wait(&v_land[u % NRAW], (uint32_t)((u / NRAW) & 1), 10);             // the raw tile has landed
-            if (u >= kStages) wait(&o_done[u % kStages], ph3(u - kStages), 8);   // P V(u-3) has completed
-#pragma unroll
-            for (int half = 0; half < NPC / BATCH; ++half) {
-                float4 a[BATCH], c[BATCH];
-#pragma unroll
-                for (int i = 0; i < BATCH; ++i) {
-                    const int r = pm.row(half * BATCH + i);
-                    a[i] = *reinterpret_cast<const float4 *>(raw + sw128(r, pch));
-                    c[i] = *reinterpret_cast<const float4 *>(raw + sw128(r, pch + 1));
-                }
-#pragma unroll
-                for (int i = 0; i < BATCH; ++i) {
-                    const int r = pm.row(half * BATCH + i);
-                    const float4 ah = hi4(a[i]), ch = hi4(c[i]);
-                    amax = amax8(amax, a[i], c[i]);
-                    // key r, columns 8 pc ..: V_hi in column block pc, V_lo in column block D / 8 + pc
-                    uint8_t *dst = v16 + (r >> 3) * (32 * D) + (r & 7) * 16;
-                    *reinterpret_cast<uint4 *>(dst + pc * 128) =
-                        make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
-                    *reinterpret_cast<uint4 *>(dst + (PPR + pc) * 128) =
-                        make_uint4(pack_f16(a[i].x - ah.x, a[i].y - ah.y), pack_f16(a[i].z - ah.z, a[i].w - ah.w),
-                                   pack_f16(c[i].x - ch.x, c[i].y - ch.y), pack_f16(c[i].z - ch.z, c[i].w - ch.w));
-                }
-            }
-            proxy_fence();
-            arrive(&v_full[u % kStages]);
-        }
-        publish_amax(&s_amax[2], amax);
-        __syncthreads();
+        if (qk_role) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
         return;
     }
 
@@ -414,26 +396,40 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     const int wq = warp;                             // TMEM lane quadrant of this warp
     const int rloc = wq * 32 + lane;                 // row inside the block = TMEM lane
     const int row = q0 + rloc;
+    // The worker stages its own query row: times the softmax scale (scores come out in the log2 domain) and times a
+    // power of two of its own that brings the row's largest magnitude near 2^14; what the scores then carry too much
+    // (the row's factor and K's per-head factor) is taken out again by `sfac` below, inside the exponent's multiply-add.
+    float sfac;
     {
-        float amax = 0.0f;
         const bool ok = row < S;
         const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
+        float amax = 0.0f;
 #pragma unroll
-        for (int j = 0; j < PPR; ++j) {              // 8 floats at a time
+        for (int j = 0; j < 2 * PPR; ++j) {
+            const float4 a = ok ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+        }
+        const float sq = range_scale(amax * qscale);
+        const float qs = qscale * sq;
+        sfac = 1.0f / sq;                            // a power of two: exact
+#pragma unroll
+        for (int j = 0; j < PPR; ++j) {              // 8 floats at a time (the row is read again: it is in L1)
             float4 a = ok ? __ldg(src + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 c = ok ? __ldg(src + 2 * j + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
-            a.x *= qscale; a.y *= qscale; a.z *= qscale; a.w *= qscale;     // scores come out in the log2 domain
-            c.x *= qscale; c.y *= qscale; c.z *= qscale; c.w *= qscale;
+            a.x *= qs; a.y *= qs; a.z *= qs; a.w *= qs;
+            c.x *= qs; c.y *= qs; c.z *= qs; c.w *= qs;
             const float4 ah = hi4(a), ch = hi4(c);
-            amax = amax8(amax, a, c);
             *reinterpret_cast<uint4 *>(q_16 + off16(rloc, j, kQBlk)) =
                 make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
             *reinterpret_cast<uint4 *>(q_16 + off16(rloc, PPR + j, kQBlk)) =
                 make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
                            pack_f16(c.x - ch.x, c.y - ch.y), pack_f16(c.z - ch.z, c.w - ch.w));
         }
-        publish_amax(&s_amax[0], amax);
     }
+    // V's tiles carry factors of their own; P(t) is made smaller by tile t's factor over the head's smallest one (that of
+    // the head's largest |V|), which leaves with the output
+    const float vhs = range_scale(hmax[bh]), vinv = 1.0f / vhs;
+    const float *tmax_k = tmax + (size_t)bh * ntk, *tmax_v = tmax + ntiles + (size_t)bh * ntk;
     proxy_fence();
     tc_fence_before();
     __syncthreads();
@@ -446,7 +442,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
         const int buf = t % kBufs;
         const int j0 = t * kKeys;
         const uint32_t s_addr = lane_base + kColX + buf * kKeys;
-        wait(&s_full[t % kStages], ph3(t), 1);       // S(t) is in TMEM
+        wait(&s_full[t % KST], phn(t, KST), 1);      // S(t) is in TMEM
         tc_fence_after();
         const int wrow0 = q0 + wq * 32;              // first row of this warp
         // columns of this tile that the row sees; the warp's last row sees the most, its first row the fewest
@@ -465,6 +461,8 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             tmem_wait_ld();
             mx = fmaxf(mx, chunk_max(v, c * 32, nvalid, c * 32 + 32 > nmin));
         }
+        const float tfac = sfac / range_scale(__ldg(tmax_k + t));   // what this tile's scores carry too much: the row's and the tile's factors
+        mx *= tfac;                                  // the row's largest true score (tfac > 0)
         if (t == 0) {
             m_ref = fmaxf(mx, -1e30f);
         } else {
@@ -475,7 +473,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
                 const float alpha = grow ? ex2_approx(m_ref - mx) : 1.0f;
                 if (grow) m_ref = mx;
                 l *= alpha;
-                wait(&o_done[(t - 1) % kStages], ph3(t - 1), 2);     // P V(t-1) has completed
+                wait(&o_done[(t - 1) % VST], phn(t - 1, VST), 2);    // P V(t-1) has completed
                 tc_fence_after();
 #pragma unroll 1
                 for (int hh = 0; hh < (2 * D) / 16; ++hh) {
@@ -490,13 +488,14 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
         }
 
         // ---- second sweep: exponentials; P_hi and P_lo over S in place ---------------------------------
-        const float nm = kPShift - m_ref;
+        const float vrel = fminf(vhs / range_scale(__ldg(tmax_v + t)), 1.0f);   // <= 1: this V tile's factor against the head's (a tile of zeros: 1)
+        const float nm = kPShift - m_ref + log2_of_pow2(vrel);
         float psum = 0.0f;
 #pragma unroll 1
         for (int c = 0; c < nch; ++c) {
             tmem_ld32(s_addr + c * 32, v);
             tmem_wait_ld();
-            psum += chunk_exp(v, s_addr + c * 32, c * 32, nvalid, c * 32 + 32 > nmin, nm);
+            psum += chunk_exp(v, s_addr + c * 32, c * 32, nvalid, c * 32 + 32 > nmin, tfac, nm);
         }
 #pragma unroll 1
         for (int c = nch; c < kKeys / 32; ++c) {     // chunks that no row of this warp sees
@@ -506,16 +505,17 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             tmem_st16_u32(s_addr + c * 32, z);
             tmem_st16_u32(s_addr + c * 32 + 16, z);
         }
-        l += psum;
+        l += psum / vrel;                            // the row sum counts the probabilities themselves (a power of two: exact)
         tmem_wait_st();
         tc_fence_before();
         arrive(&p_full[buf]);
     }
 
     {
-        wait(&o_done[(nt - 1) % kStages], ph3(nt - 1), 3);
+        wait(&o_done[(nt - 1) % VST], phn(nt - 1, VST), 3);
         tc_fence_after();
-        const float inv = 1.0f / fmaxf(l, 1e-20f);
+        const float linv = 1.0f / fmaxf(l, 1e-20f);  // for the probabilities
+        const float inv = linv * vinv;
         const bool store = !abort_flag && row < S;
         float4 *dst = reinterpret_cast<float4 *>(O + (tok0 + (row < S ? row : 0)) * (size_t)E + hcol);
 #pragma unroll 1
@@ -542,8 +542,9 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             const bool vec = (S & 3) == 0;               // then every 4-column group of a row is 16-byte aligned
             for (int u = nt; u < nk; ++u) {
                 const int buf = u % kBufs, j0 = (u - nt) * kKeys;
+                const float tfac2 = sfac / range_scale(__ldg(tmax_k + (u - nt)));
                 const uint32_t s_addr = lane_base + kColX + buf * kKeys;
-                wait(&s_full[u % kStages], ph3(u), 1);
+                wait(&s_full[u % KST], phn(u, KST), 1);
                 tc_fence_after();
                 const bool warp_dead = CAUSAL && j0 > wrow0 + 31;
                 const int ncols = min(kKeys, S - j0);                                   // columns of this tile that exist
@@ -566,7 +567,7 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
                     for (int i = 0; i < 4; ++i) {
                         const int c = 4 * c4 + i;
                         const float sc = c < 32 ? v0[c & 31] : v1[c & 31];
-                        o[i] = c < nvalid ? ex2_approx(sc - m_ref + kPShift) * inv : 0.0f;
+                        o[i] = c < nvalid ? ex2_approx(fmaf(sc, tfac2, kPShift - m_ref)) * linv : 0.0f;
                     }
                     *reinterpret_cast<float4 *>(tb + lane * 256 + ((c4 ^ (lane & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
                 }
@@ -606,46 +607,98 @@ mha_tc16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) {
-        // Range of the fp16 pieces: beyond fp16's largest number they saturate; below its smallest normal numbers a
-        // lo part is flushed, an absolute error of up to 2^-25 per fp16 value, which matters when it is neither small
-        // in itself nor small beside the scores it is added to.  (Q carries the softmax scale here.)
-        const float aq = __uint_as_float(s_amax[0]), ak = __uint_as_float(s_amax[1]), av = __uint_as_float(s_amax[2]);
-        const bool over = !(aq <= 65504.0f) || !(ak <= 65504.0f) || !(av <= 65504.0f);
-        const float flush = (float)D * 2.98e-8f * (aq + ak);
-        if (over || (flush > 3.8e-6f && (aq + ak) > 8.0f * aq * ak)) atomicOr(&g_tc16_notice, 1);
-    }
 }
+
+// The packed operands of a call live in a buffer of the library, one per device and stream (a call's kernels read it
+// after the call has returned; calls on different streams must not share it).  It grows to the largest call.
+struct PackScratch {
+    std::mutex mu;
+    struct Entry { int dev; cudaStream_t st; uint8_t *buf; size_t cap; };
+    std::vector<Entry> entries;
+    int get(int dev, cudaStream_t st, size_t need, uint8_t **out)
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        Entry *e = nullptr;
+        for (auto &x : entries) if (x.dev == dev && x.st == st) e = &x;
+        if (!e) { entries.push_back({dev, st, nullptr, 0}); e = &entries.back(); }
+        if (e->cap < need) {
+            if (e->buf) cudaFree(e->buf);        // waits for the kernels that read it
+            e->buf = nullptr;
+            e->cap = 0;
+            const cudaError_t err = cudaMalloc(&e->buf, need);
+            if (err != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMalloc(%zu) for the packed K and V: %s", need, cudaGetErrorString(err));
+            e->cap = need;
+        }
+        *out = e->buf;
+        return HIPGPT_OK;
+    }
+    void release()
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (auto &x : entries) if (x.buf) cudaFree(x.buf);
+        entries.clear();
+    }
+};
+PackScratch g_pack;
 
 template <int D, bool CAUSAL, bool PROBS>
 int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, float *probs, int B, int S, int E, int H, cudaStream_t st)
 {
     using C = Tc16Cfg<D>;
     auto kern = mha_tc16_kernel<D, CAUSAL, PROBS>;
-    // two blocks per SM (256 TMEM columns each): at least 100 KB, so that a third block never shares the SM;
-    // one block per SM (512 columns): more than half of the SM's shared memory
+    // two blocks per SM (256 TMEM columns each): at least 100 KB, so that a third block never shares the SM
     size_t smem = C::kSmemBytes + 1024;
-    if (C::BLOCKS_PER_SM == 2 && smem < 100 * 1024) smem = 100 * 1024;
-    if (C::BLOCKS_PER_SM == 1 && smem < 120 * 1024) smem = 120 * 1024;
+    if (smem < 100 * 1024) smem = 100 * 1024;
     static_assert(C::kSmemBytes + 1024 + 2048 <= 232448 / C::BLOCKS_PER_SM, "shared memory of a block");
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     const int nqblk = (S + kRows - 1) / kRows;
-    const long long blocks = (long long)B * H * nqblk;
-    if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
-    const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    // raw tiles land as rows of 128 bytes with the 128-byte swizzle; the converting threads read them back the same way
-    CUtensorMap kmap, vmap;
-    int rc = tma_plane_map(&kmap, k, B, S, E, kKeys, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc == HIPGPT_OK) rc = tma_plane_map(&vmap, v, B, S, E, kKeys, CU_TENSOR_MAP_SWIZZLE_128B);
+    const int ntk = (S + kKeys - 1) / kKeys;
+    // The call is cut into groups of batches whose packed K and V (as many bytes as the fp32 K and V) stay in L2
+    // between the kernel that writes them and the kernel that reads them; the scratch buffer is one group's size.
+    const size_t per_batch = (size_t)H * ntk * (C::kK16Stage + C::kV16Stage);
+    size_t group_bytes = 96u << 20;
+    if (const char *env = getenv("HIPGPT_PACK_GROUP_MB")) { const long v = atol(env); if (v > 0) group_bytes = (size_t)v << 20; }
+    long long gb = (long long)(group_bytes / per_batch);
+    if (gb < 1) gb = 1;
+    if (gb > B) gb = B;
+    while (gb * H > 65535) --gb;                     // grid.y of the pack kernel
+    if (gb < 1) return fail(HIPGPT_ERR_BAD_ARG, "%d heads are too many", H);
+    if (gb * H * (long long)nqblk > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", gb * H * (long long)nqblk);
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    const size_t kbytes = (size_t)gb * H * ntk * C::kK16Stage, vbytes = (size_t)gb * H * ntk * C::kV16Stage;
+    uint8_t *scratch = nullptr;
+    const size_t gtiles = (size_t)gb * H * ntk;
+    int rc = g_pack.get(dev, st, kbytes + vbytes + (2 * gtiles + (size_t)gb * H) * sizeof(float), &scratch);
     if (rc != HIPGPT_OK) return rc;
-    kern<<<(unsigned)blocks, C::THREADS, smem, st>>>(kmap, vmap, q, out, probs, S, E, H, B * H, nqblk, qscale);
-    return check_launch("mha_tc16_kernel");
+    float *tmax = reinterpret_cast<float *>(scratch + kbytes + vbytes);      // [2][group's tiles]: largest |K|, |V| of every tile
+    float *hmax = tmax + 2 * gtiles;                                         // [group's (batch, head) pairs]: largest |V|
+    const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
+    for (long long b0 = 0; b0 < B; b0 += gb) {
+        const int nb = (int)(B - b0 < gb ? B - b0 : gb);
+        const size_t off = (size_t)b0 * S * E;       // the group's first token in every plane and in the output
+        e = cudaMemsetAsync(hmax, 0, (size_t)nb * H * sizeof(float), st);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+        const int ntiles = nb * H * ntk;
+        kv_pack_kernel<D><<<dim3((unsigned)ntk, (unsigned)(nb * H)), kPackThreads, 0, st>>>(k + off, v + off, tmax, hmax, scratch, scratch + kbytes, S, E, H, ntk, ntiles);
+        rc = check_launch("kv_pack_kernel");
+        if (rc != HIPGPT_OK) return rc;
+        kern<<<(unsigned)(nb * H * nqblk), C::THREADS, smem, st>>>(scratch, scratch + kbytes, tmax, hmax, ntiles, q + off, out + off,
+                                                                   probs ? probs + (size_t)b0 * H * S * S : nullptr, S, E, H, nb * H, nqblk, ntk, qscale);
+        rc = check_launch("mha_tc16_kernel");
+        if (rc != HIPGPT_OK) return rc;
+    }
+    return HIPGPT_OK;
 }
 
 }  // namespace
 
 bool mha_tc16_supports(int head_dim) { return head_dim == 32 || head_dim == 64; }
+
+// Frees the packed-operand buffers (hipgpt_release_workspace).
+void tc16_release_scratch() { g_pack.release(); }
 
 // `probs` (optional): [B][H][S][S], written by a second sweep over the key tiles
 int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, float *probs,

@@ -312,6 +312,7 @@ int hipgpt_mha_forward_bf16_host(const void *h_qkv, void *h_out, int B, int S, i
 
 void hipgpt_release_workspace(void)
 {
+    tc16_release_scratch();
     std::lock_guard<std::mutex> lock(g_ws.mu);
     if (g_ws.dev) cudaFree(g_ws.dev);
     for (int i = 0; i < Workspace::kStreams; ++i) if (g_ws.streams[i]) { cudaStreamDestroy(g_ws.streams[i]); g_ws.streams[i] = nullptr; }

@@ -73,6 +73,13 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tensor_m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
 }
 
+// Plain bulk copy global -> shared (both 16-byte aligned, a multiple of 16 bytes), completion counted on the mbarrier.
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // Asks L2 for one box of a rank-3 tensor map; nothing is written to shared memory and nothing signals completion.
 __device__ __forceinline__ void tma_prefetch_3d(const void *tensor_map, int c0, int c1, int c2)
 {
