@@ -46,9 +46,7 @@ from hipgpt_b200 import synth  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture that the named summary under
 # profiles/ records: (workload, kernel) -> (bytes, summary).  A kernel without a capture of its own reports null.
-TRAFFIC = {("c2", "mha_head_kernel"): (25.25e6, "profiles/mha_head_kernel_c2_causal.md"),
-           ("c2", "mha_tc16_kernel"): (25.23e6, "profiles/mha_tc16_kernel_c2_causal.md"),
-           ("c3", "mha_tc16_kernel"): (130.6e6, "profiles/mha_tc16_kernel_c3_causal.md")}
+TRAFFIC = {("c2", "mha_head_kernel"): (25.25e6, "profiles/mha_head_kernel_c2_causal.md")}
 FALLBACK_HBM_GBS = 6650.0
 # --kernel: name -> (algo, tensor-kernel selector) of hipgpt_mha_forward_ex, and the kernel's name in a launch list
 KERNELS = {"auto": None, "whole_head": (3, 6, "mha_head_kernel"), "tiled": (3, 5, "mha_tc16_kernel"),
@@ -57,6 +55,14 @@ KERNELS = {"auto": None, "whole_head": (3, 6, "mha_head_kernel"), "tiled": (3, 5
 
 def flops_of(B, H, S, D, causal):
     return 2.0 * B * H * D * S * (S + 1) if causal else 4.0 * B * H * float(S) * S * D
+
+
+def tiled_launches(B, H, S, D):
+    """Kernels one call of the tiled fp32 kernel launches: the library cuts the batches into groups whose packed K
+    and V (as many bytes as the fp32 K and V) stay below 96 MB, and runs a pack kernel and an attention kernel per group."""
+    per_batch = H * ((S + 63) // 64) * 64 * 2 * D * 2 * 2
+    gb = max(1, min(B, (96 << 20) // per_batch))
+    return 2 * ((B + gb - 1) // gb)
 
 
 def bytes_of(B, H, S, D, probs):
@@ -83,7 +89,7 @@ def parse():
     ap.add_argument("--no-scaling", action="store_true", help="skip the C5 sharded leg (key scaling_c5)")
     ap.add_argument("--kernel", default="auto", choices=sorted(KERNELS),
                     help="fp32 attention kernel: auto is what hipgpt_mha_forward picks; the others go through hipgpt_mha_forward_ex")
-    ap.add_argument("--bf16-variant", type=int, default=0, help="--dtype bf16: 0 default, 1 one worker per query row, 2 two workers, 3 two workers and 128-key tiles")
+    ap.add_argument("--bf16-variant", type=int, default=0, help="--dtype bf16: passed to hipgpt_mha_forward_bf16_ex (0, 1, 2 run the same kernel)")
     return ap.parse_args()
 
 
@@ -477,7 +483,11 @@ def run_ours(args):
     # tensor work per fp32 product, in TF32 products: the default kernel runs one TF32 product and two FP16
     # products (twice the TF32 rate); 3 would be the figure of the split-TF32 variant
     tc16 = tensor_kernel and not bf16
-    tf32_products = (2.0 if (tc16 and args.kernel != "split_tf32") else 3.0) * (1.5 if args.probs else 1.0)
+    # tensor work per fp32 product in TF32-rate products: whole-head kernel one TF32 + two FP16 products for Q K^T
+    # (2) and three FP16 products for P V (1.5); tiled kernel three FP16 products for both (1.5); split-TF32 three
+    whole_head = (KERNELS[args.kernel][2] == "mha_head_kernel") if KERNELS[args.kernel] else (D == 32 and S <= 256)
+    tiled = tc16 and not whole_head and args.kernel in ("auto", "tiled")
+    tf32_products = (1.5 if tiled else 1.75 if (tc16 and whole_head) else 3.0) * (1.5 if (args.probs and tiled) else 1.0)
     t_pipe = (flops_launch / (bf16_peak * 1e12)) if bf16 else (tf32_products * flops_launch / (tf32_peak * 1e12)) if tensor_kernel else flops_launch / (fma_peak * 1e12)
     src = "measured" if peaks else "fallback"
     if bf16 and t_hbm < t_pipe:
@@ -499,7 +509,8 @@ def run_ours(args):
               "mha_tc16_kernel" if tensor_kernel else "mha_rows_kernel" if D == 128 else "mha_generic_kernel")
     traffic = TRAFFIC.get((args.workload, kernel)) if (args.causal and not args.probs and not bf16) else None
     roofline.update({"kernel": kernel, "traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None,
-                     "us_per_launch": launch_ms * 1e3, "algorithmic_bytes_per_launch": per_batch_bytes,
+                     "us_per_launch": launch_ms * 1e3, "kernels_per_launch": tiled_launches(B, H, S, D) if tiled else 1,
+                     "algorithmic_bytes_per_launch": per_batch_bytes,
                      "algorithmic_flops_per_launch": flops_launch,
                      "vs_fp32_fma_ceiling": {"achieved_tflops": achieved, "ffma_peak_tflops": fma_peak, "ratio": achieved / fma_peak,
                                              "note": "fp32-grade result rate against the FFMA pipe ceiling measured in this run"},
@@ -513,7 +524,7 @@ def run_ours(args):
                        "l2": f"{sets} distinct input batches per step, {sets * per_batch_bytes / 1e6:.0f} MB > 126 MB L2",
                        "parallelism": f"batch-major shards x{world}" + (", NCCL all-gather of outputs in chunks, overlapped" if args.gather else ", no collective")},
             "clocks": clocks.summary(), "roofline": roofline,
-            "gpu_launches": args.steps * sets}
+            "gpu_launches": args.steps * sets * (tiled_launches(B, H, S, D) if tiled else 1)}
 
     # the scaling configuration through the library's sharded driver (every N, the default workload only)
     if args.workload == "c2" and not args.no_scaling and not bf16:

@@ -104,9 +104,8 @@ HIPGPT_API int hipgpt_mha_forward_planes(const float *d_qkv, float *d_out, float
  */
 HIPGPT_API int hipgpt_mha_forward_bf16(const void *d_q, const void *d_k, const void *d_v, void *d_out,
                             int B, int S, int E, int H, int causal, void *stream);
-/* The same with the kernel's schedule exposed: variant 0 = the default, 1 = one worker thread per query
- * row (it owns the 64 scores of a tile), 2 = two worker threads per query row (32 scores each; twice the
- * warps per SM).  Same results to the stated tolerance; the row sums differ in summation order. */
+/* The same call with a `variant` argument that earlier versions used to choose between schedules of the
+ * kernel.  There is one schedule now: 0, 1 and 2 are accepted and run it, anything else is refused. */
 HIPGPT_API int hipgpt_mha_forward_bf16_ex(const void *d_q, const void *d_k, const void *d_v, void *d_out,
                                int B, int S, int E, int H, int causal, int variant, void *stream);
 

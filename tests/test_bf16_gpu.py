@@ -38,7 +38,7 @@ SHAPES = [(1, 1, 1, 64), (2, 2, 7, 64), (1, 2, 64, 64), (1, 1, 128, 64), (1, 3, 
 
 @pytest.mark.parametrize("shape", SHAPES)
 @pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("variant", [1, 2])       # one or two worker threads per query row
+@pytest.mark.parametrize("variant", [0, 2])       # the `variant` argument is accepted (0, 1, 2) and ignored
 def test_bf16_kernel_matches_oracle(shape, causal, variant):
     B, H, S, D = shape
     E = H * D
