@@ -74,28 +74,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
     return r;
 }
 
-// Two fp32 operations in one instruction (sm_100 has fused multiply-add and add on pairs of registers), and the
-// three-input maximum.  (A cubic on the FMA pipe for a share of the exponentials, to relieve the special-function
-// unit, was measured too: +3 % at S = 1024, -2 % at S = 2048, not kept.)
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c)
-{
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<const uint64_t *>(&a)), "l"(*reinterpret_cast<const uint64_t *>(&b)), "l"(*reinterpret_cast<const uint64_t *>(&c)));
-    return *reinterpret_cast<float2 *>(&d);
-}
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b)
-{
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<const uint64_t *>(&a)), "l"(*reinterpret_cast<const uint64_t *>(&b)));
-    return *reinterpret_cast<float2 *>(&d);
-}
-__device__ __forceinline__ float max3(float a, float b, float c)
-{
-    float r;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-
+// (A cubic on the FMA pipe for a share of the exponentials, to relieve the special-function unit, was measured:
+// +3 % at S = 1024, -2 % at S = 2048, not kept.)
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 

@@ -78,9 +78,9 @@ __device__ __forceinline__ float chunk_max(float (&v)[32], int col0, int nvalid,
     }
     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-        m4[0] = fmaxf(m4[0], v[j]); m4[1] = fmaxf(m4[1], v[j + 1]);
-        m4[2] = fmaxf(m4[2], v[j + 2]); m4[3] = fmaxf(m4[3], v[j + 3]);
+    for (int j = 0; j < 32; j += 8) {
+        m4[0] = max3(m4[0], v[j], v[j + 1]); m4[1] = max3(m4[1], v[j + 2], v[j + 3]);
+        m4[2] = max3(m4[2], v[j + 4], v[j + 5]); m4[3] = max3(m4[3], v[j + 6], v[j + 7]);
     }
     return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
 }
@@ -94,24 +94,26 @@ __device__ __forceinline__ float chunk_exp(float (&v)[32], uint32_t addr, int co
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (col0 + j < nvalid) ? v[j] : -INFINITY;
     }
-    float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // pairs of values per instruction where the hardware has one (multiply-add, add)
+    float2 ps[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+    const float2 cs2 = make_float2(cscale, cscale), nm2 = make_float2(nmc, nmc);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         uint32_t hi[8], lo[8];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
-            const float s0 = v[16 * half + j], s1 = v[16 * half + j + 1];
-            const float p0 = ex2_approx(fmaf(s0, cscale, nmc)), p1 = ex2_approx(fmaf(s1, cscale, nmc));
-            ps[j & 3] += p0;
-            ps[(j + 1) & 3] += p1;
-            const float h0 = tf32_hi(p0), h1 = tf32_hi(p1);      // 11 leading bits: exact in fp16
-            hi[j >> 1] = pack_f16(h0, h1);
-            lo[j >> 1] = pack_f16(p0 - h0, p1 - h1);
+            const float2 x = ffma2(make_float2(v[16 * half + j], v[16 * half + j + 1]), cs2, nm2);
+            const float2 p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            ps[(j >> 1) & 1] = fadd2(ps[(j >> 1) & 1], p);
+            const float2 h = make_float2(tf32_hi(p.x), tf32_hi(p.y));            // 11 leading bits: exact in fp16
+            const float2 l = fadd2(p, make_float2(-h.x, -h.y));
+            hi[j >> 1] = pack_f16(h.x, h.y);
+            lo[j >> 1] = pack_f16(l.x, l.y);
         }
         tmem_st8_u32(addr + 8 * half, hi);
         tmem_st8_u32(addr + 16 + 8 * half, lo);
     }
-    return (ps[0] + ps[1]) + (ps[2] + ps[3]);
+    return (ps[0].x + ps[0].y) + (ps[1].x + ps[1].y);
 }
 
 __device__ __forceinline__ void chunk_zero(uint32_t addr)

@@ -253,6 +253,27 @@ __device__ __forceinline__ void tmem_st8_u32(uint32_t addr, const uint32_t (&v)[
 
 __device__ __forceinline__ float4 hi4(float4 x) { return make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w)); }
 
+// Two fp32 operations in one instruction (sm_100 has fused multiply-add and add on pairs of registers), and the
+// three-input maximum: the softmax sweeps are bound by the instructions they issue.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<const uint64_t *>(&a)), "l"(*reinterpret_cast<const uint64_t *>(&b)), "l"(*reinterpret_cast<const uint64_t *>(&c)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<const uint64_t *>(&a)), "l"(*reinterpret_cast<const uint64_t *>(&b)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // byte offset of 16-byte chunk c of row r in a tile of 128-byte rows, SWIZZLE_128B
 __device__ __forceinline__ int sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
 
