@@ -90,39 +90,46 @@ __device__ __forceinline__ float chunk_max(float (&v)[32], int col0, int nvalid,
     }
     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-        m4[0] = fmaxf(m4[0], v[j]); m4[1] = fmaxf(m4[1], v[j + 1]);
-        m4[2] = fmaxf(m4[2], v[j + 2]); m4[3] = fmaxf(m4[3], v[j + 3]);
+    for (int j = 0; j < 32; j += 8) {
+        m4[0] = max3(m4[0], v[j], v[j + 1]); m4[1] = max3(m4[1], v[j + 2], v[j + 3]);
+        m4[2] = max3(m4[2], v[j + 4], v[j + 5]); m4[3] = max3(m4[3], v[j + 6], v[j + 7]);
     }
     return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
 }
 
-// One chunk of scores (log2 domain, times 1 / sfac) -> P = 2^(s sfac + nm), cut into fp16 hi and lo, written over the chunk's own 32 TMEM
-// columns (16 of packed P_hi, then 16 of packed P_lo).  Returns the sum of P.
-__device__ __forceinline__ float chunk_exp(float (&v)[32], uint32_t addr, int col0, int nvalid, bool need_mask, float sfac, float nm)
+// One chunk of scores (log2 domain, times 1 / sfac; hidden ones are -inf: their exponential is exactly 0) -> P = 2^(s sfac + nm),
+// cut into fp16 hi and lo, written over the chunk's own 32 TMEM columns (16 of packed P_hi, then 16 of packed P_lo).
+// Returns the sum of P.
+__device__ __forceinline__ float chunk_exp(const float (&v)[32], uint32_t addr, float sfac, float nm)
 {
-    if (need_mask) {
-        // a hidden score becomes -inf: its exponential is exactly 0
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = (col0 + j < nvalid) ? v[j] : -INFINITY;
-    }
-    float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float2 ps[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+    const float2 sf2 = make_float2(sfac, sfac), nm2 = make_float2(nm, nm);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         uint32_t hi[8], lo[8];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
-            const float p0 = ex2_approx(fmaf(v[16 * half + j], sfac, nm)), p1 = ex2_approx(fmaf(v[16 * half + j + 1], sfac, nm));
-            ps[j & 3] += p0;
-            ps[(j + 1) & 3] += p1;
-            const float h0 = tf32_hi(p0), h1 = tf32_hi(p1);      // 11 leading bits: exact in fp16
-            hi[j >> 1] = pack_f16(h0, h1);
-            lo[j >> 1] = pack_f16(p0 - h0, p1 - h1);
+            const float2 x = ffma2(make_float2(v[16 * half + j], v[16 * half + j + 1]), sf2, nm2);
+            const float2 p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            ps[(j >> 1) & 1] = fadd2(ps[(j >> 1) & 1], p);
+            const float2 h = make_float2(tf32_hi(p.x), tf32_hi(p.y));            // 11 leading bits: exact in fp16
+            const float2 l = fadd2(p, make_float2(-h.x, -h.y));
+            hi[j >> 1] = pack_f16(h.x, h.y);
+            lo[j >> 1] = pack_f16(l.x, l.y);
         }
         tmem_st8_u32(addr + 8 * half, hi);
         tmem_st8_u32(addr + 16 + 8 * half, lo);
     }
-    return (ps[0] + ps[1]) + (ps[2] + ps[3]);
+    return (ps[0].x + ps[0].y) + (ps[1].x + ps[1].y);
+}
+
+__device__ __forceinline__ void tmem_zero32(uint32_t addr)
+{
+    uint32_t z[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) z[j] = 0u;
+    tmem_st16_u32(addr, z);
+    tmem_st16_u32(addr + 16, z);
 }
 
 // The power of two that brings a largest magnitude `amax` into [2^14, 2^15): fp16 then holds the 11 leading bits of
@@ -239,6 +246,7 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
     __shared__ uint64_t k_full[KST], v_full[VST], s_full[KST], o_done[VST], p_full[kBufs];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
+    __shared__ float q_sfac[kRows];                  // per query row: one over the power of two that its staged copy carries
 
     const int tid = threadIdx.x, lane = tid & 31;
     // read from one lane, so that the compiler knows the warp's number (and every role that follows from it) to be warp-uniform
@@ -396,35 +404,47 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
     const int wq = warp;                             // TMEM lane quadrant of this warp
     const int rloc = wq * 32 + lane;                 // row inside the block = TMEM lane
     const int row = q0 + rloc;
-    // The worker stages its own query row: times the softmax scale (scores come out in the log2 domain) and times a
-    // power of two of its own that brings the row's largest magnitude near 2^14; what the scores then carry too much
-    // (the row's factor and K's per-head factor) is taken out again by `sfac` below, inside the exponent's multiply-add.
+    // The warp stages its 32 query rows: times the softmax scale (scores come out in the log2 domain) and times a power of
+    // two per row that brings the row's largest magnitude near 2^14; what the scores then carry too much (the row's factor
+    // and K's per-tile factor) is taken out again by `sfac` below, inside the exponent's multiply-add.  D / 4 lanes read
+    // one row (whole 128-byte lines per request; a thread reading its own row would touch 32 lines per instruction, twice,
+    // and cost the block ~9000 cycles before its first product), all loads in flight at once.
     float sfac;
     {
-        const bool ok = row < S;
-        const float4 *src = reinterpret_cast<const float4 *>(Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol);
-        float amax = 0.0f;
+        constexpr int LPR = D / 4, RPI = 32 / LPR, NI = 32 / RPI;      // lanes per row, rows per instruction, instructions
+        const int c4 = lane % LPR, rsub = lane / LPR;
+        float4 qv[NI];
 #pragma unroll
-        for (int j = 0; j < 2 * PPR; ++j) {
-            const float4 a = ok ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+        for (int i = 0; i < NI; ++i) {
+            const int rg = q0 + wq * 32 + i * RPI + rsub;
+            qv[i] = rg < S ? __ldg(reinterpret_cast<const float4 *>(Q + (tok0 + rg) * (size_t)E + hcol) + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const float sq = range_scale(amax * qscale);
-        const float qs = qscale * sq;
-        sfac = 1.0f / sq;                            // a power of two: exact
+        // the rows' largest magnitudes first, all exchanges side by side (an exchange between two stores would keep the
+        // compiler from overlapping the rows' dependent chains)
+        float amax[NI];
 #pragma unroll
-        for (int j = 0; j < PPR; ++j) {              // 8 floats at a time (the row is read again: it is in L1)
-            float4 a = ok ? __ldg(src + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-            float4 c = ok ? __ldg(src + 2 * j + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < NI; ++i) amax[i] = fmaxf(fmaxf(fabsf(qv[i].x), fabsf(qv[i].y)), fmaxf(fabsf(qv[i].z), fabsf(qv[i].w)));
+#pragma unroll
+        for (int o = 1; o < LPR; o <<= 1) {
+#pragma unroll
+            for (int i = 0; i < NI; ++i) amax[i] = fmaxf(amax[i], __shfl_xor_sync(0xffffffffu, amax[i], o));
+        }
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int r = wq * 32 + i * RPI + rsub;
+            float4 a = qv[i];
+            const float sq = range_scale(amax[i] * qscale);
+            const float qs = qscale * sq;
             a.x *= qs; a.y *= qs; a.z *= qs; a.w *= qs;
-            c.x *= qs; c.y *= qs; c.z *= qs; c.w *= qs;
-            const float4 ah = hi4(a), ch = hi4(c);
-            *reinterpret_cast<uint4 *>(q_16 + off16(rloc, j, kQBlk)) =
-                make_uint4(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w), pack_f16(ch.x, ch.y), pack_f16(ch.z, ch.w));
-            *reinterpret_cast<uint4 *>(q_16 + off16(rloc, PPR + j, kQBlk)) =
-                make_uint4(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w),
-                           pack_f16(c.x - ch.x, c.y - ch.y), pack_f16(c.z - ch.z, c.w - ch.w));
+            const float4 ah = hi4(a);
+            // values 4 c4 .. 4 c4 + 3 of the row: one half of a 16-byte chunk of the hi part, and of the lo part
+            *reinterpret_cast<uint2 *>(q_16 + off16(r, c4 >> 1, kQBlk) + (c4 & 1) * 8) = make_uint2(pack_f16(ah.x, ah.y), pack_f16(ah.z, ah.w));
+            *reinterpret_cast<uint2 *>(q_16 + off16(r, PPR + (c4 >> 1), kQBlk) + (c4 & 1) * 8) =
+                make_uint2(pack_f16(a.x - ah.x, a.y - ah.y), pack_f16(a.z - ah.z, a.w - ah.w));
+            if (c4 == 0) q_sfac[r] = __uint_as_float(0x7F000000u - __float_as_uint(sq));      // 1 / sq, a power of two within 2^+-126
         }
+        __syncwarp();
+        sfac = q_sfac[rloc];
     }
     // V's tiles carry factors of their own; P(t) is made smaller by tile t's factor over the head's smallest one (that of
     // the head's largest |V|), which leaves with the output
@@ -438,7 +458,14 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
     const uint32_t o_addr = lane_base + kColO;
 
     float m_ref = 0.0f, l = 0.0f;                    // reference maximum (log2 domain) and row sum (of P, which carries 2^6)
+    // the tiles' largest magnitudes are fetched one tile ahead: their latency (L2) must not stand between the sweeps
+    float kmx_next = __ldg(tmax_k), vmx_next = __ldg(tmax_v);
     for (int t = 0; t < nt; ++t) {
+        const float kmx = kmx_next, vmx = vmx_next;
+        if (t + 1 < nt) {
+            kmx_next = __ldg(tmax_k + t + 1);
+            vmx_next = __ldg(tmax_v + t + 1);
+        }
         const int buf = t % kBufs;
         const int j0 = t * kKeys;
         const uint32_t s_addr = lane_base + kColX + buf * kKeys;
@@ -452,16 +479,17 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
         const int nmin = CAUSAL ? max(0, min(ncols, wrow0 - j0 + 1)) : ncols;
         const int nch = (nwarp + 31) >> 5;           // 32-column chunks with any visible key (0: the tile is above the diagonal for the warp)
 
-        // ---- first sweep: the row's largest score of this tile ------------------------------------
+        // ---- the tile's scores are read once and stay in registers for both sweeps -------------------
+        // (chunks of 32 columns; a chunk that no row of the warp sees is not read)
+        float v0[32], v1[32];
+        if (nch > 0) tmem_ld32(s_addr, v0);
+        if (nch > 1) tmem_ld32(s_addr + 32, v1);
+        tmem_wait_ld();
+        // ---- first sweep: the row's largest score of this tile (hidden scores become -inf here) ------
         float mx = -INFINITY;
-        float v[32];
-#pragma unroll 1
-        for (int c = 0; c < nch; ++c) {
-            tmem_ld32(s_addr + c * 32, v);
-            tmem_wait_ld();
-            mx = fmaxf(mx, chunk_max(v, c * 32, nvalid, c * 32 + 32 > nmin));
-        }
-        const float tfac = sfac / range_scale(__ldg(tmax_k + t));   // what this tile's scores carry too much: the row's and the tile's factors
+        if (nch > 0) mx = chunk_max(v0, 0, nvalid, 32 > nmin);
+        if (nch > 1) mx = fmaxf(mx, chunk_max(v1, 32, nvalid, 64 > nmin));
+        const float tfac = sfac / range_scale(kmx);   // what this tile's scores carry too much: the row's and the tile's factors
         mx *= tfac;                                  // the row's largest true score (tfac > 0)
         if (t == 0) {
             m_ref = fmaxf(mx, -1e30f);
@@ -488,23 +516,13 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
         }
 
         // ---- second sweep: exponentials; P_hi and P_lo over S in place ---------------------------------
-        const float vrel = fminf(vhs / range_scale(__ldg(tmax_v + t)), 1.0f);   // <= 1: this V tile's factor against the head's (a tile of zeros: 1)
+        const float vrel = fminf(vhs / range_scale(vmx), 1.0f);   // <= 1: this V tile's factor against the head's (a tile of zeros: 1)
         const float nm = kPShift - m_ref + log2_of_pow2(vrel);
         float psum = 0.0f;
-#pragma unroll 1
-        for (int c = 0; c < nch; ++c) {
-            tmem_ld32(s_addr + c * 32, v);
-            tmem_wait_ld();
-            psum += chunk_exp(v, s_addr + c * 32, c * 32, nvalid, c * 32 + 32 > nmin, tfac, nm);
-        }
-#pragma unroll 1
-        for (int c = nch; c < kKeys / 32; ++c) {     // chunks that no row of this warp sees
-            uint32_t z[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) z[j] = 0u;
-            tmem_st16_u32(s_addr + c * 32, z);
-            tmem_st16_u32(s_addr + c * 32 + 16, z);
-        }
+        if (nch > 0) psum = chunk_exp(v0, s_addr, tfac, nm);
+        else tmem_zero32(s_addr);
+        if (nch > 1) psum += chunk_exp(v1, s_addr + 32, tfac, nm);
+        else tmem_zero32(s_addr + 32);               // a chunk that no row of this warp sees
         l += psum / vrel;                            // the row sum counts the probabilities themselves (a power of two: exact)
         tmem_wait_st();
         tc_fence_before();
