@@ -97,19 +97,18 @@ struct Bf16Cfg {
 
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(kThreads, 2)
-mha_bf16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const __nv_bfloat16 *__restrict__ Q,
+mha_bf16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                 __nv_bfloat16 *__restrict__ O, int S, int E, int H, int BH, int nqblk, float cscale)
 {
     static_assert(D == 64, "rows of the operand tiles are 128 bytes");
     using C = Bf16Cfg<D>;
-    constexpr int CPR = D / 8;                       // 16-byte chunks per row
     constexpr int TILE = C::kTileBytes;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *q_s = base;                             // [128][D] bf16, row r chunk c at r*128 + ((c ^ (r & 7)) * 16)
     uint8_t *k_s = q_s + C::kQBytes;                 // [stage][64 keys][D], the same layout (K-major operand)
     uint8_t *v_s = k_s + kStages * TILE;             // [stage][64 keys][D], the same bytes read as an N-major operand
-    __shared__ uint64_t k_full[kStages], v_full[kStages], s_full[kStages], o_done[kStages], p_full[kBufs];
+    __shared__ uint64_t k_full[kStages], v_full[kStages], s_full[kStages], o_done[kStages], p_full[kBufs], q_full;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
@@ -134,11 +133,12 @@ mha_bf16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             mbar_init(&o_done[i], 1);                // tcgen05.commit after P V(t): O is up to date, and the V stage is free
         }
         for (int i = 0; i < kBufs; ++i) mbar_init(&p_full[i], kWorkers / 32);    // one arrival per worker warp
+        mbar_init(&q_full, 1);
     }
     __syncthreads();
 
     // site codes in the status word: 1 S ready, 2 O complete (rescale), 3 O complete (end), 4 K tile landed,
-    // 5 P written, 6 V tile landed, 7 K stage free, 8 V stage free
+    // 5 P written, 6 V tile landed, 7 K stage free, 8 V stage free, 9 Q tile landed
     // (the polling loop exists once, out of line: an already completed phase costs one test)
     auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
         if (abort_flag || mbar_test(bar, parity)) return;
@@ -166,12 +166,19 @@ mha_bf16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
             }
             __syncwarp();
         };
+        // the query tile: two boxes of 64 rows (rows past S come as zeros); no thread touches it
+        if (qk_role && lane == 0) {
+            mbar_arrive_expect_tx(&q_full, (uint32_t)C::kQBytes);
+            tma_load_3d(q_s, &qmap, (int)hcol, q0, b, &q_full);
+            tma_load_3d(q_s + TILE, &qmap, (int)hcol, q0 + kKeys, b, &q_full);
+        }
+        __syncwarp();
         for (int u = 0; u < kStages; ++u) {
             if (qk_role) copy_tile(&kmap, k_s, k_full, u);
             else copy_tile(&vmap, v_s, v_full, u);
         }
         tc_fence_before();
-        __syncthreads();                             // Q staged; TMEM allocated
+        __syncthreads();                             // TMEM allocated
         tc_fence_after();
         const uint32_t tmem = tmem_base_slot;
         if (qk_role) {
@@ -184,6 +191,7 @@ mha_bf16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
                     if (elect_one()) mma_f16_ss(tmem + kColX + (t % kBufs) * kKeys, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_qk, k ? 1u : 0u);
                 if (elect_one()) tc_commit(&s_full[t % kStages]);    // S is ready, and this K stage may be refilled
             };
+            wait(&q_full, 0, 9);
             wait(&k_full[0], 0, 4);
             tc_fence_after();
             issue_qk(0);
@@ -229,18 +237,8 @@ mha_bf16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     const int wq = warp;                             // TMEM lane quadrant of this warp
     const int rloc = wq * 32 + lane;                 // row inside the block = TMEM lane
     const int row = q0 + rloc;
-    {
-        const bool ok = row < S;
-        const __nv_bfloat16 *src = Q + (tok0 + (ok ? row : 0)) * (size_t)E + hcol;
-        uint8_t *dst = q_s + rloc * 128;
-#pragma unroll
-        for (int c = 0; c < CPR; ++c) cp_async16(dst + ((c ^ (rloc & 7)) << 4), src + c * 8, ok);
-        cp_async_commit();
-        cp_async_wait<0>();
-    }
-    proxy_fence();
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();                                 // TMEM allocated
     tc_fence_after();
     const uint32_t lane_base = tmem_base_slot + ((uint32_t)(wq * 32) << 16);
     const uint32_t o_addr = lane_base + kColO;
@@ -387,12 +385,13 @@ int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int 
     const long long blocks = (long long)B * H * nqblk;
     if (blocks > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "grid of %lld blocks is too large", blocks);
     if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return fail(HIPGPT_ERR_BAD_ARG, "bf16 attention needs 16-byte aligned planes");
-    CUtensorMap kmap, vmap;
-    int rc = bf16_plane_map(&kmap, k, B, S, E);
+    CUtensorMap qmap, kmap, vmap;
+    int rc = bf16_plane_map(&qmap, q, B, S, E);
+    if (rc == HIPGPT_OK) rc = bf16_plane_map(&kmap, k, B, S, E);
     if (rc == HIPGPT_OK) rc = bf16_plane_map(&vmap, v, B, S, E);
     if (rc != HIPGPT_OK) return rc;
     const float cscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<(unsigned)blocks, kThreads, smem, st>>>(kmap, vmap, static_cast<const __nv_bfloat16 *>(q), static_cast<__nv_bfloat16 *>(out), S, E, H, B * H,
+    kern<<<(unsigned)blocks, kThreads, smem, st>>>(qmap, kmap, vmap, static_cast<__nv_bfloat16 *>(out), S, E, H, B * H,
                                                    nqblk, cscale);
     return check_launch("mha_bf16_kernel");
 }
