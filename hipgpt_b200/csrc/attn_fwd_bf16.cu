@@ -7,7 +7,8 @@
 // = TMEM lane) and two issuing warps.  Two blocks per SM.  Per tile of 64 keys:
 //   copy     one lane asks the TMA unit for the bf16 K / V tile ([64 keys][64 values] = rows of 128 bytes, rank-3
 //            maps {E, S, B} over this GPU's own memory, 128-byte swizzle, keys past S arrive as zeros) straight into
-//            its operand layout, four stages each; a stage is refilled once the product that read it has completed;
+//            its operand layout, four stages each; a stage is refilled once the product that read it has completed
+//            (the query tile comes the same way, once, as two such boxes);
 //   S        = Q K^T (M=128, N=64, 4 instructions of K=16) into one of three TMEM buffers, up to two tiles
 //            ahead of the softmax;
 //   softmax  the worker reads its 64 scores from TMEM once; maximum, exponentials (scale folded into
@@ -76,8 +77,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 
 // (A cubic on the FMA pipe for a share of the exponentials, to relieve the special-function unit, was measured:
 // +3 % at S = 1024, -2 % at S = 2048, not kept.)
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // The polling part of a bounded wait; on expiry the block's abort flag is raised and the site recorded.
 __device__ __noinline__ void bf16_wait_slow(uint64_t *bar, uint32_t parity, int site, volatile int *abort_flag)
