@@ -12,10 +12,11 @@
 //   O = P V:    P = 2^(s - m + 6) cut into fp16 P_hi, P_lo, written over S in place (per 32-column chunk: 16 columns
 //               of packed P_hi, 16 of packed P_lo); V as [V_hi | V_lo], N-major:  P_hi [V_hi | V_lo] (N = 2 D) and
 //               P_lo V_hi (N = D, added to the second half), A operand from TMEM, 8 instructions per 64 keys.
-// Range: magnitudes up to fp16's largest number; beyond it the conversions saturate and the kernel raises the
-// accuracy notice.  Small magnitudes cost absolute, not relative, accuracy: a lo part below 6e-5 is a subnormal fp16
-// (steps of 6e-8), which the notice's test weighs against the scores it is added to.  The split-TF32 kernel
-// (attn_fwd_tc.cu) has the whole fp32 range.
+// Range: the whole fp32 range.  Every fp16 piece is formed from a copy of the operand scaled by a power of two (exact)
+// that brings the largest magnitude of its unit into [2^14, 2^15): per query row for Q, per 64-key tile for K and for V.
+// The factors leave again where they cost nothing: Q's and K's inside the multiply-add that forms the exponent, V's
+// tile factor (relative to the head's) as a power of two folded into P, the head's with the final division.  The
+// accuracy notice is therefore never raised by this kernel.
 //
 // Two kernels.  kv_pack_kernel cuts K and V into their fp16 pieces once per call and writes them, tile by tile, as
 // the exact shared-memory images of the operand stages (K: rows of [K_hi | K_lo], K-major, 128-byte swizzle; V:
@@ -28,7 +29,10 @@
 //   TMEM (256 columns): X0, X1 (64 each): S(t), overwritten in place by P(t);  O (2 D): [P_hi V_hi | P_hi V_lo + P_lo V_hi],
 //   accumulated over ALL tiles.  Workers (thread = query row = TMEM lane) never read O back per tile: the reference
 //   maximum only moves (and O is rescaled, by the whole warp) when a row's maximum grew by more than 2^8.
-//   With P double-buffered, the worker goes from tile t straight to tile t+1 while P V(t) runs.
+//   With P double-buffered, the worker goes from tile t straight to tile t+1 while P V(t) runs.  It reads a tile's
+//   scores from TMEM once and keeps them in registers for the maximum and for the exponentials; additions and
+//   multiply-adds work on pairs of values per instruction (the sweeps are bound by the instructions they issue).
+//   A warp stages its 32 query rows with whole-line reads (D / 4 lanes per row), all in flight at once.
 // Every wait is bounded: on expiry the block raises a flag that cuts all later waits short,
 // records a status code, skips its stores, frees its TMEM and returns.
 #include "tc_primitives.cuh"
