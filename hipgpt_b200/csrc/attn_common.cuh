@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "hipgpt_attn.h"
 
@@ -13,6 +14,35 @@ namespace hipgpt {
 int fail(int code, const char *fmt, ...);
 // Checks the launch that was just enqueued; HIPGPT_OK or HIPGPT_ERR_CUDA.
 int check_launch(const char *what);
+
+// Launch with programmatic stream serialization: the kernel's blocks may become resident, and run their prologue
+// (barriers, TMEM, roles), while the last blocks of the kernel before it on the stream are still running, once those
+// have let their dependents go.  Such a kernel must execute dependency_wait() before its first access to global
+// memory; the wait returns when the kernel before it has completed and its writes are visible.
+// HIPGPT_NO_OVERLAPPED_LAUNCH=1 launches the plain way.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    static const bool plain = [] { const char *e = getenv("HIPGPT_NO_OVERLAPPED_LAUNCH"); return e && *e && *e != '0'; }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = plain ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+// The kernel before this one on the stream has completed and its writes are visible (returns at once for a plain launch).
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The kernel after this one on the stream may start its blocks as soon as every block of this grid has said so or exited.
+__device__ __forceinline__ void dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 constexpr float kLog2e = 1.4426950408889634f;
 

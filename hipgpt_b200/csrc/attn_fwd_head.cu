@@ -220,9 +220,25 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
                 mbar_init(&b0_free, 1);
             }
             __syncwarp();
-            if ((int)blockIdx.x < BH) { load_qk(blockIdx.x); load_v(blockIdx.x); }
             asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+            // Everything above ran beside the tail of the kernel before this one on the stream; the first read of global
+            // memory waits for it.  The kernel after this one may bring its blocks in as soon as this grid's SMs free up.
+            // The first head's tiles are asked into L2 before the wait (a prefetch reads nothing into the SM; L2 is
+            // where the other kernel's writes land too, so it cannot go stale): all SMs ask for their operands in the
+            // same microsecond after the wait, and that burst then hits L2 instead of HBM.
+            if (lane == 0 && (int)blockIdx.x < BH) {
+                const int b = (int)blockIdx.x / H, c0 = ((int)blockIdx.x % H) * 32;
+                for (int t = 0; t < nq; ++t) {
+                    tma_prefetch_3d(&maps.k, c0, t * kTile, b);
+                    tma_prefetch_3d(&maps.q, c0, t * kTile, b);
+                }
+                for (int t = 0; t < nq; ++t) tma_prefetch_3d(&maps.v, c0, t * kTile, b);
+            }
+            __syncwarp();
+            dependents_may_start();
+            dependency_wait();
+            if ((int)blockIdx.x < BH) { load_qk(blockIdx.x); load_v(blockIdx.x); }
         }
         tc_fence_before();
         __syncthreads();                             // barriers initialised, TMEM allocated
@@ -696,7 +712,8 @@ int launch_head_cfg(const HeadMaps &maps, float *out, float *probs, int B, int S
     if (bh > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "%lld (batch, head) pairs are too many", bh);
     const unsigned grid = (unsigned)(bh < sms ? bh : sms);
     const float cscale = (1.0f / sqrtf(32.0f)) * kLog2e;
-    kern<<<grid, kHeadThreads, smem, st>>>(maps, out, probs, S, E, H, (int)bh, cscale);
+    const cudaError_t le = launch_overlapped(kern, dim3(grid), dim3(kHeadThreads), smem, st, maps, out, probs, S, E, H, (int)bh, cscale);
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "mha_head_kernel launch: %s", cudaGetErrorString(le));
     return check_launch("mha_head_kernel");
 }
 
