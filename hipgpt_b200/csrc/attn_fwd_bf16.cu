@@ -165,6 +165,10 @@ mha_bf16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant_
             }
             __syncwarp();
         };
+        // Up to here the block ran beside the tail of the kernel before it on the stream (overlapped launch); its first
+        // read of global memory waits for that kernel, and the kernel after this one may bring its blocks in.
+        dependents_may_start();
+        dependency_wait();
         // the query tile: two boxes of 64 rows (rows past S come as zeros); no thread touches it
         if (qk_role && lane == 0) {
             mbar_arrive_expect_tx(&q_full, (uint32_t)C::kQBytes);
@@ -390,8 +394,9 @@ int launch_bf16_cfg(const void *q, const void *k, const void *v, void *out, int 
     if (rc == HIPGPT_OK) rc = bf16_plane_map(&vmap, v, B, S, E);
     if (rc != HIPGPT_OK) return rc;
     const float cscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    kern<<<(unsigned)blocks, kThreads, smem, st>>>(qmap, kmap, vmap, static_cast<__nv_bfloat16 *>(out), S, E, H, B * H,
-                                                   nqblk, cscale);
+    const cudaError_t le = launch_overlapped(kern, dim3((unsigned)blocks), dim3(kThreads), smem, st, qmap, kmap, vmap, static_cast<__nv_bfloat16 *>(out), S, E, H, B * H,
+                                             nqblk, cscale);
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "mha_bf16_kernel launch: %s", cudaGetErrorString(le));
     return check_launch("mha_bf16_kernel");
 }
 

@@ -155,20 +155,20 @@ __device__ __forceinline__ float log2_of_pow2(float p) { return (float)((int)((_
 // rows (coalesced) and writes 16-byte chunks that fill whole 128-byte lines of the image.
 // Every tile is scaled by a power of two of its own (range_scale of the tile's largest magnitude), so that no operand
 // magnitude costs accuracy: the block holds its pieces in registers, finds the two maxima, converts.  The maxima go to
-// tmax[0][tile] (K) and tmax[1][tile] (V), V's largest over the whole head to hmax[bh] (zeroed before the launch;
-// non-negative floats order like their bit patterns): the attention kernel takes the factors out again.
+// tmax[0][tile] (K) and tmax[1][tile] (V): the attention kernel takes the factors out again.
 // K image: [HB blocks][64 rows][128 bytes], a row of block j holds values 64 j .. 64 j + 63 of [K_hi (D) | K_lo (D)],
 // 16-byte chunks swizzled by the row (the layout a K-major, 128-byte-swizzled operand has in shared memory).
 // V image: key r, column block cb (8 columns of [V_hi (D) | V_lo (D)]) at (r / 8) * 32 D + cb * 128 + (r % 8) * 16:
 // 8 keys x 8 columns form one 128-byte core matrix of an N-major operand without swizzle.  Keys past S are zeros.
 template <int D>
 __global__ void __launch_bounds__(kPackThreads)
-kv_pack_kernel(const float *__restrict__ K, const float *__restrict__ V, float *__restrict__ tmax, float *__restrict__ hmax,
+kv_pack_kernel(const float *__restrict__ K, const float *__restrict__ V, float *__restrict__ tmax,
                uint8_t *__restrict__ kimg, uint8_t *__restrict__ vimg, int S, int E, int H, int ntk, int ntiles)
 {
     using C = Tc16Cfg<D>;
     constexpr int PPR = C::PPR, RPT = kPackThreads / PPR, NP = kKeys / RPT;      // rows covered per pass, pieces per thread
     __shared__ float red[2][kPackThreads / 32];
+    dependents_may_start();                          // the attention kernel's blocks may come in as this grid's blocks leave
     const int kt = blockIdx.x, bh = blockIdx.y;
     const int b = bh / H, h = bh % H;
     const int pid = threadIdx.x, pc = pid % PPR, r0 = pid / PPR;
@@ -203,7 +203,6 @@ kv_pack_kernel(const float *__restrict__ K, const float *__restrict__ V, float *
     if (pid == 0) {
         tmax[tile] = mk;
         tmax[ntiles + tile] = mv;
-        atomicMax(reinterpret_cast<unsigned *>(hmax) + bh, __float_as_uint(mv));     // a NaN's pattern is "no scaling" too
     }
     const float sk = range_scale(mk), sv = range_scale(mv);
 #pragma unroll
@@ -236,7 +235,7 @@ kv_pack_kernel(const float *__restrict__ K, const float *__restrict__ V, float *
 
 template <int D, bool CAUSAL, bool PROBS>
 __global__ void __launch_bounds__(Tc16Cfg<D>::THREADS, Tc16Cfg<D>::BLOCKS_PER_SM)
-mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vimg, const float *__restrict__ tmax, const float *__restrict__ hmax, int ntiles, const float *__restrict__ Q,
+mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vimg, const float *__restrict__ tmax, int ntiles, const float *__restrict__ Q,
                 float *__restrict__ O, float *__restrict__ P, int S, int E, int H, int BH, int nqblk, int ntk, float qscale)
 {
     using C = Tc16Cfg<D>;
@@ -328,6 +327,7 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
             }
             __syncwarp();
         };
+        dependency_wait();                           // the pack kernel has completed: its images may be fetched
         if (qk_role) {
             for (int u = 0; u < KST; ++u) copy_k(u);
         } else {
@@ -450,10 +450,16 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
         __syncwarp();
         sfac = q_sfac[rloc];
     }
-    // V's tiles carry factors of their own; P(t) is made smaller by tile t's factor over the head's smallest one (that of
-    // the head's largest |V|), which leaves with the output
-    const float vhs = range_scale(hmax[bh]), vinv = 1.0f / vhs;
+    // The rows above were read beside the tail of the pack kernel; what it wrote is read from here on.
+    dependency_wait();
+    // V's tiles carry factors of their own; P(t) is made smaller by tile t's factor over the smallest one among the
+    // block's tiles (that of their largest |V|), which leaves with the output
     const float *tmax_k = tmax + (size_t)bh * ntk, *tmax_v = tmax + ntiles + (size_t)bh * ntk;
+    float vmax_all = 0.0f;
+    for (int t = lane; t < nt; t += 32) vmax_all = fmaxf(vmax_all, __ldg(tmax_v + t));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) vmax_all = fmaxf(vmax_all, __shfl_xor_sync(0xffffffffu, vmax_all, o));
+    const float vhs = range_scale(vmax_all), vinv = 1.0f / vhs;
     proxy_fence();
     tc_fence_before();
     __syncthreads();
@@ -693,22 +699,21 @@ int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, 
     const size_t kbytes = (size_t)gb * H * ntk * C::kK16Stage, vbytes = (size_t)gb * H * ntk * C::kV16Stage;
     uint8_t *scratch = nullptr;
     const size_t gtiles = (size_t)gb * H * ntk;
-    int rc = g_pack.get(dev, st, kbytes + vbytes + (2 * gtiles + (size_t)gb * H) * sizeof(float), &scratch);
+    int rc = g_pack.get(dev, st, kbytes + vbytes + 2 * gtiles * sizeof(float), &scratch);
     if (rc != HIPGPT_OK) return rc;
     float *tmax = reinterpret_cast<float *>(scratch + kbytes + vbytes);      // [2][group's tiles]: largest |K|, |V| of every tile
-    float *hmax = tmax + 2 * gtiles;                                         // [group's (batch, head) pairs]: largest |V|
     const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
     for (long long b0 = 0; b0 < B; b0 += gb) {
         const int nb = (int)(B - b0 < gb ? B - b0 : gb);
         const size_t off = (size_t)b0 * S * E;       // the group's first token in every plane and in the output
-        e = cudaMemsetAsync(hmax, 0, (size_t)nb * H * sizeof(float), st);
-        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
         const int ntiles = nb * H * ntk;
-        kv_pack_kernel<D><<<dim3((unsigned)ntk, (unsigned)(nb * H)), kPackThreads, 0, st>>>(k + off, v + off, tmax, hmax, scratch, scratch + kbytes, S, E, H, ntk, ntiles);
+        kv_pack_kernel<D><<<dim3((unsigned)ntk, (unsigned)(nb * H)), kPackThreads, 0, st>>>(k + off, v + off, tmax, scratch, scratch + kbytes, S, E, H, ntk, ntiles);
         rc = check_launch("kv_pack_kernel");
         if (rc != HIPGPT_OK) return rc;
-        kern<<<(unsigned)(nb * H * nqblk), C::THREADS, smem, st>>>(scratch, scratch + kbytes, tmax, hmax, ntiles, q + off, out + off,
-                                                                   probs ? probs + (size_t)b0 * H * S * S : nullptr, S, E, H, nb * H, nqblk, ntk, qscale);
+        // the attention kernel's blocks start (and stage their query rows) while the pack kernel's last blocks run
+        e = launch_overlapped(kern, dim3((unsigned)(nb * H * nqblk)), dim3(C::THREADS), smem, st, (const uint8_t *)scratch, (const uint8_t *)(scratch + kbytes),
+                              (const float *)tmax, ntiles, q + off, out + off, probs ? probs + (size_t)b0 * H * S * S : nullptr, S, E, H, nb * H, nqblk, ntk, qscale);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "mha_tc16_kernel launch: %s", cudaGetErrorString(e));
         rc = check_launch("mha_tc16_kernel");
         if (rc != HIPGPT_OK) return rc;
     }
