@@ -79,10 +79,12 @@ HIPGPT_API int hipgpt_mha_forward(const float *d_q, const float *d_k, const floa
 
 /* The same with an explicit kernel selector (HIPGPT_ALGO_*).  `warps`: for HIPGPT_ALGO_ROWS the
  * number of warps per thread block (0 = default); for HIPGPT_ALGO_TENSOR one of HIPGPT_TENSOR_*.
- * Every kernel holds 1e-5 on unit-scale data.  TILED and WHOLE_HEAD keep that accuracy while Q, K (and for
- * TILED, V) stay within fp16's range (about 1e-4 .. 6e4; WHOLE_HEAD rescales V by a power of two per head,
- * so V may have any magnitude); outside it their correction terms saturate or are flushed, the result
- * falls to plain TF32 grade (~3e-4 relative), and the launch raises the flag that
+ * Every kernel holds 1e-5 on unit-scale data.  TILED scales its operands into fp16's range by exact powers of two
+ * (per query row, per 64-key tile of K and of V) and keeps that accuracy for any fp32 magnitude; it keeps the fp16
+ * images of K and V in a buffer of the library (per device and stream; hipgpt_release_workspace() frees it).
+ * WHOLE_HEAD keeps the accuracy while Q and K stay within fp16's range (about 1e-4 .. 6e4; it rescales V by a
+ * power of two per head, so V may have any magnitude); outside it its correction terms saturate or are flushed,
+ * the result falls to plain TF32 grade (~3e-4 relative), and the launch raises the flag that
  * hipgpt_accuracy_notice() reports.  SPLIT_TF32 and the FFMA kernels have the full fp32 range. */
 HIPGPT_API int hipgpt_mha_forward_ex(const float *d_q, const float *d_k, const float *d_v,
                           float *d_out, float *d_probs,
