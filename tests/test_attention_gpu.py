@@ -216,7 +216,7 @@ def test_default_kernels_report_operands_outside_the_fp16_range(shape):
         raised = _notice()
         whole_head = D == 32 and S <= 256
         if not whole_head:
-            # the tiled kernel scales K and V per head and Q per row by powers of two before it cuts them into fp16
+            # the tiled kernel scales K and V per 64-key tile and Q per row by powers of two before it cuts them into fp16
             # pieces: no operand magnitude costs it accuracy
             assert rel <= 1e-5 and raised == 0, (name, rel, raised)
         elif name == "V beyond 65504":
