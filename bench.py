@@ -19,7 +19,8 @@ Default workload: B=32 H=8 S=256 head_dim=32, fp32, causal, probabilities not st
             (workload c2), else the measured tensor rate; the fp32 FFMA ceiling timed in the same
             run is reported beside it
   scaling_c5  (default run) the largest workload through the sharded C-ABI driver: compute alone,
-            compute in chunks, and with the overlapped all-gather of the outputs when N > 1
+            compute in chunks, and with the all-gather of the outputs beside it when N > 1 (NCCL, and
+            the library's own stores into the peers' mapped buffers)
   cpu_baseline  the CPU oracle (a port of the reference arithmetic) on this box's host cores
 
 With N > 1 (torchrun, one rank per GPU) every rank runs the same step on its own batches
@@ -249,8 +250,9 @@ def workload_config(args, cfg):
 
 def scaling_c5_leg(world, rank, lib):
     """BASELINE.json's scaling configuration (B=64 H=16 S=2048 head_dim=64, causal, fp32 and bf16 storage) with its
-    batches split over the ranks by the library's own driver (hipgpt_mha_forward_sharded): compute only, and with the
-    NCCL all-gather of the outputs, chunk by chunk behind the arithmetic.  Device time per call from CUDA events,
+    batches split over the ranks by the library's own driver (hipgpt_mha_forward_sharded): compute only, with the
+    NCCL all-gather of the outputs chunk by chunk behind the arithmetic, and with the library's own transport (a small
+    copy kernel that stores each chunk into the peers' mapped buffers).  Device time per call from CUDA events,
     max over ranks; L2 is flushed between calls (at 8 ranks a rank's bf16 inputs are smaller than L2)."""
     import torch
     import torch.distributed as dist
@@ -277,7 +279,8 @@ def scaling_c5_leg(world, rank, lib):
         g = torch.Generator(device="cuda")
         g.manual_seed(4 + rank)
         loc = torch.randn((3, Bl * S, E), device="cuda", generator=g, dtype=torch.float32).to(dtype)
-        full = torch.empty((B * S, E), device="cuda", dtype=dtype)
+        # the output lives in the buffer that every rank maps from every other (needed by the peer-store transport)
+        full = sh.output_tensor(B * S, E, dtype) if world > 1 else torch.empty((B * S, E), device="cuda", dtype=dtype)
         chunks = chunks_for(full.element_size())
 
         def call(ch, gather):
@@ -306,8 +309,9 @@ def scaling_c5_leg(world, rank, lib):
                 total += ms
             return total / reps
         res = {}
-        for label, ch, gather in (("compute_only", 1, False), ("compute_chunked", chunks, False), ("with_gather", chunks, True)):
-            if label == "with_gather" and world == 1:
+        for label, ch, gather in (("compute_only", 1, 0), ("compute_chunked", chunks, 0), ("with_gather", chunks, sharding.GATHER_NCCL),
+                                  ("with_gather_peer_stores", chunks, sharding.GATHER_PEER_STORES)):
+            if gather and world == 1:
                 continue
             ms = timed(ch, gather)
             res[label] = {"ms": ms, "tflops": flops_of(B, H, S, D, True) / (ms * 1e-3) / 1e12}

@@ -58,6 +58,7 @@ SIGNATURES = {
     "hipgpt_shard_create": (_i, [C.POINTER(_vp), _vp, _i, _i]),
     "hipgpt_shard_destroy": (None, [_vp]),
     "hipgpt_mha_forward_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "hipgpt_shard_output_buffer": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "hipgpt_shard_nccl_version": (_i, []),
     "hipgpt_probe_fma": (_i, [_vp, _i, _i, C.POINTER(C.c_double), _vp]),
     "hipgpt_kernel_status": (_i, [C.POINTER(_i)]),

@@ -77,6 +77,8 @@ int launch_mha_tc16(const float *q, const float *k, const float *v, float *out, 
 bool mha_tc16_supports(int head_dim);
 int tc16_status_fetch(int *status);
 void tc16_release_scratch();
+// Copies `bytes` from src to each of up to seven peer addresses with plain stores (shard_push.cu).
+int launch_shard_push(const void *src, void *const *dst, int ndst, size_t bytes, cudaStream_t st);
 int tc16_notice_fetch(int *notice);
 // whole-head kernel (head_dim 32, S <= 256): TMA loads, 128-key products, all score tiles of a head in TMEM
 int launch_mha_head(const float *q, const float *k, const float *v, float *out, float *probs, int B, int S, int E, int H, int causal, cudaStream_t st);

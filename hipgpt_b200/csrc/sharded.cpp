@@ -12,6 +12,16 @@
 // are placed as soon as blocks of the next chunk's attention kernel retire, and the transfer of chunk c
 // overlaps the arithmetic of chunk c + 1.  The kernels read local memory only.
 //
+// Second transport (gather = HIPGPT_GATHER_PEER_STORES): NCCL's thread blocks are large and wait for attention blocks
+// to retire before they find room, and the measured time of the NCCL form is close to compute + gather.  Here every
+// rank maps every other rank's output buffer (inter-process memory handles, exchanged once through the
+// communicator), and after a chunk's kernels a copy kernel of 128-thread blocks without shared memory
+// (shard_push.cu) stores the chunk into the peers' buffers with plain stores over NVLink; those blocks fit beside two
+// resident attention blocks on every SM.  No kernel waits for another GPU: a four-byte-per-rank collective on the
+// communication stream before the first copy (every rank has reached this call on its stream, so its buffer may be
+// written) and after the last one (every rank's copies have completed, which for a kernel means performed) orders
+// the ranks.
+//
 // NCCL is loaded at run time (dlopen of libnccl.so.2: in a torch process that is the copy torch already
 // loaded), so the single-GPU library has no link dependency on it.
 #include <dlfcn.h>
@@ -62,6 +72,8 @@ Nccl *nccl()
 
 int nccl_fail(Nccl *n, ncclResult_t r, const char *what) { return fail(HIPGPT_ERR_CUDA, "%s: %s", what, n->GetErrorString(r)); }
 
+int cuda_fail(cudaError_t e, const char *what) { return fail(HIPGPT_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e)); }
+
 }  // namespace
 }  // namespace hipgpt
 
@@ -74,6 +86,13 @@ struct hipgpt_shard_ctx {
     static constexpr int kMaxChunks = 64;
     cudaEvent_t computed[kMaxChunks] = {};      // chunk c's attention kernels have been enqueued and will have finished
     cudaEvent_t gathered = nullptr;             // the last all-gather has finished
+    cudaEvent_t entered = nullptr;              // the caller's stream has reached the call
+    // peer-store transport
+    static constexpr int kMaxPeers = 8;
+    uint8_t *own_out = nullptr;                 // this rank's output buffer (hipgpt_shard_output_buffer)
+    size_t own_bytes = 0;
+    uint8_t *peer_out[kMaxPeers] = {};          // the same buffer of every rank as mapped here; [rank] = own_out
+    int *sync_words = nullptr;                  // [world] ints on the device: the ordering collective's operand
 };
 
 extern "C" {
@@ -118,6 +137,9 @@ int hipgpt_shard_create(hipgpt_shard_ctx **out, const void *id128, int rank, int
     if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, hi);
     for (int i = 0; i < hipgpt_shard_ctx::kMaxChunks && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&c->computed[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->gathered, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->entered, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaMalloc(&c->sync_words, sizeof(int) * (size_t)(world > 0 ? world : 1));
+    if (e == cudaSuccess) e = cudaMemset(c->sync_words, 0, sizeof(int) * (size_t)world);
     if (e != cudaSuccess) {
         hipgpt_shard_destroy(c);
         return fail(HIPGPT_ERR_CUDA, "stream or event creation: %s", cudaGetErrorString(e));
@@ -134,9 +156,80 @@ int hipgpt_shard_create(hipgpt_shard_ctx **out, const void *id128, int rank, int
     return HIPGPT_OK;
 }
 
+// Every rank has passed this point on its communication stream (a collective of four bytes per rank), and the host has waited for it.
+static int ranks_meet(hipgpt_shard_ctx *c)
+{
+    if (c->world > 1 && c->comm) {
+        Nccl *n = nccl();
+        const ncclResult_t r = n->AllGather(c->sync_words + c->rank, c->sync_words, sizeof(int), ncclChar, c->comm, c->comm_stream);
+        if (r != 0) return nccl_fail(n, r, "ncclAllGather (ordering)");
+    }
+    const cudaError_t e = cudaStreamSynchronize(c->comm_stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return HIPGPT_OK;
+}
+
+// Unmaps the peers' buffers, waits until every rank has done so, frees this rank's.
+static int release_output_buffer(hipgpt_shard_ctx *c)
+{
+    if (!c->own_out) return HIPGPT_OK;
+    cudaDeviceSynchronize();
+    for (int p = 0; p < c->world && p < hipgpt_shard_ctx::kMaxPeers; ++p)
+        if (p != c->rank && c->peer_out[p]) cudaIpcCloseMemHandle(c->peer_out[p]);
+    const int rc = ranks_meet(c);
+    cudaFree(c->own_out);
+    c->own_out = nullptr;
+    c->own_bytes = 0;
+    for (auto &p : c->peer_out) p = nullptr;
+    return rc;
+}
+
+int hipgpt_shard_output_buffer(hipgpt_shard_ctx *c, size_t bytes, void **d_out)
+{
+    if (!c || !d_out) return fail(HIPGPT_ERR_NULL, "context and d_out must not be NULL");
+    if (c->world > hipgpt_shard_ctx::kMaxPeers) return fail(HIPGPT_ERR_UNSUPPORTED, "the peer-store transport takes at most %d ranks", hipgpt_shard_ctx::kMaxPeers);
+    if (bytes == 0) return fail(HIPGPT_ERR_BAD_ARG, "an output buffer of 0 bytes");
+    int rc = release_output_buffer(c);
+    if (rc != HIPGPT_OK) return rc;
+    cudaError_t e = cudaMalloc(&c->own_out, bytes);
+    if (e != cudaSuccess) { c->own_out = nullptr; return cuda_fail(e, "cudaMalloc of the output buffer"); }
+    c->own_bytes = bytes;
+    c->peer_out[c->rank] = c->own_out;
+    if (c->world > 1) {
+        // the handles travel through the communicator: [world] handles on the device, all-gathered in place
+        Nccl *n = nccl();
+        cudaIpcMemHandle_t mine, all[hipgpt_shard_ctx::kMaxPeers];
+        uint8_t *d_handles = nullptr;
+        e = cudaIpcGetMemHandle(&mine, c->own_out);
+        if (e == cudaSuccess) e = cudaMalloc(&d_handles, sizeof(mine) * (size_t)c->world);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d_handles + sizeof(mine) * (size_t)c->rank, &mine, sizeof(mine), cudaMemcpyHostToDevice, c->comm_stream);
+        if (e != cudaSuccess) { cudaFree(d_handles); return cuda_fail(e, "inter-process handle of the output buffer"); }
+        const ncclResult_t r = n->AllGather(d_handles + sizeof(mine) * (size_t)c->rank, d_handles, sizeof(mine), ncclChar, c->comm, c->comm_stream);
+        if (r != 0) { cudaFree(d_handles); return nccl_fail(n, r, "ncclAllGather (handles)"); }
+        e = cudaMemcpyAsync(all, d_handles, sizeof(mine) * (size_t)c->world, cudaMemcpyDeviceToHost, c->comm_stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->comm_stream);
+        cudaFree(d_handles);
+        if (e != cudaSuccess) return cuda_fail(e, "exchange of the handles");
+        for (int p = 0; p < c->world; ++p) {
+            if (p == c->rank) continue;
+            void *mapped = nullptr;
+            e = cudaIpcOpenMemHandle(&mapped, all[p], cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle of a peer's output buffer");
+            c->peer_out[p] = static_cast<uint8_t *>(mapped);
+        }
+        rc = ranks_meet(c);                      // every rank has mapped every buffer before any of them is used
+        if (rc != HIPGPT_OK) return rc;
+    }
+    *d_out = c->own_out;
+    return HIPGPT_OK;
+}
+
 void hipgpt_shard_destroy(hipgpt_shard_ctx *c)
 {
     if (!c) return;
+    release_output_buffer(c);
+    if (c->sync_words) cudaFree(c->sync_words);
+    if (c->entered) cudaEventDestroy(c->entered);
     if (c->comm) nccl()->CommDestroy(c->comm);
     for (cudaEvent_t ev : c->computed) if (ev) cudaEventDestroy(ev);
     if (c->gathered) cudaEventDestroy(c->gathered);
@@ -162,8 +255,23 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int k = B / (c->world * chunks);
     const size_t batch = (size_t)S * E * elem_bytes;             // bytes of one batch item of a plane
+    if (gather < 0 || gather > HIPGPT_GATHER_PEER_STORES) return fail(HIPGPT_ERR_BAD_ARG, "gather = %d is none of 0, 1, 2", gather);
     const bool comm = gather && c->world > 1;
+    const bool push = comm && gather == HIPGPT_GATHER_PEER_STORES;
     Nccl *n = comm ? nccl() : nullptr;
+    if (push) {
+        const uint8_t *o = static_cast<const uint8_t *>(d_out);
+        const size_t need = (size_t)B * batch;
+        if (!c->own_out || o < c->own_out || o + need > c->own_out + c->own_bytes)
+            return fail(HIPGPT_ERR_BAD_ARG, "gather = 2 needs d_out inside the buffer of hipgpt_shard_output_buffer (%zu bytes needed)", need);
+        if (((size_t)k * batch) & 15) return fail(HIPGPT_ERR_BAD_ARG, "a rank's chunk of %zu bytes is not a multiple of 16", (size_t)k * batch);
+        // no rank writes into a peer that has not reached this call on its stream
+        cudaError_t e = cudaEventRecord(c->entered, st);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm_stream, c->entered, 0);
+        if (e != cudaSuccess) return cuda_fail(e, "event hand-off");
+        const ncclResult_t r = n->AllGather(c->sync_words + c->rank, c->sync_words, sizeof(int), ncclChar, c->comm, c->comm_stream);
+        if (r != 0) return nccl_fail(n, r, "ncclAllGather (ordering)");
+    }
     const uint8_t *q = static_cast<const uint8_t *>(d_q), *kk = static_cast<const uint8_t *>(d_k), *v = static_cast<const uint8_t *>(d_v);
     uint8_t *out = static_cast<uint8_t *>(d_out);
     for (int ch = 0; ch < chunks; ++ch) {
@@ -179,8 +287,22 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
         cudaError_t e = cudaEventRecord(c->computed[ch], st);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm_stream, c->computed[ch], 0);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "event hand-off: %s", cudaGetErrorString(e));
+        if (push) {
+            void *dst[hipgpt_shard_ctx::kMaxPeers];
+            int nd = 0;
+            const size_t off = (size_t)(mine - c->own_out);
+            for (int p = 1; p < c->world; ++p) dst[nd++] = c->peer_out[(c->rank + p) % c->world] + off;      // each rank starts with its right-hand neighbour
+            const int prc = launch_shard_push(mine, dst, nd, (size_t)k * batch, c->comm_stream);
+            if (prc != HIPGPT_OK) return prc;
+            continue;
+        }
         const ncclResult_t r = n->AllGather(mine, block, (size_t)k * batch, ncclChar, c->comm, c->comm_stream);
         if (r != 0) return nccl_fail(n, r, "ncclAllGather");
+    }
+    if (push) {
+        // every rank's copies have completed (a kernel that has completed has performed its stores)
+        const ncclResult_t r = n->AllGather(c->sync_words + c->rank, c->sync_words, sizeof(int), ncclChar, c->comm, c->comm_stream);
+        if (r != 0) return nccl_fail(n, r, "ncclAllGather (ordering)");
     }
     if (comm) {
         cudaError_t e = cudaEventRecord(c->gathered, c->comm_stream);

@@ -12,6 +12,7 @@ the tests of this host logic).
 from __future__ import annotations
 
 import ctypes as C
+import sys
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -91,6 +92,9 @@ def local_planes_chunked(qkv: torch.Tensor, B: int, S: int, E: int, world: int, 
     return torch.cat(parts, dim=1).reshape(3, (B // world) * S, E).contiguous()
 
 
+GATHER_NONE, GATHER_NCCL, GATHER_PEER_STORES = 0, 1, 2
+
+
 class ShardedAttention:
     """One per process (= per GPU): an NCCL communicator of the library's own, a high-priority communication stream
     and the per-chunk events.  torch.distributed only carries the 128-byte id from rank 0 to the other ranks."""
@@ -109,9 +113,26 @@ class ShardedAttention:
         self._h = C.c_void_p()
         _capi.check(lib.hipgpt_shard_create(C.byref(self._h), ident, self.rank, self.world))
 
-    def forward(self, q, k, v, out, B: int, S: int, E: int, H: int, *, causal: bool = False, chunks: int = 1, gather: bool = True):
+    def output_tensor(self, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """Collective.  A [rows, cols] tensor in memory that the library allocated on every rank and mapped into every
+        other rank (hipgpt_shard_output_buffer): the `out` that forward(..., gather=GATHER_PEER_STORES) needs.  One per
+        object; asking again releases the previous one (collectively)."""
+        nbytes = rows * cols * torch.empty((), dtype=dtype).element_size()
+        ptr = C.c_void_p()
+        _capi.check(_capi.lib().hipgpt_shard_output_buffer(self._h, C.c_size_t(nbytes), C.byref(ptr)))
+        typestr = {torch.float32: "<f4", torch.bfloat16: "<u2", torch.float16: "<f2"}[dtype]
+
+        class _Raw:                                # the CUDA array interface: torch wraps the memory without copying it
+            __cuda_array_interface__ = {"shape": (rows, cols), "typestr": typestr, "data": (ptr.value, False), "version": 3, "strides": None}
+
+        t = torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
+        return t.view(dtype) if t.dtype != dtype else t
+
+    def forward(self, q, k, v, out, B: int, S: int, E: int, H: int, *, causal: bool = False, chunks: int = 1, gather=True):
         """q, k, v: this rank's batches (local_planes_chunked order), fp32 or bf16 CUDA tensors (or raw addresses with
-        elem_bytes given by `out`'s dtype); out: the whole [B*S, E] output.  Asynchronous on torch's current stream."""
+        elem_bytes given by `out`'s dtype); out: the whole [B*S, E] output.  Asynchronous on torch's current stream.
+        gather: False / True (NCCL all-gather per chunk) / GATHER_PEER_STORES (the library's own copy kernel into the
+        peers' buffers; `out` must come from output_tensor)."""
         esz = out.element_size()
         ptr = lambda t: t if isinstance(t, int) else t.data_ptr()
         _capi.check(_capi.lib().hipgpt_mha_forward_sharded(self._h, ptr(q), ptr(k), ptr(v), out.data_ptr(), B, S, E, H, int(causal),
@@ -123,6 +144,8 @@ class ShardedAttention:
             self._h = C.c_void_p()
 
     def __del__(self):
+        if sys is None or sys.is_finalizing():                    # releasing the mapped buffers is a collective: not at interpreter exit
+            return
         try:
             self.close()
         except Exception:

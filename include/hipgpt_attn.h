@@ -291,7 +291,22 @@ HIPGPT_API int hipgpt_gpt_set_mode(hipgpt_gpt *g, int mode);
  *                             finally waits for the last gather.  gather = 0 leaves only this rank's batches valid.
  *                             elem_bytes 4 = fp32 planes, 2 = bf16 planes (head_dim 64).  Results are the bits of the
  *                             unsharded call.
+ *                             gather = HIPGPT_GATHER_PEER_STORES (2): the same result without the collective's kernels:
+ *                             d_out must lie in the buffer of hipgpt_shard_output_buffer, which every rank has mapped
+ *                             from every other; after a chunk's kernels a small copy kernel of this library stores
+ *                             the chunk into the peers' buffers over NVLink, beside the next chunk's arithmetic (its
+ *                             blocks fit on SMs that attention blocks occupy; NCCL's do not).  A collective of four
+ *                             bytes per rank before the first and after the last copy orders the ranks: none writes
+ *                             into a peer that has not reached the call on its `stream`, and `stream` continues once
+ *                             every rank's copies have landed.  World size at most 8.
+ *   hipgpt_shard_output_buffer  collective: allocates `bytes` of device memory on every rank (the same size on all),
+ *                             exchanges inter-process memory handles and maps the peers' buffers; *d_out is this
+ *                             rank's.  One per context; a second call, and hipgpt_shard_destroy, release the first
+ *                             (collectively).
  */
+#define HIPGPT_GATHER_NONE        0
+#define HIPGPT_GATHER_NCCL        1
+#define HIPGPT_GATHER_PEER_STORES 2
 typedef struct hipgpt_shard_ctx hipgpt_shard_ctx;
 HIPGPT_API int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end);
 HIPGPT_API int hipgpt_shard_chunk_range(int B, int world, int rank, int chunks, int chunk, int *b_begin, int *b_end);
@@ -300,6 +315,7 @@ HIPGPT_API int hipgpt_shard_create(hipgpt_shard_ctx **out, const void *id128, in
 HIPGPT_API void hipgpt_shard_destroy(hipgpt_shard_ctx *ctx);
 HIPGPT_API int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *ctx, const void *d_q, const void *d_k, const void *d_v, void *d_out,
                                int B, int S, int E, int H, int causal, int elem_bytes, int chunks, int gather, void *stream);
+HIPGPT_API int hipgpt_shard_output_buffer(hipgpt_shard_ctx *ctx, size_t bytes, void **d_out);
 HIPGPT_API int hipgpt_shard_nccl_version(void);
 
 /*

@@ -1,6 +1,6 @@
 """The library's multi-GPU driver on two real GPUs: each rank computes its chunks of batches, the chunks are
-all-gathered in place by NCCL while the next chunk computes, and every rank must end with exactly the bits of
-the unsharded call.  Skipped on a box with one GPU.  No rank leaves mid-step, nothing is made to fail."""
+all-gathered in place by NCCL while the next chunk computes (or stored into the peers' mapped buffers by the
+library's own copy kernel), and every rank must end with exactly the bits of the unsharded call.  Skipped on a box with one GPU.  No rank leaves mid-step, nothing is made to fail."""
 import os
 import socket
 
@@ -45,6 +45,15 @@ def _worker(rank, world, port, ret):
                 sh.forward(loc[0], loc[1], loc[2], out, B, S, E, H, causal=causal, chunks=chunks, gather=True)
                 torch.cuda.synchronize()
                 ok = ok and bool(torch.equal(out, whole))
+                # the library's own transport: stores into the peers' mapped buffers instead of the collective's kernels
+                pout = sh.output_tensor(B * S, E, dtype)
+                pout.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()                       # every rank's buffer is filled before any peer writes into it
+                for _ in range(2):                   # twice: the second call writes over a buffer the peers have just read
+                    sh.forward(loc[0], loc[1], loc[2], pout, B, S, E, H, causal=causal, chunks=chunks, gather=sharding.GATHER_PEER_STORES)
+                    torch.cuda.synchronize()
+                    ok = ok and bool(torch.equal(pout, whole))
                 # without the gather only this rank's batches are written
                 out2 = torch.full((B * S, E), float("nan"), device="cuda", dtype=dtype)
                 sh.forward(loc[0], loc[1], loc[2], out2, B, S, E, H, causal=causal, chunks=chunks, gather=False)
