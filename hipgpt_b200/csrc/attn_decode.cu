@@ -48,6 +48,8 @@ decode_split_vec_kernel(const float *__restrict__ q, const float *__restrict__ k
                         float *__restrict__ out, float *__restrict__ scratch,
                         int H, int D, int ctx, int cap, int nsplit, float qscale, const int *__restrict__ pos_ptr)
 {
+    dependency_wait();                             // overlapped launch: nothing is read before the kernel before this one has completed
+    dependents_may_start();
     if (pos_ptr) ctx = *pos_ptr + 1;               // context length kept on the device (replayed CUDA graphs)
     constexpr int KPW = 32 / LPK;                  // keys per warp and step
     __shared__ float sm[kWarps][LPK][6];
@@ -135,6 +137,8 @@ decode_split_scalar_kernel(const float *__restrict__ q, const float *__restrict_
                            float *__restrict__ out, float *__restrict__ scratch,
                            int H, int D, int ctx, int cap, int nsplit, float qscale, const int *__restrict__ pos_ptr)
 {
+    dependency_wait();
+    dependents_may_start();
     if (pos_ptr) ctx = *pos_ptr + 1;
     constexpr int EPL = kMaxD / 32;
     __shared__ float sm_o[kWarps][kMaxD];
@@ -204,6 +208,8 @@ decode_split_scalar_kernel(const float *__restrict__ q, const float *__restrict_
 __global__ void __launch_bounds__(kThreads)
 decode_combine_kernel(const float *__restrict__ scratch, float *__restrict__ out, int H, int D, int nsplit)
 {
+    dependency_wait();
+    dependents_may_start();
     const int bh = blockIdx.x;
     const int b = bh / H, h = bh % H;
     const int stride = rec_stride(D);
@@ -246,19 +252,24 @@ int launch_decode(const float *q, const float *kc, const float *vc, float *out, 
     if ((long long)B * H > 65535) return fail(HIPGPT_ERR_BAD_ARG, "B*H = %lld exceeds 65535 rows per launch", (long long)B * H);
     const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
     const dim3 grid(nsplit, B * H);
+    // Overlapped launches: a kernel's blocks are placed while the kernel before it on the stream drains, and wait for it
+    // before they read anything (the first statement of every kernel here).
+    cudaError_t le = cudaSuccess;
     if (D % 4 == 0 && D <= 128) {
         if (D <= 32)
-            decode_split_vec_kernel<8><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
+            le = launch_overlapped(decode_split_vec_kernel<8>, grid, dim3(kThreads), 0, st, q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
         else if (D <= 64)
-            decode_split_vec_kernel<16><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
+            le = launch_overlapped(decode_split_vec_kernel<16>, grid, dim3(kThreads), 0, st, q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
         else
-            decode_split_vec_kernel<32><<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
+            le = launch_overlapped(decode_split_vec_kernel<32>, grid, dim3(kThreads), 0, st, q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
     } else {
-        decode_split_scalar_kernel<<<grid, kThreads, 0, st>>>(q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
+        le = launch_overlapped(decode_split_scalar_kernel, grid, dim3(kThreads), 0, st, q, kc, vc, out, scratch, H, D, ctx, cap, nsplit, qscale, pos_ptr);
     }
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "decode_split_kernel launch: %s", cudaGetErrorString(le));
     int rc = check_launch("decode_split_kernel");
     if (rc != HIPGPT_OK || nsplit == 1) return rc;
-    decode_combine_kernel<<<B * H, kThreads, 0, st>>>(scratch, out, H, D, nsplit);
+    le = launch_overlapped(decode_combine_kernel, dim3(B * H), dim3(kThreads), 0, st, (const float *)scratch, out, H, D, nsplit);
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "decode_combine_kernel launch: %s", cudaGetErrorString(le));
     return check_launch("decode_combine_kernel");
 }
 

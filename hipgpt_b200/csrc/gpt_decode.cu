@@ -55,6 +55,8 @@ __global__ void embed_kernel(const int *__restrict__ prompts, int n_prompt, cons
                              const int *__restrict__ pos_ptr, const float *__restrict__ tok, const float *__restrict__ pos,
                              float *__restrict__ x, int E, int V)
 {
+    dependency_wait();                               // overlapped launch: nothing is read before the kernel before this one has completed
+    dependents_may_start();
     const int b = blockIdx.x;
     const int p = *pos_ptr;
     const int id = p < n_prompt ? prompts[(size_t)b * n_prompt + p] : ids[b];
@@ -181,6 +183,8 @@ matmul_rows_kernel(const float *__restrict__ A, int lda, const float *__restrict
                    const float *__restrict__ W, const float *__restrict__ bias, MatmulOut o, int M, int K, int N, int relu)
 {
     extern __shared__ float a_s[];
+    dependency_wait();
+    dependents_may_start();
     matmul_rows_body<false>(blockIdx.x, blockIdx.y, a_s, A, lda, ln_g, ln_b, W, bias, o, M, K, N, relu);
 }
 
@@ -192,6 +196,8 @@ argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ ids_nex
 {
     __shared__ float sv[256];
     __shared__ int si[256];
+    dependency_wait();
+    dependents_may_start();
     const int b = blockIdx.x;
     const float *row = logits + (size_t)b * V;
     float best = -INFINITY;
@@ -222,7 +228,12 @@ argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ ids_nex
     }
 }
 
-__global__ void advance_pos_kernel(int *pos_ptr) { *pos_ptr += 1; }
+__global__ void advance_pos_kernel(int *pos_ptr)
+{
+    dependency_wait();
+    dependents_may_start();
+    *pos_ptr += 1;
+}
 
 struct LayerW {
     const float *wqkv, *wo, *w1, *w2, *bqkv, *bo, *b1, *b2, *g1, *be1, *g2, *be2;
@@ -578,7 +589,8 @@ int matmul(const GptDecoder &g, const float *A, int lda, const float *ln_g, cons
 {
     const dim3 grid((N + 31) / 32, (M + kRowsPerBlock - 1) / kRowsPerBlock);
     const size_t smem = (size_t)kRowsPerBlock * (K + kSeg * 32) * sizeof(float);
-    matmul_rows_kernel<<<grid, 32 * kSeg, smem, g.stream>>>(A, lda, ln_g, ln_b, W, bias, o, M, K, N, relu);
+    const cudaError_t le = launch_overlapped(matmul_rows_kernel, grid, dim3(32 * kSeg), smem, g.stream, A, lda, ln_g, ln_b, W, bias, o, M, K, N, relu);
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "matmul_rows_kernel launch: %s", cudaGetErrorString(le));
     return check_launch("matmul_rows_kernel");
 }
 
@@ -590,7 +602,11 @@ MatmulOut plain_out(float *out, int ldo, const float *res) { return MatmulOut{ou
 int enqueue_step(GptDecoder &g, int B, int n_prompt, int n_new)
 {
     const int E = g.E, F = g.F, V = g.V, D = g.E / g.H;
-    embed_kernel<<<B, 128, 0, g.stream>>>(g.d_prompts, n_prompt, g.d_ids, g.d_pos, g.tok, g.pos, g.d_x, E, V);
+    // every launch of the step is an overlapped one (captured into the graph as programmatic dependencies): a kernel's
+    // blocks are placed while the kernel before it drains and wait for it before their first read
+    cudaError_t le = launch_overlapped(embed_kernel, dim3(B), dim3(128), 0, g.stream, (const int *)g.d_prompts, n_prompt, (const int *)g.d_ids, (const int *)g.d_pos,
+                                       (const float *)g.tok, (const float *)g.pos, g.d_x, E, V);
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "embed_kernel launch: %s", cudaGetErrorString(le));
     int rc = check_launch("embed_kernel");
     if (rc) return rc;
     const int ns = decode_splits(B, g.H, D, g.S);        // fixed for the whole graph; short contexts leave splits empty
@@ -606,9 +622,11 @@ int enqueue_step(GptDecoder &g, int B, int n_prompt, int n_new)
         if ((rc = matmul(g, g.d_ff, F, nullptr, nullptr, w.w2, w.b2, plain_out(g.d_x, E, g.d_x), B, F, E, 0))) return rc;
     }
     if ((rc = matmul(g, g.d_x, E, nullptr, nullptr, g.wout, nullptr, plain_out(g.d_logits, V, nullptr), B, E, V, 0))) return rc;
-    argmax_kernel<<<B, 256, 0, g.stream>>>(g.d_logits, V, g.d_ids, g.d_out, n_new, n_prompt, g.d_pos);
+    le = launch_overlapped(argmax_kernel, dim3(B), dim3(256), 0, g.stream, (const float *)g.d_logits, V, g.d_ids, g.d_out, n_new, n_prompt, (const int *)g.d_pos);
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "argmax_kernel launch: %s", cudaGetErrorString(le));
     if ((rc = check_launch("argmax_kernel"))) return rc;
-    advance_pos_kernel<<<1, 1, 0, g.stream>>>(g.d_pos);
+    le = launch_overlapped(advance_pos_kernel, dim3(1), dim3(1), 0, g.stream, g.d_pos);
+    if (le != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "advance_pos_kernel launch: %s", cudaGetErrorString(le));
     return check_launch("advance_pos_kernel");
 }
 
