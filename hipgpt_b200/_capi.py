@@ -34,6 +34,7 @@ SIGNATURES = {
     "hipgpt_mha_backward": (_i, [_vp] * 9 + [_sz, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_mha_backward_planes": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "hipgpt_matmul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hipgpt_matmul_tc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "hipgpt_layer_norm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "hipgpt_dropout": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "hipgpt_add_inplace": (_i, [_vp, _vp, C.c_longlong, _vp]),

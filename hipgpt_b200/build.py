@@ -21,7 +21,7 @@ LIB = os.path.join(LIBDIR, "libhipgpt_attn.so")
 OBJDIR = os.path.join(LIBDIR, "obj")
 
 SOURCES = ["attn_fwd_rows.cu", "attn_fwd_tc.cu", "attn_fwd_bf16.cu", "attn_fwd_tc16.cu", "attn_fwd_head.cu", "attn_fwd_generic.cu", "attn_unfused.cu", "attn_bwd.cu", "layer_ops.cu", "attn_decode.cu", "gpt_decode.cu", "probe.cu", "wait_probe.cu", "capi.cu",
-           "compat_launchers.cpp", "checkpoint.cpp", "sharded.cpp", "shard_push.cu"]
+           "compat_launchers.cpp", "checkpoint.cpp", "sharded.cpp", "shard_push.cu", "gemm_tc.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "-I", os.path.join(ROOT, "include"), "-I", CSRC]

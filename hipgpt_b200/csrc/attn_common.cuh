@@ -96,6 +96,10 @@ int launch_mha_backward(const float *g, const float *q, const float *k, const fl
                         float *dq, float *dk, float *dv, float *scratch, int B, int S, int E, int H, int causal, cudaStream_t st);
 // the launchers either side of attention (layer_ops.cu)
 int launch_matmul_exact(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st);
+// The same product on the tensor pipe with fp32-grade (not bit-identical) results (gemm_tc.cu); its status word and scratch.
+int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st);
+int gemm_tc_status_fetch(int *status);
+void gemm_tc_release_scratch();
 int launch_mha_generic(const float *q, const float *k, const float *v, float *out, float *probs,
                        int B, int S, int E, int H, int causal, cudaStream_t st);
 int launch_sdp(const float *Q, const float *K, float *scores, int B, int S, int D, cudaStream_t st);

@@ -149,10 +149,11 @@ static int fetch_status_words(int *status)
     if (rc == HIPGPT_OK) rc = bf16_status_fetch(&b);
     if (rc == HIPGPT_OK) rc = tc16_status_fetch(&d);
     if (rc == HIPGPT_OK) rc = head_status_fetch(&h);
-    int pr = 0;
+    int pr = 0, gm = 0;
     if (rc == HIPGPT_OK) rc = probe_status_fetch(&pr);
+    if (rc == HIPGPT_OK) rc = gemm_tc_status_fetch(&gm);
     if (rc != HIPGPT_OK) return rc;
-    *status = a ? a : (b ? 100 + b : (d ? 300 + d : (h ? 400 + h : (pr ? 900 + pr : 0))));
+    *status = a ? a : (b ? 100 + b : (d ? 300 + d : (h ? 400 + h : (gm ? 500 + gm : (pr ? 900 + pr : 0)))));
     return HIPGPT_OK;
 }
 
@@ -313,6 +314,7 @@ int hipgpt_mha_forward_bf16_host(const void *h_qkv, void *h_out, int B, int S, i
 void hipgpt_release_workspace(void)
 {
     tc16_release_scratch();
+    gemm_tc_release_scratch();
     std::lock_guard<std::mutex> lock(g_ws.mu);
     if (g_ws.dev) cudaFree(g_ws.dev);
     for (int i = 0; i < Workspace::kStreams; ++i) if (g_ws.streams[i]) { cudaStreamDestroy(g_ws.streams[i]); g_ws.streams[i] = nullptr; }

@@ -1,0 +1,385 @@
+// The projections either side of attention on the Blackwell tensor pipe (tcgen05 + TMEM) with fp32-grade results:
+//   C[M][K] = A[M][N] B[N][K] (+ bias[K]),  the reference's argument order, N the inner dimension
+// (HipGPT launch_matmul / launch_matmul_add_bias, src/hip_kernels.cpp:69-154; callers src/transformer_layer.cpp:217,220).
+// The exact mode (one accumulator per output, inner index ascending, FMA: bit-identical to the reference's order) is
+// hipgpt_matmul in layer_ops.cu; this is the fast mode: same operands, same output, 1e-5 instead of identical bits.
+//
+// Arithmetic (the scheme of the tiled attention kernel): every fp32 operand x is scaled by a power of two (exact) and cut
+// into hi (its 11 leading bits, exact in fp16) and lo = x - hi (rounded to fp16's 11 bits); a*b = a_hi*b_hi + a_hi*b_lo +
+// a_lo*b_hi as kind::f16 products with fp32 accumulation in the tensor core, the dropped a_lo*b_lo is 2^-22 relative.
+// Scales: one per row of A (range_scale of the row's largest magnitude) and one for the whole of B; both leave in the
+// epilogue.  An element of B more than 2^-20 below B's largest magnitude keeps fewer bits (its lo part becomes a
+// subnormal fp16); the exact mode is there for such operands.
+//
+// Three kinds of launches per call:
+//   gemm_amax_kernel     largest |B|  (B is at most a few MB here: one pass)
+//   gemm_pack_a_kernel   A -> per (128-row tile, 64-deep slice) the shared-memory image of a K-major operand stage with
+//                        128-byte swizzle: a block of A_hi rows and a block of A_lo rows (fp16); row scales to a vector
+//   gemm_pack_b_kernel   B -> per (64-deep slice, 128-column tile) the image of an N-major operand stage without
+//                        swizzle, columns [B_hi (128) | B_lo (128)]
+//   gemm_tc_kernel       one block per 128 x 128 output tile: a producer warp fetches whole stages with bulk copies
+//                        (three stages of 64 KB in flight), an issuing warp forms A_hi [B_hi | B_lo] (N = 256) and
+//                        A_lo B_hi (N = 128, onto the second half) for every slice, 8 instructions per slice, into 256
+//                        TMEM columns; four warps (thread = output row = TMEM lane) add the halves, take the scales
+//                        out, add the bias and store.
+// Rows, columns and depth beyond the matrices are zeros in the images; stores are bounded by M and K.
+// Every wait is bounded: on expiry the block records a status code, skips its stores, frees its TMEM and returns.
+#include "tc_primitives.cuh"
+
+#include <math.h>
+
+#include <mutex>
+#include <vector>
+
+namespace hipgpt {
+namespace {
+
+constexpr int kTM = 128, kTN = 128, kTK = 64;     // output tile and depth of a slice
+constexpr int kStages = 3;
+constexpr int kABlk = kTM * 128;                  // bytes of one block of an A stage: 128 rows of 64 fp16
+constexpr int kAStage = 2 * kABlk;                // [A_hi | A_lo]
+constexpr int kBStage = kTK * 2 * kTN * 2;        // 64 deep x [B_hi (128) | B_lo (128)] fp16
+constexpr int kGroupStride = 2 * kTN * 16;        // bytes between groups of 8 reduction rows of a B stage (32 column blocks of 128 bytes)
+constexpr int kGemmThreads = 192;                 // 4 epilogue warps, a producer warp, an issuing warp
+constexpr int kTmemCols = 256;
+constexpr size_t kGemmSmem = (size_t)kStages * (kAStage + kBStage) + 1024;
+
+__device__ int g_gemm_status = 0;
+
+__device__ __forceinline__ float pow2_scale(float amax)
+{
+    // the power of two that brings `amax` into [2^14, 2^15); 1 for zero, infinite or NaN input
+    if (!(amax > 0.0f && amax <= 3.0e38f)) return 1.0f;
+    const int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+    int sh = 14 - e;
+    sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+    return __uint_as_float((uint32_t)(127 + sh) << 23);
+}
+__device__ __forceinline__ float pow2_inverse(float p) { return __uint_as_float(0x7F000000u - __float_as_uint(p)); }
+
+// largest |x| of n floats -> *out (zeroed before the launch; non-negative floats order like their bit patterns)
+__global__ void __launch_bounds__(256) gemm_amax_kernel(const float *__restrict__ x, size_t n, float *out)
+{
+    dependents_may_start();
+    float m = 0.0f;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) m = fmaxf(m, fabsf(__ldg(x + i)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(reinterpret_cast<unsigned *>(out), __float_as_uint(m));
+}
+
+// One warp per row of A (rows up to the padded count: rows past M are zeros).  A lane owns runs of 8 consecutive values
+// (one 16-byte chunk of fp16).  Image: stage (mt, kt) at ((mt * KT + kt) * kAStage); block 0 = hi, block 1 = lo; row r,
+// chunk c at r * 128 + ((c ^ (r & 7)) * 16).
+__global__ void __launch_bounds__(128) gemm_pack_a_kernel(const float *__restrict__ A, uint8_t *__restrict__ img, float *__restrict__ row_inv,
+                                                           int M, int N, int KT)
+{
+    // overlapped launch: placed while the kernel before it drains; waiting for it here also orders the product kernel,
+    // which waits for this one, after everything before
+    dependency_wait();
+    dependents_may_start();
+    const int lane = threadIdx.x & 31;
+    const int m = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const bool live = m < M;
+    const float *row = A + (size_t)(live ? m : 0) * N;
+    const bool vec = (N & 3) == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0;
+    auto load8 = [&](int k0, float (&v)[8]) {
+        if (live && vec && k0 + 8 <= N) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(row + k0)), b = __ldg(reinterpret_cast<const float4 *>(row + k0) + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (live && k0 + j < N) ? __ldg(row + k0 + j) : 0.0f;
+        }
+    };
+    const int depth = KT * kTK;
+    float amax = 0.0f;
+    for (int k0 = lane * 8; k0 < depth; k0 += 256) {
+        float v[8];
+        load8(k0, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = pow2_scale(amax);
+    if (lane == 0) row_inv[m] = pow2_inverse(s);
+    const int mt = m / kTM, r = m % kTM;
+    for (int k0 = lane * 8; k0 < depth; k0 += 256) {             // the row is read again: it is in L1 / L2
+        float v[8];
+        load8(k0, v);
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a = v[2 * j] * s, b = v[2 * j + 1] * s;
+            const float ah = tf32_hi(a), bh = tf32_hi(b);
+            hi[j] = pack_f16(ah, bh);
+            lo[j] = pack_f16(a - ah, b - bh);
+        }
+        const int kt = k0 / kTK, c = (k0 % kTK) >> 3;
+        uint8_t *stage = img + ((size_t)mt * KT + kt) * kAStage;
+        *reinterpret_cast<uint4 *>(stage + sw128(r, c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4 *>(stage + kABlk + sw128(r, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+// One block per (64-deep slice kt, 128-column tile nt) of B [N][K] (N inner, K the output width).  A thread owns 8
+// consecutive columns of one reduction row.  Image: stage (nt, kt) at ((nt * KT + kt) * kBStage); reduction row r,
+// column block cb (8 columns of [B_hi (128) | B_lo (128)]) at (r / 8) * kGroupStride + cb * 128 + (r % 8) * 16.
+__global__ void __launch_bounds__(128) gemm_pack_b_kernel(const float *__restrict__ B, const float *__restrict__ amax, uint8_t *__restrict__ img,
+                                                           int N, int K, int KT)
+{
+    dependency_wait();                               // the largest magnitude has been found
+    dependents_may_start();
+    const int kt = blockIdx.x, nt = blockIdx.y;
+    const float s = pow2_scale(*amax);
+    const int cb = threadIdx.x & 15, r0 = threadIdx.x >> 4;      // 16 threads cover the 128 columns of a row, 8 rows per pass
+    const bool vec = (K & 3) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
+    uint8_t *stage = img + ((size_t)nt * KT + kt) * kBStage;
+#pragma unroll
+    for (int pass = 0; pass < kTK / 8; ++pass) {
+        const int r = r0 + 8 * pass;
+        const int n = kt * kTK + r, c0 = nt * kTN + 8 * cb;
+        float v[8];
+        if (n < N && vec && c0 + 8 <= K) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(B + (size_t)n * K + c0)), b = __ldg(reinterpret_cast<const float4 *>(B + (size_t)n * K + c0) + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (n < N && c0 + j < K) ? __ldg(B + (size_t)n * K + c0 + j) : 0.0f;
+        }
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a = v[2 * j] * s, b = v[2 * j + 1] * s;
+            const float ah = tf32_hi(a), bh = tf32_hi(b);
+            hi[j] = pack_f16(ah, bh);
+            lo[j] = pack_f16(a - ah, b - bh);
+        }
+        uint8_t *dst = stage + (r >> 3) * kGroupStride + (r & 7) * 16;
+        *reinterpret_cast<uint4 *>(dst + cb * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4 *>(dst + (16 + cb) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+__device__ __noinline__ void gemm_wait_slow(uint64_t *bar, uint32_t parity, int site, volatile int *abort_flag)
+{
+    if (!mbar_wait(bar, parity)) {
+        *abort_flag = 1;
+        atomicCAS(&g_gemm_status, 0, site);
+    }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bimg, const float *__restrict__ row_inv, const float *__restrict__ b_amax,
+               const float *__restrict__ bias, float *__restrict__ C, int M, int K, int KT)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_s = base;                              // [stage][A_hi block | A_lo block]
+    uint8_t *b_s = base + kStages * kAStage;          // [stage][64 deep][B_hi | B_lo]
+    __shared__ uint64_t full[kStages], empty[kStages], acc_done;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // warp-uniform for the compiler
+    const int nt = blockIdx.x, mt = blockIdx.y;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        mbar_init(&acc_done, 1);
+    }
+    __syncthreads();
+    // site codes in the status word: 1 stage landed, 2 stage free, 3 accumulator complete
+    auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
+        if (abort_flag || mbar_test(bar, parity)) return;
+        gemm_wait_slow(bar, parity, site, &abort_flag);
+    };
+
+    if (warp == 4) {
+        // ---- producer: whole stages by bulk copies ----
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        dependents_may_start();
+        dependency_wait();                            // the pack kernels have completed
+        tc_fence_before();
+        __syncthreads();                              // TMEM allocated
+        for (int kt = 0; kt < KT; ++kt) {
+            const int s = kt % kStages;
+            if (kt >= kStages) wait(&empty[s], (uint32_t)((kt / kStages - 1) & 1), 2);       // the products that read the stage have completed
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&full[s], (uint32_t)(kAStage + kBStage));
+                const uint8_t *asrc = aimg + ((size_t)mt * KT + kt) * kAStage, *bsrc = bimg + ((size_t)nt * KT + kt) * kBStage;
+                bulk_load(a_s + s * kAStage, asrc, kABlk, &full[s]);
+                bulk_load(a_s + s * kAStage + kABlk, asrc + kABlk, kABlk, &full[s]);
+                bulk_load(b_s + s * kBStage, bsrc, kBStage / 2, &full[s]);
+                bulk_load(b_s + s * kBStage + kBStage / 2, bsrc + kBStage / 2, kBStage / 2, &full[s]);
+            }
+            __syncwarp();
+        }
+        __syncwarp();
+        tc_fence_before();
+        __syncthreads();                              // the output has been read from TMEM
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"(kTmemCols) : "memory");
+        return;
+    }
+    if (warp == 5) {
+        // ---- issuing warp: stays converged, elects the lane per instruction ----
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+        const uint32_t tmem = tmem_base_slot;
+        constexpr uint32_t id_wide = idesc_f16(kTM, 2 * kTN) | (1u << 16);       // A_hi x [B_hi | B_lo], B N-major
+        constexpr uint32_t id_half = idesc_f16(kTM, kTN) | (1u << 16);           // A_lo x B_hi
+        for (int kt = 0; kt < KT; ++kt) {
+            const int s = kt % kStages;
+            wait(&full[s], (uint32_t)((kt / kStages) & 1), 1);
+            tc_fence_after();
+            const uint64_t da_hi = make_desc(smem_u32(a_s + s * kAStage), 16, 1024, 2);
+            const uint64_t da_lo = make_desc(smem_u32(a_s + s * kAStage + kABlk), 16, 1024, 2);
+            // N-major B without swizzle: lbo = bytes between groups of 8 reduction rows, sbo = bytes between blocks of 8 columns
+            const uint64_t db = make_desc(smem_u32(b_s + s * kBStage), kGroupStride, 128, 0);
+#pragma unroll
+            for (int k = 0; k < kTK / 16; ++k)        // 16 deep = 32 bytes of an A row = two groups of B
+                if (elect_one()) mma_h_ss(tmem, da_hi + (uint64_t)(2 * k), db + (uint64_t)(k * 2 * (kGroupStride >> 4)), id_wide, (kt | k) ? 1u : 0u);
+#pragma unroll
+            for (int k = 0; k < kTK / 16; ++k)
+                if (elect_one()) mma_h_ss(tmem + kTN, da_lo + (uint64_t)(2 * k), db + (uint64_t)(k * 2 * (kGroupStride >> 4)), id_half, 1u);
+            if (elect_one()) tc_commit(&empty[s]);
+        }
+        if (elect_one()) tc_commit(&acc_done);
+        __syncwarp();
+        tc_fence_before();
+        __syncthreads();
+        return;
+    }
+
+    // ---- epilogue warps: thread = output row = TMEM lane ----
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const int r = warp * 32 + lane, m = mt * kTM + r;
+    const uint32_t lane_base = tmem_base_slot + ((uint32_t)(warp * 32) << 16);
+    const float unscale = (m < M ? __ldg(row_inv + m) : 0.0f) * pow2_inverse(pow2_scale(__ldg(b_amax)));
+    wait(&acc_done, 0, 3);
+    tc_fence_after();
+    const int c_base = nt * kTN;
+    const bool store = !abort_flag && m < M;
+    float *dst = C + (size_t)(m < M ? m : 0) * K + c_base;
+    const bool vec = (K & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTN; c0 += 16) {
+        float a[16], b[16];
+        tmem_ld16(lane_base + c0, a);                 // A_hi B_hi
+        tmem_ld16(lane_base + kTN + c0, b);           // the correction terms
+        tmem_wait_ld();
+        if (!store || c_base + c0 >= K) continue;
+        float o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int c = c_base + c0 + j;
+            o[j] = (a[j] + b[j]) * unscale + ((bias && c < K) ? __ldg(bias + c) : 0.0f);
+        }
+        if (vec && c_base + c0 + 16 <= K) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(dst + c0)[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (c_base + c0 + j < K) dst[c0 + j] = o[j];
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+}
+
+// The packed operands of a call live in a buffer of the library, one per device and stream; it grows to the largest call.
+struct GemmScratch {
+    std::mutex mu;
+    struct Entry { int dev; cudaStream_t st; uint8_t *buf; size_t cap; };
+    std::vector<Entry> entries;
+    int get(int dev, cudaStream_t st, size_t need, uint8_t **out)
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        Entry *e = nullptr;
+        for (auto &x : entries) if (x.dev == dev && x.st == st) e = &x;
+        if (!e) { entries.push_back({dev, st, nullptr, 0}); e = &entries.back(); }
+        if (e->cap < need) {
+            if (e->buf) cudaFree(e->buf);            // waits for the kernels that read it
+            e->buf = nullptr;
+            e->cap = 0;
+            const cudaError_t err = cudaMalloc(&e->buf, need);
+            if (err != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMalloc(%zu) for the packed operands: %s", need, cudaGetErrorString(err));
+            e->cap = need;
+        }
+        *out = e->buf;
+        return HIPGPT_OK;
+    }
+    void release()
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (auto &x : entries) if (x.buf) cudaFree(x.buf);
+        entries.clear();
+    }
+};
+GemmScratch g_gemm;
+
+}  // namespace
+
+void gemm_tc_release_scratch() { g_gemm.release(); }
+
+int gemm_tc_status_fetch(int *status)
+{
+    int v = 0;
+    const cudaError_t e = cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(v));
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+    if (v) { const int zero = 0; cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero)); }
+    *status = v;
+    return HIPGPT_OK;
+}
+
+// C[M][K] = A[M][N] B[N][K] (+ bias), fp32-grade on the tensor pipe.  C must not alias A or B.
+int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st)
+{
+    const int MT = (M + kTM - 1) / kTM, NT = (K + kTN - 1) / kTN, KT = (N + kTK - 1) / kTK;
+    if (MT > 65535) return fail(HIPGPT_ERR_BAD_ARG, "M = %d is beyond %d rows per call", M, 65535 * kTM);
+    if (KT == 0) return fail(HIPGPT_ERR_BAD_ARG, "an inner dimension of 0");
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    const size_t abytes = (size_t)MT * KT * kAStage, bbytes = (size_t)NT * KT * kBStage, rbytes = ((size_t)MT * kTM * sizeof(float) + 255) & ~(size_t)255;
+    uint8_t *scratch = nullptr;
+    int rc = g_gemm.get(dev, st, abytes + bbytes + rbytes + 256, &scratch);
+    if (rc != HIPGPT_OK) return rc;
+    uint8_t *aimg = scratch, *bimg = scratch + abytes;
+    float *row_inv = reinterpret_cast<float *>(scratch + abytes + bbytes), *b_amax = reinterpret_cast<float *>(scratch + abytes + bbytes + rbytes);
+    static bool attr_set = false;
+    if (!attr_set) {
+        e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    e = cudaMemsetAsync(b_amax, 0, sizeof(float), st);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    const size_t nb = (size_t)N * K;
+    size_t ablocks = (nb + 256 * 8 - 1) / (256 * 8);
+    if (ablocks > 1184) ablocks = 1184;
+    gemm_amax_kernel<<<(unsigned)ablocks, 256, 0, st>>>(B, nb, b_amax);
+    rc = check_launch("gemm_amax_kernel");
+    if (rc != HIPGPT_OK) return rc;
+    e = launch_overlapped(gemm_pack_b_kernel, dim3((unsigned)KT, (unsigned)NT), dim3(128), 0, st, B, (const float *)b_amax, bimg, N, K, KT);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_b_kernel launch: %s", cudaGetErrorString(e));
+    rc = check_launch("gemm_pack_b_kernel");
+    if (rc != HIPGPT_OK) return rc;
+    e = launch_overlapped(gemm_pack_a_kernel, dim3((unsigned)(MT * kTM / 4)), dim3(128), 0, st, A, aimg, row_inv, M, N, KT);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_a_kernel launch: %s", cudaGetErrorString(e));
+    rc = check_launch("gemm_pack_a_kernel");
+    if (rc != HIPGPT_OK) return rc;
+    e = launch_overlapped(gemm_tc_kernel, dim3((unsigned)NT, (unsigned)MT), dim3(kGemmThreads), kGemmSmem, st, (const uint8_t *)aimg, (const uint8_t *)bimg,
+                          (const float *)row_inv, (const float *)b_amax, bias, C, M, K, KT);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_tc_kernel launch: %s", cudaGetErrorString(e));
+    return check_launch("gemm_tc_kernel");
+}
+
+}  // namespace hipgpt

@@ -283,6 +283,16 @@ int hipgpt_matmul(const float *d_A, const float *d_B, const float *d_bias, float
     return launch_matmul_exact(d_A, d_B, d_bias, d_C, M, N, K, static_cast<cudaStream_t>(stream));
 }
 
+int hipgpt_matmul_tc(const float *d_A, const float *d_B, const float *d_bias, float *d_C, int M, int N, int K, void *stream)
+{
+    if (M < 0 || N < 0 || K < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: M=%d N=%d K=%d", M, N, K);
+    if (M == 0 || K == 0) return HIPGPT_OK;
+    if (!d_C || (N > 0 && (!d_A || !d_B))) return fail(HIPGPT_ERR_NULL, "A, B and C must not be NULL");
+    if (N == 0) return launch_matmul_exact(d_A, d_B, d_bias, d_C, M, N, K, static_cast<cudaStream_t>(stream));   // bias (or zeros) only
+    if (d_C == d_A || d_C == d_B) return fail(HIPGPT_ERR_UNSUPPORTED, "the tensor-core product does not work in place; hipgpt_matmul does (K <= 256)");
+    return launch_matmul_tc(d_A, d_B, d_bias, d_C, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
 int hipgpt_layer_norm(const float *d_in, float *d_out, const float *d_gamma, const float *d_beta, int rows, int E, void *stream)
 {
     if (rows < 0 || E < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: rows=%d E=%d", rows, E);

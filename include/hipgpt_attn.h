@@ -168,6 +168,11 @@ HIPGPT_API int hipgpt_mha_backward_planes(const float *d_grad_out, const float *
  *                            k ascending, fused multiply-add, bias added once at the end, so bit-identical to
  *                            that arithmetic.  d_A == d_C (the reference's in-place output projection,
  *                            src/transformer_layer.cpp:220) is allowed when K <= 256 and K % 4 == 0.
+ *   hipgpt_matmul_tc         the same product on the tensor pipe (tcgen05): every operand cut into fp16 pieces after a
+ *                            power-of-two scaling (per row of A, one for B), three products per product, fp32
+ *                            accumulation: 1e-5 on unit-scale data instead of identical bits, several times the
+ *                            rate.  Not in place.  The packed operands live in a buffer of the library (per device
+ *                            and stream; hipgpt_release_workspace() frees it).
  *   hipgpt_layer_norm        replaces launch_layer_norm_forward (src/hip_kernels.cpp:757-848), eps 1e-5;
  *                            agrees with the reference's 64-lane reduction order to rounding (~1e-7).
  *   hipgpt_dropout           replaces launch_dropout_forward (src/hip_kernels.cpp:944-970): the mask depends
@@ -179,6 +184,7 @@ HIPGPT_API int hipgpt_mha_backward_planes(const float *d_grad_out, const float *
  *                            (launch_embedding_lookup, src/hip_kernels.cpp:537-599)
  */
 HIPGPT_API int hipgpt_matmul(const float *d_A, const float *d_B, const float *d_bias, float *d_C, int M, int N, int K, void *stream);
+HIPGPT_API int hipgpt_matmul_tc(const float *d_A, const float *d_B, const float *d_bias, float *d_C, int M, int N, int K, void *stream);
 HIPGPT_API int hipgpt_layer_norm(const float *d_in, float *d_out, const float *d_gamma, const float *d_beta, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_dropout(const float *d_in, float *d_out, float *d_mask, float p, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_add_inplace(float *d_a, const float *d_b, long long n, void *stream);

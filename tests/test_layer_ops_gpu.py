@@ -39,6 +39,32 @@ def test_matmul_is_bit_identical_to_the_reference_order(M, N, K, bias):
     assert np.array_equal(dC.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("M,N,K,bias", [(8192, 256, 768, True), (300, 256, 768, True), (64, 1024, 256, True), (257, 256, 1024, False), (130, 64, 5000, False),
+                                        (33, 100, 20, True), (5, 7, 3, False), (1, 256, 256, True), (129, 65, 129, True)])
+def test_tensor_core_matmul_is_fp32_grade(M, N, K, bias):
+    """hipgpt_matmul_tc: the projections on the tensor pipe.  Not the reference's summation order, so not its bits: the
+    bar is 1e-5 relative to the largest output against a float64 product (the exact-order kernel's own distance from
+    float64 on these shapes is ~1e-6), for unit-scale operands and for operands far outside fp16's range."""
+    lib = _capi.lib()
+    for sa, sw in ((1.0, 0.1), (1e6, 1e-9), (3e-7, 2e4)):
+        A, W = synth.normal(1, (M, N)) * np.float32(sa), synth.normal(2, (N, K)) * np.float32(sw)
+        b = (synth.normal(3, (K,)) * np.float32(sa * sw)) if bias else None
+        want = A.astype(np.float64) @ W.astype(np.float64) + (b.astype(np.float64) if bias else 0.0)
+        dA, dW, dC = dev(A), dev(W), torch.full((M, K), float("nan"), device="cuda")
+        db = dev(b) if bias else None
+        _capi.check(lib.hipgpt_matmul_tc(dA.data_ptr(), dW.data_ptr(), db.data_ptr() if bias else None, dC.data_ptr(), M, N, K, _st()))
+        torch.cuda.synchronize()
+        st = C.c_int(-1)
+        _capi.check(lib.hipgpt_kernel_status(C.byref(st)))
+        assert st.value == 0
+        got = dC.cpu().numpy().astype(np.float64)
+        assert np.isfinite(got).all()
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max(), (sa, sw)
+    # in place is refused (the exact kernel supports it)
+    sq = torch.zeros((64, 64), device="cuda")
+    assert lib.hipgpt_matmul_tc(sq.data_ptr(), sq.data_ptr(), None, sq.data_ptr(), 64, 64, 64, _st()) == _capi.ERR_UNSUPPORTED
+
+
 def test_matmul_in_place_like_the_layers_output_projection():
     """src/transformer_layer.cpp:220 passes d_attn_output_ as both A and C."""
     lib = _capi.lib()
