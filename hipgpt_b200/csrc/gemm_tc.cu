@@ -11,17 +11,18 @@
 // epilogue.  An element of B more than 2^-20 below B's largest magnitude keeps fewer bits (its lo part becomes a
 // subnormal fp16); the exact mode is there for such operands.
 //
-// Three kinds of launches per call:
+// Four kernels per call:
 //   gemm_amax_kernel     largest |B|  (B is at most a few MB here: one pass)
 //   gemm_pack_a_kernel   A -> per (128-row tile, 64-deep slice) the shared-memory image of a K-major operand stage with
 //                        128-byte swizzle: a block of A_hi rows and a block of A_lo rows (fp16); row scales to a vector
 //   gemm_pack_b_kernel   B -> per (64-deep slice, 128-column tile) the image of an N-major operand stage without
 //                        swizzle, columns [B_hi (128) | B_lo (128)]
-//   gemm_tc_kernel       one block per 128 x 128 output tile: a producer warp fetches whole stages with bulk copies
-//                        (three stages of 64 KB in flight), an issuing warp forms A_hi [B_hi | B_lo] (N = 256) and
-//                        A_lo B_hi (N = 128, onto the second half) for every slice, 8 instructions per slice, into 256
-//                        TMEM columns; four warps (thread = output row = TMEM lane) add the halves, take the scales
-//                        out, add the bias and store.
+//   gemm_tc_kernel       one block per SM, 128 x 128 output tiles in turn: a producer warp fetches whole stages with bulk
+//                        copies (three stages of 64 KB in flight, running on into the next tile), an issuing warp forms
+//                        A_hi [B_hi | B_lo] (N = 256) and A_lo B_hi (N = 128, onto the second half) for every slice, 8
+//                        instructions per slice, into one of two accumulators of 256 TMEM columns; four warps (thread =
+//                        output row = TMEM lane) add the halves, take the scales out, add the bias and store one tile
+//                        while the products of the next one run.
 // Rows, columns and depth beyond the matrices are zeros in the images; stores are bounded by M and K.
 // Every wait is bounded: on expiry the block records a status code, skips its stores, frees its TMEM and returns.
 #include "tc_primitives.cuh"
@@ -41,7 +42,7 @@ constexpr int kAStage = 2 * kABlk;                // [A_hi | A_lo]
 constexpr int kBStage = kTK * 2 * kTN * 2;        // 64 deep x [B_hi (128) | B_lo (128)] fp16
 constexpr int kGroupStride = 2 * kTN * 16;        // bytes between groups of 8 reduction rows of a B stage (32 column blocks of 128 bytes)
 constexpr int kGemmThreads = 192;                 // 4 epilogue warps, a producer warp, an issuing warp
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;                    // two accumulators of [A_hi B_hi (128) | corrections (128)]
 constexpr size_t kGemmSmem = (size_t)kStages * (kAStage + kBStage) + 1024;
 
 __device__ int g_gemm_status = 0;
@@ -62,7 +63,17 @@ __global__ void __launch_bounds__(256) gemm_amax_kernel(const float *__restrict_
 {
     dependents_may_start();
     float m = 0.0f;
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) m = fmaxf(m, fabsf(__ldg(x + i)));
+    const size_t tid = (size_t)blockIdx.x * 256 + threadIdx.x, nthr = (size_t)gridDim.x * 256;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const size_t n4 = n / 4;
+        for (size_t i = tid; i < n4; i += nthr) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + i);
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+        }
+        for (size_t i = 4 * n4 + tid; i < n; i += nthr) m = fmaxf(m, fabsf(__ldg(x + i)));
+    } else {
+        for (size_t i = tid; i < n; i += nthr) m = fmaxf(m, fabsf(__ldg(x + i)));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(reinterpret_cast<unsigned *>(out), __float_as_uint(m));
@@ -123,21 +134,20 @@ __global__ void __launch_bounds__(128) gemm_pack_a_kernel(const float *__restric
     }
 }
 
-// One block per (64-deep slice kt, 128-column tile nt) of B [N][K] (N inner, K the output width).  A thread owns 8
-// consecutive columns of one reduction row.  Image: stage (nt, kt) at ((nt * KT + kt) * kBStage); reduction row r,
+// One block per 8 reduction rows of a (64-deep slice kt, 128-column tile nt) of B [N][K] (N inner, K the output width).
+// A thread owns 8 consecutive columns of one reduction row.  Image: stage (nt, kt) at ((nt * KT + kt) * kBStage); reduction row r,
 // column block cb (8 columns of [B_hi (128) | B_lo (128)]) at (r / 8) * kGroupStride + cb * 128 + (r % 8) * 16.
 __global__ void __launch_bounds__(128) gemm_pack_b_kernel(const float *__restrict__ B, const float *__restrict__ amax, uint8_t *__restrict__ img,
                                                            int N, int K, int KT)
 {
     dependency_wait();                               // the largest magnitude has been found
     dependents_may_start();
-    const int kt = blockIdx.x, nt = blockIdx.y;
+    const int kt = blockIdx.x >> 3, pass = blockIdx.x & 7, nt = blockIdx.y;
     const float s = pow2_scale(*amax);
-    const int cb = threadIdx.x & 15, r0 = threadIdx.x >> 4;      // 16 threads cover the 128 columns of a row, 8 rows per pass
+    const int cb = threadIdx.x & 15, r0 = threadIdx.x >> 4;      // 16 threads cover the 128 columns of a row, 8 rows per block
     const bool vec = (K & 3) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
     uint8_t *stage = img + ((size_t)nt * KT + kt) * kBStage;
-#pragma unroll
-    for (int pass = 0; pass < kTK / 8; ++pass) {
+    {
         const int r = r0 + 8 * pass;
         const int n = kt * kTK + r, c0 = nt * kTN + 8 * cb;
         float v[8];
@@ -172,31 +182,33 @@ __device__ __noinline__ void gemm_wait_slow(uint64_t *bar, uint32_t parity, int 
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bimg, const float *__restrict__ row_inv, const float *__restrict__ b_amax,
-               const float *__restrict__ bias, float *__restrict__ C, int M, int K, int KT)
+               const float *__restrict__ bias, float *__restrict__ C, int M, int K, int KT, int NT, int ntiles)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *a_s = base;                              // [stage][A_hi block | A_lo block]
     uint8_t *b_s = base + kStages * kAStage;          // [stage][64 deep][B_hi | B_lo]
-    __shared__ uint64_t full[kStages], empty[kStages], acc_done;
+    __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // warp-uniform for the compiler
-    const int nt = blockIdx.x, mt = blockIdx.y;
 
     if (tid == 0) {
         abort_flag = 0;
         for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-        mbar_init(&acc_done, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
     }
     __syncthreads();
-    // site codes in the status word: 1 stage landed, 2 stage free, 3 accumulator complete
+    // site codes in the status word: 1 stage landed, 2 stage free, 3 accumulator complete, 4 accumulator drained
     auto wait = [&](uint64_t *bar, uint32_t parity, int site) {
         if (abort_flag || mbar_test(bar, parity)) return;
         gemm_wait_slow(bar, parity, site, &abort_flag);
     };
+    // The block takes output tiles blockIdx.x, + gridDim.x, ... (column tile fastest: blocks that run side by side share
+    // the rows of A).  Stages are counted through all tiles (g), accumulators alternate between two halves of TMEM, so
+    // the copies of the next tile and its products run while the four epilogue warps drain the tile before it.
 
     if (warp == 4) {
         // ---- producer: whole stages by bulk copies ----
@@ -206,22 +218,26 @@ gemm_tc_kernel(const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bim
         dependency_wait();                            // the pack kernels have completed
         tc_fence_before();
         __syncthreads();                              // TMEM allocated
-        for (int kt = 0; kt < KT; ++kt) {
-            const int s = kt % kStages;
-            if (kt >= kStages) wait(&empty[s], (uint32_t)((kt / kStages - 1) & 1), 2);       // the products that read the stage have completed
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&full[s], (uint32_t)(kAStage + kBStage));
-                const uint8_t *asrc = aimg + ((size_t)mt * KT + kt) * kAStage, *bsrc = bimg + ((size_t)nt * KT + kt) * kBStage;
-                bulk_load(a_s + s * kAStage, asrc, kABlk, &full[s]);
-                bulk_load(a_s + s * kAStage + kABlk, asrc + kABlk, kABlk, &full[s]);
-                bulk_load(b_s + s * kBStage, bsrc, kBStage / 2, &full[s]);
-                bulk_load(b_s + s * kBStage + kBStage / 2, bsrc + kBStage / 2, kBStage / 2, &full[s]);
+        int g = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+            const int nt = t % NT, mt = t / NT;
+            for (int kt = 0; kt < KT; ++kt, ++g) {
+                const int s = g % kStages;
+                if (g >= kStages) wait(&empty[s], (uint32_t)((g / kStages - 1) & 1), 2);     // the products that read the stage have completed
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&full[s], (uint32_t)(kAStage + kBStage));
+                    const uint8_t *asrc = aimg + ((size_t)mt * KT + kt) * kAStage, *bsrc = bimg + ((size_t)nt * KT + kt) * kBStage;
+                    bulk_load(a_s + s * kAStage, asrc, kABlk, &full[s]);
+                    bulk_load(a_s + s * kAStage + kABlk, asrc + kABlk, kABlk, &full[s]);
+                    bulk_load(b_s + s * kBStage, bsrc, kBStage / 2, &full[s]);
+                    bulk_load(b_s + s * kBStage + kBStage / 2, bsrc + kBStage / 2, kBStage / 2, &full[s]);
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
         __syncwarp();
         tc_fence_before();
-        __syncthreads();                              // the output has been read from TMEM
+        __syncthreads();                              // the last output has been read from TMEM
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"(kTmemCols) : "memory");
         return;
     }
@@ -233,23 +249,29 @@ gemm_tc_kernel(const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bim
         const uint32_t tmem = tmem_base_slot;
         constexpr uint32_t id_wide = idesc_f16(kTM, 2 * kTN) | (1u << 16);       // A_hi x [B_hi | B_lo], B N-major
         constexpr uint32_t id_half = idesc_f16(kTM, kTN) | (1u << 16);           // A_lo x B_hi
-        for (int kt = 0; kt < KT; ++kt) {
-            const int s = kt % kStages;
-            wait(&full[s], (uint32_t)((kt / kStages) & 1), 1);
+        int g = 0, i = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++i) {
+            const uint32_t acc = tmem + (uint32_t)((i & 1) * 2 * kTN);
+            if (i >= 2) wait(&acc_empty[i & 1], (uint32_t)((i / 2 - 1) & 1), 4);             // the epilogue has read this half's previous tile
             tc_fence_after();
-            const uint64_t da_hi = make_desc(smem_u32(a_s + s * kAStage), 16, 1024, 2);
-            const uint64_t da_lo = make_desc(smem_u32(a_s + s * kAStage + kABlk), 16, 1024, 2);
-            // N-major B without swizzle: lbo = bytes between groups of 8 reduction rows, sbo = bytes between blocks of 8 columns
-            const uint64_t db = make_desc(smem_u32(b_s + s * kBStage), kGroupStride, 128, 0);
+            for (int kt = 0; kt < KT; ++kt, ++g) {
+                const int s = g % kStages;
+                wait(&full[s], (uint32_t)((g / kStages) & 1), 1);
+                tc_fence_after();
+                const uint64_t da_hi = make_desc(smem_u32(a_s + s * kAStage), 16, 1024, 2);
+                const uint64_t da_lo = make_desc(smem_u32(a_s + s * kAStage + kABlk), 16, 1024, 2);
+                // N-major B without swizzle: lbo = bytes between groups of 8 reduction rows, sbo = bytes between blocks of 8 columns
+                const uint64_t db = make_desc(smem_u32(b_s + s * kBStage), kGroupStride, 128, 0);
 #pragma unroll
-            for (int k = 0; k < kTK / 16; ++k)        // 16 deep = 32 bytes of an A row = two groups of B
-                if (elect_one()) mma_h_ss(tmem, da_hi + (uint64_t)(2 * k), db + (uint64_t)(k * 2 * (kGroupStride >> 4)), id_wide, (kt | k) ? 1u : 0u);
+                for (int k = 0; k < kTK / 16; ++k)    // 16 deep = 32 bytes of an A row = two groups of B
+                    if (elect_one()) mma_h_ss(acc, da_hi + (uint64_t)(2 * k), db + (uint64_t)(k * 2 * (kGroupStride >> 4)), id_wide, (kt | k) ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < kTK / 16; ++k)
-                if (elect_one()) mma_h_ss(tmem + kTN, da_lo + (uint64_t)(2 * k), db + (uint64_t)(k * 2 * (kGroupStride >> 4)), id_half, 1u);
-            if (elect_one()) tc_commit(&empty[s]);
+                for (int k = 0; k < kTK / 16; ++k)
+                    if (elect_one()) mma_h_ss(acc + kTN, da_lo + (uint64_t)(2 * k), db + (uint64_t)(k * 2 * (kGroupStride >> 4)), id_half, 1u);
+                if (elect_one()) tc_commit(&empty[s]);
+            }
+            if (elect_one()) tc_commit(&acc_full[i & 1]);
         }
-        if (elect_one()) tc_commit(&acc_done);
         __syncwarp();
         tc_fence_before();
         __syncthreads();
@@ -260,35 +282,44 @@ gemm_tc_kernel(const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bim
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const int r = warp * 32 + lane, m = mt * kTM + r;
-    const uint32_t lane_base = tmem_base_slot + ((uint32_t)(warp * 32) << 16);
-    const float unscale = (m < M ? __ldg(row_inv + m) : 0.0f) * pow2_inverse(pow2_scale(__ldg(b_amax)));
-    wait(&acc_done, 0, 3);
-    tc_fence_after();
-    const int c_base = nt * kTN;
-    const bool store = !abort_flag && m < M;
-    float *dst = C + (size_t)(m < M ? m : 0) * K + c_base;
+    const float b_inv = pow2_inverse(pow2_scale(__ldg(b_amax)));
     const bool vec = (K & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+    int i = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++i) {
+        const int nt = t % NT, mt = t / NT;
+        const int r = warp * 32 + lane, m = mt * kTM + r;
+        const uint32_t lane_base = tmem_base_slot + ((uint32_t)(warp * 32) << 16) + (uint32_t)((i & 1) * 2 * kTN);
+        const float unscale = (m < M ? __ldg(row_inv + m) : 0.0f) * b_inv;
+        wait(&acc_full[i & 1], (uint32_t)((i / 2) & 1), 3);
+        tc_fence_after();
+        const int c_base = nt * kTN;
+        const bool store = !abort_flag && m < M;
+        float *dst = C + (size_t)(m < M ? m : 0) * K + c_base;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kTN; c0 += 16) {
-        float a[16], b[16];
-        tmem_ld16(lane_base + c0, a);                 // A_hi B_hi
-        tmem_ld16(lane_base + kTN + c0, b);           // the correction terms
-        tmem_wait_ld();
-        if (!store || c_base + c0 >= K) continue;
-        float o[16];
+        for (int c0 = 0; c0 < kTN; c0 += 16) {
+            float a[16], b[16];
+            tmem_ld16(lane_base + c0, a);             // A_hi B_hi
+            tmem_ld16(lane_base + kTN + c0, b);       // the correction terms
+            tmem_wait_ld();
+            if (!store || c_base + c0 >= K) continue;
+            float o[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int c = c_base + c0 + j;
-            o[j] = (a[j] + b[j]) * unscale + ((bias && c < K) ? __ldg(bias + c) : 0.0f);
+            for (int j = 0; j < 16; ++j) {
+                const int c = c_base + c0 + j;
+                o[j] = (a[j] + b[j]) * unscale + ((bias && c < K) ? __ldg(bias + c) : 0.0f);
+            }
+            if (vec && c_base + c0 + 16 <= K) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(dst + c0)[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) if (c_base + c0 + j < K) dst[c0 + j] = o[j];
+            }
         }
-        if (vec && c_base + c0 + 16 <= K) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(dst + c0)[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) if (c_base + c0 + j < K) dst[c0 + j] = o[j];
-        }
+        // this half of TMEM may take the tile after next
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[i & 1])) : "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -363,12 +394,12 @@ int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C
     e = cudaMemsetAsync(b_amax, 0, sizeof(float), st);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
     const size_t nb = (size_t)N * K;
-    size_t ablocks = (nb + 256 * 8 - 1) / (256 * 8);
+    size_t ablocks = (nb + 256 * 4 - 1) / (256 * 4);
     if (ablocks > 1184) ablocks = 1184;
     gemm_amax_kernel<<<(unsigned)ablocks, 256, 0, st>>>(B, nb, b_amax);
     rc = check_launch("gemm_amax_kernel");
     if (rc != HIPGPT_OK) return rc;
-    e = launch_overlapped(gemm_pack_b_kernel, dim3((unsigned)KT, (unsigned)NT), dim3(128), 0, st, B, (const float *)b_amax, bimg, N, K, KT);
+    e = launch_overlapped(gemm_pack_b_kernel, dim3((unsigned)(KT * (kTK / 8)), (unsigned)NT), dim3(128), 0, st, B, (const float *)b_amax, bimg, N, K, KT);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_b_kernel launch: %s", cudaGetErrorString(e));
     rc = check_launch("gemm_pack_b_kernel");
     if (rc != HIPGPT_OK) return rc;
@@ -376,8 +407,13 @@ int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_a_kernel launch: %s", cudaGetErrorString(e));
     rc = check_launch("gemm_pack_a_kernel");
     if (rc != HIPGPT_OK) return rc;
-    e = launch_overlapped(gemm_tc_kernel, dim3((unsigned)NT, (unsigned)MT), dim3(kGemmThreads), kGemmSmem, st, (const uint8_t *)aimg, (const uint8_t *)bimg,
-                          (const float *)row_inv, (const float *)b_amax, bias, C, M, K, KT);
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const long long ntiles = (long long)MT * NT;
+    if (ntiles > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "%lld output tiles are too many", ntiles);
+    const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);           // one block per SM, each takes tiles in turn
+    e = launch_overlapped(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), kGemmSmem, st, (const uint8_t *)aimg, (const uint8_t *)bimg,
+                          (const float *)row_inv, (const float *)b_amax, bias, C, M, K, KT, NT, (int)ntiles);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_tc_kernel launch: %s", cudaGetErrorString(e));
     return check_launch("gemm_tc_kernel");
 }
