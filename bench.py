@@ -22,6 +22,7 @@ Default workload: B=32 H=8 S=256 head_dim=32, fp32, causal, probabilities not st
             compute in chunks, and with the all-gather of the outputs beside it when N > 1 (NCCL, and
             the library's own stores into the peers' mapped buffers)
   cpu_baseline  the CPU oracle (a port of the reference arithmetic) on this box's host cores
+  decode, projections  (default run) the greedy generation driver, and the matmuls either side of attention
 
 With N > 1 (torchrun, one rank per GPU) every rank runs the same step on its own batches
 (batch-major shards of an N-times larger batch; no kernel reads another GPU's memory), and
@@ -189,6 +190,50 @@ def cpu_leg(cfg, causal, seconds, steps=None, warmup=0):
         info["reference_build_noncausal"] = {"tflops": flops_of(1, H, S, D, False) / tr / 1e12,
                                              "sample": "1 batch item, launch_multihead_attention compiled for the host"}
     return tf, info
+
+
+def projections_leg(lib):
+    """The projections either side of attention at the default workload's shapes (QKV: [B*S, E] x [E, 3E]; output: [B*S, E] x
+    [E, E], bias added): the exact-order kernel (bit-identical to the reference's summation order) and the tensor-core kernel
+    (fp32-grade), CUDA-event time per call over input batches that together exceed L2."""
+    import torch
+    c = synth.CONFIGS["c2"]
+    M, E = c["B"] * c["S"], c["H"] * c["D"]
+    st = torch.cuda.current_stream().cuda_stream
+    out = {}
+    for name, (N, K) in (("qkv", (E, 3 * E)), ("out", (E, E))):
+        sets = 8
+        A = torch.randn((sets, M, N), device="cuda")
+        W = torch.randn((N, K), device="cuda") * 0.05
+        b = torch.randn((K,), device="cuda")
+        Cc = torch.empty((sets, M, K), device="cuda")
+        res = {"M": M, "N_inner": N, "K_out": K, "flops": 2.0 * M * N * K}
+        for label, fn in (("exact_order", lib.hipgpt_matmul), ("tensor_core", lib.hipgpt_matmul_tc)):
+            def step():
+                for s in range(sets):
+                    rc = fn(A[s].data_ptr(), W.data_ptr(), b.data_ptr(), Cc[s].data_ptr(), M, N, K, st)
+                    if rc:
+                        _capi_check(rc)
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record()
+            for _ in range(reps):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / reps / sets * 1e3
+            res[label] = {"us_per_call": us, "tflops": 2.0 * M * N * K / us / 1e6}
+        out[name] = res
+        del A, W, b, Cc
+    return out
+
+
+def _capi_check(rc):
+    from hipgpt_b200 import _capi
+    _capi.check(rc)
 
 
 def decode_leg():
@@ -576,6 +621,7 @@ def run_ours(args):
         _, info = cpu_leg(cfg, args.causal, seconds=args.cpu_seconds)
         line["cpu_baseline"] = info
         line["decode"] = decode_leg()
+        line["projections"] = projections_leg(lib)
     if rank == 0:
         emit(line)
     if world > 1:
