@@ -47,14 +47,25 @@ void launch_attention_weighted_sum(const float* softmax, const float* V, float* 
     die_on(hipgpt_attention_weighted_sum(softmax, V, output, B, S, D, nullptr), "launch_attention_weighted_sum");
 }
 
+// HIPGPT_FAST_MATMUL=1 in the environment sends the products that are not in place to the tensor-core kernel (fp32-grade
+// instead of the reference's summation order bit for bit); the in-place output projection
+// (src/transformer_layer.cpp:220) and everything else keep the exact kernel.
+static bool fast_matmul()
+{
+    static const bool on = [] { const char *e = getenv("HIPGPT_FAST_MATMUL"); return e && *e && *e != '0'; }();
+    return on;
+}
+
 void launch_matmul(const float* A, const float* B, float* C, int M, int N, int K)
 {
-    die_on(hipgpt_matmul(A, B, nullptr, C, M, N, K, nullptr), "launch_matmul");
+    if (fast_matmul() && C != A && C != B && N > 0) die_on(hipgpt_matmul_tc(A, B, nullptr, C, M, N, K, nullptr), "launch_matmul");
+    else die_on(hipgpt_matmul(A, B, nullptr, C, M, N, K, nullptr), "launch_matmul");
 }
 
 void launch_matmul_add_bias(const float* A, const float* B, const float* bias, float* C, int M, int N, int K)
 {
-    die_on(hipgpt_matmul(A, B, bias, C, M, N, K, nullptr), "launch_matmul_add_bias");
+    if (fast_matmul() && C != A && C != B && N > 0) die_on(hipgpt_matmul_tc(A, B, bias, C, M, N, K, nullptr), "launch_matmul_add_bias");
+    else die_on(hipgpt_matmul(A, B, bias, C, M, N, K, nullptr), "launch_matmul_add_bias");
 }
 
 void launch_layer_norm_forward(const float* input, float* output, const float* gamma, const float* beta, int N, int E)
