@@ -199,8 +199,9 @@ needs_ref_run = pytest.mark.skipif(not os.path.exists(REF_RUN), reason="oracle/_
 
 
 @needs_ref_run
+@pytest.mark.parametrize("fast_matmul", [False, True])
 @pytest.mark.parametrize("B,S,E,H,F", [(2, 64, 64, 2, 96), (32, 256, 256, 8, 1024)])
-def test_reference_transformer_layer_runs_on_this_library(tmp_path, B, S, E, H, F):
+def test_reference_transformer_layer_runs_on_this_library(tmp_path, B, S, E, H, F, fast_matmul):
     """HipGPT's own TransformerLayer (src/transformer_layer.cpp compiled where it lies): load() the weights,
     forward() on the GPU with every launcher resolved by this library, against the CPU oracle of the block.
     The second shape is the training default (benchmark configuration 2)."""
@@ -210,7 +211,8 @@ def test_reference_transformer_layer_runs_on_this_library(tmp_path, B, S, E, H, 
         checkpoint.write_layer(f, w, E, H, F)
     x.tofile(os.path.join(tmp_path, "x.bin"))
     r = subprocess.run([REF_RUN, "layer", os.path.join(tmp_path, "layer.bin"), os.path.join(tmp_path, "x.bin"),
-                        os.path.join(tmp_path, "y.bin")] + [str(v) for v in (B, S, E, H, F)], capture_output=True, text=True, timeout=300)
+                        os.path.join(tmp_path, "y.bin")] + [str(v) for v in (B, S, E, H, F)], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, HIPGPT_FAST_MATMUL="1" if fast_matmul else "0"))    # 1: the tensor-core projections
     assert r.returncode == 0, r.stderr
     got = np.fromfile(os.path.join(tmp_path, "y.bin"), dtype=np.float32).reshape(B * S, E)
     want = ob.layer_forward(x, w, B, S, E, H, F, dropout_p=0.1)
