@@ -20,7 +20,7 @@ Default workload: B=32 H=8 S=256 head_dim=32, fp32, causal, probabilities not st
             run is reported beside it
   scaling_c5  (default run) the largest workload through the sharded C-ABI driver: compute alone,
             compute in chunks, and with the all-gather of the outputs beside it when N > 1 (NCCL, and
-            the library's own stores into the peers' mapped buffers)
+            the library's own transports into the peers' mapped buffers: stores of a copy kernel, copy-engine copies)
   cpu_baseline  the CPU oracle (a port of the reference arithmetic) on this box's host cores
   decode, projections  (default run) the greedy generation driver, and the matmuls either side of attention
 
@@ -296,8 +296,8 @@ def workload_config(args, cfg):
 def scaling_c5_leg(world, rank, lib):
     """BASELINE.json's scaling configuration (B=64 H=16 S=2048 head_dim=64, causal, fp32 and bf16 storage) with its
     batches split over the ranks by the library's own driver (hipgpt_mha_forward_sharded): compute only, with the
-    NCCL all-gather of the outputs chunk by chunk behind the arithmetic, and with the library's own transport (a small
-    copy kernel that stores each chunk into the peers' mapped buffers).  Device time per call from CUDA events,
+    NCCL all-gather of the outputs chunk by chunk behind the arithmetic, and with the library's own transports into the
+    peers' mapped buffers (a small copy kernel's stores; one copy-engine copy per peer and chunk).  Device time per call from CUDA events,
     max over ranks; L2 is flushed between calls (at 8 ranks a rank's bf16 inputs are smaller than L2)."""
     import torch
     import torch.distributed as dist
@@ -354,12 +354,14 @@ def scaling_c5_leg(world, rank, lib):
                 total += ms
             return total / reps
         res = {}
+        few = next(ch for ch in range(min(4, Bl), 0, -1) if Bl % ch == 0)       # the copy-engine transport hides behind fewer, larger chunks
         for label, ch, gather in (("compute_only", 1, 0), ("compute_chunked", chunks, 0), ("with_gather", chunks, sharding.GATHER_NCCL),
-                                  ("with_gather_peer_stores", chunks, sharding.GATHER_PEER_STORES)):
+                                  ("with_gather_peer_stores", chunks, sharding.GATHER_PEER_STORES),
+                                  ("with_gather_peer_copies", few, sharding.GATHER_PEER_COPIES)):
             if gather and world == 1:
                 continue
             ms = timed(ch, gather)
-            res[label] = {"ms": ms, "tflops": flops_of(B, H, S, D, True) / (ms * 1e-3) / 1e12}
+            res[label] = {"ms": ms, "tflops": flops_of(B, H, S, D, True) / (ms * 1e-3) / 1e12, "chunks": ch}
         res["gather_chunks"] = chunks
         res["gathered_bytes_per_rank"] = int((B - Bl) * S * E * full.element_size()) if world > 1 else 0
         out[name] = res

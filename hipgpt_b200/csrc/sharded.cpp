@@ -21,6 +21,9 @@
 // communication stream before the first copy (every rank has reached this call on its stream, so its buffer may be
 // written) and after the last one (every rank's copies have completed, which for a kernel means performed) orders
 // the ranks.
+// Third transport (gather = HIPGPT_GATHER_PEER_COPIES): the same mapped buffers and the same ordering, but the data is
+// moved by copy engines: one cudaMemcpyAsync per peer and chunk, each on a stream of its peer, so that no SM and no issue
+// slot is taken from the attention kernels.
 //
 // NCCL is loaded at run time (dlopen of libnccl.so.2: in a torch process that is the copy torch already
 // loaded), so the single-GPU library has no link dependency on it.
@@ -93,6 +96,8 @@ struct hipgpt_shard_ctx {
     size_t own_bytes = 0;
     uint8_t *peer_out[kMaxPeers] = {};          // the same buffer of every rank as mapped here; [rank] = own_out
     int *sync_words = nullptr;                  // [world] ints on the device: the ordering collective's operand
+    cudaStream_t peer_stream[kMaxPeers] = {};   // copy-engine transport: one stream per peer, so that the copies to different peers run side by side
+    cudaEvent_t peer_done[kMaxPeers] = {};
 };
 
 extern "C" {
@@ -138,6 +143,11 @@ int hipgpt_shard_create(hipgpt_shard_ctx **out, const void *id128, int rank, int
     for (int i = 0; i < hipgpt_shard_ctx::kMaxChunks && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&c->computed[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->gathered, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->entered, cudaEventDisableTiming);
+    for (int p = 0; p < world && p < hipgpt_shard_ctx::kMaxPeers && e == cudaSuccess; ++p) {
+        if (p == rank) continue;
+        e = cudaStreamCreateWithPriority(&c->peer_stream[p], cudaStreamNonBlocking, hi);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->peer_done[p], cudaEventDisableTiming);
+    }
     if (e == cudaSuccess) e = cudaMalloc(&c->sync_words, sizeof(int) * (size_t)(world > 0 ? world : 1));
     if (e == cudaSuccess) e = cudaMemset(c->sync_words, 0, sizeof(int) * (size_t)world);
     if (e != cudaSuccess) {
@@ -229,6 +239,8 @@ void hipgpt_shard_destroy(hipgpt_shard_ctx *c)
     if (!c) return;
     release_output_buffer(c);
     if (c->sync_words) cudaFree(c->sync_words);
+    for (auto &ps : c->peer_stream) if (ps) cudaStreamDestroy(ps);
+    for (auto &pe : c->peer_done) if (pe) cudaEventDestroy(pe);
     if (c->entered) cudaEventDestroy(c->entered);
     if (c->comm) nccl()->CommDestroy(c->comm);
     for (cudaEvent_t ev : c->computed) if (ev) cudaEventDestroy(ev);
@@ -255,15 +267,16 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int k = B / (c->world * chunks);
     const size_t batch = (size_t)S * E * elem_bytes;             // bytes of one batch item of a plane
-    if (gather < 0 || gather > HIPGPT_GATHER_PEER_STORES) return fail(HIPGPT_ERR_BAD_ARG, "gather = %d is none of 0, 1, 2", gather);
+    if (gather < 0 || gather > HIPGPT_GATHER_PEER_COPIES) return fail(HIPGPT_ERR_BAD_ARG, "gather = %d is none of 0, 1, 2, 3", gather);
     const bool comm = gather && c->world > 1;
-    const bool push = comm && gather == HIPGPT_GATHER_PEER_STORES;
+    const bool push = comm && (gather == HIPGPT_GATHER_PEER_STORES || gather == HIPGPT_GATHER_PEER_COPIES);
+    const bool dma = comm && gather == HIPGPT_GATHER_PEER_COPIES;
     Nccl *n = comm ? nccl() : nullptr;
     if (push) {
         const uint8_t *o = static_cast<const uint8_t *>(d_out);
         const size_t need = (size_t)B * batch;
         if (!c->own_out || o < c->own_out || o + need > c->own_out + c->own_bytes)
-            return fail(HIPGPT_ERR_BAD_ARG, "gather = 2 needs d_out inside the buffer of hipgpt_shard_output_buffer (%zu bytes needed)", need);
+            return fail(HIPGPT_ERR_BAD_ARG, "gather = 2 and 3 need d_out inside the buffer of hipgpt_shard_output_buffer (%zu bytes needed)", need);
         if (((size_t)k * batch) & 15) return fail(HIPGPT_ERR_BAD_ARG, "a rank's chunk of %zu bytes is not a multiple of 16", (size_t)k * batch);
         // no rank writes into a peer that has not reached this call on its stream
         cudaError_t e = cudaEventRecord(c->entered, st);
@@ -271,6 +284,13 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
         if (e != cudaSuccess) return cuda_fail(e, "event hand-off");
         const ncclResult_t r = n->AllGather(c->sync_words + c->rank, c->sync_words, sizeof(int), ncclChar, c->comm, c->comm_stream);
         if (r != 0) return nccl_fail(n, r, "ncclAllGather (ordering)");
+        if (dma) {
+            // the per-peer copy streams start behind that collective
+            e = cudaEventRecord(c->entered, c->comm_stream);
+            for (int p = 0; p < c->world && e == cudaSuccess; ++p)
+                if (p != c->rank) e = cudaStreamWaitEvent(c->peer_stream[p], c->entered, 0);
+            if (e != cudaSuccess) return cuda_fail(e, "event hand-off");
+        }
     }
     const uint8_t *q = static_cast<const uint8_t *>(d_q), *kk = static_cast<const uint8_t *>(d_k), *v = static_cast<const uint8_t *>(d_v);
     uint8_t *out = static_cast<uint8_t *>(d_out);
@@ -285,8 +305,19 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
         if (rc != HIPGPT_OK) return rc;
         if (!comm) continue;
         cudaError_t e = cudaEventRecord(c->computed[ch], st);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm_stream, c->computed[ch], 0);
+        if (e == cudaSuccess && !dma) e = cudaStreamWaitEvent(c->comm_stream, c->computed[ch], 0);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "event hand-off: %s", cudaGetErrorString(e));
+        if (dma) {
+            // one copy per peer and chunk, each on its peer's stream: copy engines move the data, no SM is used
+            const size_t off = (size_t)(mine - c->own_out);
+            for (int i = 1; i < c->world && e == cudaSuccess; ++i) {
+                const int p = (c->rank + i) % c->world;
+                e = cudaStreamWaitEvent(c->peer_stream[p], c->computed[ch], 0);
+                if (e == cudaSuccess) e = cudaMemcpyAsync(c->peer_out[p] + off, mine, (size_t)k * batch, cudaMemcpyDeviceToDevice, c->peer_stream[p]);
+            }
+            if (e != cudaSuccess) return cuda_fail(e, "peer copy");
+            continue;
+        }
         if (push) {
             void *dst[hipgpt_shard_ctx::kMaxPeers];
             int nd = 0;
@@ -299,8 +330,17 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
         const ncclResult_t r = n->AllGather(mine, block, (size_t)k * batch, ncclChar, c->comm, c->comm_stream);
         if (r != 0) return nccl_fail(n, r, "ncclAllGather");
     }
+    if (dma) {
+        cudaError_t e = cudaSuccess;
+        for (int p = 0; p < c->world && e == cudaSuccess; ++p) {
+            if (p == c->rank) continue;
+            e = cudaEventRecord(c->peer_done[p], c->peer_stream[p]);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm_stream, c->peer_done[p], 0);
+        }
+        if (e != cudaSuccess) return cuda_fail(e, "event hand-off");
+    }
     if (push) {
-        // every rank's copies have completed (a kernel that has completed has performed its stores)
+        // every rank's copies have completed (a kernel, or a copy, that has completed has performed its stores)
         const ncclResult_t r = n->AllGather(c->sync_words + c->rank, c->sync_words, sizeof(int), ncclChar, c->comm, c->comm_stream);
         if (r != 0) return nccl_fail(n, r, "ncclAllGather (ordering)");
     }

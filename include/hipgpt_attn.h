@@ -305,6 +305,9 @@ HIPGPT_API int hipgpt_gpt_set_mode(hipgpt_gpt *g, int mode);
  *                             bytes per rank before the first and after the last copy orders the ranks: none writes
  *                             into a peer that has not reached the call on its `stream`, and `stream` continues once
  *                             every rank's copies have landed.  World size at most 8.
+ *                             gather = HIPGPT_GATHER_PEER_COPIES (3): the same with one cudaMemcpyAsync per peer and chunk,
+ *                             each on a stream of its peer: copy engines move the data and no SM is taken from the
+ *                             attention kernels (measured the best of the three beside them).
  *   hipgpt_shard_output_buffer  collective: allocates `bytes` of device memory on every rank (the same size on all),
  *                             exchanges inter-process memory handles and maps the peers' buffers; *d_out is this
  *                             rank's.  One per context; a second call, and hipgpt_shard_destroy, release the first
@@ -313,6 +316,7 @@ HIPGPT_API int hipgpt_gpt_set_mode(hipgpt_gpt *g, int mode);
 #define HIPGPT_GATHER_NONE        0
 #define HIPGPT_GATHER_NCCL        1
 #define HIPGPT_GATHER_PEER_STORES 2
+#define HIPGPT_GATHER_PEER_COPIES 3   /* as 2, but one cudaMemcpyAsync per peer and chunk on a stream per peer: copy engines, no SM */
 typedef struct hipgpt_shard_ctx hipgpt_shard_ctx;
 HIPGPT_API int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end);
 HIPGPT_API int hipgpt_shard_chunk_range(int B, int world, int rank, int chunks, int chunk, int *b_begin, int *b_end);

@@ -50,10 +50,14 @@ def _worker(rank, world, port, ret):
                 pout.fill_(float("nan"))
                 torch.cuda.synchronize()
                 dist.barrier()                       # every rank's buffer is filled before any peer writes into it
-                for _ in range(2):                   # twice: the second call writes over a buffer the peers have just read
-                    sh.forward(loc[0], loc[1], loc[2], pout, B, S, E, H, causal=causal, chunks=chunks, gather=sharding.GATHER_PEER_STORES)
+                for mode in (sharding.GATHER_PEER_STORES, sharding.GATHER_PEER_STORES, sharding.GATHER_PEER_COPIES, sharding.GATHER_PEER_COPIES):
+                    # each twice: the second call writes over a buffer the peers have just read
+                    sh.forward(loc[0], loc[1], loc[2], pout, B, S, E, H, causal=causal, chunks=chunks, gather=mode)
                     torch.cuda.synchronize()
                     ok = ok and bool(torch.equal(pout, whole))
+                    pout.fill_(float("nan"))
+                    torch.cuda.synchronize()
+                    dist.barrier()
                 # without the gather only this rank's batches are written
                 out2 = torch.full((B * S, E), float("nan"), device="cuda", dtype=dtype)
                 sh.forward(loc[0], loc[1], loc[2], out2, B, S, E, H, causal=causal, chunks=chunks, gather=False)
