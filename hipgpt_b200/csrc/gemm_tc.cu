@@ -189,6 +189,7 @@ gemm_tc_kernel(const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bim
     uint8_t *a_s = base;                              // [stage][A_hi block | A_lo block]
     uint8_t *b_s = base + kStages * kAStage;          // [stage][64 deep][B_hi | B_lo]
     __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+    __shared__ __align__(16) float epi[4][32 * 32];  // per epilogue warp: a 32 x 32 piece of the output on its way out
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
@@ -293,28 +294,49 @@ gemm_tc_kernel(const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bim
         wait(&acc_full[i & 1], (uint32_t)((i / 2) & 1), 3);
         tc_fence_after();
         const int c_base = nt * kTN;
-        const bool store = !abort_flag && m < M;
-        float *dst = C + (size_t)(m < M ? m : 0) * K + c_base;
+        const bool live = !abort_flag;
+        // 32 columns at a time; the warp turns its 32 x 32 piece through shared memory (16-byte chunk c of row r at
+        // r * 128 + ((c ^ (r & 7)) * 16)) so that a store instruction writes four rows of 128 contiguous bytes instead
+        // of 32 rows of 16
+        uint8_t *tb = reinterpret_cast<uint8_t *>(epi[warp]);
 #pragma unroll 1
-        for (int c0 = 0; c0 < kTN; c0 += 16) {
-            float a[16], b[16];
-            tmem_ld16(lane_base + c0, a);             // A_hi B_hi
-            tmem_ld16(lane_base + kTN + c0, b);       // the correction terms
+        for (int c0 = 0; c0 < kTN; c0 += 32) {
+            float a[32], b[32];
+            tmem_ld32(lane_base + c0, a);             // A_hi B_hi
+            tmem_ld32(lane_base + kTN + c0, b);       // the correction terms
             tmem_wait_ld();
-            if (!store || c_base + c0 >= K) continue;
-            float o[16];
+            if (c_base + c0 >= K) continue;           // warp-uniform: a tile past the last column
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int c = c_base + c0 + j;
-                o[j] = (a[j] + b[j]) * unscale + ((bias && c < K) ? __ldg(bias + c) : 0.0f);
+            for (int j4 = 0; j4 < 8; ++j4) {
+                float o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = c_base + c0 + 4 * j4 + j;
+                    o[j] = (a[4 * j4 + j] + b[4 * j4 + j]) * unscale + ((bias && c < K) ? __ldg(bias + c) : 0.0f);
+                }
+                *reinterpret_cast<float4 *>(tb + lane * 128 + ((j4 ^ (lane & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
             }
-            if (vec && c_base + c0 + 16 <= K) {
+            __syncwarp();
+            const int ch = lane & 7;
+            const int col = c_base + c0 + 4 * ch;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) reinterpret_cast<float4 *>(dst + c0)[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) if (c_base + c0 + j < K) dst[c0 + j] = o[j];
+            for (int i = 0; i < 8; ++i) {
+                const int rr = 4 * i + (lane >> 3);
+                const int mrow = mt * kTM + warp * 32 + rr;
+                const float4 val = *reinterpret_cast<const float4 *>(tb + rr * 128 + ((ch ^ (rr & 7)) << 4));
+                if (live && mrow < M) {
+                    float *dst = C + (size_t)mrow * K + col;
+                    if (vec && col + 4 <= K) {
+                        *reinterpret_cast<float4 *>(dst) = val;
+                    } else {
+                        if (col < K) dst[0] = val.x;
+                        if (col + 1 < K) dst[1] = val.y;
+                        if (col + 2 < K) dst[2] = val.z;
+                        if (col + 3 < K) dst[3] = val.w;
+                    }
+                }
             }
+            __syncwarp();                             // the piece is out before the next one is staged
         }
         // this half of TMEM may take the tile after next
         tc_fence_before();
