@@ -87,6 +87,7 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline leg")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="run only the greedy-generation leg and print its JSON")
+    ap.add_argument("--projections-only", action="store_true", help="run only the projections leg (the matmuls either side of attention) and print its JSON")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-scaling", action="store_true", help="skip the C5 sharded leg (key scaling_c5)")
     ap.add_argument("--kernel", default="auto", choices=sorted(KERNELS),
@@ -208,7 +209,7 @@ def projections_leg(lib):
         b = torch.randn((K,), device="cuda")
         Cc = torch.empty((sets, M, K), device="cuda")
         res = {"M": M, "N_inner": N, "K_out": K, "flops": 2.0 * M * N * K}
-        for label, fn in (("exact_order", lib.hipgpt_matmul), ("tensor_core", lib.hipgpt_matmul_tc)):
+        for label, fn in (("tensor_core", lib.hipgpt_matmul_tc), ("exact_order", lib.hipgpt_matmul)):
             def step():
                 for s in range(sets):
                     rc = fn(A[s].data_ptr(), W.data_ptr(), b.data_ptr(), Cc[s].data_ptr(), M, N, K, st)
@@ -653,6 +654,13 @@ def main():
     args = parse()
     if args.decode_only:
         emit(decode_leg())
+    elif args.projections_only:
+        import torch
+        from hipgpt_b200 import _capi
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+        torch.cuda.set_device(0)
+        emit(projections_leg(_capi.lib()))
     elif args.impl == "reference":
         run_reference(args)
     else:
