@@ -22,7 +22,8 @@ Default workload: B=32 H=8 S=256 head_dim=32, fp32, causal, probabilities not st
             compute in chunks, and with the all-gather of the outputs beside it when N > 1 (NCCL, and
             the library's own transports into the peers' mapped buffers: stores of a copy kernel, copy-engine copies)
   cpu_baseline  the CPU oracle (a port of the reference arithmetic) on this box's host cores
-  decode, projections  (default run) the greedy generation driver, and the matmuls either side of attention
+  decode, projections, attention_block  (default run) the greedy generation driver, the matmuls either side of attention, and
+            the layer's QKV projection + attention + output projection as one sequence
 
 With N > 1 (torchrun, one rank per GPU) every rank runs the same step on its own batches
 (batch-major shards of an N-times larger batch; no kernel reads another GPU's memory), and
@@ -229,6 +230,57 @@ def projections_leg(lib):
             res[label] = {"us_per_call": us, "tflops": 2.0 * M * N * K / us / 1e6}
         out[name] = res
         del A, W, b, Cc
+    return out
+
+
+def attention_block_leg(lib):
+    """TransformerLayer::self_attention_forward's three launches at the default workload (src/transformer_layer.cpp:214-222:
+    QKV projection with bias, launch_multihead_attention on the [T, 3E] output read as three stacked planes, output
+    projection with bias), non-causal like the reference: with the exact-order matmul and stored probabilities (what the
+    reference's layer asks for, in place output projection), and with the tensor-core matmul, with and without the
+    probabilities.  CUDA-event time per block over rotating buffers larger than L2."""
+    import torch
+    c = synth.CONFIGS["c2"]
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    E, T = H * D, B * S
+    st = torch.cuda.current_stream().cuda_stream
+    sets = 4
+    x = torch.randn((sets, T, E), device="cuda")
+    wqkv, bqkv = torch.randn((E, 3 * E), device="cuda") * 0.05, torch.randn((3 * E,), device="cuda") * 0.1
+    wo, bo = torch.randn((E, E), device="cuda") * 0.05, torch.randn((E,), device="cuda") * 0.1
+    qkv = torch.empty((sets, 3, T, E), device="cuda")
+    att = torch.empty((sets, T, E), device="cuda")
+    y = torch.empty((sets, T, E), device="cuda")
+    probs = torch.empty((sets, B, H, S, S), device="cuda")
+    plane = T * E * 4
+
+    def block(s, fast, want_probs):
+        mm = lib.hipgpt_matmul_tc if fast else lib.hipgpt_matmul
+        q = qkv[s].data_ptr()
+        rc = mm(x[s].data_ptr(), wqkv.data_ptr(), bqkv.data_ptr(), q, T, E, 3 * E, st)
+        rc = rc or lib.hipgpt_mha_forward(q, q + plane, q + 2 * plane, att[s].data_ptr(), probs[s].data_ptr() if want_probs else None, B, S, E, H, 0, st)
+        if fast:
+            rc = rc or mm(att[s].data_ptr(), wo.data_ptr(), bo.data_ptr(), y[s].data_ptr(), T, E, E, st)
+        else:
+            rc = rc or lib.hipgpt_matmul(att[s].data_ptr(), wo.data_ptr(), bo.data_ptr(), att[s].data_ptr(), T, E, E, st)      # in place, like the reference
+        if rc:
+            _capi_check(rc)
+    out = {"config": f"B={B} S={S} E={E} H={H}, non-causal: QKV projection + attention + output projection"}
+    for label, fast, want_probs in (("tensor_core_matmul_no_probs", True, False), ("tensor_core_matmul_probs_stored", True, True),
+                                    ("exact_matmul_probs_stored", False, True)):
+        for _ in range(3):
+            for s in range(sets):
+                block(s, fast, want_probs)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            for s in range(sets):
+                block(s, fast, want_probs)
+        e1.record()
+        torch.cuda.synchronize()
+        out[label] = {"us_per_block": e0.elapsed_time(e1) / reps / sets * 1e3}
     return out
 
 
@@ -625,6 +677,7 @@ def run_ours(args):
         line["cpu_baseline"] = info
         line["decode"] = decode_leg()
         line["projections"] = projections_leg(lib)
+        line["attention_block"] = attention_block_leg(lib)
     if rank == 0:
         emit(line)
     if world > 1:
@@ -660,7 +713,7 @@ def main():
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
         torch.cuda.set_device(0)
-        emit(projections_leg(_capi.lib()))
+        emit({"projections": projections_leg(_capi.lib()), "attention_block": attention_block_leg(_capi.lib())})
     elif args.impl == "reference":
         run_reference(args)
     else:
