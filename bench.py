@@ -60,11 +60,17 @@ def flops_of(B, H, S, D, causal):
     return 2.0 * B * H * D * S * (S + 1) if causal else 4.0 * B * H * float(S) * S * D
 
 
-def tiled_launches(B, H, S, D):
+def tiled_launches(B, H, S, D, causal=True):
     """Kernels one call of the tiled fp32 kernel launches: the library cuts the batches into groups whose packed K
-    and V (as many bytes as the fp32 K and V) stay below 96 MB, and runs a pack kernel and an attention kernel per group."""
+    and V (as many bytes as the fp32 K and V) stay below 96 MB, and runs a pack kernel and an attention kernel per group
+    (mirrors launch_tc16_cfg in attn_fwd_tc16.cu)."""
     per_batch = H * ((S + 63) // 64) * 64 * 2 * D * 2 * 2
-    gb = max(1, min(B, (96 << 20) // per_batch))
+    gb = max(1, (int(os.environ.get("HIPGPT_PACK_GROUP_MB", "96")) << 20) // per_batch)
+    env = os.environ.get("HIPGPT_PACK_OVERLAP", "")
+    overlap = (not causal) if env == "" else env[:1] != "0"
+    if B > gb and gb >= 2 and overlap:
+        gb //= 2                                   # several groups: two half-size buffers, group g + 1 packed while g is attended to
+    gb = min(gb, B)
     return 2 * ((B + gb - 1) // gb)
 
 
@@ -613,7 +619,7 @@ def run_ours(args):
               "mha_tc16_kernel" if tensor_kernel else "mha_rows_kernel" if D == 128 else "mha_generic_kernel")
     traffic = TRAFFIC.get((args.workload, kernel)) if (args.causal and not args.probs and not bf16) else None
     roofline.update({"kernel": kernel, "traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None,
-                     "us_per_launch": launch_ms * 1e3, "kernels_per_launch": tiled_launches(B, H, S, D) if tiled else 1,
+                     "us_per_launch": launch_ms * 1e3, "kernels_per_launch": tiled_launches(B, H, S, D, bool(args.causal)) if tiled else 1,
                      "algorithmic_bytes_per_launch": per_batch_bytes,
                      "algorithmic_flops_per_launch": flops_launch,
                      "vs_fp32_fma_ceiling": {"achieved_tflops": achieved, "ffma_peak_tflops": fma_peak, "ratio": achieved / fma_peak,
@@ -628,7 +634,7 @@ def run_ours(args):
                        "l2": f"{sets} distinct input batches per step, {sets * per_batch_bytes / 1e6:.0f} MB > 126 MB L2",
                        "parallelism": f"batch-major shards x{world}" + (", NCCL all-gather of outputs in chunks, overlapped" if args.gather else ", no collective")},
             "clocks": clocks.summary(), "roofline": roofline,
-            "gpu_launches": args.steps * sets * (tiled_launches(B, H, S, D) if tiled else 1)}
+            "gpu_launches": args.steps * sets * (tiled_launches(B, H, S, D, bool(args.causal)) if tiled else 1)}
 
     # the scaling configuration through the library's sharded driver (every N, the default workload only)
     if args.workload == "c2" and not args.no_scaling and not bf16:

@@ -641,14 +641,28 @@ mha_tc16_kernel(const uint8_t *__restrict__ kimg, const uint8_t *__restrict__ vi
 // after the call has returned; calls on different streams must not share it).  It grows to the largest call.
 struct PackScratch {
     std::mutex mu;
-    struct Entry { int dev; cudaStream_t st; uint8_t *buf; size_t cap; };
+    // side: the stream on which the groups after the first are packed while the group before them is attended to;
+    // entered: the caller's stream has reached the call; packed[i], attended[i]: buffer i has been written / read
+    struct Entry { int dev; cudaStream_t st; uint8_t *buf; size_t cap; cudaStream_t side; cudaEvent_t entered, packed[2], attended[2]; };
     std::vector<Entry> entries;
-    int get(int dev, cudaStream_t st, size_t need, uint8_t **out)
+    int get(int dev, cudaStream_t st, size_t need, uint8_t **out, Entry **entry = nullptr)
     {
         std::lock_guard<std::mutex> lock(mu);
         Entry *e = nullptr;
         for (auto &x : entries) if (x.dev == dev && x.st == st) e = &x;
-        if (!e) { entries.push_back({dev, st, nullptr, 0}); e = &entries.back(); }
+        if (!e) { entries.push_back({dev, st, nullptr, 0, nullptr, nullptr, {nullptr, nullptr}, {nullptr, nullptr}}); e = &entries.back(); }
+        if (entry) {
+            *entry = e;                              // entries are only appended, and only under the lock: take care below
+            if (!e->side) {
+                cudaError_t err = cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking);
+                if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->entered, cudaEventDisableTiming);
+                for (int i = 0; i < 2 && err == cudaSuccess; ++i) {
+                    err = cudaEventCreateWithFlags(&e->packed[i], cudaEventDisableTiming);
+                    if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->attended[i], cudaEventDisableTiming);
+                }
+                if (err != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "stream or event for the packing: %s", cudaGetErrorString(err));
+            }
+        }
         if (e->cap < need) {
             if (e->buf) cudaFree(e->buf);        // waits for the kernels that read it
             e->buf = nullptr;
@@ -663,7 +677,15 @@ struct PackScratch {
     void release()
     {
         std::lock_guard<std::mutex> lock(mu);
-        for (auto &x : entries) if (x.buf) cudaFree(x.buf);
+        for (auto &x : entries) {
+            if (x.buf) cudaFree(x.buf);
+            if (x.side) cudaStreamDestroy(x.side);
+            if (x.entered) cudaEventDestroy(x.entered);
+            for (int i = 0; i < 2; ++i) {
+                if (x.packed[i]) cudaEventDestroy(x.packed[i]);
+                if (x.attended[i]) cudaEventDestroy(x.attended[i]);
+            }
+        }
         entries.clear();
     }
 };
@@ -689,6 +711,14 @@ int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, 
     if (const char *env = getenv("HIPGPT_PACK_GROUP_MB")) { const long v = atol(env); if (v > 0) group_bytes = (size_t)v << 20; }
     long long gb = (long long)(group_bytes / per_batch);
     if (gb < 1) gb = 1;
+    // A call of several groups can pack group g + 1 on a second stream while group g is attended to: two buffers of half
+    // a group each (the same footprint in L2), events in both directions.  Measured at B=64 H=16 S=2048 head_dim 64:
+    // unmasked 292 -> 309 TFLOP/s; causal 256 -> 249 (half-size groups leave the causal kernel, whose blocks differ in
+    // length, a longer tail per launch, and 128 - 192 MB of buffers do not help either: 252 - 254).  So it is the default
+    // for unmasked calls only; HIPGPT_PACK_OVERLAP=0 / 1 forces it off / on for both.
+    static const int overlap_env = [] { const char *e = getenv("HIPGPT_PACK_OVERLAP"); return (!e || !*e) ? -1 : (*e != '0' ? 1 : 0); }();
+    const bool overlap = (overlap_env < 0 ? !CAUSAL : overlap_env == 1) && B > gb && gb >= 2;
+    if (overlap) gb = gb / 2;
     if (gb > B) gb = B;
     while (gb * H > 65535) --gb;                     // grid.y of the pack kernel
     if (gb < 1) return fail(HIPGPT_ERR_BAD_ARG, "%d heads are too many", H);
@@ -697,25 +727,52 @@ int launch_tc16_cfg(const float *q, const float *k, const float *v, float *out, 
     e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
     const size_t kbytes = (size_t)gb * H * ntk * C::kK16Stage, vbytes = (size_t)gb * H * ntk * C::kV16Stage;
-    uint8_t *scratch = nullptr;
     const size_t gtiles = (size_t)gb * H * ntk;
-    int rc = g_pack.get(dev, st, kbytes + vbytes + 2 * gtiles * sizeof(float), &scratch);
+    const size_t one = (kbytes + vbytes + 2 * gtiles * sizeof(float) + 1023) & ~(size_t)1023;      // one buffer: K images, V images, the tiles' maxima
+    uint8_t *scratch = nullptr;
+    PackScratch::Entry *ent = nullptr;
+    int rc = g_pack.get(dev, st, overlap ? 2 * one : one, &scratch, overlap ? &ent : nullptr);
     if (rc != HIPGPT_OK) return rc;
-    float *tmax = reinterpret_cast<float *>(scratch + kbytes + vbytes);      // [2][group's tiles]: largest |K|, |V| of every tile
+    cudaStream_t side = nullptr;
+    cudaEvent_t entered = nullptr, packed[2] = {nullptr, nullptr}, attended[2] = {nullptr, nullptr};
+    if (overlap) {                                   // copies: the vector of entries may move
+        side = ent->side; entered = ent->entered;
+        for (int i = 0; i < 2; ++i) { packed[i] = ent->packed[i]; attended[i] = ent->attended[i]; }
+        e = cudaEventRecord(entered, st);            // K and V are valid from here on, and earlier calls have read the buffers
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(side, entered, 0);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "event hand-off: %s", cudaGetErrorString(e));
+    }
     const float qscale = (1.0f / sqrtf((float)D)) * kLog2e;
-    for (long long b0 = 0; b0 < B; b0 += gb) {
+    int g = 0;
+    for (long long b0 = 0; b0 < B; b0 += gb, ++g) {
         const int nb = (int)(B - b0 < gb ? B - b0 : gb);
         const size_t off = (size_t)b0 * S * E;       // the group's first token in every plane and in the output
         const int ntiles = nb * H * ntk;
-        kv_pack_kernel<D><<<dim3((unsigned)ntk, (unsigned)(nb * H)), kPackThreads, 0, st>>>(k + off, v + off, tmax, scratch, scratch + kbytes, S, E, H, ntk, ntiles);
+        uint8_t *buf = scratch + (overlap ? (size_t)(g & 1) * one : 0);
+        float *tmax = reinterpret_cast<float *>(buf + kbytes + vbytes);      // [2][group's tiles]: largest |K|, |V| of every tile
+        const cudaStream_t ps = overlap ? side : st;
+        if (overlap && g >= 2) {
+            e = cudaStreamWaitEvent(side, attended[g & 1], 0);               // the group that used this buffer has been attended to
+            if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "event hand-off: %s", cudaGetErrorString(e));
+        }
+        kv_pack_kernel<D><<<dim3((unsigned)ntk, (unsigned)(nb * H)), kPackThreads, 0, ps>>>(k + off, v + off, tmax, buf, buf + kbytes, S, E, H, ntk, ntiles);
         rc = check_launch("kv_pack_kernel");
         if (rc != HIPGPT_OK) return rc;
-        // the attention kernel's blocks start (and stage their query rows) while the pack kernel's last blocks run
-        e = launch_overlapped(kern, dim3((unsigned)(nb * H * nqblk)), dim3(C::THREADS), smem, st, (const uint8_t *)scratch, (const uint8_t *)(scratch + kbytes),
+        if (overlap) {
+            e = cudaEventRecord(packed[g & 1], side);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(st, packed[g & 1], 0);
+            if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "event hand-off: %s", cudaGetErrorString(e));
+        }
+        // (one stream:) the attention kernel's blocks start, and stage their query rows, while the pack kernel's last blocks run
+        e = launch_overlapped(kern, dim3((unsigned)(nb * H * nqblk)), dim3(C::THREADS), smem, st, (const uint8_t *)buf, (const uint8_t *)(buf + kbytes),
                               (const float *)tmax, ntiles, q + off, out + off, probs ? probs + (size_t)b0 * H * S * S : nullptr, S, E, H, nb * H, nqblk, ntk, qscale);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "mha_tc16_kernel launch: %s", cudaGetErrorString(e));
         rc = check_launch("mha_tc16_kernel");
         if (rc != HIPGPT_OK) return rc;
+        if (overlap) {
+            e = cudaEventRecord(attended[g & 1], st);
+            if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "event hand-off: %s", cudaGetErrorString(e));
+        }
     }
     return HIPGPT_OK;
 }
