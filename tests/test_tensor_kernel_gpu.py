@@ -197,3 +197,23 @@ def test_tiled_kernel_rescales_when_row_maxima_grow(D, want_probs):
         assert float(np.abs(out - ref_out).max()) <= 1e-4     # scores reach ~100: the fp32 arithmetic itself is good to ~1e-5 here
         if want_probs:
             assert float(np.abs(probs - ref_probs).max()) <= 1e-4
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("want_probs", [False, True])
+def test_tiled_kernel_in_several_groups_of_batches(monkeypatch, causal, want_probs):
+    """The tiled kernel cuts a call into groups of batches whose packed K and V stay in L2 (96 MB by default); unmasked
+    calls of several groups pack the next group on a second stream.  A 1 MB limit makes a small call take that path:
+    7 batches in groups of 1 (unmasked, two buffers in turn) or 2 (causal, a ragged last group), three calls in a row."""
+    monkeypatch.setenv("HIPGPT_PACK_GROUP_MB", "1")
+    B, H, S, D = 7, 2, 512, 64                       # 0.5 MB of packed operands per batch item
+    E = H * D
+    for rep in range(3):
+        qkv = synth.qkv_planes(2900 + rep, B, S, E)
+        ref_out, ref_probs = ob.mha(qkv, B, S, E, H, causal=causal, want_probs=want_probs)
+        out, probs = gpu_mha(qkv, B, S, E, H, causal, want_probs, algo=_capi.ALGO_TENSOR)
+        assert _status() == 0
+        assert np.isfinite(out).all()
+        assert float(np.abs(out - ref_out).max()) <= TOL
+        if want_probs:
+            assert float(np.abs(probs - ref_probs).max()) <= TOL
