@@ -216,10 +216,16 @@ def projections_leg(lib):
         b = torch.randn((K,), device="cuda")
         Cc = torch.empty((sets, M, K), device="cuda")
         res = {"M": M, "N_inner": N, "K_out": K, "flops": 2.0 * M * N * K}
-        for label, fn in (("tensor_core", lib.hipgpt_matmul_tc), ("exact_order", lib.hipgpt_matmul)):
+        import ctypes
+        packed = ctypes.c_void_p()
+        _capi_check(lib.hipgpt_matmul_tc_prepare(W.data_ptr(), N, K, ctypes.byref(packed), st))
+        for label, fn in (("tensor_core", lib.hipgpt_matmul_tc), ("tensor_core_weights_packed_once", None), ("exact_order", lib.hipgpt_matmul)):
             def step():
                 for s in range(sets):
-                    rc = fn(A[s].data_ptr(), W.data_ptr(), b.data_ptr(), Cc[s].data_ptr(), M, N, K, st)
+                    if fn is None:
+                        rc = lib.hipgpt_matmul_tc_prepared(A[s].data_ptr(), packed, b.data_ptr(), Cc[s].data_ptr(), M, st)
+                    else:
+                        rc = fn(A[s].data_ptr(), W.data_ptr(), b.data_ptr(), Cc[s].data_ptr(), M, N, K, st)
                     if rc:
                         _capi_check(rc)
             for _ in range(3):
@@ -235,6 +241,8 @@ def projections_leg(lib):
             us = e0.elapsed_time(e1) / reps / sets * 1e3
             res[label] = {"us_per_call": us, "tflops": 2.0 * M * N * K / us / 1e6}
         out[name] = res
+        torch.cuda.synchronize()
+        lib.hipgpt_matmul_tc_release(packed)
         del A, W, b, Cc
     return out
 
@@ -260,20 +268,30 @@ def attention_block_leg(lib):
     probs = torch.empty((sets, B, H, S, S), device="cuda")
     plane = T * E * 4
 
+    import ctypes
+    pqkv, po = ctypes.c_void_p(), ctypes.c_void_p()
+    _capi_check(lib.hipgpt_matmul_tc_prepare(wqkv.data_ptr(), E, 3 * E, ctypes.byref(pqkv), st))
+    _capi_check(lib.hipgpt_matmul_tc_prepare(wo.data_ptr(), E, E, ctypes.byref(po), st))
+
     def block(s, fast, want_probs):
         mm = lib.hipgpt_matmul_tc if fast else lib.hipgpt_matmul
         q = qkv[s].data_ptr()
-        rc = mm(x[s].data_ptr(), wqkv.data_ptr(), bqkv.data_ptr(), q, T, E, 3 * E, st)
+        if fast == 2:
+            rc = lib.hipgpt_matmul_tc_prepared(x[s].data_ptr(), pqkv, bqkv.data_ptr(), q, T, st)
+        else:
+            rc = mm(x[s].data_ptr(), wqkv.data_ptr(), bqkv.data_ptr(), q, T, E, 3 * E, st)
         rc = rc or lib.hipgpt_mha_forward(q, q + plane, q + 2 * plane, att[s].data_ptr(), probs[s].data_ptr() if want_probs else None, B, S, E, H, 0, st)
-        if fast:
+        if fast == 2:
+            rc = rc or lib.hipgpt_matmul_tc_prepared(att[s].data_ptr(), po, bo.data_ptr(), y[s].data_ptr(), T, st)
+        elif fast:
             rc = rc or mm(att[s].data_ptr(), wo.data_ptr(), bo.data_ptr(), y[s].data_ptr(), T, E, E, st)
         else:
             rc = rc or lib.hipgpt_matmul(att[s].data_ptr(), wo.data_ptr(), bo.data_ptr(), att[s].data_ptr(), T, E, E, st)      # in place, like the reference
         if rc:
             _capi_check(rc)
     out = {"config": f"B={B} S={S} E={E} H={H}, non-causal: QKV projection + attention + output projection"}
-    for label, fast, want_probs in (("tensor_core_matmul_no_probs", True, False), ("tensor_core_matmul_probs_stored", True, True),
-                                    ("exact_matmul_probs_stored", False, True)):
+    for label, fast, want_probs in (("tensor_core_matmul_weights_packed_once_no_probs", 2, False), ("tensor_core_matmul_no_probs", 1, False),
+                                    ("tensor_core_matmul_probs_stored", 1, True), ("exact_matmul_probs_stored", 0, True)):
         for _ in range(3):
             for s in range(sets):
                 block(s, fast, want_probs)
@@ -287,6 +305,9 @@ def attention_block_leg(lib):
         e1.record()
         torch.cuda.synchronize()
         out[label] = {"us_per_block": e0.elapsed_time(e1) / reps / sets * 1e3}
+    torch.cuda.synchronize()
+    lib.hipgpt_matmul_tc_release(pqkv)
+    lib.hipgpt_matmul_tc_release(po)
     return out
 
 

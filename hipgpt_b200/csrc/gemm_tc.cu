@@ -392,6 +392,66 @@ int gemm_tc_status_fetch(int *status)
     return HIPGPT_OK;
 }
 
+namespace {
+
+int set_gemm_attr()
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    return HIPGPT_OK;
+}
+
+// B -> its stage images and its largest magnitude (three launches on `st`; the first is a plain one, so everything
+// enqueued before has completed when the images are written)
+int pack_b(const float *B, int N, int K, uint8_t *bimg, float *b_amax, cudaStream_t st)
+{
+    const int NT = (K + kTN - 1) / kTN, KT = (N + kTK - 1) / kTK;
+    cudaError_t e = cudaMemsetAsync(b_amax, 0, sizeof(float), st);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    const size_t nb = (size_t)N * K;
+    size_t ablocks = (nb + 256 * 4 - 1) / (256 * 4);
+    if (ablocks > 1184) ablocks = 1184;
+    gemm_amax_kernel<<<(unsigned)ablocks, 256, 0, st>>>(B, nb, b_amax);
+    int rc = check_launch("gemm_amax_kernel");
+    if (rc != HIPGPT_OK) return rc;
+    e = launch_overlapped(gemm_pack_b_kernel, dim3((unsigned)(KT * (kTK / 8)), (unsigned)NT), dim3(128), 0, st, B, (const float *)b_amax, bimg, N, K, KT);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_b_kernel launch: %s", cudaGetErrorString(e));
+    return check_launch("gemm_pack_b_kernel");
+}
+
+// A -> its stage images, then the product kernel, with B's images given
+int pack_a_and_multiply(const float *A, const uint8_t *bimg, const float *b_amax, const float *bias, float *C, int M, int N, int K,
+                        uint8_t *aimg, float *row_inv, bool first_is_plain, int dev, cudaStream_t st)
+{
+    const int MT = (M + kTM - 1) / kTM, NT = (K + kTN - 1) / kTN, KT = (N + kTK - 1) / kTK;
+    cudaError_t e;
+    if (first_is_plain) {
+        // nothing of this call precedes the pack kernel: a plain launch, so that the product kernel, which waits for the
+        // pack kernel only, is ordered after everything before the call (the kernel's own wait then returns at once)
+        gemm_pack_a_kernel<<<(unsigned)(MT * kTM / 4), 128, 0, st>>>(A, aimg, row_inv, M, N, KT);
+    } else {
+        e = launch_overlapped(gemm_pack_a_kernel, dim3((unsigned)(MT * kTM / 4)), dim3(128), 0, st, A, aimg, row_inv, M, N, KT);
+        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_a_kernel launch: %s", cudaGetErrorString(e));
+    }
+    int rc = check_launch("gemm_pack_a_kernel");
+    if (rc != HIPGPT_OK) return rc;
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const long long ntiles = (long long)MT * NT;
+    if (ntiles > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "%lld output tiles are too many", ntiles);
+    const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);           // one block per SM, each takes tiles in turn
+    e = launch_overlapped(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), kGemmSmem, st, (const uint8_t *)aimg, bimg,
+                          (const float *)row_inv, b_amax, bias, C, M, K, KT, NT, (int)ntiles);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_tc_kernel launch: %s", cudaGetErrorString(e));
+    return check_launch("gemm_tc_kernel");
+}
+
+}  // namespace
+
 // C[M][K] = A[M][N] B[N][K] (+ bias), fp32-grade on the tensor pipe.  C must not alias A or B.
 int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st)
 {
@@ -407,37 +467,58 @@ int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C
     if (rc != HIPGPT_OK) return rc;
     uint8_t *aimg = scratch, *bimg = scratch + abytes;
     float *row_inv = reinterpret_cast<float *>(scratch + abytes + bbytes), *b_amax = reinterpret_cast<float *>(scratch + abytes + bbytes + rbytes);
-    static bool attr_set = false;
-    if (!attr_set) {
-        e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
-        if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr_set = true;
-    }
-    e = cudaMemsetAsync(b_amax, 0, sizeof(float), st);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
-    const size_t nb = (size_t)N * K;
-    size_t ablocks = (nb + 256 * 4 - 1) / (256 * 4);
-    if (ablocks > 1184) ablocks = 1184;
-    gemm_amax_kernel<<<(unsigned)ablocks, 256, 0, st>>>(B, nb, b_amax);
-    rc = check_launch("gemm_amax_kernel");
+    rc = set_gemm_attr();
+    if (rc == HIPGPT_OK) rc = pack_b(B, N, K, bimg, b_amax, st);
     if (rc != HIPGPT_OK) return rc;
-    e = launch_overlapped(gemm_pack_b_kernel, dim3((unsigned)(KT * (kTK / 8)), (unsigned)NT), dim3(128), 0, st, B, (const float *)b_amax, bimg, N, K, KT);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_b_kernel launch: %s", cudaGetErrorString(e));
-    rc = check_launch("gemm_pack_b_kernel");
+    return pack_a_and_multiply(A, bimg, b_amax, bias, C, M, N, K, aimg, row_inv, false, dev, st);
+}
+
+// ---- a right-hand side packed once (the weights of a layer) and used by many products ---------------------------
+struct PackedB {
+    int dev, N, K;
+    uint8_t *bimg;
+    float *b_amax;
+};
+
+int matmul_tc_prepare(const float *B, int N, int K, PackedB **out, cudaStream_t st)
+{
+    const int NT = (K + kTN - 1) / kTN, KT = (N + kTK - 1) / kTK;
+    if (KT == 0 || NT == 0) return fail(HIPGPT_ERR_BAD_ARG, "an empty right-hand side: N=%d K=%d", N, K);
+    PackedB *p = new PackedB{0, N, K, nullptr, nullptr};
+    cudaError_t e = cudaGetDevice(&p->dev);
+    const size_t bbytes = (size_t)NT * KT * kBStage;
+    if (e == cudaSuccess) e = cudaMalloc(&p->bimg, bbytes + 256);
+    if (e != cudaSuccess) { delete p; return fail(HIPGPT_ERR_CUDA, "cudaMalloc(%zu) for the packed right-hand side: %s", bbytes + 256, cudaGetErrorString(e)); }
+    p->b_amax = reinterpret_cast<float *>(p->bimg + bbytes);
+    const int rc = pack_b(B, N, K, p->bimg, p->b_amax, st);
+    if (rc != HIPGPT_OK) { cudaFree(p->bimg); delete p; return rc; }
+    *out = p;
+    return HIPGPT_OK;
+}
+
+void matmul_tc_release(PackedB *p)
+{
+    if (!p) return;
+    cudaFree(p->bimg);                               // waits for the kernels that read it
+    delete p;
+}
+
+int launch_matmul_tc_prepared(const float *A, const PackedB *b, const float *bias, float *C, int M, cudaStream_t st)
+{
+    const int N = b->N, K = b->K;
+    const int MT = (M + kTM - 1) / kTM, KT = (N + kTK - 1) / kTK;
+    if (MT > 65535) return fail(HIPGPT_ERR_BAD_ARG, "M = %d is beyond %d rows per call", M, 65535 * kTM);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev != b->dev) return fail(HIPGPT_ERR_BAD_ARG, "the right-hand side was packed on device %d, the current device is %d", b->dev, dev);
+    const size_t abytes = (size_t)MT * KT * kAStage, rbytes = ((size_t)MT * kTM * sizeof(float) + 255) & ~(size_t)255;
+    uint8_t *scratch = nullptr;
+    int rc = g_gemm.get(dev, st, abytes + rbytes, &scratch);
     if (rc != HIPGPT_OK) return rc;
-    e = launch_overlapped(gemm_pack_a_kernel, dim3((unsigned)(MT * kTM / 4)), dim3(128), 0, st, A, aimg, row_inv, M, N, KT);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_a_kernel launch: %s", cudaGetErrorString(e));
-    rc = check_launch("gemm_pack_a_kernel");
+    rc = set_gemm_attr();
     if (rc != HIPGPT_OK) return rc;
-    int sms = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    const long long ntiles = (long long)MT * NT;
-    if (ntiles > 2147483647LL) return fail(HIPGPT_ERR_BAD_ARG, "%lld output tiles are too many", ntiles);
-    const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);           // one block per SM, each takes tiles in turn
-    e = launch_overlapped(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), kGemmSmem, st, (const uint8_t *)aimg, (const uint8_t *)bimg,
-                          (const float *)row_inv, (const float *)b_amax, bias, C, M, K, KT, NT, (int)ntiles);
-    if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_tc_kernel launch: %s", cudaGetErrorString(e));
-    return check_launch("gemm_tc_kernel");
+    return pack_a_and_multiply(A, b->bimg, b->b_amax, bias, C, M, N, K, scratch, reinterpret_cast<float *>(scratch + abytes), true, dev, st);
 }
 
 }  // namespace hipgpt

@@ -173,6 +173,12 @@ HIPGPT_API int hipgpt_mha_backward_planes(const float *d_grad_out, const float *
  *                            accumulation: 1e-5 on unit-scale data instead of identical bits, several times the
  *                            rate.  Not in place.  The packed operands live in a buffer of the library (per device
  *                            and stream; hipgpt_release_workspace() frees it).
+ *   hipgpt_matmul_tc_prepare / _prepared / _release
+ *                            the same with the right-hand side (a layer's weights) packed once: prepare() allocates
+ *                            device memory for B's packed form and fills it (asynchronously on `stream`; B may be
+ *                            freed once that stream has passed the call), prepared() multiplies any number of A's
+ *                            with it (on streams ordered after it), release() frees it.  Saves two of the four
+ *                            launches of every product.
  *   hipgpt_layer_norm        replaces launch_layer_norm_forward (src/hip_kernels.cpp:757-848), eps 1e-5;
  *                            agrees with the reference's 64-lane reduction order to rounding (~1e-7).
  *   hipgpt_dropout           replaces launch_dropout_forward (src/hip_kernels.cpp:944-970): the mask depends
@@ -185,6 +191,10 @@ HIPGPT_API int hipgpt_mha_backward_planes(const float *d_grad_out, const float *
  */
 HIPGPT_API int hipgpt_matmul(const float *d_A, const float *d_B, const float *d_bias, float *d_C, int M, int N, int K, void *stream);
 HIPGPT_API int hipgpt_matmul_tc(const float *d_A, const float *d_B, const float *d_bias, float *d_C, int M, int N, int K, void *stream);
+typedef struct hipgpt_packed_matrix hipgpt_packed_matrix;
+HIPGPT_API int hipgpt_matmul_tc_prepare(const float *d_B, int N, int K, hipgpt_packed_matrix **out, void *stream);
+HIPGPT_API int hipgpt_matmul_tc_prepared(const float *d_A, const hipgpt_packed_matrix *b, const float *d_bias, float *d_C, int M, void *stream);
+HIPGPT_API void hipgpt_matmul_tc_release(hipgpt_packed_matrix *b);
 HIPGPT_API int hipgpt_layer_norm(const float *d_in, float *d_out, const float *d_gamma, const float *d_beta, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_dropout(const float *d_in, float *d_out, float *d_mask, float p, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_add_inplace(float *d_a, const float *d_b, long long n, void *stream);

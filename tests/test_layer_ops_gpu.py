@@ -65,6 +65,32 @@ def test_tensor_core_matmul_is_fp32_grade(M, N, K, bias):
     assert lib.hipgpt_matmul_tc(sq.data_ptr(), sq.data_ptr(), None, sq.data_ptr(), 64, 64, 64, _st()) == _capi.ERR_UNSUPPORTED
 
 
+def test_tensor_core_matmul_with_weights_packed_once():
+    """hipgpt_matmul_tc_prepare / _prepared: the right-hand side packed once gives the bits of the one-call form, for any
+    number of left-hand sides, also after the original weights have been overwritten."""
+    lib = _capi.lib()
+    N, K = 256, 768
+    W, b = synth.normal(12, (N, K), 0.05), synth.normal(13, (K,))
+    dW, db = dev(W), dev(b)
+    h = C.c_void_p()
+    _capi.check(lib.hipgpt_matmul_tc_prepare(dW.data_ptr(), N, K, C.byref(h), _st()))
+    torch.cuda.synchronize()
+    dW2 = dW.clone()
+    dW.fill_(float("nan"))                              # the packed form does not refer to the original
+    for M in (1, 130, 1000):
+        A = synth.normal(14 + M, (M, N))
+        dA = dev(A)
+        c1 = torch.full((M, K), float("nan"), device="cuda")
+        c2 = torch.full((M, K), float("nan"), device="cuda")
+        _capi.check(lib.hipgpt_matmul_tc_prepared(dA.data_ptr(), h, db.data_ptr(), c1.data_ptr(), M, _st()))
+        _capi.check(lib.hipgpt_matmul_tc(dA.data_ptr(), dW2.data_ptr(), db.data_ptr(), c2.data_ptr(), M, N, K, _st()))
+        torch.cuda.synchronize()
+        assert torch.equal(c1, c2)
+        want = A.astype(np.float64) @ W.astype(np.float64) + b.astype(np.float64)
+        assert np.abs(c1.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+    lib.hipgpt_matmul_tc_release(h)
+
+
 def test_matmul_in_place_like_the_layers_output_projection():
     """src/transformer_layer.cpp:220 passes d_attn_output_ as both A and C."""
     lib = _capi.lib()
