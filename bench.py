@@ -437,11 +437,28 @@ def scaling_c5_leg(world, rank, lib):
         few = next(ch for ch in range(min(4, Bl), 0, -1) if Bl % ch == 0)       # the copy-engine transport hides behind fewer, larger chunks
         for label, ch, gather in (("compute_only", 1, 0), ("compute_chunked", chunks, 0), ("with_gather", chunks, sharding.GATHER_NCCL),
                                   ("with_gather_peer_stores", chunks, sharding.GATHER_PEER_STORES),
-                                  ("with_gather_peer_copies", few, sharding.GATHER_PEER_COPIES)):
+                                  ("with_gather_peer_copies", few, sharding.GATHER_PEER_COPIES),
+                                  ("with_gather_peer_both", chunks, sharding.GATHER_PEER_BOTH)):
             if gather and world == 1:
                 continue
+            if gather:
+                full.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
             ms = timed(ch, gather)
             res[label] = {"ms": ms, "tflops": flops_of(B, H, S, D, True) / (ms * 1e-3) / 1e12, "chunks": ch}
+            if gather:
+                # a size-independent property of the gathered output: every rank holds the same bytes, and their checksum is
+                # the sum of the checksums of the parts the ranks computed
+                view = full.view(torch.int16 if full.element_size() == 2 else torch.int32).view(ch, world, -1)
+                mine = view[:, rank].to(torch.int64).sum()
+                whole = view.to(torch.int64).sum()
+                parts = mine.clone()
+                dist.all_reduce(parts)
+                lo, hi = whole.clone(), whole.clone()
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+                dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                res[label]["gathered_checksums_agree"] = bool(int(lo) == int(hi) == int(parts))
         res["gather_chunks"] = chunks
         res["gathered_bytes_per_rank"] = int((B - Bl) * S * E * full.element_size()) if world > 1 else 0
         out[name] = res

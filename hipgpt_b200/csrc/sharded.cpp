@@ -23,7 +23,8 @@
 // the ranks.
 // Third transport (gather = HIPGPT_GATHER_PEER_COPIES): the same mapped buffers and the same ordering, but the data is
 // moved by copy engines: one cudaMemcpyAsync per peer and chunk, each on a stream of its peer, so that no SM and no issue
-// slot is taken from the attention kernels.
+// slot is taken from the attention kernels.  gather = HIPGPT_GATHER_PEER_BOTH serves some peers one way and the others the
+// other way at the same time (HIPGPT_GATHER_COPY_PEERS overrides how many go to the copy engines).
 //
 // NCCL is loaded at run time (dlopen of libnccl.so.2: in a torch process that is the copy torch already
 // loaded), so the single-GPU library has no link dependency on it.
@@ -267,16 +268,26 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int k = B / (c->world * chunks);
     const size_t batch = (size_t)S * E * elem_bytes;             // bytes of one batch item of a plane
-    if (gather < 0 || gather > HIPGPT_GATHER_PEER_COPIES) return fail(HIPGPT_ERR_BAD_ARG, "gather = %d is none of 0, 1, 2, 3", gather);
+    if (gather < 0 || gather > HIPGPT_GATHER_PEER_BOTH) return fail(HIPGPT_ERR_BAD_ARG, "gather = %d is none of 0, 1, 2, 3, 4", gather);
     const bool comm = gather && c->world > 1;
-    const bool push = comm && (gather == HIPGPT_GATHER_PEER_STORES || gather == HIPGPT_GATHER_PEER_COPIES);
-    const bool dma = comm && gather == HIPGPT_GATHER_PEER_COPIES;
+    const bool push = comm && gather >= HIPGPT_GATHER_PEER_STORES;            // any transport into the peers' mapped buffers
+    // peers (rank + 1 .. rank + n_copy) are served by copy engines, the others by the copy kernel's stores
+    int n_copy = 0;
+    if (comm && gather == HIPGPT_GATHER_PEER_COPIES) n_copy = c->world - 1;
+    if (comm && gather == HIPGPT_GATHER_PEER_BOTH) {
+        n_copy = ((c->world - 1) * 3 + 3) / 7;       // the two transports' rates beside the kernels measured about 3 : 4
+        if (const char *env = getenv("HIPGPT_GATHER_COPY_PEERS")) n_copy = atoi(env);
+        if (n_copy < 0) n_copy = 0;
+        if (n_copy > c->world - 1) n_copy = c->world - 1;
+    }
+    const bool dma = n_copy > 0;
+    const bool stores = push && n_copy < c->world - 1;
     Nccl *n = comm ? nccl() : nullptr;
     if (push) {
         const uint8_t *o = static_cast<const uint8_t *>(d_out);
         const size_t need = (size_t)B * batch;
         if (!c->own_out || o < c->own_out || o + need > c->own_out + c->own_bytes)
-            return fail(HIPGPT_ERR_BAD_ARG, "gather = 2 and 3 need d_out inside the buffer of hipgpt_shard_output_buffer (%zu bytes needed)", need);
+            return fail(HIPGPT_ERR_BAD_ARG, "gather = 2, 3 and 4 need d_out inside the buffer of hipgpt_shard_output_buffer (%zu bytes needed)", need);
         if (((size_t)k * batch) & 15) return fail(HIPGPT_ERR_BAD_ARG, "a rank's chunk of %zu bytes is not a multiple of 16", (size_t)k * batch);
         // no rank writes into a peer that has not reached this call on its stream
         cudaError_t e = cudaEventRecord(c->entered, st);
@@ -287,8 +298,7 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
         if (dma) {
             // the per-peer copy streams start behind that collective
             e = cudaEventRecord(c->entered, c->comm_stream);
-            for (int p = 0; p < c->world && e == cudaSuccess; ++p)
-                if (p != c->rank) e = cudaStreamWaitEvent(c->peer_stream[p], c->entered, 0);
+            for (int i = 1; i <= n_copy && e == cudaSuccess; ++i) e = cudaStreamWaitEvent(c->peer_stream[(c->rank + i) % c->world], c->entered, 0);
             if (e != cudaSuccess) return cuda_fail(e, "event hand-off");
         }
     }
@@ -305,26 +315,24 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
         if (rc != HIPGPT_OK) return rc;
         if (!comm) continue;
         cudaError_t e = cudaEventRecord(c->computed[ch], st);
-        if (e == cudaSuccess && !dma) e = cudaStreamWaitEvent(c->comm_stream, c->computed[ch], 0);
+        if (e == cudaSuccess && (!push || stores)) e = cudaStreamWaitEvent(c->comm_stream, c->computed[ch], 0);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "event hand-off: %s", cudaGetErrorString(e));
-        if (dma) {
-            // one copy per peer and chunk, each on its peer's stream: copy engines move the data, no SM is used
+        if (push) {
             const size_t off = (size_t)(mine - c->own_out);
-            for (int i = 1; i < c->world && e == cudaSuccess; ++i) {
+            // one copy per copy-engine peer and chunk, each on its peer's stream: no SM is used
+            for (int i = 1; i <= n_copy && e == cudaSuccess; ++i) {
                 const int p = (c->rank + i) % c->world;
                 e = cudaStreamWaitEvent(c->peer_stream[p], c->computed[ch], 0);
                 if (e == cudaSuccess) e = cudaMemcpyAsync(c->peer_out[p] + off, mine, (size_t)k * batch, cudaMemcpyDeviceToDevice, c->peer_stream[p]);
             }
             if (e != cudaSuccess) return cuda_fail(e, "peer copy");
-            continue;
-        }
-        if (push) {
-            void *dst[hipgpt_shard_ctx::kMaxPeers];
-            int nd = 0;
-            const size_t off = (size_t)(mine - c->own_out);
-            for (int p = 1; p < c->world; ++p) dst[nd++] = c->peer_out[(c->rank + p) % c->world] + off;      // each rank starts with its right-hand neighbour
-            const int prc = launch_shard_push(mine, dst, nd, (size_t)k * batch, c->comm_stream);
-            if (prc != HIPGPT_OK) return prc;
+            if (stores) {
+                void *dst[hipgpt_shard_ctx::kMaxPeers];
+                int nd = 0;
+                for (int i = n_copy + 1; i < c->world; ++i) dst[nd++] = c->peer_out[(c->rank + i) % c->world] + off;
+                const int prc = launch_shard_push(mine, dst, nd, (size_t)k * batch, c->comm_stream);
+                if (prc != HIPGPT_OK) return prc;
+            }
             continue;
         }
         const ncclResult_t r = n->AllGather(mine, block, (size_t)k * batch, ncclChar, c->comm, c->comm_stream);
@@ -332,8 +340,8 @@ int hipgpt_mha_forward_sharded(hipgpt_shard_ctx *c, const void *d_q, const void 
     }
     if (dma) {
         cudaError_t e = cudaSuccess;
-        for (int p = 0; p < c->world && e == cudaSuccess; ++p) {
-            if (p == c->rank) continue;
+        for (int i = 1; i <= n_copy && e == cudaSuccess; ++i) {
+            const int p = (c->rank + i) % c->world;
             e = cudaEventRecord(c->peer_done[p], c->peer_stream[p]);
             if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm_stream, c->peer_done[p], 0);
         }

@@ -92,7 +92,7 @@ def local_planes_chunked(qkv: torch.Tensor, B: int, S: int, E: int, world: int, 
     return torch.cat(parts, dim=1).reshape(3, (B // world) * S, E).contiguous()
 
 
-GATHER_NONE, GATHER_NCCL, GATHER_PEER_STORES, GATHER_PEER_COPIES = 0, 1, 2, 3
+GATHER_NONE, GATHER_NCCL, GATHER_PEER_STORES, GATHER_PEER_COPIES, GATHER_PEER_BOTH = 0, 1, 2, 3, 4
 
 
 class ShardedAttention:

@@ -327,6 +327,7 @@ HIPGPT_API int hipgpt_gpt_set_mode(hipgpt_gpt *g, int mode);
 #define HIPGPT_GATHER_NCCL        1
 #define HIPGPT_GATHER_PEER_STORES 2
 #define HIPGPT_GATHER_PEER_COPIES 3   /* as 2, but one cudaMemcpyAsync per peer and chunk on a stream per peer: copy engines, no SM */
+#define HIPGPT_GATHER_PEER_BOTH   4   /* 3 for the first three sevenths of the peers, 2 for the others, side by side */
 typedef struct hipgpt_shard_ctx hipgpt_shard_ctx;
 HIPGPT_API int hipgpt_shard_range(int B, int world, int rank, int *b_begin, int *b_end);
 HIPGPT_API int hipgpt_shard_chunk_range(int B, int world, int rank, int chunks, int chunk, int *b_begin, int *b_end);

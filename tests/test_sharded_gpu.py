@@ -50,7 +50,8 @@ def _worker(rank, world, port, ret):
                 pout.fill_(float("nan"))
                 torch.cuda.synchronize()
                 dist.barrier()                       # every rank's buffer is filled before any peer writes into it
-                for mode in (sharding.GATHER_PEER_STORES, sharding.GATHER_PEER_STORES, sharding.GATHER_PEER_COPIES, sharding.GATHER_PEER_COPIES):
+                for mode in (sharding.GATHER_PEER_STORES, sharding.GATHER_PEER_STORES, sharding.GATHER_PEER_COPIES, sharding.GATHER_PEER_COPIES,
+                             sharding.GATHER_PEER_BOTH):
                     # each twice: the second call writes over a buffer the peers have just read
                     sh.forward(loc[0], loc[1], loc[2], pout, B, S, E, H, causal=causal, chunks=chunks, gather=mode)
                     torch.cuda.synchronize()
