@@ -127,6 +127,7 @@ __device__ __forceinline__ void chunk_zero(uint32_t addr)
 
 struct HeadMaps {
     CUtensorMap q, k, v;
+    CUtensorMap q32;                             // Q in boxes of 32 rows (a causal head's first query tile, below)
 };
 
 template <bool CAUSAL, bool PROBS>
@@ -155,6 +156,13 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
     // that follow from it) to be the same for the whole warp: descriptors then live in uniform registers
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int nq = S > kTile ? 2 : 1;            // query tiles = key tiles of a head
+    // A causal head of two tiles has two diagonal score tiles, (q0, k0) and (q1, k1), where a warp's work grows with its
+    // rows: the warp of TMEM lanes 96-127 sweeps four 32-column chunks, that of lanes 0-31 one.  A warp's number fixes
+    // both its lanes and its scheduler (warp mod 4), so one scheduler would get 4 + 4 + 4 chunks of exponentials per
+    // head and another 1 + 4 + 1.  The first query tile's rows are therefore kept in TMEM lanes with the four groups of
+    // 32 in reverse order (tile row r in lanes of group 3 - r / 32): the copies place them so, and every place that
+    // turns a lane of that tile into a row (mask, output row, probabilities) turns it back.  9 chunks per scheduler.
+    const bool flip0 = CAUSAL && nq == 2;
 
     // site codes: 1 Q/K/V landed, 2 operand converted, 3 S ready, 4 P written, 5 output complete,
     // 6 row maxima exchanged, 7 row sums exchanged, 8 previous head's output read, 9 V maximum exchanged,
@@ -187,7 +195,12 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
                     mbar_arrive_expect_tx(&ld_k[t], kTileBytes);
                     tma_load_3d(k_raw + t * kTileBytes, &maps.k, c0, t * kTile, b, &ld_k[t]);
                     mbar_arrive_expect_tx(&ld_q[t], kTileBytes);
-                    tma_load_3d(q_raw + t * kTileBytes, &maps.q, c0, t * kTile, b, &ld_q[t]);
+                    if (t == 0 && flip0) {
+                        for (int g = 0; g < 4; ++g)
+                            tma_load_3d(q_raw + (3 - g) * (32 * 128), &maps.q32, c0, g * 32, b, &ld_q[0]);
+                    } else {
+                        tma_load_3d(q_raw + t * kTileBytes, &maps.q, c0, t * kTile, b, &ld_q[t]);
+                    }
                 }
             }
             __syncwarp();
@@ -530,9 +543,10 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
             const uint32_t s_addr = lane_base + (uint32_t)(buf * kTile);
             const int ncols = min(kTile, S - k * kTile);
             const bool diag = CAUSAL && q == k;
-            const int nwarp = diag ? min(ncols, wq * 32 + 32) : ncols;
+            const int eq = (flip0 && q == 0) ? 3 - wq : wq;     // the group of 32 rows of the tile that this warp's lanes hold
+            const int nwarp = diag ? min(ncols, eq * 32 + 32) : ncols;
             const int nch = (nwarp + 31) >> 5;
-            const int wrow0 = q * kTile + wq * 32;              // first row of this warp
+            const int wrow0 = q * kTile + eq * 32;              // first row of this warp
             const float inv = 1.0f / fmaxf(l_total, 1e-20f);
             uint8_t *tb = (grp == 0 ? q_raw : grp == 1 ? q_16 : k_raw) + wq * 4096;   // [32 rows][128 bytes], 16-byte chunks swizzled by the row
             float *pw = P + ((size_t)hd * S + wrow0) * (size_t)S + (size_t)k * kTile;
@@ -597,9 +611,10 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
             const uint32_t s_addr = lane_base + (uint32_t)(buf * kTile);
             const int ncols = min(kTile, S - k * kTile);                      // keys of this tile that exist
             const bool diag = CAUSAL && q == k;
-            const int nvalid = diag ? min(ncols, rloc + 1) : ncols;           // keys this row sees
-            const int nwarp = diag ? min(ncols, wq * 32 + 32) : ncols;        // ... the warp's last row sees
-            const int nmin = diag ? min(ncols, wq * 32 + 1) : ncols;          // ... its first row sees
+            const int eq = (flip0 && q == 0) ? 3 - wq : wq;                   // the group of 32 rows of the tile that this warp's lanes hold
+            const int nvalid = diag ? min(ncols, eq * 32 + lane + 1) : ncols; // keys this row sees
+            const int nwarp = diag ? min(ncols, eq * 32 + 32) : ncols;        // ... the warp's last row sees
+            const int nmin = diag ? min(ncols, eq * 32 + 1) : ncols;          // ... its first row sees
             const int nch = (nwarp + 31) >> 5;                                // 32-column chunks with any visible key
             wait(&s_full[buf], spar, 3);
             tc_fence_after();
@@ -665,7 +680,7 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
             tc_fence_after();
             if (PROBS && !(!CAUSAL && njobs == 2 && ji == 0)) store_probs(job, l);
             const float inv = (1.0f / fmaxf(l, 1e-20f)) * s_vinv[par];
-            const int row = q * kTile + rloc;
+            const int row = q * kTile + ((flip0 && q == 0) ? 3 - wq : wq) * 32 + lane;
             const bool store = !abort_flag && row < S;
             float4 *dst = reinterpret_cast<float4 *>(O + ((size_t)b * S + (row < S ? row : 0)) * (size_t)E + (size_t)h * 32);
             const uint32_t o_addr = lane_base + kColO + (uint32_t)(q * 64);
@@ -734,6 +749,7 @@ int launch_mha_head(const float *q, const float *k, const float *v, float *out, 
     if (B == 0 || S == 0) return HIPGPT_OK;
     HeadMaps maps;
     int rc = tma_plane_map(&maps.q, q, B, S, E, kTile, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == HIPGPT_OK) rc = tma_plane_map(&maps.q32, q, B, S, E, 32, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == HIPGPT_OK) rc = tma_plane_map(&maps.k, k, B, S, E, kTile, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc == HIPGPT_OK) rc = tma_plane_map(&maps.v, v, B, S, E, kTile, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HIPGPT_OK) return rc;
