@@ -40,6 +40,7 @@ SIGNATURES = {
     "hipgpt_matmul_tc_release": (None, [_vp]),
     "hipgpt_layer_norm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "hipgpt_dropout": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
+    "hipgpt_dropout_residual": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "hipgpt_add_inplace": (_i, [_vp, _vp, C.c_longlong, _vp]),
     "hipgpt_relu": (_i, [_vp, C.c_longlong, _vp]),
     "hipgpt_embedding_lookup": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -176,6 +176,45 @@ __global__ void dropout_index_kernel(const float *in, float *out, float *__restr
     if (mask) mask[idx] = drop ? 0.0f : 1.0f;
 }
 
+// out = residual + dropout(in): the sub-layer tail of the reference's block (dropout in place, then the residual
+// add, src/transformer_layer.cpp:242-244 and :250-252) in one pass over memory instead of three.  The same generator,
+// the same division, the same addition: bit-identical to hipgpt_dropout followed by hipgpt_add_inplace.  Four
+// consecutive elements per thread when the count and the pointers allow 16-byte accesses.
+__device__ __forceinline__ bool dropped(unsigned idx, float p)
+{
+    const unsigned s = idx + 1u;
+    unsigned t = idx * (idx >> 8) + 1u;          // the reference's block of an element is idx / 256
+    t ^= t >> 2;
+    t ^= t << 1;
+    t ^= s ^ (s << 4);
+    return __fdiv_rn((float)(t + 1u), 4294967296.0f) < p;
+}
+
+__global__ void __launch_bounds__(256)
+dropout_residual_kernel(const float *in, const float *residual, float *out, float *__restrict__ mask, float p, unsigned n, int vec)   // out may be in or residual
+{
+    const float keep = __fsub_rn(1.0f, p);
+    if (vec) {
+        const unsigned i4 = (blockIdx.x * 256u + threadIdx.x) * 4u;
+        if (i4 >= n) return;
+        const float4 x = *reinterpret_cast<const float4 *>(in + i4), r = *reinterpret_cast<const float4 *>(residual + i4);
+        const bool d0 = dropped(i4, p), d1 = dropped(i4 + 1u, p), d2 = dropped(i4 + 2u, p), d3 = dropped(i4 + 3u, p);
+        float4 o;
+        o.x = __fadd_rn(r.x, d0 ? 0.0f : __fdiv_rn(x.x, keep));
+        o.y = __fadd_rn(r.y, d1 ? 0.0f : __fdiv_rn(x.y, keep));
+        o.z = __fadd_rn(r.z, d2 ? 0.0f : __fdiv_rn(x.z, keep));
+        o.w = __fadd_rn(r.w, d3 ? 0.0f : __fdiv_rn(x.w, keep));
+        *reinterpret_cast<float4 *>(out + i4) = o;
+        if (mask) *reinterpret_cast<float4 *>(mask + i4) = make_float4(d0 ? 0.f : 1.f, d1 ? 0.f : 1.f, d2 ? 0.f : 1.f, d3 ? 0.f : 1.f);
+    } else {
+        const unsigned idx = blockIdx.x * 256u + threadIdx.x;
+        if (idx >= n) return;
+        const bool d = dropped(idx, p);
+        out[idx] = __fadd_rn(residual[idx], d ? 0.0f : __fdiv_rn(in[idx], keep));
+        if (mask) mask[idx] = d ? 0.0f : 1.0f;
+    }
+}
+
 __global__ void add_inplace_kernel(float *__restrict__ a, const float *__restrict__ b, long long n)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -245,6 +284,17 @@ int launch_dropout_index(const float *in, float *out, float *mask, float p, long
     if (n > 0xffffffffLL) return fail(HIPGPT_ERR_BAD_ARG, "dropout over %lld elements: the reference's index is 32 bits wide", n);
     dropout_index_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, out, mask, p, (unsigned)n);
     return check_launch("dropout_index_kernel");
+}
+
+int launch_dropout_residual(const float *in, const float *residual, float *out, float *mask, float p, long long n, cudaStream_t st)
+{
+    if (n == 0) return HIPGPT_OK;
+    if (n > 0xffffffffLL) return fail(HIPGPT_ERR_BAD_ARG, "dropout over %lld elements: the reference's index is 32 bits wide", n);
+    const uintptr_t all = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(mask);
+    const int vec = (n % 4 == 0) && (all & 15) == 0;
+    const long long threads = vec ? n / 4 : n;
+    dropout_residual_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(in, residual, out, mask, p, (unsigned)n, vec);
+    return check_launch("dropout_residual_kernel");
 }
 
 int launch_add_inplace_n(float *a, const float *b, long long n, cudaStream_t st)
@@ -330,6 +380,15 @@ int hipgpt_dropout(const float *d_in, float *d_out, float *d_mask, float p, int 
     if (rows == 0 || E == 0) return HIPGPT_OK;
     if (!d_in || !d_out) return fail(HIPGPT_ERR_NULL, "input and output must not be NULL");
     return launch_dropout_index(d_in, d_out, d_mask, p, (long long)rows * E, static_cast<cudaStream_t>(stream));
+}
+
+int hipgpt_dropout_residual(const float *d_in, const float *d_residual, float *d_out, float *d_mask, float p, int rows, int E, void *stream)
+{
+    if (rows < 0 || E < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: rows=%d E=%d", rows, E);
+    if (!(p >= 0.0f && p < 1.0f)) return fail(HIPGPT_ERR_BAD_ARG, "dropout probability %g outside [0, 1)", (double)p);
+    if (rows == 0 || E == 0) return HIPGPT_OK;
+    if (!d_in || !d_residual || !d_out) return fail(HIPGPT_ERR_NULL, "input, residual and output must not be NULL");
+    return launch_dropout_residual(d_in, d_residual, d_out, d_mask, p, (long long)rows * E, static_cast<cudaStream_t>(stream));
 }
 
 int hipgpt_add_inplace(float *d_a, const float *d_b, long long n, void *stream)

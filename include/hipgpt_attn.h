@@ -184,6 +184,10 @@ HIPGPT_API int hipgpt_mha_backward_planes(const float *d_grad_out, const float *
  *   hipgpt_dropout           replaces launch_dropout_forward (src/hip_kernels.cpp:944-970): the mask depends
  *                            on the element index only (generator at :24-42); bit-identical; d_mask may be
  *                            NULL; in place (d_in == d_out) allowed.
+ *   hipgpt_dropout_residual  out = residual + dropout(in): the tail of each sub-layer of the reference's block
+ *                            (src/transformer_layer.cpp:242-244, 250-252: dropout in place, device copy, add) in one
+ *                            pass over memory; bit-identical to hipgpt_dropout followed by hipgpt_add_inplace; d_out
+ *                            may be d_in or d_residual; d_mask may be NULL.
  *   hipgpt_add_inplace       a += b           (launch_add_inplace, src/hip_kernels.cpp:721-730)
  *   hipgpt_relu              a = max(0, a)    (launch_relu, src/hip_kernels.cpp:248-258)
  *   hipgpt_embedding_lookup  out[t] = tok[id_t] + pos[t mod S], zeros for an id outside [0, V)
@@ -197,6 +201,7 @@ HIPGPT_API int hipgpt_matmul_tc_prepared(const float *d_A, const hipgpt_packed_m
 HIPGPT_API void hipgpt_matmul_tc_release(hipgpt_packed_matrix *b);
 HIPGPT_API int hipgpt_layer_norm(const float *d_in, float *d_out, const float *d_gamma, const float *d_beta, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_dropout(const float *d_in, float *d_out, float *d_mask, float p, int rows, int E, void *stream);
+HIPGPT_API int hipgpt_dropout_residual(const float *d_in, const float *d_residual, float *d_out, float *d_mask, float p, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_add_inplace(float *d_a, const float *d_b, long long n, void *stream);
 HIPGPT_API int hipgpt_relu(float *d_a, long long n, void *stream);
 HIPGPT_API int hipgpt_embedding_lookup(const int *d_ids, const float *d_tok, const float *d_pos, float *d_out,

@@ -146,6 +146,28 @@ def test_dropout_mask_is_the_reference_index_hash():
     assert lib.hipgpt_dropout(dx.data_ptr(), dx.data_ptr(), None, 1.0, rows, E, _st()) == _capi.ERR_BAD_ARG
 
 
+@pytest.mark.parametrize("rows,E", [(8192, 256), (33, 100), (7, 3), (1, 1)])
+def test_fused_dropout_residual_equals_the_two_launchers(rows, E):
+    """hipgpt_dropout_residual = hipgpt_dropout followed by hipgpt_add_inplace, bit for bit, mask included; in place too."""
+    lib = _capi.lib()
+    x, r = synth.normal(70 + E, (rows, E)), synth.normal(71 + E, (rows, E))
+    dx, dr = dev(x), dev(r)
+    two, mask2 = torch.empty_like(dx), torch.empty_like(dx)
+    _capi.check(lib.hipgpt_dropout(dx.data_ptr(), two.data_ptr(), mask2.data_ptr(), C.c_float(0.1), rows, E, _st()))
+    res = dr.clone()
+    _capi.check(lib.hipgpt_add_inplace(res.data_ptr(), two.data_ptr(), rows * E, _st()))
+    one, mask1 = torch.full_like(dx, float("nan")), torch.full_like(dx, float("nan"))
+    _capi.check(lib.hipgpt_dropout_residual(dx.data_ptr(), dr.data_ptr(), one.data_ptr(), mask1.data_ptr(), C.c_float(0.1), rows, E, _st()))
+    torch.cuda.synchronize()
+    assert torch.equal(one, res) and torch.equal(mask1, mask2)
+    # in place on the residual, without a mask, from an address that is not 16-byte aligned
+    buf = torch.zeros(rows * E + 1, device="cuda")
+    buf[1:] = dr.view(-1)
+    _capi.check(lib.hipgpt_dropout_residual(dx.data_ptr(), buf[1:].data_ptr(), buf[1:].data_ptr(), None, C.c_float(0.1), rows, E, _st()))
+    torch.cuda.synchronize()
+    assert torch.equal(buf[1:].view(rows, E), res)
+
+
 def test_add_relu_embedding_are_exact():
     lib = _capi.lib()
     n = 100003
