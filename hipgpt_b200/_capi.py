@@ -38,6 +38,8 @@ SIGNATURES = {
     "hipgpt_matmul_tc_prepare": (_i, [_vp, _i, _i, C.POINTER(_vp), _vp]),
     "hipgpt_matmul_tc_prepared": (_i, [_vp, _vp, _vp, _vp, _i, _vp]),
     "hipgpt_matmul_tc_release": (None, [_vp]),
+    "hipgpt_ln_matmul_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hipgpt_ln_matmul_tc_prepared": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "hipgpt_layer_norm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "hipgpt_dropout": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "hipgpt_dropout_residual": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),

@@ -97,10 +97,10 @@ int launch_mha_backward(const float *g, const float *q, const float *k, const fl
 // the launchers either side of attention (layer_ops.cu)
 int launch_matmul_exact(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st);
 // The same product on the tensor pipe with fp32-grade (not bit-identical) results (gemm_tc.cu); its status word and scratch.
-int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st);
+int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st, const float *ln_g = nullptr, const float *ln_b = nullptr);
 struct PackedB;                                  // a right-hand side packed once for many products
 int matmul_tc_prepare(const float *B, int N, int K, PackedB **out, cudaStream_t st);
-int launch_matmul_tc_prepared(const float *A, const PackedB *b, const float *bias, float *C, int M, cudaStream_t st);
+int launch_matmul_tc_prepared(const float *A, const PackedB *b, const float *bias, float *C, int M, cudaStream_t st, const float *ln_g = nullptr, const float *ln_b = nullptr);
 void matmul_tc_release(PackedB *p);
 int gemm_tc_status_fetch(int *status);
 void gemm_tc_release_scratch();

@@ -82,8 +82,11 @@ __global__ void __launch_bounds__(256) gemm_amax_kernel(const float *__restrict_
 // One warp per row of A (rows up to the padded count: rows past M are zeros).  A lane owns runs of 8 consecutive values
 // (one 16-byte chunk of fp16).  Image: stage (mt, kt) at ((mt * KT + kt) * kAStage); block 0 = hi, block 1 = lo; row r,
 // chunk c at r * 128 + ((c ^ (r & 7)) * 16).
+// With ln_g / ln_b given, the row is layer-normalised first (mean and variance over its N values, eps 1e-5, times gamma
+// plus beta: launch_layer_norm_forward, src/hip_kernels.cpp:757-848, to rounding), so that LN + projection of the
+// reference's block (src/transformer_layer.cpp:240-241, 246-247) need no pass over memory of their own.
 __global__ void __launch_bounds__(128) gemm_pack_a_kernel(const float *__restrict__ A, uint8_t *__restrict__ img, float *__restrict__ row_inv,
-                                                           int M, int N, int KT)
+                                                           int M, int N, int KT, const float *__restrict__ ln_g, const float *__restrict__ ln_b)
 {
     // overlapped launch: placed while the kernel before it drains; waiting for it here also orders the product kernel,
     // which waits for this one, after everything before
@@ -94,7 +97,7 @@ __global__ void __launch_bounds__(128) gemm_pack_a_kernel(const float *__restric
     const bool live = m < M;
     const float *row = A + (size_t)(live ? m : 0) * N;
     const bool vec = (N & 3) == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0;
-    auto load8 = [&](int k0, float (&v)[8]) {
+    auto raw8 = [&](int k0, float (&v)[8]) {
         if (live && vec && k0 + 8 <= N) {
             const float4 a = __ldg(reinterpret_cast<const float4 *>(row + k0)), b = __ldg(reinterpret_cast<const float4 *>(row + k0) + 1);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
@@ -104,6 +107,37 @@ __global__ void __launch_bounds__(128) gemm_pack_a_kernel(const float *__restric
         }
     };
     const int depth = KT * kTK;
+    float mean = 0.0f, rstd = 1.0f;
+    if (ln_g) {
+        float sum = 0.0f;
+        for (int k0 = lane * 8; k0 < depth; k0 += 256) {
+            float v[8];
+            raw8(k0, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += v[j];             // values past N are zeros
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        mean = sum / (float)N;
+        float var = 0.0f;
+        for (int k0 = lane * 8; k0 < depth; k0 += 256) {
+            float v[8];
+            raw8(k0, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { const float d = (k0 + j < N) ? v[j] - mean : 0.0f; var = fmaf(d, d, var); }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+        rstd = 1.0f / sqrtf(var / (float)N + 1e-5f);
+    }
+    auto load8 = [&](int k0, float (&v)[8]) {
+        raw8(k0, v);
+        if (ln_g) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                v[j] = (live && k0 + j < N) ? __ldg(ln_g + k0 + j) * (v[j] - mean) * rstd + __ldg(ln_b + k0 + j) : 0.0f;
+        }
+    };
     float amax = 0.0f;
     for (int k0 = lane * 8; k0 < depth; k0 += 256) {
         float v[8];
@@ -425,16 +459,16 @@ int pack_b(const float *B, int N, int K, uint8_t *bimg, float *b_amax, cudaStrea
 
 // A -> its stage images, then the product kernel, with B's images given
 int pack_a_and_multiply(const float *A, const uint8_t *bimg, const float *b_amax, const float *bias, float *C, int M, int N, int K,
-                        uint8_t *aimg, float *row_inv, bool first_is_plain, int dev, cudaStream_t st)
+                        uint8_t *aimg, float *row_inv, bool first_is_plain, int dev, cudaStream_t st, const float *ln_g = nullptr, const float *ln_b = nullptr)
 {
     const int MT = (M + kTM - 1) / kTM, NT = (K + kTN - 1) / kTN, KT = (N + kTK - 1) / kTK;
     cudaError_t e;
     if (first_is_plain) {
         // nothing of this call precedes the pack kernel: a plain launch, so that the product kernel, which waits for the
         // pack kernel only, is ordered after everything before the call (the kernel's own wait then returns at once)
-        gemm_pack_a_kernel<<<(unsigned)(MT * kTM / 4), 128, 0, st>>>(A, aimg, row_inv, M, N, KT);
+        gemm_pack_a_kernel<<<(unsigned)(MT * kTM / 4), 128, 0, st>>>(A, aimg, row_inv, M, N, KT, ln_g, ln_b);
     } else {
-        e = launch_overlapped(gemm_pack_a_kernel, dim3((unsigned)(MT * kTM / 4)), dim3(128), 0, st, A, aimg, row_inv, M, N, KT);
+        e = launch_overlapped(gemm_pack_a_kernel, dim3((unsigned)(MT * kTM / 4)), dim3(128), 0, st, A, aimg, row_inv, M, N, KT, ln_g, ln_b);
         if (e != cudaSuccess) return fail(HIPGPT_ERR_CUDA, "gemm_pack_a_kernel launch: %s", cudaGetErrorString(e));
     }
     int rc = check_launch("gemm_pack_a_kernel");
@@ -453,7 +487,7 @@ int pack_a_and_multiply(const float *A, const uint8_t *bimg, const float *b_amax
 }  // namespace
 
 // C[M][K] = A[M][N] B[N][K] (+ bias), fp32-grade on the tensor pipe.  C must not alias A or B.
-int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st)
+int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, cudaStream_t st, const float *ln_g, const float *ln_b)
 {
     const int MT = (M + kTM - 1) / kTM, NT = (K + kTN - 1) / kTN, KT = (N + kTK - 1) / kTK;
     if (MT > 65535) return fail(HIPGPT_ERR_BAD_ARG, "M = %d is beyond %d rows per call", M, 65535 * kTM);
@@ -470,7 +504,7 @@ int launch_matmul_tc(const float *A, const float *B, const float *bias, float *C
     rc = set_gemm_attr();
     if (rc == HIPGPT_OK) rc = pack_b(B, N, K, bimg, b_amax, st);
     if (rc != HIPGPT_OK) return rc;
-    return pack_a_and_multiply(A, bimg, b_amax, bias, C, M, N, K, aimg, row_inv, false, dev, st);
+    return pack_a_and_multiply(A, bimg, b_amax, bias, C, M, N, K, aimg, row_inv, false, dev, st, ln_g, ln_b);
 }
 
 // ---- a right-hand side packed once (the weights of a layer) and used by many products ---------------------------
@@ -503,7 +537,7 @@ void matmul_tc_release(PackedB *p)
     delete p;
 }
 
-int launch_matmul_tc_prepared(const float *A, const PackedB *b, const float *bias, float *C, int M, cudaStream_t st)
+int launch_matmul_tc_prepared(const float *A, const PackedB *b, const float *bias, float *C, int M, cudaStream_t st, const float *ln_g, const float *ln_b)
 {
     const int N = b->N, K = b->K;
     const int MT = (M + kTM - 1) / kTM, KT = (N + kTK - 1) / kTK;
@@ -518,7 +552,7 @@ int launch_matmul_tc_prepared(const float *A, const PackedB *b, const float *bia
     if (rc != HIPGPT_OK) return rc;
     rc = set_gemm_attr();
     if (rc != HIPGPT_OK) return rc;
-    return pack_a_and_multiply(A, b->bimg, b->b_amax, bias, C, M, N, K, scratch, reinterpret_cast<float *>(scratch + abytes), true, dev, st);
+    return pack_a_and_multiply(A, b->bimg, b->b_amax, bias, C, M, N, K, scratch, reinterpret_cast<float *>(scratch + abytes), true, dev, st, ln_g, ln_b);
 }
 
 }  // namespace hipgpt

@@ -365,6 +365,27 @@ int hipgpt_matmul_tc_prepared(const float *d_A, const hipgpt_packed_matrix *b, c
 
 void hipgpt_matmul_tc_release(hipgpt_packed_matrix *b) { matmul_tc_release(reinterpret_cast<PackedB *>(b)); }
 
+int hipgpt_ln_matmul_tc(const float *d_A, const float *d_gamma, const float *d_beta, const float *d_B, const float *d_bias, float *d_C,
+                        int M, int N, int K, void *stream)
+{
+    if (M < 0 || N <= 0 || K < 0) return fail(HIPGPT_ERR_BAD_ARG, "bad size: M=%d N=%d K=%d", M, N, K);
+    if (M == 0 || K == 0) return HIPGPT_OK;
+    if (!d_A || !d_B || !d_C || !d_gamma || !d_beta) return fail(HIPGPT_ERR_NULL, "A, gamma, beta, B and C must not be NULL");
+    if (d_C == d_A || d_C == d_B) return fail(HIPGPT_ERR_UNSUPPORTED, "the tensor-core product does not work in place");
+    return launch_matmul_tc(d_A, d_B, d_bias, d_C, M, N, K, static_cast<cudaStream_t>(stream), d_gamma, d_beta);
+}
+
+int hipgpt_ln_matmul_tc_prepared(const float *d_A, const float *d_gamma, const float *d_beta, const hipgpt_packed_matrix *b, const float *d_bias,
+                                 float *d_C, int M, void *stream)
+{
+    if (!b) return fail(HIPGPT_ERR_NULL, "the packed right-hand side must not be NULL");
+    if (M < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: M=%d", M);
+    if (M == 0) return HIPGPT_OK;
+    if (!d_A || !d_C || !d_gamma || !d_beta) return fail(HIPGPT_ERR_NULL, "A, gamma, beta and C must not be NULL");
+    if (d_A == d_C) return fail(HIPGPT_ERR_UNSUPPORTED, "the tensor-core product does not work in place");
+    return launch_matmul_tc_prepared(d_A, reinterpret_cast<const PackedB *>(b), d_bias, d_C, M, static_cast<cudaStream_t>(stream), d_gamma, d_beta);
+}
+
 int hipgpt_layer_norm(const float *d_in, float *d_out, const float *d_gamma, const float *d_beta, int rows, int E, void *stream)
 {
     if (rows < 0 || E < 0) return fail(HIPGPT_ERR_BAD_ARG, "negative size: rows=%d E=%d", rows, E);

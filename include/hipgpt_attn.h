@@ -179,6 +179,10 @@ HIPGPT_API int hipgpt_mha_backward_planes(const float *d_grad_out, const float *
  *                            freed once that stream has passed the call), prepared() multiplies any number of A's
  *                            with it (on streams ordered after it), release() frees it.  Saves two of the four
  *                            launches of every product.
+ *   hipgpt_ln_matmul_tc, hipgpt_ln_matmul_tc_prepared
+ *                            C = LayerNorm(A) B (+ bias): the layer norm before each projection of the reference's
+ *                            block (src/transformer_layer.cpp:240-241 and 246-247) done by the kernel that packs
+ *                            A, so it costs no pass over memory and no launch of its own; fp32-grade like the product.
  *   hipgpt_layer_norm        replaces launch_layer_norm_forward (src/hip_kernels.cpp:757-848), eps 1e-5;
  *                            agrees with the reference's 64-lane reduction order to rounding (~1e-7).
  *   hipgpt_dropout           replaces launch_dropout_forward (src/hip_kernels.cpp:944-970): the mask depends
@@ -199,6 +203,10 @@ typedef struct hipgpt_packed_matrix hipgpt_packed_matrix;
 HIPGPT_API int hipgpt_matmul_tc_prepare(const float *d_B, int N, int K, hipgpt_packed_matrix **out, void *stream);
 HIPGPT_API int hipgpt_matmul_tc_prepared(const float *d_A, const hipgpt_packed_matrix *b, const float *d_bias, float *d_C, int M, void *stream);
 HIPGPT_API void hipgpt_matmul_tc_release(hipgpt_packed_matrix *b);
+HIPGPT_API int hipgpt_ln_matmul_tc(const float *d_A, const float *d_gamma, const float *d_beta, const float *d_B, const float *d_bias, float *d_C,
+                        int M, int N, int K, void *stream);
+HIPGPT_API int hipgpt_ln_matmul_tc_prepared(const float *d_A, const float *d_gamma, const float *d_beta, const hipgpt_packed_matrix *b,
+                                 const float *d_bias, float *d_C, int M, void *stream);
 HIPGPT_API int hipgpt_layer_norm(const float *d_in, float *d_out, const float *d_gamma, const float *d_beta, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_dropout(const float *d_in, float *d_out, float *d_mask, float p, int rows, int E, void *stream);
 HIPGPT_API int hipgpt_dropout_residual(const float *d_in, const float *d_residual, float *d_out, float *d_mask, float p, int rows, int E, void *stream);

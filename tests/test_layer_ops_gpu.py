@@ -91,6 +91,36 @@ def test_tensor_core_matmul_with_weights_packed_once():
     lib.hipgpt_matmul_tc_release(h)
 
 
+@pytest.mark.parametrize("M,N,K", [(8192, 256, 768), (130, 100, 136), (5, 64, 7)])
+def test_layer_norm_fused_into_the_tensor_core_projection(M, N, K):
+    """hipgpt_ln_matmul_tc(_prepared): LayerNorm(A) B + bias against a float64 restatement (mean, variance / N, eps 1e-5)."""
+    lib = _capi.lib()
+    A, W = synth.normal(30, (M, N)) * np.float32(3.0) + np.float32(0.5), synth.normal(31, (N, K), 0.1)
+    g, be, b = synth.normal(32, (N,)) * np.float32(0.2) + np.float32(1.0), synth.normal(33, (N,), 0.1), synth.normal(34, (K,))
+    a64 = A.astype(np.float64)
+    mu, var = a64.mean(axis=1, keepdims=True), a64.var(axis=1, keepdims=True)
+    ln = g.astype(np.float64) * (a64 - mu) / np.sqrt(var + 1e-5) + be.astype(np.float64)
+    want = ln @ W.astype(np.float64) + b.astype(np.float64)
+    dA, dW, dg, dbe, db = dev(A), dev(W), dev(g), dev(be), dev(b)
+    c1 = torch.full((M, K), float("nan"), device="cuda")
+    _capi.check(lib.hipgpt_ln_matmul_tc(dA.data_ptr(), dg.data_ptr(), dbe.data_ptr(), dW.data_ptr(), db.data_ptr(), c1.data_ptr(), M, N, K, _st()))
+    h = C.c_void_p()
+    _capi.check(lib.hipgpt_matmul_tc_prepare(dW.data_ptr(), N, K, C.byref(h), _st()))
+    c2 = torch.full((M, K), float("nan"), device="cuda")
+    _capi.check(lib.hipgpt_ln_matmul_tc_prepared(dA.data_ptr(), dg.data_ptr(), dbe.data_ptr(), h, db.data_ptr(), c2.data_ptr(), M, _st()))
+    torch.cuda.synchronize()
+    lib.hipgpt_matmul_tc_release(h)
+    assert torch.equal(c1, c2)
+    assert np.abs(c1.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+    # and against the separate launchers of this library: hipgpt_layer_norm, then the product
+    y = torch.empty_like(dA)
+    _capi.check(lib.hipgpt_layer_norm(dA.data_ptr(), y.data_ptr(), dg.data_ptr(), dbe.data_ptr(), M, N, _st()))
+    c3 = torch.full((M, K), float("nan"), device="cuda")
+    _capi.check(lib.hipgpt_matmul_tc(y.data_ptr(), dW.data_ptr(), db.data_ptr(), c3.data_ptr(), M, N, K, _st()))
+    torch.cuda.synchronize()
+    assert float((c1 - c3).abs().max()) <= 1e-5 * np.abs(want).max()
+
+
 def test_matmul_in_place_like_the_layers_output_projection():
     """src/transformer_layer.cpp:220 passes d_attn_output_ as both A and C."""
     lib = _capi.lib()
