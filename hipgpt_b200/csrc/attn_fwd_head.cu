@@ -463,6 +463,8 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
     if (grp < 2 && (int)blockIdx.x < BH) convert_kq(0);
 
     int it = 0;
+    float v_sc = 1.0f;                               // group 2: V's scale for the head about to be converted,
+    bool v_scale_known = false;                      // ... when it was found during the head before
     for (int hd = blockIdx.x; hd < BH; hd += gridDim.x, ++it) {
         const uint32_t par = (uint32_t)(it & 1);
         const int b = hd / H, h = hd % H;
@@ -472,16 +474,15 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
         // group's two sweeps it ran beside the other groups' exponentials and took longer: measured slower.)
         // K and Q of this head were converted before the loop (first head) or behind the previous head's
         // exponentials.
-        auto convert_v = [&]() {
-            // V: scaled by a power of two so that the head's largest magnitude lies in [2^14, 2^15), then
-            // [V_hi | V_lo].  The previous head's P V products must have completed before V16 is overwritten.
-            if (it > 0) {
-                wait(&o_done[0], (uint32_t)((it - 1) & 1), 5);
-                if (nq == 2) wait(&o_done[1], (uint32_t)((it - 1) & 1), 5);
-            }
+        // The power of two for the head this block takes `itn`-th, from the largest magnitude of its raw V tiles (a
+        // sweep over them and an exchange between the group's four warps).  It needs the raw tiles only, so for every
+        // head but the first it runs early: behind the group's exponentials of the head before, while that head's P V
+        // products still read the fp16 copy.  What then stands between two heads is the conversion alone.
+        auto v_scale = [&](int itn) {
+            const uint32_t parn = (uint32_t)(itn & 1);
             float amax = 0.0f;
             for (int t = 0; t < nq; ++t) {
-                wait(&ld_v[t], par, 1);
+                wait(&ld_v[t], parn, 1);
                 const uint8_t *src = v_raw + t * kTileBytes;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -491,10 +492,10 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            if (lane == 0) vmaxw[par][wq] = amax;
+            if (lane == 0) vmaxw[parn][wq] = amax;
             arrive(&vx);
-            wait(&vx, par, 9);
-            const float vm = fmaxf(fmaxf(vmaxw[par][0], vmaxw[par][1]), fmaxf(vmaxw[par][2], vmaxw[par][3]));
+            wait(&vx, parn, 9);
+            const float vm = fmaxf(fmaxf(vmaxw[parn][0], vmaxw[parn][1]), fmaxf(vmaxw[parn][2], vmaxw[parn][3]));
             float sc = 1.0f, inv = 1.0f;
             if (vm > 0.0f && vm <= 3.0e38f) {
                 const int e = (int)((__float_as_uint(vm) >> 23) & 0xffu) - 127;
@@ -502,7 +503,15 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
                 sc = __uint_as_float((uint32_t)(127 + sh) << 23);
                 inv = __uint_as_float((uint32_t)(127 - sh) << 23);
             }
-            if (tid == 2 * kTile) s_vinv[par] = inv;
+            if (tid == 2 * kTile) s_vinv[parn] = inv;
+            return sc;
+        };
+        auto convert_v = [&](float sc) {
+            // V: scaled, then [V_hi | V_lo].  The previous head's P V products must have completed before V16 is overwritten.
+            if (it > 0) {
+                wait(&o_done[0], (uint32_t)((it - 1) & 1), 5);
+                if (nq == 2) wait(&o_done[1], (uint32_t)((it - 1) & 1), 5);
+            }
             for (int t = 0; t < nq; ++t) {
                 const int key = t * kTile + rloc;
                 const uint8_t *src = v_raw + t * kTileBytes;
@@ -525,7 +534,13 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
             }
         
         };
-        if (grp == 2) convert_v();
+        // (Letting the conversion wait until the group has swept its score tile for the row maxima, so that the group at
+        // the other end of the exchange is not held up by it, measured slower: 15.42 against 15.30 us.)
+        if (grp == 2) {
+            if (!v_scale_known) v_sc = v_scale(it);
+            v_scale_known = false;
+            convert_v(v_sc);
+        }
 
         // ---- score tiles of this group --------------------------------------------------------------------
         // Per tile: row maximum (first sweep over the tile's columns in TMEM), exchange of the maximum with
@@ -664,6 +679,10 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
         // the next head's K and Q have landed by now (their copies were issued when this head's Q K^T had
         // completed): converting them here lets its Q K^T run while this head's output is stored
         if (!PROBS && grp < 2 && hd + (int)gridDim.x < BH) convert_kq(it + 1);
+        if (!PROBS && grp == 2 && hd + (int)gridDim.x < BH) {
+            v_sc = v_scale(it + 1);                  // the next head's raw V has landed (its copies were issued when this head's V had been converted)
+            v_scale_known = true;
+        }
         // ---- output: (P_hi V_hi + corrections) / (l * V's scale); the groups of a query tile share its columns ----
 #pragma unroll 1
         for (int ji = 0; ji < njobs; ++ji) {
