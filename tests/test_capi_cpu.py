@@ -95,6 +95,34 @@ def test_bad_arguments_are_rejected_before_any_cuda_call():
     assert lib.hipgpt_mha_decode(None, None, None, None, None, 0, 1, 1, 32, 5, 4, None) == _capi.ERR_BAD_ARG  # ctx > cap
 
 
+def test_projection_and_sharding_entry_points_check_their_arguments_first():
+    """The entry points added beside attention (tensor-core projections, fused dropout + residual, the sharded driver's
+    transports) refuse bad sizes, NULL pointers and in-place use before any CUDA call, so on a box without a GPU too."""
+    lib = _capi.lib()
+    one = (C.c_float * 4)()
+    p = C.cast(one, C.c_void_p)
+    assert lib.hipgpt_matmul_tc(None, None, None, None, -1, 4, 4, None) == _capi.ERR_BAD_ARG
+    assert lib.hipgpt_matmul_tc(None, None, None, None, 4, 4, 4, None) == _capi.ERR_NULL
+    assert lib.hipgpt_matmul_tc(None, None, None, None, 0, 4, 4, None) == 0                       # nothing to do
+    assert lib.hipgpt_matmul_tc(p, p, None, p, 2, 2, 2, None) == _capi.ERR_UNSUPPORTED             # in place
+    assert b"in place" in lib.hipgpt_last_error()
+    h = C.c_void_p()
+    assert lib.hipgpt_matmul_tc_prepare(None, 4, 4, C.byref(h), None) == _capi.ERR_NULL
+    assert lib.hipgpt_matmul_tc_prepare(p, 0, 4, C.byref(h), None) == _capi.ERR_BAD_ARG
+    assert lib.hipgpt_matmul_tc_prepared(p, None, None, p, 2, None) == _capi.ERR_NULL
+    assert lib.hipgpt_ln_matmul_tc(p, None, None, p, None, p, 2, 2, 2, None) == _capi.ERR_NULL      # gamma and beta are required
+    assert lib.hipgpt_ln_matmul_tc(p, p, p, p, None, p, 2, 0, 2, None) == _capi.ERR_BAD_ARG         # a layer norm over nothing
+    lib.hipgpt_matmul_tc_release(None)                                                              # accepted, like free(NULL)
+    assert lib.hipgpt_dropout_residual(p, p, p, None, C.c_float(1.0), 1, 4, None) == _capi.ERR_BAD_ARG   # p must be below 1
+    assert lib.hipgpt_dropout_residual(None, p, p, None, C.c_float(0.1), 1, 4, None) == _capi.ERR_NULL
+    assert lib.hipgpt_dropout_residual(None, None, None, None, C.c_float(0.1), 0, 4, None) == 0
+    assert lib.hipgpt_mha_forward_sharded(None, p, p, p, p, 8, 4, 32, 1, 0, 4, 1, 0, None) == _capi.ERR_NULL       # no context
+    assert lib.hipgpt_shard_output_buffer(None, 16, C.byref(h)) == _capi.ERR_NULL
+    b0, b1 = C.c_int(), C.c_int()
+    assert lib.hipgpt_shard_chunk_range(10, 2, 0, 3, 0, C.byref(b0), C.byref(b1)) == _capi.ERR_BAD_ARG      # 10 batches do not split into 2 x 3 runs
+    assert lib.hipgpt_shard_chunk_range(12, 2, 1, 3, 2, C.byref(b0), C.byref(b1)) == 0 and (b0.value, b1.value) == (10, 12)
+
+
 def test_decode_scratch_size_query():
     lib = _capi.lib()
     assert lib.hipgpt_mha_decode_scratch_bytes(8, 8, 32, 256) > 0
