@@ -303,6 +303,18 @@ mha_head_kernel(const __grid_constant__ HeadMaps maps, float *__restrict__ O, fl
                     wait(&cv_q[q], par, 2);
                     tc_fence_after();
                     issue_qk(q, k, t);
+                    // The next head's tiles are asked into L2 now: this head's operands have landed, so the memory system is
+                    // idle, and the copies that fetch them once this head's Q K^T products have completed (all SMs within the
+                    // same microsecond again) then hit L2.
+                    if (CAUSAL && t == 0 && has_next && !PROBS && lane == 0) {
+                        const int nb = next / H, nc0 = (next % H) * 32;
+                        for (int u = 0; u < nq; ++u) {
+                            tma_prefetch_3d(&maps.k, nc0, u * kTile, nb);
+                            tma_prefetch_3d(&maps.q, nc0, u * kTile, nb);
+                        }
+                        for (int u = 0; u < nq; ++u) tma_prefetch_3d(&maps.v, nc0, u * kTile, nb);
+                    }
+                    __syncwarp();
                 }
                 // ---- the operands' range (see g_head_notice) ------------------------------------------
                 if (lane == 0) {
