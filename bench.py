@@ -200,7 +200,7 @@ def cpu_leg(cfg, causal, seconds, steps=None, warmup=0):
     return tf, info
 
 
-def projections_leg(lib):
+def projections_leg(lib, fma_peak=None):
     """The projections either side of attention at the default workload's shapes (QKV: [B*S, E] x [E, 3E]; output: [B*S, E] x
     [E, E], bias added): the exact-order kernel (bit-identical to the reference's summation order) and the tensor-core kernel
     (fp32-grade), CUDA-event time per call over input batches that together exceed L2."""
@@ -208,6 +208,11 @@ def projections_leg(lib):
     c = synth.CONFIGS["c2"]
     M, E = c["B"] * c["S"], c["H"] * c["D"]
     st = torch.cuda.current_stream().cuda_stream
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        peaks = {}
+    tf32_peak = float(peaks.get("bf16_tflops", 1590.0)) / 2.0
     out = {}
     for name, (N, K) in (("qkv", (E, 3 * E)), ("out", (E, E))):
         sets = 8
@@ -239,7 +244,16 @@ def projections_leg(lib):
             e1.record()
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) / reps / sets * 1e3
-            res[label] = {"us_per_call": us, "tflops": 2.0 * M * N * K / us / 1e6}
+            tfl = 2.0 * M * N * K / us / 1e6
+            res[label] = {"us_per_call": us, "tflops": tfl}
+            # what bounds each kernel: the tensor pipe for the fp16-piece product (three fp16 products per product = 1.5
+            # products at the TF32 rate, which is half the measured dense bf16 rate), the FFMA pipe for the exact order
+            if fn is not lib.hipgpt_matmul:
+                res[label]["roofline"] = {"bound": "tensor", "achieved": 1.5 * tfl, "peak": tf32_peak, "unit": "TFLOP/s", "frac": 1.5 * tfl / tf32_peak,
+                                          "peak_source": "half of MEASURED_PEAKS.json bf16_tflops" + ("" if peaks else " (fallback)")}
+            elif fma_peak:
+                res[label]["roofline"] = {"bound": "fma", "achieved": tfl, "peak": fma_peak, "unit": "TFLOP/s", "frac": tfl / fma_peak,
+                                          "peak_source": "fp32 FFMA loop timed in this run"}
         out[name] = res
         torch.cuda.synchronize()
         lib.hipgpt_matmul_tc_release(packed)
@@ -720,7 +734,7 @@ def run_ours(args):
         _, info = cpu_leg(cfg, args.causal, seconds=args.cpu_seconds)
         line["cpu_baseline"] = info
         line["decode"] = decode_leg()
-        line["projections"] = projections_leg(lib)
+        line["projections"] = projections_leg(lib, fma_peak)
         line["attention_block"] = attention_block_leg(lib)
     if rank == 0:
         emit(line)
